@@ -1,0 +1,45 @@
+// C entry points of the kernel library (all launch on the given stream and
+// return 0 on success, a negative code when an argument is rejected or a launch
+// fails). Pointers are device pointers unless stated otherwise. `status` is an
+// int32[8] device buffer that kernels use to report bounded-wait timeouts and
+// failed index checks instead of trapping; see common/ptx.cuh.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- gemm_bf16.cu
+size_t ab200_linear_bf16_workspace_bytes(int M, int N, int K);
+int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                      long long ldo, int M, int N, int K, const void* bias, const void* residual,
+                      long long ldr, int act, void* workspace, size_t workspace_bytes,
+                      int force_splits, int* status, cudaStream_t stream);
+int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long ldw, void* out,
+                       long long ldo, int M, int N, int K, int* status, cudaStream_t stream);
+
+// ---- elementwise.cu
+int ab200_embedding(const void* ids, const void* table, void* out, long long T, int hidden,
+                    long long vocab, long long vocab_start, cudaStream_t stream);
+int ab200_rmsnorm(const void* x, long long ldx, void* residual, const void* weight, void* y,
+                  long long ldy, long long T, int hidden, float eps, cudaStream_t stream);
+int ab200_layernorm(const void* x, const void* residual, const void* gamma, const void* beta,
+                    void* y, long long T, int hidden, float eps, cudaStream_t stream);
+int ab200_silu_mul(const void* x, void* out, long long T, int inter, cudaStream_t stream);
+int ab200_rope_cache(void* qkv, long long ld, const void* positions, const void* slots,
+                     const void* inv_freq, void* k_cache, void* v_cache, long long T, int Hq,
+                     int Hkv, int D, int block_size, long long num_slots, int rotate_q, int* status,
+                     cudaStream_t stream);
+int ab200_gather_rows(const void* src, long long ld, const void* idx, void* dst, long long R,
+                      int hidden, cudaStream_t stream);
+int ab200_argmax_sample(const void* logits, int dtype, long long ld, long long B, int V,
+                        const void* temperature, const void* seeds, void* out_ids, void* out_vals,
+                        long long index_offset, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,546 @@
+// Flash attention for sm_100a on tensor memory: one kernel serves chunked
+// prefill, decode (with split-KV) and the bidirectional encoder.
+//
+// A CTA owns 128 "rows": 128/G consecutive query tokens times the G query heads
+// that share one KV head (GQA packing), so K and V are fetched once per KV head.
+// Per 128-key tile:  S = Q K^T  is a tcgen05.mma into TMEM (K-major operands
+// straight from TMA, 128B swizzle); four softmax warps read their own row of S
+// with tcgen05.ld, keep the running max/sum, write P (bf16) into swizzled shared
+// memory; P V is a second tcgen05.mma whose B operand is the V tile in its
+// natural [key][d] layout (an MN-major descriptor), so nothing is transposed.
+// S and PV are double-buffered in TMEM (4 x 128 columns): QK^T of tile j+1 runs
+// on the tensor core while the softmax warps work on tile j. The output
+// accumulator stays in registers (one row per thread) and is rescaled on the fly.
+//
+// K/V come either from a paged cache [num_blocks, Hkv, block_size, D] through a
+// block table (one TMA box per block) or from a contiguous [T, Hkv*D]-strided
+// tensor (encoder). With several KV splits per sequence each CTA writes a
+// normalised fp32 partial and its log-sum-exp; attention_merge_kernel folds them.
+//
+// The reference obtains attention from vLLM's FlashAttention wrappers
+// (arctic_inference/vllm/attention/flash_attn_forest_cascade.py:1004-1026,
+// 1725-1796), which on this architecture run the sm_80 mma.sync kernels.
+
+#include <float.h>
+#include <math.h>
+
+#include "api.h"
+#include "common/ptx.cuh"
+#include "common/tensormap.h"
+
+namespace ab200 {
+
+constexpr int kAttThreads = 192;  // 4 softmax warps + TMA warp + MMA warp
+constexpr int kTileKeys = 128;
+
+struct AttnArgs {
+  const int* work;          // [num_work][8], see AttnWork
+  const int* block_tables;  // [num_seqs][max_blocks] (paged mode)
+  int max_blocks;
+  int block_size;  // 0 = contiguous K/V
+  int G;           // query heads per KV head
+  int Hq, Hkv;
+  int causal;
+  float scale_log2;  // softmax scale * log2(e)
+  float scale;
+  __nv_bfloat16* out;  // [T, Hq*D], row stride ldo
+  long long ldo;
+  float* o_part;    // [max_splits][T][Hq][D]
+  float* lse_part;  // [max_splits][T][Hq]
+  float* lse_out;   // optional [T][Hq]
+  long long T;
+  int* status;
+};
+
+// work item layout (int32 x 8)
+//  0 seq index   1 first query token (row of q/out)   2 number of query tokens (0 = no-op)
+//  3 position of the first query token   4 kv_start   5 kv_end (exclusive)
+//  6 split index   7 number of splits of this sequence
+//  In contiguous mode field 0 is the row of the sequence's first key in the K/V tensor.
+
+template <int D>
+__global__ void __launch_bounds__(kAttThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p) {
+  constexpr int kHalves = D / 64;
+  constexpr uint32_t kQBytes = 128 * D * 2;
+  constexpr uint32_t kKVBytes = kTileKeys * D * 2;
+  constexpr uint32_t kPBytes = 128 * kTileKeys * 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + kQBytes;          // 2 stages
+  const uint32_t sV = sK + 2 * kKVBytes;     // 2 stages
+  const uint32_t sP = sV + 2 * kKVBytes;
+  uint8_t* pP = smem + kQBytes + 4 * kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQBytes + 4 * kKVBytes + kPBytes);
+  const uint32_t bb = smem_u32(bars);
+  // barrier indices
+  const uint32_t q_full = bb;
+  auto k_full = [&](int s) { return bb + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bb + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bb + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bb + 8u * (7 + s); };
+  auto s_full = [&](int s) { return bb + 8u * (9 + s); };
+  auto s_empty = [&](int s) { return bb + 8u * (11 + s); };
+  auto o_full = [&](int s) { return bb + 8u * (13 + s); };
+  auto o_empty = [&](int s) { return bb + 8u * (15 + s); };
+  const uint32_t p_full = bb + 8u * 17;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int* wk = p.work + (long long)blockIdx.x * 8;
+  const int seq = wk[0];
+  const int q_tok0 = wk[1];
+  const int n_q_tok = wk[2];
+  if (n_q_tok <= 0) return;  // padding entry of a fixed-size work list
+  const int q_pos0 = wk[3];
+  const int kv_start = wk[4];
+  int kv_end = wk[5];
+  const int split = wk[6];
+  const int num_splits = wk[7];
+  const int kvh = blockIdx.y;
+  if (p.causal) kv_end = min(kv_end, q_pos0 + n_q_tok);
+  const int n_tiles = kv_end > kv_start ? (kv_end - kv_start + kTileKeys - 1) / kTileKeys : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+      mbar_init(s_full(s), 1);
+      mbar_init(s_empty(s), 4);
+      mbar_init(o_full(s), 1);
+      mbar_init(o_empty(s), 4);
+    }
+    mbar_init(p_full, 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  // Stale shared memory may hold non-finite bit patterns; keys that are never
+  // loaded (past the end of a sequence) are multiplied by P = 0 and must be finite.
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem + kQBytes);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < (int)(4 * kKVBytes / 16); i += kAttThreads) z[i] = zero;
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;        // S buffers at columns 0, 128
+  const uint32_t tO = tmem_base + 256;  // PV buffers at columns 256, 384
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, kQBytes);
+      for (int h = 0; h < kHalves; ++h)
+        tma_load_4d(sQ + h * 16384u, &tmap_q, q_full, h * 64, 0, kvh, q_tok0);
+    }
+    const int bs = p.block_size;
+    const int blocks_per_tile = bs > 0 ? kTileKeys / bs : 0;
+    const int* bt = bs > 0 ? p.block_tables + (long long)seq * p.max_blocks : nullptr;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      const int key0 = kv_start + j * kTileKeys;
+      const int nkeys = min(kTileKeys, kv_end - key0);
+      for (int kv = 0; kv < 2; ++kv) {
+        const uint32_t full = kv == 0 ? k_full(st) : v_full(st);
+        const uint32_t empty = kv == 0 ? k_empty(st) : v_empty(st);
+        const uint32_t dst = (kv == 0 ? sK : sV) + (uint32_t)st * kKVBytes;
+        const CUtensorMap* tm = kv == 0 ? &tmap_k : &tmap_v;
+        if (!mbar_wait(empty, ph ^ 1u, abort_flag, p.status, 500 + kv * 10 + st, j)) {
+          ok = false;
+          break;
+        }
+        if (bs > 0) {
+          const int nblk = (nkeys + bs - 1) / bs;
+          if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(nblk * bs * D * 2));
+          __syncwarp();
+          if (lane < nblk) {
+            const int bid = bt[key0 / bs + lane];
+            for (int h = 0; h < kHalves; ++h)
+              tma_load_4d(dst + h * 16384u + (uint32_t)(lane * bs) * 128u, tm, full, h * 64, 0, kvh,
+                          bid);
+          }
+        } else {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(full, kKVBytes);
+            for (int h = 0; h < kHalves; ++h)
+              tma_load_3d(dst + h * 16384u, tm, full, h * 64, kvh, seq + key0);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t idesc_s = make_idesc(128, kTileKeys, 1, 1, 0, 0);
+      const uint32_t idesc_pv = make_idesc(128, D, 1, 1, 0, 1);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 600, 0);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(k_full(st), ph, abort_flag, p.status, 610 + st, j)) return false;
+        if (!mbar_wait(s_empty(st), ph ^ 1u, abort_flag, p.status, 620 + st, j)) return false;
+        tc_fence_after();
+        const uint32_t kb = sK + (uint32_t)st * kKVBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t qd = make_desc_kmajor_sw128(sQ + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
+          const uint64_t kd = make_desc_kmajor_sw128(kb + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
+          umma_f16_ss(tS + (uint32_t)st * 128u, qd, kd, idesc_s, k > 0 ? 1u : 0u);
+        }
+        tc_commit(k_empty(st));
+        tc_commit(s_full(st));
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(v_full(st), ph, abort_flag, p.status, 630 + st, j)) return false;
+        if (!mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.status, 640, j)) return false;
+        if (!mbar_wait(o_empty(st), ph ^ 1u, abort_flag, p.status, 650 + st, j)) return false;
+        tc_fence_after();
+        const uint32_t vb = sV + (uint32_t)st * kKVBytes;
+#pragma unroll
+        for (int k = 0; k < kTileKeys / 16; ++k) {
+          const uint64_t pd = make_desc_kmajor_sw128(sP + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
+          const uint64_t vd = make_desc_mnmajor_sw128(vb, 16384u) + 128u * k;
+          umma_f16_ss(tO + (uint32_t)st * 128u, pd, vd, idesc_pv, k > 0 ? 1u : 0u);
+        }
+        tc_commit(v_empty(st));
+        tc_commit(o_full(st));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);
+        if (ok) ok = issue_pv(j);
+      }
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const int row = warp * 32 + lane;
+    const int tok_local = row / p.G;
+    const int g = row % p.G;
+    const bool valid_row = tok_local < n_q_tok;
+    const int q_pos = q_pos0 + tok_local;
+    const int limit = p.causal ? min(q_pos, kv_end - 1) : kv_end - 1;  // last visible key
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    float m = -INFINITY;
+    float l = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    uint8_t* p_row = pP + (size_t)row * 128;
+    bool ok = true;
+
+    auto fold_pv = [&](int jj, float alpha) -> bool {
+      const int st = jj & 1;
+      const uint32_t ph = (uint32_t)(jj >> 1) & 1u;
+      // o_full was already waited for by the caller
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(tO + (uint32_t)st * 128u + lane_off + (uint32_t)c * 32u, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) o[c * 32 + t] = (o[c * 32 + t] + __uint_as_float(r[t])) * alpha;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_empty(st));
+      (void)ph;
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      const int key0 = kv_start + j * kTileKeys;
+      if (!mbar_wait(s_full(st), ph, abort_flag, p.status, 700 + st, j)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t ts = tS + (uint32_t)st * 128u + lane_off;
+      const bool need_mask = key0 + kTileKeys - 1 > limit;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(ts + (uint32_t)c * 32u, r);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t)
+            if (key0 + c * 32 + t <= limit) mx = fmaxf(mx, __uint_as_float(r[t]));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(r[t]));
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f((m - m_safe) * p.scale_log2);  // m = -inf -> 0
+      const float neg_ms = -m_safe * p.scale_log2;
+      // P(j) overwrites the buffer PV(j-1) reads from: wait for that product first.
+      if (j > 0) {
+        if (!mbar_wait(o_full((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abort_flag, p.status,
+                       710, j)) {
+          ok = false;
+          break;
+        }
+      }
+      // pass 2: probabilities -> swizzled shared memory
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(ts + (uint32_t)c * 32u, r);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          float e = exp2f(fmaf(__uint_as_float(r[t]), p.scale_log2, neg_ms));
+          if (need_mask && key0 + c * 32 + t > limit) e = 0.f;
+          pv[t] = e;
+          lsum += e;
+        }
+        uint8_t* line = p_row + (size_t)(c >> 1) * 16384;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 q;
+          q.x = pack_bf16x2(pv[8 * i + 0], pv[8 * i + 1]);
+          q.y = pack_bf16x2(pv[8 * i + 2], pv[8 * i + 3]);
+          q.z = pack_bf16x2(pv[8 * i + 4], pv[8 * i + 5]);
+          q.w = pack_bf16x2(pv[8 * i + 6], pv[8 * i + 7]);
+          const int chunk = ((c & 1) * 4 + i) ^ (row & 7);
+          *reinterpret_cast<uint4*>(line + chunk * 16) = q;
+        }
+      }
+      l = l * alpha + lsum;
+      m = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty(st));
+        mbar_arrive(p_full);
+      }
+      if (j > 0) fold_pv(j - 1, alpha);
+    }
+    if (ok && n_tiles > 0) {
+      const int jl = n_tiles - 1;
+      if (mbar_wait(o_full(jl & 1), (uint32_t)(jl >> 1) & 1u, abort_flag, p.status, 720, jl)) {
+        fold_pv(jl, 1.0f);
+      } else {
+        ok = false;
+      }
+    }
+    if (ok && valid_row) {
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const long long tok = (long long)q_tok0 + tok_local;
+      const int head = kvh * p.G + g;
+      const float lse = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
+      if (num_splits <= 1) {
+        __nv_bfloat16* dst = p.out + tok * p.ldo + (long long)head * D;
+#pragma unroll
+        for (int i = 0; i < D; i += 8) {
+          uint4 q;
+          q.x = pack_bf16x2(o[i] * inv_l, o[i + 1] * inv_l);
+          q.y = pack_bf16x2(o[i + 2] * inv_l, o[i + 3] * inv_l);
+          q.z = pack_bf16x2(o[i + 4] * inv_l, o[i + 5] * inv_l);
+          q.w = pack_bf16x2(o[i + 6] * inv_l, o[i + 7] * inv_l);
+          *reinterpret_cast<uint4*>(dst + i) = q;
+        }
+        if (p.lse_out) p.lse_out[tok * p.Hq + head] = lse;
+      } else {
+        float* dst = p.o_part + (((long long)split * p.T + tok) * p.Hq + head) * D;
+#pragma unroll
+        for (int i = 0; i < D; i += 4)
+          *reinterpret_cast<float4*>(dst + i) =
+              make_float4(o[i] * inv_l, o[i + 1] * inv_l, o[i + 2] * inv_l, o[i + 3] * inv_l);
+        p.lse_part[((long long)split * p.T + tok) * p.Hq + head] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Fold split-KV partials: out = sum_s w_s O_s / sum_s w_s, w_s = exp(lse_s - max lse).
+// tok_splits[t] = number of splits that cover token t (<= 1: nothing to do).
+template <int D>
+__global__ void attention_merge_kernel(const float* __restrict__ o_part,
+                                       const float* __restrict__ lse_part,
+                                       const int* __restrict__ tok_splits, long long T, int Hq,
+                                       __nv_bfloat16* __restrict__ out, long long ldo,
+                                       float* __restrict__ lse_out) {
+  const long long tok = blockIdx.x;
+  const int ns = tok_splits[tok];
+  if (ns <= 1) return;
+  for (int idx = threadIdx.x; idx < Hq * (D / 4); idx += blockDim.x) {
+    const int head = idx / (D / 4);
+    const int d4 = (idx % (D / 4)) * 4;
+    float mx = -INFINITY;
+    for (int s = 0; s < ns; ++s) mx = fmaxf(mx, lse_part[((long long)s * T + tok) * Hq + head]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+    for (int s = 0; s < ns; ++s) {
+      const float lse = lse_part[((long long)s * T + tok) * Hq + head];
+      const float w = (lse == -INFINITY) ? 0.f : __expf(lse - mx);
+      const float4 v =
+          *reinterpret_cast<const float4*>(o_part + (((long long)s * T + tok) * Hq + head) * D + d4);
+      acc.x += w * v.x;
+      acc.y += w * v.y;
+      acc.z += w * v.z;
+      acc.w += w * v.w;
+      wsum += w;
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    uint2 q;
+    q.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    q.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + tok * ldo + (long long)head * D + d4) = q;
+    if (lse_out && d4 == 0) lse_out[tok * Hq + head] = wsum > 0.f ? mx + logf(wsum) : -INFINITY;
+  }
+}
+
+template <int D>
+static int launch_attention(const void* q, long long ldq, const void* k, const void* v,
+                            long long ld_kv, long long num_blocks, int block_size,
+                            const int* block_tables, int max_blocks, const int* work, int num_work,
+                            const int* tok_splits, int max_splits, long long T, int Hq, int Hkv,
+                            int causal, float scale, void* out, long long ldo, float* o_part,
+                            float* lse_part, float* lse_out, int* status, cudaStream_t stream) {
+  const int G = Hq / Hkv;
+  if (G <= 0 || Hq % Hkv || 128 % G) return -2;
+  if (block_size > 0 && (kTileKeys % block_size || block_size < 8)) return -2;
+  static bool attr_set = false;
+  const size_t smem = 128 * D * 2 + 4 * (size_t)kTileKeys * D * 2 + 128 * kTileKeys * 2 + 256 + 1024;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  CUtensorMap tq, tk, tv;
+  {
+    // q viewed as [T][Hkv][G][D]
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)G, (uint64_t)Hkv, (uint64_t)T};
+    const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)G * D * 2, (uint64_t)ldq * 2};
+    const uint32_t box[4] = {64, (uint32_t)G, 1, (uint32_t)(128 / G)};
+    if (make_tmap_nd(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box) != 0) return -4;
+  }
+  if (block_size > 0) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)block_size, (uint64_t)Hkv, (uint64_t)num_blocks};
+    const uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)block_size * D * 2,
+                                 (uint64_t)Hkv * block_size * D * 2};
+    const uint32_t box[4] = {64, (uint32_t)block_size, 1, 1};
+    if (make_tmap_nd(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box) != 0) return -4;
+    if (make_tmap_nd(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box) != 0) return -4;
+  } else {
+    // contiguous: k/v rows are tokens with stride ld_kv, heads packed [Hkv][D]
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)num_blocks /* = rows */};
+    const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)ld_kv * 2};
+    const uint32_t box[3] = {64, 1, (uint32_t)kTileKeys};
+    if (make_tmap_nd(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box) != 0) return -4;
+    if (make_tmap_nd(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box) != 0) return -4;
+  }
+  AttnArgs a;
+  a.work = work;
+  a.block_tables = block_tables;
+  a.max_blocks = max_blocks;
+  a.block_size = block_size;
+  a.G = G;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.causal = causal;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.ldo = ldo;
+  a.o_part = o_part;
+  a.lse_part = lse_part;
+  a.lse_out = lse_out;
+  a.T = T;
+  a.status = status;
+  dim3 grid((unsigned)num_work, (unsigned)Hkv);
+  attention_kernel<D><<<grid, kAttThreads, smem, stream>>>(tq, tk, tv, a);
+  if (cudaGetLastError() != cudaSuccess) return -5;
+  if (max_splits > 1) {
+    attention_merge_kernel<D><<<(unsigned)T, 128, 0, stream>>>(
+        o_part, lse_part, tok_splits, T, Hq, reinterpret_cast<__nv_bfloat16*>(out), ldo, lse_out);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+  }
+  return 0;
+}
+
+}  // namespace ab200
+
+using namespace ab200;
+
+extern "C" {
+
+// q: [T, Hq*D] rows with stride ldq. Paged mode (block_size > 0): k/v are caches
+// [num_blocks, Hkv, block_size, D]. Contiguous mode (block_size == 0): k/v are
+// [num_blocks(=rows), Hkv*D] with row stride ld_kv. `work` is an int32 [num_work, 8]
+// device array (layout above). With max_splits > 1, o_part/lse_part/tok_splits
+// must be given: o_part fp32 [max_splits, T, Hq, D], lse_part fp32 [max_splits, T, Hq].
+int ab200_attention(const void* q, long long ldq, const void* k, const void* v, long long ld_kv,
+                    long long num_blocks, int block_size, const void* block_tables, int max_blocks,
+                    const void* work, int num_work, const void* tok_splits, int max_splits,
+                    long long T, int Hq, int Hkv, int D, int causal, float scale, void* out,
+                    long long ldo, void* o_part, void* lse_part, void* lse_out, int* status,
+                    cudaStream_t stream) {
+  if (num_work <= 0 || T <= 0) return 0;
+  if ((ldq % 8) || (ldo % 8) || (ld_kv % 8)) return -2;
+  if (max_splits > 1 && (o_part == nullptr || lse_part == nullptr || tok_splits == nullptr)) return -2;
+  if (D == 128)
+    return launch_attention<128>(q, ldq, k, v, ld_kv, num_blocks, block_size,
+                                 reinterpret_cast<const int*>(block_tables), max_blocks,
+                                 reinterpret_cast<const int*>(work), num_work,
+                                 reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv,
+                                 causal, scale, out, ldo, reinterpret_cast<float*>(o_part),
+                                 reinterpret_cast<float*>(lse_part),
+                                 reinterpret_cast<float*>(lse_out), status, stream);
+  if (D == 64)
+    return launch_attention<64>(q, ldq, k, v, ld_kv, num_blocks, block_size,
+                                reinterpret_cast<const int*>(block_tables), max_blocks,
+                                reinterpret_cast<const int*>(work), num_work,
+                                reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv,
+                                causal, scale, out, ldo, reinterpret_cast<float*>(o_part),
+                                reinterpret_cast<float*>(lse_part),
+                                reinterpret_cast<float*>(lse_out), status, stream);
+  return -2;
+}
+
+}  // extern "C"

@@ -1,0 +1,586 @@
+// bf16 linear layer  out[M,N] = x[M,K] * w[N,K]^T  (+bias)(+residual)(activation)
+// for sm_100a: a persistent, warp-specialised kernel in which one thread issues
+// tcgen05.mma (UMMA 128 x bn x 16, fp32 accumulators in tensor memory), one
+// thread feeds a ring of 128B-swizzled shared-memory stages with TMA, and four
+// epilogue warps drain the double-buffered TMEM accumulators with tcgen05.ld.
+//
+// Two orientations share the kernel:
+//   * token-major  (M > 256): A operand = x tile (128 tokens), B = w tile (bn features)
+//   * feature-major (M <= 256, decode): A operand = w tile (128 features), B = all
+//     tokens (bn = M rounded up to 16); the accumulator holds out^T and the
+//     epilogue stores it transposed. Every SM then streams weights even when
+//     only a handful of tokens are in flight, and split-K adds parallelism when
+//     N/128 alone cannot fill 148 SMs. Split-K partial sums go to an fp32
+//     scratch buffer supplied by the caller and are folded by a second kernel.
+//
+// The reference relies on library GEMMs for these layers (vLLM linear layers
+// reached from arctic_inference/vllm/swiftkv/llama_swiftkv.py:165-202).
+
+#include <math.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "common/ptx.cuh"
+#include "common/tensormap.h"
+
+namespace ab200 {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;  // bf16 elements: one 128-byte swizzle atom per row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
+
+struct GemmArgs {
+  int rows_a, rows_b, K;
+  int bn, stages, splits, kblocks_per_split, kblocks_total;
+  int tiles_a, tiles_b;
+  int transposed;  // 0: out[a_row*ldo + b_row], 1: out[b_row*ldo + a_row]
+  int out_f32;     // 1: write fp32 partial sums (split-K), no bias/residual/activation
+  int act;         // 0 none, 1 gelu (erf)
+  int b_mn_major;  // 1: the B operand is given as [K, rows_b] (rows_b contiguous)
+  uint32_t tmem_cols;
+  long long ldo, ldr, partial_stride;
+  void* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int* status;
+};
+
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t b_bytes = (uint32_t)p.bn * kBlockK * 2;
+  const uint32_t stage_bytes = kABytes + b_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * stage_bytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bars_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bars_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bars_base + 8u * (kMaxStages + s); };
+  auto tfull_bar = [&](int a) { return bars_base + 8u * (2 * kMaxStages + a); };
+  auto tempty_bar = [&](int a) { return bars_base + 8u * (2 * kMaxStages + 2 + a); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t acc_stride = p.tmem_cols / 2;
+
+  const int total_work = p.tiles_a * p.tiles_b * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int tile_a = w % p.tiles_a;
+        const int rest = w / p.tiles_a;
+        const int tile_b = rest % p.tiles_b;
+        const int split = rest / p.tiles_b;
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 100 + stage, kb)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+          const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes;
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, tile_a * kBlockM);
+          if (!p.b_mn_major) {
+            tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * kBlockK, tile_b * p.bn);
+          } else {
+            // [64 k-rows][64 n] boxes, one per 64-wide atom along N
+            for (int j = 0; j < p.bn / 64; ++j)
+              tma_load_2d(a_dst + kABytes + (uint32_t)j * 8192u, &tmap_b, full_bar(stage),
+                          tile_b * p.bn + j * 64, kb * kBlockK);
+          }
+          ++issued;
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Unwinding: give copies that were already issued a short time to land.
+        const int pending = (int)min((long long)p.stages, issued);
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) {
+            s = p.stages - 1;
+            ph ^= 1u;
+          }
+          mbar_drain(full_bar(s), ph);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      const uint32_t idesc =
+          make_idesc(kBlockM, (uint32_t)p.bn, 1, 1, 0, p.b_mn_major ? 1u : 0u);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int split = (w / p.tiles_a) / p.tiles_b;
+        const int kb0 = split * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 200 + acc, w)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * acc_stride;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 300 + stage, kb)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + (uint32_t)stage * stage_bytes;
+          const uint64_t a_desc = make_desc_kmajor_sw128(a_addr);
+          const uint64_t b_desc = p.b_mn_major ? make_desc_mnmajor_sw128(a_addr + kABytes, 8192u)
+                                               : make_desc_kmajor_sw128(a_addr + kABytes);
+          // K-major: 16 bf16 (32 bytes) further inside the swizzle atom = +2 in the encoded
+          // address; MN-major: 16 rows of 128 bytes further = +128.
+          const uint64_t b_step = p.b_mn_major ? 128u : 2u;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            umma_f16_ss(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + b_step * (uint64_t)k, idesc,
+                        (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // --------------------------------- epilogue --------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int row = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      const int tile_a = w % p.tiles_a;
+      const int rest = w / p.tiles_a;
+      const int tile_b = rest % p.tiles_b;
+      const int split = rest / p.tiles_b;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 400 + acc, w)) break;
+      tc_fence_after();
+      const uint32_t t_addr =
+          tmem_base + (uint32_t)acc * acc_stride + ((uint32_t)(quad * 32) << 16);
+      const long long a_row = (long long)tile_a * kBlockM + row;
+      const bool row_ok = a_row < p.rows_a;
+      const long long b0 = (long long)tile_b * p.bn;
+
+      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+        uint32_t r[16];
+        __syncwarp();
+        tmem_ld_x16(t_addr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        float v[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) v[t] = __uint_as_float(r[t]);
+        if (!row_ok) continue;
+        if (p.out_f32) {
+          float* o = reinterpret_cast<float*>(p.out) + (long long)split * p.partial_stride;
+          if (!p.transposed) {
+            float* dst = o + a_row * p.ldo + b0 + c0;
+#pragma unroll
+            for (int t = 0; t < 16; t += 4) {
+              if (b0 + c0 + t + 4 <= p.rows_b)
+                *reinterpret_cast<float4*>(dst + t) = make_float4(v[t], v[t + 1], v[t + 2], v[t + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              const long long b_row = b0 + c0 + t;
+              if (b_row < p.rows_b) o[b_row * p.ldo + a_row] = v[t];
+            }
+          }
+          continue;
+        }
+        if (!p.transposed) {
+          const long long col = b0 + c0;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int t = 0; t < 16; ++t)
+              if (col + t < p.rows_b) v[t] += __bfloat162float(p.bias[col + t]);
+          }
+          if (p.act == 1) {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) v[t] = gelu_erf(v[t]);
+          }
+          if (p.residual != nullptr) {
+            const __nv_bfloat16* rs = p.residual + a_row * p.ldr + col;
+#pragma unroll
+            for (int t = 0; t < 16; t += 8) {
+              if (col + t + 8 <= p.rows_b) {
+                const uint4 q = *reinterpret_cast<const uint4*>(rs + t);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const float2 f = __bfloat1622float2(h[u]);
+                  v[t + 2 * u] += f.x;
+                  v[t + 2 * u + 1] += f.y;
+                }
+              }
+            }
+          }
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + a_row * p.ldo + col;
+#pragma unroll
+          for (int t = 0; t < 16; t += 8) {
+            if (col + t + 8 <= p.rows_b) {
+              uint4 q;
+              q.x = pack_bf16x2(v[t], v[t + 1]);
+              q.y = pack_bf16x2(v[t + 2], v[t + 3]);
+              q.z = pack_bf16x2(v[t + 4], v[t + 5]);
+              q.w = pack_bf16x2(v[t + 6], v[t + 7]);
+              *reinterpret_cast<uint4*>(dst + t) = q;
+            }
+          }
+        } else {
+          // accumulator holds out^T: this thread owns output feature a_row
+          const float bias = (p.bias != nullptr) ? __bfloat162float(p.bias[a_row]) : 0.f;
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const long long b_row = b0 + c0 + t;
+            if (b_row < p.rows_b) {
+              float x = v[t] + bias;
+              if (p.act == 1) x = gelu_erf(x);
+              if (p.residual != nullptr) x += __bfloat162float(p.residual[b_row * p.ldr + a_row]);
+              o[b_row * p.ldo + a_row] = __float2bfloat16(x);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+// out[m,n] = sum_s partial[s][m,n] (+bias[n]) -> activation -> (+residual[m,n])
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits,
+                                     long long partial_stride, int M, int N,
+                                     __nv_bfloat16* __restrict__ out, long long ldo,
+                                     const __nv_bfloat16* __restrict__ bias,
+                                     const __nv_bfloat16* __restrict__ residual, long long ldr,
+                                     int act) {
+  const long long n4 = N / 4;
+  const long long total = (long long)M * n4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / n4;
+    const long long n = (i % n4) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v =
+          *reinterpret_cast<const float4*>(partial + s * partial_stride + m * (long long)N + n);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      if (bias != nullptr) v[t] += __bfloat162float(bias[n + t]);
+      if (act == 1) v[t] = gelu_erf(v[t]);
+      if (residual != nullptr) v[t] += __bfloat162float(residual[m * ldr + n + t]);
+    }
+    uint2 q;
+    q.x = pack_bf16x2(v[0], v[1]);
+    q.y = pack_bf16x2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(out + m * ldo + n) = q;
+  }
+}
+
+// ------------------------------- host side ---------------------------------
+struct TmapKey {
+  const void* ptr;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= k.ld * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    h ^= k.box_rows * 0x27D4EB2F165667C5ull + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+static int get_tmap_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
+                         uint64_t ld, uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  CUtensorMap m;
+  int rc = make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rows, cols, ld * 2, box_rows,
+                        kBlockK);
+  if (rc != 0) return rc;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+static int pick_stages(int bn) {
+  const int stage_bytes = (int)kABytes + bn * kBlockK * 2;
+  int s = (227 * 1024 - 2048) / stage_bytes;
+  if (s > kMaxStages) s = kMaxStages;
+  return s;
+}
+
+static uint32_t pow2_at_least(uint32_t v) {
+  uint32_t p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+}  // namespace ab200
+
+using namespace ab200;
+
+extern "C" {
+
+// Number of fp32 scratch bytes ab200_linear_bf16 may need for (M, N, K).
+size_t ab200_linear_bf16_workspace_bytes(int M, int N, int K) {
+  if (M > 256) return 0;
+  return (size_t)8 * (size_t)M * (size_t)N * sizeof(float);
+}
+
+// force_splits: 0 = heuristic, >0 = use exactly this split-K factor (feature-major only).
+int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                      long long ldo, int M, int N, int K, const void* bias, const void* residual,
+                      long long ldr, int act, void* workspace, size_t workspace_bytes,
+                      int force_splits, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (N % 8) || (ldx % 8) || (ldw % 8) || (ldo % 8) ||
+      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return -2;
+  if (residual != nullptr && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -2;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return -3;
+    attr_set = true;
+  }
+
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.K = K;
+  a.kblocks_total = (K + kBlockK - 1) / kBlockK;
+  a.status = status;
+  a.act = act;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  a.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  a.ldr = ldr;
+  a.ldo = ldo;
+  a.out = out;
+  a.splits = 1;
+
+  const void* pa;
+  const void* pb;
+  long long lda, ldb;
+  const int sms = num_sms();
+  if (M <= 256) {
+    // feature-major: weights are the 128-row operand, all tokens form the N side
+    a.transposed = 1;
+    a.rows_a = N;
+    a.rows_b = M;
+    a.bn = ((M + 15) / 16) * 16;
+    pa = w;
+    lda = ldw;
+    pb = x;
+    ldb = ldx;
+    a.tiles_a = (N + kBlockM - 1) / kBlockM;
+    a.tiles_b = 1;
+    int splits = force_splits;
+    if (splits <= 0) {
+      splits = 1;
+      while (a.tiles_a * splits * 2 <= sms + sms / 4 && splits < 8 &&
+             a.kblocks_total / (splits * 2) >= 8)
+        splits *= 2;
+    }
+    if (splits > 8) splits = 8;
+    if (splits > a.kblocks_total) splits = a.kblocks_total;
+    if (splits > 1 &&
+        (workspace == nullptr || workspace_bytes < (size_t)splits * M * N * sizeof(float)))
+      splits = 1;
+    a.splits = splits;
+  } else {
+    a.transposed = 0;
+    a.rows_a = M;
+    a.rows_b = N;
+    pa = x;
+    lda = ldx;
+    pb = w;
+    ldb = ldw;
+    a.tiles_a = (M + kBlockM - 1) / kBlockM;
+    const int tiles256 = a.tiles_a * ((N + 255) / 256);
+    a.bn = (tiles256 >= sms && N >= 256) ? 256 : 128;
+    if (N < 128) a.bn = ((N + 15) / 16) * 16;
+    a.tiles_b = (N + a.bn - 1) / a.bn;
+  }
+  a.kblocks_per_split = (a.kblocks_total + a.splits - 1) / a.splits;
+  a.splits = (a.kblocks_total + a.kblocks_per_split - 1) / a.kblocks_per_split;
+  a.stages = pick_stages(a.bn);
+  a.tmem_cols = pow2_at_least(2u * (uint32_t)a.bn);
+
+  void* final_out = out;
+  if (a.splits > 1) {
+    a.out_f32 = 1;
+    a.out = workspace;
+    a.ldo = N;  // partials are stored as [split][M][N] regardless of orientation
+    a.partial_stride = (long long)M * N;
+  }
+
+  CUtensorMap ta, tb;
+  if (get_tmap_bf16(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K, (uint64_t)lda, kBlockM) != 0) return -4;
+  if (get_tmap_bf16(&tb, pb, (uint64_t)a.rows_b, (uint64_t)K, (uint64_t)ldb, (uint32_t)a.bn) != 0)
+    return -4;
+
+  const int total = a.tiles_a * a.tiles_b * a.splits;
+  const int grid = total < sms ? total : sms;
+  const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 1024;
+  gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, a);
+  if (cudaGetLastError() != cudaSuccess) return -5;
+
+  if (a.splits > 1) {
+    const long long total4 = (long long)M * (N / 4);
+    int blocks = (int)((total4 + 255) / 256);
+    if (blocks > sms * 8) blocks = sms * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(
+        reinterpret_cast<const float*>(workspace), a.splits, a.partial_stride, M, N,
+        reinterpret_cast<__nv_bfloat16*>(final_out), ldo,
+        reinterpret_cast<const __nv_bfloat16*>(bias),
+        reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+  }
+  return 0;
+}
+
+
+// out[M,N] = x[M,K] * wt[K,N] with wt row-major (N contiguous): exercises the
+// MN-major shared-memory descriptor for the B operand. N must be a multiple of 64.
+int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long ldw, void* out,
+                       long long ldo, int M, int N, int K, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (N % 64) || (ldx % 8) || (ldw % 8) || (ldo % 8)) return -2;
+  if (cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           227 * 1024) != cudaSuccess)
+    return -3;
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.K = K;
+  a.kblocks_total = (K + kBlockK - 1) / kBlockK;
+  a.kblocks_per_split = a.kblocks_total;
+  a.splits = 1;
+  a.status = status;
+  a.ldo = ldo;
+  a.out = out;
+  a.rows_a = M;
+  a.rows_b = N;
+  a.b_mn_major = 1;
+  a.bn = (N % 128 == 0) ? 128 : 64;
+  a.tiles_a = (M + kBlockM - 1) / kBlockM;
+  a.tiles_b = N / a.bn;
+  a.stages = pick_stages(a.bn);
+  a.tmem_cols = pow2_at_least(2u * (uint32_t)a.bn);
+  CUtensorMap ta, tb;
+  if (get_tmap_bf16(&ta, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, kBlockM) != 0) return -4;
+  if (make_tmap_2d(&tb, wt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)K, (uint64_t)N,
+                   (uint64_t)ldw * 2, 64, 64) != 0)
+    return -4;
+  const int total = a.tiles_a * a.tiles_b;
+  const int sms = num_sms();
+  const int grid = total < sms ? total : sms;
+  const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 1024;
+  gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // extern "C"

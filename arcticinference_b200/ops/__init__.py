@@ -1,0 +1,375 @@
+"""Tensor-level ops of the engine.
+
+CUDA tensors always run the hand-written sm_100a kernels from ``_kernels.so``
+(a missing or unloadable library raises -- there is no silent fallback on a
+GPU). CPU tensors run the PyTorch restatements in :mod:`.reference`, which are
+also the oracles of the numerics tests.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from . import reference as ref
+
+__all__ = [
+    "linear", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "rope_cache",
+    "gather_rows", "argmax_sample", "AttentionMetadata", "build_attention_metadata",
+    "attention", "attention_contiguous", "check_status", "count_launches", "launch_counter",
+]
+
+
+class _LaunchCounter:
+    """Counts launches of this package's own kernels (used by bench.py)."""
+
+    def __init__(self):
+        self.n = 0
+
+    def add(self, k: int = 1):
+        self.n += k
+
+
+launch_counter = _LaunchCounter()
+
+
+def count_launches() -> int:
+    return launch_counter.n
+
+
+def _native():
+    from . import native
+    return native
+
+
+def check_status(device=None):
+    _native().check_status(device)
+
+
+_ACT = {None: 0, "none": 0, "gelu": 1}
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=None, out=None,
+           force_splits: int = 0) -> torch.Tensor:
+    """``out = act(x @ w.T + bias) + residual``; x [M, K] (row stride free), w [N, K]."""
+    if not x.is_cuda:
+        y = ref.linear(x, w, bias, residual, act)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    nat = _native()
+    L = nat.lib()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    assert out.stride(1) == 1
+    if M == 0:
+        return out
+    ws = nat.workspace(x.device)
+    rc = L.ab200_linear_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+        M, N, K, nat.ptr(bias), nat.ptr(residual),
+        residual.stride(0) if residual is not None else 0, _ACT[act],
+        ws.data_ptr(), ws.numel(), force_splits, nat.status_buffer(x.device).data_ptr(),
+        nat.stream_ptr())
+    nat.check(rc, "linear_bf16 M=%d N=%d K=%d" % (M, N, K))
+    launch_counter.add(1)
+    return out
+
+
+def gemm_nn(x: torch.Tensor, wt: torch.Tensor) -> torch.Tensor:
+    """``x @ wt`` with wt [K, N] row-major (MN-major B operand path)."""
+    if not x.is_cuda:
+        return (x.float() @ wt.float()).to(x.dtype)
+    nat = _native()
+    M, K = x.shape
+    N = wt.shape[1]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    rc = nat.lib().ab200_gemm_bf16_nn(x.data_ptr(), x.stride(0), wt.data_ptr(), wt.stride(0),
+                                      out.data_ptr(), out.stride(0), M, N, K,
+                                      nat.status_buffer(x.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "gemm_bf16_nn")
+    launch_counter.add(1)
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0, out=None):
+    if not table.is_cuda:
+        return ref.embedding(ids, table, vocab_start)
+    nat = _native()
+    ids = ids.to(torch.int64).contiguous()
+    T, H = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    rc = nat.lib().ab200_embedding(ids.data_ptr(), table.data_ptr(), out.data_ptr(), T, H,
+                                   table.shape[0], vocab_start, nat.stream_ptr())
+    nat.check(rc, "embedding")
+    launch_counter.add(1)
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual=None, out=None):
+    """y = RMSNorm(x (+ residual)); ``residual`` (contiguous) is updated in place."""
+    if not x.is_cuda:
+        y = ref.rmsnorm(x, weight, eps, residual)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    nat = _native()
+    T, H = x.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+    if residual is not None:
+        assert residual.is_contiguous()
+    rc = nat.lib().ab200_rmsnorm(x.data_ptr(), x.stride(0), nat.ptr(residual), weight.data_ptr(),
+                                 out.data_ptr(), out.stride(0), T, H, float(eps), nat.stream_ptr())
+    nat.check(rc, "rmsnorm")
+    launch_counter.add(1)
+    return out
+
+
+def layernorm(x, gamma, beta, eps: float, residual=None):
+    if not x.is_cuda:
+        return ref.layernorm(x, gamma, beta, eps, residual)
+    nat = _native()
+    x = x.contiguous()
+    T, H = x.shape
+    out = torch.empty_like(x)
+    if residual is not None:
+        residual = residual.contiguous()
+    rc = nat.lib().ab200_layernorm(x.data_ptr(), nat.ptr(residual), gamma.data_ptr(),
+                                   beta.data_ptr(), out.data_ptr(), T, H, float(eps),
+                                   nat.stream_ptr())
+    nat.check(rc, "layernorm")
+    launch_counter.add(1)
+    return out
+
+
+def silu_mul(x: torch.Tensor, out=None):
+    if not x.is_cuda:
+        return ref.silu_mul(x)
+    nat = _native()
+    assert x.is_contiguous()
+    T, two_i = x.shape
+    if out is None:
+        out = torch.empty(T, two_i // 2, dtype=x.dtype, device=x.device)
+    rc = nat.lib().ab200_silu_mul(x.data_ptr(), out.data_ptr(), T, two_i // 2, nat.stream_ptr())
+    nat.check(rc, "silu_mul")
+    launch_counter.add(1)
+    return out
+
+
+def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, rotate_q=True):
+    """In-place neox RoPE on the q and k parts of ``qkv`` [T, (Hq+2Hkv)*D] and write of the
+    rotated k and of v into the paged caches [num_blocks, Hkv, block_size, D]."""
+    if not qkv.is_cuda:
+        return ref.rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D,
+                              rotate_q)
+    nat = _native()
+    T = qkv.shape[0]
+    bs = k_cache.shape[2]
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert positions.dtype == torch.int64 and (slots is None or slots.dtype == torch.int64)
+    rc = nat.lib().ab200_rope_cache(
+        qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), nat.ptr(slots), inv_freq.data_ptr(),
+        k_cache.data_ptr(), v_cache.data_ptr(), T, Hq, Hkv, D, bs, k_cache.shape[0] * bs,
+        1 if rotate_q else 0, nat.status_buffer(qkv.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "rope_cache")
+    launch_counter.add(1)
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor, out=None):
+    if not src.is_cuda:
+        return ref.gather_rows(src, idx)
+    nat = _native()
+    R, H = idx.numel(), src.shape[1]
+    if out is None:
+        out = torch.empty(R, H, dtype=src.dtype, device=src.device)
+    rc = nat.lib().ab200_gather_rows(src.data_ptr(), src.stride(0), idx.data_ptr(), out.data_ptr(),
+                                     R, H, nat.stream_ptr())
+    nat.check(rc, "gather_rows")
+    launch_counter.add(1)
+    return out
+
+
+def argmax_sample(logits: torch.Tensor, temperature=None, seeds=None, index_offset: int = 0,
+                  out_ids=None, out_vals=None):
+    """Row-wise token choice: arg-max where temperature <= 0, else an exact softmax sample
+    (Gumbel-max). Returns (ids int64 [B], best value fp32 [B])."""
+    if not logits.is_cuda:
+        return ref.argmax_sample(logits, temperature, seeds, index_offset)
+    nat = _native()
+    B, V = logits.shape
+    assert logits.stride(1) == 1
+    if out_ids is None:
+        out_ids = torch.empty(B, dtype=torch.int64, device=logits.device)
+    if out_vals is None:
+        out_vals = torch.empty(B, dtype=torch.float32, device=logits.device)
+    dt = 0 if logits.dtype == torch.bfloat16 else 1
+    assert logits.dtype in (torch.bfloat16, torch.float32)
+    rc = nat.lib().ab200_argmax_sample(logits.data_ptr(), dt, logits.stride(0), B, V,
+                                       nat.ptr(temperature), nat.ptr(seeds), out_ids.data_ptr(),
+                                       out_vals.data_ptr(), index_offset, nat.stream_ptr())
+    nat.check(rc, "argmax_sample")
+    launch_counter.add(1)
+    return out_ids, out_vals
+
+
+# --------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------
+TILE_KEYS = 128
+
+
+@dataclass
+class AttentionMetadata:
+    """Host-built description of one attention call (shared by all layers of a step).
+
+    ``work`` is the [num_work, 8] int32 table consumed by the kernel
+    (csrc/attention.cu): one entry per (query tile, KV split)."""
+    q_lens: list
+    kv_lens: list
+    num_tokens: int
+    work: torch.Tensor | None = None
+    tok_splits: torch.Tensor | None = None
+    block_tables: torch.Tensor | None = None
+    max_splits: int = 1
+    num_work: int = 0
+    o_part: torch.Tensor | None = None
+    lse_part: torch.Tensor | None = None
+    extra: dict = field(default_factory=dict)
+
+
+def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: int = 148,
+                        Hkv: int = 1, seq_rows=None, allow_split: bool = True):
+    """Pure-host planner. Returns (work [n,8] int32 ndarray, tok_splits [T] int32, max_splits).
+
+    Query tokens of a sequence are cut into tiles of 128/G tokens. When the call has too few
+    tiles to occupy the GPU (decode), the keys of each sequence are cut into up to 16 splits
+    of whole 128-key tiles."""
+    tpt = 128 // G
+    rows = []
+    T = int(sum(q_lens))
+    tok_splits = np.ones(max(T, 1), dtype=np.int32)
+    n_tiles_total = sum((ql + tpt - 1) // tpt for ql in q_lens)
+    t0 = 0
+    max_splits = 1
+    for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        if ql <= 0:
+            continue
+        seq_field = i if seq_rows is None else int(seq_rows[i])
+        key_tiles = (kl + TILE_KEYS - 1) // TILE_KEYS
+        ns = 1
+        if allow_split and n_tiles_total * Hkv < num_sms and key_tiles > 4:
+            want = max(1, num_sms // max(1, n_tiles_total * Hkv))
+            ns = int(min(16, want, max(1, key_tiles // 2)))
+        tiles_per_split = (key_tiles + ns - 1) // ns
+        ns = (key_tiles + tiles_per_split - 1) // tiles_per_split
+        max_splits = max(max_splits, ns)
+        for a in range(0, ql, tpt):
+            n = min(tpt, ql - a)
+            q_pos0 = kl - ql + a
+            for s in range(ns):
+                ks = s * tiles_per_split * TILE_KEYS
+                ke = min(kl, (s + 1) * tiles_per_split * TILE_KEYS)
+                rows.append((seq_field, t0 + a, n, q_pos0, ks, ke, s, ns))
+        if ns > 1:
+            tok_splits[t0:t0 + ql] = ns
+        t0 += ql
+    if causal:
+        # heaviest tiles first: later query tiles see more keys
+        rows.sort(key=lambda r: -(min(r[5], r[3] + r[2]) - r[4]))
+    work = np.asarray(rows, dtype=np.int32).reshape(-1, 8)
+    return work, tok_splits, max_splits
+
+
+def build_attention_metadata(q_lens, kv_lens, block_tables, G, Hq, D, device, causal=True,
+                             Hkv=None, seq_rows=None, allow_split=True,
+                             work_capacity: int | None = None) -> AttentionMetadata:
+    Hkv = Hkv if Hkv is not None else Hq // G
+    work, tok_splits, max_splits = plan_attention_work(q_lens, kv_lens, G, causal, Hkv=Hkv,
+                                                       seq_rows=seq_rows, allow_split=allow_split)
+    T = int(sum(q_lens))
+    n = work.shape[0]
+    if work_capacity is not None:
+        assert n <= work_capacity
+        pad = np.zeros((work_capacity - n, 8), dtype=np.int32)
+        work = np.concatenate([work, pad], 0)
+    meta = AttentionMetadata(list(q_lens), list(kv_lens), T)
+    dev = torch.device(device)
+    meta.work = torch.from_numpy(work).to(dev, non_blocking=True)
+    meta.tok_splits = torch.from_numpy(tok_splits).to(dev, non_blocking=True)
+    meta.block_tables = block_tables
+    meta.max_splits = max_splits
+    meta.num_work = work.shape[0]
+    if max_splits > 1 and dev.type == "cuda":
+        meta.o_part = torch.empty(max_splits, T, Hq, D, dtype=torch.float32, device=dev)
+        meta.lse_part = torch.empty(max_splits, T, Hq, dtype=torch.float32, device=dev)
+    return meta
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              meta: AttentionMetadata, Hq: int, Hkv: int, D: int, scale: float | None = None,
+              causal: bool = True, out=None, lse_out=None):
+    """Paged attention. q: [T, Hq*D] (row stride free); caches [num_blocks, Hkv, block_size, D];
+    ``meta.block_tables`` int32 [num_seqs, max_blocks]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    T = q.shape[0]
+    if not q.is_cuda:
+        o, lse = ref.attention(q, k_cache, v_cache, meta.block_tables, meta.q_lens, meta.kv_lens,
+                               Hq, Hkv, D, scale, causal, return_lse=True)
+        if lse_out is not None:
+            lse_out.copy_(lse)
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
+    nat = _native()
+    if out is None:
+        out = torch.empty(T, Hq * D, dtype=q.dtype, device=q.device)
+    bt = meta.block_tables
+    assert bt.dtype == torch.int32 and bt.is_contiguous()
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    rc = nat.lib().ab200_attention(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 0, k_cache.shape[0],
+        k_cache.shape[2], bt.data_ptr(), bt.shape[1], meta.work.data_ptr(), meta.num_work,
+        nat.ptr(meta.tok_splits), meta.max_splits, T, Hq, Hkv, D, 1 if causal else 0,
+        float(scale), out.data_ptr(), out.stride(0), nat.ptr(meta.o_part), nat.ptr(meta.lse_part),
+        nat.ptr(lse_out), nat.status_buffer(q.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "attention")
+    launch_counter.add(2 if meta.max_splits > 1 else 1)
+    return out
+
+
+def attention_contiguous(q, k, v, seq_lens, H: int, D: int, scale: float | None = None,
+                         causal: bool = False, meta: AttentionMetadata | None = None, out=None):
+    """Varlen attention over packed sequences whose K/V rows are contiguous (encoder path).
+    q, k, v: [T, H*D] views with a common row stride (e.g. slices of a fused qkv buffer)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        return ref.attention_contiguous(q, k, v, seq_lens, H, D, scale, causal)
+    nat = _native()
+    T = q.shape[0]
+    if meta is None:
+        starts = np.concatenate([[0], np.cumsum(seq_lens)[:-1]]).astype(np.int64)
+        meta = build_attention_metadata(seq_lens, seq_lens, None, 1, H, D, q.device, causal=causal,
+                                        Hkv=H, seq_rows=starts, allow_split=False)
+    if out is None:
+        out = torch.empty(T, H * D, dtype=q.dtype, device=q.device)
+    assert k.stride(0) == v.stride(0)
+    rc = nat.lib().ab200_attention(
+        q.data_ptr(), q.stride(0), k.data_ptr(), v.data_ptr(), k.stride(0), T, 0, None, 0,
+        meta.work.data_ptr(), meta.num_work, None, 1, T, H, H, D, 1 if causal else 0, float(scale),
+        out.data_ptr(), out.stride(0), None, None, None,
+        nat.status_buffer(q.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "attention_contiguous")
+    launch_counter.add(1)
+    return out

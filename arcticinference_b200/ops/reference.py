@@ -1,0 +1,165 @@
+"""Plain PyTorch restatements of every op in :mod:`arcticinference_b200.ops`.
+
+They serve two purposes: they are the fp32 oracles the GPU numerics tests
+compare the sm_100a kernels against, and they are the implementation used for
+CPU tensors (unit tests of the engine, ``gloo`` multi-process tests). They are
+never used for CUDA tensors by the engine.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def linear(x, w, bias=None, residual=None, act=None):
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if act == "gelu":
+        y = F.gelu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def embedding(ids, table, vocab_start=0):
+    local = ids - vocab_start
+    valid = (local >= 0) & (local < table.shape[0])
+    out = table[local.clamp(0, table.shape[0] - 1)]
+    return out * valid.unsqueeze(-1).to(out.dtype)
+
+
+def rmsnorm(x, weight, eps, residual=None):
+    """Returns y; when ``residual`` is given it is updated in place with x + residual."""
+    if residual is not None:
+        s = (x.float() + residual.float()).to(x.dtype)
+        residual.copy_(s)
+        xf = s.float()
+    else:
+        xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (xf * inv * weight.float()).to(x.dtype)
+
+
+def layernorm(x, gamma, beta, eps, residual=None):
+    xf = x.float()
+    if residual is not None:
+        xf = xf + residual.float()
+    return F.layer_norm(xf, (x.shape[-1],), gamma.float(), beta.float(), eps).to(x.dtype)
+
+
+def silu_mul(x):
+    inter = x.shape[-1] // 2
+    g, u = x[..., :inter].float(), x[..., inter:].float()
+    return (F.silu(g) * u).to(x.dtype)
+
+
+def rope_rotate(x, positions, inv_freq):
+    """neox pairing: element i is rotated with element i + D/2. x: [T, H, D]."""
+    ang = positions.float().unsqueeze(-1) * inv_freq.float().unsqueeze(0)  # [T, D/2]
+    cos, sin = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+    half = x.shape[-1] // 2
+    a, b = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], -1).to(x.dtype)
+
+
+def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, rotate_q=True):
+    """In-place RoPE on q (and k), then write k, v into caches [nb, Hkv, bs, D]."""
+    T = qkv.shape[0]
+    bs = k_cache.shape[2]
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D: (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D: (Hq + 2 * Hkv) * D].view(T, Hkv, D)
+    if rotate_q:
+        q.copy_(rope_rotate(q, positions, inv_freq))
+    k_rot = rope_rotate(k, positions, inv_freq)
+    if slots is not None:
+        ok = slots >= 0
+        s = slots[ok]
+        blk, off = s // bs, s % bs
+        k_cache[blk, :, off] = k_rot[ok]
+        v_cache[blk, :, off] = v[ok]
+
+
+def gather_rows(src, idx):
+    return src[idx]
+
+
+def argmax_sample(logits, temperature=None, seeds=None, index_offset=0):
+    """Greedy where temperature <= 0. (Sampling rows use torch's own generator on CPU.)"""
+    ids = logits.float().argmax(-1)
+    vals = logits.float().max(-1).values
+    if temperature is not None and bool((temperature > 0).any()):
+        t = temperature.clamp_min(1e-6).unsqueeze(-1)
+        probs = torch.softmax(logits.float() / t, -1)
+        g = torch.Generator(device="cpu")
+        g.manual_seed(int(seeds[0]) if seeds is not None else 0)
+        samp = torch.multinomial(probs.cpu(), 1, generator=g).squeeze(-1).to(ids.device)
+        ids = torch.where(temperature > 0, samp, ids)
+    return ids + index_offset, vals
+
+
+def attention(q, k_cache, v_cache, block_tables, q_lens, kv_lens, Hq, Hkv, D, scale, causal=True,
+              return_lse=False):
+    """Paged attention oracle. q: [T, Hq*D]; caches [nb, Hkv, bs, D];
+    sequence i owns q rows [sum(q_lens[:i]), +q_lens[i]) whose positions are the last
+    q_lens[i] positions of its kv_lens[i] keys."""
+    T = q.shape[0]
+    bs = k_cache.shape[2]
+    out = torch.zeros(T, Hq * D, dtype=q.dtype, device=q.device)
+    lse = torch.full((T, Hq), -math.inf, dtype=torch.float32, device=q.device)
+    G = Hq // Hkv
+    t0 = 0
+    for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        if ql == 0:
+            continue
+        nblk = (kl + bs - 1) // bs
+        blocks = block_tables[i, :nblk].long()
+        k = k_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nblk * bs, D)[:, :kl].float()
+        v = v_cache[blocks].permute(1, 0, 2, 3).reshape(Hkv, nblk * bs, D)[:, :kl].float()
+        qi = q[t0:t0 + ql].view(ql, Hq, D).permute(1, 0, 2).float()  # [Hq, ql, D]
+        k = k.repeat_interleave(G, 0)
+        v = v.repeat_interleave(G, 0)
+        s = torch.einsum("hqd,hkd->hqk", qi, k) * scale
+        if causal:
+            qpos = torch.arange(kl - ql, kl, device=q.device).view(1, ql, 1)
+            kpos = torch.arange(kl, device=q.device).view(1, 1, kl)
+            s = s.masked_fill(kpos > qpos, -math.inf)
+        lse[t0:t0 + ql] = torch.logsumexp(s, -1).t()
+        p = torch.softmax(s, -1)
+        o = torch.einsum("hqk,hkd->hqd", p, v)
+        out[t0:t0 + ql] = o.permute(1, 0, 2).reshape(ql, Hq * D).to(q.dtype)
+        t0 += ql
+    return (out, lse) if return_lse else out
+
+
+def attention_contiguous(q, k, v, seq_lens, H, D, scale, causal=False):
+    """Varlen attention over packed sequences (encoder). q/k/v: [T, H*D]."""
+    T = q.shape[0]
+    out = torch.zeros(T, H * D, dtype=q.dtype, device=q.device)
+    t0 = 0
+    for n in seq_lens:
+        qi = q[t0:t0 + n].view(n, H, D).permute(1, 0, 2).float()
+        ki = k[t0:t0 + n].view(n, H, D).permute(1, 0, 2).float()
+        vi = v[t0:t0 + n].view(n, H, D).permute(1, 0, 2).float()
+        s = torch.einsum("hqd,hkd->hqk", qi, ki) * scale
+        if causal:
+            s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=q.device), 1),
+                              -math.inf)
+        o = torch.einsum("hqk,hkd->hqd", torch.softmax(s, -1), vi)
+        out[t0:t0 + n] = o.permute(1, 0, 2).reshape(n, H * D).to(q.dtype)
+        t0 += n
+    return out
+
+
+def merge_attn_states(o1, lse1, o2, lse2):
+    """Combine two attention results over disjoint key sets. o: [T, H, D], lse: [T, H]."""
+    m = torch.maximum(lse1, lse2)
+    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w1, w2 = torch.exp(lse1 - m), torch.exp(lse2 - m)
+    den = (w1 + w2).clamp_min(1e-30)
+    o = (o1.float() * w1.unsqueeze(-1) + o2.float() * w2.unsqueeze(-1)) / den.unsqueeze(-1)
+    return o.to(o1.dtype), m + torch.log(den)

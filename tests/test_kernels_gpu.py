@@ -1,0 +1,231 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 restatements."""
+
+import math
+
+import pytest
+import torch
+
+from arcticinference_b200 import ops
+from arcticinference_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(a, b, atol, rtol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = err > tol
+    assert not bool(bad.any()), "max err %.4g at %d elements (max ref %.4g)" % (
+        float(err.max()), int(bad.sum()), float(b.abs().max()))
+
+
+# ----------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("T,H", [(1, 64), (7, 768), (33, 4096), (5, 8192)])
+def test_rmsnorm(T, H):
+    x, w = _rand(T, H), _rand(H)
+    y = ops.rmsnorm(x, w, 1e-5)
+    _close(y, ref.rmsnorm(x, w, 1e-5), 2e-2, 2e-2)
+    res = _rand(T, H)
+    res_ref = res.clone()
+    y = ops.rmsnorm(x, w, 1e-5, residual=res)
+    y_ref = ref.rmsnorm(x, w, 1e-5, residual=res_ref)
+    _close(res, res_ref, 1e-2, 1e-2)
+    _close(y, y_ref, 3e-2, 2e-2)
+    ops.check_status()
+
+
+def test_rmsnorm_strided_input():
+    buf = _rand(9, 3 * 1024)
+    x = buf[:, 1024:2048]
+    w = _rand(1024)
+    _close(ops.rmsnorm(x, w, 1e-6), ref.rmsnorm(x, w, 1e-6), 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("T,H", [(3, 768), (17, 1024)])
+def test_layernorm(T, H):
+    x, r, g, b = _rand(T, H), _rand(T, H), _rand(H), _rand(H)
+    _close(ops.layernorm(x, g, b, 1e-12), ref.layernorm(x, g, b, 1e-12), 3e-2, 2e-2)
+    _close(ops.layernorm(x, g, b, 1e-12, residual=r), ref.layernorm(x, g, b, 1e-12, residual=r),
+           3e-2, 2e-2)
+
+
+def test_silu_mul():
+    x = _rand(19, 2 * 14336)
+    _close(ops.silu_mul(x), ref.silu_mul(x), 2e-2, 2e-2)
+
+
+def test_embedding_and_gather():
+    table = _rand(1000, 512)
+    ids = torch.randint(0, 1000, (37,), device=DEV)
+    assert torch.equal(ops.embedding(ids, table), table[ids])
+    # vocab-parallel shard: ids outside [start, start+V) give zeros
+    out = ops.embedding(ids + 500, table, vocab_start=600)
+    exp = ref.embedding(ids + 500, table, vocab_start=600)
+    assert torch.equal(out, exp)
+    idx = torch.tensor([5, 0, 36, 7], device=DEV)
+    src = _rand(37, 256)
+    assert torch.equal(ops.gather_rows(src, idx), src[idx])
+
+
+def test_argmax_sample():
+    logits = _rand(9, 128256, scale=3.0)
+    ids, vals = ops.argmax_sample(logits)
+    assert torch.equal(ids, logits.float().argmax(-1))
+    _close(vals, logits.float().max(-1).values, 1e-6, 0)
+    lf = logits.float()
+    ids2, _ = ops.argmax_sample(lf, index_offset=1000)
+    assert torch.equal(ids2, lf.argmax(-1) + 1000)
+    # sampling: distribution sanity on a tiny vocabulary
+    small = torch.tensor([[0.0, 1.0, 2.0, -20.0]], device=DEV).repeat(4000, 1)
+    temp = torch.ones(4000, device=DEV)
+    seeds = torch.arange(4000, device=DEV, dtype=torch.int64) * 7919 + 13
+    s_ids, _ = ops.argmax_sample(small, temperature=temp, seeds=seeds)
+    freq = torch.bincount(s_ids, minlength=4).float() / 4000
+    exp = torch.softmax(small[0], -1)
+    assert float((freq - exp).abs().max()) < 0.04
+
+
+def test_rope_cache():
+    T, Hq, Hkv, D, bs, nb = 23, 8, 2, 128, 32, 6
+    qkv = _rand(T, (Hq + 2 * Hkv) * D)
+    qkv_ref = qkv.clone()
+    pos = torch.randint(0, 100000, (T,), device=DEV)
+    slots = torch.randperm(nb * bs, device=DEV)[:T]
+    slots[3] = -1
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=DEV).float() / D))
+    kc, vc = torch.zeros(nb, Hkv, bs, D, device=DEV, dtype=torch.bfloat16), \
+        torch.zeros(nb, Hkv, bs, D, device=DEV, dtype=torch.bfloat16)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    ops.rope_cache(qkv, pos, slots, inv_freq, kc, vc, Hq, Hkv, D)
+    ref.rope_cache(qkv_ref, pos, slots, inv_freq, kc_ref, vc_ref, Hq, Hkv, D)
+    ops.check_status()
+    _close(qkv[:, :Hq * D], qkv_ref[:, :Hq * D], 3e-2, 2e-2)
+    _close(kc, kc_ref, 3e-2, 2e-2)
+    assert torch.equal(vc, vc_ref)
+
+
+# ------------------------------------------------------------------------------------ GEMM
+GEMM_SHAPES = [
+    (128, 128, 64), (128, 256, 128), (300, 512, 256), (1000, 1024, 4096), (4096, 6144, 4096),
+    (2048, 4096, 14336), (257, 136, 72), (513, 128256, 512),
+    # feature-major (decode) orientation
+    (1, 4096, 4096), (8, 6144, 4096), (17, 4096, 14336), (64, 28672, 4096), (130, 1024, 512),
+    (256, 4096, 4096), (3, 136, 72),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_linear(M, N, K):
+    x = _rand(M, K)
+    w = _rand(N, K, scale=1.0 / math.sqrt(K))
+    y = ops.linear(x, w)
+    ops.check_status()
+    _close(y, ref.linear(x, w), 3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("M", [5, 128, 700])
+def test_linear_epilogue(M):
+    N, K = 768, 3072
+    x, w = _rand(M, K), _rand(N, K, scale=1.0 / math.sqrt(K))
+    b, r = _rand(N), _rand(M, N)
+    _close(ops.linear(x, w, bias=b), ref.linear(x, w, bias=b), 3e-2, 2e-2)
+    _close(ops.linear(x, w, bias=b, act="gelu"), ref.linear(x, w, bias=b, act="gelu"), 3e-2, 2e-2)
+    _close(ops.linear(x, w, bias=b, residual=r), ref.linear(x, w, bias=b, residual=r), 4e-2, 2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_linear_split_k(splits):
+    M, N, K = 24, 1024, 4096
+    x, w = _rand(M, K), _rand(N, K, scale=1.0 / math.sqrt(K))
+    b, r = _rand(N), _rand(M, N)
+    y = ops.linear(x, w, bias=b, residual=r, force_splits=splits)
+    ops.check_status()
+    _close(y, ref.linear(x, w, bias=b, residual=r), 4e-2, 2e-2)
+
+
+def test_linear_strided_views():
+    # x is a column slice of a wider buffer; out is a column slice too
+    buf = _rand(200, 3 * 512)
+    w = _rand(384, 512, scale=1.0 / math.sqrt(512))
+    out_buf = torch.zeros(200, 1024, device=DEV, dtype=torch.bfloat16)
+    ops.linear(buf[:, 512:1024], w, out=out_buf[:, 128:512])
+    ops.check_status()
+    _close(out_buf[:, 128:512], ref.linear(buf[:, 512:1024], w), 3e-2, 2e-2)
+    assert float(out_buf[:, :128].abs().max()) == 0 and float(out_buf[:, 512:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 256, 512), (1024, 192, 128)])
+def test_gemm_nn(M, N, K):
+    x, wt = _rand(M, K), _rand(K, N, scale=1.0 / math.sqrt(K))
+    y = ops.gemm_nn(x, wt)
+    ops.check_status()
+    _close(y, x.float() @ wt.float(), 3e-2, 2e-2)
+
+
+# ------------------------------------------------------------------------------- attention
+def _paged_case(q_lens, kv_lens, Hq, Hkv, D, bs, seed=0):
+    torch.manual_seed(seed)
+    T = sum(q_lens)
+    nblk_seq = [(k + bs - 1) // bs for k in kv_lens]
+    nb = sum(nblk_seq) + 3
+    perm = torch.randperm(nb)[: sum(nblk_seq)].int()
+    maxb = max(nblk_seq)
+    bt = torch.zeros(len(q_lens), maxb, dtype=torch.int32)
+    o = 0
+    for i, n in enumerate(nblk_seq):
+        bt[i, :n] = perm[o:o + n]
+        o += n
+    q = _rand(T, Hq * D)
+    kc = _rand(nb, Hkv, bs, D)
+    vc = _rand(nb, Hkv, bs, D)
+    return q, kc, vc, bt.to(DEV)
+
+
+@pytest.mark.parametrize("q_lens,kv_lens,Hq,Hkv,D,bs", [
+    ([128], [128], 4, 1, 128, 32),
+    ([200, 57], [200, 57], 8, 2, 128, 16),
+    ([300], [812], 8, 2, 128, 64),           # chunked prefill with a cached prefix
+    ([1, 1, 1], [700, 33, 129], 8, 2, 128, 32),   # decode
+    ([4, 4], [1500, 260], 32, 8, 128, 32),   # speculative verification, 4 tokens per sequence
+    ([100, 30], [100, 30], 16, 2, 128, 128),  # G = 8
+    ([64, 200], [64, 200], 12, 12, 64, 16),  # head_dim 64, no GQA
+])
+def test_paged_attention(q_lens, kv_lens, Hq, Hkv, D, bs):
+    q, kc, vc, bt = _paged_case(q_lens, kv_lens, Hq, Hkv, D, bs)
+    meta = ops.build_attention_metadata(q_lens, kv_lens, bt, Hq // Hkv, Hq, D, DEV)
+    lse = torch.empty(sum(q_lens), Hq, device=DEV, dtype=torch.float32)
+    out = ops.attention(q, kc, vc, meta, Hq, Hkv, D, lse_out=lse)
+    ops.check_status()
+    exp, lse_ref = ref.attention(q, kc, vc, bt, q_lens, kv_lens, Hq, Hkv, D, 1 / math.sqrt(D),
+                                 return_lse=True)
+    _close(out, exp, 2e-2, 2e-2)
+    _close(lse, lse_ref, 2e-2, 1e-2)
+
+
+def test_paged_attention_split_kv():
+    q_lens, kv_lens, Hq, Hkv, D, bs = [1, 2], [4000, 1111], 8, 2, 128, 32
+    q, kc, vc, bt = _paged_case(q_lens, kv_lens, Hq, Hkv, D, bs)
+    meta = ops.build_attention_metadata(q_lens, kv_lens, bt, Hq // Hkv, Hq, D, DEV)
+    assert meta.max_splits > 1
+    out = ops.attention(q, kc, vc, meta, Hq, Hkv, D)
+    ops.check_status()
+    exp = ref.attention(q, kc, vc, bt, q_lens, kv_lens, Hq, Hkv, D, 1 / math.sqrt(D))
+    _close(out, exp, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("H,D,seq_lens", [(12, 64, [50, 128, 3, 512]), (4, 128, [77, 300])])
+def test_encoder_attention(H, D, seq_lens):
+    T = sum(seq_lens)
+    qkv = _rand(T, 3 * H * D)
+    q, k, v = qkv[:, :H * D], qkv[:, H * D:2 * H * D], qkv[:, 2 * H * D:]
+    out = ops.attention_contiguous(q, k, v, seq_lens, H, D)
+    ops.check_status()
+    _close(out, ref.attention_contiguous(q, k, v, seq_lens, H, D, 1 / math.sqrt(D)), 2e-2, 2e-2)
