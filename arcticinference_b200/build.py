@@ -112,6 +112,8 @@ def build_suffix_tree(force: bool = False) -> Path:
     src_dir = CSRC / "suffix_tree"
     srcs = sorted(src_dir.glob("*.cc"))
     out = suffix_lib_path()
+    if not srcs:
+        raise RuntimeError("no suffix-tree sources under %s" % src_dir)
     deps = srcs + list(src_dir.glob("*.h"))
     if not force and out.exists() and out.stat().st_mtime >= _newest(deps):
         return out
@@ -128,7 +130,8 @@ def build_suffix_tree(force: bool = False) -> Path:
 
 
 def build_all(force: bool = False) -> None:
-    build_suffix_tree(force)
+    if any((CSRC / "suffix_tree").glob("*.cc")):
+        build_suffix_tree(force)
     build_kernels(force)
 
 

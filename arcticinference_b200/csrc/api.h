@@ -29,7 +29,8 @@ int ab200_rmsnorm(const void* x, long long ldx, void* residual, const void* weig
                   long long ldy, long long T, int hidden, float eps, cudaStream_t stream);
 int ab200_layernorm(const void* x, const void* residual, const void* gamma, const void* beta,
                     void* y, long long T, int hidden, float eps, cudaStream_t stream);
-int ab200_silu_mul(const void* x, void* out, long long T, int inter, cudaStream_t stream);
+int ab200_silu_mul(const void* x, void* out, long long T, int inter, int nblk,
+                   cudaStream_t stream);
 int ab200_rope_cache(void* qkv, long long ld, const void* positions, const void* slots,
                      const void* inv_freq, void* k_cache, void* v_cache, long long T, int Hq,
                      int Hkv, int D, int block_size, long long num_slots, int rotate_q, int* status,

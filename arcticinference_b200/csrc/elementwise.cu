@@ -176,22 +176,28 @@ layernorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
 }
 
 // -------------------------------- SiLU * mul --------------------------------
-// x: [T, 2*I] (gate | up), out: [T, I]
+// x: [T, nblk * 2 * inter] laid out as nblk blocks of (gate | up); out: [T, nblk * inter].
+// nblk = 1 is the usual fused gate/up layout; nblk > 1 is the rank-major layout whose
+// blocks are the tensor-parallel shards.
 __global__ void silu_mul_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, long long T,
-                                int inter) {
+                                int inter, int nblk) {
   const int nvec = inter / 8;
-  const long long total = T * nvec;
+  const long long per_row = (long long)nblk * nvec;
+  const long long total = T * per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / nvec;
-    const int c = (int)(i % nvec);
-    const uint4* row = reinterpret_cast<const uint4*>(x + t * 2ll * inter);
+    const long long t = i / per_row;
+    const int r = (int)(i % per_row);
+    const int b = r / nvec;
+    const int c = r % nvec;
+    const uint4* row =
+        reinterpret_cast<const uint4*>(x + (t * nblk + b) * 2ll * inter);
     float g[8], u[8];
     unpack8(row[c], g);
     unpack8(row[nvec + c], u);
 #pragma unroll
     for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
-    reinterpret_cast<uint4*>(out + t * (long long)inter)[c] = pack8(g);
+    reinterpret_cast<uint4*>(out + (t * nblk + b) * (long long)inter)[c] = pack8(g);
   }
 }
 
@@ -395,14 +401,15 @@ int ab200_layernorm(const void* x, const void* residual, const void* gamma, cons
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-int ab200_silu_mul(const void* x, void* out, long long T, int inter, cudaStream_t stream) {
+int ab200_silu_mul(const void* x, void* out, long long T, int inter, int nblk,
+                   cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (inter % 8) return -2;
-  const long long total = T * (inter / 8);
+  if ((inter % 8) || nblk < 1) return -2;
+  const long long total = T * nblk * (inter / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   silu_mul_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(x),
-                                                        reinterpret_cast<bf16*>(out), T, inter);
+                                                        reinterpret_cast<bf16*>(out), T, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

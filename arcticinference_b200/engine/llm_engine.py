@@ -1,0 +1,165 @@
+"""The engine: scheduler + KV manager + model runner behind ``add_request`` / ``step``.
+
+One engine object runs in every rank's process (SPMD); request admission must
+therefore be identical on every rank (offline ``LLM.generate`` calls are; the
+servers broadcast admitted requests from rank 0 before each step).
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Iterable, Optional
+
+import torch
+
+from ..config import EngineArgs, EngineConfig
+from ..utils.tokenizer import get_tokenizer
+from .kv_cache import KVCacheManager
+from .model_runner import ModelRunner
+from .outputs import CompletionOutput, RequestOutput
+from .request import Request, RequestStatus
+from .sampling_params import SamplingParams
+from .scheduler import Scheduler
+
+
+class LLMEngine:
+    def __init__(self, config: EngineConfig, device: Optional[str] = None, comm=None):
+        self.config = config
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        shard = None
+        if comm is not None:
+            shard = comm.shard_spec()
+        self.comm = comm
+        self.runner = ModelRunner(config, self.device, comm=comm, shard=shard)
+        self.runner.load_model()
+        self.num_blocks = self.runner.determine_num_blocks()
+        self.runner.init_kv_cache(self.num_blocks)
+        self.kv_manager = KVCacheManager(self.num_blocks, config.cache.block_size,
+                                         config.cache.enable_prefix_caching)
+        self.scheduler = Scheduler(config.scheduler, self.kv_manager, config.speculative,
+                                   token_multiple=config.parallel.sp)
+        self.tokenizer = get_tokenizer(config.tokenizer or config.model.name_or_path,
+                                       config.model.vocab_size)
+        self._seq = 0
+        self._parents: dict[str, dict] = {}
+        self.step_count = 0
+        self.sleeping_level = 0
+        self.stats = {"prompt_tokens": 0, "generation_tokens": 0, "steps": 0,
+                      "draft_tokens": 0, "accepted_tokens": 0}
+        if config.speculative is not None:
+            from ..spec_decode.propose import attach_speculation
+            attach_speculation(self)
+
+    @classmethod
+    def from_engine_args(cls, args: EngineArgs, device=None, comm=None) -> "LLMEngine":
+        return cls(args.create_engine_config(), device=device, comm=comm)
+
+    # --------------------------------------------------------------- requests
+    def add_request(self, request_id: Optional[str], prompt, params: SamplingParams,
+                    arrival_time: Optional[float] = None, routing_key=None) -> str:
+        if request_id is None:
+            request_id = "req-%d" % self._seq
+        self._seq += 1
+        text = None
+        if isinstance(prompt, str):
+            text = prompt
+            ids = self.tokenizer.encode(prompt)
+        elif isinstance(prompt, dict):
+            text = prompt.get("prompt")
+            ids = prompt.get("prompt_token_ids")
+            if ids is None:
+                ids = self.tokenizer.encode(text)
+        else:
+            ids = list(prompt)
+        ids = [int(t) for t in ids]
+        eos = self.config.model.eos_token_id
+        if eos is None:
+            eos = getattr(self.tokenizer, "eos_token_id", None)
+        now = arrival_time if arrival_time is not None else time.time()
+        if params.n == 1:
+            self.scheduler.add_request(Request(request_id, ids, params, prompt=text,
+                                               eos_token_id=eos, arrival_time=now,
+                                               routing_key=routing_key))
+        else:
+            self._parents[request_id] = {"n": params.n, "done": {}, "prompt": text, "ids": ids}
+            for i in range(params.n):
+                self.scheduler.add_request(Request(
+                    "%s#%d" % (request_id, i), ids, params.clone_for_sample(i), prompt=text,
+                    eos_token_id=eos, parent_id=request_id, sample_index=i, arrival_time=now))
+        return request_id
+
+    def abort_request(self, request_id: str) -> None:
+        self.scheduler.abort(request_id)
+        if self.runner.suffix_cache is not None:
+            self.runner.suffix_cache.stop_request(request_id)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------- step
+    def step(self) -> list[RequestOutput]:
+        if self.sleeping_level:
+            raise RuntimeError("engine is sleeping; call wake_up() first")
+        out = self.scheduler.schedule()
+        if out.is_empty:
+            return []
+        result = self.runner.execute(out)
+        finished = self.scheduler.update_from_output(out, result.new_tokens, result.drafts)
+        self.step_count += 1
+        self.stats["steps"] += 1
+        for s in out.scheduled:
+            if s.start < s.request.num_prompt_tokens:
+                self.stats["prompt_tokens"] += min(s.num_tokens,
+                                                   s.request.num_prompt_tokens - s.start)
+            if s.num_draft:
+                self.stats["draft_tokens"] += s.num_draft
+        for toks in result.new_tokens.values():
+            self.stats["generation_tokens"] += len(toks)
+            self.stats["accepted_tokens"] += len(toks) - 1
+        outputs = []
+        for req in finished:
+            if self.runner.suffix_cache is not None:
+                self.runner.suffix_cache.stop_request(req.request_id)
+            ro = self._finalize(req)
+            if ro is not None:
+                outputs.append(ro)
+        return outputs
+
+    def _completion(self, req: Request) -> CompletionOutput:
+        text = self.tokenizer.decode(req.output_token_ids,
+                                     skip_special_tokens=req.sampling_params.skip_special_tokens)
+        return CompletionOutput(req.sample_index, text, list(req.output_token_ids),
+                                req.finish_reason, req.output_logprobs)
+
+    def _finalize(self, req: Request) -> Optional[RequestOutput]:
+        comp = self._completion(req)
+        if req.parent_id is None:
+            return RequestOutput(req.request_id, req.prompt, req.prompt_token_ids, [comp], True,
+                                 req.metrics, num_cached_tokens=req.num_cached_tokens)
+        parent = self._parents[req.parent_id]
+        parent["done"][req.sample_index] = (comp, req.metrics)
+        if len(parent["done"]) < parent["n"]:
+            return None
+        del self._parents[req.parent_id]
+        comps = [parent["done"][i][0] for i in range(parent["n"])]
+        return RequestOutput(req.parent_id, parent["prompt"], parent["ids"], comps, True,
+                             parent["done"][0][1], num_cached_tokens=req.num_cached_tokens)
+
+    # ------------------------------------------------------------ sleep / wake
+    def sleep(self, level: int = 1) -> None:
+        """Level 1 frees the KV cache; level 2 also moves the weights (and the drafter's)
+        to host memory (reference: arctic_inference/server/worker.py:275-390,
+        arctic_inference/vllm/patches.py:284-310)."""
+        if self.scheduler.has_work():
+            raise RuntimeError("cannot sleep with unfinished requests")
+        from .sleep import sleep_engine
+        sleep_engine(self, level)
+
+    def wake_up(self, tags: Optional[Iterable[str]] = None) -> None:
+        from .sleep import wake_engine
+        wake_engine(self, tags)
+
+    def reset_prefix_cache(self) -> None:
+        self.kv_manager.reset_prefix_cache()

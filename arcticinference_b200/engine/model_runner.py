@@ -1,0 +1,305 @@
+"""Turns a :class:`SchedulerOutput` into device work: input staging, the model's
+forward pass (eager, or a replayed CUDA graph for decode-shaped steps), logits,
+sampling and draft verification.
+
+One runner lives in every rank's process. All ranks build identical inputs
+from identical scheduler state, so there is no per-step broadcast of scheduler
+output between processes (the reference inherits vLLM's shared-memory message
+queue for that: arctic_inference/vllm/ulysses.py:672-796 and worker RPCs).
+
+Shift parallelism (arctic_inference/vllm/model_runner.py:636-662): a step runs
+in tensor-parallel mode when it carries at most ``shift_parallel_threshold``
+tokens, otherwise in Ulysses sequence-parallel mode; both modes address the
+same paged KV cache.
+"""
+
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..config import EngineConfig
+from ..models.llama import ForwardBatch, LlamaForCausalLM, ShardSpec
+from .kv_cache import KVCacheTensors
+from .scheduler import SchedulerOutput
+
+
+@dataclass
+class StepResult:
+    new_tokens: dict          # request_id -> list[int]
+    drafts: dict              # request_id -> list[int] proposals for the next step
+    num_tokens: int
+    mode: str
+
+
+def _pinned(n, dtype, device):
+    t = torch.empty(n, dtype=dtype)
+    if torch.device(device).type == "cuda":
+        t = t.pin_memory()
+    return t
+
+
+class ModelRunner:
+    def __init__(self, config: EngineConfig, device="cuda", comm=None, shard: ShardSpec = None):
+        self.config = config
+        self.device = torch.device(device)
+        self.comm = comm
+        self.shard = shard or ShardSpec()
+        mcfg = config.model
+        self.model = LlamaForCausalLM(mcfg, self.shard, self.device, torch.bfloat16, comm=comm)
+        self.kv: Optional[KVCacheTensors] = None
+        self.num_blocks = 0
+        self.block_size = config.cache.block_size
+        self.sp = config.parallel.sp
+        self.shift = config.parallel.enable_shift_parallel
+        self.shift_threshold = config.parallel.shift_parallel_threshold
+        self.G = self.model.h // self.model.hkv
+        self.proposer = None          # set by the engine when speculation is configured
+        self.suffix_cache = None
+        self._graphs = {}
+        self._stage_cap = 0
+        self._h_stage = None
+        self._stage_events = [None, None]
+        self._stage_idx = 0
+        self.h2d_bytes = 0
+        self.h2d_total = 0
+        self.d2h_total = 0
+        self.last_step_device_ms = None
+        self.mode_counts = {"sp": 0, "tp": 0}
+        self.step_timer_events = None
+
+    # ------------------------------------------------------------------ set-up
+    def load_model(self) -> None:
+        cfg = self.config
+        if cfg.load_format == "dummy" or not cfg.model.name_or_path or \
+                cfg.model.name_or_path in __import__("arcticinference_b200.config",
+                                                     fromlist=["PRESETS"]).PRESETS:
+            self.model.init_random(cfg.seed)
+        else:
+            from ..models.loader import load_llama_weights
+            load_llama_weights(self.model, cfg.model.name_or_path)
+        if cfg.model.quantization == "fp8":
+            from ..models.quant import quantize_model_fp8
+            quantize_model_fp8(self.model)
+
+    def determine_num_blocks(self) -> int:
+        cfg = self.config
+        m = self.model
+        per_block = KVCacheTensors.bytes_per_block(cfg.model.num_hidden_layers, m.hkv,
+                                                   self.block_size, m.D)
+        if cfg.cache.num_gpu_blocks is not None:
+            return cfg.cache.num_gpu_blocks
+        if self.device.type != "cuda":
+            return 512
+        free, total = torch.cuda.mem_get_info(self.device)
+        # leave room for activations of the largest step and for split-K / split-KV scratch
+        reserve = 6 << 30
+        budget = int(total * cfg.cache.gpu_memory_utilization) - (total - free) - reserve
+        need_max = (cfg.scheduler.max_model_len + self.block_size - 1) // self.block_size
+        n = max(budget // per_block, 0)
+        if n < need_max + 1:
+            raise RuntimeError("not enough GPU memory for one max_model_len sequence "
+                               "(%d blocks available, %d needed)" % (n, need_max + 1))
+        # cap: block ids are int32 and the tensor maps index blocks with 32-bit coordinates
+        return int(min(n, 1 << 22))
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        m = self.model
+        self.num_blocks = num_blocks
+        self.kv = KVCacheTensors(self.config.model.num_hidden_layers, num_blocks, m.hkv,
+                                 self.block_size, m.D, torch.bfloat16, self.device)
+
+    # ------------------------------------------------------------- mode choice
+    def choose_mode(self, total_tokens: int) -> str:
+        if self.sp <= 1:
+            return "tp"
+        if self.shift and total_tokens <= self.shift_threshold:
+            return "tp"
+        return "sp"
+
+    # ---------------------------------------------------------- input staging
+    def _stage(self, n_int64: int) -> torch.Tensor:
+        """Pinned staging memory for one step's integer inputs. Two buffers alternate and
+        each is guarded by an event, so the host never rewrites a buffer whose
+        host-to-device copy is still queued (steps that sample nothing do not synchronise)."""
+        if n_int64 > self._stage_cap:
+            if self.device.type == "cuda":
+                torch.cuda.current_stream().synchronize()
+            self._stage_cap = max(n_int64, 2 * self._stage_cap, 1 << 16)
+            self._h_stage = [_pinned(self._stage_cap, torch.int64, self.device) for _ in range(2)]
+            self._stage_events = [None, None]
+            self._stage_idx = 0
+        self._stage_idx ^= 1
+        ev = self._stage_events[self._stage_idx]
+        if ev is not None:
+            ev.synchronize()
+        return self._h_stage[self._stage_idx][:n_int64]
+
+    def _stage_done(self) -> None:
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._stage_events[self._stage_idx] = ev
+
+    def prepare(self, out: SchedulerOutput):
+        """Build the flat batch. Returns (ForwardBatch, rows) where ``rows[i]`` is the list of
+        sampled row indices (into logits) of scheduled request i."""
+        bs = self.block_size
+        sched = out.scheduled
+        mode = self.choose_mode(out.total_tokens)
+        N = out.total_tokens
+        pad_to = self.sp if mode == "sp" else 1
+        Np = (N + pad_to - 1) // pad_to * pad_to
+        q_lens, kv_lens = [], []
+        n_sel = sum((s.num_draft + 1) if s.samples else 0 for s in sched)
+        max_blocks = max(len(s.request.block_ids) for s in sched)
+        stage = self._stage(3 * Np + n_sel + n_sel)
+        h = stage.numpy()
+        ids, pos, slots = h[:Np], h[Np:2 * Np], h[2 * Np:3 * Np]
+        sel = h[3 * Np:3 * Np + n_sel]
+        sel_pos = h[3 * Np + n_sel:3 * Np + 2 * n_sel]
+        bt = np.zeros((len(sched), max_blocks), dtype=np.int32)
+        t = 0
+        k = 0
+        rows = []
+        sel_q_lens = []
+        for i, s in enumerate(sched):
+            r = s.request
+            n = s.num_tokens
+            toks = r.all_token_ids
+            known = len(toks)
+            seq = toks[s.start:min(s.start + n, known)]
+            if len(seq) < n:
+                seq = seq + list(r.spec_token_ids[:n - len(seq)])
+            ids[t:t + n] = seq
+            p = np.arange(s.start, s.start + n, dtype=np.int64)
+            pos[t:t + n] = p
+            blocks = np.asarray(r.block_ids, dtype=np.int64)
+            slots[t:t + n] = blocks[p // bs] * bs + p % bs
+            bt[i, :len(r.block_ids)] = r.block_ids
+            q_lens.append(n)
+            kv_lens.append(s.start + n)
+            if s.samples:
+                m = s.num_draft + 1
+                idx = np.arange(t + n - m, t + n, dtype=np.int64)
+                sel[k:k + m] = idx
+                sel_pos[k:k + m] = p[n - m:]
+                rows.append(list(range(k, k + m)))
+                sel_q_lens.append(m)
+                k += m
+            else:
+                rows.append([])
+                sel_q_lens.append(0)
+            t += n
+        if Np > N:
+            ids[N:] = 0
+            pos[N:] = 0
+            slots[N:] = -1
+        dev = self.device
+        d = stage.to(dev, non_blocking=True)
+        self._stage_done()
+        self.h2d_bytes = stage.numel() * 8 + bt.nbytes
+        self.h2d_total += self.h2d_bytes
+        bt_t = torch.from_numpy(bt).to(dev, non_blocking=True)
+        m = self.model
+        if Np > N:
+            # padding tokens form a sequence of their own that attends to nothing real
+            q_lens_a, kv_lens_a = q_lens + [Np - N], kv_lens + [Np - N]
+            bt_pad = np.zeros((len(sched) + 1, max_blocks), dtype=np.int32)
+            bt_pad[:-1] = bt
+            bt_t = torch.from_numpy(bt_pad).to(dev, non_blocking=True)
+        else:
+            q_lens_a, kv_lens_a = q_lens, kv_lens
+        meta = ops.build_attention_metadata(q_lens_a, kv_lens_a, bt_t, self.G, m.h, m.D, dev,
+                                            Hkv=m.hkv)
+        batch = ForwardBatch(input_ids=d[:Np], positions=d[Np:2 * Np], slots=d[2 * Np:3 * Np],
+                             attn_meta=meta, logits_indices=d[3 * Np:3 * Np + n_sel],
+                             num_tokens=Np, mode=mode)
+        if self.config.model.is_swiftkv:
+            batch.sel_positions = d[3 * Np + n_sel:3 * Np + 2 * n_sel]
+            if n_sel:
+                sq = [x for x in sel_q_lens if x > 0]
+                skv = [kv for kv, x in zip(kv_lens, sel_q_lens) if x > 0]
+                keep = [i for i, x in enumerate(sel_q_lens) if x > 0]
+                bt_sel = bt_t[torch.as_tensor(keep, device=dev)].contiguous() \
+                    if len(keep) != bt_t.shape[0] else bt_t
+                batch.sel_attn_meta = ops.build_attention_metadata(sq, skv, bt_sel, self.G, m.h,
+                                                                   m.D, dev, Hkv=m.hkv)
+        return batch, rows
+
+    # ---------------------------------------------------------------- sampling
+    def _sample(self, logits: torch.Tensor, sched, rows) -> torch.Tensor:
+        """Returns int64 [num_rows] token ids on the device."""
+        greedy = all(s.request.sampling_params.greedy for s in sched if s.samples)
+        plain = all(not s.request.sampling_params.needs_full_logits for s in sched if s.samples)
+        comm = self.comm
+        sharded = comm is not None and comm.ways > 1
+        if plain:
+            temps = seeds = None
+            if not greedy:
+                n = logits.shape[0]
+                tv = np.zeros(n, dtype=np.float32)
+                sv = np.zeros(n, dtype=np.int64)
+                for s, rr in zip(sched, rows):
+                    sp = s.request.sampling_params
+                    base = sp.seed if sp.seed is not None else hash(s.request.request_id) & 0xFFFFFFF
+                    for j, row in enumerate(rr):
+                        tv[row] = 0.0 if sp.greedy else sp.temperature
+                        sv[row] = (base * 1000003 + s.request.num_tokens + j) & 0x7FFFFFFFFFFFFFFF
+                temps = torch.from_numpy(tv).to(self.device, non_blocking=True)
+                seeds = torch.from_numpy(sv).to(self.device, non_blocking=True)
+            offset = 0
+            if sharded:
+                offset = self.model.vocab_shard(comm.ways, self.shard.head_block)[0]
+            ids, vals = ops.argmax_sample(logits, temps, seeds, index_offset=offset)
+            if sharded:
+                ids = comm.argmax_exchange(ids, vals)
+            return ids
+        # full-distribution path (top-p / top-k / logprobs): framework-level torch ops
+        if sharded:
+            logits = comm.gather_vocab(logits, self.config.model.vocab_size)
+        from .sampler import sample_full
+        return sample_full(logits, sched, rows)
+
+    # ------------------------------------------------------------------- step
+    @torch.inference_mode()
+    def execute(self, out: SchedulerOutput) -> StepResult:
+        sched = out.scheduled
+        batch, rows = self.prepare(out)
+        self.mode_counts[batch.mode] += 1
+        new_tokens: dict = {}
+        drafts: dict = {}
+        if batch.logits_indices.numel() == 0:
+            # pure prefill chunk: KV only
+            self.model.forward(batch, self.kv)
+            return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)
+        hidden = self.model.forward(batch, self.kv)
+        logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
+        ids_dev = self._sample(logits, sched, rows)
+        ids = ids_dev.tolist()  # device -> host; synchronises the step
+        self.d2h_total += ids_dev.numel() * 8
+        accepted_rows = []
+        for s, rr in zip(sched, rows):
+            if not s.samples:
+                continue
+            r = s.request
+            target = [ids[j] for j in rr]
+            toks = [target[0]]
+            if s.num_draft:
+                draft = r.spec_token_ids[:s.num_draft]
+                for j, dtok in enumerate(draft):
+                    if dtok != target[j]:
+                        break
+                    toks.append(target[j + 1])
+            new_tokens[r.request_id] = toks
+            accepted_rows.append(rr[len(toks) - 1])
+        if self.proposer is not None or self.suffix_cache is not None:
+            from ..spec_decode.propose import propose_drafts
+            drafts = propose_drafts(self, sched, rows, new_tokens, hidden, accepted_rows)
+        return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)

@@ -1,0 +1,97 @@
+"""Request state tracked by the scheduler."""
+
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+from .outputs import RequestMetrics
+from .sampling_params import SamplingParams
+
+
+class RequestStatus(enum.Enum):
+    WAITING = 0
+    RUNNING = 1
+    PREEMPTED = 2
+    FINISHED_STOPPED = 3
+    FINISHED_LENGTH = 4
+    FINISHED_ABORTED = 5
+
+    @property
+    def finished(self) -> bool:
+        return self.value >= 3
+
+
+_FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED_LENGTH: "length",
+                  RequestStatus.FINISHED_ABORTED: "abort"}
+
+
+@dataclass
+class Request:
+    request_id: str
+    prompt_token_ids: list[int]
+    sampling_params: SamplingParams
+    prompt: Optional[str] = None
+    eos_token_id: Optional[int] = None
+    parent_id: Optional[str] = None   # set for the samples of an n > 1 request
+    sample_index: int = 0
+    arrival_time: float = field(default_factory=time.time)
+    status: RequestStatus = RequestStatus.WAITING
+    output_token_ids: list[int] = field(default_factory=list)
+    # number of tokens (prompt + output) whose KV is in the cache
+    num_computed_tokens: int = 0
+    block_ids: list[int] = field(default_factory=list)
+    num_cached_tokens: int = 0
+    # draft tokens to verify in the next step (speculative decoding)
+    spec_token_ids: list[int] = field(default_factory=list)
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)
+    output_logprobs: Optional[list] = None
+    routing_key: Optional[str] = None
+
+    def __post_init__(self):
+        self.metrics.arrival_time = self.arrival_time
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return len(self.prompt_token_ids)
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    @property
+    def all_token_ids(self) -> list[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt_token_ids)
+        return self.prompt_token_ids[i] if i < n else self.output_token_ids[i - n]
+
+    @property
+    def is_prefilling(self) -> bool:
+        return self.num_computed_tokens < self.num_tokens - 1 or not self.output_token_ids and \
+            self.num_computed_tokens < self.num_prompt_tokens
+
+    @property
+    def finish_reason(self) -> Optional[str]:
+        return _FINISH_REASON.get(self.status)
+
+    def check_stop(self, max_model_len: int) -> bool:
+        """Update ``status`` after tokens were appended; True when finished."""
+        sp = self.sampling_params
+        n_out = len(self.output_token_ids)
+        if n_out >= sp.min_tokens and n_out > 0:
+            last = self.output_token_ids[-1]
+            if not sp.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id:
+                self.status = RequestStatus.FINISHED_STOPPED
+                return True
+            if sp.stop_token_ids and last in sp.stop_token_ids:
+                self.status = RequestStatus.FINISHED_STOPPED
+                return True
+        if (sp.max_tokens is not None and n_out >= sp.max_tokens) or \
+                self.num_tokens >= max_model_len:
+            self.status = RequestStatus.FINISHED_LENGTH
+            return True
+        return False

@@ -1,0 +1,356 @@
+"""Llama-family decoder (Llama 3.x, and the SwiftKV variant) on the engine's own ops.
+
+Weight layout ("rank-major"): with W = TP*SP head-sharding ways, the fused QKV
+weight is stored as W consecutive row blocks, block p holding
+``[q heads of p | k heads of p | v heads of p]``, and the fused gate/up weight as
+blocks ``[gate_p | up_p]``. Consequences:
+
+* the tensor-parallel shard of rank p is a contiguous row view of the full
+  matrix, so the shift-parallel (full-TP) mode needs no second copy of the
+  weights -- the reference loads a second, TP*SP-sharded model instance for it
+  (arctic_inference/vllm/model_runner.py:1692-1714);
+* in sequence-parallel mode the QKV GEMM's output columns are already grouped
+  by destination rank, which is the "pack" step of the Ulysses all-to-all
+  (arctic_inference/vllm/ulysses.py:418-438).
+
+Head ownership: rank (s, t) -- global rank s*TP + t -- owns head block
+p = t*SP + s in both modes (arctic_inference/vllm/ulysses.py:222-251), so the
+paged KV cache is identical in both modes.
+
+SwiftKV (arctic_inference/vllm/swiftkv/llama_swiftkv.py:220-309): layers
+>= num_key_value_layers get their K/V for every token from one fused projection
+of ``norm_swiftkv(hidden + residual)`` taken after layer num_key_value_layers-1;
+only the tokens that will be sampled continue through those layers.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+
+
+def compute_inv_freq(cfg: ModelConfig, device) -> torch.Tensor:
+    """RoPE inverse frequencies [head_dim/2] fp32, with Llama-3 frequency scaling baked in."""
+    D = cfg.head_dim
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+    rs = cfg.rope_scaling
+    if rs and rs.get("rope_type", rs.get("type")) == "llama3":
+        factor = rs["factor"]
+        lo, hi = rs["low_freq_factor"], rs["high_freq_factor"]
+        old = rs["original_max_position_embeddings"]
+        wavelen = 2 * math.pi / inv
+        smooth = ((old / wavelen) - lo) / (hi - lo)
+        scaled = torch.where(wavelen > old / lo, inv / factor,
+                             torch.where(wavelen < old / hi, inv,
+                                         (1 - smooth) * inv / factor + smooth * inv))
+        inv = scaled
+    elif rs and rs.get("rope_type", rs.get("type")) == "linear":
+        inv = inv / rs["factor"]
+    return inv.float().to(device)
+
+
+@dataclass
+class ShardSpec:
+    """Where this rank sits in the TP x SP grid and what it stores."""
+    tp: int = 1
+    sp: int = 1
+    tp_rank: int = 0
+    sp_rank: int = 0
+
+    @property
+    def ways(self) -> int:
+        return self.tp * self.sp
+
+    @property
+    def head_block(self) -> int:
+        """Index p of the head block this rank owns (in both modes)."""
+        return self.tp_rank * self.sp + self.sp_rank
+
+    @property
+    def stored_blocks(self) -> range:
+        """Head blocks whose weights this rank keeps (all blocks of its TP shard)."""
+        return range(self.tp_rank * self.sp, (self.tp_rank + 1) * self.sp)
+
+
+class LlamaLayerWeights:
+    __slots__ = ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown", "wq_swiftkv",
+                 "extra")
+
+    def __init__(self):
+        self.input_norm = self.post_norm = self.wqkv = self.wo = self.wgu = self.wdown = None
+        self.wq_swiftkv = None
+        self.extra = {}
+
+
+class LlamaModel:
+    """Weights + forward pass of one rank."""
+
+    def __init__(self, cfg: ModelConfig, shard: Optional[ShardSpec] = None, device="cuda",
+                 dtype=torch.bfloat16):
+        self.cfg = cfg
+        self.shard = shard or ShardSpec()
+        self.device = torch.device(device)
+        self.dtype = dtype
+        W = self.shard.ways
+        self.D = cfg.head_dim
+        self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        if self.Hq % W:
+            raise ValueError("query heads must divide by TP*SP")
+        self.h = self.Hq // W                      # query heads per block
+        self.hkv = max(1, self.Hkv // W)           # kv heads per block
+        self.kv_repl = max(1, W // self.Hkv)       # ranks sharing one kv head
+        self.blk_rows = (self.h + 2 * self.hkv) * self.D
+        self.inter = cfg.intermediate_size
+        if self.inter % W:
+            raise ValueError("intermediate_size must divide by TP*SP")
+        self.inter_blk = self.inter // W
+        self.n_stored = len(self.shard.stored_blocks)
+        self.layers: list[LlamaLayerWeights] = []
+        self.embed = None
+        self.norm = None
+        self.lm_head = None       # rows of the vocabulary shard this rank scores
+        self.norm_swiftkv = None
+        self.wkv_swiftkv = None   # fused [L_later * 2*hkv*D (per stored block...), H]
+        self.inv_freq = compute_inv_freq(cfg, self.device)
+        self.scale = 1.0 / math.sqrt(self.D)
+        self.n_kv_layers = cfg.num_key_value_layers if cfg.is_swiftkv else cfg.num_hidden_layers
+
+    # ------------------------------------------------------------------ weights
+    def kv_head_of_block(self, p: int) -> range:
+        """Global kv heads held by head block p."""
+        if self.Hkv >= self.shard.ways:
+            return range(p * self.hkv, (p + 1) * self.hkv)
+        return range(p // self.kv_repl, p // self.kv_repl + 1)
+
+    def vocab_shard(self, mode_ways: int, index: int) -> tuple[int, int]:
+        V = self.cfg.vocab_size
+        per = (V + mode_ways - 1) // mode_ways
+        per = (per + 7) // 8 * 8
+        lo = min(V, index * per)
+        return lo, min(V, lo + per)
+
+    def init_random(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random N(0, std) weights, identical on every rank for the blocks they share."""
+        cfg, dev, dt = self.cfg, self.device, self.dtype
+        H = cfg.hidden_size
+        gen = torch.Generator(device=dev)
+
+        def rnd(tag: int, *shape):
+            gen.manual_seed(seed * 1000003 + tag)
+            return (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * std).to(dt)
+
+        blocks = list(self.shard.stored_blocks)
+        self.embed = rnd(1, cfg.vocab_size, H)
+        self.norm = torch.ones(H, device=dev, dtype=dt)
+        self.lm_head = self.embed if cfg.tie_word_embeddings else rnd(2, cfg.vocab_size, H)
+        self.layers = []
+        for l in range(cfg.num_hidden_layers):
+            lw = LlamaLayerWeights()
+            lw.input_norm = torch.ones(H, device=dev, dtype=dt)
+            lw.post_norm = torch.ones(H, device=dev, dtype=dt)
+            base = 100 + l * 1000
+            lw.wqkv = torch.cat([rnd(base + 1 + p, self.blk_rows, H) for p in blocks], 0)
+            lw.wgu = torch.cat([rnd(base + 300 + p, 2 * self.inter_blk, H) for p in blocks], 0)
+            lw.wo = torch.cat([rnd(base + 500 + p, H, self.h * self.D) for p in blocks], 1)
+            lw.wdown = torch.cat([rnd(base + 700 + p, H, self.inter_blk) for p in blocks], 1)
+            if cfg.is_swiftkv and l >= self.n_kv_layers:
+                # later layers: the q rows of wqkv act as q_proj_swiftkv; their k/v rows are
+                # unused and the swiftkv k/v projections live in self.wkv_swiftkv
+                pass
+            self.layers.append(lw)
+        if cfg.is_swiftkv:
+            self.norm_swiftkv = torch.ones(H, device=dev, dtype=dt)
+            n_later = cfg.num_hidden_layers - self.n_kv_layers
+            # rows: for each stored block p, for each later layer: [k heads | v heads]
+            rows_per_blk = n_later * 2 * self.hkv * self.D
+            self.wkv_swiftkv = torch.cat([rnd(90000 + p, rows_per_blk, H) for p in blocks], 0)
+
+    def num_parameters(self) -> int:
+        n = self.embed.numel() + self.norm.numel()
+        if self.lm_head is not self.embed:
+            n += self.lm_head.numel()
+        for lw in self.layers:
+            n += sum(t.numel() for t in (lw.input_norm, lw.post_norm, lw.wqkv, lw.wo, lw.wgu,
+                                         lw.wdown))
+        if self.wkv_swiftkv is not None:
+            n += self.wkv_swiftkv.numel() + self.norm_swiftkv.numel()
+        return n
+
+    def named_tensors(self):
+        yield "embed", self.embed
+        yield "norm", self.norm
+        yield "lm_head", self.lm_head
+        if self.norm_swiftkv is not None:
+            yield "norm_swiftkv", self.norm_swiftkv
+            yield "wkv_swiftkv", self.wkv_swiftkv
+        for i, lw in enumerate(self.layers):
+            for name in ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown"):
+                yield "layers.%d.%s" % (i, name), getattr(lw, name)
+
+
+@dataclass
+class ForwardBatch:
+    """One step's inputs, identical on every rank (the scheduler runs SPMD)."""
+    input_ids: torch.Tensor        # [N] int64
+    positions: torch.Tensor        # [N] int64
+    slots: torch.Tensor            # [N] int64, -1 for padding
+    attn_meta: object              # ops.AttentionMetadata over all N tokens
+    logits_indices: torch.Tensor   # [B] int64 rows that are sampled
+    num_tokens: int
+    mode: str = "tp"               # "sp": Ulysses sequence parallel; "tp": tensor parallel
+    # SwiftKV: metadata / positions of the sampled rows only
+    sel_attn_meta: object = None
+    sel_positions: Optional[torch.Tensor] = None
+
+
+class LlamaForCausalLM(LlamaModel):
+    """Adds the forward pass. ``comm`` is a :class:`parallel.Communicator` (None on 1 GPU)."""
+
+    def __init__(self, cfg, shard=None, device="cuda", dtype=torch.bfloat16, comm=None):
+        super().__init__(cfg, shard, device, dtype)
+        self.comm = comm
+
+    # --------------------------------------------------------------- shard views
+    def _qkv_w(self, lw, mode):
+        if mode == "sp" or self.n_stored == 1:
+            return lw.wqkv
+        i = self.shard.sp_rank
+        return lw.wqkv[i * self.blk_rows:(i + 1) * self.blk_rows]
+
+    def _gu_w(self, lw, mode):
+        if mode == "sp" or self.n_stored == 1:
+            return lw.wgu
+        i = self.shard.sp_rank
+        return lw.wgu[i * 2 * self.inter_blk:(i + 1) * 2 * self.inter_blk]
+
+    def _o_w(self, lw, mode):
+        if mode == "sp" or self.n_stored == 1:
+            return lw.wo
+        i = self.shard.sp_rank
+        return lw.wo[:, i * self.h * self.D:(i + 1) * self.h * self.D]
+
+    def _down_w(self, lw, mode):
+        if mode == "sp" or self.n_stored == 1:
+            return lw.wdown
+        i = self.shard.sp_rank
+        return lw.wdown[:, i * self.inter_blk:(i + 1) * self.inter_blk]
+
+    # ------------------------------------------------------------------- layers
+    def _attention_block(self, lw, x, batch, kv, layer, mode, meta, positions, slots,
+                         q_only=False):
+        """x: normalised hidden rows this rank works on. Returns o_proj output (before the
+        tensor-parallel reduction in tp mode)."""
+        comm = self.comm
+        h, hkv, D = self.h, self.hkv, self.D
+        if mode == "sp" and comm is not None and comm.sp > 1:
+            # local tokens x all stored head blocks -> all tokens x own head block
+            qkv = comm.qkv_scatter_heads(x, lw.wqkv, self.blk_rows)
+        else:
+            w = self._qkv_w(lw, mode)
+            if q_only:
+                w = w[: h * D]
+            qkv = ops.linear(x, w)
+        if q_only:
+            ops.rope_cache(qkv, positions, None, self.inv_freq, kv.k[layer], kv.v[layer], h, 0, D)
+            q = qkv
+        else:
+            ops.rope_cache(qkv, positions, slots, self.inv_freq, kv.k[layer], kv.v[layer], h, hkv, D)
+            q = qkv[:, : h * D]
+        if mode == "sp" and comm is not None and comm.sp > 1:
+            attn = comm.attention_gather_tokens(q, kv.k[layer], kv.v[layer], meta, h, hkv, D,
+                                                self.scale)
+        else:
+            attn = ops.attention(q, kv.k[layer], kv.v[layer], meta, h, hkv, D, self.scale)
+        return ops.linear(attn, self._o_w(lw, mode))
+
+    def _mlp_block(self, lw, x, mode):
+        gu = ops.linear(x, self._gu_w(lw, mode))
+        nblk = self.n_stored if (mode == "sp" or self.n_stored == 1) else 1
+        act = ops.silu_mul_blocked(gu, nblk)
+        return ops.linear(act, self._down_w(lw, mode))
+
+    def _reduce(self, t, mode):
+        comm = self.comm
+        if comm is None:
+            return t
+        if mode == "tp":
+            return comm.all_reduce_full(t) if comm.ways > 1 else t
+        return comm.all_reduce_tp(t) if comm.tp > 1 else t
+
+    def _run_layers(self, lo, hi, h, residual, batch, kv, mode, meta, positions, slots,
+                    q_only=False, merged_first=False):
+        eps = self.cfg.rms_norm_eps
+        for l in range(lo, hi):
+            lw = self.layers[l]
+            if residual is None:
+                residual = h
+                x = ops.rmsnorm(h, lw.input_norm, eps)
+            elif merged_first and l == lo:
+                x = ops.rmsnorm(residual, lw.input_norm, eps)
+            else:
+                x = ops.rmsnorm(h, lw.input_norm, eps, residual=residual)
+            h = self._reduce(self._attention_block(lw, x, batch, kv, l, mode, meta, positions,
+                                                   slots, q_only), mode)
+            x = ops.rmsnorm(h, lw.post_norm, eps, residual=residual)
+            h = self._reduce(self._mlp_block(lw, x, mode), mode)
+        return h, residual
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, batch: ForwardBatch, kv) -> torch.Tensor:
+        """Returns the final-norm hidden states of the sampled rows, [B, H]."""
+        cfg, comm, mode = self.cfg, self.comm, batch.mode
+        eps = cfg.rms_norm_eps
+        ids, positions, slots = batch.input_ids, batch.positions, batch.slots
+        if mode == "sp" and comm is not None and comm.sp > 1:
+            ids = comm.local_token_slice(ids)  # contiguous N/SP slice of this rank
+        h = ops.embedding(ids, self.embed)
+        h, residual = self._run_layers(0, self.n_kv_layers, h, None, batch, kv, mode,
+                                       batch.attn_meta, positions, slots)
+        if not cfg.is_swiftkv:
+            if mode == "sp" and comm is not None and comm.sp > 1:
+                # hand the sampled rows (hidden and residual) to every rank
+                h, residual = comm.gather_rows_all(h, residual, batch.logits_indices)
+            else:
+                h = ops.gather_rows(h, batch.logits_indices)
+                residual = ops.gather_rows(residual, batch.logits_indices)
+            return ops.rmsnorm(h, self.norm, eps, residual=residual)
+
+        # ---- SwiftKV: one projection produces K/V of all later layers for every token
+        s = ops.rmsnorm(h, self.norm_swiftkv, eps, residual=residual)  # residual <- h + residual
+        if mode == "sp" and comm is not None and comm.sp > 1:
+            s, residual = comm.swiftkv_boundary(s, residual)  # later layers run tensor-parallel
+        n_later = cfg.num_hidden_layers - self.n_kv_layers
+        wkv = self.wkv_swiftkv
+        rows_blk = n_later * 2 * self.hkv * self.D
+        if self.n_stored > 1:
+            i = self.shard.sp_rank
+            wkv = wkv[i * rows_blk:(i + 1) * rows_blk]
+        kv_all = ops.linear(s, wkv)
+        width = 2 * self.hkv * self.D
+        for j in range(n_later):
+            ops.rope_cache(kv_all[:, j * width:(j + 1) * width], positions, slots, self.inv_freq,
+                           kv.k[self.n_kv_layers + j], kv.v[self.n_kv_layers + j], 0, self.hkv,
+                           self.D)
+        x_sel = ops.gather_rows(residual, batch.logits_indices)
+        h, residual = self._run_layers(self.n_kv_layers, cfg.num_hidden_layers, None, x_sel, batch,
+                                       kv, "tp", batch.sel_attn_meta, batch.sel_positions, None,
+                                       q_only=True, merged_first=True)
+        return ops.rmsnorm(h, self.norm, eps, residual=residual)
+
+    def compute_logits(self, hidden: torch.Tensor, fp32: bool = False) -> torch.Tensor:
+        """Logits of this rank's vocabulary shard (the full vocabulary on one GPU)."""
+        comm = self.comm
+        if comm is None or comm.ways == 1:
+            w = self.lm_head
+        else:
+            lo, hi = self.vocab_shard(comm.ways, self.shard.head_block)
+            w = self.lm_head[lo:hi]
+        if fp32:
+            return hidden.float() @ w.float().t()
+        return ops.linear(hidden, w)

@@ -17,7 +17,7 @@ import torch
 from . import reference as ref
 
 __all__ = [
-    "linear", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "rope_cache",
+    "linear", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "silu_mul_blocked", "rope_cache",
     "gather_rows", "argmax_sample", "AttentionMetadata", "build_attention_metadata",
     "attention", "attention_contiguous", "check_status", "count_launches", "launch_counter",
 ]
@@ -153,18 +153,24 @@ def layernorm(x, gamma, beta, eps: float, residual=None):
     return out
 
 
-def silu_mul(x: torch.Tensor, out=None):
+def silu_mul_blocked(x: torch.Tensor, nblk: int = 1, out=None):
+    """x: [T, nblk * 2 * I] as nblk blocks of (gate | up) -> [T, nblk * I]."""
     if not x.is_cuda:
-        return ref.silu_mul(x)
+        return ref.silu_mul_blocked(x, nblk)
     nat = _native()
     assert x.is_contiguous()
-    T, two_i = x.shape
+    T, width = x.shape
+    inter = width // (2 * nblk)
     if out is None:
-        out = torch.empty(T, two_i // 2, dtype=x.dtype, device=x.device)
-    rc = nat.lib().ab200_silu_mul(x.data_ptr(), out.data_ptr(), T, two_i // 2, nat.stream_ptr())
+        out = torch.empty(T, nblk * inter, dtype=x.dtype, device=x.device)
+    rc = nat.lib().ab200_silu_mul(x.data_ptr(), out.data_ptr(), T, inter, nblk, nat.stream_ptr())
     nat.check(rc, "silu_mul")
     launch_counter.add(1)
     return out
+
+
+def silu_mul(x: torch.Tensor, out=None):
+    return silu_mul_blocked(x, 1, out)
 
 
 def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, rotate_q=True):

@@ -47,7 +47,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_embedding": (I, [P, P, P, LL, I, LL, LL, P]),
         "ab200_rmsnorm": (I, [P, LL, P, P, P, LL, LL, I, F, P]),
         "ab200_layernorm": (I, [P, P, P, P, P, LL, I, F, P]),
-        "ab200_silu_mul": (I, [P, P, LL, I, P]),
+        "ab200_silu_mul": (I, [P, P, LL, I, I, P]),
         "ab200_rope_cache": (I, [P, LL, P, P, P, P, P, LL, I, I, I, I, LL, I, P, P]),
         "ab200_gather_rows": (I, [P, LL, P, P, LL, I, P]),
         "ab200_argmax_sample": (I, [P, I, LL, LL, I, P, P, P, P, LL, P]),

@@ -57,6 +57,13 @@ def silu_mul(x):
     return (F.silu(g) * u).to(x.dtype)
 
 
+def silu_mul_blocked(x, nblk=1):
+    T, width = x.shape
+    inter = width // (2 * nblk)
+    v = x.view(T, nblk, 2, inter).float()
+    return (F.silu(v[:, :, 0]) * v[:, :, 1]).reshape(T, nblk * inter).to(x.dtype)
+
+
 def rope_rotate(x, positions, inv_freq):
     """neox pairing: element i is rotated with element i + D/2. x: [T, H, D]."""
     ang = positions.float().unsqueeze(-1) * inv_freq.float().unsqueeze(0)  # [T, D/2]

@@ -1,0 +1,45 @@
+"""Tokenizer glue: a Hugging Face tokenizer when a model directory provides one,
+otherwise a byte-level stand-in so that synthetic (random-weight) presets can be
+driven with text prompts."""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+
+class ByteTokenizer:
+    """UTF-8 bytes shifted past a few special ids; round-trips any string."""
+
+    def __init__(self, vocab_size: int = 1024):
+        self.vocab_size = vocab_size
+        self.bos_token_id = 1
+        self.eos_token_id = 2
+        self.pad_token_id = 0
+        self._offset = 3
+
+    def encode(self, text: str, add_special_tokens: bool = True) -> list[int]:
+        ids = [b + self._offset for b in text.encode("utf-8")]
+        ids = [i % self.vocab_size for i in ids]
+        return ([self.bos_token_id] if add_special_tokens else []) + ids
+
+    def decode(self, ids, skip_special_tokens: bool = True) -> str:
+        bs = bytes((i - self._offset) % 256 for i in ids
+                   if not (skip_special_tokens and i < self._offset))
+        return bs.decode("utf-8", errors="replace")
+
+    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True, **kw):
+        text = "".join("<|%s|>\n%s\n" % (m["role"], m["content"]) for m in messages)
+        if add_generation_prompt:
+            text += "<|assistant|>\n"
+        return self.encode(text) if tokenize else text
+
+
+def get_tokenizer(name_or_path: Optional[str], vocab_size: int = 1024):
+    if name_or_path and os.path.isdir(name_or_path):
+        try:
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(name_or_path)
+        except Exception:
+            pass
+    return ByteTokenizer(vocab_size)
