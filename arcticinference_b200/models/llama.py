@@ -136,40 +136,11 @@ class LlamaModel:
         return lo, min(V, lo + per)
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> None:
-        """Random N(0, std) weights, identical on every rank for the blocks they share."""
-        cfg, dev, dt = self.cfg, self.device, self.dtype
-        H = cfg.hidden_size
-        gen = torch.Generator(device=dev)
-
-        def rnd(tag: int, *shape):
-            gen.manual_seed(seed * 1000003 + tag)
-            return (torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32) * std).to(dt)
-
-        blocks = list(self.shard.stored_blocks)
-        self.embed = rnd(1, cfg.vocab_size, H)
-        self.norm = torch.ones(H, device=dev, dtype=dt)
-        self.lm_head = self.embed if cfg.tie_word_embeddings else rnd(2, cfg.vocab_size, H)
-        self.layers = []
-        for l in range(cfg.num_hidden_layers):
-            lw = LlamaLayerWeights()
-            lw.input_norm = torch.ones(H, device=dev, dtype=dt)
-            lw.post_norm = torch.ones(H, device=dev, dtype=dt)
-            base = 100 + l * 1000
-            lw.wqkv = torch.cat([rnd(base + 1 + p, self.blk_rows, H) for p in blocks], 0)
-            lw.wgu = torch.cat([rnd(base + 300 + p, 2 * self.inter_blk, H) for p in blocks], 0)
-            lw.wo = torch.cat([rnd(base + 500 + p, H, self.h * self.D) for p in blocks], 1)
-            lw.wdown = torch.cat([rnd(base + 700 + p, H, self.inter_blk) for p in blocks], 1)
-            if cfg.is_swiftkv and l >= self.n_kv_layers:
-                # later layers: the q rows of wqkv act as q_proj_swiftkv; their k/v rows are
-                # unused and the swiftkv k/v projections live in self.wkv_swiftkv
-                pass
-            self.layers.append(lw)
-        if cfg.is_swiftkv:
-            self.norm_swiftkv = torch.ones(H, device=dev, dtype=dt)
-            n_later = cfg.num_hidden_layers - self.n_kv_layers
-            # rows: for each stored block p, for each later layer: [k heads | v heads]
-            rows_per_blk = n_later * 2 * self.hkv * self.D
-            self.wkv_swiftkv = torch.cat([rnd(90000 + p, rows_per_blk, H) for p in blocks], 0)
+        """Random N(0, std) weights in checkpoint (Hugging Face) naming, packed through the
+        same path as a real checkpoint: the logical model is the same for every TP x SP
+        layout and every rank."""
+        from .loader import load_llama_state, random_llama_state
+        load_llama_state(self, random_llama_state(self.cfg, seed, std, self.device, self.dtype))
 
     def num_parameters(self) -> int:
         n = self.embed.numel() + self.norm.numel()

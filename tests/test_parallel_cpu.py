@@ -1,0 +1,113 @@
+"""Multi-rank engine logic on CPU ranks (gloo): Ulysses SP, full TP, shift parallelism and
+TP x SP grids must reproduce the single-rank engine's logits."""
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+PROMPTS = [list(range(3, 70)), [9, 8, 7, 6, 5], list(range(100, 131))]
+
+
+def _run_engine(llm, steps=3):
+    """Return logits of the sampled rows for the first ``steps`` engine steps."""
+    from arcticinference_b200 import SamplingParams
+    eng = llm.engine
+    for p in PROMPTS:
+        eng.add_request(None, p, SamplingParams(temperature=0, max_tokens=4, ignore_eos=True))
+    outs = []
+    modes = []
+    for _ in range(steps):
+        out = eng.scheduler.schedule()
+        batch, rows = eng.runner.prepare(out)
+        with torch.inference_mode():
+            h = eng.runner.model.forward(batch, eng.runner.kv)
+            logits = eng.runner.model.compute_logits(h)
+            if eng.comm is not None and eng.comm.ways > 1:
+                logits = eng.comm.gather_vocab(logits, eng.config.model.vocab_size)
+        outs.append(logits.float().clone())
+        modes.append(batch.mode)
+        ids = logits.float().argmax(-1).tolist()
+        new = {}
+        for s, rr in zip(out.scheduled, rows):
+            if s.samples:
+                new[s.request.request_id] = [ids[rr[0]]]
+        eng.scheduler.update_from_output(out, new)
+    return outs, modes
+
+
+def _full_weights(model_name, seed=0):
+    from arcticinference_b200 import LLM
+    llm = LLM(model=model_name, device="cpu", num_gpu_blocks_override=64, block_size=16,
+              max_model_len=512, seed=seed)
+    return llm
+
+
+def _worker(rank, world, port, tp, sp, shift, model_name, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    sys.path.insert(0, ROOT)
+    torch.set_num_threads(1)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from arcticinference_b200 import LLM
+    from arcticinference_b200.parallel.comm import Communicator
+    comm = Communicator(tp, sp, None)
+    llm = LLM(model=model_name, device="cpu", comm=comm, num_gpu_blocks_override=64, block_size=16,
+              max_model_len=512, tensor_parallel_size=tp, ulysses_sequence_parallel_size=sp,
+              enable_shift_parallel=shift, shift_parallel_threshold=8)
+    outs, modes = _run_engine(llm)
+    if rank == 0:
+        q.put(([o.numpy() for o in outs], modes))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _launch(tp, sp, shift, model_name):
+    world = tp * sp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, tp, sp, shift, model_name, q))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return res
+
+
+@pytest.mark.parametrize("tp,sp,shift,model", [
+    (1, 2, False, "llama-tiny"),
+    (2, 1, False, "llama-tiny"),
+    (1, 2, True, "llama-tiny"),
+    (2, 2, True, "llama-tiny"),
+    (1, 2, True, "llama-tiny-swiftkv"),
+])
+def test_parallel_modes_match_single_rank(tp, sp, shift, model):
+    ref_llm = _full_weights(model)
+    ref_outs, _ = _run_engine(ref_llm)
+    outs, modes = _launch(tp, sp, shift, model)
+    if shift:
+        assert "sp" in modes and "tp" in modes   # prefill in SP mode, decode in TP mode
+    for a, b in zip(outs, ref_outs):
+        a = torch.from_numpy(a)
+        assert a.shape == b.shape
+        err = (a - b).abs().max().item()
+        assert err < 0.05 * max(1.0, b.abs().max().item()), (err, modes)
