@@ -41,6 +41,34 @@ int ab200_argmax_sample(const void* logits, int dtype, long long ld, long long B
                         const void* temperature, const void* seeds, void* out_ids, void* out_vals,
                         long long index_offset, cudaStream_t stream);
 
+// ---- attention.cu
+int ab200_attention(const void* q, long long ldq, const void* k, const void* v, long long ld_kv,
+                    long long num_blocks, int block_size, const void* block_tables, int max_blocks,
+                    const void* work, int num_work, const void* tok_splits, int max_splits,
+                    long long T, int Hq, int Hkv, int D, int causal, float scale, void* out,
+                    long long ldo, void* o_part, void* lse_part, void* lse_out, int tile_keys,
+                    int* status, cudaStream_t stream);
+int ab200_attention_scatter(const void* q, long long ldq, const void* k, const void* v,
+                            long long num_blocks, int block_size, const void* block_tables,
+                            int max_blocks, const void* work, int num_work,
+                            const void* tok_splits, int max_splits, long long T, int Hq, int Hkv,
+                            int D, float scale, const void* const* peer_ptrs, int world,
+                            int peer_tokens, long long ldo, void* o_part, void* lse_part,
+                            int tile_keys, int* status, cudaStream_t stream);
+int ab200_linear_bf16_scatter(const void* x, long long ldx, const void* w, long long ldw,
+                              const void* const* peer_ptrs, int world, int peer_cols,
+                              long long peer_row_off, long long ldo, int M, int N, int K,
+                              int* status, cudaStream_t stream);
+
+// ---- comm.cu (pointer arrays are host arrays of `world` device pointers)
+int ab200_barrier(const void* const* flag_ptrs, int my_rank, int world, void* epoch_ctr,
+                  int* status, cudaStream_t stream);
+int ab200_allreduce(const void* const* part_ptrs, int world, void* out, const void* residual,
+                    long long n_elems, cudaStream_t stream);
+int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long rows_per_rank,
+                            const void* idx, void* dst, long long R, int hidden,
+                            cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,9 +8,14 @@
 // with tcgen05.ld, keep the running max/sum, write P (bf16) into swizzled shared
 // memory; P V is a second tcgen05.mma whose B operand is the V tile in its
 // natural [key][d] layout (an MN-major descriptor), so nothing is transposed.
-// S and PV are double-buffered in TMEM (4 x 128 columns): QK^T of tile j+1 runs
-// on the tensor core while the softmax warps work on tile j. The output
-// accumulator stays in registers (one row per thread) and is rescaled on the fly.
+// S is double-buffered in TMEM: QK^T of tile j+1 runs on the tensor core while the
+// softmax warps work on tile j. The output accumulator lives in TMEM as well: P V
+// accumulates in place, and a warp rescales its rows of O (tcgen05.ld / multiply /
+// tcgen05.st) only in the tiles where one of its running maxima moved, which after
+// the first few tiles is rare. Key tiles are 128 wide for prefill; decode-shaped
+// calls (a handful of query rows per sequence) use 64-wide tiles, whose smaller
+// footprint (112 KB of shared memory, 256 TMEM columns, < 170 registers) lets two
+// CTAs share an SM and overlap one CTA's softmax with the other's loads.
 //
 // K/V come either from a paged cache [num_blocks, Hkv, block_size, D] through a
 // block table (one TMA box per block) or from a contiguous [T, Hkv*D]-strided
@@ -23,6 +28,7 @@
 
 #include <float.h>
 #include <math.h>
+#include <string.h>
 
 #include "api.h"
 #include "common/ptx.cuh"
@@ -31,7 +37,6 @@
 namespace ab200 {
 
 constexpr int kAttThreads = 192;  // 4 softmax warps + TMA warp + MMA warp
-constexpr int kTileKeys = 128;
 
 struct AttnArgs {
   const int* work;          // [num_work][8], see AttnWork
@@ -50,6 +55,11 @@ struct AttnArgs {
   float* lse_out;   // optional [T][Hq]
   long long T;
   int* status;
+  // Peer scatter (Ulysses head->sequence exchange fused into the epilogue): when
+  // peer_tokens > 0, the output row of token t is written into peer_out[t / peer_tokens] at
+  // row t % peer_tokens (the pointers already include this rank's column offset).
+  int peer_tokens;
+  __nv_bfloat16* peer_out[16];
 };
 
 // work item layout (int32 x 8)
@@ -58,18 +68,24 @@ struct AttnArgs {
 //  6 split index   7 number of splits of this sequence
 //  In contiguous mode field 0 is the row of the sequence's first key in the K/V tensor.
 
-template <int D>
-__global__ void __launch_bounds__(kAttThreads, 1)
+template <int D, int TK>
+__global__ void __launch_bounds__(kAttThreads, (TK == 64 ? 2 : 1))
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p) {
   constexpr int kHalves = D / 64;
   constexpr uint32_t kQBytes = 128 * D * 2;
-  constexpr uint32_t kKVBytes = kTileKeys * D * 2;
-  constexpr uint32_t kPBytes = 128 * kTileKeys * 2;
+  constexpr uint32_t kKVBytes = TK * D * 2;
+  constexpr uint32_t kPBytes = 128 * TK * 2;
+  constexpr uint32_t kHalf = TK * 128;     // bytes of one 64-wide d half of a K/V stage
+  constexpr int kChunks = TK / 32;         // 32-column chunks of a row of S
+  constexpr uint32_t kTmemCols = (TK == 128) ? 512 : 256;  // 2 S buffers + O
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) report_error(p.status, kErrBadArgument, 900, (int)(smem_u32(smem) & 1023u));
+    return;
+  }
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sK = sQ + kQBytes;          // 2 stages
   const uint32_t sV = sK + 2 * kKVBytes;     // 2 stages
@@ -106,7 +122,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int num_splits = wk[7];
   const int kvh = blockIdx.y;
   if (p.causal) kv_end = min(kv_end, q_pos0 + n_q_tok);
-  const int n_tiles = kv_end > kv_start ? (kv_end - kv_start + kTileKeys - 1) / kTileKeys : 0;
+  const int n_tiles = kv_end > kv_start ? (kv_end - kv_start + TK - 1) / TK : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -128,7 +144,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     prefetch_tensormap(&tmap_v);
   }
   if (warp == 5) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
   // Stale shared memory may hold non-finite bit patterns; keys that are never
@@ -143,8 +159,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;        // S buffers at columns 0, 128
-  const uint32_t tO = tmem_base + 256;  // PV buffers at columns 256, 384
+  const uint32_t tS = tmem_base;           // S buffers at columns 0, TK
+  const uint32_t tO = tmem_base + 2 * TK;  // output accumulator, D columns
 
   if (warp == 4) {
     // ------------------------------ TMA producer ------------------------------
@@ -154,14 +170,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tma_load_4d(sQ + h * 16384u, &tmap_q, q_full, h * 64, 0, kvh, q_tok0);
     }
     const int bs = p.block_size;
-    const int blocks_per_tile = bs > 0 ? kTileKeys / bs : 0;
     const int* bt = bs > 0 ? p.block_tables + (long long)seq * p.max_blocks : nullptr;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      const int key0 = kv_start + j * kTileKeys;
-      const int nkeys = min(kTileKeys, kv_end - key0);
+      const int key0 = kv_start + j * TK;
+      const int nkeys = min(TK, kv_end - key0);
       for (int kv = 0; kv < 2; ++kv) {
         const uint32_t full = kv == 0 ? k_full(st) : v_full(st);
         const uint32_t empty = kv == 0 ? k_empty(st) : v_empty(st);
@@ -178,14 +193,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           if (lane < nblk) {
             const int bid = bt[key0 / bs + lane];
             for (int h = 0; h < kHalves; ++h)
-              tma_load_4d(dst + h * 16384u + (uint32_t)(lane * bs) * 128u, tm, full, h * 64, 0, kvh,
+              tma_load_4d(dst + h * kHalf + (uint32_t)(lane * bs) * 128u, tm, full, h * 64, 0, kvh,
                           bid);
           }
         } else {
           if (lane == 0) {
             mbar_arrive_expect_tx(full, kKVBytes);
             for (int h = 0; h < kHalves; ++h)
-              tma_load_3d(dst + h * 16384u, tm, full, h * 64, kvh, seq + key0);
+              tma_load_3d(dst + h * kHalf, tm, full, h * 64, kvh, seq + key0);
           }
         }
         __syncwarp();
@@ -194,7 +209,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   } else if (warp == 5) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0 && n_tiles > 0) {
-      const uint32_t idesc_s = make_idesc(128, kTileKeys, 1, 1, 0, 0);
+      const uint32_t idesc_s = make_idesc(128, TK, 1, 1, 0, 0);
       const uint32_t idesc_pv = make_idesc(128, D, 1, 1, 0, 1);
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 600, 0);
       auto issue_s = [&](int j) -> bool {
@@ -207,8 +222,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t qd = make_desc_kmajor_sw128(sQ + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
-          const uint64_t kd = make_desc_kmajor_sw128(kb + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
-          umma_f16_ss(tS + (uint32_t)st * 128u, qd, kd, idesc_s, k > 0 ? 1u : 0u);
+          const uint64_t kd = make_desc_kmajor_sw128(kb + (uint32_t)(k / 4) * kHalf) + 2u * (k % 4);
+          umma_f16_ss(tS + (uint32_t)st * TK, qd, kd, idesc_s, k > 0 ? 1u : 0u);
         }
         tc_commit(k_empty(st));
         tc_commit(s_full(st));
@@ -219,14 +234,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         if (!mbar_wait(v_full(st), ph, abort_flag, p.status, 630 + st, j)) return false;
         if (!mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.status, 640, j)) return false;
-        if (!mbar_wait(o_empty(st), ph ^ 1u, abort_flag, p.status, 650 + st, j)) return false;
         tc_fence_after();
         const uint32_t vb = sV + (uint32_t)st * kKVBytes;
 #pragma unroll
-        for (int k = 0; k < kTileKeys / 16; ++k) {
+        for (int k = 0; k < TK / 16; ++k) {
           const uint64_t pd = make_desc_kmajor_sw128(sP + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
-          const uint64_t vd = make_desc_mnmajor_sw128(vb, 16384u) + 128u * k;
-          umma_f16_ss(tO + (uint32_t)st * 128u, pd, vd, idesc_pv, k > 0 ? 1u : 0u);
+          const uint64_t vd = make_desc_mnmajor_sw128(vb, kHalf) + 128u * k;
+          // O accumulates in tensor memory across key tiles
+          umma_f16_ss(tO, pd, vd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(v_empty(st));
         tc_commit(o_full(st));
@@ -249,99 +264,137 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     float m = -INFINITY;
     float l = 0.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
     uint8_t* p_row = pP + (size_t)row * 128;
     bool ok = true;
+    const uint32_t to = tO + lane_off;
 
-    auto fold_pv = [&](int jj, float alpha) -> bool {
-      const int st = jj & 1;
-      const uint32_t ph = (uint32_t)(jj >> 1) & 1u;
-      // o_full was already waited for by the caller
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(tO + (uint32_t)st * 128u + lane_off + (uint32_t)c * 32u, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 32; ++t) o[c * 32 + t] = (o[c * 32 + t] + __uint_as_float(r[t])) * alpha;
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_empty(st));
-      (void)ph;
-      return true;
-    };
-
+    // Decode tiles hold a few valid rows: warps whose 32 rows are all padding only keep the
+    // barrier protocol going (their rows of P are never read back by anyone).
+    const bool warp_active = warp * 32 < n_q_tok * p.G;
+    const float sc = p.scale_log2;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j & 1;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      const int key0 = kv_start + j * kTileKeys;
+      const int key0 = kv_start + j * TK;
       if (!mbar_wait(s_full(st), ph, abort_flag, p.status, 700 + st, j)) {
         ok = false;
         break;
       }
+      if (!warp_active) {
+        // staying one product behind the active warps keeps the arrival counts of
+        // consecutive tiles apart
+        if (j > 0 && !mbar_wait(o_full((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abort_flag,
+                                p.status, 711, j)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive(s_empty(st));
+          mbar_arrive(p_full);
+        }
+        continue;
+      }
       tc_fence_after();
-      const uint32_t ts = tS + (uint32_t)st * 128u + lane_off;
-      const bool need_mask = key0 + kTileKeys - 1 > limit;
-      // pass 1: row maximum
-      float mx = -INFINITY;
+      const uint32_t ts = tS + (uint32_t)st * TK + lane_off;
+      const bool need_mask = key0 + TK - 1 > limit;
+      uint32_t ra[32], rb[32];
+      // pass 1: row maximum (four independent chains; one warp per scheduler cannot hide a
+      // long dependent chain). TMEM reads are software-pipelined.
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      tmem_ld_x32(ts, ra);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(ts + (uint32_t)c * 32u, r);
-        tmem_ld_wait();
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        tmem_ld_wait_dep(cur);
+        // next chunk; after the last one, chunk 0 again for pass 2
+        tmem_ld_x32(ts + (uint32_t)((c + 1) % kChunks) * 32u, nxt);
         if (need_mask) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t)
-            if (key0 + c * 32 + t <= limit) mx = fmaxf(mx, __uint_as_float(r[t]));
+          for (int t = 0; t < 32; t += 4) {
+            const int k = key0 + c * 32 + t;
+            mx0 = fmaxf(mx0, k + 0 <= limit ? __uint_as_float(cur[t + 0]) : -INFINITY);
+            mx1 = fmaxf(mx1, k + 1 <= limit ? __uint_as_float(cur[t + 1]) : -INFINITY);
+            mx2 = fmaxf(mx2, k + 2 <= limit ? __uint_as_float(cur[t + 2]) : -INFINITY);
+            mx3 = fmaxf(mx3, k + 3 <= limit ? __uint_as_float(cur[t + 3]) : -INFINITY);
+          }
         } else {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(r[t]));
+          for (int t = 0; t < 32; t += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(cur[t + 0]));
+            mx1 = fmaxf(mx1, __uint_as_float(cur[t + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(cur[t + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(cur[t + 3]));
+          }
         }
       }
-      const float m_new = fmaxf(m, mx);
+      const float m_new = fmaxf(fmaxf(m, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f((m - m_safe) * p.scale_log2);  // m = -inf -> 0
-      const float neg_ms = -m_safe * p.scale_log2;
-      // P(j) overwrites the buffer PV(j-1) reads from: wait for that product first.
+      const float alpha = ex2_approx((m - m_safe) * sc);  // m = -inf -> 0
+      const float neg_ms = -m_safe * sc;
+      // P(j) overwrites the buffer PV(j-1) reads from, and a rescale of O must not race with
+      // PV(j-1) accumulating into it: wait for that product first.
       if (j > 0) {
         if (!mbar_wait(o_full((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abort_flag, p.status,
                        710, j)) {
           ok = false;
           break;
         }
+        // The running maxima settle after a few tiles; only then-rare tiles pay for this.
+        if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+          tc_fence_after();
+          uint32_t rc[32];
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld_x32(to + (uint32_t)c * 32u, rc);
+            tmem_ld_wait_dep(rc);
+#pragma unroll
+            for (int t = 0; t < 32; ++t) rc[t] = __float_as_uint(__uint_as_float(rc[t]) * alpha);
+            tmem_st_x32(to + (uint32_t)c * 32u, rc);
+          }
+          tmem_st_wait();
+        }
       }
-      // pass 2: probabilities -> swizzled shared memory
-      float lsum = 0.f;
+      // pass 2: probabilities -> swizzled shared memory (chunk 0 is already in flight in the
+      // buffer pass 1 left as "next")
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(ts + (uint32_t)c * 32u, r);
-        tmem_ld_wait();
-        float pv[32];
+      for (int c = 0; c < kChunks; ++c) {
+        constexpr int kFlip = kChunks & 1;  // parity of the buffer that holds chunk 0
+        uint32_t(&cur)[32] = ((c + kFlip) & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = ((c + kFlip) & 1) ? ra : rb;
+        tmem_ld_wait_dep(cur);
+        if (c + 1 < kChunks) tmem_ld_x32(ts + (uint32_t)(c + 1) * 32u, nxt);
+        uint32_t pk[16];
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float e = exp2f(fmaf(__uint_as_float(r[t]), p.scale_log2, neg_ms));
-          if (need_mask && key0 + c * 32 + t > limit) e = 0.f;
-          pv[t] = e;
-          lsum += e;
+        for (int t = 0; t < 32; t += 4) {
+          float e0 = ex2_approx(fmaf(__uint_as_float(cur[t + 0]), sc, neg_ms));
+          float e1 = ex2_approx(fmaf(__uint_as_float(cur[t + 1]), sc, neg_ms));
+          float e2 = ex2_approx(fmaf(__uint_as_float(cur[t + 2]), sc, neg_ms));
+          float e3 = ex2_approx(fmaf(__uint_as_float(cur[t + 3]), sc, neg_ms));
+          if (need_mask) {
+            const int k = key0 + c * 32 + t;
+            e0 = k + 0 <= limit ? e0 : 0.f;
+            e1 = k + 1 <= limit ? e1 : 0.f;
+            e2 = k + 2 <= limit ? e2 : 0.f;
+            e3 = k + 3 <= limit ? e3 : 0.f;
+          }
+          s0 += e0;
+          s1 += e1;
+          s2 += e2;
+          s3 += e3;
+          pk[t / 2] = pack_bf16x2(e0, e1);
+          pk[t / 2 + 1] = pack_bf16x2(e2, e3);
         }
         uint8_t* line = p_row + (size_t)(c >> 1) * 16384;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          uint4 q;
-          q.x = pack_bf16x2(pv[8 * i + 0], pv[8 * i + 1]);
-          q.y = pack_bf16x2(pv[8 * i + 2], pv[8 * i + 3]);
-          q.z = pack_bf16x2(pv[8 * i + 4], pv[8 * i + 5]);
-          q.w = pack_bf16x2(pv[8 * i + 6], pv[8 * i + 7]);
           const int chunk = ((c & 1) * 4 + i) ^ (row & 7);
-          *reinterpret_cast<uint4*>(line + chunk * 16) = q;
+          *reinterpret_cast<uint4*>(line + chunk * 16) =
+              make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
         }
       }
-      l = l * alpha + lsum;
+      l = l * alpha + ((s0 + s1) + (s2 + s3));
       m = m_new;
       tc_fence_before();
       fence_proxy_async_smem();
@@ -350,40 +403,58 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_arrive(s_empty(st));
         mbar_arrive(p_full);
       }
-      if (j > 0) fold_pv(j - 1, alpha);
     }
-    if (ok && n_tiles > 0) {
+    if (ok && n_tiles > 0 && warp_active) {
       const int jl = n_tiles - 1;
-      if (mbar_wait(o_full(jl & 1), (uint32_t)(jl >> 1) & 1u, abort_flag, p.status, 720, jl)) {
-        fold_pv(jl, 1.0f);
-      } else {
+      if (!mbar_wait(o_full(jl & 1), (uint32_t)(jl >> 1) & 1u, abort_flag, p.status, 720, jl))
         ok = false;
-      }
+      tc_fence_after();
     }
-    if (ok && valid_row) {
+    if (ok && warp_active) {  // warp-uniform: every lane takes part in the TMEM reads
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const long long tok = (long long)q_tok0 + tok_local;
       const int head = kvh * p.G + g;
       const float lse = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
-      if (num_splits <= 1) {
-        __nv_bfloat16* dst = p.out + tok * p.ldo + (long long)head * D;
+      __nv_bfloat16* dst16 = p.out + tok * p.ldo + (long long)head * D;
+      if (p.peer_tokens > 0)
+        dst16 = p.peer_out[tok / p.peer_tokens] + (tok % p.peer_tokens) * p.ldo + (long long)head * D;
+      float* dst32 = p.o_part + (((long long)split * p.T + tok) * p.Hq + head) * D;
 #pragma unroll
-        for (int i = 0; i < D; i += 8) {
-          uint4 q;
-          q.x = pack_bf16x2(o[i] * inv_l, o[i + 1] * inv_l);
-          q.y = pack_bf16x2(o[i + 2] * inv_l, o[i + 3] * inv_l);
-          q.z = pack_bf16x2(o[i + 4] * inv_l, o[i + 5] * inv_l);
-          q.w = pack_bf16x2(o[i + 6] * inv_l, o[i + 7] * inv_l);
-          *reinterpret_cast<uint4*>(dst + i) = q;
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rc[32];
+        if (n_tiles > 0) {
+          tmem_ld_x32(to + (uint32_t)c * 32u, rc);
+          tmem_ld_wait_dep(rc);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) rc[t] = 0u;
         }
-        if (p.lse_out) p.lse_out[tok * p.Hq + head] = lse;
-      } else {
-        float* dst = p.o_part + (((long long)split * p.T + tok) * p.Hq + head) * D;
+        if (valid_row) {
+          if (num_splits <= 1) {
 #pragma unroll
-        for (int i = 0; i < D; i += 4)
-          *reinterpret_cast<float4*>(dst + i) =
-              make_float4(o[i] * inv_l, o[i + 1] * inv_l, o[i + 2] * inv_l, o[i + 3] * inv_l);
-        p.lse_part[((long long)split * p.T + tok) * p.Hq + head] = lse;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 q;
+              q.x = pack_bf16x2(__uint_as_float(rc[i]) * inv_l, __uint_as_float(rc[i + 1]) * inv_l);
+              q.y = pack_bf16x2(__uint_as_float(rc[i + 2]) * inv_l, __uint_as_float(rc[i + 3]) * inv_l);
+              q.z = pack_bf16x2(__uint_as_float(rc[i + 4]) * inv_l, __uint_as_float(rc[i + 5]) * inv_l);
+              q.w = pack_bf16x2(__uint_as_float(rc[i + 6]) * inv_l, __uint_as_float(rc[i + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(dst16 + c * 32 + i) = q;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst32 + c * 32 + i) = make_float4(
+                  __uint_as_float(rc[i]) * inv_l, __uint_as_float(rc[i + 1]) * inv_l,
+                  __uint_as_float(rc[i + 2]) * inv_l, __uint_as_float(rc[i + 3]) * inv_l);
+          }
+        }
+      }
+      if (valid_row) {
+        if (num_splits <= 1) {
+          if (p.lse_out) p.lse_out[tok * p.Hq + head] = lse;
+        } else {
+          p.lse_part[((long long)split * p.T + tok) * p.Hq + head] = lse;
+        }
       }
     }
   }
@@ -392,7 +463,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __syncthreads();
   if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -403,10 +474,15 @@ __global__ void attention_merge_kernel(const float* __restrict__ o_part,
                                        const float* __restrict__ lse_part,
                                        const int* __restrict__ tok_splits, long long T, int Hq,
                                        __nv_bfloat16* __restrict__ out, long long ldo,
-                                       float* __restrict__ lse_out) {
+                                       float* __restrict__ lse_out, AttnArgs pa) {
   const long long tok = blockIdx.x;
   const int ns = tok_splits[tok];
   if (ns <= 1) return;
+  long long out_row = tok;
+  if (pa.peer_tokens > 0) {
+    out = pa.peer_out[tok / pa.peer_tokens];
+    out_row = tok % pa.peer_tokens;
+  }
   for (int idx = threadIdx.x; idx < Hq * (D / 4); idx += blockDim.x) {
     const int head = idx / (D / 4);
     const int d4 = (idx % (D / 4)) * 4;
@@ -429,28 +505,34 @@ __global__ void attention_merge_kernel(const float* __restrict__ o_part,
     uint2 q;
     q.x = pack_bf16x2(acc.x * inv, acc.y * inv);
     q.y = pack_bf16x2(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(out + tok * ldo + (long long)head * D + d4) = q;
+    *reinterpret_cast<uint2*>(out + out_row * ldo + (long long)head * D + d4) = q;
     if (lse_out && d4 == 0) lse_out[tok * Hq + head] = wsum > 0.f ? mx + logf(wsum) : -INFINITY;
   }
 }
 
-template <int D>
+template <int D, int TK>
 static int launch_attention(const void* q, long long ldq, const void* k, const void* v,
                             long long ld_kv, long long num_blocks, int block_size,
                             const int* block_tables, int max_blocks, const int* work, int num_work,
                             const int* tok_splits, int max_splits, long long T, int Hq, int Hkv,
                             int causal, float scale, void* out, long long ldo, float* o_part,
-                            float* lse_part, float* lse_out, int* status, cudaStream_t stream) {
+                            float* lse_part, float* lse_out, int* status, cudaStream_t stream,
+                            const void* const* peer_ptrs = nullptr, int world = 0,
+                            int peer_tokens = 0) {
   const int G = Hq / Hkv;
+  if (peer_tokens > 0 && (world < 1 || world > 16 || peer_ptrs == nullptr)) return -2;
   if (G <= 0 || Hq % Hkv || 128 % G) return -2;
-  if (block_size > 0 && (kTileKeys % block_size || block_size < 8)) return -2;
-  static bool attr_set = false;
-  const size_t smem = 128 * D * 2 + 4 * (size_t)kTileKeys * D * 2 + 128 * kTileKeys * 2 + 256 + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (block_size > 0 && (TK % block_size || block_size < 8)) return -2;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -3;
+  const size_t smem = 128 * D * 2 + 4 * (size_t)TK * D * 2 + 128 * TK * 2 + 256;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(attention_kernel<D, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return -3;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   CUtensorMap tq, tk, tv;
   {
@@ -471,11 +553,15 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
     // contiguous: k/v rows are tokens with stride ld_kv, heads packed [Hkv][D]
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)num_blocks /* = rows */};
     const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)ld_kv * 2};
-    const uint32_t box[3] = {64, 1, (uint32_t)kTileKeys};
+    const uint32_t box[3] = {64, 1, (uint32_t)TK};
     if (make_tmap_nd(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box) != 0) return -4;
     if (make_tmap_nd(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box) != 0) return -4;
   }
   AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.peer_tokens = peer_tokens;
+  for (int i = 0; i < world && peer_tokens > 0; ++i)
+    a.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(peer_ptrs[i]));
   a.work = work;
   a.block_tables = block_tables;
   a.max_blocks = max_blocks;
@@ -494,11 +580,11 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
   a.T = T;
   a.status = status;
   dim3 grid((unsigned)num_work, (unsigned)Hkv);
-  attention_kernel<D><<<grid, kAttThreads, smem, stream>>>(tq, tk, tv, a);
+  attention_kernel<D, TK><<<grid, kAttThreads, smem, stream>>>(tq, tk, tv, a);
   if (cudaGetLastError() != cudaSuccess) return -5;
   if (max_splits > 1) {
     attention_merge_kernel<D><<<(unsigned)T, 128, 0, stream>>>(
-        o_part, lse_part, tok_splits, T, Hq, reinterpret_cast<__nv_bfloat16*>(out), ldo, lse_out);
+        o_part, lse_part, tok_splits, T, Hq, reinterpret_cast<__nv_bfloat16*>(out), ldo, lse_out, a);
     if (cudaGetLastError() != cudaSuccess) return -5;
   }
   return 0;
@@ -510,37 +596,58 @@ using namespace ab200;
 
 extern "C" {
 
+#define AB200_ATTN_DISPATCH(...)                                                       \
+  do {                                                                                 \
+    const bool small = tile_keys == 64 && (block_size == 0 || block_size <= 64);        \
+    if (D == 128) return small ? launch_attention<128, 64>(__VA_ARGS__)                \
+                               : launch_attention<128, 128>(__VA_ARGS__);              \
+    if (D == 64) return small ? launch_attention<64, 64>(__VA_ARGS__)                  \
+                              : launch_attention<64, 128>(__VA_ARGS__);                \
+    return -2;                                                                         \
+  } while (0)
+
 // q: [T, Hq*D] rows with stride ldq. Paged mode (block_size > 0): k/v are caches
 // [num_blocks, Hkv, block_size, D]. Contiguous mode (block_size == 0): k/v are
 // [num_blocks(=rows), Hkv*D] with row stride ld_kv. `work` is an int32 [num_work, 8]
 // device array (layout above). With max_splits > 1, o_part/lse_part/tok_splits
 // must be given: o_part fp32 [max_splits, T, Hq, D], lse_part fp32 [max_splits, T, Hq].
+// tile_keys: 128 (prefill) or 64 (decode-shaped calls: few query rows per sequence).
 int ab200_attention(const void* q, long long ldq, const void* k, const void* v, long long ld_kv,
                     long long num_blocks, int block_size, const void* block_tables, int max_blocks,
                     const void* work, int num_work, const void* tok_splits, int max_splits,
                     long long T, int Hq, int Hkv, int D, int causal, float scale, void* out,
-                    long long ldo, void* o_part, void* lse_part, void* lse_out, int* status,
-                    cudaStream_t stream) {
+                    long long ldo, void* o_part, void* lse_part, void* lse_out, int tile_keys,
+                    int* status, cudaStream_t stream) {
   if (num_work <= 0 || T <= 0) return 0;
   if ((ldq % 8) || (ldo % 8) || (ld_kv % 8)) return -2;
   if (max_splits > 1 && (o_part == nullptr || lse_part == nullptr || tok_splits == nullptr)) return -2;
-  if (D == 128)
-    return launch_attention<128>(q, ldq, k, v, ld_kv, num_blocks, block_size,
-                                 reinterpret_cast<const int*>(block_tables), max_blocks,
-                                 reinterpret_cast<const int*>(work), num_work,
-                                 reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv,
-                                 causal, scale, out, ldo, reinterpret_cast<float*>(o_part),
-                                 reinterpret_cast<float*>(lse_part),
-                                 reinterpret_cast<float*>(lse_out), status, stream);
-  if (D == 64)
-    return launch_attention<64>(q, ldq, k, v, ld_kv, num_blocks, block_size,
-                                reinterpret_cast<const int*>(block_tables), max_blocks,
-                                reinterpret_cast<const int*>(work), num_work,
-                                reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv,
-                                causal, scale, out, ldo, reinterpret_cast<float*>(o_part),
-                                reinterpret_cast<float*>(lse_part),
-                                reinterpret_cast<float*>(lse_out), status, stream);
-  return -2;
+  AB200_ATTN_DISPATCH(q, ldq, k, v, ld_kv, num_blocks, block_size,
+                      reinterpret_cast<const int*>(block_tables), max_blocks,
+                      reinterpret_cast<const int*>(work), num_work,
+                      reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv, causal, scale,
+                      out, ldo, reinterpret_cast<float*>(o_part), reinterpret_cast<float*>(lse_part),
+                      reinterpret_cast<float*>(lse_out), status, stream);
+}
+
+// Paged attention whose output rows are scattered to `world` peer buffers (see AttnArgs):
+// token t goes to peer_ptrs[t / peer_tokens], row t % peer_tokens, row stride ldo.
+int ab200_attention_scatter(const void* q, long long ldq, const void* k, const void* v,
+                            long long num_blocks, int block_size, const void* block_tables,
+                            int max_blocks, const void* work, int num_work,
+                            const void* tok_splits, int max_splits, long long T, int Hq, int Hkv,
+                            int D, float scale, const void* const* peer_ptrs, int world,
+                            int peer_tokens, long long ldo, void* o_part, void* lse_part,
+                            int tile_keys, int* status, cudaStream_t stream) {
+  if (num_work <= 0 || T <= 0) return 0;
+  if ((ldq % 8) || (ldo % 8) || peer_tokens <= 0) return -2;
+  if (max_splits > 1 && (o_part == nullptr || lse_part == nullptr || tok_splits == nullptr)) return -2;
+  AB200_ATTN_DISPATCH(q, ldq, k, v, 0, num_blocks, block_size,
+                      reinterpret_cast<const int*>(block_tables), max_blocks,
+                      reinterpret_cast<const int*>(work), num_work,
+                      reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv, 1, scale,
+                      const_cast<void*>(peer_ptrs[0]), ldo, reinterpret_cast<float*>(o_part),
+                      reinterpret_cast<float*>(lse_part), nullptr, status, stream, peer_ptrs, world,
+                      peer_tokens);
 }
 
 }  // extern "C"

@@ -47,6 +47,13 @@ struct GemmArgs {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   int* status;
+  // Peer scatter (Ulysses sequence->head exchange fused into the epilogue): when
+  // peer_cols > 0, output feature f goes to buffer peer_out[f / peer_cols], column
+  // f % peer_cols, row (token + peer_row_off). The buffers are the ranks' symmetric heaps,
+  // reached with plain peer stores over NVLink.
+  int peer_cols;
+  long long peer_row_off;
+  __nv_bfloat16* peer_out[16];
 };
 
 __device__ __forceinline__ float gelu_erf(float x) {
@@ -273,6 +280,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + a_row * p.ldo + col;
+          if (p.peer_cols > 0)  // a 16-column chunk never straddles a destination (peer_cols % 16 == 0)
+            dst = p.peer_out[col / p.peer_cols] + (a_row + p.peer_row_off) * p.ldo +
+                  col % p.peer_cols;
 #pragma unroll
           for (int t = 0; t < 16; t += 8) {
             if (col + t + 8 <= p.rows_b) {
@@ -288,6 +298,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // accumulator holds out^T: this thread owns output feature a_row
           const float bias = (p.bias != nullptr) ? __bfloat162float(p.bias[a_row]) : 0.f;
           __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out);
+          long long o_col = a_row, o_row_off = 0;
+          if (p.peer_cols > 0) {
+            o = p.peer_out[a_row / p.peer_cols];
+            o_col = a_row % p.peer_cols;
+            o_row_off = p.peer_row_off;
+          }
 #pragma unroll
           for (int t = 0; t < 16; ++t) {
             const long long b_row = b0 + c0 + t;
@@ -295,7 +311,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
               float x = v[t] + bias;
               if (p.act == 1) x = gelu_erf(x);
               if (p.residual != nullptr) x += __bfloat162float(p.residual[b_row * p.ldr + a_row]);
-              o[b_row * p.ldo + a_row] = __float2bfloat16(x);
+              o[(b_row + o_row_off) * p.ldo + o_col] = __float2bfloat16(x);
             }
           }
         }
@@ -429,11 +445,12 @@ size_t ab200_linear_bf16_workspace_bytes(int M, int N, int K) {
   return (size_t)8 * (size_t)M * (size_t)N * sizeof(float);
 }
 
-// force_splits: 0 = heuristic, >0 = use exactly this split-K factor (feature-major only).
-int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out,
-                      long long ldo, int M, int N, int K, const void* bias, const void* residual,
-                      long long ldr, int act, void* workspace, size_t workspace_bytes,
-                      int force_splits, int* status, cudaStream_t stream) {
+static int launch_linear(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                         long long ldo, int M, int N, int K, const void* bias,
+                         const void* residual, long long ldr, int act, void* workspace,
+                         size_t workspace_bytes, int force_splits, int* status,
+                         cudaStream_t stream, const void* const* peer_ptrs, int world,
+                         int peer_cols, long long peer_row_off) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (N % 8) || (ldx % 8) || (ldw % 8) || (ldo % 8) ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
@@ -441,16 +458,27 @@ int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw
     return -2;
   if (residual != nullptr && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -2;
 
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -3;
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return -3;
-    attr_set = true;
+    attr_set[dev] = true;
   }
 
   GemmArgs a;
   memset(&a, 0, sizeof(a));
+  if (peer_cols > 0) {
+    if (world < 1 || world > 16 || (peer_cols % 16) || N != world * peer_cols) return -2;
+    a.peer_cols = peer_cols;
+    a.peer_row_off = peer_row_off;
+    for (int i = 0; i < world; ++i)
+      a.peer_out[i] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(peer_ptrs[i]));
+    force_splits = 1;  // partial sums would need the scatter in the reduce kernel as well
+  }
   a.K = K;
   a.kblocks_total = (K + kBlockK - 1) / kBlockK;
   a.status = status;
@@ -543,6 +571,29 @@ int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw
   return 0;
 }
 
+
+// force_splits: 0 = heuristic, >0 = use exactly this split-K factor (feature-major only).
+int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                      long long ldo, int M, int N, int K, const void* bias, const void* residual,
+                      long long ldr, int act, void* workspace, size_t workspace_bytes,
+                      int force_splits, int* status, cudaStream_t stream) {
+  return launch_linear(x, ldx, w, ldw, out, ldo, M, N, K, bias, residual, ldr, act, workspace,
+                       workspace_bytes, force_splits, status, stream, nullptr, 0, 0, 0);
+}
+
+// Linear layer whose output columns are scattered to `world` peer buffers: feature f of
+// token m lands in peer_ptrs[f / peer_cols] at row (m + peer_row_off), column f % peer_cols
+// (row stride ldo). N must equal world * peer_cols. The caller synchronises the ranks
+// (ab200_barrier) before the destination buffers are read.
+int ab200_linear_bf16_scatter(const void* x, long long ldx, const void* w, long long ldw,
+                              const void* const* peer_ptrs, int world, int peer_cols,
+                              long long peer_row_off, long long ldo, int M, int N, int K,
+                              int* status, cudaStream_t stream) {
+  if (peer_cols <= 0 || world <= 0) return -2;
+  return launch_linear(x, ldx, w, ldw, const_cast<void*>(peer_ptrs[0]), ldo, M, N, K, nullptr,
+                       nullptr, 0, 0, nullptr, 0, 1, status, stream, peer_ptrs, world, peer_cols,
+                       peer_row_off);
+}
 
 // out[M,N] = x[M,K] * wt[K,N] with wt row-major (N contiguous): exercises the
 // MN-major shared-memory descriptor for the B operand. N must be a multiple of 64.

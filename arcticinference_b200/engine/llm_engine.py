@@ -33,6 +33,12 @@ class LLMEngine:
             shard = comm.shard_spec()
         self.comm = comm
         self.runner = ModelRunner(config, self.device, comm=comm, shard=shard)
+        if comm is not None and getattr(comm, "fused", False):
+            m = self.runner.model
+            sp = config.parallel.sp
+            max_tokens = (config.scheduler.max_num_batched_tokens + sp - 1) // sp * sp + sp
+            comm.setup(max_tokens, max_tokens, m.blk_rows, config.model.hidden_size,
+                       sp * m.h * m.D)
         self.runner.load_model()
         self.num_blocks = self.runner.determine_num_blocks()
         self.runner.init_kv_cache(self.num_blocks)

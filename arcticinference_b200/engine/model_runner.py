@@ -63,6 +63,9 @@ class ModelRunner:
         self.proposer = None          # set by the engine when speculation is configured
         self.suffix_cache = None
         self._graphs = {}
+        self._graph_pool = None
+        self._graph_sizes = None
+        self.graph_replays = 0
         self._stage_cap = 0
         self._h_stage = None
         self._stage_events = [None, None]
@@ -267,21 +270,73 @@ class ModelRunner:
         from .sampler import sample_full
         return sample_full(logits, sched, rows)
 
+    # ------------------------------------------------------------- CUDA graphs
+    def graph_pool(self):
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
+
+    def _decode_graph(self, out: SchedulerOutput):
+        """The captured graph for this step, or None when the step must run eagerly."""
+        if self.config.enforce_eager or self.device.type != "cuda":
+            return None
+        for s in out.scheduled:
+            if not s.samples or s.num_tokens != s.num_draft + 1:
+                return None
+            sp = s.request.sampling_params
+            if not sp.greedy or sp.needs_full_logits:
+                return None
+        from .cuda_graph import DecodeGraph, bucket_for, canonical_sizes
+        mode = self.choose_mode(out.total_tokens)
+        mult = self.sp if mode == "sp" else 1
+        if self._graph_sizes is None:
+            self._graph_sizes = canonical_sizes(512)
+        bucket = bucket_for((out.total_tokens + mult - 1) // mult, self._graph_sizes)
+        if bucket is None:
+            return None
+        bucket *= mult
+        # every sequence needs a block-table row, plus one for the padding sequence
+        if len(out.scheduled) + 1 > bucket and out.total_tokens < bucket:
+            return None
+        key = (mode, bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            g = DecodeGraph(self, mode, bucket)
+            g.fill(out)
+            try:
+                g.capture()
+            except Exception as e:  # keep serving eagerly if this shape cannot be captured
+                import logging
+                logging.getLogger(__name__).warning("CUDA graph capture failed for %s: %s", key, e)
+                g = False
+            self._graphs[key] = g
+        return g or None
+
     # ------------------------------------------------------------------- step
     @torch.inference_mode()
     def execute(self, out: SchedulerOutput) -> StepResult:
         sched = out.scheduled
-        batch, rows = self.prepare(out)
-        self.mode_counts[batch.mode] += 1
         new_tokens: dict = {}
         drafts: dict = {}
-        if batch.logits_indices.numel() == 0:
-            # pure prefill chunk: KV only
-            self.model.forward(batch, self.kv)
-            return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)
-        hidden = self.model.forward(batch, self.kv)
-        logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
-        ids_dev = self._sample(logits, sched, rows)
+        g = self._decode_graph(out)
+        if g is not None:
+            rows = g.fill(out)
+            self.mode_counts[g.mode] += 1
+            self.graph_replays += 1
+            ids_dev, hidden = g.replay()
+            self.h2d_total += g.h64.numel() * 8 + g.h32.numel() * 4
+            num_tokens, mode = g.bucket, g.mode
+        else:
+            batch, rows = self.prepare(out)
+            self.mode_counts[batch.mode] += 1
+            num_tokens, mode = batch.num_tokens, batch.mode
+            if batch.logits_indices.numel() == 0:
+                # pure prefill chunk: KV only
+                self.model.forward(batch, self.kv)
+                return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)
+            hidden = self.model.forward(batch, self.kv)
+            logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
+            ids_dev = self._sample(logits, sched, rows)
         ids = ids_dev.tolist()  # device -> host; synchronises the step
         self.d2h_total += ids_dev.numel() * 8
         accepted_rows = []
@@ -302,4 +357,4 @@ class ModelRunner:
         if self.proposer is not None or self.suffix_cache is not None:
             from ..spec_decode.propose import propose_drafts
             drafts = propose_drafts(self, sched, rows, new_tokens, hidden, accepted_rows)
-        return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)
+        return StepResult(new_tokens, drafts, num_tokens, mode)

@@ -238,13 +238,25 @@ class LlamaForCausalLM(LlamaModel):
                                                 self.scale)
         else:
             attn = ops.attention(q, kv.k[layer], kv.v[layer], meta, h, hkv, D, self.scale)
-        return ops.linear(attn, self._o_w(lw, mode))
+        return self._linear_reduce(attn, self._o_w(lw, mode), mode)
 
     def _mlp_block(self, lw, x, mode):
         gu = ops.linear(x, self._gu_w(lw, mode))
         nblk = self.n_stored if (mode == "sp" or self.n_stored == 1) else 1
         act = ops.silu_mul_blocked(gu, nblk)
-        return ops.linear(act, self._down_w(lw, mode))
+        return self._linear_reduce(act, self._down_w(lw, mode), mode)
+
+    def _linear_reduce(self, x, w, mode):
+        """Row-parallel linear followed by the reduction its mode needs. With the fused
+        communicator the GEMM writes its partial product straight into the symmetric heap."""
+        comm = self.comm
+        need = comm is not None and ((mode == "tp" and comm.ways > 1) or
+                                     (mode == "sp" and comm.tp > 1))
+        if need and comm.fused:
+            t = ops.linear(x, w, out=comm.reduce_buffer(x.shape[0], w.shape[0]))
+        else:
+            t = ops.linear(x, w)
+        return self._reduce(t, mode) if need else t
 
     def _reduce(self, t, mode):
         comm = self.comm
@@ -266,10 +278,9 @@ class LlamaForCausalLM(LlamaModel):
                 x = ops.rmsnorm(residual, lw.input_norm, eps)
             else:
                 x = ops.rmsnorm(h, lw.input_norm, eps, residual=residual)
-            h = self._reduce(self._attention_block(lw, x, batch, kv, l, mode, meta, positions,
-                                                   slots, q_only), mode)
+            h = self._attention_block(lw, x, batch, kv, l, mode, meta, positions, slots, q_only)
             x = ops.rmsnorm(h, lw.post_norm, eps, residual=residual)
-            h = self._reduce(self._mlp_block(lw, x, mode), mode)
+            h = self._mlp_block(lw, x, mode)
         return h, residual
 
     # ------------------------------------------------------------------ forward
@@ -278,6 +289,8 @@ class LlamaForCausalLM(LlamaModel):
         cfg, comm, mode = self.cfg, self.comm, batch.mode
         eps = cfg.rms_norm_eps
         ids, positions, slots = batch.input_ids, batch.positions, batch.slots
+        if comm is not None and comm.fused:
+            comm.begin_forward()
         if mode == "sp" and comm is not None and comm.sp > 1:
             ids = comm.local_token_slice(ids)  # contiguous N/SP slice of this rank
         h = ops.embedding(ids, self.embed)

@@ -251,11 +251,13 @@ class AttentionMetadata:
     num_work: int = 0
     o_part: torch.Tensor | None = None
     lse_part: torch.Tensor | None = None
+    tile_keys: int = 128     # 64 for decode-shaped calls (few query rows per sequence)
     extra: dict = field(default_factory=dict)
 
 
 def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: int = 148,
-                        Hkv: int = 1, seq_rows=None, allow_split: bool = True):
+                        Hkv: int = 1, seq_rows=None, allow_split: bool = True,
+                        max_splits_cap: int = 16):
     """Pure-host planner. Returns (work [n,8] int32 ndarray, tok_splits [T] int32, max_splits).
 
     Query tokens of a sequence are cut into tiles of 128/G tokens. When the call has too few
@@ -266,6 +268,8 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
     T = int(sum(q_lens))
     tok_splits = np.ones(max(T, 1), dtype=np.int32)
     n_tiles_total = sum((ql + tpt - 1) // tpt for ql in q_lens)
+    if q_lens and max(q_lens) * G <= 32:
+        num_sms *= 2  # decode-shaped calls run two CTAs per SM (64-key tiles)
     t0 = 0
     max_splits = 1
     for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
@@ -276,7 +280,7 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
         ns = 1
         if allow_split and n_tiles_total * Hkv < num_sms and key_tiles > 4:
             want = max(1, num_sms // max(1, n_tiles_total * Hkv))
-            ns = int(min(16, want, max(1, key_tiles // 2)))
+            ns = int(min(16, max_splits_cap, want, max(1, key_tiles // 2)))
         tiles_per_split = (key_tiles + ns - 1) // ns
         ns = (key_tiles + tiles_per_split - 1) // tiles_per_split
         max_splits = max(max_splits, ns)
@@ -295,6 +299,11 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
         rows.sort(key=lambda r: -(min(r[5], r[3] + r[2]) - r[4]))
     work = np.asarray(rows, dtype=np.int32).reshape(-1, 8)
     return work, tok_splits, max_splits
+
+
+def pick_tile_keys(q_lens, G: int) -> int:
+    """64-key tiles when every sequence's query rows fit one warp of the 128-row tile."""
+    return 64 if q_lens and max(q_lens) * G <= 32 else 128
 
 
 def build_attention_metadata(q_lens, kv_lens, block_tables, G, Hq, D, device, causal=True,
@@ -316,6 +325,7 @@ def build_attention_metadata(q_lens, kv_lens, block_tables, G, Hq, D, device, ca
     meta.block_tables = block_tables
     meta.max_splits = max_splits
     meta.num_work = work.shape[0]
+    meta.tile_keys = pick_tile_keys(q_lens, G)
     if max_splits > 1 and dev.type == "cuda":
         meta.o_part = torch.empty(max_splits, T, Hq, D, dtype=torch.float32, device=dev)
         meta.lse_part = torch.empty(max_splits, T, Hq, dtype=torch.float32, device=dev)
@@ -349,7 +359,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         k_cache.shape[2], bt.data_ptr(), bt.shape[1], meta.work.data_ptr(), meta.num_work,
         nat.ptr(meta.tok_splits), meta.max_splits, T, Hq, Hkv, D, 1 if causal else 0,
         float(scale), out.data_ptr(), out.stride(0), nat.ptr(meta.o_part), nat.ptr(meta.lse_part),
-        nat.ptr(lse_out), nat.status_buffer(q.device).data_ptr(), nat.stream_ptr())
+        nat.ptr(lse_out), meta.tile_keys, nat.status_buffer(q.device).data_ptr(), nat.stream_ptr())
     nat.check(rc, "attention")
     launch_counter.add(2 if meta.max_splits > 1 else 1)
     return out
@@ -374,7 +384,7 @@ def attention_contiguous(q, k, v, seq_lens, H: int, D: int, scale: float | None 
     rc = nat.lib().ab200_attention(
         q.data_ptr(), q.stride(0), k.data_ptr(), v.data_ptr(), k.stride(0), T, 0, None, 0,
         meta.work.data_ptr(), meta.num_work, None, 1, T, H, H, D, 1 if causal else 0, float(scale),
-        out.data_ptr(), out.stride(0), None, None, None,
+        out.data_ptr(), out.stride(0), None, None, None, 128,
         nat.status_buffer(q.device).data_ptr(), nat.stream_ptr())
     nat.check(rc, "attention_contiguous")
     launch_counter.add(1)

@@ -52,7 +52,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_gather_rows": (I, [P, LL, P, P, LL, I, P]),
         "ab200_argmax_sample": (I, [P, I, LL, LL, I, P, P, P, P, LL, P]),
         "ab200_attention": (I, [P, LL, P, P, LL, LL, I, P, I, P, I, P, I, LL, I, I, I, I, F, P,
-                                LL, P, P, P, P, P]),
+                                LL, P, P, P, I, P, P]),
     }
     for name, (res, args) in sigs.items():
         if hasattr(L, name):

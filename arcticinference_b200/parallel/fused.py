@@ -1,0 +1,172 @@
+"""Collectives fused into the compute kernels over NVLink peer memory.
+
+Every rank allocates one symmetric heap (``torch.distributed._symmetric_memory``)
+that all ranks map. The hot exchanges then happen inside the kernels:
+
+* sequence -> head exchange (the reference's first ``all_to_all_single``,
+  arctic_inference/vllm/ulysses.py:436-438): the QKV projection GEMM's epilogue
+  stores each head block's columns directly into the owning rank's ``qkv`` buffer
+  (``ab200_linear_bf16_scatter``), rows in global token order;
+* head -> sequence exchange (ulysses.py:450-455): the attention kernel's epilogue
+  stores each token's output row into the buffer of the rank that owns the token
+  (``ab200_attention_scatter``); the o_proj GEMM then reads local memory only;
+* tensor-parallel reductions of shift mode: the row-parallel GEMM writes its
+  partial product into the heap and ``ab200_allreduce`` sums all ranks' partials
+  with peer loads (fp32 accumulation in rank order, so all ranks get the same bits).
+
+Between a producer kernel and its consumers runs ``ab200_barrier`` (flag exchange
+with bounded waits). All loads of remote data are plain peer loads or TMA loads
+from *local* memory; nothing here uses cluster-multicast loads.
+
+Supported shapes of the rank grid: TP=1 x SP=N (with or without shift) and TP=N x
+SP=1. TP x SP grids with both > 1 use the library-collective communicator.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import logging
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import native
+from .comm import Communicator
+
+logger = logging.getLogger(__name__)
+
+_ALIGN = 1 << 12
+
+
+def _ptr_array(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class FusedCommunicator(Communicator):
+    fused = True
+
+    def __init__(self, tp: int, sp: int, device: torch.device):
+        super().__init__(tp, sp, device)
+        if tp > 1 and sp > 1:
+            raise NotImplementedError("fused communicator supports TP=1 x SP=N or TP=N x SP=1")
+        self._heap = None
+        self._layout = None
+        self._ar_index = 0
+        self._declared = False
+
+    # ------------------------------------------------------------------ heap
+    def setup(self, max_tokens: int, max_tp_tokens: int, blk_rows: int, hidden: int,
+              attn_cols: int) -> None:
+        """Allocate and exchange the symmetric heap. ``max_tokens``: largest (padded) step;
+        ``max_tp_tokens``: largest tensor-parallel step; ``attn_cols`` = SP * h * D."""
+        import torch.distributed._symmetric_memory as symm_mem
+        W = self.ways
+        n_local = (max_tokens + self.sp - 1) // self.sp
+        sizes = {
+            "flags": 4096,
+            "qkv": max_tokens * blk_rows * 2 if self.sp > 1 else 0,
+            "attn": n_local * attn_cols * 2 if self.sp > 1 else 0,
+            "ar0": max_tp_tokens * hidden * 2,
+            "ar1": max_tp_tokens * hidden * 2,
+        }
+        off, layout = 0, {}
+        for k, v in sizes.items():
+            layout[k] = (off, v)
+            off += (v + _ALIGN - 1) // _ALIGN * _ALIGN
+        self._layout = layout
+        self._heap = symm_mem.empty(off, dtype=torch.uint8, device=self.device)
+        self._heap.zero_()
+        self._hdl = symm_mem.rendezvous(self._heap, dist.group.WORLD)
+        self._peer_base = [int(p) for p in self._hdl.buffer_ptrs]
+        assert len(self._peer_base) == W
+        self._max_tokens, self._max_tp_tokens = max_tokens, max_tp_tokens
+        self._blk_rows, self._hidden, self._attn_cols = blk_rows, hidden, attn_cols
+        self._flag_ptrs = _ptr_array([b + layout["flags"][0] for b in self._peer_base])
+        self._epoch_ptr = self._peer_base[self.rank] + layout["flags"][0] + 1024
+        self._qkv_ptrs = _ptr_array([b + layout["qkv"][0] for b in self._peer_base])
+        self._ar_ptrs = [_ptr_array([b + layout[k][0] for b in self._peer_base])
+                         for k in ("ar0", "ar1")]
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+        L = native.lib()
+        P, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        native.declare("ab200_barrier", I, [P, I, I, P, P, P])
+        native.declare("ab200_allreduce", I, [P, I, P, P, LL, P])
+        native.declare("ab200_gather_rows_peers", I, [P, I, LL, P, P, LL, I, P])
+        native.declare("ab200_linear_bf16_scatter", I, [P, LL, P, LL, P, I, I, LL, LL, I, I, I, P, P])
+        native.declare("ab200_attention_scatter", I, [P, LL, P, P, LL, I, P, I, P, I, P, I, LL, I, I,
+                                                      I, F, P, I, I, LL, P, P, I, P, P])
+        self._lib = L
+
+    def _view(self, key: str, rows: int, cols: int) -> torch.Tensor:
+        off, size = self._layout[key]
+        assert rows * cols * 2 <= size, "symmetric heap region %s too small" % key
+        return self._heap[off:off + rows * cols * 2].view(torch.bfloat16).view(rows, cols)
+
+    def device_barrier(self) -> None:
+        rc = self._lib.ab200_barrier(self._flag_ptrs, self.rank, self.ways, self._epoch_ptr,
+                                     native.status_buffer(self.device).data_ptr(),
+                                     native.stream_ptr())
+        native.check(rc, "barrier")
+        ops.launch_counter.add(1)
+
+    def begin_forward(self) -> None:
+        self._ar_index = 0
+
+    # ------------------------------------------------------- Ulysses exchanges
+    def qkv_scatter_heads(self, x_local, wqkv, blk_rows: int) -> torch.Tensor:
+        n = x_local.shape[0]
+        N = n * self.sp
+        s = self.topo.sp_rank
+        rc = self._lib.ab200_linear_bf16_scatter(
+            x_local.data_ptr(), x_local.stride(0), wqkv.data_ptr(), wqkv.stride(0),
+            self._qkv_ptrs, self.sp, blk_rows, s * n, blk_rows, n, wqkv.shape[0],
+            x_local.shape[1], native.status_buffer(self.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "linear_bf16_scatter")
+        ops.launch_counter.add(1)
+        self.device_barrier()
+        return self._view("qkv", N, blk_rows)
+
+    def attention_gather_tokens(self, q, k_cache, v_cache, meta, h, hkv, D, scale):
+        N = q.shape[0]
+        n = N // self.sp
+        s = self.topo.sp_rank
+        cols = self.sp * h * D
+        off = self._layout["attn"][0] + s * h * D * 2
+        ptrs = _ptr_array([b + off for b in self._peer_base])
+        bt = meta.block_tables
+        rc = self._lib.ab200_attention_scatter(
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0],
+            k_cache.shape[2], bt.data_ptr(), bt.shape[1], meta.work.data_ptr(), meta.num_work,
+            native.ptr(meta.tok_splits), meta.max_splits, N, h, hkv, D, float(scale), ptrs,
+            self.sp, n, cols, native.ptr(meta.o_part), native.ptr(meta.lse_part), meta.tile_keys,
+            native.status_buffer(self.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "attention_scatter")
+        ops.launch_counter.add(2 if meta.max_splits > 1 else 1)
+        self.device_barrier()
+        return self._view("attn", n, cols)
+
+    # --------------------------------------------------------------- reductions
+    def reduce_buffer(self, rows: int, cols: int) -> torch.Tensor:
+        """Heap buffer a row-parallel GEMM should write its partial product into."""
+        return self._view("ar%d" % (self._ar_index & 1), rows, cols)
+
+    def all_reduce_full(self, t: torch.Tensor) -> torch.Tensor:
+        rows, cols = t.shape
+        key = self._ar_index & 1
+        buf = self._view("ar%d" % key, rows, cols)
+        if t.data_ptr() != buf.data_ptr():
+            buf.copy_(t)
+        self._ar_index += 1
+        self.device_barrier()
+        out = torch.empty(rows, cols, dtype=t.dtype, device=t.device)
+        rc = self._lib.ab200_allreduce(self._ar_ptrs[key], self.ways, out.data_ptr(), None,
+                                       rows * cols, native.stream_ptr())
+        native.check(rc, "allreduce")
+        ops.launch_counter.add(1)
+        return out
+
+    def all_reduce_tp(self, t: torch.Tensor) -> torch.Tensor:
+        # TP=N x SP=1: the TP group is the whole grid
+        return self.all_reduce_full(t)

@@ -1,0 +1,135 @@
+"""Micro-benchmarks of the hot kernels, one case per invocation (also the workload for
+``ncu`` captures: each case launches its kernel a handful of times on inputs larger than
+L2 but of at most a few GB).
+
+    python benchmarks/kernel_bench.py --case gemm_prefill   [--iters 20]
+    python benchmarks/kernel_bench.py --case attn_decode --no-time   # for ncu: 3 launches only
+
+Timing: CUDA events around each launch, an L2 flush (256 MiB write) between iterations,
+median reported, with achieved TFLOP/s or GB/s against the measured peaks in
+MEASURED_PEAKS.json when present.
+"""
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from arcticinference_b200 import ops  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def R(*s):
+    return (torch.randn(*s, device=DEV) * 0.05).to(torch.bfloat16)
+
+
+def timeit(fn, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def paged(q_lens, kv_lens, Hq=32, Hkv=8, D=128, bs=64):
+    T = sum(q_lens)
+    nblk = [(k + bs - 1) // bs for k in kv_lens]
+    bt = torch.zeros(len(q_lens), max(nblk), dtype=torch.int32)
+    o = 1
+    for i, n in enumerate(nblk):
+        bt[i, :n] = torch.arange(o, o + n)
+        o += n
+    q, kc, vc = R(T, Hq * D), R(o, Hkv, bs, D), R(o, Hkv, bs, D)
+    meta = ops.build_attention_metadata(q_lens, kv_lens, bt.to(DEV), Hq // Hkv, Hq, D, DEV)
+    return q, kc, vc, meta
+
+
+CASES = {
+    # name: (kind, params)
+    "gemm_prefill": ("gemm", (8192, 28672, 4096)),
+    "gemm_prefill_qkv": ("gemm", (8192, 6144, 4096)),
+    "gemm_prefill_down": ("gemm", (8192, 4096, 14336)),
+    "gemm_decode": ("gemm", (32, 28672, 4096)),
+    "gemm_decode_o": ("gemm", (32, 4096, 4096)),
+    "gemm_decode_down": ("gemm", (32, 4096, 14336)),
+    "gemm_mid": ("gemm", (512, 28672, 4096)),
+    "attn_prefill": ("attn", ([8192], [8192])),
+    "attn_prefill_4x2048": ("attn", ([2048] * 4, [2048] * 4)),
+    "attn_decode": ("attn", ([1] * 32, [2000] * 32)),
+    "attn_decode_128": ("attn", ([1] * 128, [2000] * 128)),
+    "attn_decode_long": ("attn", ([1] * 8, [8000] * 8)),
+    "attn_verify": ("attn", ([4] * 32, [2000] * 32)),
+    "rmsnorm": ("rmsnorm", (8192, 4096)),
+    "silu_mul": ("silu", (8192, 14336)),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, choices=sorted(CASES))
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-time", action="store_true", help="three plain launches (for ncu)")
+    a = ap.parse_args()
+    hbm, tf, src = peaks()
+    kind, prm = CASES[a.case]
+    if kind == "gemm":
+        M, N, K = prm
+        x, w = R(M, K), R(N, K)
+        fn = lambda: ops.linear(x, w)
+        flops, byts = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    elif kind == "attn":
+        ql, kl = prm
+        q, kc, vc, meta = paged(ql, kl)
+        fn = lambda: ops.attention(q, kc, vc, meta, 32, 8, 128)
+        flops = sum(4.0 * a_ * (b_ - a_ / 2.0) * 32 * 128 for a_, b_ in zip(ql, kl))
+        byts = sum(b_ * 8 * 128 * 2 * 2.0 for b_ in kl) + 2.0 * sum(ql) * 32 * 128 * 2
+    elif kind == "rmsnorm":
+        T, H = prm
+        x, w, res = R(T, H), R(H), R(T, H)
+        fn = lambda: ops.rmsnorm(x, w, 1e-5, residual=res)
+        flops, byts = 0.0, 4.0 * T * H * 2
+    else:
+        T, I = prm
+        g = R(T, 2 * I)
+        fn = lambda: ops.silu_mul(g)
+        flops, byts = 0.0, 3.0 * T * I * 2
+    if a.no_time:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ops.check_status()
+        print("ran", a.case)
+        return
+    ms = timeit(fn, a.iters)
+    ops.check_status()
+    t = ms / 1e3
+    print(json.dumps({"case": a.case, "us": ms * 1e3, "tflops": flops / t / 1e12,
+                      "gbs": byts / t / 1e9, "frac_of_%s_bf16" % src: flops / t / 1e12 / tf,
+                      "frac_of_%s_hbm" % src: byts / t / 1e9 / hbm}))
+
+
+if __name__ == "__main__":
+    main()

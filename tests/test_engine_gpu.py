@@ -100,3 +100,20 @@ def test_sleep_wake_roundtrip():
         after = llm.generate([p], sp)[0].outputs[0].token_ids
         assert after == before
     ops.check_status()
+
+
+@pytest.mark.parametrize("model", ["llama-small", "llama-tiny-swiftkv"])
+def test_cuda_graph_decode_matches_eager(model):
+    sp = SamplingParams(temperature=0, max_tokens=12, ignore_eos=True)
+    prompts = [{"prompt_token_ids": list(range(5, 5 + n))} for n in (40, 7, 300, 65, 130)]
+    kw = dict(model=model, device="cuda:0", num_gpu_blocks_override=256, block_size=16,
+              max_model_len=1024)
+    eager = LLM(enforce_eager=True, **kw)
+    a = eager.generate(prompts, sp)
+    graphed = LLM(enforce_eager=False, **kw)
+    b = graphed.generate(prompts, sp)
+    ops.check_status()
+    assert graphed.engine.runner.graph_replays > 0
+    assert eager.engine.runner.graph_replays == 0
+    for x, y in zip(a, b):
+        assert x.outputs[0].token_ids == y.outputs[0].token_ids
