@@ -60,6 +60,23 @@ int ab200_linear_bf16_scatter(const void* x, long long ldx, const void* w, long 
                               long long peer_row_off, long long ldo, int M, int N, int K,
                               int* status, cudaStream_t stream);
 
+// ---- speculator.cu
+int ab200_spec_ln(const void* x, long long ldx, const void* w, const void* b, void* y,
+                  long long ldy, long long rows, int hidden, float eps, float out_scale,
+                  cudaStream_t stream);
+int ab200_mlp_spec_step(const void* proj, long long ldp, const void* emb, const void* tok,
+                        float emb_scale, const void* ln_w, const void* ln_b, void* out,
+                        long long ldo, long long rows, int dim, float eps, int tanh_approx,
+                        cudaStream_t stream);
+int ab200_sum_lstm(const void* gates, long long ldg, const void* emb, int emb_cols,
+                   const void* tok, float alpha, const void* prev_c, long long ldc,
+                   const void* w_cell, const void* b_cell, const void* w_state,
+                   const void* b_state, void* c_out, void* h_out, long long ldo, long long rows,
+                   int D, float eps, int tanh_approx, cudaStream_t stream);
+int ab200_verify_greedy(const void* input_ids, const void* target, const void* row_start,
+                        const void* num_draft, int R, int max_draft, void* accepted,
+                        void* next_tok, void* sel_row, void* out_tokens, cudaStream_t stream);
+
 // ---- comm.cu (pointer arrays are host arrays of `world` device pointers)
 int ab200_barrier(const void* const* flag_ptrs, int my_rank, int world, void* epoch_ctr,
                   int* status, cudaStream_t stream);

@@ -1,0 +1,239 @@
+"""Arctic draft models: the MLP speculator and the LSTM ("sum_lstm") speculator.
+
+Both turn the target model's last hidden state at the last accepted token, plus the
+newly sampled token, into ``n_predict`` further draft tokens, one head per token
+(arctic_inference/vllm/spec_dec/arctic_speculator.py:122-459 and :462-1067).
+
+MLP head i:   state = GELU(LN_i(W_proj,i . prev + (emb_w / state_w) . E_i[tok]))
+LSTM head i:  gates = W_projs[min(i,1)] . prev + (emb_w / state_w) . repeat4(E_forget[tok])
+              c = c_prev . sig(f) + GELU(LN_cell(g_c)) . sig(i);  state = GELU(LN_state(c)) . sig(o)
+then          logits = W_head . state,  tok = argmax,  prev = state
+with state_w = 0.5 ** (0.5 / n_predict), emb_w = sqrt((1 - state_w^2) * inner_dim / 2) and, when
+``scale_input`` is set, prev_0 = RMSNorm(hidden) / sqrt(2).
+
+Each step is three launches: the projection GEMM, one fused cell kernel (embedding gather +
+gate sum + both normalisations + activations, ``csrc/speculator.cu``) and the LM-head GEMM,
+followed by the arg-max kernel. On a multi-GPU engine every rank holds the whole draft model
+and computes the same draft: the speculator is small next to 180 GB of HBM, and replication
+removes the embedding all-reduce and the top-1 all-gather the reference needs per head
+(arctic_inference/vllm/spec_dec/vocab_parallel_embedding.py:437,
+arctic_speculator.py:332-342).
+
+Checkpoint format: ``config.json`` with ``n_predict, vocab_size, emb_dim, inner_dim, proj_dim,
+input_hidden_dim, tie_weights, tie_lstm_embs, scale_input, method``; dims may be dotted strings
+("4096.4096"). Weight names may carry a ``speculator.`` prefix. LSTM gate projections may be
+stored fused (``projs.N.weight``) or split (``forget_proj/input_proj/output_proj/cell_proj.N``),
+fused here in the order f, i, o, c (arctic_speculator.py:1027-1067).
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import dataclass
+from typing import Iterable, Optional
+
+import torch
+
+from .. import ops
+from ..ops import spec_ops
+
+
+def _first_dim(v) -> int:
+    if isinstance(v, str):
+        return int(v.split(".")[0])
+    if isinstance(v, (list, tuple)):
+        return int(v[0])
+    return int(v)
+
+
+@dataclass
+class SpeculatorConfig:
+    n_predict: int = 3
+    vocab_size: int = 128256
+    emb_dim: int = 4096
+    inner_dim: int = 4096
+    proj_dim: int = 4096
+    input_hidden_dim: int = 4096
+    tie_weights: bool = True
+    tie_lstm_embs: bool = True
+    scale_input: bool = True
+    method: str = "sum_lstm"      # "mlp" | "sum_rnn" | "sum_lstm"
+    num_lookahead_tokens: Optional[int] = None
+    base_model_archs: Optional[list] = None
+    architecture: str = "ArcticLSTMSpeculatorPreTrainedModel"
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "SpeculatorConfig":
+        archs = d.get("architectures") or ["MLPSpeculatorPreTrainedModel"]
+        arch = archs[0]
+        method = d.get("method")
+        if method is None:
+            method = "sum_rnn" if "LSTM" in arch or "MLPVariant" in arch else "mlp"
+        emb = _first_dim(d.get("emb_dim", 4096))
+        inner = _first_dim(d.get("inner_dim", 0)) or emb
+        return cls(n_predict=int(d.get("n_predict", 3)), vocab_size=int(d["vocab_size"]),
+                   emb_dim=emb, inner_dim=inner, proj_dim=_first_dim(d.get("proj_dim", inner)) or inner,
+                   input_hidden_dim=int(d.get("input_hidden_dim", emb)),
+                   tie_weights=bool(d.get("tie_weights", False)),
+                   tie_lstm_embs=bool(d.get("tie_lstm_embs", True)),
+                   scale_input=bool(d.get("scale_input", False)), method=method,
+                   num_lookahead_tokens=d.get("num_lookahead_tokens"),
+                   base_model_archs=d.get("base_model_archs"), architecture=arch)
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "SpeculatorConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return cls.from_dict(json.load(f))
+
+
+class ArcticSpeculator:
+    """Weights + the n-head proposal loop of either speculator type."""
+
+    LN_EPS = 1e-6
+
+    def __init__(self, cfg: SpeculatorConfig, device="cuda", dtype=torch.bfloat16):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.n_predict = cfg.n_predict
+        self.lstm = cfg.method == "sum_lstm"
+        self.state_weight = 0.5 ** (0.5 / cfg.n_predict)
+        self.emb_weight = math.sqrt((1 - self.state_weight ** 2) * (cfg.inner_dim / 2))
+        self.alpha = self.emb_weight / self.state_weight
+        self.w: dict[str, torch.Tensor] = {}
+
+    # ----------------------------------------------------------------- weight indexing
+    def _idx(self, kind: str, i: int) -> int:
+        if not self.cfg.tie_weights:
+            return i
+        return min(i, 1) if kind == "proj" else 0
+
+    def expected_tensors(self) -> dict:
+        c = self.cfg
+        shapes = {}
+        n = c.n_predict
+        if self.lstm:
+            shapes["forget_emb.0.weight"] = (c.vocab_size, c.emb_dim)
+            if not c.tie_lstm_embs:
+                for g in ("input", "output", "cell"):
+                    shapes["%s_emb.0.weight" % g] = (c.vocab_size, c.emb_dim)
+            shapes["projs.0.weight"] = (4 * c.proj_dim, c.input_hidden_dim)
+            if n > 1:
+                shapes["projs.1.weight"] = (4 * c.proj_dim, c.inner_dim)
+            for ln in ("cell_ln", "state_ln"):
+                shapes["%s.0.weight" % ln] = (c.inner_dim,)
+                shapes["%s.0.bias" % ln] = (c.inner_dim,)
+            shapes["head.0.weight"] = (c.vocab_size, c.inner_dim)
+        else:
+            heads = range(n)
+            for i in heads:
+                if self._idx("emb", i) == i:
+                    shapes["emb.%d.weight" % i] = (c.vocab_size, c.inner_dim)
+                    shapes["ln.%d.weight" % i] = (c.inner_dim,)
+                    shapes["ln.%d.bias" % i] = (c.inner_dim,)
+                    shapes["head.%d.weight" % i] = (c.vocab_size, c.inner_dim)
+                if self._idx("proj", i) == i:
+                    shapes["proj.%d.weight" % i] = (c.inner_dim,
+                                                    c.input_hidden_dim if i == 0 else c.inner_dim)
+        return shapes
+
+    def init_random(self, seed: int = 0, std: float = 0.02) -> None:
+        gen = torch.Generator(device=self.device)
+        for k, (name, shape) in enumerate(sorted(self.expected_tensors().items())):
+            gen.manual_seed(seed * 7919 + 31 * k + 5)
+            if name.endswith("ln.0.weight") or (".weight" in name and len(shape) == 1):
+                t = torch.ones(shape, device=self.device, dtype=self.dtype)
+            elif name.endswith(".bias"):
+                t = torch.zeros(shape, device=self.device, dtype=self.dtype)
+            else:
+                t = (torch.randn(*shape, generator=gen, device=self.device,
+                                 dtype=torch.float32) * std).to(self.dtype)
+            self.w[name] = t
+
+    def load_state(self, state: Iterable) -> None:
+        """(name, tensor) pairs in checkpoint naming (optionally prefixed ``speculator.``)."""
+        split: dict[tuple, dict] = {}
+        for name, t in state:
+            if name.startswith("speculator."):
+                name = name[len("speculator."):]
+            parts = name.split(".")
+            if parts[0] in ("forget_proj", "input_proj", "output_proj", "cell_proj"):
+                split.setdefault((parts[1], parts[2]), {})[parts[0]] = t
+                continue
+            self.w[name] = t.to(device=self.device, dtype=self.dtype).contiguous()
+        for (idx, kind), gates in split.items():
+            fused = torch.cat([gates[g] for g in ("forget_proj", "input_proj", "output_proj",
+                                                  "cell_proj")], 0)
+            self.w["projs.%s.%s" % (idx, kind)] = fused.to(device=self.device,
+                                                           dtype=self.dtype).contiguous()
+        if self.lstm and not self.cfg.tie_lstm_embs:
+            self.w["forget_emb.0.weight"] = torch.cat(
+                [self.w.pop("%s_emb.0.weight" % g) if g != "forget" else self.w["forget_emb.0.weight"]
+                 for g in ("forget", "input", "output", "cell")], 1).contiguous()
+        missing = [k for k in self.expected_tensors() if k not in self.w and "_emb" not in k[1:]]
+        if missing:
+            raise ValueError("speculator checkpoint lacks %s" % missing[:6])
+
+    def load_pretrained(self, path: str) -> None:
+        from .loader import iter_safetensors_dir
+        self.load_state(iter_safetensors_dir(path))
+
+    def weight_slots(self):
+        """(owner, key) pairs of every tensor, for sleep / wake and weight sync."""
+        return [(self.w, k) for k in list(self.w)]
+
+    def num_parameters(self) -> int:
+        return sum(t.numel() for t in self.w.values())
+
+    # ------------------------------------------------------------------------ forward
+    def propose(self, hidden: torch.Tensor, tokens: torch.Tensor,
+                n_predict: Optional[int] = None) -> torch.Tensor:
+        """hidden: [B, input_hidden_dim] target hidden states at the last accepted tokens;
+        tokens: [B] int64 the tokens just sampled. Returns draft tokens int64 [B, n_predict]."""
+        n = n_predict or self.n_predict
+        B = hidden.shape[0]
+        w = self.w
+        out = torch.empty(B, n, dtype=torch.int64, device=hidden.device)
+        prev = hidden
+        if self.cfg.scale_input:
+            prev = spec_ops.spec_ln(prev, None, None, self.LN_EPS, 1.0 / math.sqrt(2.0))
+        tok = tokens.to(torch.int64).contiguous()
+        c = None
+        for i in range(n):
+            if self.lstm:
+                gates = ops.linear(prev, w["projs.%d.weight" % min(i, 1)])
+                c, prev = spec_ops.sum_lstm(gates, w["forget_emb.0.weight"], tok, self.alpha, c,
+                                            w["cell_ln.0.weight"], w.get("cell_ln.0.bias"),
+                                            w["state_ln.0.weight"], w.get("state_ln.0.bias"),
+                                            self.LN_EPS)
+                head = w["head.0.weight"]
+            else:
+                k = self._idx("emb", i)
+                proj = ops.linear(prev, w["proj.%d.weight" % self._idx("proj", i)])
+                prev = spec_ops.mlp_spec_step(proj, w["emb.%d.weight" % k], tok, self.alpha,
+                                              w["ln.%d.weight" % k], w.get("ln.%d.bias" % k),
+                                              self.LN_EPS)
+                head = w["head.%d.weight" % k]
+            logits = ops.linear(prev, head)
+            tok, _ = ops.argmax_sample(logits)
+            tok = tok.clamp_(0, self.cfg.vocab_size - 1)
+            out[:, i] = tok
+        return out
+
+
+def build_speculator(path_or_cfg, device="cuda", seed: int = 0) -> ArcticSpeculator:
+    """A speculator from a checkpoint directory, or a random one from a config / preset dict."""
+    if isinstance(path_or_cfg, SpeculatorConfig):
+        spec = ArcticSpeculator(path_or_cfg, device)
+        spec.init_random(seed)
+        return spec
+    if isinstance(path_or_cfg, dict):
+        spec = ArcticSpeculator(SpeculatorConfig.from_dict(path_or_cfg), device)
+        spec.init_random(seed)
+        return spec
+    cfg = SpeculatorConfig.from_pretrained(path_or_cfg)
+    spec = ArcticSpeculator(cfg, device)
+    spec.load_pretrained(path_or_cfg)
+    return spec

@@ -51,6 +51,10 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_rope_cache": (I, [P, LL, P, P, P, P, P, LL, I, I, I, I, LL, I, P, P]),
         "ab200_gather_rows": (I, [P, LL, P, P, LL, I, P]),
         "ab200_argmax_sample": (I, [P, I, LL, LL, I, P, P, P, P, LL, P]),
+        "ab200_spec_ln": (I, [P, LL, P, P, P, LL, LL, I, F, F, P]),
+        "ab200_mlp_spec_step": (I, [P, LL, P, P, F, P, P, P, LL, LL, I, F, I, P]),
+        "ab200_sum_lstm": (I, [P, LL, P, I, P, F, P, LL, P, P, P, P, P, P, LL, LL, I, F, I, P]),
+        "ab200_verify_greedy": (I, [P, P, P, P, I, I, P, P, P, P, P]),
         "ab200_attention": (I, [P, LL, P, P, LL, LL, I, P, I, P, I, P, I, LL, I, I, I, I, F, P,
                                 LL, P, P, P, I, P, P]),
     }

@@ -117,3 +117,26 @@ def test_cuda_graph_decode_matches_eager(model):
     assert eager.engine.runner.graph_replays == 0
     for x, y in zip(a, b):
         assert x.outputs[0].token_ids == y.outputs[0].token_ids
+
+
+@pytest.mark.parametrize("spec", [
+    {"method": "suffix"},
+    {"method": "arctic", "model": "random", "num_speculative_tokens": 3,
+     "enable_suffix_decoding": True},
+])
+def test_speculative_decoding_preserves_output_on_gpu(spec):
+    kw = dict(model="llama-small", device="cuda:0", num_gpu_blocks_override=256, block_size=16,
+              max_model_len=1024)
+    prompts = [{"prompt_token_ids": [5, 6, 7, 8, 9, 10] * 8}, {"prompt_token_ids": list(range(40, 75))}]
+    sp = SamplingParams(temperature=0, max_tokens=32, ignore_eos=True)
+    base = LLM(**kw).generate(prompts, sp)
+    llm = LLM(speculative_config=spec, **kw)
+    outs = llm.generate(prompts, sp)
+    ops.check_status()
+    assert llm.engine.stats["draft_tokens"] > 0
+    match = sum(int(a == b) for x, y in zip(base, outs)
+                for a, b in zip(x.outputs[0].token_ids, y.outputs[0].token_ids))
+    total = sum(len(x.outputs[0].token_ids) for x in base)
+    # verification batches several tokens per row, which can flip bf16 near-ties
+    assert match >= 0.6 * total
+    assert all(len(o.outputs[0].token_ids) == 32 for o in outs)

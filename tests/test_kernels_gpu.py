@@ -229,3 +229,59 @@ def test_encoder_attention(H, D, seq_lens):
     out = ops.attention_contiguous(q, k, v, seq_lens, H, D)
     ops.check_status()
     _close(out, ref.attention_contiguous(q, k, v, seq_lens, H, D, 1 / math.sqrt(D)), 2e-2, 2e-2)
+
+
+# ------------------------------------------------------------------------------ speculator
+from arcticinference_b200.ops import spec_ops  # noqa: E402
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (37, 4096), (5, 1000), (3, 8192)])
+def test_spec_ln(rows, hidden):
+    x, w, b = _rand(rows, hidden), _rand(hidden), _rand(hidden)
+    _close(spec_ops.spec_ln(x, w, b), spec_ops.spec_ln_ref(x, w, b), 3e-2, 2e-2)
+    _close(spec_ops.spec_ln(x, None, None, 1e-6, 0.7071), spec_ops.spec_ln_ref(x, None, None, 1e-6, 0.7071),
+           2e-2, 2e-2)
+    buf = _rand(rows, 2 * hidden)   # pitched rows
+    _close(spec_ops.spec_ln(buf[:, hidden:], w, None), spec_ops.spec_ln_ref(buf[:, hidden:], w, None),
+           3e-2, 2e-2)
+
+
+@pytest.mark.parametrize("B,D", [(1, 4096), (33, 4096), (4, 1024), (7, 520)])
+@pytest.mark.parametrize("tanh", [False, True])
+def test_sum_lstm(B, D, tanh):
+    gates, prev_c = _rand(B, 4 * D), _rand(B, D)
+    emb = _rand(100, D)
+    tok = torch.randint(0, 100, (B,), device=DEV)
+    wc, bc, ws, bs = _rand(D), _rand(D, scale=0.1), _rand(D), _rand(D, scale=0.1)
+    for pc in (None, prev_c):
+        c, h = spec_ops.sum_lstm(gates, emb, tok, 1.3, pc, wc, bc, ws, bs, 1e-6, tanh)
+        c_ref, h_ref = spec_ops.sum_lstm_ref(gates, emb, tok, 1.3, pc, wc, bc, ws, bs, 1e-6, tanh)
+        _close(c, c_ref, 4e-2, 3e-2)
+        _close(h, h_ref, 6e-2, 3e-2)
+    emb4 = _rand(100, 4 * D)        # untied gate embeddings
+    c, h = spec_ops.sum_lstm(gates, emb4, tok, 0.9, prev_c, wc, None, ws, None)
+    c_ref, h_ref = spec_ops.sum_lstm_ref(gates, emb4, tok, 0.9, prev_c, wc, None, ws, None)
+    _close(c, c_ref, 4e-2, 3e-2)
+    _close(h, h_ref, 6e-2, 3e-2)
+
+
+def test_mlp_spec_step():
+    B, D = 19, 4096
+    proj, emb = _rand(B, D), _rand(50, D)
+    tok = torch.randint(0, 50, (B,), device=DEV)
+    w, b = _rand(D), _rand(D, scale=0.1)
+    _close(spec_ops.mlp_spec_step(proj, emb, tok, 2.1, w, b),
+           spec_ops.mlp_spec_step_ref(proj, emb, tok, 2.1, w, b), 5e-2, 3e-2)
+
+
+def test_verify_greedy():
+    input_ids = torch.tensor([10, 11, 12, 13, 20, 30, 31, 32], device=DEV)
+    target = torch.tensor([11, 12, 99, 14, 21, 31, 32, 33], device=DEV)
+    row_start = torch.tensor([0, 4, 5, -1], dtype=torch.int32, device=DEV)
+    num_draft = torch.tensor([3, 0, 2, 0], dtype=torch.int32, device=DEV)
+    acc, nxt, sel, out = spec_ops.verify_greedy(input_ids, target, row_start, num_draft, 3)
+    assert acc.tolist() == [2, 0, 2, 0]
+    assert nxt.tolist()[:3] == [99, 21, 33]
+    assert sel.tolist()[:3] == [2, 4, 7]
+    assert out.tolist()[:3] == [[11, 12, 99, -1], [21, -1, -1, -1], [31, 32, 33, -1]]
+    assert out.tolist()[3] == [-1, -1, -1, -1]
