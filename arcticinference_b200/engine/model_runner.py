@@ -66,6 +66,7 @@ class ModelRunner:
         self._graph_pool = None
         self._graph_sizes = None
         self.graph_replays = 0
+        self.cascade_steps = 0
         self._stage_cap = 0
         self._h_stage = None
         self._stage_events = [None, None]
@@ -157,6 +158,17 @@ class ModelRunner:
         sched = out.scheduled
         mode = self.choose_mode(out.total_tokens)
         N = out.total_tokens
+        plan = None
+        fc = self.config.forest_cascade
+        if fc.enabled and mode == "tp" and self.device.type == "cuda":
+            from . import forest_cascade as fca
+            if fca.gate(fc, [s.num_tokens for s in sched], all(s.samples for s in sched)):
+                plan = fca.plan_groups([s.request.block_ids for s in sched],
+                                       [s.start for s in sched], bs, fc)
+                if plan is not None:
+                    sched = [sched[i] for i in plan.order]
+                    out.scheduled = sched
+                    self.cascade_steps += 1
         pad_to = self.sp if mode == "sp" else 1
         Np = (N + pad_to - 1) // pad_to * pad_to
         q_lens, kv_lens = [], []
@@ -219,8 +231,21 @@ class ModelRunner:
             bt_t = torch.from_numpy(bt_pad).to(dev, non_blocking=True)
         else:
             q_lens_a, kv_lens_a = q_lens, kv_lens
-        meta = ops.build_attention_metadata(q_lens_a, kv_lens_a, bt_t, self.G, m.h, m.D, dev,
-                                            Hkv=m.hkv)
+        if plan is not None and Np == N:
+            from . import forest_cascade as fca
+            work, tok_splits, table, max_splits = fca.build_cascade_work(
+                plan, q_lens, kv_lens, [s.request.block_ids for s in sched], bs, self.G)
+            meta = ops.AttentionMetadata(list(q_lens), list(kv_lens), N)
+            meta.work = torch.from_numpy(work).to(dev, non_blocking=True)
+            meta.tok_splits = torch.from_numpy(tok_splits).to(dev, non_blocking=True)
+            meta.block_tables = torch.from_numpy(table).to(dev, non_blocking=True)
+            meta.max_splits, meta.num_work = max_splits, work.shape[0]
+            meta.tile_keys = ops.pick_tile_keys(q_lens, self.G)
+            meta.o_part = torch.empty(max_splits, N, m.h, m.D, dtype=torch.float32, device=dev)
+            meta.lse_part = torch.empty(max_splits, N, m.h, dtype=torch.float32, device=dev)
+        else:
+            meta = ops.build_attention_metadata(q_lens_a, kv_lens_a, bt_t, self.G, m.h, m.D, dev,
+                                                Hkv=m.hkv)
         batch = ForwardBatch(input_ids=d[:Np], positions=d[Np:2 * Np], slots=d[2 * Np:3 * Np],
                              attn_meta=meta, logits_indices=d[3 * Np:3 * Np + n_sel],
                              num_tokens=Np, mode=mode)
@@ -280,6 +305,9 @@ class ModelRunner:
         """The captured graph for this step, or None when the step must run eagerly."""
         if self.config.enforce_eager or self.device.type != "cuda":
             return None
+        fc = self.config.forest_cascade
+        if fc.enabled and len(out.scheduled) >= fc.min_batch_size:
+            return None  # cascade steps plan their own attention work list
         for s in out.scheduled:
             if not s.samples or s.num_tokens != s.num_draft + 1:
                 return None

@@ -18,7 +18,7 @@ from . import reference as ref
 
 __all__ = [
     "linear", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "silu_mul_blocked", "rope_cache",
-    "gather_rows", "argmax_sample", "AttentionMetadata", "build_attention_metadata",
+    "gather_rows", "argmax_sample", "AttentionMetadata", "build_attention_metadata", "pick_tile_keys", "plan_attention_work",
     "attention", "attention_contiguous", "check_status", "count_launches", "launch_counter",
 ]
 

@@ -140,3 +140,21 @@ def test_speculative_decoding_preserves_output_on_gpu(spec):
     # verification batches several tokens per row, which can flip bf16 near-ties
     assert match >= 0.6 * total
     assert all(len(o.outputs[0].token_ids) == 32 for o in outs)
+
+
+def test_forest_cascade_matches_plain_decode():
+    """Parallel samples of one long prompt share its KV blocks: the cascade reads them once."""
+    kw = dict(model="llama-small", device="cuda:0", num_gpu_blocks_override=512, block_size=16,
+              max_model_len=1024)
+    shared = list(range(7, 7 + 400))
+    prompts = [{"prompt_token_ids": shared + [900 + i]} for i in range(10)]
+    sp = SamplingParams(temperature=0, max_tokens=6, ignore_eos=True)
+    plain = LLM(**kw).generate(prompts, sp)
+    fca = LLM(forest_cascade_attn_configs="{}", **kw)
+    fca.generate(prompts[:1], sp)          # fills the prefix cache: later requests share blocks
+    outs = fca.generate(prompts, sp)
+    ops.check_status()
+    assert fca.engine.runner.cascade_steps > 0
+    match = sum(int(a == b) for x, y in zip(plain, outs)
+                for a, b in zip(x.outputs[0].token_ids, y.outputs[0].token_ids))
+    assert match >= 0.8 * 60
