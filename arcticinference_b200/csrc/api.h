@@ -60,6 +60,23 @@ int ab200_linear_bf16_scatter(const void* x, long long ldx, const void* w, long 
                               long long peer_row_off, long long ldo, int M, int N, int K,
                               int* status, cudaStream_t stream);
 
+// ---- gemm_fp8.cu
+int ab200_quant_fp8(const void* x, long long ldx, void* xq, long long ldq, void* sx_t,
+                    long long ld_sx, long long M, int K, cudaStream_t stream);
+int ab200_dequant_fp8(const void* wq, long long ldw, const void* sw, long long ld_sw, void* out,
+                      long long ldo, long long N, int K, cudaStream_t stream);
+int ab200_linear_w8a16(const void* x, long long ldx, const void* wq, long long ldw, const void* sw,
+                       long long ld_sw, void* out, long long ldo, int M, int N, int K,
+                       void* workspace, size_t workspace_bytes, int force_splits,
+                       const void* const* peer_ptrs, int world, int peer_cols,
+                       long long peer_row_off, int* status, cudaStream_t stream);
+size_t ab200_linear_fp8_workspace_bytes(int M, int N, int K);
+int ab200_linear_fp8(const void* xq, long long ldxq, const void* sx_t, long long ld_sx,
+                     const void* wq, long long ldw, const void* sw, long long ld_sw, void* out,
+                     long long ldo, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                     int force_splits, const void* const* peer_ptrs, int world, int peer_cols,
+                     long long peer_row_off, int* status, cudaStream_t stream);
+
 // ---- speculator.cu
 int ab200_spec_ln(const void* x, long long ldx, const void* w, const void* b, void* y,
                   long long ldy, long long rows, int hidden, float eps, float out_scale,

@@ -25,7 +25,18 @@ def _model_tensors(engine):
     prop = getattr(engine.runner, "proposer", None)
     if prop is not None and hasattr(prop, "weight_slots"):
         items.extend(prop.weight_slots())
-    return items
+    # an fp8 weight is two tensors (codes, block scales); its bf16 prefill shadow is derived
+    # data, dropped while asleep and rebuilt on wake
+    from ..models.quant import Fp8Weight
+    out = []
+    for owner, name in items:
+        t = _get(owner, name) if (isinstance(owner, dict) and name in owner) or \
+            (not isinstance(owner, dict) and hasattr(owner, name)) else None
+        if isinstance(t, Fp8Weight):
+            out.extend([(t, "q"), (t, "scale")])
+        else:
+            out.append((owner, name))
+    return out
 
 
 def _get(owner, name):
@@ -50,7 +61,13 @@ def sleep_engine(engine, level: int = 1) -> None:
     engine._sleep_store = {}
     if level == 2:
         seen = {}
+        from ..models.quant import Fp8Weight
+        engine._sleep_shadows = []
         for owner, name in _model_tensors(engine):
+            if isinstance(owner, Fp8Weight) and owner.shadow is not None:
+                owner.shadow = None
+                if owner not in engine._sleep_shadows:
+                    engine._sleep_shadows.append(owner)
             t = _get(owner, name)
             if not isinstance(t, torch.Tensor) or not t.is_cuda:
                 continue
@@ -79,6 +96,9 @@ def wake_engine(engine, tags=None) -> None:
                 restored[id(host)] = host.to(dev, non_blocking=True)
             _set(owner, name, restored[id(host)])
         engine._sleep_store = {}
+        for w in getattr(engine, "_sleep_shadows", []):
+            w.make_shadow()
+        engine._sleep_shadows = []
         engine._awake_tags.add("weights")
     if "kv_cache" in tags and "kv_cache" not in engine._awake_tags:
         engine.runner.init_kv_cache(engine.num_blocks)

@@ -1,0 +1,141 @@
+"""Block-scaled fp8 weights (e4m3, one fp32 scale per 128 x 128 block).
+
+:class:`Fp8Weight` behaves like the [N, K] matrix it stands for as far as the model code
+needs: ``shape``, row slices and column slices on 128 boundaries (the tensor-parallel shard
+views of shift parallelism), so ``ops.linear(x, w)`` works with either a bf16 tensor or an
+``Fp8Weight``. The layout matches fp8 block-quantised checkpoints (``weight`` +
+``weight_scale_inv``; reference: arctic_inference/vllm/spec_dec/fp8.py:140-180).
+"""
+
+from __future__ import annotations
+
+import torch
+
+BLOCK = 128
+FP8_MAX = 448.0
+
+
+class Fp8Weight:
+    """``shadow`` is an optional expanded bf16 copy of the same matrix. Decode streams the fp8
+    codes (half the bytes per step); long prefill is compute bound and multiplies the shadow
+    directly instead of expanding the codes on every call. Whether a model keeps shadows is a
+    memory decision made once at load time (:func:`quantize_model_fp8`)."""
+
+    __slots__ = ("q", "scale", "shadow")
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor, shadow: torch.Tensor = None):
+        assert q.dim() == 2 and scale.dim() == 2
+        self.q = q            # [N, K] float8_e4m3fn (row stride free)
+        self.scale = scale    # [N/128, K/128] fp32 (row stride free)
+        self.shadow = shadow  # [N, K] bf16 or None
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    @property
+    def device(self):
+        return self.q.device
+
+    @property
+    def is_cuda(self):
+        return self.q.is_cuda
+
+    def numel(self):
+        return self.q.numel()
+
+    def __getitem__(self, idx) -> "Fp8Weight":
+        if isinstance(idx, slice):
+            rows, cols = idx, slice(None)
+        else:
+            rows, cols = idx
+
+        def blk(s: slice, n: int) -> slice:
+            a, b, _ = s.indices(n)
+            if a % BLOCK or (b % BLOCK and b != n):
+                raise ValueError("fp8 weight slices must fall on 128 boundaries")
+            return slice(a // BLOCK, (b + BLOCK - 1) // BLOCK)
+
+        N, K = self.q.shape
+        return Fp8Weight(self.q[rows, cols], self.scale[blk(rows, N), blk(cols, K)],
+                         None if self.shadow is None else self.shadow[rows, cols])
+
+    def make_shadow(self) -> None:
+        self.shadow = self.dequantize().contiguous()
+
+    def dequantize(self) -> torch.Tensor:
+        N, K = self.q.shape
+        s = self.scale.repeat_interleave(BLOCK, 0)[:N].repeat_interleave(BLOCK, 1)[:, :K]
+        return (self.q.float() * s).to(torch.bfloat16)
+
+
+def quantize_weight_fp8(w: torch.Tensor) -> Fp8Weight:
+    """bf16 [N, K] -> e4m3 codes + per-block scales (scale = amax / 448)."""
+    N, K = w.shape
+    if N % BLOCK or K % BLOCK:
+        raise ValueError("fp8 block quantisation needs dimensions that are multiples of 128, "
+                         "got %s" % (tuple(w.shape),))
+    wf = w.float().view(N // BLOCK, BLOCK, K // BLOCK, BLOCK)
+    amax = wf.abs().amax(dim=(1, 3)).clamp_min(1e-10)
+    scale = amax / FP8_MAX
+    q = (wf / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return Fp8Weight(q.view(N, K).contiguous(), scale.contiguous())
+
+
+SHADOW_MAX_FRACTION = 0.2     # of the device's memory
+
+
+def model_fp8_weights(model) -> list:
+    out = []
+    for lw in model.layers:
+        for name in ("wqkv", "wo", "wgu", "wdown"):
+            w = getattr(lw, name)
+            if isinstance(w, Fp8Weight):
+                out.append(w)
+    if isinstance(getattr(model, "wkv_swiftkv", None), Fp8Weight):
+        out.append(model.wkv_swiftkv)
+    return out
+
+
+def quantize_model_fp8(model, prefill_shadow="auto") -> None:
+    """Replace the linear weights of a decoder with block-scaled fp8 (embeddings, norms and
+    the LM head stay in bf16, as in the fp8 checkpoints the reference serves).
+
+    ``prefill_shadow``: True / False / "auto". With "auto" the expanded bf16 copies are kept
+    when they take at most SHADOW_MAX_FRACTION of the GPU's memory (an 8B model's 14 GB on a
+    180 GB part), otherwise long prefill expands each weight into a shared scratch matrix."""
+    for lw in model.layers:
+        for name in ("wqkv", "wo", "wgu", "wdown"):
+            w = getattr(lw, name)
+            if isinstance(w, torch.Tensor):
+                setattr(lw, name, quantize_weight_fp8(w))
+    if getattr(model, "wkv_swiftkv", None) is not None and isinstance(model.wkv_swiftkv, torch.Tensor):
+        model.wkv_swiftkv = quantize_weight_fp8(model.wkv_swiftkv)
+    on_gpu = torch.cuda.is_available() and model.device.type == "cuda"
+    if on_gpu:
+        torch.cuda.empty_cache()
+    ws = model_fp8_weights(model)
+    if prefill_shadow == "auto":
+        need = sum(2 * w.numel() for w in ws)
+        total = torch.cuda.get_device_properties(model.device).total_memory if on_gpu else 0
+        prefill_shadow = on_gpu and need <= SHADOW_MAX_FRACTION * total
+    if prefill_shadow:
+        for w in ws:
+            w.make_shadow()
+
+
+def quant_activation_ref(x: torch.Tensor):
+    """Per-token, per-128-k dynamic quantisation (PyTorch restatement of quant_fp8_kernel).
+    Returns (xq float8 [M, K], sx_t fp32 [K/128, M])."""
+    M, K = x.shape
+    xf = x.float().view(M, K // BLOCK, BLOCK)
+    scale = xf.abs().amax(-1).clamp_min(1e-10) / FP8_MAX
+    q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.view(M, K), scale.t().contiguous()
+
+
+def linear_fp8_ref(x: torch.Tensor, w: Fp8Weight) -> torch.Tensor:
+    xq, sx_t = quant_activation_ref(x)
+    M, K = x.shape
+    xd = xq.float().view(M, K // BLOCK, BLOCK) * sx_t.t().unsqueeze(-1)
+    return (xd.view(M, K) @ w.dequantize().float().t()).to(torch.bfloat16)

@@ -17,7 +17,7 @@ import torch
 from . import reference as ref
 
 __all__ = [
-    "linear", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "silu_mul_blocked", "rope_cache",
+    "linear", "linear_fp8", "quant_fp8", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "silu_mul_blocked", "rope_cache",
     "gather_rows", "argmax_sample", "AttentionMetadata", "build_attention_metadata", "pick_tile_keys", "plan_attention_work",
     "attention", "attention_contiguous", "check_status", "count_launches", "launch_counter",
 ]
@@ -52,9 +52,106 @@ def check_status(device=None):
 _ACT = {None: 0, "none": 0, "gelu": 1}
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, act=None, out=None,
+def quant_fp8(x: torch.Tensor):
+    """bf16 [M, K] -> (e4m3 codes [M, K], scales fp32 [K/128, M]) per token and 128-wide k group."""
+    from ..models import quant
+    if not x.is_cuda:
+        return quant.quant_activation_ref(x)
+    nat = _native()
+    M, K = x.shape
+    xq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    sx_t = torch.empty(K // 128, M, dtype=torch.float32, device=x.device)
+    rc = nat.lib().ab200_quant_fp8(x.data_ptr(), x.stride(0), xq.data_ptr(), xq.stride(0),
+                                   sx_t.data_ptr(), sx_t.stride(0), M, K, nat.stream_ptr())
+    nat.check(rc, "quant_fp8")
+    launch_counter.add(1)
+    return xq, sx_t
+
+
+DEQUANT_MIN_TOKENS = 512
+_dequant_scratch: dict = {}
+
+
+def dequant_fp8(w) -> torch.Tensor:
+    """The weight as a bf16 matrix: its resident shadow copy when the model keeps one, else
+    expanded into a (per-device, reused) scratch matrix."""
+    if getattr(w, "shadow", None) is not None:
+        return w.shadow
+    if not w.is_cuda:
+        return w.dequantize()
+    nat = _native()
+    N, K = w.shape
+    idx = w.device.index
+    buf = _dequant_scratch.get(idx)
+    if buf is None or buf.numel() < N * K:
+        buf = torch.empty(max(N * K, 28672 * 4096), dtype=torch.bfloat16, device=w.device)
+        _dequant_scratch[idx] = buf
+    out = buf[:N * K].view(N, K)
+    rc = nat.lib().ab200_dequant_fp8(w.q.data_ptr(), w.q.stride(0), w.scale.data_ptr(),
+                                     w.scale.stride(0), out.data_ptr(), out.stride(0), N, K,
+                                     nat.stream_ptr())
+    nat.check(rc, "dequant_fp8")
+    launch_counter.add(1)
+    return out
+
+
+W8A16_MAX_TOKENS = 128
+
+
+def linear_fp8(x: torch.Tensor, w, out=None, force_splits: int = 0, peer=None,
+               mode: str = "auto") -> torch.Tensor:
+    """Block-scaled fp8 linear: x bf16 [M, K] is quantised on the fly; w is an ``Fp8Weight``.
+    ``peer`` = (ptr_array, world, peer_cols, row_off, ldo) scatters the output (see
+    ``ab200_linear_bf16_scatter``)."""
+    from ..models import quant
+    if not x.is_cuda:
+        y = quant.linear_fp8_ref(x, w)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    nat = _native()
+    M, K = x.shape
+    N = w.shape[0]
+    if M >= DEQUANT_MIN_TOKENS and peer is None and mode == "auto":
+        # long prefill: expand the weight once into bf16 scratch and run the bf16 GEMM, so the
+        # activations stay in bf16 and the tensor cores never wait on per-block rescaling
+        return linear(x, dequant_fp8(w), out=out)
+    ws = nat.workspace(x.device)
+    if peer is None:
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        out_ptr, ldo, pp, world, pcols, poff = out.data_ptr(), out.stride(0), None, 0, 0, 0
+    else:
+        pp, world, pcols, poff, ldo = peer
+        out_ptr = None
+    if M <= W8A16_MAX_TOKENS and mode != "w8a8":
+        # decode: weight-only fp8, activations stay bf16, weights are expanded inside the kernel
+        rc = nat.lib().ab200_linear_w8a16(
+            x.data_ptr(), x.stride(0), w.q.data_ptr(), w.q.stride(0), w.scale.data_ptr(),
+            w.scale.stride(0), out_ptr, ldo, M, N, K, ws.data_ptr(), ws.numel(), force_splits, pp,
+            world, pcols, poff, nat.status_buffer(x.device).data_ptr(), nat.stream_ptr())
+        nat.check(rc, "linear_w8a16 M=%d N=%d K=%d" % (M, N, K))
+        launch_counter.add(1)
+        return out
+    xq, sx_t = quant_fp8(x)
+    rc = nat.lib().ab200_linear_fp8(
+        xq.data_ptr(), xq.stride(0), sx_t.data_ptr(), sx_t.stride(0), w.q.data_ptr(),
+        w.q.stride(0), w.scale.data_ptr(), w.scale.stride(0), out_ptr, ldo, M, N, K,
+        ws.data_ptr(), ws.numel(), force_splits, pp, world, pcols, poff,
+        nat.status_buffer(x.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "linear_fp8 M=%d N=%d K=%d" % (M, N, K))
+    launch_counter.add(1)
+    return out
+
+
+def linear(x: torch.Tensor, w, bias=None, residual=None, act=None, out=None,
            force_splits: int = 0) -> torch.Tensor:
-    """``out = act(x @ w.T + bias) + residual``; x [M, K] (row stride free), w [N, K]."""
+    """``out = act(x @ w.T + bias) + residual``; x [M, K] (row stride free), w [N, K] bf16 or
+    an ``Fp8Weight``."""
+    if not isinstance(w, torch.Tensor):
+        assert bias is None and residual is None and act is None
+        return linear_fp8(x, w, out=out, force_splits=force_splits)
     if not x.is_cuda:
         y = ref.linear(x, w, bias, residual, act)
         if out is not None:

@@ -51,6 +51,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_rope_cache": (I, [P, LL, P, P, P, P, P, LL, I, I, I, I, LL, I, P, P]),
         "ab200_gather_rows": (I, [P, LL, P, P, LL, I, P]),
         "ab200_argmax_sample": (I, [P, I, LL, LL, I, P, P, P, P, LL, P]),
+        "ab200_quant_fp8": (I, [P, LL, P, LL, P, LL, LL, I, P]),
+        "ab200_dequant_fp8": (I, [P, LL, P, LL, P, LL, LL, I, P]),
+        "ab200_linear_w8a16": (I, [P, LL, P, LL, P, LL, P, LL, I, I, I, P, SZ, I, P, I, I, LL, P, P]),
+        "ab200_linear_fp8": (I, [P, LL, P, LL, P, LL, P, LL, P, LL, I, I, I, P, SZ, I, P, I, I, LL,
+                                 P, P]),
         "ab200_spec_ln": (I, [P, LL, P, P, P, LL, LL, I, F, F, P]),
         "ab200_mlp_spec_step": (I, [P, LL, P, P, F, P, P, P, LL, LL, I, F, I, P]),
         "ab200_sum_lstm": (I, [P, LL, P, I, P, F, P, LL, P, P, P, P, P, P, LL, LL, I, F, I, P]),

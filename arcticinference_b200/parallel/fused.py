@@ -119,6 +119,12 @@ class FusedCommunicator(Communicator):
         n = x_local.shape[0]
         N = n * self.sp
         s = self.topo.sp_rank
+        if not isinstance(wqkv, torch.Tensor) and n >= ops.DEQUANT_MIN_TOKENS:
+            wqkv = ops.dequant_fp8(wqkv)          # long prefill: expand once, bf16 GEMM
+        if not isinstance(wqkv, torch.Tensor):   # block-scaled fp8 weights
+            ops.linear_fp8(x_local, wqkv, peer=(self._qkv_ptrs, self.sp, blk_rows, s * n, blk_rows))
+            self.device_barrier()
+            return self._view("qkv", N, blk_rows)
         rc = self._lib.ab200_linear_bf16_scatter(
             x_local.data_ptr(), x_local.stride(0), wqkv.data_ptr(), wqkv.stride(0),
             self._qkv_ptrs, self.sp, blk_rows, s * n, blk_rows, n, wqkv.shape[0],

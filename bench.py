@@ -37,7 +37,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", type=str, default="llama-3.1-8b")
-    ap.add_argument("--quantization", type=str, default=None)
+    ap.add_argument("--quantization", type=str, default="fp8",
+                    help='"fp8" (block-scaled fp8 weights, bf16 activations; the named config) or "none" (bf16)')
     ap.add_argument("--requests-per-gpu", type=int, default=32)
     ap.add_argument("--input-len", type=int, default=2000)
     ap.add_argument("--output-len", type=int, default=250)
@@ -124,11 +125,12 @@ def main():
 
     from arcticinference_b200 import LLM, SamplingParams, ops
 
+    quant = None if str(args.quantization).lower() in ("none", "bf16", "") else args.quantization
     kw = dict(model=args.model, max_model_len=args.input_len + args.output_len + 64,
               max_num_batched_tokens=args.max_num_batched_tokens,
               max_num_seqs=max(256, args.requests_per_gpu * n_gpus),
               enable_prefix_caching=False, enforce_eager=args.enforce_eager,
-              quantization=args.quantization, speculative_config=args.speculative_config)
+              quantization=quant, speculative_config=args.speculative_config)
     if n_gpus > 1:
         kw.update(ulysses_sequence_parallel_size=n_gpus, enable_shift_parallel=True,
                   shift_parallel_threshold=args.shift_parallel_threshold)
@@ -205,7 +207,7 @@ def main():
             "value": value, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16" if not args.quantization else "fp8-weights/bf16-activations",
+            "dtype": "bf16" if not quant else "fp8-weights/bf16-activations",
             "data": "synthetic (uniform-random token ids, random-init weights)",
             "p50_ttft_ms": 1000 * statistics.median(ttfts) if ttfts else None,
             "p50_tpot_ms": 1000 * statistics.median(tpots) if tpots else None,

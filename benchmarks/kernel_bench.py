@@ -5,9 +5,11 @@ L2 but of at most a few GB).
     python benchmarks/kernel_bench.py --case gemm_prefill   [--iters 20]
     python benchmarks/kernel_bench.py --case attn_decode --no-time   # for ncu: 3 launches only
 
-Timing: CUDA events around each launch, an L2 flush (256 MiB write) between iterations,
-median reported, with achieved TFLOP/s or GB/s against the measured peaks in
-MEASURED_PEAKS.json when present.
+Timing: CUDA events around each launch, median reported, with achieved TFLOP/s or GB/s
+against the measured peaks in MEASURED_PEAKS.json when present. Every case keeps several
+copies of its large operand (weights, KV cache, activations) whose total exceeds twice the
+L2 capacity and rotates through them, so each timed launch reads its operands from HBM
+without the write-back traffic that a dirty flush buffer would add to the measurement.
 """
 
 import argparse
@@ -36,17 +38,25 @@ def R(*s):
     return (torch.randn(*s, device=DEV) * 0.05).to(torch.bfloat16)
 
 
-def timeit(fn, iters, warm=3):
-    for _ in range(warm):
-        fn()
+ROTATE_BYTES = 320 << 20      # > 2 x the 126 MB L2
+
+
+def copies_for(nbytes: int) -> int:
+    return max(1, min(64, -(-ROTATE_BYTES // max(int(nbytes), 1))))
+
+
+def timeit(fn, iters, warm=3, copies=1):
+    """``fn(i)`` launches the case on operand copy ``i % copies`` (``fn()`` when copies == 1:
+    such a case must stream more than L2 by itself)."""
+    call = (lambda i: fn()) if copies == 1 else (lambda i: fn(i % copies))
+    for i in range(max(warm, copies)):
+        call(i)
     torch.cuda.synchronize()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
     ts = []
-    for _ in range(iters):
-        flush.zero_()
+    for i in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        call(i)
         e1.record()
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1))
@@ -76,6 +86,12 @@ CASES = {
     "gemm_decode_o": ("gemm", (32, 4096, 4096)),
     "gemm_decode_down": ("gemm", (32, 4096, 14336)),
     "gemm_mid": ("gemm", (512, 28672, 4096)),
+    "gemm_fp8_prefill": ("gemm_fp8", (8192, 28672, 4096)),
+    "gemm_fp8_mid": ("gemm_fp8", (256, 28672, 4096)),
+    "gemm_fp8_decode": ("gemm_fp8", (32, 28672, 4096)),
+    "gemm_fp8_decode_128": ("gemm_fp8", (128, 28672, 4096)),
+    "gemm_fp8_decode_o": ("gemm_fp8", (32, 4096, 4096)),
+    "gemm_fp8_decode_down": ("gemm_fp8", (32, 4096, 14336)),
     "attn_prefill": ("attn", ([8192], [8192])),
     "attn_prefill_4x2048": ("attn", ([2048] * 4, [2048] * 4)),
     "attn_decode": ("attn", ([1] * 32, [2000] * 32)),
@@ -97,33 +113,44 @@ def main():
     kind, prm = CASES[a.case]
     if kind == "gemm":
         M, N, K = prm
-        x, w = R(M, K), R(N, K)
-        fn = lambda: ops.linear(x, w)
+        nc = copies_for(2 * N * K)
+        x, ws = R(M, K), [R(N, K) for _ in range(nc)]
+        fn = lambda i=0: ops.linear(x, ws[i])
         flops, byts = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    elif kind == "gemm_fp8":
+        from arcticinference_b200.models import quant
+        M, N, K = prm
+        nc = copies_for(N * K)
+        x, ws = R(M, K), [quant.quantize_weight_fp8(R(N, K)) for _ in range(nc)]
+        fn = lambda i=0: ops.linear(x, ws[i])
+        flops, byts = 2.0 * M * N * K, 2.0 * (M * K + M * N) + 1.0 * N * K
     elif kind == "attn":
         ql, kl = prm
-        q, kc, vc, meta = paged(ql, kl)
-        fn = lambda: ops.attention(q, kc, vc, meta, 32, 8, 128)
-        flops = sum(4.0 * a_ * (b_ - a_ / 2.0) * 32 * 128 for a_, b_ in zip(ql, kl))
         byts = sum(b_ * 8 * 128 * 2 * 2.0 for b_ in kl) + 2.0 * sum(ql) * 32 * 128 * 2
+        nc = copies_for(byts)
+        sets = [paged(ql, kl) for _ in range(nc)]
+        fn = lambda i=0: ops.attention(sets[i][0], sets[i][1], sets[i][2], sets[i][3], 32, 8, 128)
+        flops = sum(4.0 * a_ * (b_ - a_ / 2.0) * 32 * 128 for a_, b_ in zip(ql, kl))
     elif kind == "rmsnorm":
         T, H = prm
-        x, w, res = R(T, H), R(H), R(T, H)
-        fn = lambda: ops.rmsnorm(x, w, 1e-5, residual=res)
+        nc = copies_for(4 * T * H)
+        xs, w, rs = [R(T, H) for _ in range(nc)], R(H), [R(T, H) for _ in range(nc)]
+        fn = lambda i=0: ops.rmsnorm(xs[i], w, 1e-5, residual=rs[i])
         flops, byts = 0.0, 4.0 * T * H * 2
     else:
         T, I = prm
-        g = R(T, 2 * I)
-        fn = lambda: ops.silu_mul(g)
+        nc = copies_for(4 * T * I)
+        gs = [R(T, 2 * I) for _ in range(nc)]
+        fn = lambda i=0: ops.silu_mul(gs[i])
         flops, byts = 0.0, 3.0 * T * I * 2
     if a.no_time:
-        for _ in range(3):
-            fn()
+        for i in range(3):
+            fn(i % nc)
         torch.cuda.synchronize()
         ops.check_status()
         print("ran", a.case)
         return
-    ms = timeit(fn, a.iters)
+    ms = timeit(fn, a.iters, copies=nc)
     ops.check_status()
     t = ms / 1e3
     print(json.dumps({"case": a.case, "us": ms * 1e3, "tflops": flops / t / 1e12,

@@ -285,3 +285,75 @@ def test_verify_greedy():
     assert sel.tolist()[:3] == [2, 4, 7]
     assert out.tolist()[:3] == [[11, 12, 99, -1], [21, -1, -1, -1], [31, 32, 33, -1]]
     assert out.tolist()[3] == [-1, -1, -1, -1]
+
+
+# ------------------------------------------------------------------------------------- fp8
+from arcticinference_b200.models import quant  # noqa: E402
+
+
+def test_quant_fp8_matches_reference():
+    x = _rand(37, 1024, scale=2.0)
+    xq, sx = ops.quant_fp8(x)
+    rq, rs = quant.quant_activation_ref(x)
+    _close(sx, rs, 1e-7, 1e-5)
+    # codes may differ by one ulp where the scaled value sits on a rounding boundary
+    diff = (xq.float() - rq.float()).abs()
+    assert float((diff > 0).float().mean()) < 0.01
+    back = xq.float().view(37, 8, 128) * sx.t().unsqueeze(-1)
+    _close(back.view(37, 1024), x, 0.05 * float(x.float().abs().max()), 0.07)
+
+
+def _w8a8_ref(x, w):
+    """fp32 product of the activations as the quantisation kernel coded them (that kernel has
+    its own test) and the de-quantised weight: a code that sits on a rounding boundary must not
+    decide the GEMM test."""
+    xq, sx_t = ops.quant_fp8(x)
+    M, K = x.shape
+    xd = xq.float().view(M, K // 128, 128) * sx_t[:, :M].t().unsqueeze(-1)
+    return xd.view(M, K) @ w.dequantize().float().t()
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (8, 4096, 4096), (32, 6144, 4096), (100, 1024, 512), (128, 4096, 14336), (1, 256, 128),
+    (129, 256, 256), (512, 1024, 1024), (2048, 6144, 4096), (1000, 28672, 4096), (300, 384, 1792),
+])
+def test_linear_fp8(M, N, K):
+    x = _rand(M, K)
+    w = quant.quantize_weight_fp8(_rand(N, K, scale=1.0 / math.sqrt(K)))
+    # W8A8 kernel; oracle: the same quantised operands multiplied in fp32
+    y = ops.linear_fp8(x, w, mode="w8a8")
+    ops.check_status()
+    _close(y, _w8a8_ref(x, w), 5e-2, 2e-2)
+    # default dispatch (weight-only fp8 for few tokens, expanded bf16 for long prefill);
+    # oracle: bf16 activations times the de-quantised weight
+    y2 = ops.linear(x, w)
+    ops.check_status()
+    if M <= ops.W8A16_MAX_TOKENS or M >= ops.DEQUANT_MIN_TOKENS:
+        _close(y2, ref.linear(x, w.dequantize()), 5e-2, 2e-2)
+    else:   # in between, activations are quantised too
+        _close(y2, _w8a8_ref(x, w), 5e-2, 2e-2)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4])
+def test_linear_w8a16_split_k(splits):
+    x = _rand(24, 4096)
+    w = quant.quantize_weight_fp8(_rand(1024, 4096, scale=1.0 / 64))
+    y = ops.linear_fp8(x, w, force_splits=splits)
+    ops.check_status()
+    _close(y, ref.linear(x, w.dequantize()), 5e-2, 2e-2)
+
+
+def test_linear_fp8_shard_views():
+    x = _rand(64, 1024)
+    w = quant.quantize_weight_fp8(_rand(2048, 2048, scale=0.03))
+    xk = _rand(64, 2048)
+    rows = w[512:1024]
+    _close(ops.linear(xk, rows), ref.linear(xk, rows.dequantize()), 5e-2, 2e-2)
+    cols = w[:, 1024:2048]
+    xs = xk[:, 1024:2048]          # strided activation view, K-slice of the weight
+    _close(ops.linear(xs, cols), ref.linear(xs, cols.dequantize()), 5e-2, 2e-2)
+    _close(ops.linear(x, w[256:768, :1024]), ref.linear(x, w[256:768, :1024].dequantize()), 5e-2, 2e-2)
+    big = _rand(300, 1024)
+    _close(ops.linear_fp8(big, w[256:768, :1024], mode="w8a8"),
+           _w8a8_ref(big, w[256:768, :1024]), 5e-2, 2e-2)
+    ops.check_status()
