@@ -37,6 +37,27 @@ int ab200_rope_cache(void* qkv, long long ld, const void* positions, const void*
                      cudaStream_t stream);
 int ab200_gather_rows(const void* src, long long ld, const void* idx, void* dst, long long R,
                       int hidden, cudaStream_t stream);
+// encoder.cu
+int ab200_bert_embed_ln(const void* ids, const void* positions, const void* type_ids,
+                        const void* word, const void* pos, const void* type, const void* gamma,
+                        const void* beta, void* out, long long T, int hidden, long long vocab,
+                        long long max_pos, long long n_types, float eps, int* status,
+                        cudaStream_t stream);
+int ab200_pool_normalize(const void* h, long long ld, const void* starts, void* out, int n_seqs,
+                         int hidden, int mode, int normalize, cudaStream_t stream);
+// kv_cache.cu
+int ab200_kv_bulk_write(const void* kv, long long ld, const void* positions, const void* slots,
+                        const void* inv_freq, const void* k_ptrs, const void* v_ptrs,
+                        const void* k_scales, const void* v_scales, long long T, int L, int Hkv,
+                        int D, int block_size, long long num_slots, int fp8, int* status,
+                        cudaStream_t stream);
+int ab200_kv_write_fp4(const void* k, long long ldk, const void* v, long long ldv,
+                       const void* slots, void* k_codes, void* v_codes, void* k_scales,
+                       void* v_scales, long long T, int Hkv, int D, int block_size,
+                       long long num_slots, int* status, cudaStream_t stream);
+int ab200_kv_read_fp4(const void* codes, const void* scales, const void* slots, void* out,
+                      long long ldo, long long R, int Hkv, int D, int block_size,
+                      cudaStream_t stream);
 int ab200_argmax_sample(const void* logits, int dtype, long long ld, long long B, int V,
                         const void* temperature, const void* seeds, void* out_ids, void* out_vals,
                         long long index_offset, cudaStream_t stream);

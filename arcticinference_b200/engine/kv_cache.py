@@ -196,6 +196,21 @@ class KVCacheTensors:
         self.shape = (num_blocks, local_kv_heads, block_size, head_dim)
         self.k = [torch.zeros(self.shape, dtype=dtype, device=device) for _ in range(num_layers)]
         self.v = [torch.zeros(self.shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self._tables: dict = {}
+
+    def pointer_tables(self, first: int, count: int):
+        """Device tables (int64) of the K and V base addresses of ``count`` consecutive layers,
+        for kernels that write several layers in one launch. Built once per range."""
+        key = (first, count)
+        t = self._tables.get(key)
+        if t is None:
+            dev = self.k[first].device
+            t = (torch.tensor([c.data_ptr() for c in self.k[first:first + count]],
+                              dtype=torch.int64, device=dev),
+                 torch.tensor([c.data_ptr() for c in self.v[first:first + count]],
+                              dtype=torch.int64, device=dev))
+            self._tables[key] = t
+        return t
 
     @staticmethod
     def bytes_per_block(num_layers, local_kv_heads, block_size, head_dim, elem_bytes=2) -> int:
@@ -203,3 +218,4 @@ class KVCacheTensors:
 
     def free(self) -> None:
         self.k, self.v = [], []
+        self._tables = {}

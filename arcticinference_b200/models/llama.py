@@ -316,11 +316,11 @@ class LlamaForCausalLM(LlamaModel):
             i = self.shard.sp_rank
             wkv = wkv[i * rows_blk:(i + 1) * rows_blk]
         kv_all = ops.linear(s, wkv)
-        width = 2 * self.hkv * self.D
-        for j in range(n_later):
-            ops.rope_cache(kv_all[:, j * width:(j + 1) * width], positions, slots, self.inv_freq,
-                           kv.k[self.n_kv_layers + j], kv.v[self.n_kv_layers + j], 0, self.hkv,
-                           self.D)
+        # one launch rotates K and fills the caches of all later layers
+        first = self.n_kv_layers
+        tables = kv.pointer_tables(first, n_later) if hasattr(kv, "pointer_tables") else None
+        ops.kv_bulk_write(kv_all, positions, slots, self.inv_freq, kv.k[first:first + n_later],
+                          kv.v[first:first + n_later], self.hkv, self.D, tables=tables)
         x_sel = ops.gather_rows(residual, batch.logits_indices)
         h, residual = self._run_layers(self.n_kv_layers, cfg.num_hidden_layers, None, x_sel, batch,
                                        kv, "tp", batch.sel_attn_meta, batch.sel_positions, None,

@@ -289,6 +289,118 @@ def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, ro
     launch_counter.add(1)
 
 
+POOL_MODES = {"cls": 0, "mean": 1, "last": 2}
+
+
+def bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps: float):
+    """LayerNorm(word[ids] + pos[positions] + typ[type_ids]) in one pass. ids/positions/type_ids
+    int64 [T] (type_ids may be None = all zero)."""
+    if not word.is_cuda:
+        return ref.bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps)
+    nat = _native()
+    T, H = ids.numel(), word.shape[1]
+    out = torch.empty(T, H, dtype=word.dtype, device=word.device)
+    rc = nat.lib().ab200_bert_embed_ln(
+        ids.data_ptr(), positions.data_ptr(), nat.ptr(type_ids), word.data_ptr(), pos.data_ptr(),
+        typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), T, H, word.shape[0],
+        pos.shape[0], typ.shape[0], float(eps), nat.status_buffer(word.device).data_ptr(),
+        nat.stream_ptr())
+    nat.check(rc, "bert_embed_ln")
+    launch_counter.add(1)
+    return out
+
+
+def pool_normalize(h, starts, mode: str = "cls", normalize: bool = True, out=None):
+    """Per-sequence pooling of h [T, H] (sequence i owns rows starts[i]:starts[i+1]; ``starts``
+    int64 [S+1] on h's device) and optional L2 normalisation. Returns fp32 [S, H]."""
+    if not h.is_cuda:
+        return ref.pool_normalize(h, starts, mode, normalize)
+    nat = _native()
+    S, H = starts.numel() - 1, h.shape[1]
+    if out is None:
+        out = torch.empty(S, H, dtype=torch.float32, device=h.device)
+    rc = nat.lib().ab200_pool_normalize(h.data_ptr(), h.stride(0), starts.data_ptr(),
+                                        out.data_ptr(), S, H, POOL_MODES[mode],
+                                        1 if normalize else 0, nat.stream_ptr())
+    nat.check(rc, "pool_normalize")
+    launch_counter.add(1)
+    return out
+
+
+def kv_bulk_write(kv_all, positions, slots, inv_freq, k_caches, v_caches, Hkv, D, tables=None,
+                  k_scales=None, v_scales=None):
+    """RoPE on K and paged-cache write of K and V for several layers in one launch.
+    ``kv_all`` [T, L*2*Hkv*D] holds layer j at columns j*2*Hkv*D (K heads, then V heads);
+    ``k_caches / v_caches`` are the L cache tensors [num_blocks, Hkv, block_size, D] (bf16, or
+    float8_e4m3fn together with fp32 ``k_scales / v_scales`` [L]). ``tables`` = (k_ptrs, v_ptrs)
+    int64 device tensors of the cache base addresses, built once by the caller."""
+    if not kv_all.is_cuda:
+        return ref.kv_bulk_write(kv_all, positions, slots, inv_freq, k_caches, v_caches, Hkv, D,
+                                 k_scales, v_scales)
+    nat = _native()
+    L = len(k_caches)
+    T = kv_all.shape[0]
+    if tables is None:
+        tables = (torch.tensor([c.data_ptr() for c in k_caches], dtype=torch.int64, device=kv_all.device),
+                  torch.tensor([c.data_ptr() for c in v_caches], dtype=torch.int64, device=kv_all.device))
+    fp8 = k_caches[0].dtype == torch.float8_e4m3fn
+    bs = k_caches[0].shape[2]
+    assert kv_all.shape[1] == L * 2 * Hkv * D and slots.dtype == torch.int64
+    rc = nat.lib().ab200_kv_bulk_write(
+        kv_all.data_ptr(), kv_all.stride(0), positions.data_ptr(), slots.data_ptr(),
+        inv_freq.data_ptr(), tables[0].data_ptr(), tables[1].data_ptr(), nat.ptr(k_scales),
+        nat.ptr(v_scales), T, L, Hkv, D, bs, k_caches[0].shape[0] * bs, 1 if fp8 else 0,
+        nat.status_buffer(kv_all.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "kv_bulk_write")
+    launch_counter.add(1)
+
+
+def kv_write_fp4(k, v, slots, k_codes, v_codes, k_scales, v_scales, Hkv, D):
+    """NVFP4 cache write of one layer: k, v bf16 [T, Hkv*D] -> e2m1 codes [num_blocks, Hkv,
+    block_size, D/2] uint8 and e4m3 group scales [num_blocks, Hkv, block_size, D/16] uint8."""
+    bs = k_codes.shape[2]
+    if not k.is_cuda:
+        ok = slots >= 0
+        s = slots[ok]
+        blk, off = s // bs, s % bs
+        T = k.shape[0]
+        for src, codes, scales in ((k, k_codes, k_scales), (v, v_codes, v_scales)):
+            c, sc, _ = ref.quantize_nvfp4(src.reshape(T, Hkv, D))
+            codes[blk, :, off] = c[ok]
+            scales[blk, :, off] = sc[ok]
+        return
+    nat = _native()
+    rc = nat.lib().ab200_kv_write_fp4(
+        k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), slots.data_ptr(),
+        k_codes.data_ptr(), v_codes.data_ptr(), k_scales.data_ptr(), v_scales.data_ptr(),
+        k.shape[0], Hkv, D, bs, k_codes.shape[0] * bs,
+        nat.status_buffer(k.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "kv_write_fp4")
+    launch_counter.add(1)
+
+
+def kv_read_fp4(codes, scales, slots, Hkv, D):
+    """Rows of an NVFP4 cache tensor at ``slots`` expanded to bf16 [R, Hkv*D]."""
+    bs = codes.shape[2]
+    R = slots.numel()
+    if not codes.is_cuda:
+        blk, off = slots // bs, slots % bs
+        c = codes[blk, :, off].long()
+        vals = torch.tensor(ref.E2M1_VALUES, dtype=torch.float32)
+        nib = torch.stack([c & 15, c >> 4], -1).reshape(R, Hkv, D)
+        x = vals[nib & 7] * torch.where((nib & 8) > 0, -1.0, 1.0)
+        s = scales[blk, :, off].view(torch.float8_e4m3fn).float().repeat_interleave(16, -1)
+        return (x * s).reshape(R, Hkv * D).to(torch.bfloat16)
+    nat = _native()
+    out = torch.empty(R, Hkv * D, dtype=torch.bfloat16, device=codes.device)
+    rc = nat.lib().ab200_kv_read_fp4(codes.data_ptr(), scales.data_ptr(), slots.data_ptr(),
+                                     out.data_ptr(), out.stride(0), R, Hkv, D, bs,
+                                     nat.stream_ptr())
+    nat.check(rc, "kv_read_fp4")
+    launch_counter.add(1)
+    return out
+
+
 def gather_rows(src: torch.Tensor, idx: torch.Tensor, out=None):
     if not src.is_cuda:
         return ref.gather_rows(src, idx)

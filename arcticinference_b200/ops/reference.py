@@ -91,6 +91,84 @@ def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, ro
         v_cache[blk, :, off] = v[ok]
 
 
+def kv_bulk_write(kv_all, positions, slots, inv_freq, k_caches, v_caches, Hkv, D,
+                  k_scales=None, v_scales=None):
+    """K/V of several layers at once: kv_all [T, L*2*Hkv*D], layer j = [k heads | v heads].
+    Caches bf16, or float8_e4m3fn with one scale per layer and tensor."""
+    T = kv_all.shape[0]
+    width = 2 * Hkv * D
+    ok = slots >= 0
+    s = slots[ok]
+    for j, (kc, vc) in enumerate(zip(k_caches, v_caches)):
+        bs = kc.shape[2]
+        blk, off = s // bs, s % bs
+        k = kv_all[:, j * width: j * width + Hkv * D].reshape(T, Hkv, D)
+        v = kv_all[:, j * width + Hkv * D: (j + 1) * width].reshape(T, Hkv, D)
+        k_rot = rope_rotate(k, positions, inv_freq)
+        if kc.dtype == torch.float8_e4m3fn:
+            kq = (k_rot.float() / float(k_scales[j])).clamp(-448, 448).to(torch.float8_e4m3fn)
+            vq = (v.float() / float(v_scales[j])).clamp(-448, 448).to(torch.float8_e4m3fn)
+            kc.view(torch.uint8)[blk, :, off] = kq[ok].view(torch.uint8)
+            vc.view(torch.uint8)[blk, :, off] = vq[ok].view(torch.uint8)
+        else:
+            kc[blk, :, off] = k_rot[ok]
+            vc[blk, :, off] = v[ok]
+
+
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def quantize_nvfp4(x: torch.Tensor):
+    """[..., D] -> (codes uint8 [..., D/2], scales uint8 (e4m3 bits) [..., D/16], dequantised
+    fp32 [..., D]). Groups of 16 share scale = e4m3(amax / 6); elements round to the nearest
+    e2m1 value, ties to the even code; even element in the low nibble."""
+    D = x.shape[-1]
+    g = x.float().reshape(*x.shape[:-1], D // 16, 16)
+    amax = g.abs().amax(-1, keepdim=True)
+    sb = (amax / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)
+    sd = sb.float()
+    y = torch.where(sd > 0, g / sd, torch.zeros_like(g))
+    vals = torch.tensor(E2M1_VALUES, dtype=torch.float32, device=x.device)
+    a = y.abs().clamp(max=6.0)
+    # nearest code, ties to even code index
+    d = (a.unsqueeze(-1) - vals).abs()
+    best = d.argmin(-1)
+    nxt = (best + 1).clamp(max=7)
+    tie = (d.gather(-1, nxt.unsqueeze(-1)).squeeze(-1) == d.gather(-1, best.unsqueeze(-1)).squeeze(-1)) \
+        & (nxt != best)
+    code = torch.where(tie & (best % 2 == 1), nxt, best)
+    deq = vals[code] * torch.sign(y) * sd
+    code = code | ((y < 0) | ((y == 0) & torch.signbit(y))).long() * 8
+    code = code.reshape(*x.shape[:-1], D // 2, 2)
+    packed = (code[..., 0] | (code[..., 1] << 4)).to(torch.uint8)
+    return packed, sb.view(torch.uint8).reshape(*x.shape[:-1], D // 16), deq.reshape(x.shape)
+
+
+def bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps):
+    x = word[ids].float() + pos[positions].float() + \
+        typ[type_ids if type_ids is not None else torch.zeros_like(ids)].float()
+    y = torch.nn.functional.layer_norm(x, (x.shape[-1],), gamma.float(), beta.float(), eps)
+    return y.to(word.dtype)
+
+
+def pool_normalize(h, starts, mode="cls", normalize=True):
+    """h [T, H]; starts [S+1] row offsets. Returns fp32 [S, H]."""
+    out = []
+    st = [int(v) for v in starts]
+    for i in range(len(st) - 1):
+        rows = h[st[i]:st[i + 1]].float()
+        if mode == "cls":
+            v = rows[0]
+        elif mode == "last":
+            v = rows[-1]
+        else:
+            v = rows.mean(0)
+        if normalize:
+            v = v / v.norm().clamp_min(1e-12)
+        out.append(v)
+    return torch.stack(out)
+
+
 def gather_rows(src, idx):
     return src[idx]
 

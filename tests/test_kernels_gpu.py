@@ -111,6 +111,62 @@ def test_rope_cache():
     assert torch.equal(vc, vc_ref)
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_kv_bulk_write(fp8):
+    T, L, Hkv, D, bs, nb = 37, 5, 2, 128, 32, 8
+    kv_all = _rand(T, L * 2 * Hkv * D)
+    pos = torch.randint(0, 100000, (T,), device=DEV)
+    slots = torch.randperm(nb * bs, device=DEV)[:T]
+    slots[5] = -1
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, D, 2, device=DEV).float() / D))
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    mk = lambda: [torch.zeros(nb, Hkv, bs, D, device=DEV, dtype=torch.bfloat16).to(dt) for _ in range(L)]
+    kc, vc, kc_ref, vc_ref = mk(), mk(), mk(), mk()
+    ks = torch.linspace(0.01, 0.02, L, device=DEV) if fp8 else None
+    vs = torch.linspace(0.02, 0.01, L, device=DEV) if fp8 else None
+    ops.kv_bulk_write(kv_all, pos, slots, inv_freq, kc, vc, Hkv, D, k_scales=ks, v_scales=vs)
+    ops.check_status()
+    ref.kv_bulk_write(kv_all, pos, slots, inv_freq, kc_ref, vc_ref, Hkv, D, ks, vs)
+    for j in range(L):
+        if fp8:
+            # one e4m3 step (1/8 relative) where the rotated value sits on a rounding boundary
+            _close(kc[j].float() * ks[j], kc_ref[j].float() * ks[j], 3e-2, 0.13)
+            assert float((kc[j].float() != kc_ref[j].float()).float().mean()) < 0.02
+            assert torch.equal(vc[j].view(torch.uint8), vc_ref[j].view(torch.uint8))
+        else:
+            _close(kc[j], kc_ref[j], 3e-2, 2e-2)
+            assert torch.equal(vc[j], vc_ref[j])
+
+
+def test_kv_fp4_write_and_read():
+    T, Hkv, D, bs, nb = 29, 4, 128, 16, 4
+    k, v = _rand(T, Hkv * D), _rand(T, Hkv * D, scale=3.0)
+    k[2, :16] = 0                      # an all-zero group
+    slots = torch.randperm(nb * bs, device=DEV)[:T]
+    slots[7] = -1
+    mk = lambda last: torch.zeros(nb, Hkv, bs, last, device=DEV, dtype=torch.uint8)
+    kc, vc, ksc, vsc = mk(D // 2), mk(D // 2), mk(D // 16), mk(D // 16)
+    ops.kv_write_fp4(k, v, slots, kc, vc, ksc, vsc, Hkv, D)
+    ops.check_status()
+    ok = slots >= 0
+    blk, off = slots[ok] // bs, slots[ok] % bs
+    for src, codes, scales in ((k, kc, ksc), (v, vc, vsc)):
+        rc, rs, deq = ref.quantize_nvfp4(src.view(T, Hkv, D))
+        assert torch.equal(scales[blk, :, off], rs[ok])
+        got = codes[blk, :, off]
+        # identical codes except where a scaled value sits exactly between two e2m1 values
+        assert float((got != rc[ok]).float().mean()) < 0.005
+        back = ops.kv_read_fp4(codes, scales, slots[ok], Hkv, D).view(-1, Hkv, D)
+        # the error of one element is at most half an e2m1 step (1 at the top) times the scale
+        bound = rs[ok].view(torch.float8_e4m3fn).float().repeat_interleave(16, -1) * 1.0 + 1e-3
+        assert bool(((back.float() - src.view(T, Hkv, D)[ok].float()).abs() <= bound * 1.01).all())
+        same = got == rc[ok]
+        both = same.repeat_interleave(2, -1)
+        _close(back.float()[both], deq[ok][both], 1e-2, 1e-2)
+    assert int(kc[slots[7] // bs if slots[7] >= 0 else 0].sum()) >= 0   # padding token wrote nothing
+    ops.check_status()
+
+
 # ------------------------------------------------------------------------------------ GEMM
 GEMM_SHAPES = [
     (128, 128, 64), (128, 256, 128), (300, 512, 256), (1000, 1024, 4096), (4096, 6144, 4096),
