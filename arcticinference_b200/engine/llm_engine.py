@@ -105,7 +105,10 @@ class LLMEngine:
         return self.scheduler.has_work()
 
     # ------------------------------------------------------------------- step
-    def step(self) -> list[RequestOutput]:
+    def step(self, partial: bool = False) -> list[RequestOutput]:
+        """One scheduling + model step. Returns the requests that finished; with
+        ``partial`` also an unfinished ``RequestOutput`` (cumulative text and tokens) for every
+        request that produced tokens in this step, for streaming front ends."""
         if self.sleeping_level:
             raise RuntimeError("engine is sleeping; call wake_up() first")
         out = self.scheduler.schedule()
@@ -125,6 +128,15 @@ class LLMEngine:
             self.stats["generation_tokens"] += len(toks)
             self.stats["accepted_tokens"] += len(toks) - 1
         outputs = []
+        if partial:
+            done_ids = {r.request_id for r in finished}
+            for s in out.scheduled:
+                req = s.request
+                if req.request_id in done_ids or not result.new_tokens.get(req.request_id):
+                    continue
+                outputs.append(RequestOutput(req.parent_id or req.request_id, req.prompt,
+                                             req.prompt_token_ids, [self._completion(req)], False,
+                                             req.metrics, num_cached_tokens=req.num_cached_tokens))
         for req in finished:
             if self.runner.suffix_cache is not None:
                 self.runner.suffix_cache.stop_request(req.request_id)
@@ -132,6 +144,14 @@ class LLMEngine:
             if ro is not None:
                 outputs.append(ro)
         return outputs
+
+    def get_stats(self) -> dict:
+        """Load figures a router needs: queue lengths and KV-cache utilisation."""
+        d = dict(self.stats)
+        d.update(running=len(self.scheduler.running), waiting=len(self.scheduler.waiting),
+                 kv_cache_usage=float(self.kv_manager.usage), num_blocks=self.num_blocks,
+                 sleeping_level=self.sleeping_level)
+        return d
 
     def _completion(self, req: Request) -> CompletionOutput:
         text = self.tokenizer.decode(req.output_token_ids,

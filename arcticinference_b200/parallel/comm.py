@@ -201,6 +201,18 @@ class Communicator:
         dist.broadcast_object_list(box, src=src)
         return box[0]
 
+    def host_broadcast(self, obj, src: int = 0):
+        """Broadcast a Python object over a host-side (gloo) group, off the GPU streams: the
+        control channel of the serving loop. Every rank must call it in the same order."""
+        if getattr(self, "_host_group", None) is None:
+            if dist.get_backend() == "gloo":
+                self._host_group = dist.group.WORLD
+            else:
+                self._host_group = dist.new_group(backend="gloo")
+        box = [obj]
+        dist.broadcast_object_list(box, src=src, group=self._host_group)
+        return box[0]
+
 
 def init_communicator(tp: int, sp: int, backend: str = "fused", device=None) -> Communicator:
     """Create the process group from torchrun-style environment variables (if needed)
