@@ -210,3 +210,91 @@ def iter_safetensors_dir(path: str) -> Iterator:
 
 def load_llama_weights(model, path: str) -> None:
     load_llama_state(model, iter_safetensors_dir(path))
+
+
+class LlamaWeightUpdater:
+    """In-place update of a loaded model from a stream of checkpoint-named tensors.
+
+    ``deliver`` may be called in any order; as soon as every projection of a decoder layer
+    has arrived the layer's fused, sharded tensors are rebuilt and copied *into the existing
+    storage* (fp8 weights are re-quantised in place), so addresses captured in CUDA graphs or
+    registered with peers stay valid. The streamed tensors may be views of a transfer buffer
+    that is about to be reused: whatever has to outlive the call is copied first.
+    (reference: arctic_inference/server/weight_sync/receiver.py:280-331,
+    utils.py:166-294.)
+    """
+
+    def __init__(self, model):
+        self.model = model
+        self.pending: dict[int, dict] = {}
+        self.applied = 0
+        self.layers_done: set = set()
+        self._wkv_stage = None
+
+    def direct_target(self, name: str):
+        """Destination tensor when ``name`` can be received straight into engine storage."""
+        m = self.model
+        t = {"model.embed_tokens.weight": m.embed, "model.norm.weight": m.norm,
+             "model.norm_swiftkv.weight": m.norm_swiftkv,
+             "lm_head.weight": None if m.lm_head is m.embed else m.lm_head}.get(name)
+        return t if isinstance(t, torch.Tensor) else None
+
+    def deliver(self, name: str, tensor) -> None:
+        from ..server.weight_sync.utils import assign_in_place
+        m = self.model
+        if tensor is None or isinstance(tensor, str):
+            self.applied += 1            # tied tensor: shares storage with its target already
+            return
+        direct = self.direct_target(name)
+        if direct is not None:
+            if tensor.data_ptr() != direct.data_ptr():
+                direct.copy_(tensor.to(direct.dtype))
+            self.applied += 1
+            return
+        if name == "lm_head.weight":     # tied in the engine, sent separately: ignore
+            self.applied += 1
+            return
+        mt = _LAYER_RE.match(name)
+        if not mt:
+            return
+        l, key = int(mt.group(1)), mt.group(2)
+        if l >= m.cfg.num_hidden_layers:
+            return
+        d = self.pending.setdefault(l, {})
+        d[key] = tensor.clone()          # the transfer buffer is recycled before the layer is complete
+        self.applied += 1
+        if all(r in d for r in _required(m, l)):
+            self._apply_layer(l, d)
+            del self.pending[l]
+
+    def _apply_layer(self, l: int, d: dict) -> None:
+        from ..server.weight_sync.utils import assign_in_place
+        from .quant import Fp8Weight
+        m = self.model
+        old = m.layers[l]
+        later = m.cfg.is_swiftkv and l >= m.n_kv_layers
+        real_wkv = m.wkv_swiftkv
+        if later and isinstance(real_wkv, Fp8Weight):
+            # pack into a dense staging copy; re-quantised once at the end
+            if self._wkv_stage is None:
+                self._wkv_stage = real_wkv.dequantize()
+            m.wkv_swiftkv = self._wkv_stage
+        try:
+            pack_llama_layer(m, l, d)    # builds fresh fused tensors (and writes wkv rows in place)
+        finally:
+            m.wkv_swiftkv = real_wkv
+        new = m.layers[l]
+        for slot in ("wqkv", "wo", "wgu", "wdown", "input_norm", "post_norm"):
+            assign_in_place(getattr(old, slot), getattr(new, slot))
+        m.layers[l] = old
+        self.layers_done.add(l)
+
+    def finish(self) -> dict:
+        from ..server.weight_sync.utils import requantize_into
+        if self._wkv_stage is not None:
+            requantize_into(self.model.wkv_swiftkv, self._wkv_stage)
+            self._wkv_stage = None
+        incomplete = sorted(self.pending)
+        self.pending = {}
+        return {"tensors": self.applied, "layers": len(self.layers_done),
+                "incomplete_layers": incomplete}
