@@ -325,3 +325,32 @@ def test_gpu_allocator():
         a.acquire(2)
     a.release([4, 5])
     assert a.free == [4, 5, 6] and GpuAllocator([]).acquire(4) is None
+
+
+def test_process_worker_hosts_engine_in_child():
+    from arcticinference_b200.server.worker import ProcessWorker
+
+    async def main():
+        w = ProcessWorker(0, gpu_ids=None, master_port=29877, start_timeout=300)
+        cfg = ServerModelConfig(model="llama-tiny", max_model_len=128, max_num_seqs=8,
+                                extra_env={"CUDA_VISIBLE_DEVICES": ""},
+                                extra_engine_kwargs={"num_gpu_blocks_override": 64, "block_size": 16})
+        await w.initialize(cfg)
+        try:
+            assert await w.health()
+            sp = {"temperature": 0.0, "max_tokens": 5, "ignore_eos": True}
+            a, b = await asyncio.gather(w.generate([1, 2, 3], sp), w.generate([1, 2, 3], sp))
+            assert a["token_ids"] == b["token_ids"] and a["generation_len"] == 5 and a["prompt_len"] == 3
+            st = await w.get_stats()
+            assert st["generation_tokens"] >= 10
+            assert len(await w.weights_info()) == 21
+            with pytest.raises(RuntimeError):
+                await w.generate([1], {"temperature": -3})
+            await w.sleep(1)
+            assert w.status is WorkerStatus.SLEEPING
+            await w.wake_up()
+            assert (await w.generate([4, 5], sp))["generation_len"] == 5
+        finally:
+            await w.shutdown()
+        assert not await w.health()
+    run(main())
