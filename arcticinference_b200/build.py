@@ -129,10 +129,53 @@ def build_suffix_tree(force: bool = False) -> Path:
     return out
 
 
+TORCH_OPS_LIB = PKG_DIR / "_torch_ops.so"
+
+
+def build_torch_ops(force: bool = False) -> Path:
+    """Compile ``csrc/torch/torch_bindings.cpp`` (the ``torch.ops.arcticinference_b200``
+    namespace) against the installed PyTorch and link it to ``_kernels.so``."""
+    import torch
+    from torch.utils import cpp_extension
+
+    src = CSRC / "torch" / "torch_bindings.cpp"
+    build_kernels()
+    deps = [src, CSRC / "api.h"]
+    if not force and TORCH_OPS_LIB.exists() and \
+            TORCH_OPS_LIB.stat().st_mtime >= max(_newest(deps), KERNEL_LIB.stat().st_mtime):
+        return TORCH_OPS_LIB
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    inc = []
+    for d in cpp_extension.include_paths("cuda") + [str(Path(cuda_home) / "include"),
+                                                    sysconfig.get_paths()["include"]]:
+        inc += ["-isystem", d]
+    torch_lib = str(Path(torch.__file__).parent / "lib")
+    cxx = os.environ.get("CXX", "g++")
+    tmp = TORCH_OPS_LIB.with_suffix(".so.tmp%d" % os.getpid())
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           "-DTORCH_API_INCLUDE_EXTENSION_H", *inc, str(src), "-o", str(tmp),
+           "-L", torch_lib, "-L", str(Path(cuda_home) / "lib64"), "-L", str(PKG_DIR),
+           "-l:_kernels.so", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+    _run(cmd)
+    os.replace(tmp, TORCH_OPS_LIB)
+    return TORCH_OPS_LIB
+
+
+def load_torch_ops():
+    """Register ``torch.ops.arcticinference_b200`` (building the library if needed)."""
+    import torch
+    load_kernels()
+    torch.ops.load_library(str(build_torch_ops()))
+    return torch.ops.arcticinference_b200
+
+
 def build_all(force: bool = False) -> None:
     if any((CSRC / "suffix_tree").glob("*.cc")):
         build_suffix_tree(force)
     build_kernels(force)
+    build_torch_ops(force)
 
 
 def load_kernels() -> ctypes.CDLL:
