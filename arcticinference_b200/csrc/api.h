@@ -118,6 +118,8 @@ int ab200_verify_greedy(const void* input_ids, const void* target, const void* r
 // ---- comm.cu (pointer arrays are host arrays of `world` device pointers)
 int ab200_barrier(const void* const* flag_ptrs, int my_rank, int world, void* epoch_ctr,
                   int* status, cudaStream_t stream);
+int ab200_barrier_timed(const void* const* flag_ptrs, int my_rank, int world, void* epoch_ctr,
+                        int limit_ms, int* status, cudaStream_t stream);
 int ab200_allreduce(const void* const* part_ptrs, int world, void* out, const void* residual,
                     long long n_elems, cudaStream_t stream);
 int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long rows_per_rank,

@@ -55,7 +55,7 @@ __device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
 // Thread j publishes this rank's epoch into rank j's slot [my_rank] and then waits for
 // rank j's epoch in the local slot [j].
 __global__ void barrier_kernel(PeerTable flags, int my_rank, int world, unsigned int* epoch_ctr,
-                               int* status) {
+                               int* status, unsigned long long limit_ns) {
   __shared__ unsigned int epoch;
   if (threadIdx.x == 0) epoch = *epoch_ctr + 1;
   __syncthreads();
@@ -68,7 +68,7 @@ __global__ void barrier_kernel(PeerTable flags, int my_rank, int world, unsigned
     const unsigned long long t0 = globaltimer_ns();
     unsigned int spins = 0;
     while ((int)(ld_acquire_sys(mine) - e) < 0) {
-      if ((++spins & 255u) == 0u && globaltimer_ns() - t0 > kWaitLimitNs) {
+      if ((++spins & 255u) == 0u && globaltimer_ns() - t0 > limit_ns) {
         report_error(status, kErrPeerFlagTimeout, j, (int)e);
         break;
       }
@@ -149,7 +149,22 @@ int ab200_barrier(const void* const* flag_ptrs, int my_rank, int world, void* ep
   PeerTable t;
   for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < world ? const_cast<void*>(flag_ptrs[i]) : nullptr;
   barrier_kernel<<<1, 32, 0, stream>>>(t, my_rank, world,
-                                       reinterpret_cast<unsigned int*>(epoch_ctr), status);
+                                       reinterpret_cast<unsigned int*>(epoch_ctr), status,
+                                       kWaitLimitNs);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Same barrier with a caller-chosen wait limit (milliseconds). A rank whose peers never
+// arrive leaves the kernel after the limit with kErrPeerFlagTimeout in the status word and a
+// usable context: the host decides what to do about the missing peer.
+int ab200_barrier_timed(const void* const* flag_ptrs, int my_rank, int world, void* epoch_ctr,
+                        int limit_ms, int* status, cudaStream_t stream) {
+  if (world < 1 || world > kMaxPeers || limit_ms < 1 || limit_ms > 60000) return -2;
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < world ? const_cast<void*>(flag_ptrs[i]) : nullptr;
+  barrier_kernel<<<1, 32, 0, stream>>>(t, my_rank, world,
+                                       reinterpret_cast<unsigned int*>(epoch_ctr), status,
+                                       (unsigned long long)limit_ms * 1000000ull);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -321,6 +321,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+
     }
   }
 
@@ -442,7 +443,36 @@ extern "C" {
 // Number of fp32 scratch bytes ab200_linear_bf16 may need for (M, N, K).
 size_t ab200_linear_bf16_workspace_bytes(int M, int N, int K) {
   if (M > 256) return 0;
-  return (size_t)8 * (size_t)M * (size_t)N * sizeof(float);
+  return (size_t)(M <= 128 ? 16 : 8) * (size_t)M * (size_t)N * sizeof(float);
+}
+
+// One tcgen05.mma (cta_group::1) is accepted every ~186 SM cycles whatever its shape
+// (measured on B200 for M = 64/128, N = 16..256, bf16 and fp8), so a k-loop is bound by its
+// instruction count unless every instruction carries enough work. With few tokens the
+// weights therefore go on the N side, 256 features per instruction, and the tokens on the
+// (padded) M side; split-K then spreads the instructions over all SMs.
+constexpr double kMmaIssueCycles = 186.0;
+
+// Split-K factor for a one-row-of-tiles (M <= 128) token-major GEMM: the smallest estimate of
+// max(instruction-issue time, HBM time incl. fp32 partials) plus a reduce-launch penalty.
+static int pick_token_major_splits(int tiles_b, int kblocks, int M, int N, int K, int sms,
+                                   size_t workspace_bytes) {
+  int best = 1;
+  double best_t = 1e30;
+  for (int s = 1; s <= 16; s *= 2) {
+    if (s > 1 && (kblocks / s < 4 || (size_t)s * M * N * sizeof(float) > workspace_bytes)) break;
+    const int per_split = (kblocks + s - 1) / s;
+    const int waves = (tiles_b * s + sms - 1) / sms;
+    const double issue_us = waves * per_split * (kBlockK / kUmmaK) * kMmaIssueCycles / 1.9e3;
+    const double bytes = 2.0 * N * K + (s > 1 ? 2.0 * s * M * (double)N * 4.0 : 0.0);
+    const double hbm_us = bytes / 6.5e6;
+    const double t = (issue_us > hbm_us ? issue_us : hbm_us) + (s > 1 ? 4.0 : 0.0);
+    if (t < best_t - 0.25) {
+      best_t = t;
+      best = s;
+    }
+  }
+  return best;
 }
 
 static int launch_linear(const void* x, long long ldx, const void* w, long long ldw, void* out,
@@ -494,7 +524,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   const void* pb;
   long long lda, ldb;
   const int sms = num_sms();
-  if (M <= 256) {
+  if (M > kBlockM && M <= 256) {
     // feature-major: weights are the 128-row operand, all tokens form the N side
     a.transposed = 1;
     a.rows_a = N;
@@ -529,9 +559,22 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     ldb = ldw;
     a.tiles_a = (M + kBlockM - 1) / kBlockM;
     const int tiles256 = a.tiles_a * ((N + 255) / 256);
-    a.bn = (tiles256 >= sms && N >= 256) ? 256 : 128;
+    a.bn = ((tiles256 >= sms || a.tiles_a == 1) && N >= 256) ? 256 : 128;
     if (N < 128) a.bn = ((N + 15) / 16) * 16;
     a.tiles_b = (N + a.bn - 1) / a.bn;
+    if (a.tiles_a == 1) {
+      int splits = force_splits;
+      if (splits <= 0)
+        splits = (N % 4 == 0 && workspace != nullptr)
+                     ? pick_token_major_splits(a.tiles_b, a.kblocks_total, M, N, K, sms, workspace_bytes)
+                     : 1;
+      if (splits > 16) splits = 16;
+      if (splits > a.kblocks_total) splits = a.kblocks_total;
+      if (splits > 1 && (workspace == nullptr || (N % 4) ||
+                         workspace_bytes < (size_t)splits * M * N * sizeof(float)))
+        splits = 1;
+      a.splits = splits;
+    }
   }
   a.kblocks_per_split = (a.kblocks_total + a.splits - 1) / a.splits;
   a.splits = (a.kblocks_total + a.kblocks_per_split - 1) / a.kblocks_per_split;

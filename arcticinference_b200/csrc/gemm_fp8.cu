@@ -323,7 +323,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // the block scale applied (read the swizzled fp8 tile, write a swizzled bf16 tile), and the
 // tensor core runs a plain bf16 UMMA against the un-quantised bf16 activations, accumulating
 // over all of K in TMEM. No activation quantisation, no per-block rescaling, half the bytes.
-constexpr int kWaThreads = 448;  // TMA, MMA, 8 converter warps, 4 epilogue warps
+constexpr int kWaConvWarps = 16;  // the expansion is latency bound: 4 warps per scheduler hide it
+constexpr int kWaConvBufs = 4;    // converted k-blocks in flight between converters and MMA
+constexpr int kWaThreads = 64 + 32 * kWaConvWarps + 128;  // TMA, MMA, converters, 4 epilogue warps
 constexpr uint32_t kWaConvBytes = 128 * 256;  // one converted k-block: 128 rows x 128 k bf16
 
 struct WaArgs {
@@ -348,9 +350,9 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
                                              ~static_cast<uintptr_t>(1023));
   const uint32_t x_bytes = (uint32_t)p.bn * 256u;        // two 64-wide k atoms of bn rows
   const uint32_t raw_bytes = kF8ABytes + x_bytes;
-  uint8_t* conv = smem + (size_t)p.stages * raw_bytes;   // 2 converted buffers
-  uint64_t* bars = reinterpret_cast<uint64_t*>(conv + 2 * kWaConvBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kF8MaxStages + 8);
+  uint8_t* conv = smem + (size_t)p.stages * raw_bytes;   // converted buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(conv + kWaConvBufs * kWaConvBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kF8MaxStages + 2 * kWaConvBufs + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t conv_base = smem_u32(conv);
@@ -358,9 +360,9 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
   auto full_bar = [&](int s) { return bb + 8u * s; };
   auto empty_bar = [&](int s) { return bb + 8u * (kF8MaxStages + s); };
   auto cfull_bar = [&](int c) { return bb + 8u * (2 * kF8MaxStages + c); };
-  auto cempty_bar = [&](int c) { return bb + 8u * (2 * kF8MaxStages + 2 + c); };
-  auto tfull_bar = [&](int a) { return bb + 8u * (2 * kF8MaxStages + 4 + a); };
-  auto tempty_bar = [&](int a) { return bb + 8u * (2 * kF8MaxStages + 6 + a); };
+  auto cempty_bar = [&](int c) { return bb + 8u * (2 * kF8MaxStages + kWaConvBufs + c); };
+  auto tfull_bar = [&](int a) { return bb + 8u * (2 * kF8MaxStages + 2 * kWaConvBufs + a); };
+  auto tempty_bar = [&](int a) { return bb + 8u * (2 * kF8MaxStages + 2 * kWaConvBufs + 2 + a); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -371,9 +373,11 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int c = 0; c < 2; ++c) {
-      mbar_init(cfull_bar(c), 8);
+    for (int c = 0; c < kWaConvBufs; ++c) {
+      mbar_init(cfull_bar(c), kWaConvWarps);
       mbar_init(cempty_bar(c), 1);
+    }
+    for (int c = 0; c < 2; ++c) {
       mbar_init(tfull_bar(c), 1);
       mbar_init(tempty_bar(c), 4);
     }
@@ -439,8 +443,8 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * acc_stride;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int c = it & 1;
-          const uint32_t cph = (it >> 1) & 1u;
+          const int c = it % kWaConvBufs;
+          const uint32_t cph = (it / kWaConvBufs) & 1u;
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 2300 + stage, kb) ||
               !mbar_wait(cfull_bar(c), cph, abort_flag, p.status, 2400 + c, kb)) {
             ok = false;
@@ -469,9 +473,9 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (acc == 0) acc_phase ^= 1u;
       }
     }
-  } else if (warp < 10) {
+  } else if (warp < 2 + kWaConvWarps) {
     // ------------------------------ converters: fp8 tile -> scaled bf16 tile ------------------
-    const int ct = threadIdx.x - 64;  // 0..255
+    const int ct = threadIdx.x - 64;  // 0 .. 32 * kWaConvWarps - 1
     int stage = 0;
     uint32_t phase = 0;
     uint32_t it = 0;
@@ -483,8 +487,8 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int kb0 = split * p.kblocks_per_split;
       const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const int c = it & 1;
-        const uint32_t cph = (it >> 1) & 1u;
+        const int c = it % kWaConvBufs;
+        const uint32_t cph = (it / kWaConvBufs) & 1u;
         // e4m3 -> bf16 without conversion instructions: the 7 magnitude bits of an e4m3 byte,
         // shifted into a bf16's exponent/mantissa position, read as the same value times 2^-120
         // (bias 7 vs 127; subnormals line up too), so one packed bf16 multiply by
@@ -501,11 +505,11 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
         const uint8_t* raw = smem + (size_t)stage * raw_bytes;
         uint8_t* dst = conv + (size_t)c * kWaConvBytes;
-        // 128 rows x 16 eight-byte pieces of fp8, 8 per thread: sixteen lanes read one row's
-        // 128 bytes, eight lanes write one row's eight 16-byte chunks of an atom (no conflicts)
+        // 128 rows x 16 eight-byte pieces of fp8: sixteen lanes read one row's 128 bytes, eight
+        // lanes write one row's eight 16-byte chunks of an atom (no bank conflicts)
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int task = ct + u * 256;
+        for (int u = 0; u < 2048 / (32 * kWaConvWarps); ++u) {
+          const int task = ct + u * (32 * kWaConvWarps);
           const int r = task >> 4;
           const int h = task & 15;
           const uint2 q = *reinterpret_cast<const uint2*>(raw + r * 128 + (((h >> 1) ^ (r & 7)) << 4) +
@@ -785,7 +789,7 @@ int ab200_linear_w8a16(const void* x, long long ldx, const void* wq, long long l
   a.kblocks_per_split = (a.kblocks_total + splits - 1) / splits;
   a.splits = (a.kblocks_total + a.kblocks_per_split - 1) / a.kblocks_per_split;
   const int raw_bytes = (int)kF8ABytes + a.bn * 256;
-  a.stages = (227 * 1024 - 2048 - 2 * (int)kWaConvBytes) / raw_bytes;
+  a.stages = (227 * 1024 - 2048 - kWaConvBufs * (int)kWaConvBytes) / raw_bytes;
   if (a.stages > kF8MaxStages) a.stages = kF8MaxStages;
   if (a.stages < 2) return -2;
   void* final_out = out;
@@ -804,7 +808,7 @@ int ab200_linear_w8a16(const void* x, long long ldx, const void* wq, long long l
     return -4;
   const int total = a.tiles * a.splits;
   const int grid = total < sms ? total : sms;
-  const size_t smem = (size_t)a.stages * raw_bytes + 2 * kWaConvBytes + 256 + 1024;
+  const size_t smem = (size_t)a.stages * raw_bytes + kWaConvBufs * kWaConvBytes + 512 + 1024;
   gemm_w8a16_kernel<<<grid, kWaThreads, smem, stream>>>(tw, tx, a);
   if (cudaGetLastError() != cudaSuccess) return -5;
   if (a.splits > 1) {

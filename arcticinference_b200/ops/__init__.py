@@ -9,6 +9,7 @@ also the oracles of the numerics tests.
 from __future__ import annotations
 
 import math
+import sys
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -24,13 +25,62 @@ __all__ = [
 
 
 class _LaunchCounter:
-    """Counts launches of this package's own kernels (used by bench.py)."""
+    """Counts launches of this package's own kernels (used by bench.py). While an
+    :class:`OpTimer` is active every counted op also drops a CUDA event, which attributes the
+    device time since the previous op to the calling wrapper."""
 
     def __init__(self):
         self.n = 0
+        self.timer = None
 
     def add(self, k: int = 1):
         self.n += k
+        if self.timer is not None:
+            self.timer.mark(sys._getframe(1).f_code.co_name)
+
+
+class OpTimer:
+    """Per-op device time of a stretch of eager execution.
+
+        with ops.OpTimer() as t:
+            model.forward(...)
+        print(t.summary())
+
+    An event follows every op; the time between consecutive events is booked on the later op
+    (it includes that op's launch gap). ``head_start_us`` makes the GPU spin first so that the
+    host can queue ahead and the gaps are the device's own, not Python's."""
+
+    def __init__(self, head_start_us: float = 20000.0):
+        self.head_start_us = head_start_us
+        self.marks: list = []
+
+    def __enter__(self):
+        torch.cuda.synchronize()
+        if self.head_start_us > 0:
+            torch.cuda._sleep(int(self.head_start_us * 1900))
+        self.mark("_start")
+        launch_counter.timer = self
+        return self
+
+    def mark(self, name: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.marks.append((name, ev))
+
+    def __exit__(self, *exc):
+        launch_counter.timer = None
+        torch.cuda.synchronize()
+
+    def records(self) -> list:
+        return [(n1, e0.elapsed_time(e1) * 1e3)
+                for (n0, e0), (n1, e1) in zip(self.marks, self.marks[1:])]
+
+    def summary(self) -> dict:
+        out: dict = {}
+        for name, us in self.records():
+            tot, cnt = out.get(name, (0.0, 0))
+            out[name] = (tot + us, cnt + 1)
+        return dict(sorted(out.items(), key=lambda kv: -kv[1][0]))
 
 
 launch_counter = _LaunchCounter()
@@ -286,6 +336,25 @@ def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, ro
         k_cache.data_ptr(), v_cache.data_ptr(), T, Hq, Hkv, D, bs, k_cache.shape[0] * bs,
         1 if rotate_q else 0, nat.status_buffer(qkv.device).data_ptr(), nat.stream_ptr())
     nat.check(rc, "rope_cache")
+    launch_counter.add(1)
+
+
+def peer_barrier(flag_arrays, my_rank: int, epoch_counter: torch.Tensor, limit_ms: int = 1000) -> None:
+    """Flag barrier among ``len(flag_arrays)`` ranks with a bounded wait. ``flag_arrays[r]`` is
+    rank r's array of uint32 arrival slots (int32 tensors of >= 16 elements, here or in peer
+    memory); ``epoch_counter`` is this rank's int32[1] barrier count. A peer that does not
+    arrive within ``limit_ms`` leaves code 2 in the status word (``check_status`` raises
+    ``KernelTimeout``); nothing hangs."""
+    import ctypes
+    nat = _native()
+    arr = (ctypes.c_void_p * len(flag_arrays))(*[t.data_ptr() for t in flag_arrays])
+    nat.declare("ab200_barrier_timed", ctypes.c_int,
+                [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                 ctypes.c_void_p, ctypes.c_void_p])
+    rc = nat.lib().ab200_barrier_timed(arr, my_rank, len(flag_arrays), epoch_counter.data_ptr(),
+                                       int(limit_ms), nat.status_buffer(epoch_counter.device).data_ptr(),
+                                       nat.stream_ptr())
+    nat.check(rc, "barrier_timed")
     launch_counter.add(1)
 
 

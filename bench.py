@@ -39,7 +39,7 @@ def parse_args():
     ap.add_argument("--model", type=str, default="llama-3.1-8b")
     ap.add_argument("--quantization", type=str, default="fp8",
                     help='"fp8" (block-scaled fp8 weights, bf16 activations; the named config) or "none" (bf16)')
-    ap.add_argument("--requests-per-gpu", type=int, default=32)
+    ap.add_argument("--requests-per-gpu", type=int, default=128)
     ap.add_argument("--input-len", type=int, default=2000)
     ap.add_argument("--output-len", type=int, default=250)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
