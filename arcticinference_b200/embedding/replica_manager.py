@@ -287,6 +287,10 @@ def make_parser() -> argparse.ArgumentParser:
     return ap
 
 
-if __name__ == "__main__":
+def main_cli(argv=None) -> None:
     logging.basicConfig(level=logging.INFO)
-    asyncio.run(serve(make_parser().parse_args()))
+    asyncio.run(serve(make_parser().parse_args(argv)))
+
+
+if __name__ == "__main__":
+    main_cli()

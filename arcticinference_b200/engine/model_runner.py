@@ -26,6 +26,7 @@ import torch
 from .. import ops
 from ..config import EngineConfig
 from ..models.llama import ForwardBatch, LlamaForCausalLM, ShardSpec
+from ..utils.tracing import trace_range
 from .kv_cache import KVCacheTensors
 from .scheduler import SchedulerOutput
 
@@ -348,24 +349,30 @@ class ModelRunner:
         drafts: dict = {}
         g = self._decode_graph(out)
         if g is not None:
-            rows = g.fill(out)
+            with trace_range("prepare"):
+                rows = g.fill(out)
             self.mode_counts[g.mode] += 1
             self.graph_replays += 1
-            ids_dev, hidden = g.replay()
+            with trace_range("graph_replay"):
+                ids_dev, hidden = g.replay()
             self.h2d_total += g.h64.numel() * 8 + g.h32.numel() * 4
             num_tokens, mode = g.bucket, g.mode
         else:
-            batch, rows = self.prepare(out)
+            with trace_range("prepare"):
+                batch, rows = self.prepare(out)
             self.mode_counts[batch.mode] += 1
             num_tokens, mode = batch.num_tokens, batch.mode
             if batch.logits_indices.numel() == 0:
                 # pure prefill chunk: KV only
                 self.model.forward(batch, self.kv)
                 return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)
-            hidden = self.model.forward(batch, self.kv)
-            logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
-            ids_dev = self._sample(logits, sched, rows)
-        ids = ids_dev.tolist()  # device -> host; synchronises the step
+            with trace_range("forward", tokens=batch.num_tokens, mode=batch.mode):
+                hidden = self.model.forward(batch, self.kv)
+            with trace_range("sample"):
+                logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
+                ids_dev = self._sample(logits, sched, rows)
+        with trace_range("sync_tokens"):
+            ids = ids_dev.tolist()  # device -> host; synchronises the step
         self.d2h_total += ids_dev.numel() * 8
         accepted_rows = []
         for s, rr in zip(sched, rows):
@@ -384,5 +391,6 @@ class ModelRunner:
             accepted_rows.append(rr[len(toks) - 1])
         if self.proposer is not None or self.suffix_cache is not None:
             from ..spec_decode.propose import propose_drafts
-            drafts = propose_drafts(self, sched, rows, new_tokens, hidden, accepted_rows)
+            with trace_range("draft"):
+                drafts = propose_drafts(self, sched, rows, new_tokens, hidden, accepted_rows)
         return StepResult(new_tokens, drafts, num_tokens, mode)

@@ -148,6 +148,16 @@ def dequant_fp8(w) -> torch.Tensor:
 W8A16_MAX_TOKENS = 128
 
 
+def fp8_prefers_bf16(w, num_tokens: int) -> bool:
+    """Which route a block-scaled fp8 linear takes for ``num_tokens`` rows: above the
+    weight-only decode kernel's range the bf16 GEMM runs on the resident bf16 shadow when
+    the model keeps one, and on a freshly expanded copy once the step is long enough to
+    amortise the expansion; the W8A8 kernel covers what is left."""
+    if num_tokens <= W8A16_MAX_TOKENS:
+        return False
+    return getattr(w, "shadow", None) is not None or num_tokens >= DEQUANT_MIN_TOKENS
+
+
 def linear_fp8(x: torch.Tensor, w, out=None, force_splits: int = 0, peer=None,
                mode: str = "auto") -> torch.Tensor:
     """Block-scaled fp8 linear: x bf16 [M, K] is quantised on the fly; w is an ``Fp8Weight``.
@@ -163,8 +173,8 @@ def linear_fp8(x: torch.Tensor, w, out=None, force_splits: int = 0, peer=None,
     nat = _native()
     M, K = x.shape
     N = w.shape[0]
-    if M >= DEQUANT_MIN_TOKENS and peer is None and mode == "auto":
-        # long prefill: expand the weight once into bf16 scratch and run the bf16 GEMM, so the
+    if peer is None and mode == "auto" and fp8_prefers_bf16(w, M):
+        # bf16 GEMM on the shadow copy (or on a copy expanded once per long prefill step): the
         # activations stay in bf16 and the tensor cores never wait on per-block rescaling
         return linear(x, dequant_fp8(w), out=out)
     ws = nat.workspace(x.device)

@@ -119,8 +119,8 @@ class FusedCommunicator(Communicator):
         n = x_local.shape[0]
         N = n * self.sp
         s = self.topo.sp_rank
-        if not isinstance(wqkv, torch.Tensor) and n >= ops.DEQUANT_MIN_TOKENS:
-            wqkv = ops.dequant_fp8(wqkv)          # long prefill: expand once, bf16 GEMM
+        if not isinstance(wqkv, torch.Tensor) and ops.fp8_prefers_bf16(wqkv, n):
+            wqkv = ops.dequant_fp8(wqkv)          # bf16 shadow, or expanded once for long prefill
         if not isinstance(wqkv, torch.Tensor):   # block-scaled fp8 weights
             ops.linear_fp8(x_local, wqkv, peer=(self._qkv_ptrs, self.sp, blk_rows, s * n, blk_rows))
             self.device_barrier()
