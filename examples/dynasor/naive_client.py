@@ -5,6 +5,10 @@ against any OpenAI-compatible completions endpoint (what the proxy automates).
 """
 
 import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 import requests
 
