@@ -92,10 +92,9 @@ class EmbeddingEngine:
                 ids = self.tokenizer.encode(p)
                 ids = list(ids["input_ids"]) if isinstance(ids, dict) else list(ids)
             else:
-                ids = [int(t) for t in p]
-            if not ids:
-                ids = [0]
-            out.append(ids[: self.max_len])
+                ids = p
+            a = np.asarray(ids, dtype=np.int64).reshape(-1)[: self.max_len]
+            out.append(a if a.size else np.zeros(1, dtype=np.int64))
         return out
 
     def plan_batches(self, lens: Sequence[int]) -> list:
@@ -115,16 +114,16 @@ class EmbeddingEngine:
 
     # ------------------------------------------------------------------ execution
     def _fill(self, st: _Staging, seqs: list) -> tuple:
-        n, pos = 0, 0
         ids, starts = st.ids.numpy(), st.starts.numpy()
-        for j, s in enumerate(seqs):
-            m = len(s)
-            ids[0, pos:pos + m] = s
-            ids[1, pos:pos + m] = np.arange(m)
-            starts[j] = pos
-            pos += m
-        starts[len(seqs)] = pos
-        return pos, len(seqs)
+        lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=len(seqs))
+        S = len(seqs)
+        starts[0] = 0
+        np.cumsum(lens, out=starts[1:S + 1])
+        T = int(starts[S])
+        np.concatenate(seqs, out=ids[0, :T])
+        # position of token t inside its sequence = t - start of that sequence
+        ids[1, :T] = np.arange(T) - np.repeat(starts[:S], lens)
+        return T, S
 
     def _drain(self, st: _Staging, result: np.ndarray) -> None:
         if st.pending is None:

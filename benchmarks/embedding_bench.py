@@ -26,7 +26,8 @@ from arcticinference_b200.embedding.engine import EmbeddingEngine  # noqa: E402
 
 def run(engine, n_seqs, length, iters, warmup):
     rng = np.random.default_rng(0)
-    seqs = [rng.integers(0, engine.cfg.vocab_size, size=length).tolist() for _ in range(n_seqs)]
+    # pre-tokenised inputs as they arrive from the wire: one int array per sequence
+    seqs = list(rng.integers(0, engine.cfg.vocab_size, size=(n_seqs, length), dtype=np.int64))
     for _ in range(warmup):
         engine.encode(seqs[: max(64, n_seqs // 8)])
     torch.cuda.synchronize()
