@@ -93,23 +93,10 @@ class DecodeGraph:
         bt = h32[:B * MB].reshape(B, MB)
         work = h32[B * MB:B * MB + self.work_cap * 8].reshape(self.work_cap, 8)
         tok_splits = h32[B * MB + self.work_cap * 8:]
-        q_lens, kv_lens, rows = [], [], []
-        t = 0
-        for i, s in enumerate(out.scheduled):
-            req = s.request
-            n = s.num_tokens
-            seq = [req.token_at(s.start)] + list(req.spec_token_ids[:n - 1]) if n > 1 else \
-                [req.token_at(s.start)]
-            ids[t:t + n] = seq
-            p = np.arange(s.start, s.start + n, dtype=np.int64)
-            pos[t:t + n] = p
-            blocks = np.asarray(req.block_ids, dtype=np.int64)
-            slots[t:t + n] = blocks[p // bs] * bs + p % bs
-            bt[i, :len(req.block_ids)] = req.block_ids
-            q_lens.append(n)
-            kv_lens.append(s.start + n)
-            rows.append(list(range(t, t + n)))
-            t += n
+        from .model_runner import pack_tokens
+        q_lens, kv_lens, offs = pack_tokens(out.scheduled, bs, ids, pos, slots, bt)
+        rows = [[t] if n == 1 else list(range(t, t + n)) for t, n in zip(offs, q_lens)]
+        t = offs[-1] + q_lens[-1] if offs else 0
         N = t
         if N < B:
             ids[N:] = 0

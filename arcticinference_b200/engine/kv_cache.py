@@ -174,6 +174,7 @@ class KVCacheManager:
     def free(self, request) -> None:
         self.pool.release(request.block_ids)
         request.block_ids = []
+        request._block_array = None
         self._hashes.pop(request.request_id, None)
 
     def slot(self, request, position: int) -> int:

@@ -31,6 +31,46 @@ from .kv_cache import KVCacheTensors
 from .scheduler import SchedulerOutput
 
 
+def pack_tokens(sched, bs: int, ids, pos, slots, bt):
+    """Write token ids, positions, cache slots and block-table rows of the scheduled requests
+    into the staging arrays. Single-token requests (the bulk of a serving step) are gathered
+    in Python lists and written with three vector assignments; only multi-token chunks touch
+    numpy per request. Returns (q_lens, kv_lens, token offset of each request)."""
+    one_t, one_tok, one_pos, one_slot = [], [], [], []
+    q_lens, kv_lens, offs = [], [], []
+    t = 0
+    for i, s in enumerate(sched):
+        r = s.request
+        n = s.num_tokens
+        st = s.start
+        offs.append(t)
+        if n == 1:
+            one_t.append(t)
+            one_tok.append(r.token_at(st))
+            one_pos.append(st)
+            one_slot.append(r.block_ids[st // bs] * bs + st % bs)
+        else:
+            known = r.num_tokens
+            seq = r.tokens_slice(st, min(st + n, known))
+            if len(seq) < n:
+                seq = seq + list(r.spec_token_ids[:n - len(seq)])
+            ids[t:t + n] = seq
+            p = np.arange(st, st + n, dtype=np.int64)
+            pos[t:t + n] = p
+            blocks = r.block_array().astype(np.int64)
+            slots[t:t + n] = blocks[p // bs] * bs + p % bs
+        row = r.block_array()
+        bt[i, :row.size] = row
+        q_lens.append(n)
+        kv_lens.append(st + n)
+        t += n
+    if one_t:
+        ids[one_t] = one_tok
+        pos[one_t] = one_pos
+        slots[one_t] = one_slot
+    return q_lens, kv_lens, offs
+
+
 @dataclass
 class StepResult:
     new_tokens: dict          # request_id -> list[int]
@@ -172,7 +212,6 @@ class ModelRunner:
                     self.cascade_steps += 1
         pad_to = self.sp if mode == "sp" else 1
         Np = (N + pad_to - 1) // pad_to * pad_to
-        q_lens, kv_lens = [], []
         n_sel = sum((s.num_draft + 1) if s.samples else 0 for s in sched)
         max_blocks = max(len(s.request.block_ids) for s in sched)
         stage = self._stage(3 * Np + n_sel + n_sel)
@@ -181,38 +220,28 @@ class ModelRunner:
         sel = h[3 * Np:3 * Np + n_sel]
         sel_pos = h[3 * Np + n_sel:3 * Np + 2 * n_sel]
         bt = np.zeros((len(sched), max_blocks), dtype=np.int32)
-        t = 0
+        q_lens, kv_lens, offs = pack_tokens(sched, bs, ids, pos, slots, bt)
         k = 0
         rows = []
         sel_q_lens = []
-        for i, s in enumerate(sched):
-            r = s.request
-            n = s.num_tokens
-            toks = r.all_token_ids
-            known = len(toks)
-            seq = toks[s.start:min(s.start + n, known)]
-            if len(seq) < n:
-                seq = seq + list(r.spec_token_ids[:n - len(seq)])
-            ids[t:t + n] = seq
-            p = np.arange(s.start, s.start + n, dtype=np.int64)
-            pos[t:t + n] = p
-            blocks = np.asarray(r.block_ids, dtype=np.int64)
-            slots[t:t + n] = blocks[p // bs] * bs + p % bs
-            bt[i, :len(r.block_ids)] = r.block_ids
-            q_lens.append(n)
-            kv_lens.append(s.start + n)
+        for s, t in zip(sched, offs):
             if s.samples:
                 m = s.num_draft + 1
-                idx = np.arange(t + n - m, t + n, dtype=np.int64)
-                sel[k:k + m] = idx
-                sel_pos[k:k + m] = p[n - m:]
-                rows.append(list(range(k, k + m)))
+                last = t + s.num_tokens
+                if m == 1:
+                    sel[k] = last - 1
+                    sel_pos[k] = s.start + s.num_tokens - 1
+                    rows.append([k])
+                else:
+                    sel[k:k + m] = np.arange(last - m, last, dtype=np.int64)
+                    sel_pos[k:k + m] = np.arange(s.start + s.num_tokens - m, s.start + s.num_tokens,
+                                                 dtype=np.int64)
+                    rows.append(list(range(k, k + m)))
                 sel_q_lens.append(m)
                 k += m
             else:
                 rows.append([])
                 sel_q_lens.append(0)
-            t += n
         if Np > N:
             ids[N:] = 0
             pos[N:] = 0

@@ -28,7 +28,7 @@ _FINISH_REASON = {RequestStatus.FINISHED_STOPPED: "stop", RequestStatus.FINISHED
                   RequestStatus.FINISHED_ABORTED: "abort"}
 
 
-@dataclass
+@dataclass(eq=False)     # identity comparison: requests sit in lists that are searched every step
 class Request:
     request_id: str
     prompt_token_ids: list[int]
@@ -49,9 +49,28 @@ class Request:
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
     output_logprobs: Optional[list] = None
     routing_key: Optional[str] = None
+    _block_array: Optional[object] = field(default=None, repr=False)
 
     def __post_init__(self):
         self.metrics.arrival_time = self.arrival_time
+
+    def block_array(self):
+        """``block_ids`` as an int32 array, rebuilt only when the table grew (the KV manager
+        drops it when it frees the request's blocks)."""
+        a = self._block_array
+        if a is None or a.size != len(self.block_ids):
+            import numpy as np
+            a = self._block_array = np.asarray(self.block_ids, dtype=np.int32)
+        return a
+
+    def tokens_slice(self, a: int, b: int) -> list:
+        """Known tokens [a, b) without concatenating prompt and output."""
+        n = len(self.prompt_token_ids)
+        if b <= n:
+            return self.prompt_token_ids[a:b]
+        if a >= n:
+            return self.output_token_ids[a - n:b - n]
+        return self.prompt_token_ids[a:] + self.output_token_ids[:b - n]
 
     @property
     def num_prompt_tokens(self) -> int:

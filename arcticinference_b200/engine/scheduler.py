@@ -120,8 +120,8 @@ class Scheduler:
         for req in list(self.running):
             if budget <= 0:
                 break
-            if req not in self.running:  # preempted while serving an earlier request
-                continue
+            if out.preempted and req.status == RequestStatus.PREEMPTED:
+                continue                 # preempted while serving an earlier request
             if self._in_prefill(req):
                 req.spec_token_ids = []
             elif idx >= draft_limit:

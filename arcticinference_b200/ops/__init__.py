@@ -552,6 +552,9 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
     tiles to occupy the GPU (decode), the keys of each sequence are cut into up to 16 splits
     of whole 128-key tiles."""
     tpt = 128 // G
+    if len(q_lens) >= 16 and max(q_lens) == 1 and min(q_lens) == 1:
+        return _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split,
+                                 max_splits_cap)
     rows = []
     T = int(sum(q_lens))
     tok_splits = np.ones(max(T, 1), dtype=np.int32)
@@ -587,6 +590,35 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
         rows.sort(key=lambda r: -(min(r[5], r[3] + r[2]) - r[4]))
     work = np.asarray(rows, dtype=np.int32).reshape(-1, 8)
     return work, tok_splits, max_splits
+
+
+def _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split, max_splits_cap):
+    """The planner above for the one-token-per-sequence case, on arrays (same rows, same
+    order): a serving step with a thousand sequences must not spend milliseconds here."""
+    kl = np.asarray(kv_lens, dtype=np.int64)
+    R = kl.size
+    if G <= 32:
+        num_sms *= 2
+    key_tiles = (kl + TILE_KEYS - 1) // TILE_KEYS
+    ns = np.ones(R, dtype=np.int64)
+    if allow_split and R * Hkv < num_sms:
+        want = max(1, num_sms // max(1, R * Hkv))
+        cand = np.minimum(np.minimum(16, max_splits_cap), np.minimum(want, np.maximum(1, key_tiles // 2)))
+        ns = np.where(key_tiles > 4, cand, 1)
+    tps = (key_tiles + ns - 1) // ns
+    ns = (key_tiles + tps - 1) // tps
+    seq = np.arange(R, dtype=np.int64) if seq_rows is None else np.asarray(seq_rows, dtype=np.int64)
+    rep = np.repeat(np.arange(R), ns)
+    first = np.cumsum(ns) - ns
+    sidx = np.arange(rep.size) - first[rep]                     # split index within its sequence
+    ks = sidx * tps[rep] * TILE_KEYS
+    ke = np.minimum(kl[rep], (sidx + 1) * tps[rep] * TILE_KEYS)
+    work = np.stack([seq[rep], rep, np.ones_like(rep), kl[rep] - 1, ks, ke, sidx, ns[rep]], 1)
+    if causal:
+        order = np.argsort(-(np.minimum(ke, kl[rep]) - ks), kind="stable")
+        work = work[order]
+    tok_splits = ns.astype(np.int32)
+    return work.astype(np.int32), tok_splits, int(ns.max()) if R else 1
 
 
 def pick_tile_keys(q_lens, G: int) -> int:
