@@ -220,8 +220,11 @@ class SpeculativeConfig:
     suffix_max_spec_offset: float = 0.0
     suffix_min_token_prob: float = 0.1
     draft_tensor_parallel_size: Optional[int] = None
+    quantization: Optional[str] = None     # "fp8": block-scaled fp8 projections and LM heads of the drafter
 
     def __post_init__(self):
+        if self.quantization not in (None, "fp8"):
+            raise ValueError("speculator quantization must be None or 'fp8'")
         if self.method not in (None, "arctic", "mlp_speculator", "suffix"):
             raise ValueError("unknown speculative method %r" % (self.method,))
         arctic = self.method in ("arctic", "mlp_speculator")

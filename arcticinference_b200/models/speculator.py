@@ -180,6 +180,24 @@ class ArcticSpeculator:
         from .loader import iter_safetensors_dir
         self.load_state(iter_safetensors_dir(path))
 
+    def quantize_fp8(self) -> int:
+        """Store the projections and LM heads as block-scaled fp8 (embeddings and norms stay
+        bf16); matrices whose dimensions are not multiples of 128 are left alone. Returns the
+        number of tensors converted. (Reference: arctic_inference/vllm/spec_dec/fp8.py:140-309
+        quantises the same linears of its speculators.)"""
+        from .quant import quantize_weight_fp8
+        n = 0
+        for k, t in list(self.w.items()):
+            if not isinstance(t, torch.Tensor) or t.dim() != 2:
+                continue
+            if not (k.startswith("proj") or k.startswith("head")):
+                continue
+            if t.shape[0] % 128 or t.shape[1] % 128:
+                continue
+            self.w[k] = quantize_weight_fp8(t)
+            n += 1
+        return n
+
     def weight_slots(self):
         """(owner, key) pairs of every tensor, for sleep / wake and weight sync."""
         return [(self.w, k) for k in list(self.w)]

@@ -43,6 +43,9 @@ def attach_speculation(engine) -> None:
             runner.proposer = build_speculator(scfg, runner.device, seed=engine.config.seed + 1)
         else:
             runner.proposer = build_speculator(cfg.model, runner.device)
+        if cfg.quantization == "fp8":
+            n = runner.proposer.quantize_fp8()
+            logger.info("speculator: %d matrices stored as block-scaled fp8", n)
         if cfg.num_speculative_tokens is None:
             cfg.num_speculative_tokens = runner.proposer.n_predict
         if runner.proposer.cfg.vocab_size != m.vocab_size:

@@ -1,0 +1,133 @@
+"""Fused compute+collective kernels against their "GEMM, then NCCL" equivalents, on N GPUs
+of one node (one process per GPU):
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
+        benchmarks/fused_comm_bench.py
+
+Cases (Llama-3.1-8B shapes, bf16; n = tokens per rank):
+
+* qkv_scatter: QKV projection whose epilogue stores every head shard into the rank that owns
+  it (Ulysses sequence -> head exchange) vs the same GEMM into local memory followed by
+  ``all_to_all_single``;
+* allreduce: row-parallel o_proj writing its partial product into the symmetric heap + the
+  one-shot peer-load all-reduce vs the GEMM + ``dist.all_reduce``.
+
+Times are CUDA events on the launching stream, median of ``--iters`` after warm-up, maximum
+over ranks. For each fused case the roofline time is the slower of FLOPs / measured bf16 peak
+and bytes sent per GPU / 770 GB/s (measured peer-copy bandwidth per direction on this pool;
+nominal 900); the printed fraction is roofline time / measured time.
+"""
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from arcticinference_b200 import ops  # noqa: E402
+from arcticinference_b200.parallel.comm import init_communicator  # noqa: E402
+
+LINK_GBS = 770.0
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get("bf16_tflops", 1590.0)
+    return 1590.0
+
+
+def timed(fn, iters, warm=5):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(200000)          # let the host queue ahead of the device
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    t = torch.tensor([ts[len(ts) // 2]], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t) * 1e3                   # microseconds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--tokens", default="4096,512,64", help="tokens per rank, comma list")
+    a = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    comm = init_communicator(1, world, backend="fused")
+    rank, dev = comm.rank, comm.device
+    H, Hq, Hkv, D = 4096, 32, 8, 128
+    h, hkv = Hq // world, max(1, Hkv // world)
+    blk = (h + 2 * hkv) * D
+    sizes = [int(t) for t in a.tokens.split(",")]
+    nmax = max(sizes)
+    comm.setup(nmax * world, nmax * world, blk, H, world * h * D)
+    peak = peaks()
+    R = lambda *s: (torch.randn(*s, device=dev) * 0.05).to(torch.bfloat16)
+    wqkv = R(world * blk, H)               # rank-major head blocks
+    wo = R(H, h * D)                       # this rank's o_proj columns
+    res = []
+    for n in sizes:
+        x = R(n, H)
+        # ---- QKV GEMM with the head exchange in its epilogue
+        t_fused = timed(lambda: comm.qkv_scatter_heads(x, wqkv, blk), a.iters)
+        send = torch.empty(n, world * blk, dtype=torch.bfloat16, device=dev)
+        recv = torch.empty(world * n, blk, dtype=torch.bfloat16, device=dev)
+
+        def unfused():
+            ops.linear(x, wqkv, out=send)
+            # [n, W*blk] -> W chunks of [n, blk]
+            chunks = send.view(n, world, blk).transpose(0, 1).contiguous()
+            dist.all_to_all_single(recv.view(world, n, blk), chunks)
+
+        t_base = timed(unfused, a.iters)
+        flops = 2.0 * n * world * blk * H
+        sent = n * (world - 1) * blk * 2.0
+        roof = max(flops / (peak * 1e12), sent / (LINK_GBS * 1e9)) * 1e6
+        res.append({"case": "qkv_scatter", "tokens_per_rank": n, "fused_us": t_fused, "gemm_then_nccl_us": t_base,
+                    "speedup": t_base / t_fused, "roofline_us": roof, "fraction_of_roofline": roof / t_fused,
+                    "bytes_sent_per_gpu": sent, "flops": flops})
+        # ---- row-parallel GEMM + all-reduce
+        a_in = R(n, h * D)
+
+        def fused_ar():
+            comm.begin_forward()
+            buf = comm.reduce_buffer(n, H)
+            ops.linear(a_in, wo, out=buf)
+            return comm.all_reduce_full(buf)
+
+        out_local = torch.empty(n, H, dtype=torch.bfloat16, device=dev)
+
+        def nccl_ar():
+            ops.linear(a_in, wo, out=out_local)
+            dist.all_reduce(out_local)
+
+        t_f, t_b = timed(fused_ar, a.iters), timed(nccl_ar, a.iters)
+        flops = 2.0 * n * H * h * D
+        moved = n * H * 2.0 * (world - 1)          # one-shot: every rank reads the other ranks' partials
+        roof = max(flops / (peak * 1e12), moved / (LINK_GBS * 1e9)) * 1e6
+        res.append({"case": "gemm_allreduce", "tokens": n, "fused_us": t_f, "gemm_then_nccl_us": t_b,
+                    "speedup": t_b / t_f, "roofline_us": roof, "fraction_of_roofline": roof / t_f,
+                    "bytes_read_per_gpu": moved, "flops": flops})
+    ops.check_status()
+    if rank == 0:
+        for r in res:
+            print(json.dumps(r))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -78,3 +78,14 @@ def test_verify_greedy_reference():
     assert nxt.tolist() == [99, 21, 33]
     assert sel.tolist() == [2, 4, 7]
     assert out.tolist() == [[11, 12, 99, -1], [21, -1, -1, -1], [31, 32, 33, -1]]
+
+
+def test_fp8_speculator_keeps_outputs(baseline):
+    llm = LLM(speculative_config={"method": "arctic", "model": "random", "num_speculative_tokens": 3,
+                                  "quantization": "fp8"}, **KW)
+    from arcticinference_b200.models.quant import Fp8Weight
+    assert any(isinstance(t, Fp8Weight) for t in llm.engine.runner.proposer.w.values())
+    assert _tokens(llm.generate(PROMPTS, SP)) == baseline
+    llm.sleep(2)
+    llm.wake_up()
+    assert _tokens(llm.generate(PROMPTS, SP)) == baseline
