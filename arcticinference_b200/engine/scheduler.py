@@ -117,28 +117,40 @@ class Scheduler:
 
         # 1) running requests (decodes and partially prefilled prompts)
         idx = 0
+        bs = self.kv.block_size
+        max_len = cfg.max_model_len
+        sched_append = out.scheduled.append
         for req in list(self.running):
             if budget <= 0:
                 break
             if out.preempted and req.status == RequestStatus.PREEMPTED:
                 continue                 # preempted while serving an earlier request
-            if self._in_prefill(req):
-                req.spec_token_ids = []
-            elif idx >= draft_limit:
-                req.spec_token_ids = []
-            if not self._in_prefill(req):
+            nt = len(req.prompt_token_ids) + len(req.output_token_ids)
+            computed = req.num_computed_tokens
+            prefilling = computed < nt - 1
+            if not prefilling:
+                # plain decode without a draft: one token, and usually no new block
+                if not req.spec_token_ids and computed + 1 <= len(req.block_ids) * bs:
+                    idx += 1
+                    sched_append(ScheduledRequest(req, computed, 1, 0, True))
+                    budget -= 1
+                    continue
+                if idx >= draft_limit:
+                    req.spec_token_ids = []
                 idx += 1
+            else:
+                req.spec_token_ids = []
             # never let a draft run past the model length
-            room = cfg.max_model_len - req.num_tokens - 1
+            room = max_len - nt - 1
             if len(req.spec_token_ids) > max(room, 0):
                 req.spec_token_ids = req.spec_token_ids[:max(room, 0)]
-            want = req.num_tokens + len(req.spec_token_ids) - req.num_computed_tokens
+            want = nt + len(req.spec_token_ids) - computed
             n = min(want, budget)
-            if n < want and not cfg.enable_chunked_prefill and self._in_prefill(req):
+            if n < want and not cfg.enable_chunked_prefill and prefilling:
                 continue
             if n < want:
                 req.spec_token_ids = []  # a chunked prompt carries no draft
-                n = min(req.num_tokens - req.num_computed_tokens, budget)
+                n = min(nt - computed, budget)
             while not self.kv.can_allocate(req, n):
                 if not self._preempt_last(out, req):
                     break
@@ -146,9 +158,8 @@ class Scheduler:
                 continue
             self.kv.allocate(req, n)
             nd = len(req.spec_token_ids)
-            samples = req.num_computed_tokens + n >= req.num_tokens + nd
-            out.scheduled.append(ScheduledRequest(req, req.num_computed_tokens, n, nd if samples else 0,
-                                                  samples))
+            samples = computed + n >= nt + nd
+            sched_append(ScheduledRequest(req, computed, n, nd if samples else 0, samples))
             budget -= n
 
         # 2) admit waiting requests
