@@ -64,15 +64,40 @@ def test_generate_matches_reference_tokens(model):
     assert match >= 0.7 * total
 
 
+def _first_step_logits(llm, prompt, sp):
+    """Generate and return (outputs, logits of the first sampled position)."""
+    model = llm.engine.runner.model
+    seen = []
+    orig = model.compute_logits
+
+    def spy(hidden, fp32=False):
+        out = orig(hidden, fp32=fp32)
+        seen.append(out.float().clone())
+        return out
+
+    model.compute_logits = spy
+    try:
+        outs = llm.generate([prompt], sp)
+    finally:
+        model.compute_logits = orig
+    return outs, seen[0][0]
+
+
 def test_chunked_prefill_equals_single_shot():
+    # a tiny random model has near-ties in its logits, so the comparison is on the logits
+    # themselves (and on the arg-max only where it is decided by a clear margin)
     sp = SamplingParams(temperature=0, max_tokens=5, ignore_eos=True)
     prompt = {"prompt_token_ids": [(7 * i) % 1000 + 1 for i in range(700)]}
-    a = LLM(model="llama-tiny", device="cuda:0", num_gpu_blocks_override=128, block_size=16,
-            max_model_len=1024, max_num_batched_tokens=4096).generate([prompt], sp)
-    b = LLM(model="llama-tiny", device="cuda:0", num_gpu_blocks_override=128, block_size=16,
-            max_model_len=1024, max_num_batched_tokens=256).generate([prompt], sp)
+    kw = dict(model="llama-tiny", device="cuda:0", num_gpu_blocks_override=128, block_size=16,
+              max_model_len=1024, enforce_eager=True)
+    a, la = _first_step_logits(LLM(max_num_batched_tokens=4096, **kw), prompt, sp)
+    b, lb = _first_step_logits(LLM(max_num_batched_tokens=256, **kw), prompt, sp)
     ops.check_status()
-    assert a[0].outputs[0].token_ids[0] == b[0].outputs[0].token_ids[0]
+    scale = float(la.abs().max())
+    assert float((la - lb).abs().max()) < 0.03 * scale + 0.03
+    top2 = torch.topk(la, 2).values
+    if float(top2[0] - top2[1]) > 0.06 * scale + 0.06:
+        assert a[0].outputs[0].token_ids[0] == b[0].outputs[0].token_ids[0]
 
 
 def test_prefix_cache_hit_gives_same_tokens():
