@@ -424,7 +424,7 @@ class EngineArgs:
     max_num_batched_tokens: Optional[int] = None
     max_num_seqs: int = 256
     enable_chunked_prefill: bool = True
-    async_scheduling: bool = False
+    async_scheduling: bool = True
     enforce_eager: bool = False
     enable_sleep_mode: bool = False
     comm_backend: str = "fused"
@@ -485,7 +485,9 @@ class EngineArgs:
         g.add_argument("--max-num-seqs", type=int, default=256)
         g.add_argument("--no-enable-chunked-prefill", dest="enable_chunked_prefill",
                        action="store_false", default=True)
-        g.add_argument("--async-scheduling", action="store_true")
+        g.add_argument("--async-scheduling", dest="async_scheduling", action="store_true", default=True,
+                       help="queue the next decode step before the previous step's tokens are read")
+        g.add_argument("--no-async-scheduling", dest="async_scheduling", action="store_false")
         g.add_argument("--enforce-eager", action="store_true")
         g.add_argument("--enable-sleep-mode", action="store_true")
         return parser

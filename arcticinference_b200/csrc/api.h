@@ -58,6 +58,8 @@ int ab200_kv_write_fp4(const void* k, long long ldk, const void* v, long long ld
 int ab200_kv_read_fp4(const void* codes, const void* scales, const void* slots, void* out,
                       long long ldo, long long R, int Hkv, int D, int block_size,
                       cudaStream_t stream);
+int ab200_patch_ids(void* ids, const void* src_rows, const void* prev_ids, long long n,
+                    long long n_prev, cudaStream_t stream);
 int ab200_argmax_sample(const void* logits, int dtype, long long ld, long long B, int V,
                         const void* temperature, const void* seeds, void* out_ids, void* out_vals,
                         long long index_offset, cudaStream_t stream);

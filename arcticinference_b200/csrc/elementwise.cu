@@ -364,6 +364,17 @@ argmax_sample_kernel(const T* __restrict__ logits, long long ld, int V,
   }
 }
 
+// Run-ahead scheduling: rows whose input token is the previous step's sampled token (not yet
+// known on the host) take it from that step's device result.
+__global__ void patch_ids_kernel(long long* __restrict__ ids, const long long* __restrict__ src_rows,
+                                 const long long* __restrict__ prev_ids, long long n,
+                                 long long n_prev) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long j = src_rows[i];
+  if (j >= 0 && j < n_prev) ids[i] = prev_ids[j];
+}
+
 }  // namespace ab200
 
 using namespace ab200;
@@ -434,6 +445,15 @@ int ab200_gather_rows(const void* src, long long ld, const void* idx, void* dst,
   gather_rows_kernel<<<(unsigned)R, 128, 0, stream>>>(
       reinterpret_cast<const bf16*>(src), ld, reinterpret_cast<const long long*>(idx),
       reinterpret_cast<bf16*>(dst), hidden);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int ab200_patch_ids(void* ids, const void* src_rows, const void* prev_ids, long long n,
+                    long long n_prev, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  patch_ids_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<long long*>(ids), reinterpret_cast<const long long*>(src_rows),
+      reinterpret_cast<const long long*>(prev_ids), n, n_prev);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -50,7 +50,7 @@ class DecodeGraph:
         # enough KV splits to occupy the GPU when the batch is small
         self.splits = int(max(1, min(16, 148 // max(1, bucket * hkv))))
         self.work_cap = bucket * self.splits + 1
-        n64 = 3 * bucket
+        n64 = 4 * bucket      # ids | positions | slots | source rows of run-ahead tokens
         n32 = bucket * self.max_blocks + self.work_cap * 8 + bucket
         pin = dev.type == "cuda"
         self.h64 = torch.zeros(n64, dtype=torch.int64, pin_memory=pin)
@@ -80,16 +80,29 @@ class DecodeGraph:
         self.ids_out = None
         self.hidden_out = None
         self.launches = 0
+        self._uploaded = torch.cuda.Event() if pin else None
+        self._upload_pending = False
 
     # ------------------------------------------------------------- host staging
-    def fill(self, out) -> list:
-        """Write this step's inputs into the pinned buffers. Returns rows per request."""
+    def wait_uploaded(self) -> None:
+        """The pinned buffers may be rewritten once the previous upload has left them."""
+        if self._upload_pending and self._uploaded is not None:
+            self._uploaded.synchronize()
+            self._upload_pending = False
+
+    def fill(self, out, src_rows=None) -> list:
+        """Write this step's inputs into the pinned buffers. Returns rows per request.
+        ``src_rows[t]`` >= 0: token t is the previous step's sampled token at that row."""
         r = self.runner
         bs = r.block_size
         B, MB = self.bucket, self.max_blocks
         h64 = self.h64.numpy()
         h32 = self.h32.numpy()
         ids, pos, slots = h64[:B], h64[B:2 * B], h64[2 * B:3 * B]
+        src = h64[3 * B:4 * B]
+        src[:] = -1
+        if src_rows is not None:
+            src[:len(src_rows)] = src_rows
         bt = h32[:B * MB].reshape(B, MB)
         work = h32[B * MB:B * MB + self.work_cap * 8].reshape(self.work_cap, 8)
         tok_splits = h32[B * MB + self.work_cap * 8:]
@@ -116,6 +129,9 @@ class DecodeGraph:
     def upload(self) -> None:
         self.d64.copy_(self.h64, non_blocking=True)
         self.d32.copy_(self.h32, non_blocking=True)
+        if self._uploaded is not None:
+            self._uploaded.record()
+            self._upload_pending = True
 
     # ------------------------------------------------------------------ capture
     def _body(self):
@@ -145,8 +161,11 @@ class DecodeGraph:
         self.launches = ops.count_launches() - n0
         torch.cuda.synchronize()
 
-    def replay(self):
+    def replay(self, prev_ids=None):
         self.upload()
+        if prev_ids is not None:
+            B = self.bucket
+            ops.patch_ids(self.d64[:B], self.d64[3 * B:4 * B], prev_ids)
         self.graph.replay()
         ops.launch_counter.add(self.launches)
         return self.ids_out, self.hidden_out

@@ -49,11 +49,12 @@ class LLMEngine:
         self.tokenizer = get_tokenizer(config.tokenizer or config.model.name_or_path,
                                        config.model.vocab_size)
         self._seq = 0
+        self._pending = None            # a step queued on the device whose tokens are unread
         self._parents: dict[str, dict] = {}
         self.step_count = 0
         self.sleeping_level = 0
         self.stats = {"prompt_tokens": 0, "generation_tokens": 0, "steps": 0,
-                      "draft_tokens": 0, "accepted_tokens": 0}
+                      "draft_tokens": 0, "accepted_tokens": 0, "run_ahead_steps": 0}
         if config.speculative is not None:
             from ..spec_decode.propose import attach_speculation
             attach_speculation(self)
@@ -102,19 +103,55 @@ class LLMEngine:
             self.runner.suffix_cache.stop_request(request_id)
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._pending is not None
 
     # ------------------------------------------------------------------- step
     def step(self, partial: bool = False) -> list[RequestOutput]:
         """One scheduling + model step. Returns the requests that finished; with
         ``partial`` also an unfinished ``RequestOutput`` (cumulative text and tokens) for every
-        request that produced tokens in this step, for streaming front ends."""
+        request that produced tokens in this step, for streaming front ends.
+
+        With ``async_scheduling`` a decode-only step is left running on the device and its
+        tokens are read by the *next* call, after that call has already scheduled and queued
+        the following step (the host's scheduling and batching work then overlaps the GPU)."""
         if self.sleeping_level:
             raise RuntimeError("engine is sleeping; call wake_up() first")
-        out = self.scheduler.schedule()
-        if out.is_empty:
-            return []
-        result = self.runner.execute(out)
+        prev, self._pending = self._pending, None
+        if prev is None:
+            out = self.scheduler.schedule()
+            if out.is_empty:
+                return []
+            pend = self.runner.launch(out)
+            if self._can_run_ahead(out):
+                self._pending = pend
+                return []
+            return self._complete(pend, partial)
+        nxt = None
+        if self._can_run_ahead(prev.out):
+            self.scheduler.advance_provisionally(prev.out)
+            out = self.scheduler.schedule()
+            if not out.is_empty:
+                nxt = self.runner.launch(out, prev)
+                self.stats["run_ahead_steps"] += 1
+        outputs = self._complete(prev, partial)
+        self._pending = nxt
+        return outputs
+
+    def _can_run_ahead(self, out) -> bool:
+        """A step may be left in flight when the next step can be scheduled without knowing
+        its tokens: decode only, nothing waiting for admission, no drafting, device sampling."""
+        if not self.config.scheduler.async_scheduling or self.config.speculative is not None:
+            return False
+        if self.scheduler.waiting:
+            return False
+        for s in out.scheduled:
+            if not s.samples or s.num_tokens != 1 or s.request.sampling_params.needs_full_logits:
+                return False
+        return True
+
+    def _complete(self, pend, partial: bool) -> list[RequestOutput]:
+        out = pend.out
+        result = self.runner.finish(pend)
         finished = self.scheduler.update_from_output(out, result.new_tokens, result.drafts)
         self.step_count += 1
         self.stats["steps"] += 1
@@ -132,7 +169,8 @@ class LLMEngine:
             done_ids = {r.request_id for r in finished}
             for s in out.scheduled:
                 req = s.request
-                if req.request_id in done_ids or not result.new_tokens.get(req.request_id):
+                if req.request_id in done_ids or not result.new_tokens.get(req.request_id) or \
+                        req.status.finished:
                     continue
                 outputs.append(RequestOutput(req.parent_id or req.request_id, req.prompt,
                                              req.prompt_token_ids, [self._completion(req)], False,
@@ -178,7 +216,7 @@ class LLMEngine:
         """Level 1 frees the KV cache; level 2 also moves the weights (and the drafter's)
         to host memory (reference: arctic_inference/server/worker.py:275-390,
         arctic_inference/vllm/patches.py:284-310)."""
-        if self.scheduler.has_work():
+        if self.scheduler.has_work() or self._pending is not None:
             raise RuntimeError("cannot sleep with unfinished requests")
         from .sleep import sleep_engine
         sleep_engine(self, level)

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import math
 import time
+import zlib
 from dataclasses import dataclass
 from typing import Optional
 
@@ -71,6 +72,23 @@ def pack_tokens(sched, bs: int, ids, pos, slots, bt):
     return q_lens, kv_lens, offs
 
 
+PLACEHOLDER_TOKEN = -1      # stands for a sampled token the host has not read yet
+
+
+class PendingStep:
+    """A step that has been queued on the device."""
+
+    __slots__ = ("out", "rows", "ids_dev", "hidden", "num_tokens", "mode", "ids_host", "event",
+                 "row_of")
+
+    def __init__(self, out, rows, ids_dev, hidden, num_tokens, mode):
+        self.out, self.rows, self.ids_dev, self.hidden = out, rows, ids_dev, hidden
+        self.num_tokens, self.mode = num_tokens, mode
+        self.ids_host = None
+        self.event = None
+        self.row_of = {}
+
+
 @dataclass
 class StepResult:
     new_tokens: dict          # request_id -> list[int]
@@ -106,6 +124,8 @@ class ModelRunner:
         self._graphs = {}
         self._graph_pool = None
         self._graph_sizes = None
+        self._ids_host = [None, None]      # pinned landing buffers for sampled ids
+        self._ids_flip = 0
         self.graph_replays = 0
         self.cascade_steps = 0
         self._stage_cap = 0
@@ -306,7 +326,7 @@ class ModelRunner:
                 sv = np.zeros(n, dtype=np.int64)
                 for s, rr in zip(sched, rows):
                     sp = s.request.sampling_params
-                    base = sp.seed if sp.seed is not None else hash(s.request.request_id) & 0xFFFFFFF
+                    base = sp.seed if sp.seed is not None else zlib.crc32(s.request.request_id.encode()) & 0xFFFFFFF
                     for j, row in enumerate(rr):
                         tv[row] = 0.0 if sp.greedy else sp.temperature
                         sv[row] = (base * 1000003 + s.request.num_tokens + j) & 0x7FFFFFFFFFFFFFFF
@@ -371,43 +391,100 @@ class ModelRunner:
         return g or None
 
     # ------------------------------------------------------------------- step
-    @torch.inference_mode()
     def execute(self, out: SchedulerOutput) -> StepResult:
+        return self.finish(self.launch(out))
+
+    @torch.inference_mode()
+    def launch(self, out: SchedulerOutput, prev: Optional["PendingStep"] = None) -> "PendingStep":
+        """Queue one step on the device without waiting for its tokens. ``prev`` is the step
+        queued before this one whose tokens the host has not read yet: rows of this step that
+        feed ``prev``'s sampled token (a placeholder on the host) are patched on the device."""
         sched = out.scheduled
-        new_tokens: dict = {}
-        drafts: dict = {}
+        src_rows = None
+        if prev is not None and prev.ids_dev is not None:
+            # token offset of every request in this step -> row of its sampled token in prev
+            src, any_src, t = [], False, 0
+            for s in sched:
+                j = -1
+                if s.num_tokens == 1 and s.request.token_at(s.start) == PLACEHOLDER_TOKEN:
+                    j = prev.row_of.get(id(s.request), -1)
+                    any_src = any_src or j >= 0
+                src.append(j)
+                src.extend([-1] * (s.num_tokens - 1))
+                t += s.num_tokens
+            if any_src:
+                src_rows = src
         g = self._decode_graph(out)
         if g is not None:
             with trace_range("prepare"):
-                rows = g.fill(out)
+                g.wait_uploaded()
+                rows = g.fill(out, src_rows)
             self.mode_counts[g.mode] += 1
             self.graph_replays += 1
             with trace_range("graph_replay"):
-                ids_dev, hidden = g.replay()
+                ids_dev, hidden = g.replay(prev.ids_dev if src_rows is not None else None)
             self.h2d_total += g.h64.numel() * 8 + g.h32.numel() * 4
-            num_tokens, mode = g.bucket, g.mode
+            pend = PendingStep(out, rows, ids_dev, hidden, g.bucket, g.mode)
         else:
             with trace_range("prepare"):
                 batch, rows = self.prepare(out)
             self.mode_counts[batch.mode] += 1
-            num_tokens, mode = batch.num_tokens, batch.mode
+            if src_rows is not None:
+                n = batch.input_ids.numel()
+                idx = torch.tensor(src_rows + [-1] * (n - len(src_rows)), dtype=torch.int64)
+                if self.device.type == "cuda":
+                    idx = idx.pin_memory().to(self.device, non_blocking=True)
+                ops.patch_ids(batch.input_ids, idx, prev.ids_dev)
             if batch.logits_indices.numel() == 0:
                 # pure prefill chunk: KV only
                 self.model.forward(batch, self.kv)
-                return StepResult(new_tokens, drafts, batch.num_tokens, batch.mode)
+                return PendingStep(out, rows, None, None, batch.num_tokens, batch.mode)
             with trace_range("forward", tokens=batch.num_tokens, mode=batch.mode):
                 hidden = self.model.forward(batch, self.kv)
             with trace_range("sample"):
                 logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
                 ids_dev = self._sample(logits, sched, rows)
+            pend = PendingStep(out, rows, ids_dev, hidden, batch.num_tokens, batch.mode)
+        # the device result may be overwritten by the next replay of the same graph: take the
+        # host copy now, read it in finish()
+        if self.device.type == "cuda":
+            host = self._ids_host[self._ids_flip]
+            if host is None or host.numel() < pend.ids_dev.numel():
+                host = torch.empty(max(pend.ids_dev.numel(), 4096), dtype=torch.int64, pin_memory=True)
+                self._ids_host[self._ids_flip] = host
+            pend.ids_host = host[:pend.ids_dev.numel()]
+            pend.ids_host.copy_(pend.ids_dev, non_blocking=True)
+            pend.event = torch.cuda.Event()
+            pend.event.record()
+            self._ids_flip ^= 1
+        pend.row_of = {id(s.request): rr[0] for s, rr in zip(sched, rows) if rr}
+        return pend
+
+    @torch.inference_mode()
+    def finish(self, pend: "PendingStep") -> StepResult:
+        """Read the step's tokens (synchronises with the device) and turn them into per-request
+        token lists; propose drafts for the next step when speculation is on."""
+        new_tokens: dict = {}
+        drafts: dict = {}
+        sched, rows = pend.out.scheduled, pend.rows
+        if pend.ids_dev is None:
+            return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode)
         with trace_range("sync_tokens"):
-            ids = ids_dev.tolist()  # device -> host; synchronises the step
-        self.d2h_total += ids_dev.numel() * 8
+            if pend.ids_host is not None:
+                pend.event.synchronize()
+                ids = pend.ids_host.tolist()
+            else:
+                ids = pend.ids_dev.tolist()  # device -> host; synchronises the step
+        self.d2h_total += len(ids) * 8
         accepted_rows = []
         for s, rr in zip(sched, rows):
             if not s.samples:
                 continue
             r = s.request
+            if len(rr) == 1:
+                new_tokens[r.request_id] = [ids[rr[0]]]
+                accepted_rows.append(rr[0])
+                continue
             target = [ids[j] for j in rr]
             toks = [target[0]]
             if s.num_draft:
@@ -421,5 +498,5 @@ class ModelRunner:
         if self.proposer is not None or self.suffix_cache is not None:
             from ..spec_decode.propose import propose_drafts
             with trace_range("draft"):
-                drafts = propose_drafts(self, sched, rows, new_tokens, hidden, accepted_rows)
-        return StepResult(new_tokens, drafts, num_tokens, mode)
+                drafts = propose_drafts(self, sched, rows, new_tokens, pend.hidden, accepted_rows)
+        return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode)

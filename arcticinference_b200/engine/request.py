@@ -50,6 +50,10 @@ class Request:
     output_logprobs: Optional[list] = None
     routing_key: Optional[str] = None
     _block_array: Optional[object] = field(default=None, repr=False)
+    # run-ahead scheduling: the last output token is a placeholder for a token that has been
+    # sampled on the device but not read yet / the request ends with that token whatever it is
+    provisional: bool = False
+    finishing: bool = False
 
     def __post_init__(self):
         self.metrics.arrival_time = self.arrival_time

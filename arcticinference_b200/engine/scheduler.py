@@ -25,6 +25,8 @@ from ..config import SchedulerConfig, SpeculativeConfig
 from .kv_cache import KVCacheManager
 from .request import Request, RequestStatus
 
+PLACEHOLDER_TOKEN = -1      # same value as model_runner.PLACEHOLDER_TOKEN
+
 
 @dataclass
 class ScheduledRequest:
@@ -125,6 +127,8 @@ class Scheduler:
                 break
             if out.preempted and req.status == RequestStatus.PREEMPTED:
                 continue                 # preempted while serving an earlier request
+            if req.finishing:
+                continue                 # its last token is already on the way
             nt = len(req.prompt_token_ids) + len(req.output_token_ids)
             computed = req.num_computed_tokens
             prefilling = computed < nt - 1
@@ -197,6 +201,25 @@ class Scheduler:
     def _in_prefill(req: Request) -> bool:
         return req.num_computed_tokens < req.num_tokens - 1
 
+    # ----------------------------------------------------------------------------- run-ahead
+    def advance_provisionally(self, out: SchedulerOutput) -> None:
+        """Book the token that every request of a decode-only step is about to receive, before
+        the host has read it: the next step can then be scheduled and queued while this one
+        still runs. The token itself is a placeholder until ``update_from_output``."""
+        cfg = self.config
+        for s in out.scheduled:
+            req = s.request
+            if req.status.finished or req.status == RequestStatus.PREEMPTED:
+                continue
+            assert s.samples and s.num_tokens == 1 and not req.provisional
+            req.num_computed_tokens += 1
+            req.output_token_ids.append(PLACEHOLDER_TOKEN)
+            req.provisional = True
+            sp = req.sampling_params
+            if (sp.max_tokens is not None and len(req.output_token_ids) >= sp.max_tokens) or \
+                    req.num_tokens >= cfg.max_model_len:
+                req.finishing = True
+
     # ----------------------------------------------------------------------------- update
     def update_from_output(self, out: SchedulerOutput, new_tokens: dict[str, list[int]],
                            drafts: Optional[dict[str, list[int]]] = None) -> list[Request]:
@@ -207,6 +230,13 @@ class Scheduler:
         done = []
         for s in out.scheduled:
             req = s.request
+            provisional = req.provisional
+            if provisional:
+                # the step was booked ahead of time: put the real token where the placeholder is
+                req.provisional = False
+                toks = new_tokens.get(req.request_id, [])
+                if toks and req.output_token_ids and req.output_token_ids[-1] == PLACEHOLDER_TOKEN:
+                    req.output_token_ids[-1] = toks[0]
             if req.status.finished or req.status == RequestStatus.PREEMPTED:
                 continue
             if not s.samples:
@@ -215,6 +245,20 @@ class Scheduler:
                 continue
             toks = new_tokens.get(req.request_id, [])
             assert toks, "a sampling request must receive at least one token"
+            if provisional:
+                req.finishing = False
+                if req.metrics.first_token_time is None:
+                    req.metrics.first_token_time = now
+                req.metrics.last_token_time = now
+                finished = req.check_stop(self.config.max_model_len)
+                self.kv.commit(req, min(req.num_computed_tokens, req.num_tokens))
+                if finished:
+                    req.metrics.finished_time = now
+                    self.running.remove(req)
+                    self.kv.free(req)
+                    self.finished.append(req)
+                    done.append(req)
+                continue
             accepted = len(toks) - 1
             assert accepted <= s.num_draft
             # KV is valid for the fed tokens up to and including the accepted drafts

@@ -494,6 +494,19 @@ def gather_rows(src: torch.Tensor, idx: torch.Tensor, out=None):
     return out
 
 
+def patch_ids(ids: torch.Tensor, src_rows: torch.Tensor, prev_ids: torch.Tensor) -> None:
+    """In place: ``ids[i] = prev_ids[src_rows[i]]`` where ``src_rows[i] >= 0`` (all int64)."""
+    if not ids.is_cuda:
+        m = src_rows >= 0
+        ids[m] = prev_ids[src_rows[m]]
+        return
+    nat = _native()
+    rc = nat.lib().ab200_patch_ids(ids.data_ptr(), src_rows.data_ptr(), prev_ids.data_ptr(),
+                                   ids.numel(), prev_ids.numel(), nat.stream_ptr())
+    nat.check(rc, "patch_ids")
+    launch_counter.add(1)
+
+
 def argmax_sample(logits: torch.Tensor, temperature=None, seeds=None, index_offset: int = 0,
                   out_ids=None, out_vals=None):
     """Row-wise token choice: arg-max where temperature <= 0, else an exact softmax sample

@@ -55,6 +55,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_kv_bulk_write": (I, [P, LL, P, P, P, P, P, P, P, LL, I, I, I, I, LL, I, P, P]),
         "ab200_kv_write_fp4": (I, [P, LL, P, LL, P, P, P, P, P, LL, I, I, I, LL, P, P]),
         "ab200_kv_read_fp4": (I, [P, P, P, P, LL, LL, I, I, I, P]),
+        "ab200_patch_ids": (I, [P, P, P, LL, LL, P]),
         "ab200_argmax_sample": (I, [P, I, LL, LL, I, P, P, P, P, LL, P]),
         "ab200_quant_fp8": (I, [P, LL, P, LL, P, LL, LL, I, P]),
         "ab200_dequant_fp8": (I, [P, LL, P, LL, P, LL, LL, I, P]),
