@@ -183,3 +183,25 @@ def test_forest_cascade_matches_plain_decode():
     match = sum(int(a == b) for x, y in zip(plain, outs)
                 for a, b in zip(x.outputs[0].token_ids, y.outputs[0].token_ids))
     assert match >= 0.8 * 60
+
+
+def test_run_ahead_scheduling_changes_nothing():
+    sp = [SamplingParams(temperature=0, max_tokens=n, ignore_eos=True) for n in (20, 33, 5, 48)]
+    prompts = [{"prompt_token_ids": [(11 * i + j) % 997 + 1 for i in range(40 + 30 * j)]} for j in range(4)]
+    kw = dict(model="llama-tiny", device="cuda:0", num_gpu_blocks_override=256, block_size=16,
+              max_model_len=512)
+    outs = {}
+    for mode in (False, True):
+        llm = LLM(async_scheduling=mode, **kw)
+        outs[mode] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        if mode:
+            assert llm.engine.stats["run_ahead_steps"] > 20 and llm.engine.runner.graph_replays > 20
+    ops.check_status()
+    assert outs[False] == outs[True]
+    # token-dependent stop in the middle of a run-ahead stretch
+    stop = outs[False][1][10]
+    sp2 = SamplingParams(temperature=0, max_tokens=48, stop_token_ids=[stop])
+    a = LLM(async_scheduling=False, **kw).generate(prompts, sp2)
+    b = LLM(async_scheduling=True, **kw).generate(prompts, sp2)
+    assert [o.outputs[0].token_ids for o in a] == [o.outputs[0].token_ids for o in b]
+    assert [o.outputs[0].finish_reason for o in a] == [o.outputs[0].finish_reason for o in b]
