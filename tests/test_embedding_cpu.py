@@ -164,3 +164,30 @@ def test_least_loaded_and_random_policies():
     assert ReplicaManager(reps, "least_loaded").select_replica().port == 2
     assert ReplicaManager(reps, "random").select_replica().port in (1, 2)
     assert ReplicaManager([reps[2]], "round_robin").select_replica() is None
+
+
+def test_manager_launches_replica_processes():
+    async def run():
+        mgr = ReplicaManager(load_balancing="least_loaded", health_interval=0.5, startup_timeout=240)
+        try:
+            await mgr.launch("bert-tiny", 2, base_port=18510, host="127.0.0.1", devices=["cpu", "cpu"],
+                             extra=["--max-num-batched-tokens", "1024"])
+            assert [r.healthy for r in mgr.replicas] == [True, True]
+            assert mgr.replicas[0].port != mgr.replicas[1].port
+            front = InferenceServer(ManagerServicer(mgr), "127.0.0.1", 0)
+            port = await front.start()
+            async with InferenceClient("127.0.0.1", port) as c:
+                v = await c.embed(token_ids=[[1, 2, 3], [4, 5]])
+                assert v.shape == (2, 128)
+                assert (await c.get_replica_info())["n_healthy_replicas"] == 2
+                # a replica process dies: the manager notices and keeps serving from the other
+                mgr.replicas[0].process.terminate()
+                mgr.replicas[0].process.wait(timeout=20)
+                for _ in range(4):
+                    assert (await c.embed(token_ids=[[7, 8, 9]])).shape == (1, 128)
+                await asyncio.sleep(1.0)
+                assert (await c.get_replica_info())["n_healthy_replicas"] == 1
+            await front.server.stop(0)
+        finally:
+            await mgr.stop()
+    asyncio.run(run())
