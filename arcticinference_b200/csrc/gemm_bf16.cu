@@ -32,6 +32,10 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
+// Per-epilogue-warp staging tile for coalesced stores: 32 rows x 64 bf16, rows padded to 144
+// bytes so that the 16-byte accesses of eight lanes fall in distinct banks both ways.
+constexpr int kStoreStagePitch = 144;
+constexpr int kStoreStageBytes = 32 * kStoreStagePitch;
 
 struct GemmArgs {
   int rows_a, rows_b, K;
@@ -41,6 +45,8 @@ struct GemmArgs {
   int out_f32;     // 1: write fp32 partial sums (split-K), no bias/residual/activation
   int act;         // 0 none, 1 gelu (erf)
   int b_mn_major;  // 1: the B operand is given as [K, rows_b] (rows_b contiguous)
+  int coalesce;    // 1: bf16 row-major output goes through a shared-memory transpose so that a
+                   //    warp stores whole 128-byte lines (what NVLink and L2 both want)
   uint32_t tmem_cols;
   long long ldo, ldr, partial_stride;
   void* out;
@@ -71,6 +77,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * stage_bytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* store_stage = reinterpret_cast<uint8_t*>(bars) + 256;
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bars_base = smem_u32(bars);
@@ -225,6 +232,79 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool row_ok = a_row < p.rows_a;
       const long long b0 = (long long)tile_b * p.bn;
 
+      if (p.coalesce) {
+        // 64 output columns at a time: each thread converts its row, the warp transposes
+        // through its private staging tile, and every store instruction then writes four
+        // full 128-byte lines (rows) instead of 32 scattered 16-byte pieces.
+        uint8_t* stg = store_stage + (size_t)quad * kStoreStageBytes;
+        for (int c0 = 0; c0 < p.bn; c0 += 64) {
+          uint32_t r0[32], r1[32];
+          __syncwarp();
+          tmem_ld_x32(t_addr + (uint32_t)c0, r0);
+          tmem_ld_x32(t_addr + (uint32_t)(c0 + 32), r1);
+          tmem_ld_wait();
+          const long long col = b0 + c0;
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float v[8];
+#pragma unroll
+              for (int t = 0; t < 8; ++t)
+                v[t] = __uint_as_float(j < 4 ? r0[8 * j + t] : r1[8 * (j - 4) + t]);
+              const long long cj = col + 8 * j;
+              if (cj + 8 <= p.rows_b) {
+                if (p.bias != nullptr) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(p.bias + cj);
+                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const float2 f = __bfloat1622float2(h[u]);
+                    v[2 * u] += f.x;
+                    v[2 * u + 1] += f.y;
+                  }
+                }
+                if (p.act == 1) {
+#pragma unroll
+                  for (int t = 0; t < 8; ++t) v[t] = gelu_erf(v[t]);
+                }
+                if (p.residual != nullptr) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(p.residual + a_row * p.ldr + cj);
+                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const float2 f = __bfloat1622float2(h[u]);
+                    v[2 * u] += f.x;
+                    v[2 * u + 1] += f.y;
+                  }
+                }
+              }
+              uint4 q;
+              q.x = pack_bf16x2(v[0], v[1]);
+              q.y = pack_bf16x2(v[2], v[3]);
+              q.z = pack_bf16x2(v[4], v[5]);
+              q.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(stg + lane * kStoreStagePitch + 16 * j) = q;
+            }
+          }
+          __syncwarp();
+          __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + col;
+          long long row_off = 0;
+          if (p.peer_cols > 0) {  // a 64-column group never straddles a destination
+            base = p.peer_out[col / p.peer_cols] + col % p.peer_cols;
+            row_off = p.peer_row_off;
+          }
+          const int ch = lane & 7;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const long long grow = (long long)tile_a * kBlockM + quad * 32 + rr;
+            if (grow < p.rows_a && col + 8 * ch + 8 <= p.rows_b) {
+              const uint4 q = *reinterpret_cast<const uint4*>(stg + rr * kStoreStagePitch + 16 * ch);
+              *reinterpret_cast<uint4*>(base + (grow + row_off) * p.ldo + 8 * ch) = q;
+            }
+          }
+        }
+      } else
       for (int c0 = 0; c0 < p.bn; c0 += 16) {
         uint32_t r[16];
         __syncwarp();
@@ -423,9 +503,19 @@ static int num_sms() {
 
 static int pick_stages(int bn) {
   const int stage_bytes = (int)kABytes + bn * kBlockK * 2;
-  int s = (227 * 1024 - 2048) / stage_bytes;
+  int s = (227 * 1024 - 2048 - 4 * kStoreStageBytes) / stage_bytes;
   if (s > kMaxStages) s = kMaxStages;
   return s;
+}
+
+// AB200_GEMM_COALESCE=0 keeps the direct (one row per thread) stores, for A/B timing.
+static bool coalesced_stores_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("AB200_GEMM_COALESCE");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 static uint32_t pow2_at_least(uint32_t v) {
@@ -581,6 +671,11 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   a.stages = pick_stages(a.bn);
   a.tmem_cols = pow2_at_least(2u * (uint32_t)a.bn);
 
+  a.coalesce = coalesced_stores_enabled() && !a.transposed && a.splits == 1 && a.bn % 64 == 0 &&
+               N % 8 == 0 && ldo % 8 == 0 && (peer_cols == 0 || peer_cols % 64 == 0) &&
+               (reinterpret_cast<uintptr_t>(bias) % 16) == 0 &&
+               (residual == nullptr || ldr % 8 == 0);
+
   void* final_out = out;
   if (a.splits > 1) {
     a.out_f32 = 1;
@@ -596,7 +691,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
 
   const int total = a.tiles_a * a.tiles_b * a.splits;
   const int grid = total < sms ? total : sms;
-  const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 1024;
+  const size_t smem =
+      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 1024;
   gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, a);
   if (cudaGetLastError() != cudaSuccess) return -5;
 
@@ -672,7 +768,8 @@ int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long l
   const int total = a.tiles_a * a.tiles_b;
   const int sms = num_sms();
   const int grid = total < sms ? total : sms;
-  const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 1024;
+  const size_t smem =
+      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 1024;
   gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -218,6 +218,31 @@ def test_linear_strided_views():
     assert float(out_buf[:, :128].abs().max()) == 0 and float(out_buf[:, 512:].abs().max()) == 0
 
 
+@pytest.mark.parametrize("M,blk", [(300, 192), (64, 192), (1000, 80)])
+def test_linear_scatter_epilogue_local_destinations(M, blk):
+    """The scatter epilogue with both destinations in this GPU's memory: feature block j of
+    token m must land in buffer j at row m + offset (blk=192 takes the coalesced store path,
+    blk=80 the direct one)."""
+    import ctypes
+    from arcticinference_b200.ops import native
+    world, K, off = 2, 512, 7
+    x = _rand(M, K)
+    w = _rand(world * blk, K, scale=1.0 / math.sqrt(K))
+    bufs = [torch.zeros(M + 2 * off, blk, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    P, I, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    native.declare("ab200_linear_bf16_scatter", I, [P, LL, P, LL, P, I, I, LL, LL, I, I, I, P, P])
+    rc = native.lib().ab200_linear_bf16_scatter(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), ptrs, world, blk, off, blk, M,
+        world * blk, K, native.status_buffer(x.device).data_ptr(), native.stream_ptr())
+    assert rc == 0
+    ops.check_status()
+    want = ref.linear(x, w)
+    for j, b in enumerate(bufs):
+        _close(b[off:off + M], want[:, j * blk:(j + 1) * blk], 3e-2, 2e-2)
+        assert float(b[:off].abs().max()) == 0 and float(b[off + M:].abs().max()) == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 256, 512), (1024, 192, 128)])
 def test_gemm_nn(M, N, K):
     x, wt = _rand(M, K), _rand(K, N, scale=1.0 / math.sqrt(K))
