@@ -419,6 +419,45 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (p.peer_tokens > 0)
         dst16 = p.peer_out[tok / p.peer_tokens] + (tok % p.peer_tokens) * p.ldo + (long long)head * D;
       float* dst32 = p.o_part + (((long long)split * p.T + tok) * p.Hq + head) * D;
+      if (num_splits <= 1 && n_tiles > 0) {
+        // Normalised rows go through the Q tile's shared memory (free once the last product
+        // has completed; same 128-byte swizzle, so the writes are conflict-free) and leave as
+        // whole rows: one store instruction covers 32 / (D / 8) complete rows of D bf16 instead
+        // of 16-byte pieces of 32 different rows -- what a peer's memory over NVLink needs.
+        constexpr int kCh = D / 8;  // 16-byte chunks per row
+        uint8_t* my_row = smem + (size_t)row * 128;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t rc[32];
+          tmem_ld_x32(to + (uint32_t)c * 32u, rc);
+          tmem_ld_wait_dep(rc);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int j = c * 4 + i;
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(rc[8 * i]) * inv_l, __uint_as_float(rc[8 * i + 1]) * inv_l);
+            q.y = pack_bf16x2(__uint_as_float(rc[8 * i + 2]) * inv_l, __uint_as_float(rc[8 * i + 3]) * inv_l);
+            q.z = pack_bf16x2(__uint_as_float(rc[8 * i + 4]) * inv_l, __uint_as_float(rc[8 * i + 5]) * inv_l);
+            q.w = pack_bf16x2(__uint_as_float(rc[8 * i + 6]) * inv_l, __uint_as_float(rc[8 * i + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(my_row + (size_t)(j >> 3) * 16384 + (((j & 7) ^ (row & 7)) * 16)) = q;
+          }
+        }
+        __syncwarp();
+        const unsigned long long my_dst = valid_row ? reinterpret_cast<unsigned long long>(dst16) : 0ull;
+        const int j = lane % kCh;
+#pragma unroll
+        for (int it = 0; it < kCh; ++it) {
+          const int rl = it * (32 / kCh) + lane / kCh;  // row of this warp
+          const int rr = warp * 32 + rl;
+          const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, rl);
+          if (d != 0ull) {
+            const uint4 q = *reinterpret_cast<const uint4*>(
+                smem + (size_t)(j >> 3) * 16384 + (size_t)rr * 128 + (((j & 7) ^ (rr & 7)) * 16));
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(d) + 8 * j) = q;
+          }
+        }
+        if (valid_row && p.lse_out) p.lse_out[tok * p.Hq + head] = lse;
+      } else {
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t rc[32];
@@ -455,6 +494,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else {
           p.lse_part[((long long)split * p.T + tok) * p.Hq + head] = lse;
         }
+      }
       }
     }
   }
