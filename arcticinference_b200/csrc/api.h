@@ -124,6 +124,12 @@ int ab200_barrier_timed(const void* const* flag_ptrs, int my_rank, int world, vo
                         int limit_ms, int* status, cudaStream_t stream);
 int ab200_allreduce(const void* const* part_ptrs, int world, void* out, const void* residual,
                     long long n_elems, cudaStream_t stream);
+// Two-shot all-reduce in one launch (reduce-scatter by peer loads, all-gather by peer stores,
+// flag exchanges inside the kernel); the result lands in every rank's result buffer.
+long long ab200_allreduce2_flag_bytes();
+int ab200_allreduce2(const void* const* part_ptrs, const void* const* res_ptrs,
+                     const void* const* flag_ptrs, void* epochs, int my_rank, int world,
+                     long long n_elems, int* status, cudaStream_t stream);
 int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long rows_per_rank,
                             const void* idx, void* dst, long long R, int hidden,
                             cudaStream_t stream);

@@ -54,7 +54,10 @@ class LLMEngine:
         self.step_count = 0
         self.sleeping_level = 0
         self.stats = {"prompt_tokens": 0, "generation_tokens": 0, "steps": 0,
-                      "draft_tokens": 0, "accepted_tokens": 0, "run_ahead_steps": 0}
+                      "draft_tokens": 0, "accepted_tokens": 0, "run_ahead_steps": 0,
+                      # host seconds per phase: scheduling, building + queueing a step, waiting
+                      # for its tokens (the only phase the device is waited for), bookkeeping
+                      "t_schedule": 0.0, "t_launch": 0.0, "t_wait": 0.0, "t_update": 0.0}
         if config.speculative is not None:
             from ..spec_decode.propose import attach_speculation
             attach_speculation(self)
@@ -80,7 +83,8 @@ class LLMEngine:
                 ids = self.tokenizer.encode(text)
         else:
             ids = list(prompt)
-        ids = [int(t) for t in ids]
+        if not (isinstance(ids, list) and all(type(t) is int for t in ids)):
+            ids = [int(t) for t in ids]
         eos = self.config.model.eos_token_id
         if eos is None:
             eos = getattr(self.tokenizer, "eos_token_id", None)
@@ -117,22 +121,31 @@ class LLMEngine:
         if self.sleeping_level:
             raise RuntimeError("engine is sleeping; call wake_up() first")
         prev, self._pending = self._pending, None
+        st, clock = self.stats, time.perf_counter
         if prev is None:
+            t0 = clock()
             out = self.scheduler.schedule()
+            t1 = clock()
+            st["t_schedule"] += t1 - t0
             if out.is_empty:
                 return []
             pend = self.runner.launch(out)
+            st["t_launch"] += clock() - t1
             if self._can_run_ahead(out):
                 self._pending = pend
                 return []
             return self._complete(pend, partial)
         nxt = None
         if self._can_run_ahead(prev.out):
+            t0 = clock()
             self.scheduler.advance_provisionally(prev.out)
             out = self.scheduler.schedule()
+            t1 = clock()
+            st["t_schedule"] += t1 - t0
             if not out.is_empty:
                 nxt = self.runner.launch(out, prev)
-                self.stats["run_ahead_steps"] += 1
+                st["run_ahead_steps"] += 1
+                st["t_launch"] += clock() - t1
         outputs = self._complete(prev, partial)
         self._pending = nxt
         return outputs
@@ -151,8 +164,12 @@ class LLMEngine:
 
     def _complete(self, pend, partial: bool) -> list[RequestOutput]:
         out = pend.out
+        t0 = time.perf_counter()
         result = self.runner.finish(pend)
+        t1 = time.perf_counter()
         finished = self.scheduler.update_from_output(out, result.new_tokens, result.drafts)
+        self.stats["t_wait"] += t1 - t0
+        self.stats["t_update"] += time.perf_counter() - t1
         self.step_count += 1
         self.stats["steps"] += 1
         for s in out.scheduled:

@@ -138,6 +138,7 @@ class ModelRunner:
         self.last_step_device_ms = None
         self.mode_counts = {"sp": 0, "tp": 0}
         self.step_timer_events = None
+        self.sync_seconds = 0.0       # host time spent blocked on the device for sampled tokens
 
     # ------------------------------------------------------------------ set-up
     def load_model(self) -> None:
@@ -471,7 +472,9 @@ class ModelRunner:
             return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode)
         with trace_range("sync_tokens"):
             if pend.ids_host is not None:
+                t0 = time.perf_counter()
                 pend.event.synchronize()
+                self.sync_seconds += time.perf_counter() - t0
                 ids = pend.ids_host.tolist()
             else:
                 ids = pend.ids_dev.tolist()  # device -> host; synchronises the step

@@ -11,8 +11,11 @@ that all ranks map. The hot exchanges then happen inside the kernels:
   stores each token's output row into the buffer of the rank that owns the token
   (``ab200_attention_scatter``); the o_proj GEMM then reads local memory only;
 * tensor-parallel reductions of shift mode: the row-parallel GEMM writes its
-  partial product into the heap and ``ab200_allreduce`` sums all ranks' partials
-  with peer loads (fp32 accumulation in rank order, so all ranks get the same bits).
+  partial product into the heap; small reductions run ``ab200_allreduce`` (every rank sums
+  all ranks' partials with peer loads), larger ones ``ab200_allreduce2`` (one launch: each
+  rank reduces its slice by peer loads and stores the result into every rank's buffer, so
+  (W-1)/W of the tensor crosses NVLink per direction instead of W-1 times the tensor).
+  Both accumulate in fp32 in rank order, so all ranks get the same bits.
 
 Between a producer kernel and its consumers runs ``ab200_barrier`` (flag exchange
 with bounded waits). All loads of remote data are plain peer loads or TMA loads
@@ -26,6 +29,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import os
 
 import torch
 import torch.distributed as dist
@@ -69,6 +73,9 @@ class FusedCommunicator(Communicator):
             "attn": n_local * attn_cols * 2 if self.sp > 1 else 0,
             "ar0": max_tp_tokens * hidden * 2,
             "ar1": max_tp_tokens * hidden * 2,
+            "res0": max_tp_tokens * hidden * 2,
+            "res1": max_tp_tokens * hidden * 2,
+            "ar2_flags": 2 * 16 * 128 * 4,
         }
         off, layout = 0, {}
         for k, v in sizes.items():
@@ -87,12 +94,23 @@ class FusedCommunicator(Communicator):
         self._qkv_ptrs = _ptr_array([b + layout["qkv"][0] for b in self._peer_base])
         self._ar_ptrs = [_ptr_array([b + layout[k][0] for b in self._peer_base])
                          for k in ("ar0", "ar1")]
+        self._res_ptrs = [_ptr_array([b + layout[k][0] for b in self._peer_base])
+                          for k in ("res0", "res1")]
+        self._ar2_flag_ptrs = _ptr_array([b + layout["ar2_flags"][0] for b in self._peer_base])
+        self._ar2_epochs = torch.zeros(128, dtype=torch.int32, device=self.device)
+        mode = os.environ.get("AB200_ALLREDUCE", "auto").lower()
+        if mode not in ("auto", "oneshot", "twoshot"):
+            raise ValueError("AB200_ALLREDUCE must be auto, oneshot or twoshot")
+        # bytes of one rank's partial from which the two-shot kernel is used
+        self._two_shot_from = {"auto": (1 << 20) if W > 2 else (1 << 62), "oneshot": 1 << 62,
+                               "twoshot": 0}[mode]
         torch.cuda.synchronize(self.device)
         dist.barrier()
         L = native.lib()
         P, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
         native.declare("ab200_barrier", I, [P, I, I, P, P, P])
         native.declare("ab200_allreduce", I, [P, I, P, P, LL, P])
+        native.declare("ab200_allreduce2", I, [P, P, P, P, I, I, LL, P, P])
         native.declare("ab200_gather_rows_peers", I, [P, I, LL, P, P, LL, I, P])
         native.declare("ab200_linear_bf16_scatter", I, [P, LL, P, LL, P, I, I, LL, LL, I, I, I, P, P])
         native.declare("ab200_attention_scatter", I, [P, LL, P, P, LL, I, P, I, P, I, P, I, LL, I, I,
@@ -165,6 +183,15 @@ class FusedCommunicator(Communicator):
         if t.data_ptr() != buf.data_ptr():
             buf.copy_(t)
         self._ar_index += 1
+        if rows * cols * 2 >= self._two_shot_from and (rows * cols) % 8 == 0:
+            rc = self._lib.ab200_allreduce2(
+                self._ar_ptrs[key], self._res_ptrs[key], self._ar2_flag_ptrs,
+                self._ar2_epochs.data_ptr(), self.rank, self.ways, rows * cols,
+                native.status_buffer(self.device).data_ptr(), native.stream_ptr())
+            native.check(rc, "allreduce2")
+            ops.launch_counter.add(1)
+            # valid until the second reduction after this one reuses the buffer
+            return self._view("res%d" % key, rows, cols)
         self.device_barrier()
         out = torch.empty(rows, cols, dtype=t.dtype, device=t.device)
         rc = self._lib.ab200_allreduce(self._ar_ptrs[key], self.ways, out.data_ptr(), None,

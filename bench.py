@@ -42,7 +42,9 @@ def parse_args():
     ap.add_argument("--requests-per-gpu", type=int, default=128)
     ap.add_argument("--input-len", type=int, default=2000)
     ap.add_argument("--output-len", type=int, default=250)
-    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=None,
+                    help="token budget of one engine step; default 8192 per GPU, so that a step "
+                         "gives every GPU the same work whatever N is")
     ap.add_argument("--shift-parallel-threshold", type=int, default=512)
     ap.add_argument("--speculative-config", type=str, default=None)
     ap.add_argument("--enforce-eager", action="store_true")
@@ -125,6 +127,8 @@ def main():
 
     from arcticinference_b200 import LLM, SamplingParams, ops
 
+    if args.max_num_batched_tokens is None:
+        args.max_num_batched_tokens = 8192 * n_gpus
     quant = None if str(args.quantization).lower() in ("none", "bf16", "") else args.quantization
     kw = dict(model=args.model, max_model_len=args.input_len + args.output_len + 64,
               max_num_batched_tokens=args.max_num_batched_tokens,
@@ -185,6 +189,8 @@ def main():
     engine.runner.h2d_total = 0
     engine.runner.d2h_total = 0
     steps0 = engine.stats["steps"]
+    host0 = {k: engine.stats[k] for k in ("t_schedule", "t_launch", "t_wait", "t_update")}
+    sync0 = engine.runner.sync_seconds
     barrier()
     t0 = time.perf_counter()
     for k in range(args.steps):
@@ -192,6 +198,9 @@ def main():
     barrier()
     e2e_s = time.perf_counter() - t0
     e2e_steps = max(1, engine.stats["steps"] - steps0)
+    # where the host spent the end-to-end region (rank 0), milliseconds per engine step
+    host_ms = {k[2:]: 1000.0 * (engine.stats[k] - v) / e2e_steps for k, v in host0.items()}
+    host_ms["device_wait"] = 1000.0 * (engine.runner.sync_seconds - sync0) / e2e_steps
 
     t = torch.tensor([dev_ms, e2e_s * 1000.0], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -216,7 +225,9 @@ def main():
                 "output_len": args.output_len,
                 "parallelism": ("sp%d<->tp%d shift" % (n_gpus, n_gpus)) if n_gpus > 1 else "single",
                 "l2": "inputs larger than L2 (weights streamed every engine step)",
+                "max_num_batched_tokens": args.max_num_batched_tokens,
                 "engine_steps_per_wave": e2e_steps / args.steps,
+                "host_ms_per_engine_step": {k: round(v, 3) for k, v in host_ms.items()},
                 "mode_counts": dict(engine.runner.mode_counts),
             },
             "clocks": clock_info,

@@ -119,9 +119,22 @@ def test_fused_parallel_matches_single_gpu(kind, shift, model, backend):
     assert all(e < 0.08 * max(1.0, m) for e, m in errs), (errs, modes)
 
 
-def _ar_worker(rank, world, port, q):
+def test_tensor_parallel_engine_with_two_shot_allreduce(monkeypatch):
+    """Every row-parallel reduction of the engine goes through the two-shot kernel."""
+    world = _world()
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    monkeypatch.setenv("AB200_ALLREDUCE", "twoshot")   # inherited by the spawned ranks
+    outs, modes, ref_outs, _ = _launch(world, 1, world, True, "llama-small", "fused")
+    assert "tp" in modes
+    for a, b in zip(outs, ref_outs):
+        a, b = torch.from_numpy(a), torch.from_numpy(b)
+        assert (a - b).abs().max().item() < 0.08 * max(1.0, b.abs().max().item())
+
+
+def _ar_worker(rank, world, port, q, algo="oneshot"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
-                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank), AB200_ALLREDUCE=algo)
     sys.path.insert(0, ROOT)
     torch.cuda.set_device(rank)
     import torch.distributed as dist
@@ -148,14 +161,15 @@ def _ar_worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_fused_allreduce_repeated_buffers():
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+def test_fused_allreduce_repeated_buffers(algo):
     world = _world()
     if world < 2:
         pytest.skip("needs at least two GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_ar_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_ar_worker, args=(r, world, port, q, algo)) for r in range(world)]
     for p in procs:
         p.start()
     worst = q.get(timeout=300)
