@@ -651,6 +651,12 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     const int tiles256 = a.tiles_a * ((N + 255) / 256);
     a.bn = ((tiles256 >= sms || a.tiles_a == 1) && N >= 256) ? 256 : 128;
     if (N < 128) a.bn = ((N + 15) / 16) * 16;
+    if (a.tiles_a == 1 && peer_cols > 0 && N >= 256) {
+      // One row of tiles and no split-K (the scatter epilogue writes final values): a CTA
+      // streams its weight tile at a fraction of an SM's share of HBM bandwidth, so narrow the
+      // tiles until most SMs hold one.
+      while (a.bn > 64 && (N + a.bn - 1) / a.bn < (sms * 3) / 5) a.bn /= 2;
+    }
     a.tiles_b = (N + a.bn - 1) / a.bn;
     if (a.tiles_a == 1) {
       int splits = force_splits;

@@ -10,7 +10,7 @@ Cases (Llama-3.1-8B shapes, bf16; n = tokens per rank):
   it (Ulysses sequence -> head exchange) vs the same GEMM into local memory followed by
   ``all_to_all_single``;
 * allreduce: row-parallel o_proj writing its partial product into the symmetric heap + the
-  one-shot peer-load all-reduce vs the GEMM + ``dist.all_reduce``.
+  peer-memory all-reduce (one-shot and two-shot kernels) vs the GEMM + ``dist.all_reduce``.
 
 Times are CUDA events on the launching stream, median of ``--iters`` after warm-up, maximum
 over ranks. For each fused case the roofline time is the slower of FLOPs / measured bf16 peak
@@ -114,13 +114,19 @@ def main():
             ops.linear(a_in, wo, out=out_local)
             dist.all_reduce(out_local)
 
-        t_f, t_b = timed(fused_ar, a.iters), timed(nccl_ar, a.iters)
+        t_b = timed(nccl_ar, a.iters)
         flops = 2.0 * n * H * h * D
-        moved = n * H * 2.0 * (world - 1)          # one-shot: every rank reads the other ranks' partials
-        roof = max(flops / (peak * 1e12), moved / (LINK_GBS * 1e9)) * 1e6
-        res.append({"case": "gemm_allreduce", "tokens": n, "fused_us": t_f, "gemm_then_nccl_us": t_b,
-                    "speedup": t_b / t_f, "roofline_us": roof, "fraction_of_roofline": roof / t_f,
-                    "bytes_read_per_gpu": moved, "flops": flops})
+        for algo, from_bytes in (("one_shot", 1 << 62), ("two_shot", 0)):
+            comm._two_shot_from = from_bytes
+            t_f = timed(fused_ar, a.iters)
+            # bytes one rank pulls over NVLink: one-shot reads every other rank's partial in
+            # full; two-shot reads (W-1)/W of the tensor and writes as much the other way
+            moved = n * H * 2.0 * ((world - 1) if algo == "one_shot" else (world - 1) / world)
+            roof = max(flops / (peak * 1e12), moved / (LINK_GBS * 1e9)) * 1e6
+            res.append({"case": "gemm_allreduce_" + algo, "tokens": n, "fused_us": t_f,
+                        "gemm_then_nccl_us": t_b, "speedup": t_b / t_f, "roofline_us": roof,
+                        "fraction_of_roofline": roof / t_f, "bytes_read_per_gpu": moved,
+                        "flops": flops})
     ops.check_status()
     if rank == 0:
         for r in res:
