@@ -115,6 +115,59 @@ rmsnorm_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res
   }
 }
 
+// Same operation for hidden == VPT * 8 * kNormThreads exactly (2048, 4096, 8192 for VPT = 1, 2,
+// 4): the trip counts are compile-time constants, so every load of the row (x and residual)
+// is issued before the first value is used and the row takes VPT * 8 live floats per thread.
+template <int VPT>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fixed_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ residual,
+                     const bf16* __restrict__ weight, bf16* __restrict__ y, long long ldy,
+                     float eps) {
+  __shared__ float red[32];
+  constexpr int hidden = VPT * 8 * kNormThreads;
+  const long long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + row * (long long)hidden) : nullptr;
+  uint4 xq[VPT], rq[VPT], wq[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) xq[j] = xr[threadIdx.x + j * kNormThreads];
+  if (rr) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) rq[j] = rr[threadIdx.x + j * kNormThreads];
+  }
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+    wq[j] = reinterpret_cast<const uint4*>(weight)[threadIdx.x + j * kNormThreads];
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    unpack8(xq[j], vals[j]);
+    if (rr) {
+      float r[8];
+      unpack8(rq[j], r);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) vals[j][k] += r[k];
+      const uint4 q = pack8(vals[j]);
+      rr[threadIdx.x + j * kNormThreads] = q;
+      unpack8(q, vals[j]);  // normalise the value that was stored (bf16-rounded)
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += vals[j][k] * vals[j][k];
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * ldy);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    float w[8];
+    unpack8(wq[j], w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) vals[j][k] = vals[j][k] * inv * w[k];
+    yr[threadIdx.x + j * kNormThreads] = pack8(vals[j]);
+  }
+}
+
 // ------------------------------- LayerNorm ---------------------------------
 // y = LN(x (+ residual)) * gamma + beta, mean/variance in fp32.
 __global__ void __launch_bounds__(kNormThreads)
@@ -179,25 +232,47 @@ layernorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
 // x: [T, nblk * 2 * inter] laid out as nblk blocks of (gate | up); out: [T, nblk * inter].
 // nblk = 1 is the usual fused gate/up layout; nblk > 1 is the rank-major layout whose
 // blocks are the tensor-parallel shards.
-__global__ void silu_mul_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, long long T,
-                                int inter, int nblk) {
+// Each thread keeps four (gate, up) vector pairs in flight per iteration: the loads of all
+// four are issued before the first is used.
+constexpr int kSiluUnroll = 4;
+
+__global__ void __launch_bounds__(256, 4)
+silu_mul_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, long long T, int inter,
+                int nblk) {
   const int nvec = inter / 8;
   const long long per_row = (long long)nblk * nvec;
   const long long total = T * per_row;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / per_row;
-    const int r = (int)(i % per_row);
-    const int b = r / nvec;
-    const int c = r % nvec;
-    const uint4* row =
-        reinterpret_cast<const uint4*>(x + (t * nblk + b) * 2ll * inter);
-    float g[8], u[8];
-    unpack8(row[c], g);
-    unpack8(row[nvec + c], u);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total;
+       i0 += stride * kSiluUnroll) {
+    uint4 gq[kSiluUnroll], uq[kSiluUnroll];
+    long long dst[kSiluUnroll];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
-    reinterpret_cast<uint4*>(out + (t * nblk + b) * (long long)inter)[c] = pack8(g);
+    for (int j = 0; j < kSiluUnroll; ++j) {
+      const long long i = i0 + j * stride;
+      dst[j] = -1;
+      if (i < total) {
+        const long long t = i / per_row;
+        const int r = (int)(i - t * per_row);
+        const int b = r / nvec;
+        const int c = r - b * nvec;
+        const uint4* row = reinterpret_cast<const uint4*>(x + (t * nblk + b) * 2ll * inter);
+        gq[j] = row[c];
+        uq[j] = row[nvec + c];
+        dst[j] = (t * nblk + b) * (long long)nvec + c;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kSiluUnroll; ++j) {
+      if (dst[j] >= 0) {
+        float g[8], u[8];
+        unpack8(gq[j], g);
+        unpack8(uq[j], u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+        reinterpret_cast<uint4*>(out)[dst[j]] = pack8(g);
+      }
+    }
   }
 }
 
@@ -395,9 +470,20 @@ int ab200_rmsnorm(const void* x, long long ldx, void* residual, const void* weig
                   long long ldy, long long T, int hidden, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((hidden % 8) || hidden > kNormThreads * kMaxVec * 8 || (ldx % 8) || (ldy % 8)) return -2;
-  rmsnorm_kernel<<<(unsigned)T, kNormThreads, 0, stream>>>(
-      reinterpret_cast<const bf16*>(x), ldx, reinterpret_cast<bf16*>(residual),
-      reinterpret_cast<const bf16*>(weight), reinterpret_cast<bf16*>(y), ldy, hidden, eps);
+  const bf16* xp = reinterpret_cast<const bf16*>(x);
+  bf16* rp = reinterpret_cast<bf16*>(residual);
+  const bf16* wp = reinterpret_cast<const bf16*>(weight);
+  bf16* yp = reinterpret_cast<bf16*>(y);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) |
+                         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (aligned && hidden == 8 * kNormThreads)
+    rmsnorm_fixed_kernel<1><<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, eps);
+  else if (aligned && hidden == 16 * kNormThreads)
+    rmsnorm_fixed_kernel<2><<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, eps);
+  else if (aligned && hidden == 32 * kNormThreads)
+    rmsnorm_fixed_kernel<4><<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, eps);
+  else
+    rmsnorm_kernel<<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, hidden, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -27,7 +27,7 @@ def _close(a, b, atol, rtol):
 
 
 # ----------------------------------------------------------------------------- elementwise
-@pytest.mark.parametrize("T,H", [(1, 64), (7, 768), (33, 4096), (5, 8192)])
+@pytest.mark.parametrize("T,H", [(1, 64), (7, 768), (3, 2048), (33, 4096), (5, 8192)])
 def test_rmsnorm(T, H):
     x, w = _rand(T, H), _rand(H)
     y = ops.rmsnorm(x, w, 1e-5)
@@ -59,6 +59,16 @@ def test_layernorm(T, H):
 def test_silu_mul():
     x = _rand(19, 2 * 14336)
     _close(ops.silu_mul(x), ref.silu_mul(x), 2e-2, 2e-2)
+
+
+def test_silu_mul_many_rows_rank_major_blocks():
+    # more vectors than one pass of the grid covers; two (gate | up) blocks per row
+    T, inter, nblk = 6000, 1792, 2
+    x = _rand(T, nblk * 2 * inter)
+    got = ops.silu_mul_blocked(x, nblk)
+    xb = x.view(T, nblk, 2 * inter)
+    exp = torch.cat([ref.silu_mul(xb[:, b]) for b in range(nblk)], dim=1)
+    _close(got, exp, 2e-2, 2e-2)
 
 
 def test_embedding_and_gather():
