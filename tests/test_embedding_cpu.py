@@ -191,3 +191,40 @@ def test_manager_launches_replica_processes():
         finally:
             await mgr.stop()
     asyncio.run(run())
+
+
+def test_openai_embeddings_endpoint(tiny_engine):
+    """/v1/embeddings: the four input shapes, both encodings, shortened vectors, errors."""
+    import base64
+    from fastapi.testclient import TestClient
+    from arcticinference_b200.embedding.engine import AsyncEmbeddingEngine
+    from arcticinference_b200.embedding.http_server import build_app, normalise_input
+
+    assert normalise_input("a b") == ["a b"]
+    assert normalise_input([1, 2, 3]) == [[1, 2, 3]]
+    with pytest.raises(ValueError):
+        normalise_input([[1], "x"])
+    aeng = AsyncEmbeddingEngine(tiny_engine, max_wait_ms=0.5)
+    try:
+        with TestClient(build_app(aeng, "bert-tiny")) as c:
+            ids = [[5, 6, 7, 8], [9, 10]]
+            exp = tiny_engine.encode(ids)
+            r = c.post("/v1/embeddings", json={"model": "bert-tiny", "input": ids})
+            assert r.status_code == 200
+            body = r.json()
+            assert body["usage"]["prompt_tokens"] == 6 and len(body["data"]) == 2
+            got = np.array([d["embedding"] for d in body["data"]], dtype=np.float32)
+            np.testing.assert_allclose(got, exp, atol=1e-5)
+            r = c.post("/v1/embeddings", json={"input": ids[0], "encoding_format": "base64"})
+            v = np.frombuffer(base64.b64decode(r.json()["data"][0]["embedding"]), dtype="<f4")
+            np.testing.assert_allclose(v, exp[0], atol=1e-5)
+            r = c.post("/v1/embeddings", json={"input": ["hello world", "x"], "dimensions": 8})
+            short = np.array([d["embedding"] for d in r.json()["data"]])
+            assert short.shape == (2, 8)
+            np.testing.assert_allclose(np.linalg.norm(short, axis=1), 1.0, atol=1e-5)
+            assert c.post("/v1/embeddings", json={"input": []}).status_code == 400
+            assert c.post("/v1/embeddings", json={"input": "x", "encoding_format": "hex"}).status_code == 400
+            assert c.get("/v1/models").json()["data"][0]["id"] == "bert-tiny"
+            assert c.get("/stats").json()["sequences"] >= 5
+    finally:
+        aeng.stop()
