@@ -83,6 +83,8 @@ CASES = {
     "gemm_prefill_qkv": ("gemm", (8192, 6144, 4096)),
     "gemm_prefill_down": ("gemm", (8192, 4096, 14336)),
     "gemm_decode": ("gemm", (32, 28672, 4096)),
+    "gemm_decode_128": ("gemm", (128, 28672, 4096)),
+    "gemm_decode_128_down": ("gemm", (128, 4096, 14336)),
     "gemm_decode_o": ("gemm", (32, 4096, 4096)),
     "gemm_decode_down": ("gemm", (32, 4096, 14336)),
     "gemm_mid": ("gemm", (512, 28672, 4096)),
@@ -108,6 +110,8 @@ def main():
     ap.add_argument("--case", required=True, choices=sorted(CASES))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-time", action="store_true", help="three plain launches (for ncu)")
+    ap.add_argument("--splits", type=int, default=0,
+                    help="force the split-K factor of the bf16 GEMM cases (0 = the kernel's choice)")
     a = ap.parse_args()
     hbm, tf, src = peaks()
     kind, prm = CASES[a.case]
@@ -115,7 +119,7 @@ def main():
         M, N, K = prm
         nc = copies_for(2 * N * K)
         x, ws = R(M, K), [R(N, K) for _ in range(nc)]
-        fn = lambda i=0: ops.linear(x, ws[i])
+        fn = lambda i=0: ops.linear(x, ws[i], force_splits=a.splits)
         flops, byts = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
     elif kind == "gemm_fp8":
         from arcticinference_b200.models import quant
@@ -153,7 +157,7 @@ def main():
     ms = timeit(fn, a.iters, copies=nc)
     ops.check_status()
     t = ms / 1e3
-    print(json.dumps({"case": a.case, "us": ms * 1e3, "tflops": flops / t / 1e12,
+    print(json.dumps({"case": a.case, "splits": a.splits, "us": ms * 1e3, "tflops": flops / t / 1e12,
                       "gbs": byts / t / 1e9, "frac_of_%s_bf16" % src: flops / t / 1e12 / tf,
                       "frac_of_%s_hbm" % src: byts / t / 1e9 / hbm}))
 
