@@ -110,10 +110,13 @@ class AsyncLLM:
 
     def _loop(self) -> None:
         eng = self.engine
-        if eng.device.type == "cuda":
-            import torch
-            torch.cuda.set_device(eng.device)
+        futures = []
         try:
+            if eng.device.type == "cuda":
+                import torch
+                # "cuda" without an index means the device that is current in the caller
+                torch.cuda.set_device(eng.device if eng.device.index is not None
+                                      else torch.cuda.current_device())
             while True:
                 msgs = self._collect() if self.is_leader else None
                 futures = []
@@ -167,8 +170,19 @@ class AsyncLLM:
                         del self._streams[ro.request_id]
         except BaseException as e:  # noqa: BLE001 - every waiter must learn of it
             self._dead = e
+            dead = EngineDeadError("engine loop died: %r" % (e,))
             for rid in list(self._streams):
-                self._finish_stream(rid, EngineDeadError("engine loop died: %r" % (e,)))
+                self._finish_stream(rid, dead)
+            # control calls of the batch in hand, and any still queued, fail as well
+            for fut in futures:
+                fut[0].call_soon_threadsafe(_resolve, fut[1], None, dead)
+            while True:
+                try:
+                    m = self._inbox.get_nowait()
+                except queue.Empty:
+                    break
+                if m[0] == "call":
+                    m[3][0].call_soon_threadsafe(_resolve, m[3][1], None, dead)
             raise
         finally:
             for rid in list(self._streams):
@@ -229,6 +243,8 @@ class AsyncLLM:
         st = _Stream(asyncio.get_running_loop())
         self._streams[rid] = st
         self._inbox.put(("add", rid, [int(t) for t in ids], params, time.time(), routing_key))
+        if self._dead is not None:      # the loop died between the check above and the put
+            self._finish_stream(rid, EngineDeadError("engine loop died: %r" % (self._dead,)))
         try:
             while True:
                 item = await st.queue.get()

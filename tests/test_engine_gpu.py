@@ -205,3 +205,27 @@ def test_run_ahead_scheduling_changes_nothing():
     b = LLM(async_scheduling=True, **kw).generate(prompts, sp2)
     assert [o.outputs[0].token_ids for o in a] == [o.outputs[0].token_ids for o in b]
     assert [o.outputs[0].finish_reason for o in a] == [o.outputs[0].finish_reason for o in b]
+
+
+def test_async_engine_on_the_default_device_streams_tokens():
+    """The streaming front end with the device given as plain "cuda" (what the servers and
+    the trace replay use): its loop thread must come up on the current device, and a
+    request must stream to completion."""
+    import asyncio
+    from arcticinference_b200.engine.async_llm import AsyncLLM
+    llm = AsyncLLM.from_engine_args(EngineArgs(model="llama-tiny", max_model_len=256,
+                                               num_gpu_blocks_override=64)).start()
+    try:
+        assert llm.engine.device.type == "cuda"
+
+        async def run():
+            sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+            outs = await asyncio.wait_for(
+                asyncio.gather(*[llm.generate_final(list(range(5 + i, 40 + i)), sp)
+                                 for i in range(3)]), timeout=120)
+            return [len(o.outputs[0].token_ids) for o in outs]
+
+        assert asyncio.run(run()) == [12, 12, 12]
+    finally:
+        llm.shutdown()
+    ops.check_status()
