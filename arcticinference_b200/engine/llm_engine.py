@@ -37,7 +37,14 @@ class LLMEngine:
             m = self.runner.model
             sp = config.parallel.sp
             max_tokens = (config.scheduler.max_num_batched_tokens + sp - 1) // sp * sp + sp
-            comm.setup(max_tokens, max_tokens, m.blk_rows, config.model.hidden_size,
+            # largest step that runs tensor-parallel: with sequence parallelism only steps up
+            # to the shift threshold and the sampled rows of SwiftKV's later layers do (one
+            # row per request plus one per draft token; 8 rows per request bound that)
+            max_tp = max_tokens
+            if sp > 1:
+                max_tp = min(max_tokens, max(config.parallel.shift_parallel_threshold,
+                                             8 * config.scheduler.max_num_seqs) + sp)
+            comm.setup(max_tokens, max_tp, m.blk_rows, config.model.hidden_size,
                        sp * m.h * m.D)
         self.runner.load_model()
         self.num_blocks = self.runner.determine_num_blocks()
