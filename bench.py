@@ -212,6 +212,7 @@ def main():
         value = tokens_per_step * args.steps / (dev_ms / 1000.0)
         e2e_value = tokens_per_step * args.steps / (e2e_ms / 1000.0)
         line = {
+            "impl": "ours",
             "metric": "combined tok/s (prompt+generated), Llama-3.1-8B shift-parallel serving",
             "value": value, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
