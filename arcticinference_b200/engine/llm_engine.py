@@ -99,14 +99,27 @@ class LLMEngine:
         if params.n == 1:
             self.scheduler.add_request(Request(request_id, ids, params, prompt=text,
                                                eos_token_id=eos, arrival_time=now,
-                                               routing_key=routing_key))
+                                               routing_key=routing_key,
+                                               grammar=self._grammar_for(params, eos)))
         else:
             self._parents[request_id] = {"n": params.n, "done": {}, "prompt": text, "ids": ids}
             for i in range(params.n):
                 self.scheduler.add_request(Request(
                     "%s#%d" % (request_id, i), ids, params.clone_for_sample(i), prompt=text,
-                    eos_token_id=eos, parent_id=request_id, sample_index=i, arrival_time=now))
+                    eos_token_id=eos, parent_id=request_id, sample_index=i, arrival_time=now,
+                    grammar=self._grammar_for(params, eos, copy_given=True)))
         return request_id
+
+    def _grammar_for(self, params: SamplingParams, eos, copy_given: bool = False):
+        """A fresh matcher for one sequence, or None when the request is unconstrained."""
+        if params.guided_choice is None and params.grammar is None:
+            return None
+        from ..structured import build_grammar
+        g = build_grammar(params, self.tokenizer, eos, self.config.speculative)
+        if copy_given and g is params.grammar:
+            import copy
+            g = copy.deepcopy(g)
+        return g
 
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort(request_id)

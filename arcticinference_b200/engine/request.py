@@ -54,6 +54,9 @@ class Request:
     # sampled on the device but not read yet / the request ends with that token whatever it is
     provisional: bool = False
     finishing: bool = False
+    # structured output: matcher over the output tokens (structured.Grammar), advanced by
+    # ``accept_output`` as tokens are appended
+    grammar: Optional[object] = None
 
     def __post_init__(self):
         self.metrics.arrival_time = self.arrival_time
@@ -102,9 +105,16 @@ class Request:
         return _FINISH_REASON.get(self.status)
 
     def check_stop(self, max_model_len: int) -> bool:
-        """Update ``status`` after tokens were appended; True when finished."""
+        """Update ``status`` after one token was appended; True when finished."""
         sp = self.sampling_params
         n_out = len(self.output_token_ids)
+        if self.grammar is not None and n_out > 0:
+            g = self.grammar
+            if not g.finished:
+                g.accept(self.output_token_ids[-1])
+            if g.finished:
+                self.status = RequestStatus.FINISHED_STOPPED
+                return True
         if n_out >= sp.min_tokens and n_out > 0:
             last = self.output_token_ids[-1]
             if not sp.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id:

@@ -24,10 +24,34 @@ def apply_top_k_top_p(logits: torch.Tensor, top_k: torch.Tensor, top_p: torch.Te
     return torch.full_like(logits, float("-inf")).scatter(-1, order, sorted_logits)
 
 
+def apply_grammar_masks(lf: torch.Tensor, sched, rows) -> torch.Tensor:
+    """Set the logits of tokens a request's grammar forbids to -inf. With a draft under
+    verification, row j of the request is masked for the state after draft[:j]."""
+    out = lf
+    for s, rr in zip(sched, rows):
+        g = getattr(s.request, "grammar", None)
+        if g is None or not rr:
+            continue
+        draft = s.request.spec_token_ids[:s.num_draft] if s.num_draft else []
+        for row, allowed in zip(rr, g.allowed_along(draft)):
+            if allowed is None:
+                continue
+            if out is lf:
+                out = lf.clone()
+            keep = torch.as_tensor(sorted(t for t in allowed if 0 <= t < lf.shape[-1]),
+                                   dtype=torch.int64, device=lf.device)
+            masked = torch.full_like(out[row], float("-inf"))
+            if keep.numel():
+                masked[keep] = out[row, keep]
+            out[row] = masked
+    return out
+
+
 def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
     B = logits.shape[0]
     dev = logits.device
-    lf = logits.float()
+    lf = apply_grammar_masks(logits.float(), sched, rows)
+    raw = lf
     temp = torch.ones(B, device=dev)
     top_k = torch.zeros(B, dtype=torch.int64, device=dev)
     top_p = torch.ones(B, device=dev)
@@ -47,7 +71,7 @@ def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
     gen.manual_seed(seed & 0x7FFFFFFF)
     probs = lf.softmax(-1)
     sampled = torch.multinomial(probs, 1, generator=gen).squeeze(1)
-    return torch.where(greedy, logits.float().argmax(-1), sampled)
+    return torch.where(greedy, raw.argmax(-1), sampled)
 
 
 def compute_logprobs(logits: torch.Tensor, token_ids: torch.Tensor, k: int):

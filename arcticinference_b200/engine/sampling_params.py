@@ -25,6 +25,10 @@ class SamplingParams:
     skip_special_tokens: bool = True
     # one forced length per parallel sample (len == n)
     max_tokens_n: Optional[list[int]] = None
+    # structured output: the completion is exactly one of these strings / token-id lists
+    guided_choice: Optional[list] = None
+    # or any matcher implementing structured.Grammar (one fresh object per request)
+    grammar: Optional[object] = None
     extra_args: dict = field(default_factory=dict)
 
     def __post_init__(self):
@@ -48,7 +52,8 @@ class SamplingParams:
     @property
     def needs_full_logits(self) -> bool:
         """True when arg-max / Gumbel-max over raw logits is not enough."""
-        return (self.top_p < 1.0 or self.top_k > 0 or self.logprobs is not None)
+        return (self.top_p < 1.0 or self.top_k > 0 or self.logprobs is not None or
+                self.guided_choice is not None or self.grammar is not None)
 
     def clone_for_sample(self, i: int) -> "SamplingParams":
         import copy

@@ -286,5 +286,9 @@ class Scheduler:
             elif drafts:
                 d = drafts.get(req.request_id)
                 if d:
-                    req.spec_token_ids = list(d)
+                    d = list(d)
+                    if req.grammar is not None:
+                        # a draft may only run as far as the grammar allows
+                        d = d[:req.grammar.validate_draft(d)]
+                    req.spec_token_ids = d
         return done

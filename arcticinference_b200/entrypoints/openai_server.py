@@ -42,6 +42,7 @@ class CompletionRequest(BaseModel):
     ignore_eos: bool = False
     min_tokens: int = 0
     max_tokens_n: Optional[list[int]] = None
+    guided_choice: Optional[list[str]] = None   # the completion is exactly one of these
     routing_key: Optional[str] = None
 
 
@@ -69,6 +70,7 @@ class ChatCompletionRequest(BaseModel):
     add_generation_prompt: bool = True
     continue_final_message: bool = False
     routing_key: Optional[str] = None
+    guided_choice: Optional[list[str]] = None
 
 
 class TokenizeRequest(BaseModel):
@@ -90,7 +92,8 @@ def _sampling(req, max_tokens) -> SamplingParams:
                           max_tokens=max_tokens, stop=req.stop, stop_token_ids=req.stop_token_ids,
                           seed=req.seed, logprobs=lp, ignore_eos=req.ignore_eos,
                           min_tokens=getattr(req, "min_tokens", 0),
-                          max_tokens_n=getattr(req, "max_tokens_n", None))
+                          max_tokens_n=getattr(req, "max_tokens_n", None),
+                          guided_choice=getattr(req, "guided_choice", None) or None)
 
 
 def _sse(obj: Any) -> str:

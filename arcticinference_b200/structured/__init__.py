@@ -209,7 +209,10 @@ def build_grammar(params, tokenizer, eos_token_id, speculative_config=None) -> O
     seqs = []
     for c in choices:
         if isinstance(c, str):
-            ids = tokenizer.encode(c)
+            try:
+                ids = tokenizer.encode(c, add_special_tokens=False)
+            except TypeError:
+                ids = tokenizer.encode(c)
             ids = list(ids["input_ids"]) if isinstance(ids, dict) else list(ids)
         else:
             ids = [int(t) for t in c]

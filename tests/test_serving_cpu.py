@@ -141,3 +141,19 @@ def test_dead_engine_reports(async_llm):
         with pytest.raises(EngineDeadError):
             await a.generate_final([1, 2], SP)
     asyncio.run(run())
+
+
+def test_guided_choice_over_http(async_llm):
+    from fastapi.testclient import TestClient
+    from arcticinference_b200.entrypoints.openai_server import build_app
+    with TestClient(build_app(async_llm, "m")) as c:
+        r = c.post("/v1/completions", json={"model": "m", "prompt": "pick one:", "max_tokens": 16,
+                                            "temperature": 0.8, "seed": 1,
+                                            "guided_choice": ["red", "green", "blue"]})
+        assert r.status_code == 200, r.text
+        ch = r.json()["choices"][0]
+        assert ch["text"] in ("red", "green", "blue") and ch["finish_reason"] == "stop"
+        r = c.post("/v1/chat/completions", json={"model": "m", "max_tokens": 16,
+                                                 "messages": [{"role": "user", "content": "?"}],
+                                                 "guided_choice": ["yes", "no"]})
+        assert r.json()["choices"][0]["message"]["content"] in ("yes", "no")

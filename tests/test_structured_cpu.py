@@ -1,0 +1,88 @@
+"""Grammar-constrained outputs: the matchers, their take-back window, and the engine path
+(with and without speculative decoding)."""
+
+import pytest
+
+from arcticinference_b200 import LLM, SamplingParams
+from arcticinference_b200.config import SpeculativeConfig
+from arcticinference_b200.structured import (ChoiceGrammar, TokenSetGrammar, build_grammar,
+                                             rollback_window)
+
+
+def test_choice_grammar_walks_and_rolls_back():
+    g = ChoiceGrammar([[5, 6, 7], [5, 9], [4]], eos_token_id=2)
+    assert sorted(g.allowed()) == [4, 5]
+    assert not g.accept(6) and g.accept(5)
+    assert sorted(g.allowed()) == [6, 9]
+    assert g.validate_draft([6, 7, 8]) == 2          # state unchanged afterwards
+    assert sorted(g.allowed()) == [6, 9]
+    rows = g.allowed_along([6, 7])
+    assert [sorted(r) for r in rows] == [[6, 9], [7], [2]]
+    assert g.accept(6) and g.accept(7) and g.finished
+    g.rollback(2)
+    assert not g.finished and g.accept(9) and g.finished
+    with pytest.raises(ValueError):
+        g.rollback(5)
+
+
+def test_choice_that_is_a_prefix_ends_with_eos():
+    g = ChoiceGrammar([[5], [5, 6]], eos_token_id=2)
+    assert g.accept(5) and not g.finished
+    assert sorted(g.allowed()) == [2, 6]
+    assert g.accept(2) and g.finished
+    g.rollback(1)
+    assert not g.finished and g.accept(6) and g.finished
+
+
+def test_token_set_grammar():
+    g = TokenSetGrammar([7, 8, 9], max_len=3, min_len=2, eos_token_id=2)
+    assert g.allowed() == [7, 8, 9] and not g.accept(2)
+    assert g.accept(7) and g.accept(9)
+    assert g.allowed() == [7, 8, 9, 2]
+    assert g.validate_draft([8, 8]) == 1
+    assert g.accept(2) and g.finished
+    g.rollback(2)
+    assert not g.finished and g.accept(8) and g.accept(8) and g.finished
+
+
+def test_rollback_window_follows_the_longer_drafter():
+    assert rollback_window(None) == 0
+    arctic = SpeculativeConfig(method="arctic", model="random", num_speculative_tokens=3)
+    assert rollback_window(arctic) == 3
+    hybrid = SpeculativeConfig(method="arctic", model="random", num_speculative_tokens=3,
+                               enable_suffix_decoding=True)
+    assert rollback_window(hybrid) == max(3, hybrid.suffix_speculative_tokens)
+    assert rollback_window(hybrid) > 3
+
+
+CHOICES = ["yes", "no", "maybe so"]
+
+
+@pytest.mark.parametrize("spec", [None, {"method": "suffix"},
+                                  {"method": "arctic", "model": "random",
+                                   "num_speculative_tokens": 3}])
+def test_engine_output_is_one_of_the_choices(spec):
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=256, num_gpu_blocks_override=64,
+              speculative_config=spec)
+    prompts = [{"prompt_token_ids": list(range(10 + i, 40 + i))} for i in range(6)]
+    params = [SamplingParams(temperature=1.0 if i % 2 else 0.0, seed=i, max_tokens=32,
+                             guided_choice=CHOICES) for i in range(6)]
+    outs = llm.generate(prompts, params)
+    texts = [o.outputs[0].text for o in outs]
+    assert all(t in CHOICES for t in texts), texts
+    assert all(o.outputs[0].finish_reason == "stop" for o in outs)
+    # unconstrained requests in the same batch are left alone
+    mixed = llm.generate(prompts[:2], [SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True),
+                                      SamplingParams(temperature=0.0, max_tokens=8,
+                                                     guided_choice=["no"])])
+    assert len(mixed[0].outputs[0].token_ids) == 8 and mixed[1].outputs[0].text == "no"
+
+
+def test_parallel_samples_get_their_own_matcher():
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=256, num_gpu_blocks_override=64)
+    tok = llm.engine.tokenizer
+    g = build_grammar(SamplingParams(guided_choice=CHOICES), tok, 2)
+    sp = SamplingParams(n=3, temperature=1.0, seed=3, max_tokens=16, grammar=g)
+    out = llm.generate([{"prompt_token_ids": list(range(5, 30))}], sp)[0]
+    assert len(out.outputs) == 3 and all(c.text in CHOICES for c in out.outputs)
+    assert not g.finished          # the caller's object was copied, not consumed
