@@ -27,6 +27,8 @@ class SamplingParams:
     max_tokens_n: Optional[list[int]] = None
     # structured output: the completion is exactly one of these strings / token-id lists
     guided_choice: Optional[list] = None
+    # structured output: compact JSON conforming to this JSON schema (dict or JSON text)
+    guided_json: Optional[object] = None
     # or any matcher implementing structured.Grammar (one fresh object per request)
     grammar: Optional[object] = None
     extra_args: dict = field(default_factory=dict)
@@ -53,7 +55,8 @@ class SamplingParams:
     def needs_full_logits(self) -> bool:
         """True when arg-max / Gumbel-max over raw logits is not enough."""
         return (self.top_p < 1.0 or self.top_k > 0 or self.logprobs is not None or
-                self.guided_choice is not None or self.grammar is not None)
+                self.guided_choice is not None or self.guided_json is not None or
+                self.grammar is not None)
 
     def clone_for_sample(self, i: int) -> "SamplingParams":
         import copy

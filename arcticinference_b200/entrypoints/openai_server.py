@@ -43,6 +43,8 @@ class CompletionRequest(BaseModel):
     min_tokens: int = 0
     max_tokens_n: Optional[list[int]] = None
     guided_choice: Optional[list[str]] = None   # the completion is exactly one of these
+    guided_json: Optional[Union[dict, str]] = None   # compact JSON conforming to this schema
+    response_format: Optional[dict] = None
     routing_key: Optional[str] = None
 
 
@@ -71,6 +73,8 @@ class ChatCompletionRequest(BaseModel):
     continue_final_message: bool = False
     routing_key: Optional[str] = None
     guided_choice: Optional[list[str]] = None
+    guided_json: Optional[Union[dict, str]] = None
+    response_format: Optional[dict] = None
 
 
 class TokenizeRequest(BaseModel):
@@ -85,6 +89,28 @@ class DetokenizeRequest(BaseModel):
     tokens: list[int]
 
 
+def _schema_of(req):
+    """JSON schema asked for by ``guided_json`` or by an OpenAI ``response_format`` of type
+    ``json_schema`` (``{"type": "json_schema", "json_schema": {"schema": {...}}}``)."""
+    if getattr(req, "guided_json", None) is not None:
+        return req.guided_json
+    rf = getattr(req, "response_format", None)
+    if rf and rf.get("type") == "json_schema":
+        js = rf.get("json_schema") or {}
+        return js.get("schema", js) or None
+    return None
+
+
+def _checked_schema(req):
+    """The request's schema, compiled once here so that an unsupported one is a client error
+    (ValueError) instead of a failure inside the engine loop."""
+    schema = _schema_of(req)
+    if schema is not None:
+        from ..structured.json_schema import compile_schema
+        compile_schema(schema)
+    return schema
+
+
 def _sampling(req, max_tokens) -> SamplingParams:
     lp = getattr(req, "top_logprobs", None) if isinstance(req, ChatCompletionRequest) and req.logprobs \
         else (req.logprobs if not isinstance(req, ChatCompletionRequest) else None)
@@ -93,7 +119,8 @@ def _sampling(req, max_tokens) -> SamplingParams:
                           seed=req.seed, logprobs=lp, ignore_eos=req.ignore_eos,
                           min_tokens=getattr(req, "min_tokens", 0),
                           max_tokens_n=getattr(req, "max_tokens_n", None),
-                          guided_choice=getattr(req, "guided_choice", None) or None)
+                          guided_choice=getattr(req, "guided_choice", None) or None,
+                          guided_json=_checked_schema(req))
 
 
 def _sse(obj: Any) -> str:

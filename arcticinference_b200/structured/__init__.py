@@ -15,6 +15,8 @@ Built in:
   (``SamplingParams.guided_choice``), a trie over the tokenised choices.
 * :class:`TokenSetGrammar` -- every token comes from a fixed set, up to a length
   (digits-only answers and the like).
+* :class:`json_schema.JsonSchemaGrammar` -- compact JSON that conforms to a JSON schema
+  (``SamplingParams.guided_json``).
 
 Other matchers plug in by implementing :class:`Grammar`.
 """
@@ -203,6 +205,12 @@ def build_grammar(params, tokenizer, eos_token_id, speculative_config=None) -> O
     g = getattr(params, "grammar", None)
     if g is not None:
         return g
+    schema = getattr(params, "guided_json", None)
+    if schema is not None:
+        from .json_schema import JsonSchemaGrammar, Vocabulary, compile_schema
+        size = getattr(tokenizer, "vocab_size", None) or len(tokenizer)
+        return JsonSchemaGrammar(compile_schema(schema), Vocabulary.from_tokenizer(tokenizer, size),
+                                 eos_token_id)
     choices = getattr(params, "guided_choice", None)
     if not choices:
         return None

@@ -157,3 +157,26 @@ def test_guided_choice_over_http(async_llm):
                                                  "messages": [{"role": "user", "content": "?"}],
                                                  "guided_choice": ["yes", "no"]})
         assert r.json()["choices"][0]["message"]["content"] in ("yes", "no")
+
+
+def test_json_schema_response_format_over_http(async_llm):
+    import json
+    from fastapi.testclient import TestClient
+    from arcticinference_b200.entrypoints.openai_server import build_app
+    schema = {"type": "object", "properties": {"answer": {"type": "integer"},
+                                               "unit": {"enum": ["m", "s"]}}}
+    with TestClient(build_app(async_llm, "m")) as c:
+        r = c.post("/v1/chat/completions", json={
+            "model": "m", "max_tokens": 64, "temperature": 0.7, "seed": 5,
+            "messages": [{"role": "user", "content": "how far?"}],
+            "response_format": {"type": "json_schema",
+                                "json_schema": {"name": "a", "schema": schema}}})
+        assert r.status_code == 200, r.text
+        doc = json.loads(r.json()["choices"][0]["message"]["content"])
+        assert isinstance(doc["answer"], int) and doc["unit"] in ("m", "s")
+        r = c.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 64,
+                                            "guided_json": schema})
+        assert set(json.loads(r.json()["choices"][0]["text"])) == {"answer", "unit"}
+        r = c.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 8,
+                                            "guided_json": {"type": ["string", "null"]}})
+        assert r.status_code >= 400

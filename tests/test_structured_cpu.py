@@ -86,3 +86,82 @@ def test_parallel_samples_get_their_own_matcher():
     out = llm.generate([{"prompt_token_ids": list(range(5, 30))}], sp)[0]
     assert len(out.outputs) == 3 and all(c.text in CHOICES for c in out.outputs)
     assert not g.finished          # the caller's object was copied, not consumed
+
+
+# ------------------------------------------------------------------------------ JSON schema
+SCHEMA = {
+    "type": "object",
+    "properties": {
+        "name": {"type": "string", "maxLength": 6},
+        "age": {"type": "integer"},
+        "score": {"type": "number"},
+        "tags": {"type": "array", "items": {"type": "string", "maxLength": 3}, "maxItems": 2},
+        "ok": {"type": "boolean"},
+        "color": {"enum": ["red", "green", 3, None]},
+        "inner": {"$ref": "#/$defs/Point"},
+    },
+    "$defs": {"Point": {"type": "object",
+                        "properties": {"x": {"type": "integer"},
+                                       "y": {"type": "array", "items": {"type": "number"},
+                                             "minItems": 1, "maxItems": 2}}}},
+}
+
+
+def _conforms(doc):
+    assert set(doc) == {"name", "age", "score", "tags", "ok", "color", "inner"}
+    assert isinstance(doc["name"], str) and len(doc["name"]) <= 6
+    assert isinstance(doc["age"], int) and not isinstance(doc["age"], bool)
+    assert isinstance(doc["score"], (int, float))
+    assert isinstance(doc["tags"], list) and len(doc["tags"]) <= 2
+    assert isinstance(doc["ok"], bool) and doc["color"] in ("red", "green", 3, None)
+    assert isinstance(doc["inner"]["x"], int) and 1 <= len(doc["inner"]["y"]) <= 2
+
+
+def test_schema_matcher_accepts_and_rejects():
+    from arcticinference_b200.structured.json_schema import CompiledSchema
+    c = CompiledSchema(SCHEMA)
+    good = ['{"name":"ab","age":-12,"score":1.5e3,"tags":[],"ok":true,"color":"red",'
+            '"inner":{"x":0,"y":[1]}}',
+            '{"name":"a\\"b","age":0,"score":0,"tags":["x","y"],"ok":false,"color":null,'
+            '"inner":{"x":7,"y":[1.0,2]}}']
+    for g in good:
+        assert c.validate(g), g
+    bad = [good[0].replace('"ab"', '"abcdefg"'), good[0].replace("-12", "012"),
+           good[0].replace('"red"', '"blue"'), good[0].replace("[1]", "[]"),
+           good[0].replace("[]", '["a","b","c"]'), good[0][:-1], '{"age":1}']
+    for b in bad:
+        assert not c.validate(b), b
+    with pytest.raises(ValueError):
+        CompiledSchema({"type": ["string", "null"]})
+
+
+def test_schema_grammar_on_tokens_with_rollback():
+    from arcticinference_b200.structured.json_schema import (JsonSchemaGrammar, Vocabulary,
+                                                             compile_schema)
+    # a vocabulary with multi-character tokens that straddle syntax
+    words = [None, None, None, '{"', 'x', '":', '1', '2', '}', '":1', '2}', '"', ',', 'x":']
+    g = JsonSchemaGrammar(compile_schema({"type": "object", "properties": {"x": {"type": "integer"}}}),
+                          Vocabulary(words), eos_token_id=2)
+    tid = {w: i for i, w in enumerate(words) if w}
+    assert sorted(g.allowed()) == [tid['{"']]
+    assert g.accept(tid['{"'])
+    assert sorted(g.allowed()) == sorted([tid['x'], tid['x":']])
+    assert g.validate_draft([tid['x":'], tid['1'], tid['2}'], tid['1']]) == 3
+    assert g.accept(tid['x']) and g.accept(tid['":1'])
+    assert sorted(g.allowed()) == sorted([tid['1'], tid['2'], tid['}'], tid['2}']])
+    assert g.accept(tid['2}']) and g.finished
+    g.rollback(1)
+    assert not g.finished and g.accept(tid['}']) and g.finished
+
+
+@pytest.mark.parametrize("spec", [None, {"method": "suffix"}])
+def test_engine_emits_documents_that_conform(spec):
+    import json
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=512, num_gpu_blocks_override=128,
+              speculative_config=spec)
+    prompts = [{"prompt_token_ids": list(range(20 + i, 50 + i))} for i in range(4)]
+    params = [SamplingParams(temperature=0.9 if i else 0.0, seed=10 + i, max_tokens=400,
+                             guided_json=SCHEMA) for i in range(4)]
+    for o in llm.generate(prompts, params):
+        assert o.outputs[0].finish_reason == "stop", o.outputs[0].text
+        _conforms(json.loads(o.outputs[0].text))
