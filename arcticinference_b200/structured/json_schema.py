@@ -225,7 +225,8 @@ class CompiledSchema:
             if a == 6 and ch in "+-":
                 return ((nid, 7, 0),)
             if a in (6, 7, 8) and ch in _DIGITS:
-                return ((nid, 8, b + 1),) if b < 4 else None
+                # at most two exponent digits: every accepted number is a finite double
+                return ((nid, 8, b + 1),) if b < 2 else None
             return None
         if k == "seq":
             if a >= len(n.children):
