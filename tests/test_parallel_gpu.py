@@ -152,8 +152,17 @@ def _ar_worker(rank, world, port, q, algo="oneshot"):
         comm.begin_forward() if it % 4 == 0 else None
         buf = comm.reduce_buffer(rows, 1024)
         buf.copy_(t)
-        got = comm.all_reduce_full(buf)
+        got = comm.all_reduce_full(buf).clone()
         worst = max(worst, (got.float() - exp).abs().max().item())
+        # the same input reduced again gives the same bits, and every rank holds the same bits
+        buf2 = comm.reduce_buffer(rows, 1024)
+        buf2.copy_(t)
+        again = comm.all_reduce_full(buf2).clone()
+        assert torch.equal(got, again), "all-reduce is not reproducible (%s)" % algo
+        mine = got.view(torch.int16).contiguous()
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        assert all(torch.equal(e, mine) for e in every), "ranks disagree (%s)" % algo
     ops.check_status()
     if rank == 0:
         q.put(worst)
