@@ -12,9 +12,10 @@ that all ranks map. The hot exchanges then happen inside the kernels:
   (``ab200_attention_scatter``); the o_proj GEMM then reads local memory only;
 * tensor-parallel reductions of shift mode: the row-parallel GEMM writes its
   partial product into the heap; small reductions run ``ab200_allreduce`` (every rank sums
-  all ranks' partials with peer loads), larger ones ``ab200_allreduce2`` (one launch: each
+  all ranks' partials with peer loads), large ones ``ab200_allreduce2`` (one launch: each
   rank reduces its slice by peer loads and stores the result into every rank's buffer, so
-  (W-1)/W of the tensor crosses NVLink per direction instead of W-1 times the tensor).
+  (W-1)/W of the tensor crosses NVLink per direction instead of W-1 times the tensor; it
+  costs two flag exchanges, so the switch-over size falls with the number of ranks).
   Both accumulate in fp32 in rank order, so all ranks get the same bits.
 
 Between a producer kernel and its consumers runs ``ab200_barrier`` (flag exchange
@@ -101,9 +102,13 @@ class FusedCommunicator(Communicator):
         mode = os.environ.get("AB200_ALLREDUCE", "auto").lower()
         if mode not in ("auto", "oneshot", "twoshot"):
             raise ValueError("AB200_ALLREDUCE must be auto, oneshot or twoshot")
-        # bytes of one rank's partial from which the two-shot kernel is used
-        self._two_shot_from = {"auto": (1 << 20) if W > 2 else (1 << 62), "oneshot": 1 << 62,
-                               "twoshot": 0}[mode]
+        # Bytes of one rank's partial from which the two-shot kernel is used. Its two flag
+        # exchanges and the system-scope fence between them cost about 20 us more than the
+        # one-shot path (measured on two GPUs at every size); it moves (W-1)^2/W times the
+        # tensor less over NVLink, so it pays once that saving is worth 20 us at ~600 GB/s:
+        # 24 MB on 2 GPUs, 5.3 MB on 4, 2 MB on 8.
+        auto_from = int(12e6 * W / max(1, (W - 1) ** 2)) if W > 1 else (1 << 62)
+        self._two_shot_from = {"auto": auto_from, "oneshot": 1 << 62, "twoshot": 0}[mode]
         torch.cuda.synchronize(self.device)
         dist.barrier()
         L = native.lib()

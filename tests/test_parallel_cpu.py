@@ -9,15 +9,9 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
+from _mp_util import free_port as _free_port, result_or_child_failure as _result_or_child_failure
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-
-
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
 
 
 PROMPTS = [list(range(3, 70)), [9, 8, 7, 6, 5], list(range(100, 131))]
@@ -87,7 +81,7 @@ def _launch(tp, sp, shift, model_name):
              for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=300)
+    res = _result_or_child_failure(q, procs, 300)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0

@@ -10,18 +10,12 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
+from _mp_util import free_port as _free_port, result_or_child_failure as _result_or_child_failure
+
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PROMPTS = [list(range(3, 330)), [9, 8, 7, 6, 5], list(range(100, 231))]
-
-
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
 
 
 def _run_engine(llm, steps=3):
@@ -80,7 +74,7 @@ def _launch(world, tp, sp, shift, model_name, backend):
              for r in range(world)]
     for p in procs:
         p.start()
-    res = q.get(timeout=600)
+    res = _result_or_child_failure(q, procs, 600)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -181,7 +175,7 @@ def test_fused_allreduce_repeated_buffers(algo):
     procs = [ctx.Process(target=_ar_worker, args=(r, world, port, q, algo)) for r in range(world)]
     for p in procs:
         p.start()
-    worst = q.get(timeout=300)
+    worst = _result_or_child_failure(q, procs, 300)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
