@@ -136,9 +136,9 @@ class LLMEngine:
         ``partial`` also an unfinished ``RequestOutput`` (cumulative text and tokens) for every
         request that produced tokens in this step, for streaming front ends.
 
-        With ``async_scheduling`` a decode-only step is left running on the device and its
-        tokens are read by the *next* call, after that call has already scheduled and queued
-        the following step (the host's scheduling and batching work then overlaps the GPU)."""
+        With ``async_scheduling`` a step is left running on the device and its tokens are
+        read by the *next* call, after that call has already scheduled and queued the
+        following step (the host's scheduling and batching work then overlaps the GPU)."""
         if self.sleeping_level:
             raise RuntimeError("engine is sleeping; call wake_up() first")
         prev, self._pending = self._pending, None
@@ -173,13 +173,13 @@ class LLMEngine:
 
     def _can_run_ahead(self, out) -> bool:
         """A step may be left in flight when the next step can be scheduled without knowing
-        its tokens: decode only, nothing waiting for admission, no drafting, device sampling."""
+        its tokens: no drafting (the accepted length decides the next position) and device
+        sampling for every request that samples. Prompt chunks, requests that finish their
+        prompt in this step and newly admitted requests are all fine."""
         if not self.config.scheduler.async_scheduling or self.config.speculative is not None:
             return False
-        if self.scheduler.waiting:
-            return False
         for s in out.scheduled:
-            if not s.samples or s.num_tokens != 1 or s.request.sampling_params.needs_full_logits:
+            if s.samples and (s.num_draft or s.request.sampling_params.needs_full_logits):
                 return False
         return True
 

@@ -272,24 +272,24 @@ class ModelRunner:
         self._stage_done()
         self.h2d_bytes = stage.numel() * 8 + bt.nbytes
         self.h2d_total += self.h2d_bytes
-        bt_t = torch.from_numpy(bt).to(dev, non_blocking=True)
         m = self.model
         if Np > N:
             # padding tokens form a sequence of their own that attends to nothing real
             q_lens_a, kv_lens_a = q_lens + [Np - N], kv_lens + [Np - N]
             bt_pad = np.zeros((len(sched) + 1, max_blocks), dtype=np.int32)
             bt_pad[:-1] = bt
-            bt_t = torch.from_numpy(bt_pad).to(dev, non_blocking=True)
+            bt_t = ops.upload(bt_pad, dev)
         else:
             q_lens_a, kv_lens_a = q_lens, kv_lens
+            bt_t = ops.upload(bt, dev)
         if plan is not None and Np == N:
             from . import forest_cascade as fca
             work, tok_splits, table, max_splits = fca.build_cascade_work(
                 plan, q_lens, kv_lens, [s.request.block_ids for s in sched], bs, self.G)
             meta = ops.AttentionMetadata(list(q_lens), list(kv_lens), N)
-            meta.work = torch.from_numpy(work).to(dev, non_blocking=True)
-            meta.tok_splits = torch.from_numpy(tok_splits).to(dev, non_blocking=True)
-            meta.block_tables = torch.from_numpy(table).to(dev, non_blocking=True)
+            meta.work = ops.upload(work, dev)
+            meta.tok_splits = ops.upload(tok_splits, dev)
+            meta.block_tables = ops.upload(table, dev)
             meta.max_splits, meta.num_work = max_splits, work.shape[0]
             meta.tile_keys = ops.pick_tile_keys(q_lens, self.G)
             meta.o_part = torch.empty(max_splits, N, m.h, m.D, dtype=torch.float32, device=dev)
@@ -306,7 +306,7 @@ class ModelRunner:
                 sq = [x for x in sel_q_lens if x > 0]
                 skv = [kv for kv, x in zip(kv_lens, sel_q_lens) if x > 0]
                 keep = [i for i, x in enumerate(sel_q_lens) if x > 0]
-                bt_sel = bt_t[torch.as_tensor(keep, device=dev)].contiguous() \
+                bt_sel = bt_t[ops.upload(np.asarray(keep, dtype=np.int64), dev)].contiguous() \
                     if len(keep) != bt_t.shape[0] else bt_t
                 batch.sel_attn_meta = ops.build_attention_metadata(sq, skv, bt_sel, self.G, m.h,
                                                                    m.D, dev, Hkv=m.hkv)
@@ -331,8 +331,8 @@ class ModelRunner:
                     for j, row in enumerate(rr):
                         tv[row] = 0.0 if sp.greedy else sp.temperature
                         sv[row] = (base * 1000003 + s.request.num_tokens + j) & 0x7FFFFFFFFFFFFFFF
-                temps = torch.from_numpy(tv).to(self.device, non_blocking=True)
-                seeds = torch.from_numpy(sv).to(self.device, non_blocking=True)
+                temps = ops.upload(tv, self.device)
+                seeds = ops.upload(sv, self.device)
             offset = 0
             if sharded:
                 offset = self.model.vocab_shard(comm.ways, self.shard.head_block)[0]
@@ -404,14 +404,14 @@ class ModelRunner:
         src_rows = None
         if prev is not None and prev.ids_dev is not None:
             # token offset of every request in this step -> row of its sampled token in prev
-            src, any_src, t = [], False, 0
+            src = np.full(out.total_tokens, -1, dtype=np.int64)
+            any_src, t = False, 0
             for s in sched:
-                j = -1
                 if s.num_tokens == 1 and s.request.token_at(s.start) == PLACEHOLDER_TOKEN:
                     j = prev.row_of.get(id(s.request), -1)
-                    any_src = any_src or j >= 0
-                src.append(j)
-                src.extend([-1] * (s.num_tokens - 1))
+                    if j >= 0:
+                        src[t] = j
+                        any_src = True
                 t += s.num_tokens
             if any_src:
                 src_rows = src
@@ -432,10 +432,9 @@ class ModelRunner:
             self.mode_counts[batch.mode] += 1
             if src_rows is not None:
                 n = batch.input_ids.numel()
-                idx = torch.tensor(src_rows + [-1] * (n - len(src_rows)), dtype=torch.int64)
-                if self.device.type == "cuda":
-                    idx = idx.pin_memory().to(self.device, non_blocking=True)
-                ops.patch_ids(batch.input_ids, idx, prev.ids_dev)
+                if n > src_rows.size:          # rows added to pad the step take no token
+                    src_rows = np.concatenate([src_rows, np.full(n - src_rows.size, -1, np.int64)])
+                ops.patch_ids(batch.input_ids, ops.upload(src_rows, self.device), prev.ids_dev)
             if batch.logits_indices.numel() == 0:
                 # pure prefill chunk: KV only
                 self.model.forward(batch, self.kv)

@@ -54,6 +54,8 @@ class Request:
     # sampled on the device but not read yet / the request ends with that token whatever it is
     provisional: bool = False
     finishing: bool = False
+    # run-ahead scheduling: tokens of a prompt chunk whose step is queued but not completed
+    chunk_ahead: int = 0
     # structured output: matcher over the output tokens (structured.Grammar), advanced by
     # ``accept_output`` as tokens are appended
     grammar: Optional[object] = None

@@ -99,6 +99,7 @@ class Scheduler:
             self.running.remove(victim)
             self.kv.free(victim)
             victim.num_computed_tokens = 0
+            victim.chunk_ahead = 0
             victim.spec_token_ids = []
             victim.status = RequestStatus.PREEMPTED
             self.waiting.appendleft(victim)
@@ -169,6 +170,8 @@ class Scheduler:
         # 2) admit waiting requests
         while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
             req = self.waiting[0]
+            if req.provisional:
+                break   # preempted with a token still unread: re-admitted once it is known
             if req.num_computed_tokens == 0 and not req.block_ids:
                 cached = self.kv.match_prefix(req)
                 req.num_computed_tokens = cached
@@ -203,16 +206,21 @@ class Scheduler:
 
     # ----------------------------------------------------------------------------- run-ahead
     def advance_provisionally(self, out: SchedulerOutput) -> None:
-        """Book the token that every request of a decode-only step is about to receive, before
-        the host has read it: the next step can then be scheduled and queued while this one
-        still runs. The token itself is a placeholder until ``update_from_output``."""
+        """Book the outcome of a step before the host has read its tokens, so that the next
+        step can be scheduled and queued while this one still runs: a prompt chunk advances
+        the request's computed position; a sampling request also receives a placeholder for
+        the token it is about to get (``update_from_output`` puts the real one in). Draft
+        verification cannot be booked ahead (the accepted length is unknown)."""
         cfg = self.config
         for s in out.scheduled:
             req = s.request
             if req.status.finished or req.status == RequestStatus.PREEMPTED:
                 continue
-            assert s.samples and s.num_tokens == 1 and not req.provisional
-            req.num_computed_tokens += 1
+            assert not req.provisional and not req.chunk_ahead and s.num_draft == 0
+            req.num_computed_tokens += s.num_tokens
+            if not s.samples:
+                req.chunk_ahead = s.num_tokens
+                continue
             req.output_token_ids.append(PLACEHOLDER_TOKEN)
             req.provisional = True
             sp = req.sampling_params
@@ -237,10 +245,29 @@ class Scheduler:
                 toks = new_tokens.get(req.request_id, [])
                 if toks and req.output_token_ids and req.output_token_ids[-1] == PLACEHOLDER_TOKEN:
                     req.output_token_ids[-1] = toks[0]
+            if provisional and req.status == RequestStatus.PREEMPTED:
+                # preempted while its token was in flight: the token is now known and may
+                # end the request, which then must not be admitted again
+                req.finishing = False
+                if req.metrics.first_token_time is None:
+                    req.metrics.first_token_time = now
+                req.metrics.last_token_time = now
+                if req.check_stop(self.config.max_model_len):
+                    req.metrics.finished_time = now
+                    self.waiting.remove(req)
+                    self.kv.free(req)
+                    self.finished.append(req)
+                    done.append(req)
+                else:
+                    req.status = RequestStatus.PREEMPTED
+                continue
             if req.status.finished or req.status == RequestStatus.PREEMPTED:
                 continue
             if not s.samples:
-                req.num_computed_tokens += s.num_tokens
+                if req.chunk_ahead:
+                    req.chunk_ahead = 0          # the position was advanced when it was booked
+                else:
+                    req.num_computed_tokens += s.num_tokens
                 self.kv.commit(req, req.num_computed_tokens)
                 continue
             toks = new_tokens.get(req.request_id, [])

@@ -638,6 +638,18 @@ def _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split, m
     return work.astype(np.int32), tok_splits, int(ns.max()) if R else 1
 
 
+def upload(a: np.ndarray, device) -> torch.Tensor:
+    """Host array -> device tensor without stalling the host. A copy from pageable memory
+    makes the host wait until the stream has reached it, i.e. until every step queued before
+    it has finished, which would undo run-ahead stepping; so the array goes through pinned
+    memory of the caching host allocator (kept alive until the copy has run)."""
+    t = torch.from_numpy(a)
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        t = t.pin_memory()
+    return t.to(dev, non_blocking=True)
+
+
 def pick_tile_keys(q_lens, G: int) -> int:
     """64-key tiles when every sequence's query rows fit one warp of the 128-row tile."""
     return 64 if q_lens and max(q_lens) * G <= 32 else 128
@@ -657,8 +669,8 @@ def build_attention_metadata(q_lens, kv_lens, block_tables, G, Hq, D, device, ca
         work = np.concatenate([work, pad], 0)
     meta = AttentionMetadata(list(q_lens), list(kv_lens), T)
     dev = torch.device(device)
-    meta.work = torch.from_numpy(work).to(dev, non_blocking=True)
-    meta.tok_splits = torch.from_numpy(tok_splits).to(dev, non_blocking=True)
+    meta.work = upload(work, dev)
+    meta.tok_splits = upload(tok_splits, dev)
     meta.block_tables = block_tables
     meta.max_splits = max_splits
     meta.num_work = work.shape[0]

@@ -85,3 +85,41 @@ def test_streaming_with_late_arrivals():
         finally:
             llm.shutdown()
     asyncio.run(main())
+
+
+def test_mixed_steps_run_ahead_with_chunked_prompts():
+    """Prompt chunks, prompts that complete inside a step and admissions all run ahead: with
+    a small token budget the long prompts are cut into chunks that share steps with the
+    decodes of the short ones."""
+    prompts = [list(range(10, 150)), [7, 8, 9], list(range(30, 120)), [5] * 70, [1, 2]]
+    sp = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in (9, 40, 1, 22, 33)]
+    kw = dict(max_num_batched_tokens=48, max_num_seqs=4)
+    a, fa, ref = _run(False, sp, prompts, **kw)
+    b, fb, llm = _run(True, sp, prompts, **kw)
+    assert a == b and fa == fb
+    st = llm.engine.stats
+    assert st["steps"] == ref.engine.stats["steps"]
+    # nearly every step after the first was queued while its predecessor was still running
+    assert st["run_ahead_steps"] >= st["steps"] - 3, st
+    assert llm.engine._pending is None and not llm.engine.has_unfinished_requests()
+    assert all(r.chunk_ahead == 0 and not r.provisional for r in llm.engine.scheduler.finished)
+
+
+def test_mixed_steps_with_prefix_cache_and_few_blocks():
+    shared = list(range(200, 264))
+    prompts = [shared + [i, i + 1, i + 2] * 5 for i in range(1, 7)]
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+    kw = dict(max_num_batched_tokens=64, enable_prefix_caching=True)
+    a, fa, _ = _run(False, sp, prompts, blocks=20, **kw)
+    b, fb, llm = _run(True, sp, prompts, blocks=20, **kw)
+    assert a == b and fa == fb and all(len(x[0]) == 30 for x in b)
+    assert llm.engine.stats["run_ahead_steps"] > 20
+
+
+def test_full_distribution_requests_do_not_run_ahead():
+    sp = [SamplingParams(temperature=0.8, top_p=0.9, seed=3, max_tokens=12, ignore_eos=True),
+          SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)]
+    a, _, _ = _run(False, sp, PROMPTS[:2])
+    b, _, llm = _run(True, sp, PROMPTS[:2])
+    assert a == b
+    assert llm.engine.stats["run_ahead_steps"] == 0
