@@ -4,12 +4,14 @@ token ids through the tokenizer's vocabulary.
 The reference gets guided JSON from vLLM's grammar back end and evaluates it with its
 JSON-mode benchmark (tests/benchmarks/json_mode/task_description.py:6-33: flat and nested
 pydantic models with string / number / list fields). This module covers that subset of JSON
-Schema natively: ``object`` (properties are emitted in declaration order, all of them),
-``array`` (``items``, ``minItems``, ``maxItems``), ``string`` (``maxLength``, ``enum``),
-``integer``, ``number``, ``boolean``, ``null``, ``enum`` / ``const`` of any JSON literals,
-and ``$ref`` into ``$defs`` / ``definitions``. Output is compact JSON (no white space).
+Schema natively: ``object`` (properties in declaration order; with a ``required`` list the
+other properties are optional), ``array`` (``items``, ``minItems``, ``maxItems``),
+``string`` (``maxLength``, ``enum``), ``integer``, ``number``, ``boolean``, ``null``,
+``enum`` / ``const`` of any JSON literals, ``anyOf`` / ``oneOf`` / lists of types, and
+``$ref`` into ``$defs`` / ``definitions``. Output is compact JSON (no white space).
 
-The matcher is a deterministic stack machine. A state is a tuple of frames, hashable, so
+The matcher is a stack machine. One reading of the text so far is a tuple of frames; a
+state is the set of readings that are still possible (alternatives fork it), hashable, so
 the set of allowed tokens is computed once per distinct state and shared by every request
 that uses the same compiled schema.
 """
@@ -28,7 +30,7 @@ _ESCAPES = '"\\/bfnrt'
 
 # ---------------------------------------------------------------------------- compilation
 class _Node:
-    """kind: lit | str | int | num | trie | seq | arr"""
+    """kind: lit | str | int | num | trie | seq | arr | alt"""
     __slots__ = ("kind", "text", "max_len", "trie", "children", "item", "min_items", "max_items")
 
     def __init__(self, kind, **kw):
@@ -65,6 +67,11 @@ class CompiledSchema:
         self.root = self._compile(schema, 0)
         self.allowed_cache: dict = {}     # (vocabulary id, state) -> list of token ids
 
+    def _alt(self, options: list) -> int:
+        if len(options) == 1:
+            return options[0]
+        return self._add(_Node("alt", children=options))
+
     def _add(self, node: _Node) -> int:
         self.nodes.append(node)
         return len(self.nodes) - 1
@@ -84,10 +91,16 @@ class CompiledSchema:
         if "enum" in sch:
             words = [json.dumps(v, separators=(",", ":")) for v in sch["enum"]]
             return self._add(_Node("trie", trie=_make_trie(words)))
+        for key in ("anyOf", "oneOf"):
+            if key in sch:
+                return self._alt([self._compile(o, depth + 1) for o in sch[key]])
         t = sch.get("type")
         if isinstance(t, list):
-            raise ValueError("type unions are not supported")
+            rest = {k: v for k, v in sch.items() if k != "type"}
+            return self._alt([self._compile(dict(rest, type=one), depth + 1) for one in t])
         if t == "string":
+            if "pattern" in sch:
+                raise ValueError("string patterns are not supported")
             return self._add(_Node("str", max_len=sch.get("maxLength")))
         if t == "integer":
             return self._add(_Node("int"))
@@ -102,22 +115,39 @@ class CompiledSchema:
             return self._add(_Node("arr", item=item, min_items=int(sch.get("minItems", 0)),
                                    max_items=sch.get("maxItems")))
         if t == "object" or "properties" in sch:
-            props = sch.get("properties", {})
+            props = list(sch.get("properties", {}).items())
             if not props:
                 return self._add(_Node("lit", text="{}"))
-            children, lead = [], "{"
-            for name, sub in props.items():
-                children.append(self._add(_Node("lit", text=lead + json.dumps(name) + ":")))
-                children.append(self._compile(sub, depth + 1))
-                lead = ","
-            children.append(self._add(_Node("lit", text="}")))
-            return self._add(_Node("seq", children=children))
+            # Properties come in declaration order. With a "required" list the others may be
+            # left out: tail(i, emitted) is what may follow once the first i properties have
+            # been dealt with, ``emitted`` telling whether a separator is due.
+            required = set(sch["required"]) if "required" in sch else {k for k, _ in props}
+            values = [self._compile(sub, depth + 1) for _, sub in props]
+            memo: dict = {}
+
+            def tail(i: int, emitted: bool) -> int:
+                key = (i, emitted)
+                if key in memo:
+                    return memo[key]
+                if i == len(props):
+                    nid = self._add(_Node("lit", text="}"))
+                else:
+                    name = props[i][0]
+                    lead = self._add(_Node("lit", text=("," if emitted else "") +
+                                           json.dumps(name) + ":"))
+                    taken = self._add(_Node("seq", children=[lead, values[i], tail(i + 1, True)]))
+                    nid = taken if name in required else self._alt([taken, tail(i + 1, emitted)])
+                memo[key] = nid
+                return nid
+
+            return self._add(_Node("seq", children=[self._add(_Node("lit", text="{")),
+                                                    tail(0, False)]))
         raise ValueError("unsupported schema: %r" % (sch,))
 
     # ------------------------------------------------------------------------ machine
     # frames: (node id, a, b) -- the meaning of a, b depends on the node kind
-    def start(self) -> tuple:
-        return (self._enter(self.root),)
+    def start(self) -> frozenset:
+        return frozenset([(self._enter(self.root),)])
 
     def _enter(self, nid: int) -> tuple:
         n = self.nodes[nid]
@@ -150,12 +180,11 @@ class CompiledSchema:
             return a == len(n.children)
         if k == "arr":
             return a == 9
-        return False
+        return False      # alt: no JSON value is empty
 
-    def _consume(self, frame, ch: str):
-        """One character into the top frame. Returns a tuple of frames replacing it (the
-        frame itself, possibly with a child pushed above it), or None if ``ch`` does not
-        fit. Frames that only delegate (seq, arr) push their child and let it consume."""
+    def _consume_leaf(self, frame, ch: str):
+        """One character into a frame of a leaf kind (lit, trie, str, int, num): the frame
+        that replaces it, as a one-element tuple, or None if ``ch`` does not fit."""
         nid, a, b = frame
         n = self.nodes[nid]
         k = n.kind
@@ -228,53 +257,76 @@ class CompiledSchema:
                 # at most two exponent digits: every accepted number is a finite double
                 return ((nid, 8, b + 1),) if b < 2 else None
             return None
+        return None
+
+    def _consume(self, frame, ch: str) -> list:
+        """One character into the top frame: every way it can be taken, each as the tuple of
+        frames that replaces the frame (itself, possibly with children pushed above it).
+        Empty when ``ch`` does not fit. seq and arr push their child and let it consume; alt
+        forks into its options."""
+        nid, a, b = frame
+        n = self.nodes[nid]
+        k = n.kind
+        if k == "alt":
+            out = []
+            for c in n.children:
+                out.extend(self._consume(self._enter(c), ch))
+            return out
         if k == "seq":
             if a >= len(n.children):
-                return None
-            child = self._enter(n.children[a])
-            got = self._consume(child, ch)
-            if got is None:
-                return None
-            return ((nid, a + 1, 0),) + got
+                return []
+            return [((nid, a + 1, 0),) + got
+                    for got in self._consume(self._enter(n.children[a]), ch)]
         if k == "arr":
-            # a: 0 before '[', 1 right after '[', 2 after an item, 9 closed; b items so far
+            # a: 0 before '[', 1 right after '[', 2 after an item, 3 after ',', 9 closed;
+            # b items so far
             if a == 0:
-                return ((nid, 1, 0),) if ch == "[" else None
+                return [((nid, 1, 0),)] if ch == "[" else []
             if a == 1 or a == 3:
                 if a == 1 and ch == "]":
-                    return ((nid, 9, b),) if b >= n.min_items else None
+                    return [((nid, 9, b),)] if b >= n.min_items else []
                 if n.max_items is not None and b >= n.max_items:
-                    return None
-                got = self._consume(self._enter(n.item), ch)
-                if got is None:
-                    return None
-                return ((nid, 2, b + 1),) + got
+                    return []
+                return [((nid, 2, b + 1),) + got
+                        for got in self._consume(self._enter(n.item), ch)]
             if a == 2:
                 if ch == ",":
                     if n.max_items is not None and b >= n.max_items:
-                        return None
-                    return ((nid, 3, b),)
+                        return []
+                    return [((nid, 3, b),)]
                 if ch == "]":
-                    return ((nid, 9, b),) if b >= n.min_items else None
-            return None
-        return None
+                    return [((nid, 9, b),)] if b >= n.min_items else []
+            return []
+        got = self._consume_leaf(frame, ch)
+        return [] if got is None else [got]
 
-    def advance(self, state: tuple, ch: str) -> Optional[tuple]:
-        """State after ``ch``, or None. Finished frames on top are popped first when they
-        cannot take the character themselves (numbers end by look-ahead)."""
-        stack = list(state)
-        while stack:
-            got = self._consume(stack[-1], ch)
-            if got is not None:
-                stack[-1:] = list(got)
-                # drop frames that can take nothing more (closed literals, strings, arrays)
-                while stack and self._closed(stack[-1]):
-                    stack.pop()
-                return tuple(stack)
-            if not self._accepting(stack[-1]):
-                return None
-            stack.pop()
-        return None
+    def _advance_stack(self, stack: tuple, ch: str) -> list:
+        """Stacks reachable from one stack by ``ch``. Finished frames on top are popped when
+        they cannot take the character themselves (numbers end by look-ahead)."""
+        frames = list(stack)
+        while frames:
+            alts = self._consume(frames[-1], ch)
+            if alts:
+                out = []
+                for got in alts:
+                    new = frames[:-1] + list(got)
+                    # drop frames that can take nothing more (closed literals, strings, ...)
+                    while new and self._closed(new[-1]):
+                        new.pop()
+                    out.append(tuple(new))
+                return out
+            if not self._accepting(frames[-1]):
+                return []
+            frames.pop()
+        return []
+
+    def advance(self, state: frozenset, ch: str) -> Optional[frozenset]:
+        """State (a set of stacks, one per way of reading the text so far) after ``ch``, or
+        None when no reading survives."""
+        out = set()
+        for stack in state:
+            out.update(self._advance_stack(stack, ch))
+        return frozenset(out) if out else None
 
     def _closed(self, frame) -> bool:
         nid, a, b = frame
@@ -291,18 +343,20 @@ class CompiledSchema:
             return None in node and len(node) == 1
         return False
 
-    def advance_text(self, state: tuple, text: str) -> Optional[tuple]:
+    def advance_text(self, state: frozenset, text: str) -> Optional[frozenset]:
         for ch in text:
-            if not state:
-                return None
             state = self.advance(state, ch)
             if state is None:
                 return None
         return state
 
-    def complete(self, state: tuple) -> bool:
-        """True when the text so far is a whole document."""
-        return all(self._accepting(f) for f in state)
+    def complete(self, state: frozenset) -> bool:
+        """True when the text so far is a whole document under some reading."""
+        return any(all(self._accepting(f) for f in stack) for stack in state)
+
+    def exhausted(self, state: frozenset) -> bool:
+        """True when the document is whole and nothing can follow it."""
+        return all(len(stack) == 0 for stack in state)
 
     def validate(self, text: str) -> bool:
         st = self.advance_text(self.start(), text)
@@ -367,7 +421,7 @@ class JsonSchemaGrammar(Grammar):
 
     @property
     def finished(self) -> bool:
-        return self._ended or not self.state
+        return self._ended or self.c.exhausted(self.state)
 
     def allowed(self):
         if self.finished:

@@ -132,7 +132,7 @@ def test_schema_matcher_accepts_and_rejects():
     for b in bad:
         assert not c.validate(b), b
     with pytest.raises(ValueError):
-        CompiledSchema({"type": ["string", "null"]})
+        CompiledSchema({"type": "string", "pattern": "^a+$"})
 
 
 def test_schema_grammar_on_tokens_with_rollback():
@@ -165,3 +165,39 @@ def test_engine_emits_documents_that_conform(spec):
     for o in llm.generate(prompts, params):
         assert o.outputs[0].finish_reason == "stop", o.outputs[0].text
         _conforms(json.loads(o.outputs[0].text))
+
+
+def test_unions_and_optional_properties():
+    from arcticinference_b200.structured.json_schema import CompiledSchema
+    c = CompiledSchema({"type": "object", "required": ["b"], "properties": {
+        "a": {"type": "integer"}, "b": {"type": ["string", "null"]},
+        "c": {"anyOf": [{"type": "number"}, {"type": "array", "items": {"type": "integer"}}]}}})
+    for t in ['{"a":1,"b":"x","c":2.5}', '{"b":null}', '{"b":"q","c":[1,2]}', '{"a":0,"b":null}']:
+        assert c.validate(t), t
+    for t in ['{"a":1}', '{}', '{"b":1}', '{"c":1,"b":null}', '{"b":null,}', '{,"b":null}']:
+        assert not c.validate(t), t
+    # readings that share a prefix stay alive side by side: 12 is an integer and a number
+    u = CompiledSchema({"anyOf": [{"type": "integer"}, {"type": "number"}, {"const": "n/a"}]})
+    assert u.validate("12") and u.validate("1.5e2") and u.validate('"n/a"')
+    assert not u.validate('"x"') and not u.validate("1.")
+    st = u.advance_text(u.start(), "12")
+    assert len(st) == 2 and u.complete(st) and not u.exhausted(st)
+
+
+def test_engine_with_optional_fields_and_unions():
+    import json
+    schema = {"type": "object", "required": ["kind"], "properties": {
+        "kind": {"enum": ["a", "b"]}, "n": {"type": ["integer", "null"]},
+        "tags": {"type": "array", "items": {"enum": ["x", "y"]}, "maxItems": 3}}}
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=512, num_gpu_blocks_override=128)
+    prompts = [{"prompt_token_ids": list(range(40 + i, 60 + i))} for i in range(5)]
+    params = [SamplingParams(temperature=1.0, seed=i, max_tokens=200, guided_json=schema)
+              for i in range(5)]
+    seen = set()
+    for o in llm.generate(prompts, params):
+        doc = json.loads(o.outputs[0].text)
+        assert doc["kind"] in ("a", "b") and set(doc) <= {"kind", "n", "tags"}
+        assert doc.get("n") is None or isinstance(doc["n"], int)
+        assert all(t in ("x", "y") for t in doc.get("tags", [])) and len(doc.get("tags", [])) <= 3
+        seen.add(tuple(sorted(doc)))
+    assert len(seen) >= 1
