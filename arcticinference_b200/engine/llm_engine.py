@@ -113,7 +113,7 @@ class LLMEngine:
     def _grammar_for(self, params: SamplingParams, eos, copy_given: bool = False):
         """A fresh matcher for one sequence, or None when the request is unconstrained."""
         if params.guided_choice is None and params.guided_json is None and \
-                params.grammar is None:
+                params.guided_regex is None and params.grammar is None:
             return None
         from ..structured import build_grammar
         g = build_grammar(params, self.tokenizer, eos, self.config.speculative)

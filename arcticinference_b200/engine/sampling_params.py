@@ -29,6 +29,8 @@ class SamplingParams:
     guided_choice: Optional[list] = None
     # structured output: compact JSON conforming to this JSON schema (dict or JSON text)
     guided_json: Optional[object] = None
+    # structured output: the whole completion matches this regular expression
+    guided_regex: Optional[str] = None
     # or any matcher implementing structured.Grammar (one fresh object per request)
     grammar: Optional[object] = None
     extra_args: dict = field(default_factory=dict)
@@ -56,6 +58,7 @@ class SamplingParams:
         """True when arg-max / Gumbel-max over raw logits is not enough."""
         return (self.top_p < 1.0 or self.top_k > 0 or self.logprobs is not None or
                 self.guided_choice is not None or self.guided_json is not None or
+                self.guided_regex is not None or
                 self.grammar is not None)
 
     def clone_for_sample(self, i: int) -> "SamplingParams":

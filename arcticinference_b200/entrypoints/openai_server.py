@@ -44,6 +44,7 @@ class CompletionRequest(BaseModel):
     max_tokens_n: Optional[list[int]] = None
     guided_choice: Optional[list[str]] = None   # the completion is exactly one of these
     guided_json: Optional[Union[dict, str]] = None   # compact JSON conforming to this schema
+    guided_regex: Optional[str] = None              # the completion matches this expression
     response_format: Optional[dict] = None
     routing_key: Optional[str] = None
 
@@ -74,6 +75,7 @@ class ChatCompletionRequest(BaseModel):
     routing_key: Optional[str] = None
     guided_choice: Optional[list[str]] = None
     guided_json: Optional[Union[dict, str]] = None
+    guided_regex: Optional[str] = None
     response_format: Optional[dict] = None
 
 
@@ -111,6 +113,14 @@ def _checked_schema(req):
     return schema
 
 
+def _checked_regex(req):
+    pattern = getattr(req, "guided_regex", None)
+    if pattern is not None:
+        from ..structured.regex import compile_regex
+        compile_regex(pattern)
+    return pattern
+
+
 def _sampling(req, max_tokens) -> SamplingParams:
     lp = getattr(req, "top_logprobs", None) if isinstance(req, ChatCompletionRequest) and req.logprobs \
         else (req.logprobs if not isinstance(req, ChatCompletionRequest) else None)
@@ -120,7 +130,7 @@ def _sampling(req, max_tokens) -> SamplingParams:
                           min_tokens=getattr(req, "min_tokens", 0),
                           max_tokens_n=getattr(req, "max_tokens_n", None),
                           guided_choice=getattr(req, "guided_choice", None) or None,
-                          guided_json=_checked_schema(req))
+                          guided_json=_checked_schema(req), guided_regex=_checked_regex(req))
 
 
 def _sse(obj: Any) -> str:

@@ -15,8 +15,9 @@ Built in:
   (``SamplingParams.guided_choice``), a trie over the tokenised choices.
 * :class:`TokenSetGrammar` -- every token comes from a fixed set, up to a length
   (digits-only answers and the like).
-* :class:`json_schema.JsonSchemaGrammar` -- compact JSON that conforms to a JSON schema
-  (``SamplingParams.guided_json``).
+* :class:`json_schema.CharMachineGrammar` over a compiled JSON schema -- compact JSON that
+  conforms to the schema (``SamplingParams.guided_json``) -- or over a compiled regular
+  expression (``SamplingParams.guided_regex``, :mod:`regex`).
 
 Other matchers plug in by implementing :class:`Grammar`.
 """
@@ -211,6 +212,13 @@ def build_grammar(params, tokenizer, eos_token_id, speculative_config=None) -> O
         size = getattr(tokenizer, "vocab_size", None) or len(tokenizer)
         return JsonSchemaGrammar(compile_schema(schema), Vocabulary.from_tokenizer(tokenizer, size),
                                  eos_token_id)
+    pattern = getattr(params, "guided_regex", None)
+    if pattern is not None:
+        from .json_schema import CharMachineGrammar, Vocabulary
+        from .regex import compile_regex
+        size = getattr(tokenizer, "vocab_size", None) or len(tokenizer)
+        return CharMachineGrammar(compile_regex(pattern), Vocabulary.from_tokenizer(tokenizer, size),
+                                  eos_token_id)
     choices = getattr(params, "guided_choice", None)
     if not choices:
         return None

@@ -405,12 +405,13 @@ class Vocabulary:
         return v
 
 
-class JsonSchemaGrammar(Grammar):
-    """Token-level matcher for one sequence. ``eos_token_id`` is allowed once the text is a
-    whole document; a document that cannot be extended finishes by itself."""
+class CharMachineGrammar(Grammar):
+    """Token-level matcher for one sequence over a character-level machine (a compiled JSON
+    schema or regular expression: ``start / advance / advance_text / complete / exhausted``
+    and an ``allowed_cache`` dict). ``eos_token_id`` is allowed once the text is a whole
+    document; a document that cannot be extended finishes by itself."""
 
-    def __init__(self, compiled: CompiledSchema, vocab: Vocabulary,
-                 eos_token_id: Optional[int] = None):
+    def __init__(self, compiled, vocab: Vocabulary, eos_token_id: Optional[int] = None):
         self.c, self.v, self.eos = compiled, vocab, eos_token_id
         self._hist = [compiled.start()]
         self._ended = False
@@ -469,6 +470,9 @@ class JsonSchemaGrammar(Grammar):
             raise ValueError("cannot roll back %d of %d tokens" % (n, len(self._hist) - 1))
         del self._hist[-n:]
         self._ended = False
+
+
+JsonSchemaGrammar = CharMachineGrammar
 
 
 _COMPILED: dict = {}

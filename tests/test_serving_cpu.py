@@ -180,3 +180,10 @@ def test_json_schema_response_format_over_http(async_llm):
         r = c.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 8,
                                             "guided_json": {"type": "string", "pattern": "^a$"}})
         assert r.status_code >= 400
+        r = c.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 24,
+                                            "temperature": 0.9, "seed": 2,
+                                            "guided_regex": "[A-C]{2}-[0-9]{3}"})
+        import re
+        assert re.fullmatch("[A-C]{2}-[0-9]{3}", r.json()["choices"][0]["text"])
+        assert c.post("/v1/completions", json={"model": "m", "prompt": "x",
+                                               "guided_regex": "(unclosed"}).status_code == 400

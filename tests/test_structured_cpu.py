@@ -201,3 +201,48 @@ def test_engine_with_optional_fields_and_unions():
         assert all(t in ("x", "y") for t in doc.get("tags", [])) and len(doc.get("tags", [])) <= 3
         seen.add(tuple(sorted(doc)))
     assert len(seen) >= 1
+
+
+# ------------------------------------------------------------------------------------ regex
+REGEX_CASES = {
+    r"\d{3}-\d{4}": (["555-1234"], ["5555-123", "555-123", "a55-1234"]),
+    r"(yes|no|maybe)( please)?": (["yes", "no please", "maybe"], ["yes  please", "y", ""]),
+    r"[A-Z][a-z]+(, [A-Z][a-z]+)*\.": (["Hello.", "Hello, World."], ["hello.", "Hello,World."]),
+    r"^-?(0|[1-9]\d*)(\.\d+)?$": (["0", "-12.50", "7"], ["01", "1.", "--1"]),
+    r"[^abc\d]+x?": (["zzz", "qx"], ["a", "1", "zx1"]),
+    r"a{2,3}b*?c+": (["aac", "aaabbcc"], ["ac", "aaaac", "aab"]),
+    r"(?:ab)*": (["", "ab", "abab"], ["a", "aba"]),
+    r"\w+@\w+\.(com|org)": (["me@x.org"], ["me@x.net", "@x.com"]),
+}
+
+
+def test_regex_compiler_agrees_with_re():
+    import re
+    from arcticinference_b200.structured.regex import CompiledRegex
+    for pat, (good, bad) in REGEX_CASES.items():
+        c = CompiledRegex(pat)
+        for t in good:
+            assert re.fullmatch(pat, t) and c.validate(t), (pat, t)
+        for t in bad:
+            assert not re.fullmatch(pat, t) and not c.validate(t), (pat, t)
+    for pat in [r"(a", r"a)", r"*a", r"(?=a)b", r"a\1", r"[a", r"a{3,2}"]:
+        with pytest.raises(ValueError):
+            CompiledRegex(pat)
+    c = CompiledRegex(r"ab?")
+    st = c.advance_text(c.start(), "a")
+    assert c.complete(st) and not c.exhausted(st)
+    assert c.exhausted(c.advance_text(c.start(), "ab"))
+
+
+@pytest.mark.parametrize("spec", [None, {"method": "suffix"}])
+def test_engine_output_matches_the_expression(spec):
+    import re
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=256, num_gpu_blocks_override=64,
+              speculative_config=spec)
+    pat = r"(ID|REF)-\d{2,4}(/[a-f]{1,3})?"
+    prompts = [{"prompt_token_ids": list(range(15 + i, 45 + i))} for i in range(5)]
+    params = [SamplingParams(temperature=1.0 if i else 0.0, seed=i, max_tokens=40,
+                             guided_regex=pat) for i in range(5)]
+    for o in llm.generate(prompts, params):
+        assert re.fullmatch(pat, o.outputs[0].text), o.outputs[0].text
+        assert o.outputs[0].finish_reason == "stop"
