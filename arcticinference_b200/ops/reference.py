@@ -174,16 +174,19 @@ def gather_rows(src, idx):
 
 
 def argmax_sample(logits, temperature=None, seeds=None, index_offset=0):
-    """Greedy where temperature <= 0. (Sampling rows use torch's own generator on CPU.)"""
+    """Greedy where temperature <= 0; elsewhere one draw per row from softmax(logits / T) with
+    a generator seeded by that row's seed, so that a row's token does not depend on which
+    other rows share the batch (as with the per-row Gumbel noise of the CUDA kernel)."""
     ids = logits.float().argmax(-1)
     vals = logits.float().max(-1).values
     if temperature is not None and bool((temperature > 0).any()):
         t = temperature.clamp_min(1e-6).unsqueeze(-1)
-        probs = torch.softmax(logits.float() / t, -1)
-        g = torch.Generator(device="cpu")
-        g.manual_seed(int(seeds[0]) if seeds is not None else 0)
-        samp = torch.multinomial(probs.cpu(), 1, generator=g).squeeze(-1).to(ids.device)
-        ids = torch.where(temperature > 0, samp, ids)
+        probs = torch.softmax(logits.float() / t, -1).cpu()
+        ids = ids.clone()
+        for row in torch.nonzero(temperature.cpu() > 0).flatten().tolist():
+            g = torch.Generator(device="cpu")
+            g.manual_seed(int(seeds[row]) & 0x7FFFFFFFFFFFFFFF if seeds is not None else row)
+            ids[row] = torch.multinomial(probs[row], 1, generator=g)[0]
     return ids + index_offset, vals
 
 

@@ -123,3 +123,26 @@ def test_full_distribution_requests_do_not_run_ahead():
     b, _, llm = _run(True, sp, PROMPTS[:2])
     assert a == b
     assert llm.engine.stats["run_ahead_steps"] == 0
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_workloads_are_unchanged_by_run_ahead(seed):
+    """Random prompt lengths, output lengths, token budgets and cache sizes (small enough to
+    force chunking and, for some seeds, preemption): same tokens, same finish reasons, same
+    number of engine steps with and without run-ahead."""
+    import random
+    rng = random.Random(1234 + seed)
+    n = rng.randint(3, 9)
+    prompts = [[rng.randrange(3, 900) for _ in range(rng.randint(1, 120))] for _ in range(n)]
+    sp = [SamplingParams(temperature=0.0 if rng.random() < 0.7 else 0.8, seed=rng.randrange(100),
+                         max_tokens=rng.randint(1, 40), ignore_eos=rng.random() < 0.8)
+          for _ in range(n)]
+    kw = dict(max_num_batched_tokens=rng.choice([16, 48, 128, 512]),
+              max_num_seqs=rng.choice([2, 4, 16]),
+              enable_prefix_caching=rng.random() < 0.5)
+    blocks = rng.choice([20, 32, 256])
+    a, fa, ref = _run(False, sp, prompts, blocks=blocks, **kw)
+    b, fb, llm = _run(True, sp, prompts, blocks=blocks, **kw)
+    assert a == b and fa == fb, (kw, blocks)
+    assert llm.engine.stats["run_ahead_steps"] > 0
+    assert llm.engine.kv_manager.usage == ref.engine.kv_manager.usage
