@@ -358,7 +358,7 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, long long ld,
 // ------------------------- arg-max / Gumbel-max sample -----------------------
 // One block per row of logits [B, V] (bf16 or fp32). temperature <= 0: arg-max.
 // Otherwise token = argmax(logit / T + Gumbel noise), an exact softmax sample;
-// the noise comes from a counter-based hash of (seed, row, column).
+// the noise comes from a counter-based hash of (the row's seed, the token's global index).
 __device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned long long a,
                                               unsigned long long b) {
   unsigned long long z = seed + a * 0x9E3779B97F4A7C15ull + b * 0xBF58476D1CE4E5B9ull;
@@ -396,7 +396,10 @@ argmax_sample_kernel(const T* __restrict__ logits, long long ld, int V,
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     float v = load_logit<T>(lr, i);
     if (temp > 0.f) {
-      const float u = hash_uniform(seed, (unsigned long long)row, (unsigned long long)i);
+      // keyed by the row's seed and the token's index in the whole vocabulary only: a
+      // request draws the same token wherever its row sits in the batch, and the shards of
+      // a split vocabulary draw independent noise for their columns
+      const float u = hash_uniform(seed, 0ull, (unsigned long long)(index_offset + i));
       v = v / temp - __logf(-__logf(u));
     }
     if (v > best) {

@@ -100,6 +100,18 @@ def test_argmax_sample():
     freq = torch.bincount(s_ids, minlength=4).float() / 4000
     exp = torch.softmax(small[0], -1)
     assert float((freq - exp).abs().max()) < 0.04
+    # a row's draw depends on its logits and seed only, not on where it sits in the batch
+    lg = _rand(64, 5000, scale=2.0)
+    sd = torch.arange(64, device=DEV, dtype=torch.int64) * 104729 + 7
+    tt = torch.full((64,), 0.8, device=DEV)
+    base, _ = ops.argmax_sample(lg, temperature=tt, seeds=sd)
+    perm = torch.randperm(64, device=DEV)
+    moved, _ = ops.argmax_sample(lg[perm].contiguous(), temperature=tt, seeds=sd[perm].contiguous())
+    assert torch.equal(moved, base[perm])
+    # shards of a split vocabulary: the arg-max over the shards' winners is the full draw
+    lo, _ = ops.argmax_sample(lg[:, :2504].contiguous(), temperature=tt, seeds=sd)
+    hi, _ = ops.argmax_sample(lg[:, 2504:].contiguous(), temperature=tt, seeds=sd, index_offset=2504)
+    assert bool(((base == lo) | (base == hi)).all())
 
 
 def test_rope_cache():
