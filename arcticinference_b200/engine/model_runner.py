@@ -395,30 +395,34 @@ class ModelRunner:
     def execute(self, out: SchedulerOutput) -> StepResult:
         return self.finish(self.launch(out))
 
+    @staticmethod
+    def _source_rows(out: SchedulerOutput, prev: Optional["PendingStep"]):
+        """For every token of this step, the row of ``prev``'s sampled ids that holds it, or
+        -1: a request whose newest token is still a placeholder on the host takes it from the
+        previous step's device result. None when no token needs that."""
+        if prev is None or prev.ids_dev is None:
+            return None
+        src = np.full(out.total_tokens, -1, dtype=np.int64)
+        any_src, t = False, 0
+        for s in out.scheduled:
+            if s.num_tokens == 1 and s.request.token_at(s.start) == PLACEHOLDER_TOKEN:
+                j = prev.row_of.get(id(s.request), -1)
+                if j >= 0:
+                    src[t] = j
+                    any_src = True
+            t += s.num_tokens
+        return src if any_src else None
+
     @torch.inference_mode()
     def launch(self, out: SchedulerOutput, prev: Optional["PendingStep"] = None) -> "PendingStep":
         """Queue one step on the device without waiting for its tokens. ``prev`` is the step
         queued before this one whose tokens the host has not read yet: rows of this step that
         feed ``prev``'s sampled token (a placeholder on the host) are patched on the device."""
-        sched = out.scheduled
-        src_rows = None
-        if prev is not None and prev.ids_dev is not None:
-            # token offset of every request in this step -> row of its sampled token in prev
-            src = np.full(out.total_tokens, -1, dtype=np.int64)
-            any_src, t = False, 0
-            for s in sched:
-                if s.num_tokens == 1 and s.request.token_at(s.start) == PLACEHOLDER_TOKEN:
-                    j = prev.row_of.get(id(s.request), -1)
-                    if j >= 0:
-                        src[t] = j
-                        any_src = True
-                t += s.num_tokens
-            if any_src:
-                src_rows = src
         g = self._decode_graph(out)
         if g is not None:
             with trace_range("prepare"):
                 g.wait_uploaded()
+                src_rows = self._source_rows(out, prev)
                 rows = g.fill(out, src_rows)
             self.mode_counts[g.mode] += 1
             self.graph_replays += 1
@@ -430,6 +434,8 @@ class ModelRunner:
             with trace_range("prepare"):
                 batch, rows = self.prepare(out)
             self.mode_counts[batch.mode] += 1
+            # after prepare(): forest cascade may have put the requests in another order
+            src_rows = self._source_rows(out, prev)
             if src_rows is not None:
                 n = batch.input_ids.numel()
                 if n > src_rows.size:          # rows added to pad the step take no token
@@ -443,7 +449,7 @@ class ModelRunner:
                 hidden = self.model.forward(batch, self.kv)
             with trace_range("sample"):
                 logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
-                ids_dev = self._sample(logits, sched, rows)
+                ids_dev = self._sample(logits, out.scheduled, rows)
             pend = PendingStep(out, rows, ids_dev, hidden, batch.num_tokens, batch.mode)
         # the device result may be overwritten by the next replay of the same graph: take the
         # host copy now, read it in finish()
@@ -457,7 +463,7 @@ class ModelRunner:
             pend.event = torch.cuda.Event()
             pend.event.record()
             self._ids_flip ^= 1
-        pend.row_of = {id(s.request): rr[0] for s, rr in zip(sched, rows) if rr}
+        pend.row_of = {id(s.request): rr[0] for s, rr in zip(out.scheduled, rows) if rr}
         return pend
 
     @torch.inference_mode()
