@@ -297,6 +297,11 @@ class ModelRunner:
         else:
             meta = ops.build_attention_metadata(q_lens_a, kv_lens_a, bt_t, self.G, m.h, m.D, dev,
                                                 Hkv=m.hkv)
+        # the attention work list and split table are uploaded too
+        extra = sum(t.numel() * t.element_size() for t in (meta.work, meta.tok_splits)
+                    if t is not None)
+        self.h2d_bytes += extra
+        self.h2d_total += extra
         batch = ForwardBatch(input_ids=d[:Np], positions=d[Np:2 * Np], slots=d[2 * Np:3 * Np],
                              attn_meta=meta, logits_indices=d[3 * Np:3 * Np + n_sel],
                              num_tokens=Np, mode=mode)

@@ -6,7 +6,7 @@ JSON-mode benchmark (tests/benchmarks/json_mode/task_description.py:6-33: flat a
 pydantic models with string / number / list fields). This module covers that subset of JSON
 Schema natively: ``object`` (properties in declaration order; with a ``required`` list the
 other properties are optional), ``array`` (``items``, ``minItems``, ``maxItems``),
-``string`` (``maxLength``, ``enum``), ``integer``, ``number``, ``boolean``, ``null``,
+``string`` (``maxLength``, ``enum``, anchored ``pattern``), ``integer``, ``number``, ``boolean``, ``null``,
 ``enum`` / ``const`` of any JSON literals, ``anyOf`` / ``oneOf`` / lists of types, and
 ``$ref`` into ``$defs`` / ``definitions``. Output is compact JSON (no white space).
 
@@ -30,7 +30,8 @@ _ESCAPES = '"\\/bfnrt'
 
 # ---------------------------------------------------------------------------- compilation
 class _Node:
-    """kind: lit | str | int | num | trie | seq | arr | alt"""
+    """kind: lit | str | re | int | num | trie | seq | arr | alt (``re``: a string whose
+    characters match a regular expression; its machine sits in the ``trie`` slot)"""
     __slots__ = ("kind", "text", "max_len", "trie", "children", "item", "min_items", "max_items")
 
     def __init__(self, kind, **kw):
@@ -100,7 +101,15 @@ class CompiledSchema:
             return self._alt([self._compile(dict(rest, type=one), depth + 1) for one in t])
         if t == "string":
             if "pattern" in sch:
-                raise ValueError("string patterns are not supported")
+                # the pattern constrains the raw characters between the quotes; characters
+                # that would need escaping in JSON are never allowed there
+                from .regex import compile_regex
+                pat = sch["pattern"]
+                if not (pat.startswith("^") and pat.endswith("$")):
+                    raise ValueError("string patterns must be anchored (^...$): an unanchored "
+                                     "pattern constrains nothing a grammar can enforce")
+                return self._add(_Node("re", text=pat, trie=compile_regex(pat),
+                                       max_len=sch.get("maxLength")))
             return self._add(_Node("str", max_len=sch.get("maxLength")))
         if t == "integer":
             return self._add(_Node("int"))
@@ -153,6 +162,8 @@ class CompiledSchema:
         n = self.nodes[nid]
         if n.kind == "trie":
             return (nid, (), 0)            # a = path of characters into the trie
+        if n.kind == "re":
+            return (nid, None, 0)          # a = set of NFA states (None before the quote)
         return (nid, 0, 0)
 
     def _trie_at(self, n: _Node, path: tuple) -> dict:
@@ -169,6 +180,8 @@ class CompiledSchema:
         if k == "lit":
             return a == len(n.text)
         if k == "str":
+            return a == 9
+        if k == "re":
             return a == 9
         if k == "int":
             return a in (2, 3)
@@ -197,6 +210,20 @@ class CompiledSchema:
             if ch in node:
                 return ((nid, a + (ch,), 0),)
             return None
+        if k == "re":
+            rx = n.trie
+            if a is None:
+                return ((nid, rx.start(), 0),) if ch == '"' else None
+            if a == 9:
+                return None
+            if ch == '"':
+                return ((nid, 9, b),) if rx.complete(a) else None
+            if ch == "\\" or ord(ch) < 0x20 or (n.max_len is not None and b >= n.max_len):
+                return None
+            nxt = rx.advance(a, ch)
+            if nxt is None:
+                return None
+            return ((nid, nxt, b + 1 if n.max_len is not None else 0),)
         if k == "str":
             # a: 0 before the opening quote, 1 inside, 2 after a backslash, 3..6 the four hex
             # digits of \uXXXX, 9 closed; b counts characters when maxLength is set
@@ -334,7 +361,7 @@ class CompiledSchema:
         k = n.kind
         if k == "lit":
             return a == len(n.text)
-        if k in ("str", "arr"):
+        if k in ("str", "arr", "re"):
             return a == 9
         if k == "seq":
             return a == len(n.children)

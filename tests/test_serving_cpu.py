@@ -178,7 +178,7 @@ def test_json_schema_response_format_over_http(async_llm):
                                             "guided_json": schema})
         assert set(json.loads(r.json()["choices"][0]["text"])) == {"answer", "unit"}
         r = c.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 8,
-                                            "guided_json": {"type": "string", "pattern": "^a$"}})
+                                            "guided_json": {"type": "string", "pattern": "a"}})
         assert r.status_code >= 400
         r = c.post("/v1/completions", json={"model": "m", "prompt": "x", "max_tokens": 24,
                                             "temperature": 0.9, "seed": 2,

@@ -132,7 +132,7 @@ def test_schema_matcher_accepts_and_rejects():
     for b in bad:
         assert not c.validate(b), b
     with pytest.raises(ValueError):
-        CompiledSchema({"type": "string", "pattern": "^a+$"})
+        CompiledSchema({"type": "string", "pattern": "a+"})       # not anchored
 
 
 def test_schema_grammar_on_tokens_with_rollback():
@@ -246,3 +246,24 @@ def test_engine_output_matches_the_expression(spec):
     for o in llm.generate(prompts, params):
         assert re.fullmatch(pat, o.outputs[0].text), o.outputs[0].text
         assert o.outputs[0].finish_reason == "stop"
+
+
+def test_string_patterns_inside_a_schema():
+    import json
+    from arcticinference_b200.structured.json_schema import CompiledSchema
+    schema = {"type": "object", "properties": {
+        "id": {"type": "string", "pattern": "^[A-Z]{2}-\\d{3}$"},
+        "date": {"type": "string", "pattern": "^\\d{4}-\\d{2}-\\d{2}$"}}}
+    c = CompiledSchema(schema)
+    assert c.validate('{"id":"AB-123","date":"2024-01-31"}')
+    for t in ['{"id":"AB-12","date":"2024-01-31"}', '{"id":"ab-123","date":"2024-01-31"}',
+              '{"id":"AB-123","date":"2024-1-31"}']:
+        assert not c.validate(t), t
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=256, num_gpu_blocks_override=64)
+    outs = llm.generate([{"prompt_token_ids": list(range(9, 40))}] * 3,
+                        [SamplingParams(temperature=1.0, seed=i, max_tokens=60, guided_json=schema)
+                         for i in range(3)])
+    import re
+    for o in outs:
+        doc = json.loads(o.outputs[0].text)
+        assert re.fullmatch(r"[A-Z]{2}-\d{3}", doc["id"]) and re.fullmatch(r"\d{4}-\d{2}-\d{2}", doc["date"])
