@@ -81,3 +81,43 @@ def test_pipeline_layer_ranges_cover_all_layers(layers, pp):
     assert max(sizes) - min(sizes) <= 1
     if pp > 1 and layers % pp:
         assert sizes[-1] == min(sizes)      # the stage with the LM head takes no surplus
+
+
+def _group_worker(rank, world, port, q):
+    import os
+    import torch
+    import torch.distributed as dist
+    from arcticinference_b200.parallel.layout import RankLayout, create_groups
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    lay = RankLayout(tp=2, sp=2, world_size=world)
+    groups = create_groups(lay, rank, backend="gloo")
+    got = {}
+    for name in ("tp", "sp", "sp_tp"):
+        g, ranks = groups[name]
+        t = torch.tensor([1 << rank])
+        dist.all_reduce(t, group=g)
+        got[name] = (int(t), ranks)
+    q.put((rank, got))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_process_groups_are_created_as_enumerated():
+    import torch.multiprocessing as mp
+    from _mp_util import free_port
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_group_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(4))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, got in res.items():
+        for name, (mask, ranks) in got.items():
+            assert rank in ranks and mask == sum(1 << r for r in ranks), (rank, name, mask, ranks)
+    assert res[0]["tp"][1] == [0, 1] and res[0]["sp"][1] == [0, 2]
+    assert res[3]["sp_tp"][1] == [0, 2, 1, 3]
