@@ -1,0 +1,28 @@
+"""The benchmark scripts run end to end on the CPU path with a tiny model."""
+
+import importlib.util
+import os
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load(name):
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "benchmarks", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_latency_bench_reports_ttft_and_tpot():
+    res = _load("latency_bench").main(["--model", "llama-tiny", "--quantization", "none",
+                                       "--num-prompts", "2", "--warmup", "1", "--input-len", "30",
+                                       "--output-len", "6", "--device", "cpu"])
+    assert res["task"] == "single" and res["num_prompts"] == 2
+    assert res["mean_ttft_ms"] > 0 and res["mean_tpot_ms"] > 0 and res["output_tokens_per_s"] > 0
+
+
+def test_json_mode_eval_documents_conform():
+    res = _load("json_mode_eval").main(["--in-process", "llama-tiny", "--num-questions", "1",
+                                        "--max-tokens", "700", "--engine-arg", "device=cpu",
+                                        "--engine-arg", "max_model_len=1024"])
+    assert res["documents"] == 5 and res["parse_rate"] == 1.0 and res["conformance_rate"] == 1.0
