@@ -85,44 +85,67 @@ def _suffix_draft(runner, req, cfg):
 
 def propose_drafts(runner, sched, rows, new_tokens: dict, hidden: torch.Tensor,
                    accepted_rows: list) -> dict:
+    """Drafts for the next step. The speculator's heads are queued on the GPU first and their
+    tokens start their way to pinned host memory; the suffix trees are then searched on the
+    CPU while the GPU drafts, and only after that does the host wait for the speculator's
+    tokens (the reference overlaps the same two with a copy stream:
+    arctic_inference/vllm/model_runner.py:1323-1628, its mode "B"). Per request the suffix
+    draft wins when its score reaches the speculator's draft length, else the speculator's
+    draft is used (model_runner.py:1008-1023)."""
     cfg = runner.config.speculative
     reqs = [s.request for s in sched if s.samples]
     drafts: dict = {}
     if not reqs:
         return drafts
     arctic = None
+    arctic_dev = arctic_host = arctic_event = None
     if runner.proposer is not None:
         n_predict = cfg.num_speculative_tokens or runner.proposer.n_predict
         idx = torch.tensor(accepted_rows, dtype=torch.int64, device=hidden.device)
         tok = torch.tensor([new_tokens[r.request_id][-1] for r in reqs], dtype=torch.int64,
                            device=hidden.device)
         h = ops.gather_rows(hidden, idx) if hidden.is_cuda else hidden[idx]
-        arctic = runner.proposer.propose(h, tok, n_predict).tolist()
+        arctic_dev = runner.proposer.propose(h, tok, n_predict)
+        if arctic_dev.is_cuda:
+            arctic_host = torch.empty(arctic_dev.shape, dtype=arctic_dev.dtype, pin_memory=True)
+            arctic_host.copy_(arctic_dev, non_blocking=True)
+            arctic_event = torch.cuda.Event()
+            arctic_event.record()
         runner.d2h_total += len(reqs) * n_predict * 8
+
+    # suffix search on the CPU (while the GPU drafts)
+    suffix: list = [None] * len(reqs)
+    if runner.suffix_cache is not None:
+        for i, req in enumerate(reqs):
+            if req.status.finished:
+                continue
+            # tokens of this step are not in req.output_token_ids yet: look one step ahead
+            saved = req.output_token_ids
+            req.output_token_ids = saved + new_tokens[req.request_id]
+            try:
+                suffix[i] = _suffix_draft(runner, req, cfg)
+            finally:
+                req.output_token_ids = saved
+
+    if arctic_dev is not None:
+        if arctic_event is not None:
+            arctic_event.synchronize()
+            arctic = arctic_host.tolist()
+        else:
+            arctic = arctic_dev.tolist()
+
+    threshold = (cfg.num_speculative_tokens or 0) if arctic is not None else 0
     for i, req in enumerate(reqs):
         if req.status.finished:
             continue
-        # tokens of this step are not in req.output_token_ids yet: look one step ahead
-        pending = new_tokens[req.request_id]
-        saved = req.output_token_ids
-        req.output_token_ids = saved + pending
-        try:
-            d = None
-            if runner.suffix_cache is not None:
-                sd = _suffix_draft(runner, req, cfg)
-                threshold = (cfg.num_speculative_tokens or 0) if arctic is not None else 0
-                if sd is not None and sd.token_ids and sd.score >= threshold:
-                    d = [int(t) for t in sd.token_ids]
-                    runner.spec_stats["suffix_drafts"] += 1
-            if d is None and arctic is not None:
-                d = arctic[i]
-                runner.spec_stats["arctic_drafts"] += 1
-        finally:
-            req.output_token_ids = saved
-            if runner.suffix_cache is not None and hasattr(req, "_suffix_seen"):
-                # the look-ahead tokens were added to the trees; they become permanent once the
-                # scheduler appends them, so only the bookkeeping index stays as is
-                pass
+        d = None
+        sd = suffix[i]
+        if sd is not None and sd.token_ids and sd.score >= threshold:
+            d = [int(t) for t in sd.token_ids]
+            runner.spec_stats["suffix_drafts"] += 1
+        if d is None and arctic is not None:
+            d = arctic[i]
+            runner.spec_stats["arctic_drafts"] += 1
         if d:
             drafts[req.request_id] = d
             runner.spec_stats["draft_tokens"] += len(d)
