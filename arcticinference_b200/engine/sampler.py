@@ -7,6 +7,7 @@ is framework-level PyTorch on the gathered logits."""
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 
@@ -38,8 +39,8 @@ def apply_grammar_masks(lf: torch.Tensor, sched, rows) -> torch.Tensor:
                 continue
             if out is lf:
                 out = lf.clone()
-            keep = torch.as_tensor(sorted(t for t in allowed if 0 <= t < lf.shape[-1]),
-                                   dtype=torch.int64, device=lf.device)
+            keep = np.asarray(allowed, dtype=np.int64)
+            keep = torch.from_numpy(keep[(keep >= 0) & (keep < lf.shape[-1])]).to(lf.device)
             masked = torch.full_like(out[row], float("-inf"))
             if keep.numel():
                 masked[keep] = out[row, keep]

@@ -21,8 +21,11 @@ from __future__ import annotations
 import json
 from typing import Optional, Sequence
 
+import numpy as np
+
 from . import Grammar
 
+_MAX_CACHED_STATES = 1024
 _DIGITS = "0123456789"
 _HEX = "0123456789abcdefABCDEF"
 _ESCAPES = '"\\/bfnrt'
@@ -452,23 +455,28 @@ class CharMachineGrammar(Grammar):
         return self._ended or self.c.exhausted(self.state)
 
     def allowed(self):
+        """Allowed token ids as an int64 array (shared with the cache: do not modify)."""
         if self.finished:
-            return [self.eos] if self.eos is not None else []
+            return np.asarray([self.eos] if self.eos is not None else [], dtype=np.int64)
         st = self.state
         key = (self.v.uid, st)
-        toks = self.c.allowed_cache.get(key)
+        cache = self.c.allowed_cache
+        toks = cache.get(key)
         if toks is None:
-            toks = []
-            for first, ids in self.v.by_first.items():
+            ids = []
+            for first, tids in self.v.by_first.items():
                 if self.c.advance(st, first) is None:
                     continue
-                for tid in ids:
+                for tid in tids:
                     s = self.v.strings[tid]
                     if len(s) == 1 or self.c.advance_text(st, s) is not None:
-                        toks.append(tid)
-            self.c.allowed_cache[key] = toks
+                        ids.append(tid)
+            toks = np.asarray(sorted(ids), dtype=np.int64)
+            if len(cache) >= _MAX_CACHED_STATES:
+                cache.clear()       # bounded: a state's list can be as long as the vocabulary
+            cache[key] = toks
         if self.eos is not None and self.c.complete(st):
-            return toks + [self.eos]
+            return np.append(toks, self.eos)
         return toks
 
     def accept(self, token: int) -> bool:
