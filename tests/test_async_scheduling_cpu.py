@@ -146,3 +146,28 @@ def test_random_workloads_are_unchanged_by_run_ahead(seed):
     assert a == b and fa == fb, (kw, blocks)
     assert llm.engine.stats["run_ahead_steps"] > 0
     assert llm.engine.kv_manager.usage == ref.engine.kv_manager.usage
+
+
+def test_streaming_with_chunked_prompts_and_arrivals_mid_prefill():
+    prompts = [list(range(10, 130)), [3, 4, 5], list(range(200, 290)), [8] * 50]
+    sp = SamplingParams(temperature=0.0, max_tokens=18, ignore_eos=True)
+    want, _, _ = _run(False, sp, prompts, max_num_batched_tokens=32)
+
+    async def main():
+        llm = AsyncLLM.from_engine_args(
+            EngineArgs(async_scheduling=True, num_gpu_blocks_override=256, max_num_batched_tokens=32,
+                       **{k: v for k, v in KW.items() if k != "device"}), device="cpu").start()
+        try:
+            async def one(p, delay):
+                await asyncio.sleep(delay)
+                last = None
+                async for out in llm.generate(p, sp):
+                    assert -1 not in out.outputs[0].token_ids
+                    last = out
+                return last.outputs[0].token_ids
+            res = await asyncio.gather(*[one(p, 0.01 * i) for i, p in enumerate(prompts)])
+            assert [[r] for r in res] == want
+            assert llm.engine.stats["run_ahead_steps"] > 10
+        finally:
+            llm.shutdown()
+    asyncio.run(main())
