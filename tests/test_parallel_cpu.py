@@ -106,3 +106,53 @@ def test_parallel_modes_match_single_rank(tp, sp, shift, model):
         assert a.shape == b.shape
         err = (a - b).abs().max().item()
         assert err < 0.05 * max(1.0, b.abs().max().item()), (err, modes)
+
+
+def _generate_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    sys.path.insert(0, ROOT)
+    torch.set_num_threads(1)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from arcticinference_b200 import LLM, SamplingParams
+    from arcticinference_b200.parallel.comm import Communicator
+    comm = Communicator(1, world, None)
+    prompts = [list(range(3, 100)), [9, 8, 7, 6, 5], list(range(100, 160)), [4] * 33]
+    sp = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in (10, 25, 1, 14)]
+    res = []
+    for async_on in (False, True):
+        llm = LLM(model="llama-tiny", device="cpu", comm=comm, num_gpu_blocks_override=64,
+                  block_size=16, max_model_len=512, ulysses_sequence_parallel_size=world,
+                  enable_shift_parallel=True, shift_parallel_threshold=8,
+                  max_num_batched_tokens=40, async_scheduling=async_on)
+        outs = llm.generate(prompts, sp)
+        res.append(([o.outputs[0].token_ids for o in outs], llm.engine.stats["run_ahead_steps"],
+                    dict(llm.engine.runner.mode_counts)))
+    every = [None] * world
+    dist.all_gather_object(every, res[1][0])
+    if rank == 0:
+        q.put((res, every))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_run_ahead_on_two_ranks_with_chunked_prompts_and_mode_shifts():
+    """Both ranks schedule on their own (SPMD): with run-ahead stepping, chunked prompts and
+    shifts between the two modes they must still agree with each other and with synchronous
+    stepping."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_generate_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res, every = _result_or_child_failure(q, procs, 300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    (sync_tokens, sync_ahead, _), (async_tokens, async_ahead, modes) = res
+    assert sync_tokens == async_tokens
+    assert sync_ahead == 0 and async_ahead > 10
+    assert modes["sp"] > 0 and modes["tp"] > 0
+    assert all(e == async_tokens for e in every)
