@@ -26,3 +26,10 @@ def test_json_mode_eval_documents_conform():
                                         "--max-tokens", "700", "--engine-arg", "device=cpu",
                                         "--engine-arg", "max_model_len=1024"])
     assert res["documents"] == 5 and res["parse_rate"] == 1.0 and res["conformance_rate"] == 1.0
+
+
+def test_prefill_comparison_script_single_process():
+    res = _load("prefill_sp_vs_tp").main(["--mode", "sp", "--model", "llama-tiny", "--num-prompts", "2",
+                                          "--input-len", "24", "--iters", "2", "--warmup", "1",
+                                          "--device", "cpu"])
+    assert res["mode"] == "single" and res["prefill_tokens_per_s"] > 0
