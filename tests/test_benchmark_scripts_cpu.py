@@ -33,3 +33,17 @@ def test_prefill_comparison_script_single_process():
                                           "--input-len", "24", "--iters", "2", "--warmup", "1",
                                           "--device", "cpu"])
     assert res["mode"] == "single" and res["prefill_tokens_per_s"] > 0
+
+
+def test_serving_suite_starts_a_server_and_runs_tasks(tmp_path):
+    import random
+    port = random.randrange(20000, 28000)
+    res = _load("serving_suite").main([
+        "--model", "llama-tiny", "--quantization", "none", "--device", "cpu", "--configs", "baseline",
+        "--tasks", "batch,single", "--num-prompts", "4", "--single-prompts", "2", "--input-len", "30",
+        "--output-len", "6", "--vocab-size", "1000", "--port", str(port), "--ready-timeout", "120",
+        "--log-dir", str(tmp_path)])
+    row = res["baseline"]
+    assert "error" not in row, row
+    assert row["batch"]["completed"] == 4 and row["batch"]["total_token_throughput"] > 0
+    assert row["single"]["mean_ttft_ms"] > 0 and row["single"]["failed"] == 0
