@@ -267,3 +267,121 @@ def test_string_patterns_inside_a_schema():
     for o in outs:
         doc = json.loads(o.outputs[0].text)
         assert re.fullmatch(r"[A-Z]{2}-\d{3}", doc["id"]) and re.fullmatch(r"\d{4}-\d{2}-\d{2}", doc["date"])
+
+
+# ------------------------------------------------------------------ randomised schema check
+def _random_schema(rng, depth=0):
+    kinds = ["string", "integer", "number", "boolean", "null", "enum", "union"]
+    if depth < 2:
+        kinds += ["array", "object", "object"]
+    k = rng.choice(kinds)
+    if k == "string":
+        return {"type": "string", "maxLength": rng.randint(0, 6)} if rng.random() < 0.7 else {"type": "string"}
+    if k in ("integer", "number", "boolean", "null"):
+        return {"type": k}
+    if k == "enum":
+        pool = ["a", "b c", 1, 2.5, True, None, 'q"uote']
+        return {"enum": rng.sample(pool, rng.randint(1, 4))}
+    if k == "union":
+        return {"anyOf": [_random_schema(rng, depth + 1) for _ in range(rng.randint(2, 3))]}
+    if k == "array":
+        lo = rng.randint(0, 2)
+        return {"type": "array", "items": _random_schema(rng, depth + 1), "minItems": lo,
+                "maxItems": lo + rng.randint(0, 2)}
+    names = rng.sample(["a", "b", "c", "d", "key with space"], rng.randint(1, 4))
+    sch = {"type": "object", "properties": {n: _random_schema(rng, depth + 1) for n in names}}
+    if rng.random() < 0.6:
+        sch["required"] = [n for n in names if rng.random() < 0.5]
+    return sch
+
+
+def _random_instance(rng, sch):
+    if "enum" in sch:
+        return rng.choice(sch["enum"])
+    if "anyOf" in sch:
+        return _random_instance(rng, rng.choice(sch["anyOf"]))
+    t = sch["type"]
+    if t == "string":
+        n = rng.randint(0, sch.get("maxLength", 8))
+        return "".join(rng.choice('ab "\\/é\n7') for _ in range(n))
+    if t == "integer":
+        return rng.choice([0, 7, -13, 123456789])
+    if t == "number":
+        return rng.choice([0, -1.5, 2.25e10, 3, 1e-7])
+    if t == "boolean":
+        return rng.random() < 0.5
+    if t == "null":
+        return None
+    if t == "array":
+        return [_random_instance(rng, sch["items"])
+                for _ in range(rng.randint(sch["minItems"], sch["maxItems"]))]
+    req = set(sch.get("required", sch["properties"]))
+    return {n: _random_instance(rng, s) for n, s in sch["properties"].items()
+            if n in req or rng.random() < 0.5}
+
+
+def test_random_schemas_accept_their_instances_and_reject_damage():
+    import json
+    import random
+    from arcticinference_b200.structured.json_schema import CompiledSchema
+    rng = random.Random(5)
+    rejected = damaged = 0
+    for _ in range(150):
+        sch = _random_schema(rng)
+        c = CompiledSchema(sch)
+        for _ in range(4):
+            doc = _random_instance(rng, sch)
+            text = json.dumps(doc, separators=(",", ":"), ensure_ascii=rng.random() < 0.5)
+            assert c.validate(text), (sch, text)
+            # every proper prefix is a live state, and only whole documents are complete
+            st = c.start()
+            for ch in text[:-1]:
+                st = c.advance(st, ch)
+                assert st is not None, (sch, text)
+            # damage: drop or double one structural character
+            if len(text) > 1:
+                i = rng.randrange(len(text))
+                bad = text[:i] + text[i + 1:] if rng.random() < 0.5 else text[:i] + text[i] + text[i:]
+                try:
+                    same = json.loads(bad) == doc
+                except ValueError:
+                    same = False
+                if not same and not c.validate(bad):
+                    rejected += 1
+                damaged += not same
+    assert damaged > 100 and rejected > 0.5 * damaged     # most damaged texts are refused
+
+
+def _random_regex(rng, depth=0):
+    atoms = ["a", "b", "c", r"\d", r"\w", ".", "[ab]", "[^a]", "[a-c0-2]", r"\."]
+    def atom():
+        if depth < 2 and rng.random() < 0.3:
+            return "(" + _random_regex(rng, depth + 1) + ")"
+        return rng.choice(atoms)
+    parts = []
+    for _ in range(rng.randint(1, 4)):
+        a = atom()
+        q = rng.choice(["", "", "", "?", "*", "+", "{2}", "{1,2}", "{0,3}"])
+        parts.append(a + q)
+    body = "".join(parts)
+    if depth < 2 and rng.random() < 0.3:
+        body += "|" + _random_regex(rng, depth + 1)
+    return body
+
+
+def test_random_regexes_agree_with_re_on_random_strings():
+    import random
+    import re
+    from arcticinference_b200.structured.regex import CompiledRegex
+    rng = random.Random(11)
+    checked = matched = 0
+    for _ in range(200):
+        pat = _random_regex(rng)
+        c = CompiledRegex(pat)
+        for _ in range(25):
+            s = "".join(rng.choice("abc01. x") for _ in range(rng.randint(0, 7)))
+            want = re.fullmatch(pat, s) is not None
+            assert c.validate(s) == want, (pat, s, want)
+            checked += 1
+            matched += want
+    assert checked == 5000 and matched > 100
