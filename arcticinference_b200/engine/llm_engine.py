@@ -62,6 +62,12 @@ class LLMEngine:
         self.sleeping_level = 0
         self.stats = {"prompt_tokens": 0, "generation_tokens": 0, "steps": 0,
                       "draft_tokens": 0, "accepted_tokens": 0, "run_ahead_steps": 0,
+                      # speculation by draft position: how often position i was drafted /
+                      # accepted (drafts vary in width from request to request and step to
+                      # step; reference: arctic_inference/vllm/stats.py:25-67)
+                      "drafted_per_position": [], "accepted_per_position": [],
+                      # steps per execution mode and device-side wait limits that ran out
+                      "sp_steps": 0, "tp_steps": 0, "comm_timeouts": 0,
                       # host seconds per phase: scheduling, building + queueing a step, waiting
                       # for its tokens (the only phase the device is waited for), bookkeeping
                       "t_schedule": 0.0, "t_launch": 0.0, "t_wait": 0.0, "t_update": 0.0}
@@ -199,6 +205,15 @@ class LLMEngine:
                                                    s.request.num_prompt_tokens - s.start)
             if s.num_draft:
                 self.stats["draft_tokens"] += s.num_draft
+                acc = len(result.new_tokens.get(s.request.request_id, [None])) - 1
+                for name, n in (("drafted_per_position", s.num_draft),
+                                ("accepted_per_position", acc)):
+                    hist = self.stats[name]
+                    if len(hist) < n:
+                        hist.extend([0] * (n - len(hist)))
+                    for i in range(n):
+                        hist[i] += 1
+        self.stats["sp_steps" if result.mode == "sp" else "tp_steps"] += 1
         for toks in result.new_tokens.values():
             self.stats["generation_tokens"] += len(toks)
             self.stats["accepted_tokens"] += len(toks) - 1
@@ -224,6 +239,9 @@ class LLMEngine:
     def get_stats(self) -> dict:
         """Load figures a router needs: queue lengths and KV-cache utilisation."""
         d = dict(self.stats)
+        if self.device.type == "cuda":
+            from ..ops import native
+            d["comm_timeouts"] = native.timeout_count()
         d.update(running=len(self.scheduler.running), waiting=len(self.scheduler.waiting),
                  kv_cache_usage=float(self.kv_manager.usage), num_blocks=self.num_blocks,
                  sleeping_level=self.sleeping_level)

@@ -193,6 +193,19 @@ def build_app(llm: AsyncLLM, served_model_name: Optional[str] = None) -> FastAPI
             lines.append("# HELP arctic_%s %s" % (key, help_))
             lines.append("# TYPE arctic_%s %s" % (key, typ))
             lines.append('arctic_%s{model_name="%s"} %s' % (key, name, s.get(key, 0)))
+        for key, help_ in (("drafted_per_position", "drafts that reached this position"),
+                           ("accepted_per_position", "drafts accepted at this position")):
+            lines.append("# HELP arctic_%s %s" % (key, help_))
+            lines.append("# TYPE arctic_%s counter" % key)
+            for i, v in enumerate(s.get(key, [])):
+                lines.append('arctic_%s{model_name="%s",position="%d"} %s' % (key, name, i, v))
+        for key, help_ in (("sp_steps", "steps run in sequence-parallel mode"),
+                           ("tp_steps", "steps run in tensor-parallel mode"),
+                           ("run_ahead_steps", "steps queued while their predecessor ran"),
+                           ("comm_timeouts", "device-side waits that ran out")):
+            lines.append("# HELP arctic_%s %s" % (key, help_))
+            lines.append("# TYPE arctic_%s counter" % key)
+            lines.append('arctic_%s{model_name="%s"} %s' % (key, name, s.get(key, 0)))
         return PlainTextResponse("\n".join(lines) + "\n")
 
     @app.post("/tokenize")

@@ -117,6 +117,14 @@ _CODES = {1: "mbarrier wait timed out", 2: "peer flag wait timed out",
           3: "index check failed", 4: "bad argument"}
 
 
+_timeouts = 0
+
+
+def timeout_count() -> int:
+    """How many times ``check_status`` has found a device-side wait that ran out."""
+    return _timeouts
+
+
 def check_status(device=None, reset: bool = True) -> None:
     """Synchronise and raise if any kernel on ``device`` recorded an error."""
     buf = status_buffer(device)
@@ -127,6 +135,8 @@ def check_status(device=None, reset: bool = True) -> None:
         msg = "%s (code %d, block %d, detail %d/%d)" % (
             _CODES.get(vals[0], "unknown"), vals[0], vals[1], vals[2], vals[3])
         if vals[0] in (1, 2):
+            global _timeouts
+            _timeouts += 1
             raise KernelTimeout(msg)
         raise KernelError(msg)
 

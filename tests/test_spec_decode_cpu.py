@@ -89,3 +89,21 @@ def test_fp8_speculator_keeps_outputs(baseline):
     llm.sleep(2)
     llm.wake_up()
     assert _tokens(llm.generate(PROMPTS, SP)) == baseline
+
+
+def test_acceptance_histogram_by_position():
+    """Drafts vary in width; the engine counts, per draft position, how often it was drafted
+    and how often accepted (accepted counts never exceed drafted counts and never grow with
+    the position)."""
+    from arcticinference_b200 import LLM, SamplingParams
+    llm = LLM(model="llama-tiny", device="cpu", max_model_len=256, num_gpu_blocks_override=64,
+              speculative_config={"method": "suffix"})
+    prompts = [{"prompt_token_ids": [5, 6, 7, 8] * 12}, {"prompt_token_ids": list(range(9, 60))}]
+    llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+    st = llm.engine.get_stats()
+    drafted, accepted = st["drafted_per_position"], st["accepted_per_position"]
+    assert drafted and sum(drafted) == st["draft_tokens"]
+    assert sum(accepted) == st["accepted_tokens"]
+    assert all(a <= d for a, d in zip(accepted, drafted))
+    assert all(x >= y for x, y in zip(accepted, accepted[1:]))
+    assert st["tp_steps"] == st["steps"] and st["sp_steps"] == 0
