@@ -194,7 +194,22 @@ class LLMEngine:
         t0 = time.perf_counter()
         result = self.runner.finish(pend)
         t1 = time.perf_counter()
+        before = None
+        if result.logprobs:
+            before = {s.request.request_id: len(s.request.output_token_ids)
+                      for s in out.scheduled if s.request.request_id in result.logprobs}
         finished = self.scheduler.update_from_output(out, result.new_tokens, result.drafts)
+        if before:
+            for s in out.scheduled:
+                req = s.request
+                if req.request_id not in before:
+                    continue
+                n = len(req.output_token_ids) - before[req.request_id]   # a stop may cut the step short
+                lps, tops = result.logprobs[req.request_id]
+                if req.output_logprobs is None:
+                    req.output_logprobs, req.output_top_logprobs = [], []
+                req.output_logprobs.extend(lps[:n])
+                req.output_top_logprobs.extend(tops[:n])
         self.stats["t_wait"] += t1 - t0
         self.stats["t_update"] += time.perf_counter() - t1
         self.step_count += 1
@@ -250,8 +265,11 @@ class LLMEngine:
     def _completion(self, req: Request) -> CompletionOutput:
         text = self.tokenizer.decode(req.output_token_ids,
                                      skip_special_tokens=req.sampling_params.skip_special_tokens)
+        lps = req.output_logprobs
         return CompletionOutput(req.sample_index, text, list(req.output_token_ids),
-                                req.finish_reason, req.output_logprobs)
+                                req.finish_reason, list(lps) if lps is not None else None,
+                                sum(lps) if lps else None,
+                                list(req.output_top_logprobs) if lps is not None else None)
 
     def _finalize(self, req: Request) -> Optional[RequestOutput]:
         comp = self._completion(req)

@@ -79,7 +79,7 @@ class PendingStep:
     """A step that has been queued on the device."""
 
     __slots__ = ("out", "rows", "ids_dev", "hidden", "num_tokens", "mode", "ids_host", "event",
-                 "row_of")
+                 "row_of", "logprobs")
 
     def __init__(self, out, rows, ids_dev, hidden, num_tokens, mode):
         self.out, self.rows, self.ids_dev, self.hidden = out, rows, ids_dev, hidden
@@ -87,6 +87,7 @@ class PendingStep:
         self.ids_host = None
         self.event = None
         self.row_of = {}
+        self.logprobs = None      # (chosen [rows], top values [rows, k], top ids [rows, k])
 
 
 @dataclass
@@ -95,6 +96,9 @@ class StepResult:
     drafts: dict              # request_id -> list[int] proposals for the next step
     num_tokens: int
     mode: str
+    # request_id -> (log-probabilities of its new tokens, their top alternatives), for the
+    # requests that asked for log-probabilities
+    logprobs: Optional[dict] = None
 
 
 def _pinned(n, dtype, device):
@@ -139,6 +143,7 @@ class ModelRunner:
         self.mode_counts = {"sp": 0, "tp": 0}
         self.step_timer_events = None
         self.sync_seconds = 0.0       # host time spent blocked on the device for sampled tokens
+        self._step_logprobs = None
 
     # ------------------------------------------------------------------ set-up
     def load_model(self) -> None:
@@ -348,8 +353,14 @@ class ModelRunner:
         # full-distribution path (top-p / top-k / logprobs): framework-level torch ops
         if sharded:
             logits = comm.gather_vocab(logits, self.config.model.vocab_size)
-        from .sampler import sample_full
-        return sample_full(logits, sched, rows)
+        from .sampler import compute_logprobs, sample_full
+        ids = sample_full(logits, sched, rows)
+        k = max((s.request.sampling_params.logprobs or 0 for s in sched
+                 if s.samples and s.request.sampling_params.logprobs is not None), default=None)
+        if k is not None:
+            # of the distribution the model put out (before temperature, truncation, grammar)
+            self._step_logprobs = compute_logprobs(logits, ids, k)
+        return ids
 
     # ------------------------------------------------------------- CUDA graphs
     def graph_pool(self):
@@ -399,6 +410,14 @@ class ModelRunner:
     # ------------------------------------------------------------------- step
     def execute(self, out: SchedulerOutput) -> StepResult:
         return self.finish(self.launch(out))
+
+    @staticmethod
+    def _logprob_entries(lp_rows, rows, req):
+        """(log-probabilities, top alternatives) of the tokens sampled at ``rows``."""
+        chosen, topv, topi = lp_rows
+        k = req.sampling_params.logprobs or 0
+        return ([chosen[j] for j in rows],
+                [dict(zip(topi[j][:k], topv[j][:k])) for j in rows])
 
     @staticmethod
     def _source_rows(out: SchedulerOutput, prev: Optional["PendingStep"]):
@@ -454,8 +473,10 @@ class ModelRunner:
                 hidden = self.model.forward(batch, self.kv)
             with trace_range("sample"):
                 logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
+                self._step_logprobs = None
                 ids_dev = self._sample(logits, out.scheduled, rows)
             pend = PendingStep(out, rows, ids_dev, hidden, batch.num_tokens, batch.mode)
+            pend.logprobs, self._step_logprobs = self._step_logprobs, None
         # the device result may be overwritten by the next replay of the same graph: take the
         # host copy now, read it in finish()
         if self.device.type == "cuda":
@@ -490,6 +511,12 @@ class ModelRunner:
                 ids = pend.ids_dev.tolist()  # device -> host; synchronises the step
         self.d2h_total += len(ids) * 8
         accepted_rows = []
+        lp_rows = None
+        logprobs: Optional[dict] = None
+        if pend.logprobs is not None:
+            chosen, topv, topi = (t.tolist() for t in pend.logprobs)
+            lp_rows = (chosen, topv, topi)
+            logprobs = {}
         for s, rr in zip(sched, rows):
             if not s.samples:
                 continue
@@ -497,6 +524,8 @@ class ModelRunner:
             if len(rr) == 1:
                 new_tokens[r.request_id] = [ids[rr[0]]]
                 accepted_rows.append(rr[0])
+                if lp_rows is not None and r.sampling_params.logprobs is not None:
+                    logprobs[r.request_id] = self._logprob_entries(lp_rows, rr[:1], r)
                 continue
             target = [ids[j] for j in rr]
             toks = [target[0]]
@@ -508,8 +537,10 @@ class ModelRunner:
                     toks.append(target[j + 1])
             new_tokens[r.request_id] = toks
             accepted_rows.append(rr[len(toks) - 1])
+            if lp_rows is not None and r.sampling_params.logprobs is not None:
+                logprobs[r.request_id] = self._logprob_entries(lp_rows, rr[:len(toks)], r)
         if self.proposer is not None or self.suffix_cache is not None:
             from ..spec_decode.propose import propose_drafts
             with trace_range("draft"):
                 drafts = propose_drafts(self, sched, rows, new_tokens, pend.hidden, accepted_rows)
-        return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode)
+        return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode, logprobs)

@@ -12,8 +12,10 @@ class CompletionOutput:
     text: str
     token_ids: list[int]
     finish_reason: Optional[str] = None  # stop | length | abort
-    logprobs: Optional[list] = None
+    logprobs: Optional[list] = None          # log-probability of every generated token
     cumulative_logprob: Optional[float] = None
+    # per generated token, {token id: log-probability} of the most likely alternatives
+    top_logprobs: Optional[list] = None
 
 
 @dataclass

@@ -48,6 +48,7 @@ class Request:
     spec_token_ids: list[int] = field(default_factory=list)
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
     output_logprobs: Optional[list] = None
+    output_top_logprobs: Optional[list] = None
     routing_key: Optional[str] = None
     _block_array: Optional[object] = field(default=None, repr=False)
     # run-ahead scheduling: the last output token is a placeholder for a token that has been

@@ -243,11 +243,16 @@ def build_app(llm: AsyncLLM, served_model_name: Optional[str] = None) -> FastAPI
     def logprob_block(comp, chat: bool):
         if comp.logprobs is None:
             return None
+        tops = comp.top_logprobs or [{} for _ in comp.token_ids]
         if chat:
-            return {"content": [{"token": tok.decode([t]), "logprob": lp, "top_logprobs": []}
-                                for t, lp in zip(comp.token_ids, comp.logprobs)]}
+            return {"content": [{"token": tok.decode([t]), "logprob": lp,
+                                 "top_logprobs": [{"token": tok.decode([int(i)]), "logprob": v}
+                                                  for i, v in alt.items()]}
+                                for t, lp, alt in zip(comp.token_ids, comp.logprobs, tops)]}
         return {"tokens": [tok.decode([t]) for t in comp.token_ids],
-                "token_logprobs": list(comp.logprobs), "top_logprobs": None, "text_offset": None}
+                "token_logprobs": list(comp.logprobs),
+                "top_logprobs": [{tok.decode([int(i)]): v for i, v in alt.items()} for alt in tops],
+                "text_offset": None}
 
     @app.post("/v1/completions")
     async def completions(req: CompletionRequest):
