@@ -101,6 +101,9 @@ class LLMEngine:
         eos = self.config.model.eos_token_id
         if eos is None:
             eos = getattr(self.tokenizer, "eos_token_id", None)
+        if params.prompt_logprobs is not None and self.config.model.is_swiftkv:
+            raise ValueError("prompt_logprobs is not available for SwiftKV models: their later "
+                             "layers run on the sampled rows only")
         now = arrival_time if arrival_time is not None else time.time()
         if params.n == 1:
             self.scheduler.add_request(Request(request_id, ids, params, prompt=text,
@@ -185,8 +188,11 @@ class LLMEngine:
         if not self.config.scheduler.async_scheduling or self.config.speculative is not None:
             return False
         for s in out.scheduled:
-            if s.samples and (s.num_draft or s.request.sampling_params.needs_full_logits):
+            sp = s.request.sampling_params
+            if s.samples and (s.num_draft or sp.needs_full_logits):
                 return False
+            if sp.prompt_logprobs is not None and s.start < s.request.num_prompt_tokens:
+                return False        # its prompt rows are read back when the step completes
         return True
 
     def _complete(self, pend, partial: bool) -> list[RequestOutput]:
@@ -275,7 +281,8 @@ class LLMEngine:
         comp = self._completion(req)
         if req.parent_id is None:
             return RequestOutput(req.request_id, req.prompt, req.prompt_token_ids, [comp], True,
-                                 req.metrics, num_cached_tokens=req.num_cached_tokens)
+                                 req.metrics, prompt_logprobs=req.prompt_logprobs,
+                                 num_cached_tokens=req.num_cached_tokens)
         parent = self._parents[req.parent_id]
         parent["done"][req.sample_index] = (comp, req.metrics)
         if len(parent["done"]) < parent["n"]:

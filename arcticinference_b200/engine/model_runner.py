@@ -79,7 +79,7 @@ class PendingStep:
     """A step that has been queued on the device."""
 
     __slots__ = ("out", "rows", "ids_dev", "hidden", "num_tokens", "mode", "ids_host", "event",
-                 "row_of", "logprobs")
+                 "row_of", "logprobs", "prompt_logprobs")
 
     def __init__(self, out, rows, ids_dev, hidden, num_tokens, mode):
         self.out, self.rows, self.ids_dev, self.hidden = out, rows, ids_dev, hidden
@@ -88,6 +88,7 @@ class PendingStep:
         self.event = None
         self.row_of = {}
         self.logprobs = None      # (chosen [rows], top values [rows, k], top ids [rows, k])
+        self.prompt_logprobs = None   # (values [n], [(request, first position, count)])
 
 
 @dataclass
@@ -238,7 +239,17 @@ class ModelRunner:
                     self.cascade_steps += 1
         pad_to = self.sp if mode == "sp" else 1
         Np = (N + pad_to - 1) // pad_to * pad_to
-        n_sel = sum((s.num_draft + 1) if s.samples else 0 for s in sched)
+        n_smp = sum((s.num_draft + 1) if s.samples else 0 for s in sched)
+        # prompt log-probabilities: every prompt position of the chunk whose successor is a
+        # prompt token is scored too; those rows follow the sampled rows
+        prompt_spans = []       # (request, first position, count)
+        for s in sched:
+            r = s.request
+            if r.sampling_params.prompt_logprobs is not None:
+                hi = min(s.start + s.num_tokens, r.num_prompt_tokens - 1)
+                if hi > s.start:
+                    prompt_spans.append((s, s.start, hi - s.start))
+        n_sel = n_smp + sum(c for _, _, c in prompt_spans)
         max_blocks = max(len(s.request.block_ids) for s in sched)
         stage = self._stage(3 * Np + n_sel + n_sel)
         h = stage.numpy()
@@ -268,6 +279,17 @@ class ModelRunner:
             else:
                 rows.append([])
                 sel_q_lens.append(0)
+        prompt_rows = None
+        if prompt_spans:
+            off_of = {id(s): t for s, t in zip(sched, offs)}
+            prompt_rows, targets = [], []
+            for s, p0, cnt in prompt_spans:
+                t0 = off_of[id(s)] + (p0 - s.start)
+                sel[k:k + cnt] = np.arange(t0, t0 + cnt, dtype=np.int64)
+                sel_pos[k:k + cnt] = np.arange(p0, p0 + cnt, dtype=np.int64)
+                prompt_rows.append((s.request, p0, cnt))
+                targets.extend(s.request.prompt_token_ids[p0 + 1:p0 + cnt + 1])
+                k += cnt
         if Np > N:
             ids[N:] = 0
             pos[N:] = 0
@@ -310,6 +332,10 @@ class ModelRunner:
         batch = ForwardBatch(input_ids=d[:Np], positions=d[Np:2 * Np], slots=d[2 * Np:3 * Np],
                              attn_meta=meta, logits_indices=d[3 * Np:3 * Np + n_sel],
                              num_tokens=Np, mode=mode)
+        batch.num_sampled = n_smp
+        if prompt_rows:
+            batch.prompt_rows = prompt_rows
+            batch.prompt_targets = ops.upload(np.asarray(targets, dtype=np.int64), dev)
         if self.config.model.is_swiftkv:
             batch.sel_positions = d[3 * Np + n_sel:3 * Np + 2 * n_sel]
             if n_sel:
@@ -323,12 +349,13 @@ class ModelRunner:
         return batch, rows
 
     # ---------------------------------------------------------------- sampling
-    def _sample(self, logits: torch.Tensor, sched, rows) -> torch.Tensor:
-        """Returns int64 [num_rows] token ids on the device."""
+    def _sample(self, logits: torch.Tensor, sched, rows, gathered: bool = False) -> torch.Tensor:
+        """Returns int64 [num_rows] token ids on the device. ``gathered``: ``logits`` already
+        span the whole vocabulary on every rank."""
         greedy = all(s.request.sampling_params.greedy for s in sched if s.samples)
         plain = all(not s.request.sampling_params.needs_full_logits for s in sched if s.samples)
         comm = self.comm
-        sharded = comm is not None and comm.ways > 1
+        sharded = comm is not None and comm.ways > 1 and not gathered
         if plain:
             temps = seeds = None
             if not greedy:
@@ -474,12 +501,25 @@ class ModelRunner:
             with trace_range("sample"):
                 logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
                 self._step_logprobs = None
-                ids_dev = self._sample(logits, out.scheduled, rows)
+                prompt_lp, gathered = None, False
+                if batch.prompt_rows:
+                    comm = self.comm
+                    if comm is not None and comm.ways > 1:
+                        logits = comm.gather_vocab(logits, self.config.model.vocab_size)
+                        gathered = True
+                    n_s = batch.num_sampled
+                    lp = logits[n_s:].float().log_softmax(-1)
+                    prompt_lp = lp.gather(1, batch.prompt_targets.unsqueeze(1)).squeeze(1)
+                    logits = logits[:n_s]
+                ids_dev = self._sample(logits, out.scheduled, rows, gathered) \
+                    if logits.shape[0] else None
             pend = PendingStep(out, rows, ids_dev, hidden, batch.num_tokens, batch.mode)
             pend.logprobs, self._step_logprobs = self._step_logprobs, None
+            if prompt_lp is not None:
+                pend.prompt_logprobs = (prompt_lp, batch.prompt_rows)
         # the device result may be overwritten by the next replay of the same graph: take the
         # host copy now, read it in finish()
-        if self.device.type == "cuda":
+        if self.device.type == "cuda" and pend.ids_dev is not None:
             host = self._ids_host[self._ids_flip]
             if host is None or host.numel() < pend.ids_dev.numel():
                 host = torch.empty(max(pend.ids_dev.numel(), 4096), dtype=torch.int64, pin_memory=True)
@@ -499,6 +539,16 @@ class ModelRunner:
         new_tokens: dict = {}
         drafts: dict = {}
         sched, rows = pend.out.scheduled, pend.rows
+        if pend.prompt_logprobs is not None:
+            vals, spans = pend.prompt_logprobs
+            vals = vals.tolist()            # synchronises the step
+            o = 0
+            for req, p0, cnt in spans:
+                if req.prompt_logprobs is None:
+                    req.prompt_logprobs = [None] * req.num_prompt_tokens
+                # the value at index p + 1 is log P(prompt[p + 1] | prompt[:p + 1])
+                req.prompt_logprobs[p0 + 1:p0 + cnt + 1] = vals[o:o + cnt]
+                o += cnt
         if pend.ids_dev is None:
             return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode)
         with trace_range("sync_tokens"):

@@ -49,6 +49,7 @@ class Request:
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
     output_logprobs: Optional[list] = None
     output_top_logprobs: Optional[list] = None
+    prompt_logprobs: Optional[list] = None     # [None, log P(prompt[1] | prompt[:1]), ...]
     routing_key: Optional[str] = None
     _block_array: Optional[object] = field(default=None, repr=False)
     # run-ahead scheduling: the last output token is a placeholder for a token that has been

@@ -57,6 +57,7 @@ class SamplingParams:
     def needs_full_logits(self) -> bool:
         """True when arg-max / Gumbel-max over raw logits is not enough."""
         return (self.top_p < 1.0 or self.top_k > 0 or self.logprobs is not None or
+                self.prompt_logprobs is not None or
                 self.guided_choice is not None or self.guided_json is not None or
                 self.guided_regex is not None or
                 self.grammar is not None)

@@ -173,7 +173,10 @@ class Scheduler:
             if req.provisional:
                 break   # preempted with a token still unread: re-admitted once it is known
             if req.num_computed_tokens == 0 and not req.block_ids:
-                cached = self.kv.match_prefix(req)
+                # every prompt position of a request that wants prompt log-probabilities has
+                # to be computed, so it takes nothing from the prefix cache
+                cached = self.kv.match_prefix(req) \
+                    if req.sampling_params.prompt_logprobs is None else 0
                 req.num_computed_tokens = cached
                 req.num_cached_tokens = cached
                 req.metrics.num_cached_tokens = cached

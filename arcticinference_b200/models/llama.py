@@ -178,6 +178,12 @@ class ForwardBatch:
     # SwiftKV: metadata / positions of the sampled rows only
     sel_attn_meta: object = None
     sel_positions: Optional[torch.Tensor] = None
+    # the first ``num_sampled`` selected rows are sampled; further rows are prompt positions
+    # whose log-probabilities were asked for: (request, first position, count) per span and
+    # the token that follows each such position
+    num_sampled: int = 0
+    prompt_rows: Optional[list] = None
+    prompt_targets: Optional[torch.Tensor] = None
 
 
 class LlamaForCausalLM(LlamaModel):

@@ -68,3 +68,48 @@ def test_openai_logprob_blocks():
             assert len(content) == 4 and all(len(e["top_logprobs"]) == 2 for e in content)
     finally:
         llm.shutdown()
+
+
+def test_prompt_logprobs_agree_with_decoding_and_with_chunking():
+    prompt = list(range(5, 45))
+    llm = LLM(**KW)
+    gen = llm.generate([{"prompt_token_ids": prompt}],
+                       SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True, logprobs=1))[0]
+    toks, lps = gen.outputs[0].token_ids, gen.outputs[0].logprobs
+    # teacher forcing: the prompt extended by the generated tokens must score them the same
+    sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, prompt_logprobs=0)
+    full = llm.generate([{"prompt_token_ids": prompt + toks}, {"prompt_token_ids": [7, 8, 9]}],
+                        [sp, SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)])
+    pl = full[0].prompt_logprobs
+    assert len(pl) == len(prompt) + 4 and pl[0] is None and all(v <= 0 for v in pl[1:])
+    for i, want in enumerate(lps):
+        assert math.isclose(pl[len(prompt) + i], want, abs_tol=2e-2)      # bf16 model
+    assert full[1].prompt_logprobs is None
+    # the same prompt in 16-token chunks that share steps with another request's decodes
+    chunked = LLM(max_num_batched_tokens=16, **KW).generate(
+        [{"prompt_token_ids": prompt + toks}, {"prompt_token_ids": [7, 8, 9]}],
+        [sp, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)])
+    assert all(math.isclose(a, b, abs_tol=2e-2) for a, b in zip(pl[1:], chunked[0].prompt_logprobs[1:]))
+    # with run-ahead stepping on (the default) and off
+    off = LLM(async_scheduling=False, max_num_batched_tokens=16, **KW).generate(
+        [{"prompt_token_ids": prompt + toks}], sp)[0]
+    assert all(math.isclose(a, b, abs_tol=2e-2)
+               for a, b in zip(off.prompt_logprobs[1:], chunked[0].prompt_logprobs[1:]))
+
+
+def test_prompt_logprobs_refused_for_swiftkv():
+    llm = LLM(model="llama-tiny-swiftkv", device="cpu", max_model_len=256, num_gpu_blocks_override=64)
+    with pytest.raises(ValueError):
+        llm.generate([{"prompt_token_ids": [1, 2, 3]}], SamplingParams(prompt_logprobs=0))
+
+
+def test_prompt_logprobs_are_complete_when_the_prompt_is_in_the_prefix_cache():
+    llm = LLM(enable_prefix_caching=True, **KW)
+    prompt = [{"prompt_token_ids": list(range(9, 80))}]
+    sp = SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True, prompt_logprobs=0)
+    first = llm.generate(prompt, sp)[0].prompt_logprobs
+    plain = llm.generate(prompt, SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))[0]
+    assert plain.num_cached_tokens > 0 and plain.prompt_logprobs is None
+    again = llm.generate(prompt, sp)[0].prompt_logprobs
+    assert len(again) == 71 and again[0] is None and None not in again[1:]
+    assert all(math.isclose(a, b, abs_tol=2e-2) for a, b in zip(first[1:], again[1:]))

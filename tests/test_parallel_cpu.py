@@ -131,8 +131,15 @@ def _generate_worker(rank, world, port, q):
                     dict(llm.engine.runner.mode_counts)))
     every = [None] * world
     dist.all_gather_object(every, res[1][0])
+    # log-probabilities over a vocabulary that is split between the ranks
+    sp2 = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True, logprobs=2, prompt_logprobs=0)
+    par = llm.generate(prompts[:1], sp2)[0]
+    lp = (par.outputs[0].token_ids, par.outputs[0].logprobs, par.prompt_logprobs)
     if rank == 0:
-        q.put((res, every))
+        one = LLM(model="llama-tiny", device="cpu", num_gpu_blocks_override=64, block_size=16,
+                  max_model_len=512).generate(prompts[:1], sp2)[0]
+        q.put((res, every, lp, (one.outputs[0].token_ids, one.outputs[0].logprobs,
+                                one.prompt_logprobs)))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -147,7 +154,7 @@ def test_run_ahead_on_two_ranks_with_chunked_prompts_and_mode_shifts():
     procs = [ctx.Process(target=_generate_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res, every = _result_or_child_failure(q, procs, 300)
+    res, every, lp_two_ranks, lp_one_rank = _result_or_child_failure(q, procs, 300)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -156,3 +163,9 @@ def test_run_ahead_on_two_ranks_with_chunked_prompts_and_mode_shifts():
     assert sync_ahead == 0 and async_ahead > 10
     assert modes["sp"] > 0 and modes["tp"] > 0
     assert all(e == async_tokens for e in every)
+    # prompt positions are teacher-forced, so they compare across layouts; generated tokens
+    # can part ways at a near-tie of this random model, so only the first one is compared
+    a, b = lp_two_ranks[2][1:], lp_one_rank[2][1:]
+    assert len(a) == len(b) and all(abs(x - y) < 5e-2 for x, y in zip(a, b))
+    assert lp_two_ranks[0][0] == lp_one_rank[0][0]
+    assert abs(lp_two_ranks[1][0] - lp_one_rank[1][0]) < 5e-2 and len(lp_two_ranks[1]) == 4
