@@ -42,6 +42,7 @@ class CompletionRequest(BaseModel):
     ignore_eos: bool = False
     min_tokens: int = 0
     max_tokens_n: Optional[list[int]] = None
+    prompt_logprobs: Optional[int] = None     # also score the prompt tokens
     guided_choice: Optional[list[str]] = None   # the completion is exactly one of these
     guided_json: Optional[Union[dict, str]] = None   # compact JSON conforming to this schema
     guided_regex: Optional[str] = None              # the completion matches this expression
@@ -127,6 +128,7 @@ def _sampling(req, max_tokens) -> SamplingParams:
     return SamplingParams(n=req.n, temperature=req.temperature, top_p=req.top_p, top_k=req.top_k,
                           max_tokens=max_tokens, stop=req.stop, stop_token_ids=req.stop_token_ids,
                           seed=req.seed, logprobs=lp, ignore_eos=req.ignore_eos,
+                          prompt_logprobs=getattr(req, "prompt_logprobs", None),
                           min_tokens=getattr(req, "min_tokens", 0),
                           max_tokens_n=getattr(req, "max_tokens_n", None),
                           guided_choice=getattr(req, "guided_choice", None) or None,
@@ -313,6 +315,8 @@ def build_app(llm: AsyncLLM, served_model_name: Optional[str] = None) -> FastAPI
                     text = (out.prompt if out.prompt is not None else tok.decode(out.prompt_token_ids)) + text
                 choices.append({"index": i * req.n + c.index, "text": text, "token_ids": c.token_ids,
                                 "finish_reason": c.finish_reason, "logprobs": logprob_block(c, False)})
+                if req.prompt_logprobs is not None:
+                    choices[-1]["prompt_logprobs"] = out.prompt_logprobs
         return JSONResponse({"id": cid, "object": "text_completion", "created": created, "model": name,
                              "choices": choices, "usage": usage(n_in, n_out)})
 

@@ -61,6 +61,10 @@ def test_openai_logprob_blocks():
             lp = r.json()["choices"][0]["logprobs"]
             assert len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["top_logprobs"]) == 5
             assert all(len(d) >= 1 for d in lp["top_logprobs"])
+            r = c.post("/v1/completions", json={"model": "m", "prompt": [5, 6, 7, 8, 9], "max_tokens": 2,
+                                                "temperature": 0, "prompt_logprobs": 0})
+            pl = r.json()["choices"][0]["prompt_logprobs"]
+            assert len(pl) == 5 and pl[0] is None and all(v < 0 for v in pl[1:])
             r = c.post("/v1/chat/completions", json={
                 "model": "m", "max_tokens": 4, "temperature": 0, "ignore_eos": True,
                 "messages": [{"role": "user", "content": "hi"}], "logprobs": True, "top_logprobs": 2})
