@@ -229,3 +229,37 @@ def test_async_engine_on_the_default_device_streams_tokens():
     finally:
         llm.shutdown()
     ops.check_status()
+
+
+def test_run_ahead_over_chunked_prompts_changes_nothing():
+    """Prompt chunks and completing prompts run ahead too: long prompts cut into 64-token
+    chunks that share steps with other requests' decodes give the same tokens with run-ahead
+    stepping on and off, and nearly every step is queued behind its predecessor."""
+    prompts = [{"prompt_token_ids": [(7 * i + 3 * j) % 997 + 1 for i in range(n)]}
+               for j, n in enumerate((300, 12, 150, 70))]
+    sp = [SamplingParams(temperature=0, max_tokens=n, ignore_eos=True) for n in (10, 40, 1, 25)]
+    kw = dict(model="llama-tiny", device="cuda:0", num_gpu_blocks_override=256, block_size=16,
+              max_model_len=512, max_num_batched_tokens=64)
+    outs, steps = {}, {}
+    for mode in (False, True):
+        llm = LLM(async_scheduling=mode, **kw)
+        outs[mode] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        steps[mode] = llm.engine.stats["steps"]
+        if mode:
+            assert llm.engine.stats["run_ahead_steps"] >= steps[mode] - 3
+    ops.check_status()
+    assert outs[False] == outs[True] and steps[False] == steps[True]
+
+
+def test_logprobs_on_gpu_match_the_cpu_path():
+    import math
+    prompt = [{"prompt_token_ids": [(5 * i) % 991 + 2 for i in range(48)]}]
+    sp = SamplingParams(temperature=0, max_tokens=6, ignore_eos=True, logprobs=2, prompt_logprobs=0)
+    kw = dict(model="llama-tiny", num_gpu_blocks_override=64, block_size=16, max_model_len=256)
+    g = LLM(device="cuda:0", **kw).generate(prompt, sp)[0]
+    c = LLM(device="cpu", **kw).generate(prompt, sp)[0]
+    ops.check_status()
+    assert len(g.prompt_logprobs) == 48 and g.prompt_logprobs[0] is None
+    assert all(math.isclose(a, b, abs_tol=6e-2) for a, b in zip(g.prompt_logprobs[1:], c.prompt_logprobs[1:]))
+    assert len(g.outputs[0].logprobs) == 6 and len(g.outputs[0].top_logprobs[0]) == 2
+    assert math.isclose(g.outputs[0].logprobs[0], c.outputs[0].logprobs[0], abs_tol=6e-2)
