@@ -260,6 +260,6 @@ def test_logprobs_on_gpu_match_the_cpu_path():
     c = LLM(device="cpu", **kw).generate(prompt, sp)[0]
     ops.check_status()
     assert len(g.prompt_logprobs) == 48 and g.prompt_logprobs[0] is None
-    assert all(math.isclose(a, b, abs_tol=6e-2) for a, b in zip(g.prompt_logprobs[1:], c.prompt_logprobs[1:]))
+    assert all(math.isclose(a, b, abs_tol=0.12) for a, b in zip(g.prompt_logprobs[1:], c.prompt_logprobs[1:]))
     assert len(g.outputs[0].logprobs) == 6 and len(g.outputs[0].top_logprobs[0]) == 2
-    assert math.isclose(g.outputs[0].logprobs[0], c.outputs[0].logprobs[0], abs_tol=6e-2)
+    assert math.isclose(g.outputs[0].logprobs[0], c.outputs[0].logprobs[0], abs_tol=0.12)
