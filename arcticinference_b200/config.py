@@ -58,6 +58,8 @@ class ModelConfig:
     dtype: str = "bfloat16"
     quantization: Optional[str] = None  # None | "fp8"
     fp8_block_size: int = 128
+    # "channel": a scale per output feature, activations per token; "block": 128 x 128 blocks
+    fp8_scheme: str = "channel"
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
     name_or_path: str = ""
@@ -78,6 +80,8 @@ class ModelConfig:
             raise ValueError("head_dim must be 64 or 128 (tensor-memory attention tiles)")
         if self.quantization not in (None, "fp8"):
             raise ValueError("quantization must be None or 'fp8'")
+        if self.fp8_scheme not in ("channel", "block"):
+            raise ValueError("fp8_scheme must be 'channel' or 'block'")
 
     @classmethod
     def from_hf_dict(cls, d: dict, name_or_path: str = "") -> "ModelConfig":
@@ -298,6 +302,10 @@ class SpeculativeConfig:
 # --------------------------------------------------------------------------------------
 # cache / scheduler / forest cascade attention
 # --------------------------------------------------------------------------------------
+# cache element types the attention kernels can read (the cache writers also produce nvfp4)
+SUPPORTED_KV_CACHE_DTYPES = ("auto", "bfloat16")
+
+
 @dataclass
 class CacheConfig:
     block_size: int = 64
@@ -374,6 +382,19 @@ class EngineConfig:
             raise ValueError("num_key_value_heads and tensor_parallel_size must divide evenly")
         if m.is_swiftkv and p.pipeline_parallel_size > 1:
             raise ValueError("SwiftKV models do not support pipeline parallelism")
+        # Options this engine parses for command-line compatibility but cannot honour are
+        # refused here rather than ignored.
+        if p.pipeline_parallel_size > 1:
+            raise NotImplementedError(
+                "pipeline_parallel_size > 1: this engine executes the SP x TP plane of one "
+                "replica; pipeline stages are only enumerated (parallel/layout.py)")
+        if p.enable_expert_parallel:
+            raise NotImplementedError("enable_expert_parallel: no mixture-of-experts model is "
+                                      "implemented, so there is nothing to shard by expert")
+        if self.cache.kv_cache_dtype not in SUPPORTED_KV_CACHE_DTYPES:
+            raise NotImplementedError(
+                "kv_cache_dtype=%r: the attention kernels read %s caches only" %
+                (self.cache.kv_cache_dtype, " / ".join(SUPPORTED_KV_CACHE_DTYPES)))
         if self.speculative is not None and self.speculative.uses_suffix and \
                 self.speculative.method not in ("arctic", "suffix"):
             raise ValueError("suffix decoding is only available with the arctic or suffix methods")
@@ -401,6 +422,7 @@ class EngineArgs:
     served_model_name: Optional[str] = None
     dtype: str = "bfloat16"
     quantization: Optional[str] = None
+    fp8_scheme: Optional[str] = None
     load_format: str = "auto"
     seed: int = 0
     max_model_len: Optional[int] = None
@@ -446,6 +468,9 @@ class EngineArgs:
         g.add_argument("--served-model-name", type=str, default=None)
         g.add_argument("--dtype", type=str, default="bfloat16")
         g.add_argument("--quantization", "-q", type=str, default=None, choices=[None, "fp8"])
+        g.add_argument("--fp8-scheme", type=str, default=None, choices=[None, "channel", "block"],
+                       help="fp8 scale layout: one scale per output feature with per-token "
+                            "activation scales (default), or 128 x 128 blocks")
         g.add_argument("--load-format", type=str, default="auto", choices=["auto", "dummy"])
         g.add_argument("--seed", type=int, default=0)
         g.add_argument("--max-model-len", type=int, default=None)
@@ -504,6 +529,8 @@ class EngineArgs:
             model = dataclasses.replace(model, **self.hf_overrides)
         if self.quantization is not None:
             model.quantization = self.quantization
+        if self.fp8_scheme is not None:
+            model.fp8_scheme = self.fp8_scheme
         model.dtype = self.dtype
         max_len = self.max_model_len or min(model.max_position_embeddings, 8192)
         parallel = ParallelConfig(

@@ -83,6 +83,23 @@ int ab200_linear_bf16_scatter(const void* x, long long ldx, const void* w, long 
                               long long peer_row_off, long long ldo, int M, int N, int K,
                               int* status, cudaStream_t stream);
 
+// ---- gemm_bf16.cu, fp8 operands with per-token / per-feature scales
+int ab200_linear_fp8_row(const void* xq, long long ldx, const void* sx, const void* wq,
+                         long long ldw, const void* sw, void* out, long long ldo, int M, int N,
+                         int K, const void* bias, const void* residual, long long ldr, int act,
+                         void* workspace, size_t workspace_bytes, int force_splits,
+                         const void* const* peer_ptrs, int world, int peer_cols,
+                         long long peer_row_off, int* status, cudaStream_t stream);
+
+// ---- quant_row.cu
+int ab200_quant_fp8_row(const void* x, long long ldx, void* xq, long long ldq, void* sx,
+                        long long M, int K, cudaStream_t stream);
+int ab200_rmsnorm_quant(const void* x, long long ldx, void* residual, const void* weight,
+                        void* yq, long long ldq, void* sy, void* y, long long ldy, long long T,
+                        int hidden, float eps, cudaStream_t stream);
+int ab200_silu_mul_quant(const void* x, void* outq, long long ldq, void* so, long long T,
+                         int inter, int nblk, cudaStream_t stream);
+
 // ---- gemm_fp8.cu
 int ab200_quant_fp8(const void* x, long long ldx, void* xq, long long ldq, void* sx_t,
                     long long ld_sx, long long M, int K, cudaStream_t stream);

@@ -13,8 +13,16 @@
 //     N/128 alone cannot fill 148 SMs. Split-K partial sums go to an fp32
 //     scratch buffer supplied by the caller and are folded by a second kernel.
 //
+// The same kernel runs W8A8 fp8 linears whose scales are one per token and one per output
+// feature (ab200_linear_fp8_row): the operands are e4m3 bytes (a 128-byte swizzle atom is then
+// 128 k-elements and one kind::f8f6f4 instruction covers 32 of them), the whole K loop
+// accumulates in tensor memory with no rescaling on the way, and the epilogue multiplies each
+// accumulator by scale_token * scale_feature. An instruction of either kind is accepted at
+// the same interval, so the fp8 form does twice the work per unit time.
+//
 // The reference relies on library GEMMs for these layers (vLLM linear layers
-// reached from arctic_inference/vllm/swiftkv/llama_swiftkv.py:165-202).
+// reached from arctic_inference/vllm/swiftkv/llama_swiftkv.py:165-202; fp8 with per-token and
+// per-channel scales: arctic_inference/vllm/spec_dec/fp8.py:34-309).
 
 #include <math.h>
 #include <mutex>
@@ -28,6 +36,8 @@ namespace ab200 {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;  // bf16 elements: one 128-byte swizzle atom per row
+constexpr int kBlockKFp8 = 128;  // e4m3 elements in the same 128 bytes
+constexpr int kBlockKBytes = 128;
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kMaxStages = 8;
@@ -47,6 +57,10 @@ struct GemmArgs {
   int b_mn_major;  // 1: the B operand is given as [K, rows_b] (rows_b contiguous)
   int coalesce;    // 1: bf16 row-major output goes through a shared-memory transpose so that a
                    //    warp stores whole 128-byte lines (what NVLink and L2 both want)
+  int fp8;         // 1: operands are e4m3 bytes (kind::f8f6f4), 128 k-elements per stage
+  int kblock_elems;  // k-elements per stage: 64 (bf16) or 128 (fp8)
+  const float* scale_a;  // fp8: one factor per A-operand row (null = 1)
+  const float* scale_b;  // fp8: one factor per B-operand row
   uint32_t tmem_cols;
   long long ldo, ldr, partial_stride;
   void* out;
@@ -136,9 +150,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
           const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes;
-          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, tile_a * kBlockM);
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * p.kblock_elems, tile_a * kBlockM);
           if (!p.b_mn_major) {
-            tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * kBlockK, tile_b * p.bn);
+            tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * p.kblock_elems,
+                        tile_b * p.bn);
           } else {
             // [64 k-rows][64 n] boxes, one per 64-wide atom along N
             for (int j = 0; j < p.bn / 64; ++j)
@@ -170,7 +185,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
       const uint32_t idesc =
-          make_idesc(kBlockM, (uint32_t)p.bn, 1, 1, 0, p.b_mn_major ? 1u : 0u);
+          p.fp8 ? make_idesc(kBlockM, (uint32_t)p.bn, 0, 0, 0, 0)
+                : make_idesc(kBlockM, (uint32_t)p.bn, 1, 1, 0, p.b_mn_major ? 1u : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -193,13 +209,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t a_desc = make_desc_kmajor_sw128(a_addr);
           const uint64_t b_desc = p.b_mn_major ? make_desc_mnmajor_sw128(a_addr + kABytes, 8192u)
                                                : make_desc_kmajor_sw128(a_addr + kABytes);
-          // K-major: 16 bf16 (32 bytes) further inside the swizzle atom = +2 in the encoded
-          // address; MN-major: 16 rows of 128 bytes further = +128.
+          // K-major: 16 bf16 or 32 e4m3 (32 bytes) further inside the swizzle atom = +2 in the
+          // encoded address; MN-major: 16 rows of 128 bytes further = +128.
           const uint64_t b_step = p.b_mn_major ? 128u : 2u;
+          if (p.fp8) {
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            umma_f16_ss(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + b_step * (uint64_t)k, idesc,
-                        (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBlockKBytes / 32; ++k) {
+              umma_f8_ss(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              umma_f16_ss(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + b_step * (uint64_t)k, idesc,
+                          (kb > kb0 || k > 0) ? 1u : 0u);
+            }
           }
           tc_commit(empty_bar(stage));
           if (++stage == p.stages) {
@@ -231,6 +255,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long a_row = (long long)tile_a * kBlockM + row;
       const bool row_ok = a_row < p.rows_a;
       const long long b0 = (long long)tile_b * p.bn;
+      const bool scaled = p.scale_a != nullptr && !p.out_f32;
+      const float sa = (scaled && row_ok) ? p.scale_a[a_row] : 1.f;
 
       if (p.coalesce) {
         // 64 output columns at a time: each thread converts its row, the warp transposes
@@ -253,6 +279,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 v[t] = __uint_as_float(j < 4 ? r0[8 * j + t] : r1[8 * (j - 4) + t]);
               const long long cj = col + 8 * j;
               if (cj + 8 <= p.rows_b) {
+                if (scaled) {
+                  const float4 s0 = *reinterpret_cast<const float4*>(p.scale_b + cj);
+                  const float4 s1 = *reinterpret_cast<const float4*>(p.scale_b + cj + 4);
+                  v[0] *= sa * s0.x; v[1] *= sa * s0.y; v[2] *= sa * s0.z; v[3] *= sa * s0.w;
+                  v[4] *= sa * s1.x; v[5] *= sa * s1.y; v[6] *= sa * s1.z; v[7] *= sa * s1.w;
+                }
                 if (p.bias != nullptr) {
                   const uint4 q = *reinterpret_cast<const uint4*>(p.bias + cj);
                   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
@@ -331,6 +363,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
           continue;
+        }
+        if (scaled) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t)
+            if (b0 + c0 + t < p.rows_b) v[t] *= sa * p.scale_b[b0 + c0 + t];
         }
         if (!p.transposed) {
           const long long col = b0 + c0;
@@ -419,7 +456,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
                                      __nv_bfloat16* __restrict__ out, long long ldo,
                                      const __nv_bfloat16* __restrict__ bias,
                                      const __nv_bfloat16* __restrict__ residual, long long ldr,
-                                     int act) {
+                                     int act, const float* __restrict__ scale_m,
+                                     const float* __restrict__ scale_n) {
   const long long n4 = N / 4;
   const long long total = (long long)M * n4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -436,6 +474,11 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
       acc.w += v.w;
     }
     float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (scale_m != nullptr) {
+      const float sm = scale_m[m];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) v[t] *= sm * scale_n[n + t];
+    }
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       if (bias != nullptr) v[t] += __bfloat162float(bias[n + t]);
@@ -453,7 +496,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 struct TmapKey {
   const void* ptr;
   uint64_t rows, cols, ld;
-  uint32_t box_rows;
+  uint32_t box_rows;  // bit 31 set: e4m3 bytes instead of bf16
   bool operator==(const TmapKey& o) const {
     return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
   }
@@ -469,11 +512,17 @@ struct TmapKeyHash {
   }
 };
 
+static int get_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                    uint32_t box_rows, bool fp8);
 static int get_tmap_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
                          uint64_t ld, uint32_t box_rows) {
+  return get_tmap(out, ptr, rows, cols, ld, box_rows, false);
+}
+static int get_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                    uint32_t box_rows, bool fp8) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-  TmapKey key{ptr, rows, cols, ld, box_rows};
+  TmapKey key{ptr, rows, cols, ld, box_rows | (fp8 ? 0x80000000u : 0u)};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -481,8 +530,10 @@ static int get_tmap_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint6
     return 0;
   }
   CUtensorMap m;
-  int rc = make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rows, cols, ld * 2, box_rows,
-                        kBlockK);
+  int rc = fp8 ? make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_UINT8, rows, cols, ld, box_rows,
+                              kBlockKFp8)
+               : make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rows, cols, ld * 2,
+                              box_rows, kBlockK);
   if (rc != 0) return rc;
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, m);
@@ -506,16 +557,6 @@ static int pick_stages(int bn) {
   int s = (227 * 1024 - 2048 - 4 * kStoreStageBytes) / stage_bytes;
   if (s > kMaxStages) s = kMaxStages;
   return s;
-}
-
-// AB200_GEMM_COALESCE=0 keeps the direct (one row per thread) stores, for A/B timing.
-static bool coalesced_stores_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("AB200_GEMM_COALESCE");
-    v = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
 }
 
 static uint32_t pow2_at_least(uint32_t v) {
@@ -546,7 +587,7 @@ constexpr double kMmaIssueCycles = 186.0;
 // Split-K factor for a one-row-of-tiles (M <= 128) token-major GEMM: the smallest estimate of
 // max(instruction-issue time, HBM time incl. fp32 partials) plus a reduce-launch penalty.
 static int pick_token_major_splits(int tiles_b, int kblocks, int M, int N, int K, int sms,
-                                   size_t workspace_bytes) {
+                                   size_t workspace_bytes, int elem_bytes) {
   int best = 1;
   double best_t = 1e30;
   for (int s = 1; s <= 16; s *= 2) {
@@ -554,7 +595,7 @@ static int pick_token_major_splits(int tiles_b, int kblocks, int M, int N, int K
     const int per_split = (kblocks + s - 1) / s;
     const int waves = (tiles_b * s + sms - 1) / sms;
     const double issue_us = waves * per_split * (kBlockK / kUmmaK) * kMmaIssueCycles / 1.9e3;
-    const double bytes = 2.0 * N * K + (s > 1 ? 2.0 * s * M * (double)N * 4.0 : 0.0);
+    const double bytes = (double)elem_bytes * N * K + (s > 1 ? 2.0 * s * M * (double)N * 4.0 : 0.0);
     const double hbm_us = bytes / 6.5e6;
     const double t = (issue_us > hbm_us ? issue_us : hbm_us) + (s > 1 ? 4.0 : 0.0);
     if (t < best_t - 0.25) {
@@ -570,12 +611,16 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
                          const void* residual, long long ldr, int act, void* workspace,
                          size_t workspace_bytes, int force_splits, int* status,
                          cudaStream_t stream, const void* const* peer_ptrs, int world,
-                         int peer_cols, long long peer_row_off) {
+                         int peer_cols, long long peer_row_off, const float* scale_x = nullptr,
+                         const float* scale_w = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((K % 8) || (N % 8) || (ldx % 8) || (ldw % 8) || (ldo % 8) ||
+  const bool fp8 = scale_x != nullptr;  // e4m3 operands with per-token / per-feature scales
+  const int opa = fp8 ? 16 : 8;         // operand rows must start on 16-byte boundaries
+  if ((K % opa) || (N % 8) || (ldx % opa) || (ldw % opa) || (ldo % 8) ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 15))
     return -2;
+  if (fp8 && (scale_w == nullptr || (reinterpret_cast<uintptr_t>(scale_w) & 15))) return -2;
   if (residual != nullptr && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -2;
 
   static bool attr_set[64] = {false};
@@ -600,7 +645,9 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     force_splits = 1;  // partial sums would need the scatter in the reduce kernel as well
   }
   a.K = K;
-  a.kblocks_total = (K + kBlockK - 1) / kBlockK;
+  a.fp8 = fp8 ? 1 : 0;
+  a.kblock_elems = fp8 ? kBlockKFp8 : kBlockK;
+  a.kblocks_total = (K + a.kblock_elems - 1) / a.kblock_elems;
   a.status = status;
   a.act = act;
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
@@ -626,6 +673,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     ldb = ldx;
     a.tiles_a = (N + kBlockM - 1) / kBlockM;
     a.tiles_b = 1;
+    a.scale_a = scale_w;
+    a.scale_b = scale_x;
     int splits = force_splits;
     if (splits <= 0) {
       splits = 1;
@@ -648,6 +697,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     pb = w;
     ldb = ldw;
     a.tiles_a = (M + kBlockM - 1) / kBlockM;
+    a.scale_a = scale_x;
+    a.scale_b = scale_w;
     const int tiles256 = a.tiles_a * ((N + 255) / 256);
     a.bn = ((tiles256 >= sms || a.tiles_a == 1) && N >= 256) ? 256 : 128;
     if (N < 128) a.bn = ((N + 15) / 16) * 16;
@@ -662,7 +713,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
       int splits = force_splits;
       if (splits <= 0)
         splits = (N % 4 == 0 && workspace != nullptr)
-                     ? pick_token_major_splits(a.tiles_b, a.kblocks_total, M, N, K, sms, workspace_bytes)
+                     ? pick_token_major_splits(a.tiles_b, a.kblocks_total, M, N, K, sms,
+                                               workspace_bytes, fp8 ? 1 : 2)
                      : 1;
       if (splits > 16) splits = 16;
       if (splits > a.kblocks_total) splits = a.kblocks_total;
@@ -677,7 +729,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   a.stages = pick_stages(a.bn);
   a.tmem_cols = pow2_at_least(2u * (uint32_t)a.bn);
 
-  a.coalesce = coalesced_stores_enabled() && !a.transposed && a.splits == 1 && a.bn % 64 == 0 &&
+  a.coalesce = !a.transposed && a.splits == 1 && a.bn % 64 == 0 &&
                N % 8 == 0 && ldo % 8 == 0 && (peer_cols == 0 || peer_cols % 64 == 0) &&
                (reinterpret_cast<uintptr_t>(bias) % 16) == 0 &&
                (residual == nullptr || ldr % 8 == 0);
@@ -691,8 +743,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   }
 
   CUtensorMap ta, tb;
-  if (get_tmap_bf16(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K, (uint64_t)lda, kBlockM) != 0) return -4;
-  if (get_tmap_bf16(&tb, pb, (uint64_t)a.rows_b, (uint64_t)K, (uint64_t)ldb, (uint32_t)a.bn) != 0)
+  if (get_tmap(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K, (uint64_t)lda, kBlockM, fp8) != 0) return -4;
+  if (get_tmap(&tb, pb, (uint64_t)a.rows_b, (uint64_t)K, (uint64_t)ldb, (uint32_t)a.bn, fp8) != 0)
     return -4;
 
   const int total = a.tiles_a * a.tiles_b * a.splits;
@@ -710,7 +762,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
         reinterpret_cast<const float*>(workspace), a.splits, a.partial_stride, M, N,
         reinterpret_cast<__nv_bfloat16*>(final_out), ldo,
         reinterpret_cast<const __nv_bfloat16*>(bias),
-        reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act);
+        reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act, scale_x, scale_w);
     if (cudaGetLastError() != cudaSuccess) return -5;
   }
   return 0;
@@ -740,6 +792,29 @@ int ab200_linear_bf16_scatter(const void* x, long long ldx, const void* w, long 
                        peer_row_off);
 }
 
+// W8A8 fp8 linear with one scale per token and one per output feature:
+//   out[m,n] = sx[m] * sw[n] * sum_k xq[m,k] * wq[n,k]   (+bias)(activation)(+residual)
+// xq [M,K] and wq [N,K] are e4m3 bytes (row strides in elements, multiples of 16), sx fp32 [M],
+// sw fp32 [N] (16-byte aligned). With peer_ptrs the output columns are scattered to the ranks'
+// buffers as in ab200_linear_bf16_scatter (pass world = 0 for a plain output).
+int ab200_linear_fp8_row(const void* xq, long long ldx, const void* sx, const void* wq,
+                         long long ldw, const void* sw, void* out, long long ldo, int M, int N,
+                         int K, const void* bias, const void* residual, long long ldr, int act,
+                         void* workspace, size_t workspace_bytes, int force_splits,
+                         const void* const* peer_ptrs, int world, int peer_cols,
+                         long long peer_row_off, int* status, cudaStream_t stream) {
+  if (sx == nullptr || sw == nullptr) return -2;
+  if (world > 0 && peer_cols > 0) {
+    return launch_linear(xq, ldx, wq, ldw, const_cast<void*>(peer_ptrs[0]), ldo, M, N, K, nullptr,
+                         nullptr, 0, 0, nullptr, 0, 1, status, stream, peer_ptrs, world, peer_cols,
+                         peer_row_off, reinterpret_cast<const float*>(sx),
+                         reinterpret_cast<const float*>(sw));
+  }
+  return launch_linear(xq, ldx, wq, ldw, out, ldo, M, N, K, bias, residual, ldr, act, workspace,
+                       workspace_bytes, force_splits, status, stream, nullptr, 0, 0, 0,
+                       reinterpret_cast<const float*>(sx), reinterpret_cast<const float*>(sw));
+}
+
 // out[M,N] = x[M,K] * wt[K,N] with wt row-major (N contiguous): exercises the
 // MN-major shared-memory descriptor for the B operand. N must be a multiple of 64.
 int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long ldw, void* out,
@@ -752,6 +827,7 @@ int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long l
   GemmArgs a;
   memset(&a, 0, sizeof(a));
   a.K = K;
+  a.kblock_elems = kBlockK;
   a.kblocks_total = (K + kBlockK - 1) / kBlockK;
   a.kblocks_per_split = a.kblocks_total;
   a.splits = 1;

@@ -7,6 +7,8 @@
 
 #include <stdio.h>
 
+#include <atomic>
+
 #include "api.h"
 #include "linear_noalloc.h"
 
@@ -16,7 +18,9 @@ constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_scratch[AB200_NOALLOC_SCRATCH_BYTES];
 
-void* g_scratch_addr[kMaxDevices] = {nullptr};
+// One entry per device, filled on the first call there. Host threads may make that first call
+// at the same time: each looks the address up and stores the same value.
+std::atomic<void*> g_scratch_addr[kMaxDevices];
 thread_local char g_last_error[256] = "";
 
 // Device address of the scratch array on the current device (looked up once per device).
@@ -28,17 +32,17 @@ int scratch_for_current_device(void** out) {
              e == cudaSuccess ? "index out of range" : cudaGetErrorString(e));
     return AB200_ERR_SYMBOL_LOOKUP;
   }
-  if (g_scratch_addr[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     e = cudaGetSymbolAddress(&p, g_scratch);
     if (e != cudaSuccess || p == nullptr) {
       snprintf(g_last_error, sizeof(g_last_error),
                "cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
       return AB200_ERR_SYMBOL_LOOKUP;
     }
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = p;
   return 0;
 }
 

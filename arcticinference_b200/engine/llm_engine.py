@@ -17,9 +17,15 @@ from ..utils.tokenizer import get_tokenizer
 from .kv_cache import KVCacheManager
 from .model_runner import ModelRunner
 from .outputs import CompletionOutput, RequestOutput
-from .request import Request, RequestStatus
+from .request import Request, RequestStatus, StopStringMatcher
 from .sampling_params import SamplingParams
 from .scheduler import Scheduler
+
+
+def tp_rows_per_request(spec) -> int:
+    """Upper bound of the rows one request can contribute to a tensor-parallel stretch of a
+    sequence-parallel step: its sampled row plus one per draft token under verification."""
+    return 1 + (spec.max_draft_tokens if spec is not None else 0)
 
 
 class LLMEngine:
@@ -39,11 +45,13 @@ class LLMEngine:
             max_tokens = (config.scheduler.max_num_batched_tokens + sp - 1) // sp * sp + sp
             # largest step that runs tensor-parallel: with sequence parallelism only steps up
             # to the shift threshold and the sampled rows of SwiftKV's later layers do (one
-            # row per request plus one per draft token; 8 rows per request bound that)
+            # row per request plus one per draft token, and a hybrid suffix draft can be as
+            # long as the suffix tree is deep)
             max_tp = max_tokens
             if sp > 1:
                 max_tp = min(max_tokens, max(config.parallel.shift_parallel_threshold,
-                                             8 * config.scheduler.max_num_seqs) + sp)
+                                             tp_rows_per_request(config.speculative) *
+                                             config.scheduler.max_num_seqs) + sp)
             comm.setup(max_tokens, max_tp, m.blk_rows, config.model.hidden_size,
                        sp * m.h * m.D)
         self.runner.load_model()
@@ -105,18 +113,28 @@ class LLMEngine:
             raise ValueError("prompt_logprobs is not available for SwiftKV models: their later "
                              "layers run on the sampled rows only")
         now = arrival_time if arrival_time is not None else time.time()
+
+        def stops():
+            if not params.stop:
+                return None
+            return StopStringMatcher(self.tokenizer, params.stop,
+                                     getattr(params, "include_stop_str_in_output", False),
+                                     params.skip_special_tokens)
+
         if params.n == 1:
             self.scheduler.add_request(Request(request_id, ids, params, prompt=text,
                                                eos_token_id=eos, arrival_time=now,
                                                routing_key=routing_key,
-                                               grammar=self._grammar_for(params, eos)))
+                                               grammar=self._grammar_for(params, eos),
+                                               stop_matcher=stops()))
         else:
             self._parents[request_id] = {"n": params.n, "done": {}, "prompt": text, "ids": ids}
             for i in range(params.n):
                 self.scheduler.add_request(Request(
                     "%s#%d" % (request_id, i), ids, params.clone_for_sample(i), prompt=text,
                     eos_token_id=eos, parent_id=request_id, sample_index=i, arrival_time=now,
-                    grammar=self._grammar_for(params, eos, copy_given=True)))
+                    grammar=self._grammar_for(params, eos, copy_given=True),
+                    stop_matcher=stops()))
         return request_id
 
     def _grammar_for(self, params: SamplingParams, eos, copy_given: bool = False):
@@ -132,7 +150,13 @@ class LLMEngine:
         return g
 
     def abort_request(self, request_id: str) -> None:
-        self.scheduler.abort(request_id)
+        """Drops a request; for an ``n > 1`` request every sample that is still running."""
+        parent = self._parents.pop(request_id, None)
+        ids = [request_id] if parent is None else \
+            ["%s#%d" % (request_id, i) for i in range(parent["n"])]
+        for rid in ids:
+            if self.scheduler.abort(rid) is not None and self.runner.suffix_cache is not None:
+                self.runner.suffix_cache.stop_request(rid)
         if self.runner.suffix_cache is not None:
             self.runner.suffix_cache.stop_request(request_id)
 
@@ -189,8 +213,8 @@ class LLMEngine:
             return False
         for s in out.scheduled:
             sp = s.request.sampling_params
-            if s.samples and (s.num_draft or sp.needs_full_logits):
-                return False
+            if s.samples and (s.num_draft or sp.needs_full_logits or sp.stop):
+                return False        # (a stop string is looked for in the text, on the host)
             if sp.prompt_logprobs is not None and s.start < s.request.num_prompt_tokens:
                 return False        # its prompt rows are read back when the step completes
         return True
@@ -269,8 +293,8 @@ class LLMEngine:
         return d
 
     def _completion(self, req: Request) -> CompletionOutput:
-        text = self.tokenizer.decode(req.output_token_ids,
-                                     skip_special_tokens=req.sampling_params.skip_special_tokens)
+        text = req.stop_text if req.stop_text is not None else self.tokenizer.decode(
+            req.output_token_ids, skip_special_tokens=req.sampling_params.skip_special_tokens)
         lps = req.output_logprobs
         return CompletionOutput(req.sample_index, text, list(req.output_token_ids),
                                 req.finish_reason, list(lps) if lps is not None else None,

@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import math
 import time
-import zlib
 from dataclasses import dataclass
 from typing import Optional
 
@@ -29,6 +28,7 @@ from ..config import EngineConfig
 from ..models.llama import ForwardBatch, LlamaForCausalLM, ShardSpec
 from ..utils.tracing import trace_range
 from .kv_cache import KVCacheTensors
+from .sampler import row_seed
 from .scheduler import SchedulerOutput
 
 
@@ -158,7 +158,7 @@ class ModelRunner:
             load_llama_weights(self.model, cfg.model.name_or_path)
         if cfg.model.quantization == "fp8":
             from ..models.quant import quantize_model_fp8
-            quantize_model_fp8(self.model)
+            quantize_model_fp8(self.model, scheme=cfg.model.fp8_scheme)
 
     def determine_num_blocks(self) -> int:
         cfg = self.config
@@ -364,10 +364,9 @@ class ModelRunner:
                 sv = np.zeros(n, dtype=np.int64)
                 for s, rr in zip(sched, rows):
                     sp = s.request.sampling_params
-                    base = sp.seed if sp.seed is not None else zlib.crc32(s.request.request_id.encode()) & 0xFFFFFFF
                     for j, row in enumerate(rr):
                         tv[row] = 0.0 if sp.greedy else sp.temperature
-                        sv[row] = (base * 1000003 + s.request.num_tokens + j) & 0x7FFFFFFFFFFFFFFF
+                        sv[row] = row_seed(s.request, j)
                 temps = ops.upload(tv, self.device)
                 seeds = ops.upload(sv, self.device)
             offset = 0

@@ -61,6 +61,10 @@ class Request:
     # structured output: matcher over the output tokens (structured.Grammar), advanced by
     # ``accept_output`` as tokens are appended
     grammar: Optional[object] = None
+    # stop strings: matcher over the detokenised output (StopStringMatcher) and, once one was
+    # found, the output text cut at it
+    stop_matcher: Optional[object] = None
+    stop_text: Optional[str] = None
 
     def __post_init__(self):
         self.metrics.arrival_time = self.arrival_time
@@ -127,8 +131,37 @@ class Request:
             if sp.stop_token_ids and last in sp.stop_token_ids:
                 self.status = RequestStatus.FINISHED_STOPPED
                 return True
+            if self.stop_matcher is not None and self.stop_matcher.hit(self):
+                self.status = RequestStatus.FINISHED_STOPPED
+                return True
         if (sp.max_tokens is not None and n_out >= sp.max_tokens) or \
                 self.num_tokens >= max_model_len:
             self.status = RequestStatus.FINISHED_LENGTH
             return True
         return False
+
+
+class StopStringMatcher:
+    """Ends a request when its detokenised output contains one of ``stop`` strings; the text
+    handed back is cut before the match (after it with ``include_stop_str_in_output``). The
+    output is decoded again from the start at every token: stop strings are for interactive
+    requests, whose outputs are short next to the cost of a model step."""
+
+    def __init__(self, tokenizer, stop, include: bool = False, skip_special_tokens: bool = True):
+        self.tokenizer = tokenizer
+        self.stop = [s for s in ([stop] if isinstance(stop, str) else list(stop)) if s]
+        self.include = include
+        self.skip_special_tokens = skip_special_tokens
+
+    def hit(self, req: "Request") -> bool:
+        text = self.tokenizer.decode(req.output_token_ids,
+                                     skip_special_tokens=self.skip_special_tokens)
+        best = None
+        for s in self.stop:
+            i = text.find(s)
+            if i >= 0 and (best is None or i < best[0]):
+                best = (i, s)
+        if best is None:
+            return False
+        req.stop_text = text[:best[0] + (len(best[1]) if self.include else 0)]
+        return True

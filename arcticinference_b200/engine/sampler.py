@@ -7,6 +7,8 @@ is framework-level PyTorch on the gathered logits."""
 
 from __future__ import annotations
 
+import zlib
+
 import numpy as np
 import torch
 
@@ -48,31 +50,41 @@ def apply_grammar_masks(lf: torch.Tensor, sched, rows) -> torch.Tensor:
     return out
 
 
+def row_seed(request, j: int) -> int:
+    """Noise key of the j-th row a request samples in this step: its own seed (or a hash of its
+    id) and its token index, so a draw depends neither on the step's other requests nor on the
+    previous draws of the same request."""
+    sp = request.sampling_params
+    base = sp.seed if sp.seed is not None else zlib.crc32(request.request_id.encode()) & 0xFFFFFFF
+    return (base * 1000003 + request.num_tokens + j) & 0x7FFFFFFFFFFFFFFF
+
+
 def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
+    """Sampling from distributions truncated by top-k / top-p / grammar masks. The truncated,
+    temperature-scaled logits go through the same per-row Gumbel-max kernel as plain sampling
+    (a masked token's -inf never wins), keyed per row by :func:`row_seed`."""
+    from .. import ops
     B = logits.shape[0]
     dev = logits.device
     lf = apply_grammar_masks(logits.float(), sched, rows)
-    raw = lf
-    temp = torch.ones(B, device=dev)
-    top_k = torch.zeros(B, dtype=torch.int64, device=dev)
-    top_p = torch.ones(B, device=dev)
-    greedy = torch.zeros(B, dtype=torch.bool, device=dev)
-    seed = 0
+    temp = np.ones(B, dtype=np.float32)
+    top_k = np.zeros(B, dtype=np.int64)
+    top_p = np.ones(B, dtype=np.float32)
+    draw = np.zeros(B, dtype=np.float32)      # 1: sample, 0: arg-max
+    seeds = np.zeros(B, dtype=np.int64)
     for s, rr in zip(sched, rows):
         sp = s.request.sampling_params
-        for row in rr:
+        for j, row in enumerate(rr):
             temp[row] = max(sp.temperature, 1e-5)
             top_k[row] = sp.top_k
             top_p[row] = sp.top_p
-            greedy[row] = sp.greedy
-        if rr and sp.seed is not None:
-            seed = seed * 31 + sp.seed + s.request.num_tokens
-    lf = apply_top_k_top_p(lf / temp.unsqueeze(1), top_k, top_p)
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(seed & 0x7FFFFFFF)
-    probs = lf.softmax(-1)
-    sampled = torch.multinomial(probs, 1, generator=gen).squeeze(1)
-    return torch.where(greedy, raw.argmax(-1), sampled)
+            draw[row] = 0.0 if sp.greedy else 1.0
+            seeds[row] = row_seed(s.request, j)
+    temp_t = torch.from_numpy(temp).to(dev)
+    lf = apply_top_k_top_p(lf / temp_t.unsqueeze(1), torch.from_numpy(top_k).to(dev),
+                           torch.from_numpy(top_p).to(dev)).contiguous()
+    ids, _ = ops.argmax_sample(lf, torch.from_numpy(draw).to(dev), torch.from_numpy(seeds).to(dev))
+    return ids
 
 
 def compute_logprobs(logits: torch.Tensor, token_ids: torch.Tensor, k: int):

@@ -19,6 +19,7 @@ class SamplingParams:
     ignore_eos: bool = False
     stop_token_ids: Optional[list[int]] = None
     stop: Optional[list[str]] = None
+    include_stop_str_in_output: bool = False
     logprobs: Optional[int] = None
     prompt_logprobs: Optional[int] = None
     seed: Optional[int] = None

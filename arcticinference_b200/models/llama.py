@@ -120,6 +120,9 @@ class LlamaModel:
         self.inv_freq = compute_inv_freq(cfg, self.device)
         self.scale = 1.0 / math.sqrt(self.D)
         self.n_kv_layers = cfg.num_key_value_layers if cfg.is_swiftkv else cfg.num_hidden_layers
+        # fp8 weights with per-token activation scales: the norm and SiLU kernels that feed the
+        # linear layers emit quantised rows directly (set by quantize_model_fp8)
+        self.act_quant = False
 
     # ------------------------------------------------------------------ weights
     def kv_head_of_block(self, p: int) -> range:
@@ -249,7 +252,7 @@ class LlamaForCausalLM(LlamaModel):
     def _mlp_block(self, lw, x, mode):
         gu = ops.linear(x, self._gu_w(lw, mode))
         nblk = self.n_stored if (mode == "sp" or self.n_stored == 1) else 1
-        act = ops.silu_mul_blocked(gu, nblk)
+        act = ops.silu_mul_blocked(gu, nblk, quant=self.act_quant)
         return self._linear_reduce(act, self._down_w(lw, mode), mode)
 
     def _linear_reduce(self, x, w, mode):
@@ -275,17 +278,18 @@ class LlamaForCausalLM(LlamaModel):
     def _run_layers(self, lo, hi, h, residual, batch, kv, mode, meta, positions, slots,
                     q_only=False, merged_first=False):
         eps = self.cfg.rms_norm_eps
+        aq = self.act_quant
         for l in range(lo, hi):
             lw = self.layers[l]
             if residual is None:
                 residual = h
-                x = ops.rmsnorm(h, lw.input_norm, eps)
+                x = ops.rmsnorm(h, lw.input_norm, eps, quant=aq)
             elif merged_first and l == lo:
-                x = ops.rmsnorm(residual, lw.input_norm, eps)
+                x = ops.rmsnorm(residual, lw.input_norm, eps, quant=aq)
             else:
-                x = ops.rmsnorm(h, lw.input_norm, eps, residual=residual)
+                x = ops.rmsnorm(h, lw.input_norm, eps, residual=residual, quant=aq)
             h = self._attention_block(lw, x, batch, kv, l, mode, meta, positions, slots, q_only)
-            x = ops.rmsnorm(h, lw.post_norm, eps, residual=residual)
+            x = ops.rmsnorm(h, lw.post_norm, eps, residual=residual, quant=aq)
             h = self._mlp_block(lw, x, mode)
         return h, residual
 

@@ -1,4 +1,14 @@
-"""Block-scaled fp8 weights (e4m3, one fp32 scale per 128 x 128 block).
+"""fp8 (e4m3) weights in two scale layouts.
+
+:class:`Fp8RowWeight`: one fp32 scale per output feature; activations are quantised per token on
+the fly (the "FP8-dynamic" format of the checkpoints the reference benchmarks,
+tests/benchmarks/benchmark_utils.py:22-89; per-tensor and per-channel weight scales of
+arctic_inference/vllm/spec_dec/fp8.py:140-180 are special cases). The K loop then needs no
+rescaling, so the tensor cores run the whole product at the fp8 rate and the scales are applied
+once in the epilogue. This is what ``quantization="fp8"`` produces unless the block layout is
+asked for.
+
+:class:`Fp8Weight`: block-scaled, one fp32 scale per 128 x 128 block.
 
 :class:`Fp8Weight` behaves like the [N, K] matrix it stands for as far as the model code
 needs: ``shape``, row slices and column slices on 128 boundaries (the tensor-parallel shard
@@ -69,6 +79,107 @@ class Fp8Weight:
         return (self.q.float() * s).to(torch.bfloat16)
 
 
+    def requantize_from(self, dense: torch.Tensor) -> None:
+        """Overwrite codes and scales in place (addresses captured in CUDA graphs stay valid)."""
+        q = quantize_weight_fp8(dense.to(torch.bfloat16))
+        self.q.copy_(q.q)
+        self.scale.copy_(q.scale)
+        if self.shadow is not None:
+            self.shadow.copy_(q.dequantize())
+
+
+class QuantAct:
+    """Activation rows quantised per token: ``q`` e4m3 [M, K], ``scale`` fp32 [M]."""
+
+    __slots__ = ("q", "scale")
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor):
+        self.q = q
+        self.scale = scale
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    @property
+    def device(self):
+        return self.q.device
+
+    @property
+    def is_cuda(self):
+        return self.q.is_cuda
+
+    def dequantize(self) -> torch.Tensor:
+        return (self.q.float() * self.scale[:, None]).to(torch.bfloat16)
+
+
+class Fp8RowWeight(Fp8Weight):
+    """e4m3 codes [N, K] with one fp32 scale per output feature (row). Row slices carry their
+    scales along; column slices (the K shards of row-parallel layers) keep all of them."""
+
+    __slots__ = ()
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor):
+        assert q.dim() == 2 and scale.dim() == 1 and scale.shape[0] == q.shape[0]
+        self.q = q
+        self.scale = scale
+        self.shadow = None
+
+    def __getitem__(self, idx) -> "Fp8RowWeight":
+        if isinstance(idx, slice):
+            rows, cols = idx, slice(None)
+        else:
+            rows, cols = idx
+        a, _, _ = rows.indices(self.q.shape[0])
+        c, _, _ = cols.indices(self.q.shape[1])
+        if a % 4 or c % 16:
+            raise ValueError("fp8 weight slices must start on 16-byte boundaries")
+        return Fp8RowWeight(self.q[rows, cols], self.scale[rows])
+
+    def make_shadow(self) -> None:
+        pass
+
+    def dequantize(self) -> torch.Tensor:
+        return (self.q.float() * self.scale[:, None]).to(torch.bfloat16)
+
+    def requantize_from(self, dense: torch.Tensor) -> None:
+        q = quantize_weight_fp8_row(dense.to(torch.bfloat16))
+        self.q.copy_(q.q)
+        self.scale.copy_(q.scale)
+
+
+def quantize_weight_fp8_row(w: torch.Tensor) -> Fp8RowWeight:
+    """bf16 [N, K] -> e4m3 codes + one scale per row (scale = amax / 448)."""
+    N, K = w.shape
+    if K % 16:
+        raise ValueError("fp8 quantisation needs K to be a multiple of 16, got %d" % K)
+    wf = w.float()
+    scale = wf.abs().amax(dim=1).clamp_min(1e-10) / FP8_MAX
+    q = (wf / scale[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return Fp8RowWeight(q.contiguous(), scale.contiguous())
+
+
+def quant_activation_row_ref(x: torch.Tensor) -> QuantAct:
+    """Per-token dynamic quantisation (PyTorch restatement of quant_fp8_row_kernel)."""
+    xf = x.float()
+    scale = xf.abs().amax(-1).clamp_min(1e-10) / FP8_MAX
+    q = (xf * (1.0 / scale)[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return QuantAct(q, scale)
+
+
+def linear_fp8_row_ref(x, w: Fp8RowWeight, bias=None, residual=None, act=None) -> torch.Tensor:
+    """fp32 oracle of ab200_linear_fp8_row; ``x`` is a bf16 tensor or a :class:`QuantAct`."""
+    xq = x if isinstance(x, QuantAct) else quant_activation_row_ref(x)
+    y = (xq.q.float() @ w.q.float().t()) * xq.scale[:, None] * w.scale[None, :]
+    if bias is not None:
+        y = y + bias.float()
+    if act == "gelu":
+        y = torch.nn.functional.gelu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(torch.bfloat16)
+
+
 def quantize_weight_fp8(w: torch.Tensor) -> Fp8Weight:
     """bf16 [N, K] -> e4m3 codes + per-block scales (scale = amax / 448)."""
     N, K = w.shape
@@ -97,24 +208,30 @@ def model_fp8_weights(model) -> list:
     return out
 
 
-def quantize_model_fp8(model, prefill_shadow="auto") -> None:
-    """Replace the linear weights of a decoder with block-scaled fp8 (embeddings, norms and
-    the LM head stay in bf16, as in the fp8 checkpoints the reference serves).
+def quantize_model_fp8(model, prefill_shadow="auto", scheme: str = "channel") -> None:
+    """Replace the linear weights of a decoder with fp8 (embeddings, norms and the LM head stay
+    in bf16, as in the fp8 checkpoints the reference serves). ``scheme``: "channel" (one scale
+    per output feature, activations per token; the default) or "block" (128 x 128 blocks).
 
     ``prefill_shadow``: True / False / "auto". With "auto" the expanded bf16 copies are kept
     when they take at most SHADOW_MAX_FRACTION of the GPU's memory (an 8B model's 14 GB on a
     180 GB part), otherwise long prefill expands each weight into a shared scratch matrix."""
+    if scheme not in ("channel", "block"):
+        raise ValueError("fp8 scheme must be 'channel' or 'block'")
+    quant = quantize_weight_fp8_row if scheme == "channel" else quantize_weight_fp8
     for lw in model.layers:
         for name in ("wqkv", "wo", "wgu", "wdown"):
             w = getattr(lw, name)
             if isinstance(w, torch.Tensor):
-                setattr(lw, name, quantize_weight_fp8(w))
+                setattr(lw, name, quant(w))
+                del w
     if getattr(model, "wkv_swiftkv", None) is not None and isinstance(model.wkv_swiftkv, torch.Tensor):
-        model.wkv_swiftkv = quantize_weight_fp8(model.wkv_swiftkv)
+        model.wkv_swiftkv = quant(model.wkv_swiftkv)
+    model.act_quant = scheme == "channel"
     on_gpu = torch.cuda.is_available() and model.device.type == "cuda"
     if on_gpu:
         torch.cuda.empty_cache()
-    ws = model_fp8_weights(model)
+    ws = [w for w in model_fp8_weights(model) if not isinstance(w, Fp8RowWeight)]
     if prefill_shadow == "auto":
         need = sum(2 * w.numel() for w in ws)
         total = torch.cuda.get_device_properties(model.device).total_memory if on_gpu else 0

@@ -18,7 +18,7 @@ import torch
 from . import reference as ref
 
 __all__ = [
-    "linear", "linear_fp8", "quant_fp8", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "silu_mul_blocked", "rope_cache",
+    "linear", "linear_fp8", "linear_fp8_row", "quant_fp8", "quant_fp8_row", "gemm_nn", "embedding", "rmsnorm", "layernorm", "silu_mul", "silu_mul_blocked", "rope_cache",
     "gather_rows", "argmax_sample", "AttentionMetadata", "build_attention_metadata", "pick_tile_keys", "plan_attention_work",
     "attention", "attention_contiguous", "check_status", "count_launches", "launch_counter",
 ]
@@ -118,6 +118,63 @@ def quant_fp8(x: torch.Tensor):
     return xq, sx_t
 
 
+def quant_fp8_row(x: torch.Tensor):
+    """bf16 [M, K] -> ``QuantAct`` (e4m3 codes [M, K], one fp32 scale per token)."""
+    from ..models import quant
+    if not x.is_cuda:
+        return quant.quant_activation_row_ref(x)
+    nat = _native()
+    M, K = x.shape
+    assert x.stride(1) == 1
+    xq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    sx = torch.empty(M, dtype=torch.float32, device=x.device)
+    rc = nat.lib().ab200_quant_fp8_row(x.data_ptr(), x.stride(0), xq.data_ptr(), xq.stride(0),
+                                       sx.data_ptr(), M, K, nat.stream_ptr())
+    nat.check(rc, "quant_fp8_row")
+    launch_counter.add(1)
+    return quant.QuantAct(xq, sx)
+
+
+def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_splits: int = 0,
+                   peer=None) -> torch.Tensor:
+    """W8A8 fp8 linear with per-token activation scales and per-feature weight scales:
+    ``x`` is a bf16 tensor (quantised here) or a ``QuantAct``; ``w`` an ``Fp8RowWeight``.
+    ``peer`` = (ptr_array, world, peer_cols, row_off, ldo) scatters the output columns to the
+    ranks' buffers (see ``ab200_linear_bf16_scatter``)."""
+    from ..models import quant
+    if not w.is_cuda:
+        y = quant.linear_fp8_row_ref(x, w, bias, residual, act)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    xq = x if isinstance(x, quant.QuantAct) else quant_fp8_row(x)
+    nat = _native()
+    M, K = xq.q.shape
+    N = w.shape[0]
+    assert w.q.stride(1) == 1 and xq.q.stride(1) == 1 and K == w.shape[1]
+    ws = nat.workspace(w.device)
+    if peer is None:
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=w.device)
+        assert out.stride(1) == 1
+        out_ptr, ldo, pp, world, pcols, poff = out.data_ptr(), out.stride(0), None, 0, 0, 0
+    else:
+        pp, world, pcols, poff, ldo = peer
+        out_ptr = None
+    if M == 0:
+        return out
+    rc = nat.lib().ab200_linear_fp8_row(
+        xq.q.data_ptr(), xq.q.stride(0), xq.scale.data_ptr(), w.q.data_ptr(), w.q.stride(0),
+        w.scale.data_ptr(), out_ptr, ldo, M, N, K, nat.ptr(bias), nat.ptr(residual),
+        residual.stride(0) if residual is not None else 0, _ACT[act], ws.data_ptr(), ws.numel(),
+        force_splits, pp, world, pcols, poff, nat.status_buffer(w.device).data_ptr(),
+        nat.stream_ptr())
+    nat.check(rc, "linear_fp8_row M=%d N=%d K=%d" % (M, N, K))
+    launch_counter.add(1)
+    return out
+
+
 DEQUANT_MIN_TOKENS = 512
 _dequant_scratch: dict = {}
 
@@ -156,6 +213,9 @@ def fp8_prefers_bf16(w, num_tokens: int) -> bool:
     saves: 105 us against 52 us for the gate/up projection at 128 tokens), up to 128 when it
     does not. Larger steps run the bf16 GEMM on the shadow, or on a copy expanded once per call
     when the step is long enough to amortise that; the W8A8 kernel covers what is left."""
+    from ..models.quant import Fp8RowWeight
+    if isinstance(w, Fp8RowWeight):
+        return False
     shadow = getattr(w, "shadow", None) is not None
     if num_tokens <= (W8A16_SHADOW_CROSSOVER if shadow else W8A16_MAX_TOKENS):
         return False
@@ -168,6 +228,10 @@ def linear_fp8(x: torch.Tensor, w, out=None, force_splits: int = 0, peer=None,
     ``peer`` = (ptr_array, world, peer_cols, row_off, ldo) scatters the output (see
     ``ab200_linear_bf16_scatter``)."""
     from ..models import quant
+    if isinstance(w, quant.Fp8RowWeight):
+        return linear_fp8_row(x, w, out=out, force_splits=force_splits, peer=peer)
+    if isinstance(x, quant.QuantAct):
+        x = x.dequantize()
     if not x.is_cuda:
         y = quant.linear_fp8_ref(x, w)
         if out is not None:
@@ -214,8 +278,13 @@ def linear(x: torch.Tensor, w, bias=None, residual=None, act=None, out=None,
     """``out = act(x @ w.T + bias) + residual``; x [M, K] (row stride free), w [N, K] bf16 or
     an ``Fp8Weight``."""
     if not isinstance(w, torch.Tensor):
+        from ..models.quant import Fp8RowWeight
+        if isinstance(w, Fp8RowWeight):
+            return linear_fp8_row(x, w, bias, residual, act, out=out, force_splits=force_splits)
         assert bias is None and residual is None and act is None
         return linear_fp8(x, w, out=out, force_splits=force_splits)
+    if not isinstance(x, torch.Tensor):   # a quantised activation meeting a bf16 weight
+        x = x.dequantize()
     if not x.is_cuda:
         y = ref.linear(x, w, bias, residual, act)
         if out is not None:
@@ -276,16 +345,35 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0, out=
     return out
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual=None, out=None):
-    """y = RMSNorm(x (+ residual)); ``residual`` (contiguous) is updated in place."""
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual=None, out=None,
+            quant: bool = False):
+    """y = RMSNorm(x (+ residual)); ``residual`` (contiguous) is updated in place. With
+    ``quant`` the result is a ``QuantAct`` (e4m3 rows with one scale per token, produced in the
+    same pass) for an fp8 linear layer."""
     if not x.is_cuda:
         y = ref.rmsnorm(x, weight, eps, residual)
+        if quant:
+            from ..models.quant import quant_activation_row_ref
+            return quant_activation_row_ref(y)
         if out is not None:
             out.copy_(y)
             return out
         return y
     nat = _native()
     T, H = x.shape
+    if quant:
+        from ..models.quant import QuantAct
+        if residual is not None:
+            assert residual.is_contiguous()
+        yq = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=x.device)
+        sy = torch.empty(T, dtype=torch.float32, device=x.device)
+        rc = nat.lib().ab200_rmsnorm_quant(x.data_ptr(), x.stride(0), nat.ptr(residual),
+                                           weight.data_ptr(), yq.data_ptr(), yq.stride(0),
+                                           sy.data_ptr(), None, 0, T, H, float(eps),
+                                           nat.stream_ptr())
+        nat.check(rc, "rmsnorm_quant")
+        launch_counter.add(1)
+        return QuantAct(yq, sy)
     if out is None:
         out = torch.empty(T, H, dtype=x.dtype, device=x.device)
     if residual is not None:
@@ -314,14 +402,30 @@ def layernorm(x, gamma, beta, eps: float, residual=None):
     return out
 
 
-def silu_mul_blocked(x: torch.Tensor, nblk: int = 1, out=None):
-    """x: [T, nblk * 2 * I] as nblk blocks of (gate | up) -> [T, nblk * I]."""
+def silu_mul_blocked(x: torch.Tensor, nblk: int = 1, out=None, quant: bool = False):
+    """x: [T, nblk * 2 * I] as nblk blocks of (gate | up) -> [T, nblk * I]; with ``quant`` a
+    ``QuantAct`` of the same values (one scale per token over the whole output row)."""
     if not x.is_cuda:
-        return ref.silu_mul_blocked(x, nblk)
+        y = ref.silu_mul_blocked(x, nblk)
+        if quant:
+            from ..models.quant import quant_activation_row_ref
+            return quant_activation_row_ref(y)
+        return y
     nat = _native()
     assert x.is_contiguous()
     T, width = x.shape
     inter = width // (2 * nblk)
+    if quant and nblk * inter <= 32768:
+        from ..models.quant import QuantAct
+        oq = torch.empty(T, nblk * inter, dtype=torch.float8_e4m3fn, device=x.device)
+        so = torch.empty(T, dtype=torch.float32, device=x.device)
+        rc = nat.lib().ab200_silu_mul_quant(x.data_ptr(), oq.data_ptr(), oq.stride(0),
+                                            so.data_ptr(), T, inter, nblk, nat.stream_ptr())
+        nat.check(rc, "silu_mul_quant")
+        launch_counter.add(1)
+        return QuantAct(oq, so)
+    if quant:
+        return quant_fp8_row(silu_mul_blocked(x, nblk))
     if out is None:
         out = torch.empty(T, nblk * inter, dtype=x.dtype, device=x.device)
     rc = nat.lib().ab200_silu_mul(x.data_ptr(), out.data_ptr(), T, inter, nblk, nat.stream_ptr())

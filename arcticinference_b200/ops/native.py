@@ -62,6 +62,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_linear_w8a16": (I, [P, LL, P, LL, P, LL, P, LL, I, I, I, P, SZ, I, P, I, I, LL, P, P]),
         "ab200_linear_fp8": (I, [P, LL, P, LL, P, LL, P, LL, P, LL, I, I, I, P, SZ, I, P, I, I, LL,
                                  P, P]),
+        "ab200_linear_fp8_row": (I, [P, LL, P, P, LL, P, P, LL, I, I, I, P, P, LL, I, P, SZ, I, P,
+                                     I, I, LL, P, P]),
+        "ab200_quant_fp8_row": (I, [P, LL, P, LL, P, LL, I, P]),
+        "ab200_rmsnorm_quant": (I, [P, LL, P, P, P, LL, P, P, LL, LL, I, F, P]),
+        "ab200_silu_mul_quant": (I, [P, P, LL, P, LL, I, I, P]),
         "ab200_spec_ln": (I, [P, LL, P, P, P, LL, LL, I, F, F, P]),
         "ab200_mlp_spec_step": (I, [P, LL, P, P, F, P, P, P, LL, LL, I, F, I, P]),
         "ab200_sum_lstm": (I, [P, LL, P, I, P, F, P, LL, P, P, P, P, P, P, LL, LL, I, F, I, P]),

@@ -144,7 +144,7 @@ class FusedCommunicator(Communicator):
         s = self.topo.sp_rank
         if not isinstance(wqkv, torch.Tensor) and ops.fp8_prefers_bf16(wqkv, n):
             wqkv = ops.dequant_fp8(wqkv)          # bf16 shadow, or expanded once for long prefill
-        if not isinstance(wqkv, torch.Tensor):   # block-scaled fp8 weights
+        if not isinstance(wqkv, torch.Tensor):   # fp8 weights
             ops.linear_fp8(x_local, wqkv, peer=(self._qkv_ptrs, self.sp, blk_rows, s * n, blk_rows))
             self.device_barrier()
             return self._view("qkv", N, blk_rows)

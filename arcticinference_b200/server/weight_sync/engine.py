@@ -10,7 +10,7 @@ stateless group and pynccl play this role).
 Stream layout (sender rank 0 -> receiver rank 1):
 
     header   int64[2]  = (MAGIC, number of plan bytes)
-    plan     uint8[n]  = pickled TransferSchedule
+    plan     uint8[n]  = the TransferSchedule as UTF-8 JSON (TransferSchedule.to_json)
     direct tensors, one message each, in plan order
     buckets, one uint8 message each; the receiver keeps two bucket buffers so that bucket
              i+1 is in flight while the tensors of bucket i are being loaded
@@ -22,7 +22,6 @@ Stream layout (sender rank 0 -> receiver rank 1):
 from __future__ import annotations
 
 import logging
-import pickle
 from datetime import timedelta
 from typing import Callable, Iterator, Optional
 
@@ -35,6 +34,7 @@ logger = logging.getLogger(__name__)
 
 MAGIC = 0x41423230305753  # "AB200WS"
 DEFAULT_TIMEOUT_S = 120.0
+MAX_PLAN_BYTES = 64 << 20
 
 
 class Alias(str):
@@ -96,7 +96,7 @@ class Channel:
 def send_stream(ch: Channel, tensors: dict, schedule: TransferSchedule) -> int:
     """Send ``tensors`` (name -> tensor on ``ch.device`` or elsewhere) following ``schedule``.
     Returns the receiver's count of applied tensors."""
-    plan = pickle.dumps(schedule)
+    plan = schedule.to_json().encode("utf-8")
     ch.send_ints(MAGIC, len(plan))
     ch.send_bytes(plan)
     for m in schedule.direct:
@@ -133,7 +133,9 @@ def receive_stream(ch: Channel, direct_target: Optional[Callable] = None) -> Ite
     magic, n = ch.recv_ints(2)
     if magic != MAGIC:
         raise RuntimeError("weight stream: bad magic %x" % magic)
-    schedule: TransferSchedule = pickle.loads(ch.recv_bytes(n))
+    if n < 0 or n > MAX_PLAN_BYTES:
+        raise RuntimeError("weight stream: plan of %d bytes refused" % n)
+    schedule = TransferSchedule.from_json(ch.recv_bytes(n).decode("utf-8"))
     for m in schedule.direct:
         dst = direct_target(m) if direct_target is not None else None
         ok = dst is not None and tuple(dst.shape) == tuple(m.shape) and \

@@ -115,6 +115,63 @@ class TransferSchedule:
     def max_bucket_bytes(self) -> int:
         return max([b.nbytes for b in self.buckets] + [0])
 
+    # The plan crosses the wire as JSON text (never as pickled objects: the receiver must not
+    # execute what a peer sends). Tensor entries use the field names of the reference's bucket
+    # metadata, {"name", "shape", "dtype", "offset", "nbytes"}
+    # (arctic_inference/server/weight_sync/engine.py:408-429).
+    def to_json(self) -> str:
+        import json
+
+        def entry(m: TensorMeta, offset=None) -> dict:
+            d = {"name": m.name, "shape": [int(x) for x in m.shape], "dtype": m.dtype,
+                 "nbytes": m.nbytes}
+            if offset is not None:
+                d["offset"] = int(offset)
+            if m.alias_of is not None:
+                d["alias_of"] = m.alias_of
+            return d
+
+        return json.dumps({
+            "version": 1, "bucket_size": int(self.bucket_size),
+            "buckets": [{"nbytes": int(b.nbytes),
+                         "tensors": [entry(s.meta, s.offset) for s in b.slots]}
+                        for b in self.buckets],
+            "direct": [entry(m) for m in self.direct],
+            "aliases": [entry(m) for m in self.aliases]})
+
+    @classmethod
+    def from_json(cls, text) -> "TransferSchedule":
+        """Parses and validates a plan received from a peer: known dtypes, non-negative
+        sizes, slots inside their bucket, byte counts that match shape x dtype."""
+        import json
+        d = json.loads(text)
+        if not isinstance(d, dict) or d.get("version") != 1:
+            raise ValueError("weight stream: unknown plan format")
+
+        def meta(e: dict, direct: bool = False) -> TensorMeta:
+            if e["dtype"] not in _DTYPES:
+                raise ValueError("weight stream: unknown dtype %r" % (e["dtype"],))
+            shape = tuple(int(x) for x in e["shape"])
+            if any(x < 0 for x in shape):
+                raise ValueError("weight stream: negative dimension in %r" % (e["name"],))
+            m = TensorMeta(str(e["name"]), shape, e["dtype"], direct, e.get("alias_of"))
+            if int(e.get("nbytes", m.nbytes)) != m.nbytes:
+                raise ValueError("weight stream: byte count of %r does not match its shape" % m.name)
+            return m
+
+        buckets = []
+        for b in d["buckets"]:
+            bk = Bucket(int(b["nbytes"]), [])
+            for e in b["tensors"]:
+                m = meta(e)
+                off = int(e["offset"])
+                if off < 0 or off % ALIGN or off + m.nbytes > bk.nbytes:
+                    raise ValueError("weight stream: %r does not fit its bucket" % m.name)
+                bk.slots.append(Slot(m, off))
+            buckets.append(bk)
+        return cls(buckets, [meta(e, True) for e in d["direct"]],
+                   [meta(e) for e in d["aliases"]], int(d["bucket_size"]))
+
 
 def find_aliases(named: dict) -> dict:
     """name -> first name that shares its storage (tied embeddings)."""

@@ -105,14 +105,9 @@ def export_llama_state(model) -> Iterator:
 
 
 def requantize_into(dst, dense: torch.Tensor) -> None:
-    """Overwrite an ``Fp8Weight`` in place with the block-quantised ``dense`` matrix (codes,
-    scales and the bf16 prefill shadow keep their addresses, so captured graphs stay valid)."""
-    from ...models.quant import quantize_weight_fp8
-    q = quantize_weight_fp8(dense.to(torch.bfloat16))
-    dst.q.copy_(q.q)
-    dst.scale.copy_(q.scale)
-    if dst.shadow is not None:
-        dst.shadow.copy_(q.dequantize())
+    """Overwrite an fp8 weight in place with the re-quantised ``dense`` matrix (codes, scales
+    and a bf16 prefill shadow keep their addresses, so captured graphs stay valid)."""
+    dst.requantize_from(dense)
 
 
 def assign_in_place(dst, src: torch.Tensor):

@@ -25,9 +25,12 @@ import time
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-REFERENCE_UNAVAILABLE = (
-    "reference cannot be installed offline: its build needs nanobind==2.9.2 and grpcio-tools, "
-    "neither is in the wheelhouse (pip install --no-index of the reference fails in cmake)")
+METRIC = "combined tok/s (prompt+generated), Llama-3.1-8B shift-parallel serving"
+
+# Reference arm: which way of running the reference to try first for each GPU count (the rungs
+# are described in baseline/run_reference.py); the others follow in order if it fails.
+REFERENCE_RUNGS = ("plugin", "vllm-tp", "vllm-dp")
+REFERENCE_RUNG_TIMEOUT_S = 1500
 
 
 def parse_args():
@@ -105,6 +108,102 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def run_reference(args, rank, local_rank):
+    """The unmodified reference (baseline/_ref) on the image's vLLM, in a child process whose
+    environment carries nothing of the launcher's rendezvous; none of this package is imported
+    on that path. Only rank 0 gets here: vLLM starts its own worker per GPU."""
+    runner = os.path.join(REPO, "baseline", "run_reference.py")
+    if not os.path.isdir(os.path.join(REPO, "baseline", "_ref", "arctic_inference")):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref holds no copy of the reference (see DESIGN.md, Reference arm)"}))
+        return 0
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK",
+                        "GROUP_WORLD_SIZE", "ROLE_RANK", "ROLE_NAME", "ROLE_WORLD_SIZE",
+                        "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS", "PYTHONPATH")
+           and not k.startswith("TORCHELASTIC_")}
+    rungs = list(REFERENCE_RUNGS)
+    first = os.environ.get("AB200_REFERENCE_RUNG")
+    if first is None:
+        try:
+            with open(os.path.join(REPO, "baseline", "reference_rungs.json")) as f:
+                first = json.load(f).get(str(args.gpus))
+        except (OSError, ValueError):
+            first = None
+    if first in rungs:
+        rungs.remove(first)
+        rungs.insert(0, first)
+    if args.gpus == 1:
+        rungs = [r for r in rungs if r != "vllm-dp"]
+    failures = []
+    for rung in rungs:
+        cmd = [sys.executable, runner, "--rung", rung, "--gpus", str(args.gpus),
+               "--steps", str(args.steps), "--warmup", str(args.warmup),
+               "--requests-per-gpu", str(args.requests_per_gpu),
+               "--input-len", str(args.input_len), "--output-len", str(args.output_len),
+               "--shift-parallel-threshold", str(args.shift_parallel_threshold),
+               "--quantization", str(args.quantization)]
+        if args.max_num_batched_tokens:
+            cmd += ["--max-num-batched-tokens", str(args.max_num_batched_tokens)]
+        clocks = ClockSampler(enabled=not args.no_clocks)
+        clocks.start()
+        log = os.path.join(REPO, "gpurun_out", "reference_%s_n%d.log" % (rung, args.gpus))
+        os.makedirs(os.path.dirname(log), exist_ok=True)
+        try:
+            with open(log, "w") as lf:
+                p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=lf, text=True,
+                                   timeout=REFERENCE_RUNG_TIMEOUT_S, start_new_session=True)
+            rc, out = p.returncode, p.stdout
+        except subprocess.TimeoutExpired as e:
+            rc, out = -1, (e.stdout or "")
+            if isinstance(out, bytes):
+                out = out.decode(errors="replace")
+        clock_info = clocks.stop(local_rank)
+        res = None
+        for ln in reversed(out.strip().splitlines()):
+            if ln.startswith("{"):
+                try:
+                    res = json.loads(ln)
+                    break
+                except ValueError:
+                    pass
+        if rc != 0 or res is None:
+            tail = ""
+            try:
+                with open(log) as lf:
+                    tail = [l for l in lf.read().splitlines() if l.strip()][-1][-300:]
+            except (OSError, IndexError):
+                pass
+            failures.append({"rung": rung, "rc": rc, "last_line": tail})
+            continue
+        n_req = args.requests_per_gpu * args.gpus
+        line = {
+            "impl": "reference", "metric": METRIC, "value": res["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8-weights/bf16-activations (vLLM dynamic fp8)",
+            "data": "synthetic (uniform-random token ids, random-init weights)",
+            "p50_ttft_ms": res["p50_ttft_ms"], "p50_tpot_ms": res["p50_tpot_ms"],
+            "reference_class": {"plugin": "arctic_inference plug-in on vLLM %s" % res["vllm"],
+                                "vllm-tp": "plain vLLM %s, tensor parallel" % res["vllm"],
+                                "vllm-dp": "plain vLLM %s, one engine per GPU" % res["vllm"]}[rung],
+            "config": {"model": "llama-3.1-8b", "global_batch": n_req, "seq_len": args.input_len,
+                       "output_len": args.output_len, "parallelism": res["parallelism"],
+                       "timing": "wall clock around LLM.generate (engine in vLLM's own processes)",
+                       "rungs_failed": failures},
+            "clocks": clock_info,
+            "e2e": {"value": res["value"], "unit": "tokens/s",
+                    "h2d_bytes_per_step": res["h2d_bytes_per_step"],
+                    "d2h_bytes_per_step": res["d2h_bytes_per_step"],
+                    "ms_per_step": res["ms_per_step"]},
+        }
+        print(json.dumps(line))
+        return 0
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "vLLM could not serve the workload on this box: " + json.dumps(failures)}))
+    return 0
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -113,9 +212,7 @@ def main():
     n_gpus = args.gpus
 
     if args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return run_reference(args, rank, local_rank) if rank == 0 else 0
 
     import numpy as np
     import torch
@@ -213,7 +310,7 @@ def main():
         e2e_value = tokens_per_step * args.steps / (e2e_ms / 1000.0)
         line = {
             "impl": "ours",
-            "metric": "combined tok/s (prompt+generated), Llama-3.1-8B shift-parallel serving",
+            "metric": METRIC,
             "value": value, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

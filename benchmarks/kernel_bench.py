@@ -94,6 +94,17 @@ CASES = {
     "gemm_fp8_decode_128": ("gemm_fp8", (128, 28672, 4096)),
     "gemm_fp8_decode_o": ("gemm_fp8", (32, 4096, 4096)),
     "gemm_fp8_decode_down": ("gemm_fp8", (32, 4096, 14336)),
+    # W8A8 with per-token / per-feature scales (activations already quantised, as the fused
+    # norm / SiLU kernels hand them over); "*_w8a8_block" is the block-scaled kernel itself
+    "gemm_fp8row_prefill": ("gemm_fp8row", (8192, 28672, 4096)),
+    "gemm_fp8row_prefill_qkv": ("gemm_fp8row", (8192, 6144, 4096)),
+    "gemm_fp8row_prefill_down": ("gemm_fp8row", (8192, 4096, 14336)),
+    "gemm_fp8row_mid": ("gemm_fp8row", (512, 28672, 4096)),
+    "gemm_fp8row_decode": ("gemm_fp8row", (32, 28672, 4096)),
+    "gemm_fp8row_decode_128": ("gemm_fp8row", (128, 28672, 4096)),
+    "gemm_fp8row_decode_128_down": ("gemm_fp8row", (128, 4096, 14336)),
+    "gemm_fp8row_decode_o": ("gemm_fp8row", (32, 4096, 4096)),
+    "gemm_w8a8_block_prefill": ("gemm_fp8blk", (8192, 28672, 4096)),
     "attn_prefill": ("attn", ([8192], [8192])),
     "attn_prefill_4x2048": ("attn", ([2048] * 4, [2048] * 4)),
     "attn_decode": ("attn", ([1] * 32, [2000] * 32)),
@@ -101,20 +112,34 @@ CASES = {
     "attn_decode_long": ("attn", ([1] * 8, [8000] * 8)),
     "attn_verify": ("attn", ([4] * 32, [2000] * 32)),
     "rmsnorm": ("rmsnorm", (8192, 4096)),
+    "rmsnorm_quant": ("rmsnorm_q", (8192, 4096)),
     "silu_mul": ("silu", (8192, 14336)),
+    "silu_mul_quant": ("silu_q", (8192, 14336)),
+    "quant_fp8_row": ("quant_row", (8192, 4096)),
 }
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=sorted(CASES))
+    ap.add_argument("--case", required=True,
+                    help="one of: %s (or several, comma-separated; 'all' for every case)"
+                         % ", ".join(sorted(CASES)))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-time", action="store_true", help="three plain launches (for ncu)")
     ap.add_argument("--splits", type=int, default=0,
                     help="force the split-K factor of the bf16 GEMM cases (0 = the kernel's choice)")
     a = ap.parse_args()
+    names = sorted(CASES) if a.case == "all" else a.case.split(",")
+    for name in names:
+        if name not in CASES:
+            raise SystemExit("unknown case %r" % name)
+        run_case(a, name)
+        torch.cuda.empty_cache()
+
+
+def run_case(a, case):
     hbm, tf, src = peaks()
-    kind, prm = CASES[a.case]
+    kind, prm = CASES[case]
     if kind == "gemm":
         M, N, K = prm
         nc = copies_for(2 * N * K)
@@ -127,6 +152,21 @@ def main():
         nc = copies_for(N * K)
         x, ws = R(M, K), [quant.quantize_weight_fp8(R(N, K)) for _ in range(nc)]
         fn = lambda i=0: ops.linear(x, ws[i])
+        flops, byts = 2.0 * M * N * K, 2.0 * (M * K + M * N) + 1.0 * N * K
+    elif kind == "gemm_fp8row":
+        from arcticinference_b200.models import quant
+        M, N, K = prm
+        nc = copies_for(N * K)
+        xq = ops.quant_fp8_row(R(M, K))
+        ws = [quant.quantize_weight_fp8_row(R(N, K)) for _ in range(nc)]
+        fn = lambda i=0: ops.linear(xq, ws[i], force_splits=a.splits)
+        flops, byts = 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
+    elif kind == "gemm_fp8blk":
+        from arcticinference_b200.models import quant
+        M, N, K = prm
+        nc = copies_for(N * K)
+        x, ws = R(M, K), [quant.quantize_weight_fp8(R(N, K)) for _ in range(nc)]
+        fn = lambda i=0: ops.linear_fp8(x, ws[i], mode="w8a8")
         flops, byts = 2.0 * M * N * K, 2.0 * (M * K + M * N) + 1.0 * N * K
     elif kind == "attn":
         ql, kl = prm
@@ -141,6 +181,24 @@ def main():
         xs, w, rs = [R(T, H) for _ in range(nc)], R(H), [R(T, H) for _ in range(nc)]
         fn = lambda i=0: ops.rmsnorm(xs[i], w, 1e-5, residual=rs[i])
         flops, byts = 0.0, 4.0 * T * H * 2
+    elif kind == "rmsnorm_q":
+        T, H = prm
+        nc = copies_for(4 * T * H)
+        xs, w, rs = [R(T, H) for _ in range(nc)], R(H), [R(T, H) for _ in range(nc)]
+        fn = lambda i=0: ops.rmsnorm(xs[i], w, 1e-5, residual=rs[i], quant=True)
+        flops, byts = 0.0, 3.0 * T * H * 2 + T * H
+    elif kind == "quant_row":
+        T, H = prm
+        nc = copies_for(2 * T * H)
+        xs = [R(T, H) for _ in range(nc)]
+        fn = lambda i=0: ops.quant_fp8_row(xs[i])
+        flops, byts = 0.0, 3.0 * T * H
+    elif kind == "silu_q":
+        T, I = prm
+        nc = copies_for(4 * T * I)
+        gs = [R(T, 2 * I) for _ in range(nc)]
+        fn = lambda i=0: ops.silu_mul_blocked(gs[i], 1, quant=True)
+        flops, byts = 0.0, 2.0 * T * I * 2 + T * I
     else:
         T, I = prm
         nc = copies_for(4 * T * I)
@@ -152,12 +210,12 @@ def main():
             fn(i % nc)
         torch.cuda.synchronize()
         ops.check_status()
-        print("ran", a.case)
+        print("ran", case)
         return
     ms = timeit(fn, a.iters, copies=nc)
     ops.check_status()
     t = ms / 1e3
-    print(json.dumps({"case": a.case, "splits": a.splits, "us": ms * 1e3, "tflops": flops / t / 1e12,
+    print(json.dumps({"case": case, "splits": a.splits, "us": ms * 1e3, "tflops": flops / t / 1e12,
                       "gbs": byts / t / 1e9, "frac_of_%s_bf16" % src: flops / t / 1e12 / tf,
                       "frac_of_%s_hbm" % src: byts / t / 1e9 / hbm}))
 

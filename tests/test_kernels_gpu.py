@@ -460,3 +460,118 @@ def test_linear_fp8_shard_views():
     _close(ops.linear_fp8(big, w[256:768, :1024], mode="w8a8"),
            _w8a8_ref(big, w[256:768, :1024]), 5e-2, 2e-2)
     ops.check_status()
+
+
+# ------------------------------------------- fp8 with per-token / per-feature scales (W8A8)
+def _row_ref(xq, w, **kw):
+    """fp32 product of the codes the quantiser produced (it has its own test) and the weight's
+    codes, scaled per token and per feature."""
+    return quant.linear_fp8_row_ref(xq, w, **kw)
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (37, 1024), (5, 4096), (3, 14336), (2, 28672), (9, 136)])
+def test_quant_fp8_row_matches_reference(M, K):
+    x = _rand(M, K, scale=2.0)
+    got = ops.quant_fp8_row(x)
+    want = quant.quant_activation_row_ref(x)
+    _close(got.scale, want.scale, 1e-9, 1e-6)
+    diff = (got.q.float() - want.q.float()).abs()
+    assert float((diff > 0).float().mean()) < 0.01
+    _close(got.dequantize(), x, 0.04 * float(x.float().abs().max()), 0.07)
+
+
+@pytest.mark.parametrize("T,H,res", [(33, 4096, True), (5, 8192, True), (7, 768, False),
+                                     (3, 2048, True), (2, 5120, True), (1, 64, False)])
+def test_rmsnorm_quant_matches_unfused(T, H, res):
+    x, w = _rand(T, H), _rand(H, scale=0.5) + 1.0
+    r1 = _rand(T, H) if res else None
+    r2 = r1.clone() if res else None
+    got = ops.rmsnorm(x, w, 1e-5, residual=r1, quant=True)
+    y = ops.rmsnorm(x, w, 1e-5, residual=r2)
+    want = ops.quant_fp8_row(y)
+    ops.check_status()
+    if res:
+        assert torch.equal(r1, r2)
+    _close(got.scale, want.scale, 1e-9, 1e-6)
+    assert torch.equal(got.q.view(torch.uint8), want.q.view(torch.uint8))
+
+
+@pytest.mark.parametrize("T,inter,nblk", [(9, 14336, 1), (4, 1792, 8), (3, 28672, 1), (5, 256, 2),
+                                          (2, 3584, 8)])
+def test_silu_mul_quant_matches_unfused(T, inter, nblk):
+    x = _rand(T, nblk * 2 * inter)
+    got = ops.silu_mul_blocked(x, nblk, quant=True)
+    want = ops.quant_fp8_row(ops.silu_mul_blocked(x, nblk))
+    ops.check_status()
+    _close(got.scale, want.scale, 1e-9, 1e-6)
+    assert torch.equal(got.q.view(torch.uint8), want.q.view(torch.uint8))
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (8, 4096, 4096), (32, 6144, 4096), (100, 1024, 512), (128, 4096, 14336), (1, 256, 128),
+    (129, 256, 256), (200, 4096, 4096), (512, 1024, 1024), (2048, 6144, 4096),
+    (1000, 28672, 4096), (300, 384, 1792), (700, 136, 80), (17, 4096, 14336),
+])
+def test_linear_fp8_row(M, N, K):
+    x = _rand(M, K)
+    w = quant.quantize_weight_fp8_row(_rand(N, K, scale=1.0 / math.sqrt(K)))
+    xq = ops.quant_fp8_row(x)
+    y = ops.linear(xq, w)
+    ops.check_status()
+    _close(y, _row_ref(xq, w), 3e-2, 2e-2)
+    # bf16 activations are quantised on the way in; against the unquantised product the error
+    # is the fp8 rounding of both operands
+    y2 = ops.linear(x, w)
+    ops.check_status()
+    assert torch.equal(y, y2)
+    _close(y2, ref.linear(x, w.dequantize()), 8e-2, 5e-2)
+
+
+@pytest.mark.parametrize("M", [5, 128, 200, 700])
+def test_linear_fp8_row_epilogue(M):
+    N, K = 768, 3072
+    xq = ops.quant_fp8_row(_rand(M, K))
+    w = quant.quantize_weight_fp8_row(_rand(N, K, scale=1.0 / math.sqrt(K)))
+    b, r = _rand(N), _rand(M, N)
+    _close(ops.linear(xq, w, bias=b), _row_ref(xq, w, bias=b), 3e-2, 2e-2)
+    _close(ops.linear(xq, w, bias=b, act="gelu"), _row_ref(xq, w, bias=b, act="gelu"), 3e-2, 2e-2)
+    _close(ops.linear(xq, w, bias=b, residual=r), _row_ref(xq, w, bias=b, residual=r), 4e-2, 2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_linear_fp8_row_split_k(splits):
+    M, N, K = 24, 1024, 4096
+    xq = ops.quant_fp8_row(_rand(M, K))
+    w = quant.quantize_weight_fp8_row(_rand(N, K, scale=1.0 / math.sqrt(K)))
+    y = ops.linear(xq, w, force_splits=splits)
+    ops.check_status()
+    _close(y, _row_ref(xq, w), 3e-2, 2e-2)
+
+
+def test_linear_fp8_row_shard_views():
+    w = quant.quantize_weight_fp8_row(_rand(2048, 2048, scale=0.03))
+    xk = ops.quant_fp8_row(_rand(64, 2048))
+    rows = w[512:1024]
+    _close(ops.linear(xk, rows), _row_ref(xk, rows), 3e-2, 2e-2)
+    cols = w[:, 1024:2048]          # K shard: strided weight view, all feature scales
+    xs = ops.quant_fp8_row(_rand(300, 1024))
+    _close(ops.linear(xs, cols), _row_ref(xs, cols), 3e-2, 2e-2)
+    _close(ops.linear(xs, w[256:768, :1024]), _row_ref(xs, w[256:768, :1024]), 3e-2, 2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,blk", [(300, 192), (64, 192), (1000, 80)])
+def test_linear_fp8_row_scatter_epilogue_local_destinations(M, blk):
+    import ctypes
+    world, K, off = 2, 512, 7
+    xq = ops.quant_fp8_row(_rand(M, K))
+    w = quant.quantize_weight_fp8_row(_rand(world * blk, K, scale=1.0 / math.sqrt(K)))
+    bufs = [torch.zeros(M + 2 * off, blk, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    ops.linear_fp8_row(xq, w, peer=(ptrs, world, blk, off, blk))
+    ops.check_status()
+    want = _row_ref(xq, w)
+    for j, b in enumerate(bufs):
+        _close(b[off:off + M], want[:, j * blk:(j + 1) * blk], 3e-2, 2e-2)
+        assert float(b[:off].abs().max()) == 0 and float(b[off + M:].abs().max()) == 0

@@ -186,3 +186,27 @@ def test_pool_sync_with_real_workers():
         assert (await pool.close_weight_sync())["status"] == "ok"
         await pool.shutdown()
     asyncio.run(main())
+
+
+def test_transfer_plan_travels_as_validated_json():
+    import json
+    import pytest
+    import torch
+    from arcticinference_b200.server.weight_sync.schedule import TensorMeta, TransferSchedule
+    metas = [TensorMeta.of("model.layers.%d.w" % i, torch.empty(64, 48, dtype=torch.bfloat16))
+             for i in range(5)]
+    metas.append(TensorMeta.of("model.embed", torch.empty(100, 8), direct=True))
+    metas.append(TensorMeta("lm_head", (100, 8), "float32", alias_of="model.embed"))
+    plan = TransferSchedule.build(metas, bucket_size=16 << 10)
+    back = TransferSchedule.from_json(plan.to_json())
+    assert back == plan and len(back.buckets) > 1
+    bad = json.loads(plan.to_json())
+    bad["buckets"][0]["tensors"][0]["offset"] = bad["buckets"][0]["nbytes"]
+    with pytest.raises(ValueError):
+        TransferSchedule.from_json(json.dumps(bad))
+    bad = json.loads(plan.to_json())
+    bad["direct"][0]["dtype"] = "object"
+    with pytest.raises(ValueError):
+        TransferSchedule.from_json(json.dumps(bad))
+    with pytest.raises(ValueError):
+        TransferSchedule.from_json(json.dumps({"version": 2}))
