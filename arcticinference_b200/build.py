@@ -139,6 +139,8 @@ def build_torch_ops(force: bool = False) -> Path:
     from torch.utils import cpp_extension
 
     src = CSRC / "torch" / "torch_bindings.cpp"
+    if os.environ.get("ARCTIC_B200_NO_AUTOBUILD") and TORCH_OPS_LIB.exists() and not force:
+        return TORCH_OPS_LIB
     build_kernels()
     deps = [src, CSRC / "api.h"]
     if not force and TORCH_OPS_LIB.exists() and \

@@ -151,6 +151,21 @@ int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long ro
                             const void* idx, void* dst, long long R, int hidden,
                             cudaStream_t stream);
 
+
+// ---- comm_fused.cu
+int ab200_push_rows(const void* src_a, long long ld_a, const void* src_b, long long ld_b,
+                    long long rows_per_rank, int my_rank, int world, const void* idx,
+                    const void* const* dst_a, const void* const* dst_b, long long R, int hidden,
+                    cudaStream_t stream);
+int ab200_rmsnorm_allgather(const void* x, long long ldx, void* residual, const void* weight,
+                            const void* const* dst, long long row_off, int my_rank, int world,
+                            long long T, int hidden, float eps, cudaStream_t stream);
+size_t ab200_argmax_exchange_slot_bytes(int world, int max_rows);
+int ab200_argmax_exchange(const void* ids, const void* vals, int B, int max_rows,
+                          const void* const* slot_ptrs, const void* const* flag_ptrs, int my_rank,
+                          int world, void* epoch_ctr, void* out_ids, void* out_vals, int* status,
+                          cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,61 +21,17 @@
 // (arctic_inference/vllm/ulysses.py:436-455, vLLM row-parallel all-reduce).
 
 #include "api.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 
 namespace ab200 {
-
-constexpr int kMaxPeers = 16;
-
-struct PeerTable {
-  void* ptr[kMaxPeers];
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// 16-byte load at system scope: data written by another GPU's kernel must not be served
-// from a stale non-coherent cache line left by an earlier read of the same address.
-__device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
 
 // flags: per rank an array unsigned[kMaxPeers] in its heap; flags.ptr[r] is rank r's array.
 // Thread j publishes this rank's epoch into rank j's slot [my_rank] and then waits for
 // rank j's epoch in the local slot [j].
 __global__ void barrier_kernel(PeerTable flags, int my_rank, int world, unsigned int* epoch_ctr,
                                int* status, unsigned long long limit_ns) {
-  __shared__ unsigned int epoch;
-  if (threadIdx.x == 0) epoch = *epoch_ctr + 1;
-  __syncthreads();
-  const unsigned int e = epoch;
-  const int j = threadIdx.x;
-  if (j < world) {
-    __threadfence_system();
-    st_release_sys(reinterpret_cast<unsigned int*>(flags.ptr[j]) + my_rank, e);
-    const unsigned int* mine = reinterpret_cast<const unsigned int*>(flags.ptr[my_rank]) + j;
-    const unsigned long long t0 = globaltimer_ns();
-    unsigned int spins = 0;
-    while ((int)(ld_acquire_sys(mine) - e) < 0) {
-      if ((++spins & 255u) == 0u && globaltimer_ns() - t0 > limit_ns) {
-        report_error(status, kErrPeerFlagTimeout, j, (int)e);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) *epoch_ctr = e;
+  flag_barrier(flags, my_rank, world, epoch_ctr, status, limit_ns);
 }
 
 // out[i] = sum_r part_r[i] (+ residual[i]); 8 bf16 per thread per iteration.
@@ -141,12 +97,6 @@ allreduce_kernel(PeerTable parts, int world, __nv_bfloat16* __restrict__ out,
 //
 // flags layout per rank: unsigned[2][kMaxPeers][kMaxArBlocks], slot [phase][source rank][block].
 constexpr int kMaxArBlocks = 128;
-
-__device__ __forceinline__ void st_v4_global(void* p, const uint4& v) {
-  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
 
 __device__ __forceinline__ bool exchange_flags(const PeerTable& flags, int phase, int my_rank,
                                                int world, int b, unsigned int e, int* status,

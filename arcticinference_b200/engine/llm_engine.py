@@ -53,7 +53,7 @@ class LLMEngine:
                                              tp_rows_per_request(config.speculative) *
                                              config.scheduler.max_num_seqs) + sp)
             comm.setup(max_tokens, max_tp, m.blk_rows, config.model.hidden_size,
-                       sp * m.h * m.D)
+                       sp * m.h * m.D, swiftkv=config.model.is_swiftkv)
         self.runner.load_model()
         self.num_blocks = self.runner.determine_num_blocks()
         self.runner.init_kv_cache(self.num_blocks)

@@ -316,9 +316,14 @@ class LlamaForCausalLM(LlamaModel):
             return ops.rmsnorm(h, self.norm, eps, residual=residual)
 
         # ---- SwiftKV: one projection produces K/V of all later layers for every token
-        s = ops.rmsnorm(h, self.norm_swiftkv, eps, residual=residual)  # residual <- h + residual
         if mode == "sp" and comm is not None and comm.sp > 1:
-            s, residual = comm.swiftkv_boundary(s, residual)  # later layers run tensor-parallel
+            # later layers run tensor-parallel: every rank needs the normalised state of all
+            # tokens (for their K/V) and the residual of the sampled rows
+            s, x_sel = comm.swiftkv_boundary(h, residual, self.norm_swiftkv, eps,
+                                             batch.logits_indices)
+        else:
+            s = ops.rmsnorm(h, self.norm_swiftkv, eps, residual=residual)  # residual <- h + residual
+            x_sel = ops.gather_rows(residual, batch.logits_indices)
         n_later = cfg.num_hidden_layers - self.n_kv_layers
         wkv = self.wkv_swiftkv
         rows_blk = n_later * 2 * self.hkv * self.D
@@ -331,7 +336,6 @@ class LlamaForCausalLM(LlamaModel):
         tables = kv.pointer_tables(first, n_later) if hasattr(kv, "pointer_tables") else None
         ops.kv_bulk_write(kv_all, positions, slots, self.inv_freq, kv.k[first:first + n_later],
                           kv.v[first:first + n_later], self.hkv, self.D, tables=tables)
-        x_sel = ops.gather_rows(residual, batch.logits_indices)
         h, residual = self._run_layers(self.n_kv_layers, cfg.num_hidden_layers, None, x_sel, batch,
                                        kv, "tp", batch.sel_attn_meta, batch.sel_positions, None,
                                        q_only=True, merged_first=True)

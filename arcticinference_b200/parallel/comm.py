@@ -146,15 +146,18 @@ class Communicator:
         self.stats["all_reduce"] += 1
         return buf[0].to(h_local.dtype), buf[1].to(h_local.dtype).contiguous()
 
-    def swiftkv_boundary(self, s_local, res_local):
-        """All ranks need the SwiftKV-normalised hidden state and the residual of every
-        token (arctic_inference/vllm/swiftkv/llama_swiftkv.py:236-241)."""
+    def swiftkv_boundary(self, h_local, res_local, weight, eps: float, idx):
+        """``res_local += h_local``; returns the SwiftKV-normalised hidden state of every token
+        of the step ([N, H], on all ranks) and the updated residual rows of the sampled tokens
+        ``idx`` (arctic_inference/vllm/swiftkv/llama_swiftkv.py:236-241 gathers both tensors
+        whole; the later layers only read the residual at the sampled rows)."""
+        s_local = ops.rmsnorm(h_local, weight, eps, residual=res_local)
         n, H = s_local.shape
-        out = torch.empty(2, self.sp * n, H, dtype=s_local.dtype, device=s_local.device)
-        dist.all_gather_into_tensor(out[0], s_local.contiguous(), group=self.sp_group)
-        dist.all_gather_into_tensor(out[1], res_local.contiguous(), group=self.sp_group)
-        self.stats["all_gather"] += 2
-        return out[0], out[1]
+        out = torch.empty(self.sp * n, H, dtype=s_local.dtype, device=s_local.device)
+        dist.all_gather_into_tensor(out, s_local.contiguous(), group=self.sp_group)
+        self.stats["all_gather"] += 1
+        _, x_sel = self.gather_rows_all(res_local, res_local, idx)
+        return out, x_sel
 
     # ---------------------------------------------------------------- reductions
     def all_reduce_full(self, t: torch.Tensor) -> torch.Tensor:

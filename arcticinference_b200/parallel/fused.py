@@ -62,12 +62,15 @@ class FusedCommunicator(Communicator):
 
     # ------------------------------------------------------------------ heap
     def setup(self, max_tokens: int, max_tp_tokens: int, blk_rows: int, hidden: int,
-              attn_cols: int) -> None:
+              attn_cols: int, swiftkv: bool = False) -> None:
         """Allocate and exchange the symmetric heap. ``max_tokens``: largest (padded) step;
-        ``max_tp_tokens``: largest tensor-parallel step; ``attn_cols`` = SP * h * D."""
+        ``max_tp_tokens``: largest tensor-parallel step (also bounds the rows a step samples);
+        ``attn_cols`` = SP * h * D; ``swiftkv``: the model needs the boundary buffer that
+        holds the normalised hidden state of every token of a step."""
         import torch.distributed._symmetric_memory as symm_mem
         W = self.ways
         n_local = (max_tokens + self.sp - 1) // self.sp
+        self._amx_rows = max(max_tp_tokens, 1)
         sizes = {
             "flags": 4096,
             "qkv": max_tokens * blk_rows * 2 if self.sp > 1 else 0,
@@ -77,6 +80,12 @@ class FusedCommunicator(Communicator):
             "res0": max_tp_tokens * hidden * 2,
             "res1": max_tp_tokens * hidden * 2,
             "ar2_flags": 2 * 16 * 128 * 4,
+            # sampled rows handed to every rank (hidden state, residual), arg-max candidates,
+            # and the SwiftKV boundary's all-token buffer
+            "rows_a": max_tp_tokens * hidden * 2 if self.sp > 1 else 0,
+            "rows_b": max_tp_tokens * hidden * 2 if self.sp > 1 else 0,
+            "amx": 2 * W * self._amx_rows * 16,
+            "x4": max_tokens * hidden * 2 if (self.sp > 1 and swiftkv) else 0,
         }
         off, layout = 0, {}
         for k, v in sizes.items():
@@ -98,6 +107,10 @@ class FusedCommunicator(Communicator):
         self._res_ptrs = [_ptr_array([b + layout[k][0] for b in self._peer_base])
                           for k in ("res0", "res1")]
         self._ar2_flag_ptrs = _ptr_array([b + layout["ar2_flags"][0] for b in self._peer_base])
+        self._rows_ptrs = [_ptr_array([b + layout[k][0] for b in self._peer_base])
+                           for k in ("rows_a", "rows_b")]
+        self._amx_ptrs = _ptr_array([b + layout["amx"][0] for b in self._peer_base])
+        self._x4_ptrs = _ptr_array([b + layout["x4"][0] for b in self._peer_base])
         self._ar2_epochs = torch.zeros(128, dtype=torch.int32, device=self.device)
         mode = os.environ.get("AB200_ALLREDUCE", "auto").lower()
         if mode not in ("auto", "oneshot", "twoshot"):
@@ -117,6 +130,9 @@ class FusedCommunicator(Communicator):
         native.declare("ab200_allreduce", I, [P, I, P, P, LL, P])
         native.declare("ab200_allreduce2", I, [P, P, P, P, I, I, LL, P, P])
         native.declare("ab200_gather_rows_peers", I, [P, I, LL, P, P, LL, I, P])
+        native.declare("ab200_push_rows", I, [P, LL, P, LL, LL, I, I, P, P, P, LL, I, P])
+        native.declare("ab200_rmsnorm_allgather", I, [P, LL, P, P, P, LL, I, I, LL, I, F, P])
+        native.declare("ab200_argmax_exchange", I, [P, P, I, I, P, P, I, I, P, P, P, P, P])
         native.declare("ab200_linear_bf16_scatter", I, [P, LL, P, LL, P, I, I, LL, LL, I, I, I, P, P])
         native.declare("ab200_attention_scatter", I, [P, LL, P, P, LL, I, P, I, P, I, P, I, LL, I, I,
                                                       I, F, P, I, I, LL, P, P, I, P, P])
@@ -175,6 +191,60 @@ class FusedCommunicator(Communicator):
         ops.launch_counter.add(2 if meta.max_splits > 1 else 1)
         self.device_barrier()
         return self._view("attn", n, cols)
+
+    # ------------------------------------------------- sampled rows, SwiftKV boundary, arg-max
+    def _push_rows(self, a_local, b_local, idx) -> None:
+        n = a_local.shape[0]
+        rc = self._lib.ab200_push_rows(
+            a_local.data_ptr(), a_local.stride(0), native.ptr(b_local),
+            b_local.stride(0) if b_local is not None else 0, n, self.topo.sp_rank, self.sp,
+            idx.data_ptr(), self._rows_ptrs[0], self._rows_ptrs[1] if b_local is not None else None,
+            idx.numel(), a_local.shape[1], native.stream_ptr())
+        native.check(rc, "push_rows")
+        ops.launch_counter.add(1)
+
+    def gather_rows_all(self, h_local, res_local, idx):
+        """The owner of each sampled token stores its hidden-state and residual rows into every
+        rank's staging buffers (peer stores); after the barrier all ranks hold all rows."""
+        B, H = idx.numel(), h_local.shape[1]
+        assert res_local.stride(1) == 1 and h_local.stride(1) == 1
+        self._push_rows(h_local, res_local, idx)
+        self.device_barrier()
+        self.stats["fused_row_gather"] = self.stats.get("fused_row_gather", 0) + 1
+        return self._view("rows_a", B, H), self._view("rows_b", B, H)
+
+    def swiftkv_boundary(self, h_local, res_local, weight, eps: float, idx):
+        """The boundary norm writes its rows into every rank's all-token buffer as it produces
+        them; the residual travels for the sampled rows only."""
+        n, H = h_local.shape
+        N = n * self.sp
+        s = self.topo.sp_rank
+        assert res_local.is_contiguous()
+        rc = self._lib.ab200_rmsnorm_allgather(
+            h_local.data_ptr(), h_local.stride(0), res_local.data_ptr(), weight.data_ptr(),
+            self._x4_ptrs, s * n, s, self.sp, n, H, float(eps), native.stream_ptr())
+        native.check(rc, "rmsnorm_allgather")
+        ops.launch_counter.add(1)
+        self._push_rows(res_local, None, idx)
+        self.device_barrier()
+        self.stats["fused_boundary"] = self.stats.get("fused_boundary", 0) + 1
+        return self._view("x4", N, H), self._view("rows_a", idx.numel(), H)
+
+    def argmax_exchange(self, ids: torch.Tensor, vals: torch.Tensor) -> torch.Tensor:
+        """Every rank stores its (value, token) candidates into all ranks' slots, the ranks
+        meet at a flag barrier inside the same kernel, and each picks the best locally."""
+        B = ids.numel()
+        if B > self._amx_rows:
+            return super().argmax_exchange(ids, vals)
+        out = torch.empty_like(ids)
+        rc = self._lib.ab200_argmax_exchange(
+            ids.data_ptr(), vals.data_ptr(), B, self._amx_rows, self._amx_ptrs, self._flag_ptrs,
+            self.rank, self.ways, self._epoch_ptr, out.data_ptr(), None,
+            native.status_buffer(self.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "argmax_exchange")
+        ops.launch_counter.add(1)
+        self.stats["fused_argmax"] = self.stats.get("fused_argmax", 0) + 1
+        return out
 
     # --------------------------------------------------------------- reductions
     def reduce_buffer(self, rows: int, cols: int) -> torch.Tensor:

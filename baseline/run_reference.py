@@ -75,7 +75,20 @@ def parse_args():
     ap.add_argument("--seed-offset", type=int, default=0,
                     help="vllm-dp children: which share of the wave this engine serves")
     ap.add_argument("--share", type=int, default=1, help="vllm-dp children: number of shares")
+    ap.add_argument("--result", default=None,
+                    help="write the result line to this file (vLLM logs to stdout as well)")
+    ap.add_argument("--stack-dump-after", type=int, default=0,
+                    help="seconds after which the stacks of this process are dumped to stderr "
+                         "(to see where a run that does not finish is waiting)")
     return ap.parse_args()
+
+
+def emit(args, line: dict) -> None:
+    text = json.dumps(line)
+    if args.result:
+        with open(args.result, "w") as f:
+            f.write(text + "\n")
+    print(text, flush=True)
 
 
 def model_dir():
@@ -97,23 +110,24 @@ def run_dp(args):
                "--requests-per-gpu", str(args.requests_per_gpu),
                "--input-len", str(args.input_len), "--output-len", str(args.output_len),
                "--quantization", args.quantization, "--seed-offset", str(i),
-               "--share", str(args.gpus)]
-        procs.append(subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, text=True))
+               "--share", str(args.gpus),
+               "--result", os.path.join(tempfile.gettempdir(), "ab200_ref_dp_%d.json" % i)]
+        procs.append((subprocess.Popen(cmd, env=env), cmd[-1]))
     lines = []
-    for p in procs:
-        out, _ = p.communicate()
-        if p.returncode != 0:
+    for p, result in procs:
+        if p.wait() != 0:
             raise SystemExit("a data-parallel engine failed (exit %d)" % p.returncode)
-        lines.append(json.loads(out.strip().splitlines()[-1]))
+        with open(result) as f:
+            lines.append(json.loads(f.read()))
     ms = max(l["ms_per_step"] for l in lines)
     tokens = args.gpus * args.requests_per_gpu * (args.input_len + args.output_len)
     ttft = statistics.median(l["p50_ttft_ms"] for l in lines if l["p50_ttft_ms"] is not None)
     tpot = statistics.median(l["p50_tpot_ms"] for l in lines if l["p50_tpot_ms"] is not None)
-    print(json.dumps({"rung": "vllm-dp", "value": tokens / (ms / 1000.0), "ms_per_step": ms,
-                      "p50_ttft_ms": ttft, "p50_tpot_ms": tpot,
-                      "h2d_bytes_per_step": sum(l["h2d_bytes_per_step"] for l in lines),
-                      "d2h_bytes_per_step": sum(l["d2h_bytes_per_step"] for l in lines),
-                      "vllm": lines[0]["vllm"], "parallelism": "dp%d" % args.gpus}))
+    emit(args, {"rung": "vllm-dp", "value": tokens / (ms / 1000.0), "ms_per_step": ms,
+                "p50_ttft_ms": ttft, "p50_tpot_ms": tpot,
+                "h2d_bytes_per_step": sum(l["h2d_bytes_per_step"] for l in lines),
+                "d2h_bytes_per_step": sum(l["d2h_bytes_per_step"] for l in lines),
+                "vllm": lines[0]["vllm"], "parallelism": "dp%d" % args.gpus})
 
 
 def main():
@@ -122,6 +136,9 @@ def main():
         return run_dp(args)
 
     n = args.gpus
+    if args.stack_dump_after > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(args.stack_dump_after, repeat=True, file=sys.stderr)
     os.environ.setdefault("HF_HUB_OFFLINE", "1")
     os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
     os.environ.setdefault("VLLM_NO_USAGE_STATS", "1")
@@ -167,8 +184,13 @@ def main():
         return [{"prompt_token_ids": rng.integers(0, vocab, size=args.input_len).tolist()}
                 for _ in range(n_req)]
 
+    print("[run_reference] engine up, %d warm-up waves of %d requests" % (args.warmup, n_req),
+          file=sys.stderr, flush=True)
     for w in range(args.warmup):
+        t_w = time.perf_counter()
         llm.generate(make_wave(1000 + w), sp, use_tqdm=False)
+        print("[run_reference] warm-up wave %d: %.1f s" % (w, time.perf_counter() - t_w),
+              file=sys.stderr, flush=True)
 
     ttfts, tpots = [], []
     h2d = d2h = 0
@@ -187,12 +209,12 @@ def main():
     wall = time.perf_counter() - t0
 
     tokens = n_req * (args.input_len + args.output_len) * args.steps
-    print(json.dumps({
+    emit(args, {
         "rung": args.rung, "value": tokens / wall, "ms_per_step": 1000.0 * wall / args.steps,
         "p50_ttft_ms": 1000 * statistics.median(ttfts) if ttfts else None,
         "p50_tpot_ms": 1000 * statistics.median(tpots) if tpots else None,
         "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps,
-        "vllm": vllm.__version__, "parallelism": parallelism}), flush=True)
+        "vllm": vllm.__version__, "parallelism": parallelism})
     # vLLM's worker processes are torn down with the interpreter; leave without waiting for
     # destructors that have hung on some versions
     sys.stdout.flush()

@@ -30,7 +30,8 @@ METRIC = "combined tok/s (prompt+generated), Llama-3.1-8B shift-parallel serving
 # Reference arm: which way of running the reference to try first for each GPU count (the rungs
 # are described in baseline/run_reference.py); the others follow in order if it fails.
 REFERENCE_RUNGS = ("plugin", "vllm-tp", "vllm-dp")
-REFERENCE_RUNG_TIMEOUT_S = 1500
+# seconds; together they stay inside the half hour a caller may give the whole arm
+REFERENCE_RUNG_TIMEOUT_S = {"plugin": 420, "vllm-tp": 900, "vllm-dp": 400}
 
 
 def parse_args():
@@ -108,6 +109,30 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def _run_bounded(cmd, env, log, limit_s) -> int:
+    """Run a child in its own process group with stdout and stderr in ``log``; on expiry the
+    whole group is ended (vLLM's engine and worker processes included). Returns its exit code,
+    -1 after a timeout."""
+    import signal
+    with open(log, "w") as lf:
+        p = subprocess.Popen(cmd, env=env, stdout=lf, stderr=subprocess.STDOUT,
+                             start_new_session=True)
+        try:
+            return p.wait(timeout=limit_s)
+        except subprocess.TimeoutExpired:
+            for sig in (signal.SIGTERM, signal.SIGKILL):
+                try:
+                    os.killpg(p.pid, sig)
+                except ProcessLookupError:
+                    break
+                try:
+                    p.wait(timeout=20)
+                    break
+                except subprocess.TimeoutExpired:
+                    continue
+            return -1
+
+
 def run_reference(args, rank, local_rank):
     """The unmodified reference (baseline/_ref) on the image's vLLM, in a child process whose
     environment carries nothing of the launcher's rendezvous; none of this package is imported
@@ -148,25 +173,19 @@ def run_reference(args, rank, local_rank):
         clocks = ClockSampler(enabled=not args.no_clocks)
         clocks.start()
         log = os.path.join(REPO, "gpurun_out", "reference_%s_n%d.log" % (rung, args.gpus))
+        result_file = log[:-4] + ".json"
         os.makedirs(os.path.dirname(log), exist_ok=True)
-        try:
-            with open(log, "w") as lf:
-                p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=lf, text=True,
-                                   timeout=REFERENCE_RUNG_TIMEOUT_S, start_new_session=True)
-            rc, out = p.returncode, p.stdout
-        except subprocess.TimeoutExpired as e:
-            rc, out = -1, (e.stdout or "")
-            if isinstance(out, bytes):
-                out = out.decode(errors="replace")
+        if os.path.exists(result_file):
+            os.remove(result_file)
+        cmd += ["--result", result_file, "--stack-dump-after", "600"]
+        rc = _run_bounded(cmd, env, log, REFERENCE_RUNG_TIMEOUT_S[rung])
         clock_info = clocks.stop(local_rank)
         res = None
-        for ln in reversed(out.strip().splitlines()):
-            if ln.startswith("{"):
-                try:
-                    res = json.loads(ln)
-                    break
-                except ValueError:
-                    pass
+        try:
+            with open(result_file) as f:
+                res = json.loads(f.read())
+        except (OSError, ValueError):
+            pass
         if rc != 0 or res is None:
             tail = ""
             try:
