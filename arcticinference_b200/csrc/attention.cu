@@ -9,7 +9,10 @@
 // memory; P V is a second tcgen05.mma whose B operand is the V tile in its
 // natural [key][d] layout (an MN-major descriptor), so nothing is transposed.
 // S is double-buffered in TMEM: QK^T of tile j+1 runs on the tensor core while the
-// softmax warps work on tile j. The output accumulator lives in TMEM as well: P V
+// softmax warps work on tile j. With 128-key tiles P is double-buffered in shared memory as
+// well, so the softmax of tile j+1 does not wait for P(j) V(j) to finish unless it has to
+// rescale O: the tensor core then goes from one product straight into the next.
+// The output accumulator lives in TMEM as well: P V
 // accumulates in place, and a warp rescales its rows of O (tcgen05.ld / multiply /
 // tcgen05.st) only in the tiles where one of its running maxima moved, which after
 // the first few tiles is rare. Key tiles are 128 wide for prefill; decode-shaped
@@ -79,6 +82,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   constexpr uint32_t kHalf = TK * 128;     // bytes of one 64-wide d half of a K/V stage
   constexpr int kChunks = TK / 32;         // 32-column chunks of a row of S
   constexpr uint32_t kTmemCols = (TK == 128) ? 512 : 256;  // 2 S buffers + O
+  constexpr int kPStages = (TK == 128) ? 2 : 1;  // decode tiles share the SM with a second CTA
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -91,7 +95,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t sV = sK + 2 * kKVBytes;     // 2 stages
   const uint32_t sP = sV + 2 * kKVBytes;
   uint8_t* pP = smem + kQBytes + 4 * kKVBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQBytes + 4 * kKVBytes + kPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQBytes + 4 * kKVBytes + kPStages * kPBytes);
   const uint32_t bb = smem_u32(bars);
   // barrier indices
   const uint32_t q_full = bb;
@@ -103,8 +107,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   auto s_empty = [&](int s) { return bb + 8u * (11 + s); };
   auto o_full = [&](int s) { return bb + 8u * (13 + s); };
   auto o_empty = [&](int s) { return bb + 8u * (15 + s); };
-  const uint32_t p_full = bb + 8u * 17;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  auto p_full = [&](int s) { return bb + 8u * (17 + s); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -136,7 +140,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(o_full(s), 1);
       mbar_init(o_empty(s), 4);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full(0), 4);
+    mbar_init(p_full(1), 4);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_q);
@@ -233,12 +238,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         if (!mbar_wait(v_full(st), ph, abort_flag, p.status, 630 + st, j)) return false;
-        if (!mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.status, 640, j)) return false;
+        // P(j) sits in buffer j % kPStages; its barrier completes once per use of that buffer
+        const int pst = j % kPStages;
+        const uint32_t pph = (uint32_t)(j / kPStages) & 1u;
+        if (!mbar_wait(p_full(pst), pph, abort_flag, p.status, 640, j)) return false;
         tc_fence_after();
         const uint32_t vb = sV + (uint32_t)st * kKVBytes;
+        const uint32_t pb = sP + (uint32_t)pst * kPBytes;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {
-          const uint64_t pd = make_desc_kmajor_sw128(sP + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
+          const uint64_t pd = make_desc_kmajor_sw128(pb + (uint32_t)(k / 4) * 16384u) + 2u * (k % 4);
           const uint64_t vd = make_desc_mnmajor_sw128(vb, kHalf) + 128u * k;
           // O accumulates in tensor memory across key tiles
           umma_f16_ss(tO, pd, vd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
@@ -264,7 +273,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     float m = -INFINITY;
     float l = 0.f;
-    uint8_t* p_row = pP + (size_t)row * 128;
+    uint8_t* p_row0 = pP + (size_t)row * 128;
     bool ok = true;
     const uint32_t to = tO + lane_off;
 
@@ -290,7 +299,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         if (lane == 0) {
           mbar_arrive(s_empty(st));
-          mbar_arrive(p_full);
+          mbar_arrive(p_full(j % kPStages));
         }
         continue;
       }
@@ -330,18 +339,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       const float m_new = fmaxf(fmaxf(m, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2_approx((m - m_safe) * sc);  // m = -inf -> 0
+      // rows that have seen no key yet (m = -inf) hold O = 0 and l = 0: nothing to rescale
+      const float alpha = (m == -INFINITY) ? 1.0f : ex2_approx((m - m_safe) * sc);
       const float neg_ms = -m_safe * sc;
-      // P(j) overwrites the buffer PV(j-1) reads from, and a rescale of O must not race with
-      // PV(j-1) accumulating into it: wait for that product first.
+      // A rescale of O must not race with PV(j-1) accumulating into it, and P(j) overwrites the
+      // buffer that PV(j - kPStages) reads from: wait for the later of the products concerned.
+      // The running maxima settle after a few tiles; from then on the softmax of tile j runs
+      // while PV(j-1) is still on the tensor core (two P buffers) and only rare tiles rescale.
       if (j > 0) {
-        if (!mbar_wait(o_full((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abort_flag, p.status,
-                       710, j)) {
+        const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);
+        const int jw = (kPStages == 1 || rescale) ? j - 1 : j - 2;
+        if (jw >= 0 && !mbar_wait(o_full(jw & 1), (uint32_t)(jw >> 1) & 1u, abort_flag, p.status,
+                                  710, j)) {
           ok = false;
           break;
         }
-        // The running maxima settle after a few tiles; only then-rare tiles pay for this.
-        if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+        if (rescale) {
           tc_fence_after();
           uint32_t rc[32];
 #pragma unroll
@@ -386,7 +399,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           pk[t / 2] = pack_bf16x2(e0, e1);
           pk[t / 2 + 1] = pack_bf16x2(e2, e3);
         }
-        uint8_t* line = p_row + (size_t)(c >> 1) * 16384;
+        uint8_t* line = p_row0 + (size_t)(j % kPStages) * kPBytes + (size_t)(c >> 1) * 16384;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int chunk = ((c & 1) * 4 + i) ^ (row & 7);
@@ -401,7 +414,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(s_empty(st));
-        mbar_arrive(p_full);
+        mbar_arrive(p_full(j % kPStages));
       }
     }
     if (ok && n_tiles > 0 && warp_active) {
@@ -567,7 +580,8 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return -3;
-  const size_t smem = 128 * D * 2 + 4 * (size_t)TK * D * 2 + 128 * TK * 2 + 256;
+  const size_t smem =
+      128 * D * 2 + 4 * (size_t)TK * D * 2 + (TK == 128 ? 2 : 1) * (size_t)128 * TK * 2 + 256;
   if (!attr_set[dev]) {
     if (cudaFuncSetAttribute(attention_kernel<D, TK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)

@@ -5,7 +5,8 @@
 // worth. Properties: power-of-two capacity, triangular probing (visits every
 // slot), tombstones on erase, grow at 3/4 occupancy (live + tombstones), shrink
 // when live entries fall under 1/8 of the capacity, 64-bit finaliser-style mix
-// of the key. An empty map owns no heap memory.
+// of the key. Up to two entries live inside the object itself: a map that small (most child
+// and endpoint tables) owns no heap memory and is searched without hashing.
 //
 // Plays the role of csrc/suffix_decoding/int32_map.h in the reference.
 #pragma once
@@ -34,13 +35,17 @@ class Int32Map {
   }
   ~Int32Map() { release(); }
 
-  uint32_t size() const { return live_; }
-  bool empty() const { return live_ == 0; }
+  uint32_t size() const { return cap_ == 0 ? in_ : live_; }
+  bool empty() const { return size() == 0; }
   uint32_t capacity() const { return cap_; }
   size_t heap_bytes() const { return (size_t)cap_ * sizeof(Slot); }
 
   V* find(int32_t key) {
-    if (cap_ == 0) return nullptr;
+    if (cap_ == 0) {
+      for (uint32_t i = 0; i < in_; ++i)
+        if (ikey_[i] == key) return &ival_[i];
+      return nullptr;
+    }
     uint32_t i = mix(key) & (cap_ - 1);
     for (uint32_t step = 1;; ++step) {
       Slot& s = slots_[i];
@@ -54,6 +59,19 @@ class Int32Map {
 
   // Insert or overwrite. Returns a reference to the stored value.
   V& put(int32_t key, const V& value) {
+    if (cap_ == 0) {
+      for (uint32_t i = 0; i < in_; ++i)
+        if (ikey_[i] == key) {
+          ival_[i] = value;
+          return ival_[i];
+        }
+      if (in_ < kInline) {
+        ikey_[in_] = key;
+        ival_[in_] = value;
+        return ival_[in_++];
+      }
+      spill();
+    }
     if ((used_ + 1) * 4 > cap_ * 3) rehash(live_ + 1);
     uint32_t i = mix(key) & (cap_ - 1);
     int64_t grave = -1;
@@ -77,7 +95,16 @@ class Int32Map {
   }
 
   bool erase(int32_t key) {
-    if (cap_ == 0) return false;
+    if (cap_ == 0) {
+      for (uint32_t i = 0; i < in_; ++i)
+        if (ikey_[i] == key) {
+          --in_;
+          ikey_[i] = ikey_[in_];
+          ival_[i] = ival_[in_];
+          return true;
+        }
+      return false;
+    }
     uint32_t i = mix(key) & (cap_ - 1);
     for (uint32_t step = 1;; ++step) {
       Slot& s = slots_[i];
@@ -101,12 +128,18 @@ class Int32Map {
   // Visit every (key, value); the callback must not modify the map.
   template <typename F>
   void for_each(F&& f) const {
+    for (uint32_t i = 0; cap_ == 0 && i < in_; ++i) f(ikey_[i], ival_[i]);
     for (uint32_t i = 0; i < cap_; ++i)
       if (slots_[i].state == kFull) f(slots_[i].key, slots_[i].value);
   }
 
   // Any live entry (nullptr when empty).
   const std::pair<int32_t, V>* any(std::pair<int32_t, V>* scratch) const {
+    if (cap_ == 0 && in_ > 0) {
+      scratch->first = ikey_[0];
+      scratch->second = ival_[0];
+      return scratch;
+    }
     for (uint32_t i = 0; i < cap_; ++i)
       if (slots_[i].state == kFull) {
         scratch->first = slots_[i].key;
@@ -119,6 +152,7 @@ class Int32Map {
  private:
   enum : uint8_t { kEmpty = 0, kFull = 1, kTomb = 2 };
   static constexpr uint32_t kMinCap = 4;
+  static constexpr uint32_t kInline = 2;
   struct Slot {
     int32_t key;
     uint8_t state;
@@ -158,24 +192,45 @@ class Int32Map {
     ++live_;
   }
 
+  // the inline entries move to a freshly allocated table
+  void spill() {
+    const uint32_t n = in_;
+    in_ = 0;
+    slots_ = static_cast<Slot*>(std::calloc(8, sizeof(Slot)));
+    if (slots_ == nullptr) throw std::bad_alloc();
+    cap_ = 8;
+    used_ = live_ = 0;
+    for (uint32_t i = 0; i < n; ++i) put_fresh(ikey_[i], ival_[i]);
+  }
+
   void release() {
     std::free(slots_);
     slots_ = nullptr;
     cap_ = used_ = live_ = 0;
+    in_ = 0;
   }
   void steal(Int32Map& o) {
     slots_ = o.slots_;
     cap_ = o.cap_;
     used_ = o.used_;
     live_ = o.live_;
+    in_ = o.in_;
+    for (uint32_t i = 0; i < kInline; ++i) {
+      ikey_[i] = o.ikey_[i];
+      ival_[i] = o.ival_[i];
+    }
     o.slots_ = nullptr;
     o.cap_ = o.used_ = o.live_ = 0;
+    o.in_ = 0;
   }
 
   Slot* slots_ = nullptr;
   uint32_t cap_ = 0;
   uint32_t used_ = 0;  // full + tombstones
   uint32_t live_ = 0;
+  uint32_t in_ = 0;    // inline entries in use (only while cap_ == 0)
+  int32_t ikey_[kInline] = {};
+  V ival_[kInline] = {};
 };
 
 }  // namespace ab200

@@ -14,16 +14,47 @@ SuffixTree::SuffixTree(int32_t max_depth) : max_depth_(max_depth) {
   root_ = new_node();
 }
 
-SuffixTree::~SuffixTree() { free_subtree(root_); }
+SuffixTree::~SuffixTree() {
+  free_subtree(root_);
+  for (Node* n : node_pool_) delete n;
+  for (Group* g : group_pool_) delete g;
+}
 
 SuffixTree::Node* SuffixTree::new_node() {
   ++num_nodes_;
-  return new Node();
+  if (node_pool_.empty()) return new Node();
+  Node* n = node_pool_.back();
+  node_pool_.pop_back();
+  return n;
 }
 
 void SuffixTree::free_node(Node* n) {
   --num_nodes_;
-  delete n;
+  n->children.clear();
+  n->endpoints.clear();
+  n->count = 0;
+  n->token = n->length = n->ref_idx = 0;
+  n->ref = nullptr;
+  n->parent = n->head_child = n->tail_child = n->next_sibling = n->prev_sibling = nullptr;
+  n->group = nullptr;
+  node_pool_.push_back(n);
+}
+
+SuffixTree::Group* SuffixTree::new_group(Node* head, Node* tail) {
+  if (group_pool_.empty()) return new Group{head, tail};
+  Group* g = group_pool_.back();
+  group_pool_.pop_back();
+  g->head = head;
+  g->tail = tail;
+  return g;
+}
+
+void SuffixTree::free_group(Group* g) { group_pool_.push_back(g); }
+
+SuffixTree::Seq& SuffixTree::seq_for(int32_t seq_id) {
+  Seq& s = seqs_[seq_id];
+  s.id = seq_id;
+  return s;
 }
 
 void SuffixTree::free_subtree(Node* n) {
@@ -33,13 +64,9 @@ void SuffixTree::free_subtree(Node* n) {
     stack.pop_back();
     for (Node* c = x->head_child; c != nullptr; c = c->next_sibling) stack.push_back(c);
     // groups are owned by their head member
-    if (x->group != nullptr && x->group->head == x) delete x->group;
+    if (x->group != nullptr && x->group->head == x) free_group(x->group);
     free_node(x);
   }
-}
-
-const int32_t* SuffixTree::edge(const Node* n) const {
-  return seqs_.at(n->ref_seq).tokens.data() + n->ref_idx;
 }
 
 // ------------------------------------------------------------------ sibling list
@@ -64,14 +91,14 @@ void SuffixTree::link_child(Node* parent, Node* child) {
     child->group = next->group;       // cannot happen after the scan above, kept for safety
     child->group->head = child;
   } else {
-    child->group = new Group{child, child};
+    child->group = new_group(child, child);
   }
 }
 
 void SuffixTree::unlink_child(Node* parent, Node* child) {
   Group* g = child->group;
   if (g->head == child && g->tail == child) {
-    delete g;
+    free_group(g);
   } else if (g->head == child) {
     g->head = child->next_sibling;
   } else if (g->tail == child) {
@@ -113,14 +140,14 @@ void SuffixTree::bump(Node* child, int delta) {
     if (delta > 0) {
       Node* prev = child->prev_sibling;
       if (prev != nullptr && prev->count == target) {
-        delete g;
+        free_group(g);
         child->group = prev->group;
         child->group->tail = child;
       }
     } else {
       Node* next = child->next_sibling;
       if (next != nullptr && next->count == target) {
-        delete g;
+        free_group(g);
         child->group = next->group;
         child->group->head = child;
       }
@@ -149,7 +176,7 @@ void SuffixTree::bump(Node* child, int delta) {
     child->group = next->group;
     child->group->head = child;
   } else {
-    child->group = new Group{child, child};
+    child->group = new_group(child, child);
   }
 }
 
@@ -159,7 +186,7 @@ SuffixTree::Node* SuffixTree::split_first(Node* c) {
   Node* m = new_node();
   m->token = c->token;
   m->length = 1;
-  m->ref_seq = c->ref_seq;
+  m->ref = c->ref;
   m->ref_idx = c->ref_idx;
   m->count = c->count;
   replace_child(parent, c, m);
@@ -187,9 +214,19 @@ void SuffixTree::maybe_merge(Node* p) {
   free_node(p);
 }
 
-SuffixTree::Node* SuffixTree::advance(Seq& seq, int32_t seq_id, Node* at, int32_t token,
-                                      int32_t end_idx) {
-  (void)seq;
+SuffixTree::Node* SuffixTree::advance(Seq& seq, Node* at, int32_t token, int32_t end_idx) {
+  const int32_t seq_id = seq.id;
+  // A leaf that only this sequence's growing string reaches is simply made one token longer:
+  // its edge is witnessed by this sequence and the new token is the next one there.
+  if (at != root_ && at->head_child == nullptr && at->count == 1 && at->ref == &seq &&
+      at->ref_idx + at->length == end_idx - 1) {
+    int32_t* ep = at->endpoints.find(seq_id);
+    if (ep != nullptr && at->endpoints.size() == 1) {
+      at->length += 1;
+      *ep = end_idx;
+      return at;
+    }
+  }
   if (at != root_) at->endpoints.erase(seq_id);
   Node* res;
   Node** pc = at->children.find(token);
@@ -202,7 +239,7 @@ SuffixTree::Node* SuffixTree::advance(Seq& seq, int32_t seq_id, Node* at, int32_
     res = new_node();
     res->token = token;
     res->length = 1;
-    res->ref_seq = seq_id;
+    res->ref = &seq;
     res->ref_idx = end_idx - 1;
     res->count = 1;
     res->parent = at;
@@ -215,23 +252,21 @@ SuffixTree::Node* SuffixTree::advance(Seq& seq, int32_t seq_id, Node* at, int32_
 }
 
 void SuffixTree::append(int32_t seq_id, int32_t token) {
-  Seq& seq = seqs_[seq_id];
+  Seq& seq = seq_for(seq_id);
   seq.tokens.push_back(token);
   const int32_t n = (int32_t)seq.tokens.size();
   root_->count += 1;
   seq.active.push_back(root_);
   for (size_t i = 0; i < seq.active.size(); ++i)
-    seq.active[i] = advance(seq, seq_id, seq.active[i], token, n);
+    seq.active[i] = advance(seq, seq.active[i], token, n);
   // the oldest growing string has length active.size(); retire it once it is max_depth long
   if ((int32_t)seq.active.size() >= max_depth_) seq.active.erase(seq.active.begin());
 }
 
 void SuffixTree::extend(int32_t seq_id, const int32_t* tokens, size_t n) {
-  if (n == 0) {
-    seqs_[seq_id];
-    return;
-  }
-  seqs_[seq_id].tokens.reserve(seqs_[seq_id].tokens.size() + n);
+  Seq& seq = seq_for(seq_id);
+  if (n == 0) return;
+  seq.tokens.reserve(seq.tokens.size() + n);
   for (size_t i = 0; i < n; ++i) append(seq_id, tokens[i]);
 }
 
@@ -286,13 +321,13 @@ void SuffixTree::remove(int32_t seq_id) {
   std::sort(order.begin(), order.end(), [](const auto& a, const auto& b) { return a.first > b.first; });
   for (auto& [d, x] : order) {
     (void)d;
-    if (x->ref_seq != seq_id) continue;
+    if (x->ref != &it->second) continue;
     std::pair<int32_t, int32_t> ep;
     if (x->endpoints.any(&ep) != nullptr) {
-      x->ref_seq = ep.first;
+      x->ref = &seqs_.at(ep.first);
       x->ref_idx = ep.second - x->length;
     } else if (x->head_child != nullptr) {
-      x->ref_seq = x->head_child->ref_seq;
+      x->ref = x->head_child->ref;
       x->ref_idx = x->head_child->ref_idx - x->length;
     }
   }
@@ -388,6 +423,10 @@ Draft SuffixTree::speculate(const int32_t* context, size_t n, int32_t max_spec_t
                             float max_spec_factor, float max_spec_offset, float min_token_prob,
                             bool use_tree_spec) const {
   Draft best;
+  // candidate of the current match length, swapped into `best` when it wins; per thread,
+  // because callers may speculate on one tree from several threads
+  static thread_local Draft scratch;
+  Draft& d = scratch;
   const size_t max_m = std::min(n, (size_t)std::max(1, max_depth_ - 1));
   for (size_t m = 1; m <= max_m; ++m) {
     Match mt;
@@ -395,11 +434,14 @@ Draft SuffixTree::speculate(const int32_t* context, size_t n, int32_t max_spec_t
     const int32_t budget = std::min<int32_t>(
         max_spec_tokens, (int32_t)std::floor((double)m * max_spec_factor + max_spec_offset + 1e-6));
     if (budget <= 0) continue;
-    Draft d;
+    d.token_ids.clear();
+    d.parents.clear();
+    d.probs.clear();
+    d.score = 0.f;
     if (use_tree_spec) speculate_tree(mt, budget, min_token_prob, &d);
     else speculate_path(mt, budget, min_token_prob, &d);
     d.match_len = (int32_t)m;
-    if (!d.token_ids.empty() && d.score >= best.score) best = std::move(d);
+    if (!d.token_ids.empty() && d.score >= best.score) std::swap(best, d);
   }
   return best;
 }
@@ -420,8 +462,9 @@ std::string SuffixTree::check_integrity() const {
     if (x != root_) {
       if (x->count <= 0) return "non-positive count";
       if (x->length < 1) return "empty edge";
-      auto s = seqs_.find(x->ref_seq);
-      if (s == seqs_.end()) return "edge refers to a removed sequence";
+      if (x->ref == nullptr) return "edge without a witness sequence";
+      auto s = seqs_.find(x->ref->id);
+      if (s == seqs_.end() || &s->second != x->ref) return "edge refers to a removed sequence";
       if (x->ref_idx < 0 || (size_t)(x->ref_idx + x->length) > s->second.tokens.size())
         return "edge reference out of range";
       if (s->second.tokens[x->ref_idx] != x->token) return "edge key differs from its first token";

@@ -64,12 +64,13 @@ class SuffixTree {
 
  private:
   struct Group;
+  struct Seq;
   struct Node {
     int64_t count = 0;
     int32_t token = 0;    // first token of the edge (key in the parent's child table)
     int32_t length = 0;   // tokens on the edge
-    int32_t ref_seq = -1; // the edge's tokens are seq[ref_seq][ref_idx .. ref_idx + length)
     int32_t ref_idx = 0;
+    Seq* ref = nullptr;   // the edge's tokens are ref->tokens[ref_idx .. ref_idx + length)
     Node* parent = nullptr;
     Int32Map<Node*> children;
     Node* head_child = nullptr;  // child with the largest count
@@ -85,6 +86,7 @@ class SuffixTree {
     Node* tail;
   };
   struct Seq {
+    int32_t id = -1;
     std::vector<int32_t> tokens;
     // end nodes of the strings that are still shorter than max_depth, oldest start first
     std::vector<Node*> active;
@@ -92,8 +94,11 @@ class SuffixTree {
 
   Node* new_node();
   void free_node(Node* n);
+  Group* new_group(Node* head, Node* tail);
+  void free_group(Group* g);
   void free_subtree(Node* n);
-  const int32_t* edge(const Node* n) const;
+  static const int32_t* edge(const Node* n) { return n->ref->tokens.data() + n->ref_idx; }
+  Seq& seq_for(int32_t seq_id);
 
   // sibling-list maintenance
   void link_child(Node* parent, Node* child);            // child->count must be set
@@ -103,7 +108,7 @@ class SuffixTree {
 
   Node* split_first(Node* child);            // cut the first token of child's edge into a new parent
   void maybe_merge(Node* p);                 // fuse p with its only child when nothing ends at p
-  Node* advance(Seq& seq, int32_t seq_id, Node* at, int32_t token, int32_t end_idx);
+  Node* advance(Seq& seq, Node* at, int32_t token, int32_t end_idx);
 
   struct Match {
     const Node* node = nullptr;  // node whose edge the match ends in (or at)
@@ -116,7 +121,12 @@ class SuffixTree {
   int32_t max_depth_;
   Node* root_;
   size_t num_nodes_ = 0;
-  std::unordered_map<int32_t, Seq> seqs_;
+  std::unordered_map<int32_t, Seq> seqs_;   // node-based: a Seq never moves
+  // recycled nodes and groups (a sequence that grows by one token touches up to max_depth
+  // nodes; going to the allocator for each would dominate the update)
+  std::vector<Node*> node_pool_;
+  std::vector<Group*> group_pool_;
+
 };
 
 }  // namespace ab200

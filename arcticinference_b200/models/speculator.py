@@ -181,20 +181,21 @@ class ArcticSpeculator:
         self.load_state(iter_safetensors_dir(path))
 
     def quantize_fp8(self) -> int:
-        """Store the projections and LM heads as block-scaled fp8 (embeddings and norms stay
-        bf16); matrices whose dimensions are not multiples of 128 are left alone. Returns the
+        """Store the projections and LM heads as fp8 with one scale per output feature
+        (activations are quantised per token on the way in; embeddings and norms stay bf16);
+        matrices whose inner dimension is not a multiple of 16 are left alone. Returns the
         number of tensors converted. (Reference: arctic_inference/vllm/spec_dec/fp8.py:140-309
         quantises the same linears of its speculators.)"""
-        from .quant import quantize_weight_fp8
+        from .quant import quantize_weight_fp8_row
         n = 0
         for k, t in list(self.w.items()):
             if not isinstance(t, torch.Tensor) or t.dim() != 2:
                 continue
             if not (k.startswith("proj") or k.startswith("head")):
                 continue
-            if t.shape[0] % 128 or t.shape[1] % 128:
+            if t.shape[0] % 8 or t.shape[1] % 16:
                 continue
-            self.w[k] = quantize_weight_fp8(t)
+            self.w[k] = quantize_weight_fp8_row(t)
             n += 1
         return n
 

@@ -57,13 +57,12 @@ def _ensure_registered() -> None:
         return BertEncoder(*a, **k)
 
     register_config("llama_swiftkv", "Llama with SwiftKV (num_key_value_layers)")
-    for arch in ("LlamaForCausalLM", "LlamaSwiftKVForCausalLM", "MistralForCausalLM",
-                 "Qwen2ForCausalLM"):
+    for arch in ("LlamaForCausalLM", "LlamaSwiftKVForCausalLM"):
         register_model(arch, _llama)
     for arch in ("ArcticMLPSpeculatorPreTrainedModel", "ArcticLSTMSpeculatorPreTrainedModel",
                  "MLPVariantSpeculatorPreTrainedModel", "MLPSpeculatorPreTrainedModel"):
         register_model(arch, _speculator)
-    for arch in ("BertModel", "BertForMaskedLM", "XLMRobertaModel"):
+    for arch in ("BertModel", "BertForMaskedLM"):
         register_model(arch, _bert)
 
 

@@ -170,3 +170,35 @@ def test_cache_lifecycle_and_eviction():
     with pytest.raises(ValueError):
         c.speculate("zzz", [1, 2])
     assert c.max_depth == 16
+
+
+def test_fuzz_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The C++ tree alone (no interpreter in the process), compiled with ASAN + UBSAN, under
+    random append / remove / speculate traffic with an integrity check after every operation."""
+    import os
+    import shutil
+    import subprocess
+    # the first compiler that links against the sanitizer runtimes (a toolchain installed
+    # beside the system one often lacks them)
+    cands = [c for c in (os.environ.get("CXX"), "/usr/bin/g++", shutil.which("g++"),
+                         shutil.which("clang++")) if c and os.path.exists(c)]
+    if not cands:
+        pytest.skip("no C++ compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "arcticinference_b200", "csrc", "suffix_tree")
+    exe = str(tmp_path / "suffix_fuzz")
+    for cxx in cands:
+        build = subprocess.run(
+            [cxx, "-O1", "-g", "-std=c++17", "-fsanitize=address,undefined",
+             "-fno-sanitize-recover=all", "-fno-omit-frame-pointer", "-I", src,
+             os.path.join(root, "tests", "suffix_tree_fuzz.cc"),
+             os.path.join(src, "suffix_tree.cc"), "-o", exe], capture_output=True, text=True)
+        if build.returncode == 0:
+            break
+    if build.returncode != 0 and "cannot find" in build.stderr and "san" in build.stderr:
+        pytest.skip("sanitizer runtime not installed")
+    assert build.returncode == 0, build.stderr[-2000:]
+    for seed in (1, 2, 3):
+        run = subprocess.run([exe, str(seed), "400"], capture_output=True, text=True, timeout=300,
+                             env=dict(os.environ, ASAN_OPTIONS="detect_leaks=1"))
+        assert run.returncode == 0 and run.stdout.strip() == "ok", (run.stdout + run.stderr)[-3000:]
