@@ -208,9 +208,23 @@ rmsnorm_quant_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict
 
 // ----------------------------------------------------------- SiLU * mul + quant
 // x: [T, nblk * 2 * inter] as nblk blocks of (gate | up) -> outq [T, nblk * inter] e4m3 with one
-// scale per token over the whole output row.
-template <int MAXV>
-__global__ void __launch_bounds__(512)
+// scale per token over the whole output row. One CTA per row, two sweeps over the row: the
+// first finds the row's largest product, the second (its loads served by L2, the row was just
+// read) recomputes the products and stores their codes. Nothing but a running maximum is kept
+// between the sweeps, so a thread needs few registers and many rows are in flight per SM.
+constexpr int kSiluQThreads = 256;
+constexpr int kSiluQUnroll = 2;
+
+__device__ __forceinline__ void silu_mul8(const uint4& gq, const uint4& uq, float (&o)[8]) {
+  float g[8], u[8];
+  q_unpack8(gq, g);
+  q_unpack8(uq, u);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+  round_bf16x8(o);
+}
+
+__global__ void __launch_bounds__(kSiluQThreads, 4)
 silu_mul_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ outq, long long ldq,
                       float* __restrict__ so, int inter, int nblk) {
   __shared__ float red[32];
@@ -219,38 +233,55 @@ silu_mul_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ outq, lo
   const int total = nblk * nvec;
   const bf16* xrow = x + row * (long long)nblk * 2 * inter;
   float amax = 0.f;
-  uint4 packed[MAXV];  // bf16-rounded products, 8 per vector
+  for (int i0 = threadIdx.x; i0 < total; i0 += kSiluQThreads * kSiluQUnroll) {
+    uint4 gq[kSiluQUnroll], uq[kSiluQUnroll];
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int i = threadIdx.x + j * blockDim.x;
-    uint4 gq = make_uint4(0, 0, 0, 0), uq = make_uint4(0, 0, 0, 0);
-    if (i < total) {
-      const int b = i / nvec;
-      const int c = i - b * nvec;
-      const uint4* blk = reinterpret_cast<const uint4*>(xrow + (long long)b * 2 * inter);
-      gq = blk[c];
-      uq = blk[nvec + c];
+    for (int j = 0; j < kSiluQUnroll; ++j) {
+      const int i = i0 + j * kSiluQThreads;
+      gq[j] = make_uint4(0, 0, 0, 0);
+      uq[j] = make_uint4(0, 0, 0, 0);
+      if (i < total) {
+        const int b = i / nvec;
+        const int c = i - b * nvec;
+        const uint4* blk = reinterpret_cast<const uint4*>(xrow + (long long)b * 2 * inter);
+        gq[j] = blk[c];
+        uq[j] = blk[nvec + c];
+      }
     }
-    float g[8], u[8];
-    q_unpack8(gq, g);
-    q_unpack8(uq, u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
-    packed[j] = q_pack8(g);
-    q_unpack8(packed[j], g);
-    amax = fmaxf(amax, amax8(g));
+    for (int j = 0; j < kSiluQUnroll; ++j) {
+      float o[8];
+      silu_mul8(gq[j], uq[j], o);
+      amax = fmaxf(amax, amax8(o));
+    }
   }
   amax = q_block_max(amax, red);
   const float scale = fmaxf(amax, 1e-10f) / kE4m3Max;
   const float inv = 1.f / scale;
   uint2* qr = reinterpret_cast<uint2*>(outq + row * ldq);
+  for (int i0 = threadIdx.x; i0 < total; i0 += kSiluQThreads * kSiluQUnroll) {
+    uint4 gq[kSiluQUnroll], uq[kSiluQUnroll];
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int i = threadIdx.x + j * blockDim.x;
-    if (i < total) {
-      float v[8];
-      q_unpack8(packed[j], v);
-      qr[i] = to_e4m3x8(v, inv);
+    for (int j = 0; j < kSiluQUnroll; ++j) {
+      const int i = i0 + j * kSiluQThreads;
+      gq[j] = make_uint4(0, 0, 0, 0);
+      uq[j] = make_uint4(0, 0, 0, 0);
+      if (i < total) {
+        const int b = i / nvec;
+        const int c = i - b * nvec;
+        const uint4* blk = reinterpret_cast<const uint4*>(xrow + (long long)b * 2 * inter);
+        gq[j] = blk[c];
+        uq[j] = blk[nvec + c];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kSiluQUnroll; ++j) {
+      const int i = i0 + j * kSiluQThreads;
+      if (i < total) {
+        float o[8];
+        silu_mul8(gq[j], uq[j], o);
+        qr[i] = to_e4m3x8(o, inv);
+      }
     }
   }
   if (threadIdx.x == 0) so[row] = scale;
@@ -312,24 +343,15 @@ int ab200_rmsnorm_quant(const void* x, long long ldx, void* residual, const void
 }
 
 // SiLU(gate) * up over nblk fused (gate | up) blocks of width inter -> e4m3 [T, nblk * inter]
-// + one scale per token. nblk * inter must be at most 32768.
+// + one scale per token.
 int ab200_silu_mul_quant(const void* x, void* outq, long long ldq, void* so, long long T,
                          int inter, int nblk, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((inter % 8) || (ldq % 8) || nblk < 1) return -2;
-  const long long total = (long long)nblk * (inter / 8);
-  if (total > 4096) return -2;
   const bf16* xp = reinterpret_cast<const bf16*>(x);
   uint8_t* qp = reinterpret_cast<uint8_t*>(outq);
   float* sp = reinterpret_cast<float*>(so);
-  if (total <= 512)
-    silu_mul_quant_kernel<2><<<(unsigned)T, 256, 0, stream>>>(xp, qp, ldq, sp, inter, nblk);
-  else if (total <= 1024)
-    silu_mul_quant_kernel<4><<<(unsigned)T, 256, 0, stream>>>(xp, qp, ldq, sp, inter, nblk);
-  else if (total <= 2048)
-    silu_mul_quant_kernel<8><<<(unsigned)T, 256, 0, stream>>>(xp, qp, ldq, sp, inter, nblk);
-  else
-    silu_mul_quant_kernel<8><<<(unsigned)T, 512, 0, stream>>>(xp, qp, ldq, sp, inter, nblk);
+  silu_mul_quant_kernel<<<(unsigned)T, kSiluQThreads, 0, stream>>>(xp, qp, ldq, sp, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -415,7 +415,7 @@ def silu_mul_blocked(x: torch.Tensor, nblk: int = 1, out=None, quant: bool = Fal
     assert x.is_contiguous()
     T, width = x.shape
     inter = width // (2 * nblk)
-    if quant and nblk * inter <= 32768:
+    if quant:
         from ..models.quant import QuantAct
         oq = torch.empty(T, nblk * inter, dtype=torch.float8_e4m3fn, device=x.device)
         so = torch.empty(T, dtype=torch.float32, device=x.device)
@@ -424,8 +424,6 @@ def silu_mul_blocked(x: torch.Tensor, nblk: int = 1, out=None, quant: bool = Fal
         nat.check(rc, "silu_mul_quant")
         launch_counter.add(1)
         return QuantAct(oq, so)
-    if quant:
-        return quant_fp8_row(silu_mul_blocked(x, nblk))
     if out is None:
         out = torch.empty(T, nblk * inter, dtype=x.dtype, device=x.device)
     rc = nat.lib().ab200_silu_mul(x.data_ptr(), out.data_ptr(), T, inter, nblk, nat.stream_ptr())

@@ -6,7 +6,11 @@ L2 but of at most a few GB).
     python benchmarks/kernel_bench.py --case attn_decode --no-time   # for ncu: 3 launches only
 
 Timing: CUDA events around each launch, median reported, with achieved TFLOP/s or GB/s
-against the measured peaks in MEASURED_PEAKS.json when present. Every case keeps several
+against the measured peaks in MEASURED_PEAKS.json when present. Before the first event of an
+iteration the stream is given ~200 us of busy-waiting to chew on, so that the host has queued
+the event pair and the launch by the time the device reaches them: the interval is then the
+device's own time for the kernel, not the host's launch path (which for a 10 us decode kernel
+would otherwise be most of the number). Every case keeps several
 copies of its large operand (weights, KV cache, activations) whose total exceeds twice the
 L2 capacity and rotates through them, so each timed launch reads its operands from HBM
 without the write-back traffic that a dirty flush buffer would add to the measurement.
@@ -55,6 +59,7 @@ def timeit(fn, iters, warm=3, copies=1):
     ts = []
     for i in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(400000)     # head start for the host (~200 us of device time)
         e0.record()
         call(i)
         e1.record()

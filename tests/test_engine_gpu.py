@@ -252,14 +252,45 @@ def test_run_ahead_over_chunked_prompts_changes_nothing():
 
 
 def test_logprobs_on_gpu_match_the_cpu_path():
+    """Same weights on both devices (random weights are drawn by the device's own generator, so
+    they are copied across): prompt and output log-probabilities agree to bf16 accuracy."""
     import math
+    gpu, cpu = _engine_pair("llama-tiny")
     prompt = [{"prompt_token_ids": [(5 * i) % 991 + 2 for i in range(48)]}]
     sp = SamplingParams(temperature=0, max_tokens=6, ignore_eos=True, logprobs=2, prompt_logprobs=0)
-    kw = dict(model="llama-tiny", num_gpu_blocks_override=64, block_size=16, max_model_len=256)
-    g = LLM(device="cuda:0", **kw).generate(prompt, sp)[0]
-    c = LLM(device="cpu", **kw).generate(prompt, sp)[0]
+    g = gpu.generate(prompt, sp)[0]
+    c = cpu.generate(prompt, sp)[0]
     ops.check_status()
     assert len(g.prompt_logprobs) == 48 and g.prompt_logprobs[0] is None
     assert all(math.isclose(a, b, abs_tol=0.12) for a, b in zip(g.prompt_logprobs[1:], c.prompt_logprobs[1:]))
     assert len(g.outputs[0].logprobs) == 6 and len(g.outputs[0].top_logprobs[0]) == 2
     assert math.isclose(g.outputs[0].logprobs[0], c.outputs[0].logprobs[0], abs_tol=0.12)
+
+
+@pytest.mark.parametrize("scheme", ["channel", "block"])
+def test_fp8_engine_matches_the_cpu_path(scheme):
+    """fp8 linears (per-token / per-feature scales with the fused quantising norm and SiLU
+    kernels, or 128 x 128 blocks) against the PyTorch restatement with the same quantised
+    weights: first-step logits agree to the accuracy of the activations' fp8 rounding."""
+    kw = dict(model="llama-small", num_gpu_blocks_override=128, block_size=16, max_model_len=1024)
+    gpu = LLM(device="cuda:0", **kw)
+    cpu = LLM(device="cpu", **kw)
+    _copy_weights(gpu.engine.runner.model, cpu.engine.runner.model)
+    from arcticinference_b200.models.quant import quantize_model_fp8
+    for llm in (gpu, cpu):
+        quantize_model_fp8(llm.engine.runner.model, prefill_shadow=False, scheme=scheme)
+    prompts = [list(range(3, 150)), [9, 8, 7, 6], list(range(200, 260))]
+    hs = []
+    for llm in (gpu, cpu):
+        eng = llm.engine
+        for p in prompts:
+            eng.add_request(None, p, SamplingParams(temperature=0, max_tokens=4, ignore_eos=True))
+        out = eng.scheduler.schedule()
+        batch, rows = eng.runner.prepare(out)
+        with torch.inference_mode():
+            h = eng.runner.model.forward(batch, eng.runner.kv)
+            logits = eng.runner.model.compute_logits(h)
+        hs.append(logits.float().cpu())
+    ops.check_status()
+    err = (hs[0] - hs[1]).abs().max().item()
+    assert err < 0.1 * max(1.0, hs[1].abs().max().item()), err

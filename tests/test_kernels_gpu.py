@@ -520,11 +520,13 @@ def test_linear_fp8_row(M, N, K):
     ops.check_status()
     _close(y, _row_ref(xq, w), 3e-2, 2e-2)
     # bf16 activations are quantised on the way in; against the unquantised product the error
-    # is the fp8 rounding of both operands
+    # is the e4m3 rounding of the activations (up to 2^-4 relative per element, i.e. a few
+    # hundredths of the output's standard deviation, 1 here; the extremes over a million
+    # outputs reach 0.15)
     y2 = ops.linear(x, w)
     ops.check_status()
     assert torch.equal(y, y2)
-    _close(y2, ref.linear(x, w.dequantize()), 8e-2, 5e-2)
+    _close(y2, ref.linear(x, w.dequantize()), 0.25, 5e-2)
 
 
 @pytest.mark.parametrize("M", [5, 128, 200, 700])
