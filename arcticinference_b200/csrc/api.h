@@ -13,7 +13,36 @@
 extern "C" {
 #endif
 
+// Cross-rank ordering of a kernel without a barrier launch (csrc/common/peer.cuh). All
+// pointers are device pointers into the ranks' symmetric heaps, except the pointer array.
+typedef struct Ab200PeerSync {
+  // signal every rank when the kernel's last block has finished storing (sig_world = 0: off)
+  const void* const* sig_flag_ptrs;  // host array: rank r's arrival words of the channel
+  void* sig_done_ctr;                // this rank's block counter of the channel
+  void* sig_epoch_ctr;               // this rank's epoch counter of the channel
+  int sig_rank;
+  int sig_world;
+  // before reading its input, wait until every rank has signalled on this channel
+  // (wait_world = 0: off)
+  const void* wait_flags;            // this rank's arrival words of the channel
+  const void* wait_epoch_ctr;        // this rank's epoch counter of the channel
+  int wait_world;
+} Ab200PeerSync;
+
+typedef struct Ab200LinearDesc {
+  const void* x; long long ldx; const void* sx;   // sx != null: e4m3 rows + fp32 scale per token
+  const void* w; long long ldw; const void* sw;   // sw != null: e4m3 rows + fp32 scale per feature
+  void* out; long long ldo;
+  int M, N, K;
+  const void* bias; const void* residual; long long ldr; int act;
+  void* workspace; size_t workspace_bytes; int force_splits;
+  const void* const* peer_ptrs; int world; int peer_cols; long long peer_row_off;  // scatter
+  Ab200PeerSync sync;
+  int* status;
+} Ab200LinearDesc;
+
 // ---- gemm_bf16.cu
+int ab200_linear_desc(const Ab200LinearDesc* d, cudaStream_t stream);
 size_t ab200_linear_bf16_workspace_bytes(int M, int N, int K);
 int ab200_linear_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out,
                       long long ldo, int M, int N, int K, const void* bias, const void* residual,
@@ -152,6 +181,23 @@ int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long ro
                             cudaStream_t stream);
 
 
+// ---- variants with cross-rank ordering built in (see Ab200PeerSync)
+int ab200_attention_scatter_sync(const void* q, long long ldq, const void* k, const void* v,
+                                 long long num_blocks, int block_size, const void* block_tables,
+                                 int max_blocks, const void* work, int num_work,
+                                 const void* tok_splits, int max_splits, long long T, int Hq,
+                                 int Hkv, int D, float scale, const void* const* peer_ptrs,
+                                 int world, int peer_tokens, long long ldo, void* o_part,
+                                 void* lse_part, int tile_keys, const Ab200PeerSync* sync,
+                                 int* status, cudaStream_t stream);
+int ab200_rope_cache_wait(void* qkv, long long ld, const void* positions, const void* slots,
+                          const void* inv_freq, void* k_cache, void* v_cache, long long T, int Hq,
+                          int Hkv, int D, int block_size, long long num_slots, int rotate_q,
+                          const Ab200PeerSync* sync, int* status, cudaStream_t stream);
+int ab200_quant_fp8_row_wait(const void* x, long long ldx, void* xq, long long ldq, void* sx,
+                             long long M, int K, const Ab200PeerSync* sync, int* status,
+                             cudaStream_t stream);
+
 // ---- comm_fused.cu
 int ab200_push_rows(const void* src_a, long long ld_a, const void* src_b, long long ld_b,
                     long long rows_per_rank, int my_rank, int world, const void* idx,
@@ -160,6 +206,10 @@ int ab200_push_rows(const void* src_a, long long ld_a, const void* src_b, long l
 int ab200_rmsnorm_allgather(const void* x, long long ldx, void* residual, const void* weight,
                             const void* const* dst, long long row_off, int my_rank, int world,
                             long long T, int hidden, float eps, cudaStream_t stream);
+int ab200_reduce_rmsnorm(const void* const* part_ptrs, int world, long long ld_part, void* residual,
+                         const void* weight, void* y, long long ldy, void* yq, long long ldq,
+                         void* sy, void* h_out, long long ldh, long long rows, int hidden,
+                         float eps, const Ab200PeerSync* sync, int* status, cudaStream_t stream);
 size_t ab200_argmax_exchange_slot_bytes(int world, int max_rows);
 int ab200_argmax_exchange(const void* ids, const void* vals, int B, int max_rows,
                           const void* const* slot_ptrs, const void* const* flag_ptrs, int my_rank,

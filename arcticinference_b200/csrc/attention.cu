@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include "api.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
 
@@ -63,6 +64,9 @@ struct AttnArgs {
   // row t % peer_tokens (the pointers already include this rank's column offset).
   int peer_tokens;
   __nv_bfloat16* peer_out[16];
+  // completion signal to every rank once the last block has stored its rows (common/peer.cuh);
+  // with split-KV the merge kernel sends it instead
+  TailSignal sig;
 };
 
 // work item layout (int32 x 8)
@@ -86,8 +90,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
+  const unsigned int total_blocks = gridDim.x * gridDim.y;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) report_error(p.status, kErrBadArgument, 900, (int)(smem_u32(smem) & 1023u));
+    tail_signal(p.sig, total_blocks);
     return;
   }
   const uint32_t sQ = smem_u32(smem);
@@ -118,7 +124,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int seq = wk[0];
   const int q_tok0 = wk[1];
   const int n_q_tok = wk[2];
-  if (n_q_tok <= 0) return;  // padding entry of a fixed-size work list
+  if (n_q_tok <= 0) {  // padding entry of a fixed-size work list
+    tail_signal(p.sig, total_blocks);
+    return;
+  }
   const int q_pos0 = wk[3];
   const int kv_start = wk[4];
   int kv_end = wk[5];
@@ -512,6 +521,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   }
 
+  tail_signal(p.sig, total_blocks);
   tc_fence_before();
   __syncthreads();
   if (warp == 5) {
@@ -530,7 +540,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ o_part,
                                        float* __restrict__ lse_out, AttnArgs pa) {
   const long long tok = blockIdx.x;
   const int ns = tok_splits[tok];
-  if (ns <= 1) return;
+  if (ns <= 1) {
+    tail_signal(pa.sig, gridDim.x);
+    return;
+  }
   long long out_row = tok;
   if (pa.peer_tokens > 0) {
     out = pa.peer_out[tok / pa.peer_tokens];
@@ -561,6 +574,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ o_part,
     *reinterpret_cast<uint2*>(out + out_row * ldo + (long long)head * D + d4) = q;
     if (lse_out && d4 == 0) lse_out[tok * Hq + head] = wsum > 0.f ? mx + logf(wsum) : -INFINITY;
   }
+  tail_signal(pa.sig, gridDim.x);
 }
 
 template <int D, int TK>
@@ -571,7 +585,7 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
                             int causal, float scale, void* out, long long ldo, float* o_part,
                             float* lse_part, float* lse_out, int* status, cudaStream_t stream,
                             const void* const* peer_ptrs = nullptr, int world = 0,
-                            int peer_tokens = 0) {
+                            int peer_tokens = 0, const Ab200PeerSync* sync = nullptr) {
   const int G = Hq / Hkv;
   if (peer_tokens > 0 && (world < 1 || world > 16 || peer_ptrs == nullptr)) return -2;
   if (G <= 0 || Hq % Hkv || 128 % G) return -2;
@@ -633,9 +647,22 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
   a.lse_out = lse_out;
   a.T = T;
   a.status = status;
+  TailSignal sig;
+  memset(&sig, 0, sizeof(sig));
+  if (sync != nullptr && sync->sig_world > 0) {
+    if (sync->sig_world > kMaxPeers) return -2;
+    for (int i = 0; i < sync->sig_world; ++i)
+      sig.flags[i] = reinterpret_cast<unsigned int*>(const_cast<void*>(sync->sig_flag_ptrs[i]));
+    sig.done_ctr = reinterpret_cast<unsigned int*>(sync->sig_done_ctr);
+    sig.epoch_ctr = reinterpret_cast<unsigned int*>(sync->sig_epoch_ctr);
+    sig.my_rank = sync->sig_rank;
+    sig.world = sync->sig_world;
+  }
+  if (max_splits <= 1) a.sig = sig;
   dim3 grid((unsigned)num_work, (unsigned)Hkv);
   attention_kernel<D, TK><<<grid, kAttThreads, smem, stream>>>(tq, tk, tv, a);
   if (cudaGetLastError() != cudaSuccess) return -5;
+  a.sig = sig;
   if (max_splits > 1) {
     attention_merge_kernel<D><<<(unsigned)T, 128, 0, stream>>>(
         o_part, lse_part, tok_splits, T, Hq, reinterpret_cast<__nv_bfloat16*>(out), ldo, lse_out, a);
@@ -692,6 +719,22 @@ int ab200_attention_scatter(const void* q, long long ldq, const void* k, const v
                             int D, float scale, const void* const* peer_ptrs, int world,
                             int peer_tokens, long long ldo, void* o_part, void* lse_part,
                             int tile_keys, int* status, cudaStream_t stream) {
+  return ab200_attention_scatter_sync(q, ldq, k, v, num_blocks, block_size, block_tables, max_blocks,
+                                      work, num_work, tok_splits, max_splits, T, Hq, Hkv, D, scale,
+                                      peer_ptrs, world, peer_tokens, ldo, o_part, lse_part,
+                                      tile_keys, nullptr, status, stream);
+}
+
+// The same with a completion signal to every rank (sync->sig_*) instead of a barrier kernel
+// after it: the consumers of the scattered rows wait for the signal themselves.
+int ab200_attention_scatter_sync(const void* q, long long ldq, const void* k, const void* v,
+                                 long long num_blocks, int block_size, const void* block_tables,
+                                 int max_blocks, const void* work, int num_work,
+                                 const void* tok_splits, int max_splits, long long T, int Hq,
+                                 int Hkv, int D, float scale, const void* const* peer_ptrs,
+                                 int world, int peer_tokens, long long ldo, void* o_part,
+                                 void* lse_part, int tile_keys, const Ab200PeerSync* sync,
+                                 int* status, cudaStream_t stream) {
   if (num_work <= 0 || T <= 0) return 0;
   if ((ldq % 8) || (ldo % 8) || peer_tokens <= 0) return -2;
   if (max_splits > 1 && (o_part == nullptr || lse_part == nullptr || tok_splits == nullptr)) return -2;
@@ -701,7 +744,7 @@ int ab200_attention_scatter(const void* q, long long ldq, const void* k, const v
                       reinterpret_cast<const int*>(tok_splits), max_splits, T, Hq, Hkv, 1, scale,
                       const_cast<void*>(peer_ptrs[0]), ldo, reinterpret_cast<float*>(o_part),
                       reinterpret_cast<float*>(lse_part), nullptr, status, stream, peer_ptrs, world,
-                      peer_tokens);
+                      peer_tokens, sync);
 }
 
 }  // extern "C"

@@ -16,7 +16,17 @@
 //     (arctic_inference/vllm/fp32_lm_head.py:179-185 and arctic_speculator.py:328-342 use an
 //     all-gather of packed fp64 pairs).
 //
-// All remote traffic is plain peer stores; waits on peers are bounded (common/peer.cuh).
+//   * reduce_rmsnorm      -- the tensor-parallel reduction after a row-parallel linear layer,
+//     folded into the RMSNorm that follows it: every rank's GEMM leaves its partial product in
+//     its own heap and signals completion from its last block (tail_signal); this kernel waits
+//     for the W signals, sums the W partial rows with peer loads in rank order (so every rank
+//     gets the same bits), adds the residual, normalises and, for fp8 linears, quantises the
+//     row, all in one pass. GEMM -> barrier -> all-reduce -> norm becomes GEMM -> this kernel
+//     (the reference: NCCL all-reduce after vLLM's RowParallelLinear, then a norm kernel).
+//
+// All remote traffic is plain peer loads / stores; waits on peers are bounded (common/peer.cuh).
+
+#include <cuda_fp8.h>
 
 #include "api.h"
 #include "common/peer.cuh"
@@ -137,6 +147,131 @@ rmsnorm_allgather_kernel(const bf16* __restrict__ x, long long ldx, bf16* __rest
   }
 }
 
+// out row = sum over ranks r = 0..W-1 of parts[r][row] (fp32 accumulation in rank order, rounded
+// to bf16 as a stand-alone all-reduce would store it). With a weight: residual (+)= sum, then
+// y = RMSNorm(residual) * weight as bf16 and / or as e4m3 with one scale per row. Without a
+// weight only the reduced row is written (h_out). One CTA per row, the row stays in registers.
+constexpr int kRnThreads = 256;
+constexpr float kRnE4m3Max = 448.f;
+
+template <int VPT>
+__global__ void __launch_bounds__(kRnThreads)
+reduce_rmsnorm_kernel(PeerTable parts, int world, long long ld_part, bf16* __restrict__ residual,
+                      const bf16* __restrict__ weight, bf16* __restrict__ y, long long ldy,
+                      uint8_t* __restrict__ yq, long long ldq, float* __restrict__ sy,
+                      bf16* __restrict__ h_out, long long ldh, int hidden, float eps,
+                      const PeerWait wait, int* status) {
+  __shared__ float red[32];
+  __shared__ int peers_ok;
+  if (threadIdx.x < 32) {
+    const bool ok = wait_peers(wait, status, kWaitLimitNs);
+    if (threadIdx.x == 0) peers_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!peers_ok) return;
+  const long long row = blockIdx.x;
+  const int nvec = hidden / 8;
+  float vals[VPT][8];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * kRnThreads;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) vals[j][k] = 0.f;
+    if (i < nvec) {
+      uint4 v[kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < world)
+          v[r] = ld_sys_v4(reinterpret_cast<const uint4*>(
+                               reinterpret_cast<const bf16*>(parts.ptr[r]) + row * ld_part) + i);
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < world) {
+          float f[8];
+          cf_unpack8(v[r], f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) vals[j][k] += f[k];
+        }
+      }
+      const uint4 q = cf_pack8(vals[j]);   // the bf16 value an all-reduce would have stored
+      cf_unpack8(q, vals[j]);
+      if (h_out) reinterpret_cast<uint4*>(h_out + row * ldh)[i] = q;
+    }
+  }
+  if (weight == nullptr) return;
+  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + row * (long long)hidden) : nullptr;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * kRnThreads;
+    if (i < nvec) {
+      if (rr) {
+        float r[8];
+        cf_unpack8(rr[i], r);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vals[j][k] += r[k];
+        const uint4 q = cf_pack8(vals[j]);
+        rr[i] = q;
+        cf_unpack8(q, vals[j]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += vals[j][k] * vals[j][k];
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float t = (lane < kRnThreads / 32) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  const float inv_rms = rsqrtf(t / (float)hidden + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(weight);
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * kRnThreads;
+    if (i < nvec) {
+      float w[8];
+      cf_unpack8(wr[i], w);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) vals[j][k] = vals[j][k] * inv_rms * w[k];
+      const uint4 q = cf_pack8(vals[j]);
+      cf_unpack8(q, vals[j]);
+      if (y) reinterpret_cast<uint4*>(y + row * ldy)[i] = q;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(vals[j][k]));
+    }
+  }
+  if (yq == nullptr) return;
+  amax = warp_max(amax);
+  __syncthreads();
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  float m = (lane < kRnThreads / 32) ? red[lane] : 0.f;
+  m = warp_max(m);
+  const float scale = fmaxf(m, 1e-10f) / kRnE4m3Max;
+  const float inv = 1.f / scale;
+  uint2* qr = reinterpret_cast<uint2*>(yq + row * ldq);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = threadIdx.x + j * kRnThreads;
+    if (i < nvec) {
+      uint32_t w2[2];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+            make_float2(vals[j][4 * h2] * inv, vals[j][4 * h2 + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+            make_float2(vals[j][4 * h2 + 2] * inv, vals[j][4 * h2 + 3] * inv), __NV_SATFINITE,
+            __NV_E4M3);
+        w2[h2] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      qr[i] = make_uint2(w2[0], w2[1]);
+    }
+  }
+  if (threadIdx.x == 0) sy[row] = scale;
+}
+
 // One block. slots.ptr[r] is rank r's candidate array: [2 (parity)][world][max_rows] entries of
 // {float value, int32 unused, int64 token}. Phase 1: store this rank's B candidates into every
 // rank's array at [parity][my_rank]. Phase 2: flag barrier. Phase 3: per row, the best of the
@@ -233,6 +368,48 @@ int ab200_rmsnorm_allgather(const void* x, long long ldx, void* residual, const 
   rmsnorm_allgather_kernel<<<(unsigned)T, kCfThreads, 0, stream>>>(
       reinterpret_cast<const bf16*>(x), ldx, reinterpret_cast<bf16*>(residual),
       reinterpret_cast<const bf16*>(weight), t, row_off, my_rank, world, hidden, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Tensor-parallel reduction fused with the norm that follows it. part_ptrs: the ranks' partial
+// products ([rows, hidden] bf16 with row stride ld_part, in their symmetric heaps), each
+// complete once that rank has signalled on the channel `sync->wait_*` describes. weight == null:
+// only the reduced rows are written to h_out. Otherwise residual (may be null; contiguous rows)
+// is updated in place and the normalised rows go to y (bf16, may be null) and / or yq + sy (e4m3
+// + one fp32 scale per row, may be null). hidden <= 16384, a multiple of 8.
+int ab200_reduce_rmsnorm(const void* const* part_ptrs, int world, long long ld_part, void* residual,
+                         const void* weight, void* y, long long ldy, void* yq, long long ldq,
+                         void* sy, void* h_out, long long ldh, long long rows, int hidden,
+                         float eps, const Ab200PeerSync* sync, int* status, cudaStream_t stream) {
+  if (world < 1 || world > kMaxPeers || (hidden % 8) || hidden > 16384 || (ld_part % 8) ||
+      (y != nullptr && (ldy % 8)) || (yq != nullptr && ((ldq % 8) || sy == nullptr)) ||
+      (h_out != nullptr && (ldh % 8)))
+    return -2;
+  if (weight == nullptr && h_out == nullptr) return -2;
+  if (rows <= 0) return 0;
+  PeerTable t;
+  fill_table(t, part_ptrs, world);
+  PeerWait w;
+  w.flags = nullptr;
+  w.epoch_ctr = nullptr;
+  w.world = 0;
+  if (sync != nullptr && sync->wait_world > 0) {
+    if (sync->wait_world > kMaxPeers) return -2;
+    w.flags = reinterpret_cast<const unsigned int*>(sync->wait_flags);
+    w.epoch_ctr = reinterpret_cast<const unsigned int*>(sync->wait_epoch_ctr);
+    w.world = sync->wait_world;
+  }
+  const int nvec = hidden / 8;
+#define AB200_LAUNCH_RN(V)                                                                      \
+  reduce_rmsnorm_kernel<V><<<(unsigned)rows, kRnThreads, 0, stream>>>(                          \
+      t, world, ld_part, reinterpret_cast<bf16*>(residual), reinterpret_cast<const bf16*>(weight), \
+      reinterpret_cast<bf16*>(y), ldy, reinterpret_cast<uint8_t*>(yq), ldq,                     \
+      reinterpret_cast<float*>(sy), reinterpret_cast<bf16*>(h_out), ldh, hidden, eps, w, status)
+  if (nvec <= 256) AB200_LAUNCH_RN(1);
+  else if (nvec <= 512) AB200_LAUNCH_RN(2);
+  else if (nvec <= 1024) AB200_LAUNCH_RN(4);
+  else AB200_LAUNCH_RN(8);
+#undef AB200_LAUNCH_RN
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -13,6 +13,7 @@
 #include <math.h>
 
 #include "api.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 
 namespace ab200 {
@@ -269,7 +270,7 @@ silu_mul_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, long long T,
         unpack8(gq[j], g);
         unpack8(uq[j], u);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+        for (int k = 0; k < 8; ++k) g[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
         reinterpret_cast<uint4*>(out)[dst[j]] = pack8(g);
       }
     }
@@ -285,8 +286,19 @@ __global__ void __launch_bounds__(256)
 rope_cache_kernel(bf16* __restrict__ qkv, long long ld, const long long* __restrict__ positions,
                   const long long* __restrict__ slots, const float* __restrict__ inv_freq,
                   bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int Hq, int Hkv, int D,
-                  int block_size, long long num_slots, int rotate_q, int* status) {
+                  int block_size, long long num_slots, int rotate_q, int* status,
+                  const PeerWait wait) {
   extern __shared__ float cs[];  // cos[D/2] | sin[D/2]
+  // rows scattered here by the other ranks' QKV projections: wait for their completion signal
+  if (wait.world > 0) {
+    __shared__ int peers_ok;
+    if (threadIdx.x < 32) {
+      const bool ok = wait_peers(wait, status, kWaitLimitNs);
+      if (threadIdx.x == 0) peers_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!peers_ok) return;
+  }
   const long long t = blockIdx.x;
   const int half = D / 2;
   const float pos = (float)positions[t];
@@ -517,13 +529,32 @@ int ab200_rope_cache(void* qkv, long long ld, const void* positions, const void*
                      const void* inv_freq, void* k_cache, void* v_cache, long long T, int Hq,
                      int Hkv, int D, int block_size, long long num_slots, int rotate_q, int* status,
                      cudaStream_t stream) {
+  return ab200_rope_cache_wait(qkv, ld, positions, slots, inv_freq, k_cache, v_cache, T, Hq, Hkv, D,
+                               block_size, num_slots, rotate_q, nullptr, status, stream);
+}
+
+// The same, first waiting (sync->wait_*) until every rank's producer of `qkv` has signalled.
+int ab200_rope_cache_wait(void* qkv, long long ld, const void* positions, const void* slots,
+                          const void* inv_freq, void* k_cache, void* v_cache, long long T, int Hq,
+                          int Hkv, int D, int block_size, long long num_slots, int rotate_q,
+                          const Ab200PeerSync* sync, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((D % 16) || (ld % 8)) return -2;
+  PeerWait w;
+  w.flags = nullptr;
+  w.epoch_ctr = nullptr;
+  w.world = 0;
+  if (sync != nullptr && sync->wait_world > 0) {
+    if (sync->wait_world > kMaxPeers) return -2;
+    w.flags = reinterpret_cast<const unsigned int*>(sync->wait_flags);
+    w.epoch_ctr = reinterpret_cast<const unsigned int*>(sync->wait_epoch_ctr);
+    w.world = sync->wait_world;
+  }
   rope_cache_kernel<<<(unsigned)T, 256, D * sizeof(float), stream>>>(
       reinterpret_cast<bf16*>(qkv), ld, reinterpret_cast<const long long*>(positions),
       reinterpret_cast<const long long*>(slots), reinterpret_cast<const float*>(inv_freq),
       reinterpret_cast<bf16*>(k_cache), reinterpret_cast<bf16*>(v_cache), Hq, Hkv, D, block_size,
-      num_slots, rotate_q, status);
+      num_slots, rotate_q, status, w);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

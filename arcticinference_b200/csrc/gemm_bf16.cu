@@ -29,6 +29,7 @@
 #include <unordered_map>
 
 #include "api.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
 
@@ -74,6 +75,13 @@ struct GemmArgs {
   int peer_cols;
   long long peer_row_off;
   __nv_bfloat16* peer_out[16];
+  // Cross-rank ordering without a barrier kernel (common/peer.cuh): `wait` holds back the
+  // first operand load until every rank's producer of the A operand has signalled (the
+  // head->sequence exchange lands in this rank's heap); `sig` tells every rank when the last
+  // block of this kernel has finished storing (scatter epilogue, or a partial product that the
+  // peers will reduce).
+  PeerWait wait;
+  TailSignal sig;
 };
 
 __device__ __forceinline__ float gelu_erf(float x) {
@@ -131,11 +139,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    bool peers_ok = true;
+    if (p.wait.world > 0) {
+      peers_ok = wait_peers(p.wait, p.status, kWaitLimitNs);
+      fence_proxy_async_global();
+      if (!peers_ok && lane == 0) *abort_flag = 1;
+    }
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       long long issued = 0;
-      bool ok = true;
+      bool ok = peers_ok;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int tile_a = w % p.tiles_a;
         const int rest = w / p.tiles_a;
@@ -442,6 +456,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
+  tail_signal(p.sig, gridDim.x);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -457,7 +472,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
                                      const __nv_bfloat16* __restrict__ bias,
                                      const __nv_bfloat16* __restrict__ residual, long long ldr,
                                      int act, const float* __restrict__ scale_m,
-                                     const float* __restrict__ scale_n) {
+                                     const float* __restrict__ scale_n, const TailSignal sig) {
   const long long n4 = N / 4;
   const long long total = (long long)M * n4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -490,6 +505,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     q.y = pack_bf16x2(v[2], v[3]);
     *reinterpret_cast<uint2*>(out + m * ldo + n) = q;
   }
+  tail_signal(sig, gridDim.x);
 }
 
 // ------------------------------- host side ---------------------------------
@@ -612,7 +628,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
                          size_t workspace_bytes, int force_splits, int* status,
                          cudaStream_t stream, const void* const* peer_ptrs, int world,
                          int peer_cols, long long peer_row_off, const float* scale_x = nullptr,
-                         const float* scale_w = nullptr) {
+                         const float* scale_w = nullptr, const Ab200PeerSync* sync = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const bool fp8 = scale_x != nullptr;  // e4m3 operands with per-token / per-feature scales
   const int opa = fp8 ? 16 : 8;         // operand rows must start on 16-byte boundaries
@@ -702,6 +718,18 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     const int tiles256 = a.tiles_a * ((N + 255) / 256);
     a.bn = ((tiles256 >= sms || a.tiles_a == 1) && N >= 256) ? 256 : 128;
     if (N < 128) a.bn = ((N + 15) / 16) * 16;
+    if (a.tiles_a == 1 && peer_cols == 0 && a.bn == 256) {
+      // One row of tiles that streams the whole weight matrix (decode): when 256-wide tiles
+      // leave a good part of the SMs without one (gate/up of an 8B model: 112 tiles on 148
+      // SMs), narrow them to the widest size that still fits one wave. A narrower tile is also
+      // a smaller pipeline stage, i.e. one more stage of loads in flight per SM.
+      const int t256 = (N + 255) / 256;
+      if (t256 * 4 > sms * 2 && t256 * 8 < sms * 7) {
+        int bn = 256;
+        while (bn > 128 && (N + (bn - 16) - 1) / (bn - 16) <= sms) bn -= 16;
+        a.bn = bn;
+      }
+    }
     if (a.tiles_a == 1 && peer_cols > 0 && N >= 256) {
       // One row of tiles and no split-K (the scatter epilogue writes final values): a CTA
       // streams its weight tile at a fraction of an SM's share of HBM bandwidth, so narrow the
@@ -734,7 +762,26 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
                (reinterpret_cast<uintptr_t>(bias) % 16) == 0 &&
                (residual == nullptr || ldr % 8 == 0);
 
+  TailSignal sig;
+  memset(&sig, 0, sizeof(sig));
+  if (sync != nullptr) {
+    if (sync->wait_world < 0 || sync->wait_world > kMaxPeers || sync->sig_world < 0 ||
+        sync->sig_world > kMaxPeers)
+      return -2;
+    a.wait.flags = reinterpret_cast<const unsigned int*>(sync->wait_flags);
+    a.wait.epoch_ctr = reinterpret_cast<const unsigned int*>(sync->wait_epoch_ctr);
+    a.wait.world = sync->wait_world;
+    if (sync->sig_world > 0) {
+      for (int i = 0; i < sync->sig_world; ++i)
+        sig.flags[i] = reinterpret_cast<unsigned int*>(const_cast<void*>(sync->sig_flag_ptrs[i]));
+      sig.done_ctr = reinterpret_cast<unsigned int*>(sync->sig_done_ctr);
+      sig.epoch_ctr = reinterpret_cast<unsigned int*>(sync->sig_epoch_ctr);
+      sig.my_rank = sync->sig_rank;
+      sig.world = sync->sig_world;
+    }
+  }
   void* final_out = out;
+  if (a.splits == 1) a.sig = sig;   // with split-K the reduce kernel writes the output
   if (a.splits > 1) {
     a.out_f32 = 1;
     a.out = workspace;
@@ -762,7 +809,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
         reinterpret_cast<const float*>(workspace), a.splits, a.partial_stride, M, N,
         reinterpret_cast<__nv_bfloat16*>(final_out), ldo,
         reinterpret_cast<const __nv_bfloat16*>(bias),
-        reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act, scale_x, scale_w);
+        reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act, scale_x, scale_w, sig);
     if (cudaGetLastError() != cudaSuccess) return -5;
   }
   return 0;
@@ -813,6 +860,25 @@ int ab200_linear_fp8_row(const void* xq, long long ldx, const void* sx, const vo
   return launch_linear(xq, ldx, wq, ldw, out, ldo, M, N, K, bias, residual, ldr, act, workspace,
                        workspace_bytes, force_splits, status, stream, nullptr, 0, 0, 0,
                        reinterpret_cast<const float*>(sx), reinterpret_cast<const float*>(sw));
+}
+
+// One entry point for every form of the linear layer, described by a struct: bf16 operands
+// (sx == null) or e4m3 operands with per-token / per-feature scales, plain or peer-scattered
+// output, and optional cross-rank ordering (wait for the producers of x, signal completion).
+int ab200_linear_desc(const Ab200LinearDesc* d, cudaStream_t stream) {
+  if (d == nullptr) return -2;
+  const bool scatter = d->world > 0 && d->peer_cols > 0;
+  if (scatter && d->peer_ptrs == nullptr) return -2;
+  if ((d->sx == nullptr) != (d->sw == nullptr)) return -2;
+  return launch_linear(d->x, d->ldx, d->w, d->ldw,
+                       scatter ? const_cast<void*>(d->peer_ptrs[0]) : d->out, d->ldo, d->M, d->N,
+                       d->K, scatter ? nullptr : d->bias, scatter ? nullptr : d->residual,
+                       scatter ? 0 : d->ldr, scatter ? 0 : d->act, scatter ? nullptr : d->workspace,
+                       scatter ? 0 : d->workspace_bytes, scatter ? 1 : d->force_splits, d->status,
+                       stream, scatter ? d->peer_ptrs : nullptr, scatter ? d->world : 0,
+                       scatter ? d->peer_cols : 0, scatter ? d->peer_row_off : 0,
+                       reinterpret_cast<const float*>(d->sx), reinterpret_cast<const float*>(d->sw),
+                       &d->sync);
 }
 
 // out[M,N] = x[M,K] * wt[K,N] with wt row-major (N contiguous): exercises the

@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "api.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 
 namespace ab200 {
@@ -93,8 +94,19 @@ __device__ __forceinline__ float q_block_max(float v, float* red) {
 template <int MAXV>
 __global__ void __launch_bounds__(512)
 quant_fp8_row_kernel(const bf16* __restrict__ x, long long ldx, uint8_t* __restrict__ xq,
-                     long long ldq, float* __restrict__ sx, int K) {
+                     long long ldq, float* __restrict__ sx, int K, const PeerWait wait,
+                     int* status) {
   __shared__ float red[32];
+  // x may be rows that other ranks' attention kernels scattered here: wait for their signal
+  if (wait.world > 0) {
+    __shared__ int peers_ok;
+    if (threadIdx.x < 32) {
+      const bool ok = wait_peers(wait, status, kWaitLimitNs);
+      if (threadIdx.x == 0) peers_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!peers_ok) return;
+  }
   const long long row = blockIdx.x;
   const int nvec = K / 8;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
@@ -208,25 +220,26 @@ rmsnorm_quant_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict
 
 // ----------------------------------------------------------- SiLU * mul + quant
 // x: [T, nblk * 2 * inter] as nblk blocks of (gate | up) -> outq [T, nblk * inter] e4m3 with one
-// scale per token over the whole output row. One CTA per row, two sweeps over the row: the
-// first finds the row's largest product, the second (its loads served by L2, the row was just
-// read) recomputes the products and stores their codes. Nothing but a running maximum is kept
-// between the sweeps, so a thread needs few registers and many rows are in flight per SM.
+// scale per token over the whole output row. One CTA per row: the products are computed once,
+// parked as bf16 in shared memory (2 bytes per output element) while the row's largest
+// magnitude is reduced, then converted to e4m3 from there. Few registers, several rows in
+// flight per SM, one pass over HBM.
 constexpr int kSiluQThreads = 256;
-constexpr int kSiluQUnroll = 2;
+constexpr int kSiluQUnroll = 4;
 
-__device__ __forceinline__ void silu_mul8(const uint4& gq, const uint4& uq, float (&o)[8]) {
+__device__ __forceinline__ uint4 silu_mul8(const uint4& gq, const uint4& uq) {
   float g[8], u[8];
   q_unpack8(gq, g);
   q_unpack8(uq, u);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
-  round_bf16x8(o);
+  for (int k = 0; k < 8; ++k) g[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
+  return q_pack8(g);
 }
 
-__global__ void __launch_bounds__(kSiluQThreads, 4)
+__global__ void __launch_bounds__(kSiluQThreads)
 silu_mul_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ outq, long long ldq,
                       float* __restrict__ so, int inter, int nblk) {
+  extern __shared__ uint4 prod[];   // nblk * inter / 8 vectors of 8 bf16
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int nvec = inter / 8;
@@ -241,7 +254,7 @@ silu_mul_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ outq, lo
       gq[j] = make_uint4(0, 0, 0, 0);
       uq[j] = make_uint4(0, 0, 0, 0);
       if (i < total) {
-        const int b = i / nvec;
+        const int b = nblk == 1 ? 0 : i / nvec;
         const int c = i - b * nvec;
         const uint4* blk = reinterpret_cast<const uint4*>(xrow + (long long)b * 2 * inter);
         gq[j] = blk[c];
@@ -250,39 +263,24 @@ silu_mul_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ outq, lo
     }
 #pragma unroll
     for (int j = 0; j < kSiluQUnroll; ++j) {
-      float o[8];
-      silu_mul8(gq[j], uq[j], o);
-      amax = fmaxf(amax, amax8(o));
+      const int i = i0 + j * kSiluQThreads;
+      if (i < total) {
+        const uint4 p = silu_mul8(gq[j], uq[j]);
+        prod[i] = p;
+        float o[8];
+        q_unpack8(p, o);
+        amax = fmaxf(amax, amax8(o));
+      }
     }
   }
-  amax = q_block_max(amax, red);
+  amax = q_block_max(amax, red);   // its barriers also publish `prod`
   const float scale = fmaxf(amax, 1e-10f) / kE4m3Max;
   const float inv = 1.f / scale;
   uint2* qr = reinterpret_cast<uint2*>(outq + row * ldq);
-  for (int i0 = threadIdx.x; i0 < total; i0 += kSiluQThreads * kSiluQUnroll) {
-    uint4 gq[kSiluQUnroll], uq[kSiluQUnroll];
-#pragma unroll
-    for (int j = 0; j < kSiluQUnroll; ++j) {
-      const int i = i0 + j * kSiluQThreads;
-      gq[j] = make_uint4(0, 0, 0, 0);
-      uq[j] = make_uint4(0, 0, 0, 0);
-      if (i < total) {
-        const int b = i / nvec;
-        const int c = i - b * nvec;
-        const uint4* blk = reinterpret_cast<const uint4*>(xrow + (long long)b * 2 * inter);
-        gq[j] = blk[c];
-        uq[j] = blk[nvec + c];
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < kSiluQUnroll; ++j) {
-      const int i = i0 + j * kSiluQThreads;
-      if (i < total) {
-        float o[8];
-        silu_mul8(gq[j], uq[j], o);
-        qr[i] = to_e4m3x8(o, inv);
-      }
-    }
+  for (int i = threadIdx.x; i < total; i += kSiluQThreads) {
+    float o[8];
+    q_unpack8(prod[i], o);
+    qr[i] = to_e4m3x8(o, inv);
   }
   if (threadIdx.x == 0) so[row] = scale;
 }
@@ -297,22 +295,39 @@ extern "C" {
 // K must be a multiple of 8 and at most 32768.
 int ab200_quant_fp8_row(const void* x, long long ldx, void* xq, long long ldq, void* sx,
                         long long M, int K, cudaStream_t stream) {
+  return ab200_quant_fp8_row_wait(x, ldx, xq, ldq, sx, M, K, nullptr, nullptr, stream);
+}
+
+// The same, first waiting (sync->wait_*) until every rank's producer of `x` has signalled.
+int ab200_quant_fp8_row_wait(const void* x, long long ldx, void* xq, long long ldq, void* sx,
+                             long long M, int K, const Ab200PeerSync* sync, int* status,
+                             cudaStream_t stream) {
   if (M <= 0) return 0;
   if ((K % 8) || (ldx % 8) || (ldq % 8) || K > 32768) return -2;
+  PeerWait w;
+  w.flags = nullptr;
+  w.epoch_ctr = nullptr;
+  w.world = 0;
+  if (sync != nullptr && sync->wait_world > 0) {
+    if (sync->wait_world > kMaxPeers) return -2;
+    w.flags = reinterpret_cast<const unsigned int*>(sync->wait_flags);
+    w.epoch_ctr = reinterpret_cast<const unsigned int*>(sync->wait_epoch_ctr);
+    w.world = sync->wait_world;
+  }
   const bf16* xp = reinterpret_cast<const bf16*>(x);
   uint8_t* qp = reinterpret_cast<uint8_t*>(xq);
   float* sp = reinterpret_cast<float*>(sx);
   const int nvec = K / 8;
   if (nvec <= 256)
-    quant_fp8_row_kernel<1><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K);
+    quant_fp8_row_kernel<1><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 512)
-    quant_fp8_row_kernel<2><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K);
+    quant_fp8_row_kernel<2><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 1024)
-    quant_fp8_row_kernel<4><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K);
+    quant_fp8_row_kernel<4><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 2048)
-    quant_fp8_row_kernel<8><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K);
+    quant_fp8_row_kernel<8><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
   else
-    quant_fp8_row_kernel<8><<<(unsigned)M, 512, 0, stream>>>(xp, ldx, qp, ldq, sp, K);
+    quant_fp8_row_kernel<8><<<(unsigned)M, 512, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -351,7 +366,19 @@ int ab200_silu_mul_quant(const void* x, void* outq, long long ldq, void* so, lon
   const bf16* xp = reinterpret_cast<const bf16*>(x);
   uint8_t* qp = reinterpret_cast<uint8_t*>(outq);
   float* sp = reinterpret_cast<float*>(so);
-  silu_mul_quant_kernel<<<(unsigned)T, kSiluQThreads, 0, stream>>>(xp, qp, ldq, sp, inter, nblk);
+  const size_t smem = (size_t)nblk * inter * 2;
+  if (smem > 200 * 1024) return -2;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -3;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(silu_mul_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024) != cudaSuccess)
+      return -3;
+    attr_set[dev] = true;
+  }
+  silu_mul_quant_kernel<<<(unsigned)T, kSiluQThreads, smem, stream>>>(xp, qp, ldq, sp, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

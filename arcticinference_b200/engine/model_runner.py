@@ -159,6 +159,9 @@ class ModelRunner:
         if cfg.model.quantization == "fp8":
             from ..models.quant import quantize_model_fp8
             quantize_model_fp8(self.model, scheme=cfg.model.fp8_scheme)
+            if cfg.model.fp8_scheme == "block" and self.comm is not None and \
+                    getattr(self.comm, "fused", False):
+                self.comm.use_barriers = True   # block-scaled linears carry no signal hooks
 
     def determine_num_blocks(self) -> int:
         cfg = self.config

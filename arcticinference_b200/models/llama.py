@@ -236,18 +236,23 @@ class LlamaForCausalLM(LlamaModel):
             if q_only:
                 w = w[: h * D]
             qkv = ops.linear(x, w)
+        # rows that other ranks scattered into qkv: the first kernel that reads them waits
+        wait = comm.take_wait("qkv") if (comm is not None and comm.fused) else None
         if q_only:
-            ops.rope_cache(qkv, positions, None, self.inv_freq, kv.k[layer], kv.v[layer], h, 0, D)
+            ops.rope_cache(qkv, positions, None, self.inv_freq, kv.k[layer], kv.v[layer], h, 0, D,
+                           sync=wait)
             q = qkv
         else:
-            ops.rope_cache(qkv, positions, slots, self.inv_freq, kv.k[layer], kv.v[layer], h, hkv, D)
+            ops.rope_cache(qkv, positions, slots, self.inv_freq, kv.k[layer], kv.v[layer], h, hkv, D,
+                           sync=wait)
             q = qkv[:, : h * D]
         if mode == "sp" and comm is not None and comm.sp > 1:
             attn = comm.attention_gather_tokens(q, kv.k[layer], kv.v[layer], meta, h, hkv, D,
                                                 self.scale)
         else:
             attn = ops.attention(q, kv.k[layer], kv.v[layer], meta, h, hkv, D, self.scale)
-        return self._linear_reduce(attn, self._o_w(lw, mode), mode)
+        wait = comm.take_wait("attn") if (comm is not None and comm.fused) else None
+        return self._linear_reduce(attn, self._o_w(lw, mode), mode, wait)
 
     def _mlp_block(self, lw, x, mode):
         gu = ops.linear(x, self._gu_w(lw, mode))
@@ -255,17 +260,33 @@ class LlamaForCausalLM(LlamaModel):
         act = ops.silu_mul_blocked(gu, nblk, quant=self.act_quant)
         return self._linear_reduce(act, self._down_w(lw, mode), mode)
 
-    def _linear_reduce(self, x, w, mode):
+    def _linear_reduce(self, x, w, mode, wait=None):
         """Row-parallel linear followed by the reduction its mode needs. With the fused
-        communicator the GEMM writes its partial product straight into the symmetric heap."""
+        communicator the GEMM writes its partial product straight into the symmetric heap; a
+        small reduction is then left to the kernel that consumes it (the result is a
+        ``PendingReduce`` that ``_norm`` / ``_settle`` take). ``wait``: operand wait for ``x``
+        when other ranks store its rows."""
         comm = self.comm
         need = comm is not None and ((mode == "tp" and comm.ways > 1) or
                                      (mode == "sp" and comm.tp > 1))
         if need and comm.fused:
-            t = ops.linear(x, w, out=comm.reduce_buffer(x.shape[0], w.shape[0]))
+            if comm.folds_reduce(x.shape[0], w.shape[0]):
+                return comm.linear_partial(x, w, wait)
+            t = ops.linear(x, w, out=comm.reduce_buffer(x.shape[0], w.shape[0]), sync=wait)
         else:
-            t = ops.linear(x, w)
+            t = ops.linear(x, w, sync=wait) if wait is not None else ops.linear(x, w)
         return self._reduce(t, mode) if need else t
+
+    def _norm(self, h, weight, residual=None, quant=False):
+        """RMSNorm(h (+ residual)) where ``h`` may still be an unreduced row-parallel product."""
+        eps = self.cfg.rms_norm_eps
+        if isinstance(h, torch.Tensor):
+            return ops.rmsnorm(h, weight, eps, residual=residual, quant=quant)
+        return self.comm.reduce_rmsnorm(h, weight, eps, residual, quant)
+
+    def _settle(self, h):
+        """A plain tensor for ``h`` (reduces it now if it is still pending)."""
+        return h if isinstance(h, torch.Tensor) else self.comm.realize(h)
 
     def _reduce(self, t, mode):
         comm = self.comm
@@ -287,9 +308,9 @@ class LlamaForCausalLM(LlamaModel):
             elif merged_first and l == lo:
                 x = ops.rmsnorm(residual, lw.input_norm, eps, quant=aq)
             else:
-                x = ops.rmsnorm(h, lw.input_norm, eps, residual=residual, quant=aq)
+                x = self._norm(h, lw.input_norm, residual, aq)
             h = self._attention_block(lw, x, batch, kv, l, mode, meta, positions, slots, q_only)
-            x = ops.rmsnorm(h, lw.post_norm, eps, residual=residual, quant=aq)
+            x = self._norm(h, lw.post_norm, residual, aq)
             h = self._mlp_block(lw, x, mode)
         return h, residual
 
@@ -307,6 +328,7 @@ class LlamaForCausalLM(LlamaModel):
         h, residual = self._run_layers(0, self.n_kv_layers, h, None, batch, kv, mode,
                                        batch.attn_meta, positions, slots)
         if not cfg.is_swiftkv:
+            h = self._settle(h)
             if mode == "sp" and comm is not None and comm.sp > 1:
                 # hand the sampled rows (hidden and residual) to every rank
                 h, residual = comm.gather_rows_all(h, residual, batch.logits_indices)
@@ -319,10 +341,10 @@ class LlamaForCausalLM(LlamaModel):
         if mode == "sp" and comm is not None and comm.sp > 1:
             # later layers run tensor-parallel: every rank needs the normalised state of all
             # tokens (for their K/V) and the residual of the sampled rows
-            s, x_sel = comm.swiftkv_boundary(h, residual, self.norm_swiftkv, eps,
+            s, x_sel = comm.swiftkv_boundary(self._settle(h), residual, self.norm_swiftkv, eps,
                                              batch.logits_indices)
         else:
-            s = ops.rmsnorm(h, self.norm_swiftkv, eps, residual=residual)  # residual <- h + residual
+            s = self._norm(h, self.norm_swiftkv, residual)  # residual <- h + residual
             x_sel = ops.gather_rows(residual, batch.logits_indices)
         n_later = cfg.num_hidden_layers - self.n_kv_layers
         wkv = self.wkv_swiftkv
@@ -339,7 +361,7 @@ class LlamaForCausalLM(LlamaModel):
         h, residual = self._run_layers(self.n_kv_layers, cfg.num_hidden_layers, None, x_sel, batch,
                                        kv, "tp", batch.sel_attn_meta, batch.sel_positions, None,
                                        q_only=True, merged_first=True)
-        return ops.rmsnorm(h, self.norm, eps, residual=residual)
+        return self._norm(h, self.norm, residual)
 
     def compute_logits(self, hidden: torch.Tensor, fp32: bool = False) -> torch.Tensor:
         """Logits of this rank's vocabulary shard (the full vocabulary on one GPU)."""

@@ -118,8 +118,10 @@ def quant_fp8(x: torch.Tensor):
     return xq, sx_t
 
 
-def quant_fp8_row(x: torch.Tensor):
-    """bf16 [M, K] -> ``QuantAct`` (e4m3 codes [M, K], one fp32 scale per token)."""
+def quant_fp8_row(x: torch.Tensor, sync=None):
+    """bf16 [M, K] -> ``QuantAct`` (e4m3 codes [M, K], one fp32 scale per token). ``sync``: a
+    ``native.PeerSync`` whose wait part holds the kernel back until the ranks that store rows
+    of ``x`` have signalled."""
     from ..models import quant
     if not x.is_cuda:
         return quant.quant_activation_row_ref(x)
@@ -128,19 +130,51 @@ def quant_fp8_row(x: torch.Tensor):
     assert x.stride(1) == 1
     xq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
     sx = torch.empty(M, dtype=torch.float32, device=x.device)
-    rc = nat.lib().ab200_quant_fp8_row(x.data_ptr(), x.stride(0), xq.data_ptr(), xq.stride(0),
-                                       sx.data_ptr(), M, K, nat.stream_ptr())
+    import ctypes
+    rc = nat.lib().ab200_quant_fp8_row_wait(
+        x.data_ptr(), x.stride(0), xq.data_ptr(), xq.stride(0), sx.data_ptr(), M, K,
+        ctypes.byref(sync) if sync is not None else None,
+        nat.status_buffer(x.device).data_ptr(), nat.stream_ptr())
     nat.check(rc, "quant_fp8_row")
     launch_counter.add(1)
     return quant.QuantAct(xq, sx)
 
 
+def _linear_desc(x, ldx, sx, w, ldw, sw, out_ptr, ldo, M, N, K, bias, residual, act,
+                 force_splits, peer, sync, device):
+    """Fill an ``Ab200LinearDesc`` and launch it."""
+    import ctypes
+    nat = _native()
+    ws = nat.workspace(device)
+    d = nat.LinearDesc()
+    d.x, d.ldx, d.sx = x, ldx, sx
+    d.w, d.ldw, d.sw = w, ldw, sw
+    d.out, d.ldo = out_ptr, ldo
+    d.M, d.N, d.K = M, N, K
+    d.bias = nat.ptr(bias)
+    d.residual = nat.ptr(residual)
+    d.ldr = residual.stride(0) if residual is not None else 0
+    d.act = _ACT[act]
+    d.workspace, d.workspace_bytes, d.force_splits = ws.data_ptr(), ws.numel(), force_splits
+    if peer is not None:
+        pp, world, pcols, poff, pldo = peer
+        d.peer_ptrs = ctypes.cast(pp, ctypes.c_void_p)
+        d.world, d.peer_cols, d.peer_row_off, d.ldo = world, pcols, poff, pldo
+    if sync is not None:
+        d.sync = sync
+    d.status = nat.status_buffer(device).data_ptr()
+    rc = nat.lib().ab200_linear_desc(ctypes.byref(d), nat.stream_ptr())
+    return rc
+
+
 def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_splits: int = 0,
-                   peer=None) -> torch.Tensor:
+                   peer=None, sync=None) -> torch.Tensor:
     """W8A8 fp8 linear with per-token activation scales and per-feature weight scales:
     ``x`` is a bf16 tensor (quantised here) or a ``QuantAct``; ``w`` an ``Fp8RowWeight``.
     ``peer`` = (ptr_array, world, peer_cols, row_off, ldo) scatters the output columns to the
-    ranks' buffers (see ``ab200_linear_bf16_scatter``)."""
+    ranks' buffers (see ``ab200_linear_bf16_scatter``). ``sync`` (``native.PeerSync``): its
+    wait part guards the first kernel that reads ``x``, its signal part is sent by the kernel
+    that writes the output."""
     from ..models import quant
     if not w.is_cuda:
         y = quant.linear_fp8_row_ref(x, w, bias, residual, act)
@@ -148,28 +182,31 @@ def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_spl
             out.copy_(y)
             return out
         return y
-    xq = x if isinstance(x, quant.QuantAct) else quant_fp8_row(x)
     nat = _native()
+    gemm_sync = sync
+    if not isinstance(x, quant.QuantAct):
+        xq = quant_fp8_row(x, sync=sync if (sync is not None and sync.wait_world > 0) else None)
+        if sync is not None and sync.wait_world > 0:
+            # the quantiser has waited; the GEMM only signals
+            gemm_sync = nat.PeerSync.from_buffer_copy(sync)
+            gemm_sync.wait_world = 0
+    else:
+        xq = x
     M, K = xq.q.shape
     N = w.shape[0]
     assert w.q.stride(1) == 1 and xq.q.stride(1) == 1 and K == w.shape[1]
-    ws = nat.workspace(w.device)
     if peer is None:
         if out is None:
             out = torch.empty(M, N, dtype=torch.bfloat16, device=w.device)
         assert out.stride(1) == 1
-        out_ptr, ldo, pp, world, pcols, poff = out.data_ptr(), out.stride(0), None, 0, 0, 0
+        out_ptr, ldo = out.data_ptr(), out.stride(0)
     else:
-        pp, world, pcols, poff, ldo = peer
-        out_ptr = None
+        out_ptr, ldo = None, peer[4]
     if M == 0:
         return out
-    rc = nat.lib().ab200_linear_fp8_row(
-        xq.q.data_ptr(), xq.q.stride(0), xq.scale.data_ptr(), w.q.data_ptr(), w.q.stride(0),
-        w.scale.data_ptr(), out_ptr, ldo, M, N, K, nat.ptr(bias), nat.ptr(residual),
-        residual.stride(0) if residual is not None else 0, _ACT[act], ws.data_ptr(), ws.numel(),
-        force_splits, pp, world, pcols, poff, nat.status_buffer(w.device).data_ptr(),
-        nat.stream_ptr())
+    rc = _linear_desc(xq.q.data_ptr(), xq.q.stride(0), xq.scale.data_ptr(), w.q.data_ptr(),
+                      w.q.stride(0), w.scale.data_ptr(), out_ptr, ldo, M, N, K, bias, residual,
+                      act, force_splits, peer, gemm_sync, w.device)
     nat.check(rc, "linear_fp8_row M=%d N=%d K=%d" % (M, N, K))
     launch_counter.add(1)
     return out
@@ -223,13 +260,14 @@ def fp8_prefers_bf16(w, num_tokens: int) -> bool:
 
 
 def linear_fp8(x: torch.Tensor, w, out=None, force_splits: int = 0, peer=None,
-               mode: str = "auto") -> torch.Tensor:
+               mode: str = "auto", sync=None) -> torch.Tensor:
     """Block-scaled fp8 linear: x bf16 [M, K] is quantised on the fly; w is an ``Fp8Weight``.
     ``peer`` = (ptr_array, world, peer_cols, row_off, ldo) scatters the output (see
     ``ab200_linear_bf16_scatter``)."""
     from ..models import quant
     if isinstance(w, quant.Fp8RowWeight):
-        return linear_fp8_row(x, w, out=out, force_splits=force_splits, peer=peer)
+        return linear_fp8_row(x, w, out=out, force_splits=force_splits, peer=peer, sync=sync)
+    assert sync is None, "cross-rank ordering is not available for block-scaled fp8 linears"
     if isinstance(x, quant.QuantAct):
         x = x.dequantize()
     if not x.is_cuda:
@@ -274,15 +312,17 @@ def linear_fp8(x: torch.Tensor, w, out=None, force_splits: int = 0, peer=None,
 
 
 def linear(x: torch.Tensor, w, bias=None, residual=None, act=None, out=None,
-           force_splits: int = 0) -> torch.Tensor:
+           force_splits: int = 0, sync=None) -> torch.Tensor:
     """``out = act(x @ w.T + bias) + residual``; x [M, K] (row stride free), w [N, K] bf16 or
-    an ``Fp8Weight``."""
+    an ``Fp8Weight``. ``sync``: optional ``native.PeerSync`` (wait for the ranks that produce
+    ``x``, signal the ranks that consume ``out``)."""
     if not isinstance(w, torch.Tensor):
         from ..models.quant import Fp8RowWeight
         if isinstance(w, Fp8RowWeight):
-            return linear_fp8_row(x, w, bias, residual, act, out=out, force_splits=force_splits)
+            return linear_fp8_row(x, w, bias, residual, act, out=out, force_splits=force_splits,
+                                  sync=sync)
         assert bias is None and residual is None and act is None
-        return linear_fp8(x, w, out=out, force_splits=force_splits)
+        return linear_fp8(x, w, out=out, force_splits=force_splits, sync=sync)
     if not isinstance(x, torch.Tensor):   # a quantised activation meeting a bf16 weight
         x = x.dequantize()
     if not x.is_cuda:
@@ -301,6 +341,13 @@ def linear(x: torch.Tensor, w, bias=None, residual=None, act=None, out=None,
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     assert out.stride(1) == 1
     if M == 0:
+        return out
+    if sync is not None:
+        rc = _linear_desc(x.data_ptr(), x.stride(0), None, w.data_ptr(), w.stride(0), None,
+                          out.data_ptr(), out.stride(0), M, N, K, bias, residual, act,
+                          force_splits, None, sync, x.device)
+        nat.check(rc, "linear_bf16 M=%d N=%d K=%d" % (M, N, K))
+        launch_counter.add(1)
         return out
     ws = nat.workspace(x.device)
     rc = L.ab200_linear_bf16(
@@ -436,7 +483,8 @@ def silu_mul(x: torch.Tensor, out=None):
     return silu_mul_blocked(x, 1, out)
 
 
-def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, rotate_q=True):
+def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, rotate_q=True,
+               sync=None):
     """In-place neox RoPE on the q and k parts of ``qkv`` [T, (Hq+2Hkv)*D] and write of the
     rotated k and of v into the paged caches [num_blocks, Hkv, block_size, D]."""
     if not qkv.is_cuda:
@@ -447,10 +495,12 @@ def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, ro
     bs = k_cache.shape[2]
     assert k_cache.is_contiguous() and v_cache.is_contiguous()
     assert positions.dtype == torch.int64 and (slots is None or slots.dtype == torch.int64)
-    rc = nat.lib().ab200_rope_cache(
+    import ctypes
+    rc = nat.lib().ab200_rope_cache_wait(
         qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), nat.ptr(slots), inv_freq.data_ptr(),
         k_cache.data_ptr(), v_cache.data_ptr(), T, Hq, Hkv, D, bs, k_cache.shape[0] * bs,
-        1 if rotate_q else 0, nat.status_buffer(qkv.device).data_ptr(), nat.stream_ptr())
+        1 if rotate_q else 0, ctypes.byref(sync) if sync is not None else None,
+        nat.status_buffer(qkv.device).data_ptr(), nat.stream_ptr())
     nat.check(rc, "rope_cache")
     launch_counter.add(1)
 

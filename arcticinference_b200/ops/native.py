@@ -22,6 +22,26 @@ _workspace: dict[int, torch.Tensor] = {}
 WORKSPACE_BYTES = 96 << 20
 
 
+class PeerSync(ctypes.Structure):
+    """``Ab200PeerSync`` (csrc/api.h): completion signal / operand wait of one kernel launch."""
+    _fields_ = [("sig_flag_ptrs", c_void_p), ("sig_done_ctr", c_void_p),
+                ("sig_epoch_ctr", c_void_p), ("sig_rank", c_int), ("sig_world", c_int),
+                ("wait_flags", c_void_p), ("wait_epoch_ctr", c_void_p), ("wait_world", c_int)]
+
+
+class LinearDesc(ctypes.Structure):
+    """``Ab200LinearDesc`` (csrc/api.h)."""
+    _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("sx", c_void_p),
+                ("w", c_void_p), ("ldw", c_longlong), ("sw", c_void_p),
+                ("out", c_void_p), ("ldo", c_longlong),
+                ("M", c_int), ("N", c_int), ("K", c_int),
+                ("bias", c_void_p), ("residual", c_void_p), ("ldr", c_longlong), ("act", c_int),
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("force_splits", c_int),
+                ("peer_ptrs", c_void_p), ("world", c_int), ("peer_cols", c_int),
+                ("peer_row_off", c_longlong),
+                ("sync", PeerSync), ("status", c_void_p)]
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -67,6 +87,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_quant_fp8_row": (I, [P, LL, P, LL, P, LL, I, P]),
         "ab200_rmsnorm_quant": (I, [P, LL, P, P, P, LL, P, P, LL, LL, I, F, P]),
         "ab200_silu_mul_quant": (I, [P, P, LL, P, LL, I, I, P]),
+        "ab200_linear_desc": (I, [P, P]),
+        "ab200_rope_cache_wait": (I, [P, LL, P, P, P, P, P, LL, I, I, I, I, LL, I, P, P, P]),
+        "ab200_quant_fp8_row_wait": (I, [P, LL, P, LL, P, LL, I, P, P, P]),
         "ab200_spec_ln": (I, [P, LL, P, P, P, LL, LL, I, F, F, P]),
         "ab200_mlp_spec_step": (I, [P, LL, P, P, F, P, P, P, LL, LL, I, F, I, P]),
         "ab200_sum_lstm": (I, [P, LL, P, I, P, F, P, LL, P, P, P, P, P, P, LL, LL, I, F, I, P]),
