@@ -39,6 +39,10 @@ typedef struct Ab200LinearDesc {
   const void* const* peer_ptrs; int world; int peer_cols; long long peer_row_off;  // scatter
   Ab200PeerSync sync;
   int* status;
+  // fp8 weight stored in 16-row x 128-byte tiles, [N/16][K/128][16][128]: byte distance between
+  // 16-row tiles and between k-tiles (both 0: row-major). `ldw` is ignored for a tiled weight.
+  long long w_tile_stride_n;
+  long long w_tile_stride_k;
 } Ab200LinearDesc;
 
 // ---- gemm_bf16.cu

@@ -58,6 +58,7 @@ struct GemmArgs {
   int b_mn_major;  // 1: the B operand is given as [K, rows_b] (rows_b contiguous)
   int coalesce;    // 1: bf16 row-major output goes through a shared-memory transpose so that a
                    //    warp stores whole 128-byte lines (what NVLink and L2 both want)
+  int a_tiled, b_tiled;  // the operand is an fp8 weight stored as [rows/16][K/128][16][128]
   int fp8;         // 1: operands are e4m3 bytes (kind::f8f6f4), 128 k-elements per stage
   int kblock_elems;  // k-elements per stage: 64 (bf16) or 128 (fp8)
   const float* scale_a;  // fp8: one factor per A-operand row (null = 1)
@@ -164,8 +165,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
           const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes;
-          tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * p.kblock_elems, tile_a * kBlockM);
-          if (!p.b_mn_major) {
+          if (p.a_tiled)
+            tma_load_4d(a_dst, &tmap_a, full_bar(stage), 0, 0, kb, tile_a * (kBlockM / 16));
+          else
+            tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * p.kblock_elems, tile_a * kBlockM);
+          if (p.b_tiled) {
+            // 2 KB pieces (16 rows x 128 bytes) that are contiguous in memory, bn / 16 of them
+            tma_load_4d(a_dst + kABytes, &tmap_b, full_bar(stage), 0, 0, kb, tile_b * (p.bn / 16));
+          } else if (!p.b_mn_major) {
             tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * p.kblock_elems,
                         tile_b * p.bn);
           } else {
@@ -513,8 +520,10 @@ struct TmapKey {
   const void* ptr;
   uint64_t rows, cols, ld;
   uint32_t box_rows;  // bit 31 set: e4m3 bytes instead of bf16
+  uint64_t tile_stride_n = 0;  // tiled fp8 weights: bytes between 16-row tiles (0: row-major)
   bool operator==(const TmapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows && tile_stride_n == o.tile_stride_n;
   }
 };
 struct TmapKeyHash {
@@ -524,21 +533,26 @@ struct TmapKeyHash {
     h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
     h ^= k.ld * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
     h ^= k.box_rows * 0x27D4EB2F165667C5ull + (h << 6) + (h >> 2);
+    h ^= k.tile_stride_n * 0x9FB21C651E98DF25ull + (h << 6) + (h >> 2);
     return h;
   }
 };
 
 static int get_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
-                    uint32_t box_rows, bool fp8);
+                    uint32_t box_rows, bool fp8, uint64_t tile_stride_n = 0);
 static int get_tmap_bf16(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
                          uint64_t ld, uint32_t box_rows) {
   return get_tmap(out, ptr, rows, cols, ld, box_rows, false);
 }
+// tile_stride_n > 0: the matrix is an fp8 weight stored as [rows/16][K/128][16][128] bytes;
+// `ld` is then the byte distance between consecutive k-tiles of one 16-row tile and
+// tile_stride_n the distance between 16-row tiles (views of a larger tiled matrix keep their
+// parent's strides). A box of box_rows rows is box_rows/16 contiguous 2 KB pieces.
 static int get_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
-                    uint32_t box_rows, bool fp8) {
+                    uint32_t box_rows, bool fp8, uint64_t tile_stride_n) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-  TmapKey key{ptr, rows, cols, ld, box_rows | (fp8 ? 0x80000000u : 0u)};
+  TmapKey key{ptr, rows, cols, ld, box_rows | (fp8 ? 0x80000000u : 0u), tile_stride_n};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -546,7 +560,14 @@ static int get_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t c
     return 0;
   }
   CUtensorMap m;
-  int rc = fp8 ? make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_UINT8, rows, cols, ld, box_rows,
+  int rc;
+  if (tile_stride_n > 0) {
+    const uint64_t dims[4] = {128, 16, cols / 128, (rows + 15) / 16};
+    const uint64_t strides[3] = {128, ld, tile_stride_n};
+    const uint32_t box[4] = {128, 16, 1, box_rows / 16};
+    rc = make_tmap_nd(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, dims, strides, box);
+  } else
+  rc = fp8 ? make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_UINT8, rows, cols, ld, box_rows,
                               kBlockKFp8)
                : make_tmap_2d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rows, cols, ld * 2,
                               box_rows, kBlockK);
@@ -628,7 +649,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
                          size_t workspace_bytes, int force_splits, int* status,
                          cudaStream_t stream, const void* const* peer_ptrs, int world,
                          int peer_cols, long long peer_row_off, const float* scale_x = nullptr,
-                         const float* scale_w = nullptr, const Ab200PeerSync* sync = nullptr) {
+                         const float* scale_w = nullptr, const Ab200PeerSync* sync = nullptr,
+                         long long w_tile_stride_n = 0, long long w_tile_stride_k = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const bool fp8 = scale_x != nullptr;  // e4m3 operands with per-token / per-feature scales
   const int opa = fp8 ? 16 : 8;         // operand rows must start on 16-byte boundaries
@@ -637,6 +659,10 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
       (reinterpret_cast<uintptr_t>(out) & 15))
     return -2;
   if (fp8 && (scale_w == nullptr || (reinterpret_cast<uintptr_t>(scale_w) & 15))) return -2;
+  const bool w_tiled = w_tile_stride_n > 0;
+  if (w_tiled && (!fp8 || (K % 128) || (N % 16) || (w_tile_stride_n % 16) ||
+                  (w_tile_stride_k % 16) || w_tile_stride_k < 2048))
+    return -2;
   if (residual != nullptr && ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -2;
 
   static bool attr_set[64] = {false};
@@ -790,8 +816,15 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   }
 
   CUtensorMap ta, tb;
-  if (get_tmap(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K, (uint64_t)lda, kBlockM, fp8) != 0) return -4;
-  if (get_tmap(&tb, pb, (uint64_t)a.rows_b, (uint64_t)K, (uint64_t)ldb, (uint32_t)a.bn, fp8) != 0)
+  a.a_tiled = (w_tiled && a.transposed) ? 1 : 0;
+  a.b_tiled = (w_tiled && !a.transposed) ? 1 : 0;
+  if (get_tmap(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K,
+               a.a_tiled ? (uint64_t)w_tile_stride_k : (uint64_t)lda, kBlockM, fp8,
+               a.a_tiled ? (uint64_t)w_tile_stride_n : 0) != 0)
+    return -4;
+  if (get_tmap(&tb, pb, (uint64_t)a.rows_b, (uint64_t)K,
+               a.b_tiled ? (uint64_t)w_tile_stride_k : (uint64_t)ldb, (uint32_t)a.bn, fp8,
+               a.b_tiled ? (uint64_t)w_tile_stride_n : 0) != 0)
     return -4;
 
   const int total = a.tiles_a * a.tiles_b * a.splits;
@@ -878,7 +911,7 @@ int ab200_linear_desc(const Ab200LinearDesc* d, cudaStream_t stream) {
                        stream, scatter ? d->peer_ptrs : nullptr, scatter ? d->world : 0,
                        scatter ? d->peer_cols : 0, scatter ? d->peer_row_off : 0,
                        reinterpret_cast<const float*>(d->sx), reinterpret_cast<const float*>(d->sw),
-                       &d->sync);
+                       &d->sync, d->w_tile_stride_n, d->w_tile_stride_k);
 }
 
 // out[M,N] = x[M,K] * wt[K,N] with wt row-major (N contiguous): exercises the

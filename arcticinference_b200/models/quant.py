@@ -113,49 +113,97 @@ class QuantAct:
         return (self.q.float() * self.scale[:, None]).to(torch.bfloat16)
 
 
+TILE_ROWS, TILE_K = 16, 128
+
+
+def tile_fp8(q2d: torch.Tensor) -> torch.Tensor:
+    """[N, K] codes -> [N/16, K/128, 16, 128]: every 16-row x 128-byte piece contiguous."""
+    N, K = q2d.shape
+    return q2d.view(N // TILE_ROWS, TILE_ROWS, K // TILE_K, TILE_K).permute(0, 2, 1, 3).contiguous()
+
+
 class Fp8RowWeight(Fp8Weight):
-    """e4m3 codes [N, K] with one fp32 scale per output feature (row). Row slices carry their
-    scales along; column slices (the K shards of row-parallel layers) keep all of them."""
+    """e4m3 codes of an [N, K] matrix with one fp32 scale per output feature (row). Row slices
+    carry their scales along; column slices (the K shards of row-parallel layers) keep all of
+    them.
 
-    __slots__ = ()
+    Storage of the codes: row-major [N, K], or ("tiled", the default on a GPU when N % 16 == 0
+    and K % 128 == 0) [N/16, K/128, 16, 128], in which each 16-row x 128-byte piece is 2 KB of
+    consecutive memory. A GEMM stage's weight tile is then a few dozen KB in 2 KB bursts
+    instead of hundreds of 128-byte pieces one row stride apart, which is what a decode step,
+    whose time is the time to stream the weights once, needs from DRAM. Shard views are slices
+    of the first two dimensions."""
 
-    def __init__(self, q: torch.Tensor, scale: torch.Tensor):
-        assert q.dim() == 2 and scale.dim() == 1 and scale.shape[0] == q.shape[0]
+    __slots__ = ("tiled",)
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor, tiled: bool = False):
+        assert scale.dim() == 1 and q.dim() == (4 if tiled else 2)
         self.q = q
         self.scale = scale
         self.shadow = None
+        self.tiled = tiled
+        assert scale.shape[0] == self.shape[0]
+
+    @property
+    def shape(self):
+        if self.tiled:
+            return torch.Size((self.q.shape[0] * TILE_ROWS, self.q.shape[1] * TILE_K))
+        return self.q.shape
+
+    def numel(self):
+        return self.q.numel()
 
     def __getitem__(self, idx) -> "Fp8RowWeight":
         if isinstance(idx, slice):
             rows, cols = idx, slice(None)
         else:
             rows, cols = idx
-        a, _, _ = rows.indices(self.q.shape[0])
-        c, _, _ = cols.indices(self.q.shape[1])
+        N, K = self.shape
+        a, b, _ = rows.indices(N)
+        c, d, _ = cols.indices(K)
+        if self.tiled:
+            if a % TILE_ROWS or b % TILE_ROWS or c % TILE_K or d % TILE_K:
+                raise ValueError("slices of a tiled fp8 weight must fall on 16-row / 128-column "
+                                 "boundaries")
+            return Fp8RowWeight(self.q[a // TILE_ROWS:b // TILE_ROWS, c // TILE_K:d // TILE_K],
+                                self.scale[a:b], True)
         if a % 4 or c % 16:
             raise ValueError("fp8 weight slices must start on 16-byte boundaries")
         return Fp8RowWeight(self.q[rows, cols], self.scale[rows])
+
+    def codes(self) -> torch.Tensor:
+        """The codes as a row-major [N, K] tensor (a copy when the storage is tiled)."""
+        if not self.tiled:
+            return self.q
+        N, K = self.shape
+        return self.q.permute(0, 2, 1, 3).reshape(N, K)
 
     def make_shadow(self) -> None:
         pass
 
     def dequantize(self) -> torch.Tensor:
-        return (self.q.float() * self.scale[:, None]).to(torch.bfloat16)
+        return (self.codes().float() * self.scale[:, None]).to(torch.bfloat16)
 
     def requantize_from(self, dense: torch.Tensor) -> None:
-        q = quantize_weight_fp8_row(dense.to(torch.bfloat16))
-        self.q.copy_(q.q)
+        q = quantize_weight_fp8_row(dense.to(torch.bfloat16), tiled=False)
+        self.q.copy_(tile_fp8(q.q) if self.tiled else q.q)
         self.scale.copy_(q.scale)
 
 
-def quantize_weight_fp8_row(w: torch.Tensor) -> Fp8RowWeight:
-    """bf16 [N, K] -> e4m3 codes + one scale per row (scale = amax / 448)."""
+def quantize_weight_fp8_row(w: torch.Tensor, tiled=None) -> Fp8RowWeight:
+    """bf16 [N, K] -> e4m3 codes + one scale per row (scale = amax / 448). ``tiled``: storage
+    layout of the codes (see :class:`Fp8RowWeight`); None picks tiles for GPU tensors whose
+    dimensions allow them."""
     N, K = w.shape
     if K % 16:
         raise ValueError("fp8 quantisation needs K to be a multiple of 16, got %d" % K)
+    if tiled is None:
+        tiled = w.is_cuda and N % TILE_ROWS == 0 and K % TILE_K == 0
     wf = w.float()
     scale = wf.abs().amax(dim=1).clamp_min(1e-10) / FP8_MAX
     q = (wf / scale[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    if tiled:
+        return Fp8RowWeight(tile_fp8(q.contiguous()), scale.contiguous(), True)
     return Fp8RowWeight(q.contiguous(), scale.contiguous())
 
 
@@ -170,7 +218,7 @@ def quant_activation_row_ref(x: torch.Tensor) -> QuantAct:
 def linear_fp8_row_ref(x, w: Fp8RowWeight, bias=None, residual=None, act=None) -> torch.Tensor:
     """fp32 oracle of ab200_linear_fp8_row; ``x`` is a bf16 tensor or a :class:`QuantAct`."""
     xq = x if isinstance(x, QuantAct) else quant_activation_row_ref(x)
-    y = (xq.q.float() @ w.q.float().t()) * xq.scale[:, None] * w.scale[None, :]
+    y = (xq.q.float() @ w.codes().float().t()) * xq.scale[:, None] * w.scale[None, :]
     if bias is not None:
         y = y + bias.float()
     if act == "gelu":

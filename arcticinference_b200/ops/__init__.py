@@ -141,7 +141,7 @@ def quant_fp8_row(x: torch.Tensor, sync=None):
 
 
 def _linear_desc(x, ldx, sx, w, ldw, sw, out_ptr, ldo, M, N, K, bias, residual, act,
-                 force_splits, peer, sync, device):
+                 force_splits, peer, sync, device, w_tile_strides=None):
     """Fill an ``Ab200LinearDesc`` and launch it."""
     import ctypes
     nat = _native()
@@ -162,6 +162,8 @@ def _linear_desc(x, ldx, sx, w, ldw, sw, out_ptr, ldo, M, N, K, bias, residual, 
         d.world, d.peer_cols, d.peer_row_off, d.ldo = world, pcols, poff, pldo
     if sync is not None:
         d.sync = sync
+    if w_tile_strides is not None:
+        d.w_tile_stride_n, d.w_tile_stride_k = w_tile_strides
     d.status = nat.status_buffer(device).data_ptr()
     rc = nat.lib().ab200_linear_desc(ctypes.byref(d), nat.stream_ptr())
     return rc
@@ -194,7 +196,15 @@ def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_spl
         xq = x
     M, K = xq.q.shape
     N = w.shape[0]
-    assert w.q.stride(1) == 1 and xq.q.stride(1) == 1 and K == w.shape[1]
+    assert xq.q.stride(1) == 1 and K == w.shape[1]
+    tile_strides = None
+    if w.tiled:
+        assert w.q.stride(3) == 1 and w.q.stride(2) == 128
+        tile_strides = (w.q.stride(0), w.q.stride(1))
+        ldw = K
+    else:
+        assert w.q.stride(1) == 1
+        ldw = w.q.stride(0)
     if peer is None:
         if out is None:
             out = torch.empty(M, N, dtype=torch.bfloat16, device=w.device)
@@ -205,8 +215,8 @@ def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_spl
     if M == 0:
         return out
     rc = _linear_desc(xq.q.data_ptr(), xq.q.stride(0), xq.scale.data_ptr(), w.q.data_ptr(),
-                      w.q.stride(0), w.scale.data_ptr(), out_ptr, ldo, M, N, K, bias, residual,
-                      act, force_splits, peer, gemm_sync, w.device)
+                      ldw, w.scale.data_ptr(), out_ptr, ldo, M, N, K, bias, residual,
+                      act, force_splits, peer, gemm_sync, w.device, tile_strides)
     nat.check(rc, "linear_fp8_row M=%d N=%d K=%d" % (M, N, K))
     launch_counter.add(1)
     return out

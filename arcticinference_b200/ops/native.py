@@ -39,7 +39,8 @@ class LinearDesc(ctypes.Structure):
                 ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("force_splits", c_int),
                 ("peer_ptrs", c_void_p), ("world", c_int), ("peer_cols", c_int),
                 ("peer_row_off", c_longlong),
-                ("sync", PeerSync), ("status", c_void_p)]
+                ("sync", PeerSync), ("status", c_void_p),
+                ("w_tile_stride_n", c_longlong), ("w_tile_stride_k", c_longlong)]
 
 
 class KernelError(RuntimeError):

@@ -164,12 +164,7 @@ class FusedCommunicator(Communicator):
                       for i, name in enumerate(("qkv", "attn", "ar"))}
         # operand waits handed from a producing call to the call that consumes its output
         self._pending_wait = {}
-        # reductions up to this many bytes per rank are folded into the following RMSNorm
-        # (every rank then reads all W partials: more NVLink bytes than the two-shot kernel,
-        # two launches and two flag exchanges fewer)
-        self._fold_reduce_max = min(self._two_shot_from, 4 << 20)
-        if os.environ.get("AB200_FOLD_REDUCE", "1") == "0":
-            self._fold_reduce_max = 0
+
         self._ar2_epochs = torch.zeros(128, dtype=torch.int32, device=self.device)
         mode = os.environ.get("AB200_ALLREDUCE", "auto").lower()
         if mode not in ("auto", "oneshot", "twoshot"):
@@ -181,6 +176,12 @@ class FusedCommunicator(Communicator):
         # 24 MB on 2 GPUs, 5.3 MB on 4, 2 MB on 8.
         auto_from = int(12e6 * W / max(1, (W - 1) ** 2)) if W > 1 else (1 << 62)
         self._two_shot_from = {"auto": auto_from, "oneshot": 1 << 62, "twoshot": 0}[mode]
+        # reductions up to this many bytes per rank are folded into the following RMSNorm
+        # (every rank then reads all W partials: more NVLink bytes than the two-shot kernel,
+        # two launches and two flag exchanges fewer)
+        self._fold_reduce_max = min(self._two_shot_from, 4 << 20)
+        if os.environ.get("AB200_FOLD_REDUCE", "1") == "0":
+            self._fold_reduce_max = 0
         torch.cuda.synchronize(self.device)
         dist.barrier()
         L = native.lib()

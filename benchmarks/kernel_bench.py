@@ -109,6 +109,10 @@ CASES = {
     "gemm_fp8row_decode_128": ("gemm_fp8row", (128, 28672, 4096)),
     "gemm_fp8row_decode_128_down": ("gemm_fp8row", (128, 4096, 14336)),
     "gemm_fp8row_decode_o": ("gemm_fp8row", (32, 4096, 4096)),
+    "gemm_fp8row_decode_128_rowmajor": ("gemm_fp8row_rm", (128, 28672, 4096)),
+    "gemm_fp8row_decode_128_down_rowmajor": ("gemm_fp8row_rm", (128, 4096, 14336)),
+    "gemm_fp8row_prefill_rowmajor": ("gemm_fp8row_rm", (8192, 28672, 4096)),
+    "gemm_fp8row_decode_qkv": ("gemm_fp8row", (128, 6144, 4096)),
     "gemm_w8a8_block_prefill": ("gemm_fp8blk", (8192, 28672, 4096)),
     "attn_prefill": ("attn", ([8192], [8192])),
     "attn_prefill_4x2048": ("attn", ([2048] * 4, [2048] * 4)),
@@ -158,12 +162,13 @@ def run_case(a, case):
         x, ws = R(M, K), [quant.quantize_weight_fp8(R(N, K)) for _ in range(nc)]
         fn = lambda i=0: ops.linear(x, ws[i])
         flops, byts = 2.0 * M * N * K, 2.0 * (M * K + M * N) + 1.0 * N * K
-    elif kind == "gemm_fp8row":
+    elif kind in ("gemm_fp8row", "gemm_fp8row_rm"):
         from arcticinference_b200.models import quant
         M, N, K = prm
         nc = copies_for(N * K)
         xq = ops.quant_fp8_row(R(M, K))
-        ws = [quant.quantize_weight_fp8_row(R(N, K)) for _ in range(nc)]
+        tiled = None if kind == "gemm_fp8row" else False     # None: tiled storage on the GPU
+        ws = [quant.quantize_weight_fp8_row(R(N, K), tiled=tiled) for _ in range(nc)]
         fn = lambda i=0: ops.linear(xq, ws[i], force_splits=a.splits)
         flops, byts = 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
     elif kind == "gemm_fp8blk":

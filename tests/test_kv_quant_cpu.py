@@ -51,3 +51,28 @@ def test_bulk_write_cpu_matches_per_layer():
         ops.rope_cache(kv_all[:, j * w:(j + 1) * w].clone(), pos, slots, inv_freq, kc2[j], vc2[j],
                        0, Hkv, D)
         assert torch.equal(kc[j], kc2[j]) and torch.equal(vc[j], vc2[j])
+
+
+def test_tiled_fp8_weight_storage_is_the_same_matrix():
+    """Codes stored as [N/16, K/128, 16, 128] tiles stand for the same matrix as row-major
+    codes: dequantisation, shard views on tile boundaries, the linear oracle and in-place
+    re-quantisation all agree; a slice that cuts a tile is refused."""
+    import pytest
+    import torch
+    from arcticinference_b200.models import quant
+    w = (torch.randn(512, 1024) * 0.05).to(torch.bfloat16)
+    a = quant.quantize_weight_fp8_row(w, tiled=False)
+    b = quant.quantize_weight_fp8_row(w, tiled=True)
+    assert tuple(b.shape) == tuple(a.shape) == (512, 1024) and b.q.dim() == 4
+    assert torch.equal(b.codes().view(torch.uint8), a.q.view(torch.uint8))
+    s, r = b[128:384, 256:768], a[128:384, 256:768]
+    assert tuple(s.shape) == (256, 512) and torch.equal(s.scale, r.scale)
+    assert torch.equal(s.dequantize(), r.dequantize())
+    x = torch.randn(5, 512).to(torch.bfloat16)
+    assert torch.equal(quant.linear_fp8_row_ref(x, s), quant.linear_fp8_row_ref(x, r))
+    ptr = b.q.data_ptr()
+    b.requantize_from(w * 2)
+    a.requantize_from(w * 2)
+    assert b.q.data_ptr() == ptr and torch.equal(b.dequantize(), a.dequantize())
+    with pytest.raises(ValueError):
+        b[8:24]
