@@ -40,7 +40,16 @@
 
 namespace ab200 {
 
-constexpr int kAttThreads = 192;  // 4 softmax warps + TMA warp + MMA warp
+// Softmax warps: eight for 128-key tiles (two per TMEM lane quadrant, each taking half of the
+// columns of S, of P and of O of the quadrant's 32 rows: one warp per scheduler cannot hide the
+// latency of its TMEM reads and exponentials, and the softmax, not the tensor core, was the
+// longest stage of a prefill tile), four for the 64-key decode tiles, whose two CTAs per SM
+// already give every scheduler two softmax warps. Then the TMA warp and the MMA warp.
+template <int TK>
+struct AttnShape {
+  static constexpr int kSoftmaxWarps = (TK == 128) ? 8 : 4;
+  static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+};
 
 struct AttnArgs {
   const int* work;          // [num_work][8], see AttnWork
@@ -76,7 +85,7 @@ struct AttnArgs {
 //  In contiguous mode field 0 is the row of the sequence's first key in the K/V tensor.
 
 template <int D, int TK>
-__global__ void __launch_bounds__(kAttThreads, (TK == 64 ? 2 : 1))
+__global__ void __launch_bounds__(AttnShape<TK>::kThreads, (TK == 64 ? 2 : 1))
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p) {
   constexpr int kHalves = D / 64;
@@ -87,6 +96,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   constexpr int kChunks = TK / 32;         // 32-column chunks of a row of S
   constexpr uint32_t kTmemCols = (TK == 128) ? 512 : 256;  // 2 S buffers + O
   constexpr int kPStages = (TK == 128) ? 2 : 1;  // decode tiles share the SM with a second CTA
+  constexpr int kSW = AttnShape<TK>::kSoftmaxWarps;
+  constexpr int kHalves2 = kSW / 4;                // warps per lane quadrant
+  constexpr int kAttThreads = AttnShape<TK>::kThreads;
+  constexpr int kTmaWarp = kSW, kMmaWarp = kSW + 1;
+  // per-row values the two warps of a quadrant hand each other: tile maxima (double-buffered
+  // by tile parity) and, at the end, the partial row sums
+  // (1.5 KB: with 224 KB of tiles the CTA is within 3 KB of the 227 KB a block may own, so the
+  // maxima travel as bf16, rounded up; the same words carry the fp32 row sums at the end)
+  __shared__ __align__(16) __nv_bfloat16 pair_max[2][2][128];
+  __shared__ short pair_seq[2][128];   // how many values thread (half, row) has published
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -145,24 +164,26 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(s_empty(s), 4);
+      mbar_init(s_empty(s), kSW);
       mbar_init(o_full(s), 1);
       mbar_init(o_empty(s), 4);
     }
-    mbar_init(p_full(0), 4);
-    mbar_init(p_full(1), 4);
+    mbar_init(p_full(0), kSW);
+    mbar_init(p_full(1), kSW);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
   // Stale shared memory may hold non-finite bit patterns; keys that are never
   // loaded (past the end of a sequence) are multiplied by P = 0 and must be finite.
+  for (int i = threadIdx.x; i < 256; i += kAttThreads) (&pair_seq[0][0])[i] = 0;
+  // (counts stay far below 32767: a sequence of 2^21 keys is 16384 tiles)
   {
     uint4* z = reinterpret_cast<uint4*>(smem + kQBytes);
     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -176,7 +197,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tS = tmem_base;           // S buffers at columns 0, TK
   const uint32_t tO = tmem_base + 2 * TK;  // output accumulator, D columns
 
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, kQBytes);
@@ -220,7 +241,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         __syncwarp();
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0 && n_tiles > 0) {
       const uint32_t idesc_s = make_idesc(128, TK, 1, 1, 0, 0);
@@ -273,13 +294,44 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else {
     // ------------------------------ softmax warps ------------------------------
-    const int row = warp * 32 + lane;
+    const int quad = warp & 3;          // TMEM lane quadrant this warp may read
+    const int half = warp >> 2;         // which half of the quadrant's columns it takes
+    const int row = quad * 32 + lane;
+    // The two warps of a quadrant hand each other per-row values through shared memory: a
+    // thread publishes a value, then its count of published values; its partner (same lane of
+    // the other warp) polls that count, bounded like every other wait of the kernel.
+    int published = 0;
+    auto pair_publish = [&]() {
+      __threadfence_block();
+      ++published;
+      *reinterpret_cast<volatile short*>(&pair_seq[half][row]) = (short)published;
+    };
+    auto pair_wait = [&]() -> bool {
+      volatile short* seq = reinterpret_cast<volatile short*>(&pair_seq[half ^ 1][row]);
+      unsigned int spins = 0;
+      unsigned long long t0 = 0;
+      while (*seq < published) {
+        if ((++spins & 63u) == 0u) {
+          if (*abort_flag) return false;
+          if (t0 == 0) t0 = globaltimer_ns();
+          else if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            report_error(p.status, kErrBarrierTimeout, 730, published);
+            return false;
+          }
+        }
+      }
+      __threadfence_block();
+      return true;
+    };
+    constexpr int kLocalChunks = kChunks / kHalves2;   // 32-column chunks of S per warp
+    const int c_first = half * kLocalChunks;
     const int tok_local = row / p.G;
     const int g = row % p.G;
     const bool valid_row = tok_local < n_q_tok;
     const int q_pos = q_pos0 + tok_local;
     const int limit = p.causal ? min(q_pos, kv_end - 1) : kv_end - 1;  // last visible key
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     float m = -INFINITY;
     float l = 0.f;
     uint8_t* p_row0 = pP + (size_t)row * 128;
@@ -288,7 +340,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
     // Decode tiles hold a few valid rows: warps whose 32 rows are all padding only keep the
     // barrier protocol going (their rows of P are never read back by anyone).
-    const bool warp_active = warp * 32 < n_q_tok * p.G;
+    const bool warp_active = quad * 32 < n_q_tok * p.G;
     const float sc = p.scale_log2;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j & 1;
@@ -319,14 +371,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // pass 1: row maximum (four independent chains; one warp per scheduler cannot hide a
       // long dependent chain). TMEM reads are software-pipelined.
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      tmem_ld_x32(ts, ra);
+      tmem_ld_x32(ts + (uint32_t)c_first * 32u, ra);
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+      for (int cl = 0; cl < kLocalChunks; ++cl) {
+        const int c = c_first + cl;
+        uint32_t(&cur)[32] = (cl & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (cl & 1) ? ra : rb;
         tmem_ld_wait_dep(cur);
-        // next chunk; after the last one, chunk 0 again for pass 2
-        tmem_ld_x32(ts + (uint32_t)((c + 1) % kChunks) * 32u, nxt);
+        // next chunk; after the last one, this warp's first chunk again for pass 2
+        tmem_ld_x32(ts + (uint32_t)(c_first + (cl + 1) % kLocalChunks) * 32u, nxt);
         if (need_mask) {
 #pragma unroll
           for (int t = 0; t < 32; t += 4) {
@@ -346,7 +399,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
       }
-      const float m_new = fmaxf(fmaxf(m, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
+      float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      if (kHalves2 == 2) {
+        // the row's maximum over the other warp's columns
+        // Any common upper bound of the row's scores serves as the softmax reference point, so
+        // each warp rounds its maximum up to bf16 and both use the larger of the two.
+        const __nv_bfloat16 mine = __float2bfloat16_ru(m_tile);
+        *reinterpret_cast<volatile unsigned short*>(&pair_max[j & 1][half][row]) =
+            __bfloat16_as_ushort(mine);
+        pair_publish();
+        if (!__all_sync(0xffffffffu, pair_wait())) {
+          ok = false;
+          break;
+        }
+        const unsigned short theirs =
+            *reinterpret_cast<volatile unsigned short*>(&pair_max[j & 1][half ^ 1][row]);
+        m_tile = fmaxf(__bfloat162float(mine), __bfloat162float(__ushort_as_bfloat16(theirs)));
+      }
+      const float m_new = fmaxf(m, m_tile);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
       // rows that have seen no key yet (m = -inf) hold O = 0 and l = 0: nothing to rescale
       const float alpha = (m == -INFINITY) ? 1.0f : ex2_approx((m - m_safe) * sc);
@@ -367,7 +437,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tc_fence_after();
           uint32_t rc[32];
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+          for (int cl = 0; cl < D / 32 / kHalves2; ++cl) {
+            const int c = half * (D / 32 / kHalves2) + cl;
             tmem_ld_x32(to + (uint32_t)c * 32u, rc);
             tmem_ld_wait_dep(rc);
 #pragma unroll
@@ -381,12 +452,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // buffer pass 1 left as "next")
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        constexpr int kFlip = kChunks & 1;  // parity of the buffer that holds chunk 0
-        uint32_t(&cur)[32] = ((c + kFlip) & 1) ? rb : ra;
-        uint32_t(&nxt)[32] = ((c + kFlip) & 1) ? ra : rb;
+      for (int cl = 0; cl < kLocalChunks; ++cl) {
+        const int c = c_first + cl;
+        constexpr int kFlip = kLocalChunks & 1;  // parity of the buffer that holds the first chunk
+        uint32_t(&cur)[32] = ((cl + kFlip) & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = ((cl + kFlip) & 1) ? ra : rb;
         tmem_ld_wait_dep(cur);
-        if (c + 1 < kChunks) tmem_ld_x32(ts + (uint32_t)(c + 1) * 32u, nxt);
+        if (cl + 1 < kLocalChunks) tmem_ld_x32(ts + (uint32_t)(c + 1) * 32u, nxt);
         uint32_t pk[16];
 #pragma unroll
         for (int t = 0; t < 32; t += 4) {
@@ -432,6 +504,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         ok = false;
       tc_fence_after();
     }
+    if (ok && warp_active && kHalves2 == 2) {
+      // each warp summed the probabilities of its own columns: the row's sum is both parts
+      // The fp32 sums reuse the words of the maxima: one more round first, after which the
+      // partner has read the last tile's maximum.
+      float* sums = reinterpret_cast<float*>(&pair_max[0][0][0]);   // [2][128]
+      pair_publish();
+      bool got = __all_sync(0xffffffffu, pair_wait());
+      if (got) {
+        *reinterpret_cast<volatile float*>(&sums[half * 128 + row]) = l;
+        pair_publish();
+        got = __all_sync(0xffffffffu, pair_wait());
+      }
+      if (!got) ok = false;
+      else l += *reinterpret_cast<volatile float*>(&sums[(half ^ 1) * 128 + row]);
+    }
     if (ok && warp_active) {  // warp-uniform: every lane takes part in the TMEM reads
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const long long tok = (long long)q_tok0 + tok_local;
@@ -449,7 +536,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         constexpr int kCh = D / 8;  // 16-byte chunks per row
         uint8_t* my_row = smem + (size_t)row * 128;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cl = 0; cl < D / 32 / kHalves2; ++cl) {
+          const int c = half * (D / 32 / kHalves2) + cl;   // this warp's share of O's columns
           uint32_t rc[32];
           tmem_ld_x32(to + (uint32_t)c * 32u, rc);
           tmem_ld_wait_dep(rc);
@@ -465,12 +553,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
         __syncwarp();
-        const unsigned long long my_dst = valid_row ? reinterpret_cast<unsigned long long>(dst16) : 0ull;
+        bool staged = true;
+        if (kHalves2 == 2) {   // the other warp's columns of the same rows
+          pair_publish();
+          staged = __all_sync(0xffffffffu, pair_wait());
+        }
+        const unsigned long long my_dst =
+            (valid_row && staged) ? reinterpret_cast<unsigned long long>(dst16) : 0ull;
         const int j = lane % kCh;
 #pragma unroll
         for (int it = 0; it < kCh; ++it) {
-          const int rl = it * (32 / kCh) + lane / kCh;  // row of this warp
-          const int rr = warp * 32 + rl;
+          if (it % kHalves2 != half) continue;            // the pair shares the rows' stores
+          const int rl = it * (32 / kCh) + lane / kCh;  // row of this quadrant
+          const int rr = quad * 32 + rl;
           const unsigned long long d = __shfl_sync(0xffffffffu, my_dst, rl);
           if (d != 0ull) {
             const uint4 q = *reinterpret_cast<const uint4*>(
@@ -478,10 +573,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(d) + 8 * j) = q;
           }
         }
-        if (valid_row && p.lse_out) p.lse_out[tok * p.Hq + head] = lse;
+        if (valid_row && p.lse_out && half == 0) p.lse_out[tok * p.Hq + head] = lse;
       } else {
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cl = 0; cl < D / 32 / kHalves2; ++cl) {
+        const int c = half * (D / 32 / kHalves2) + cl;
         uint32_t rc[32];
         if (n_tiles > 0) {
           tmem_ld_x32(to + (uint32_t)c * 32u, rc);
@@ -510,7 +606,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
       }
-      if (valid_row) {
+      if (valid_row && half == 0) {
         if (num_splits <= 1) {
           if (p.lse_out) p.lse_out[tok * p.Hq + head] = lse;
         } else {
@@ -524,7 +620,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tail_signal(p.sig, total_blocks);
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -660,7 +756,7 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
   }
   if (max_splits <= 1) a.sig = sig;
   dim3 grid((unsigned)num_work, (unsigned)Hkv);
-  attention_kernel<D, TK><<<grid, kAttThreads, smem, stream>>>(tq, tk, tv, a);
+  attention_kernel<D, TK><<<grid, AttnShape<TK>::kThreads, smem, stream>>>(tq, tk, tv, a);
   if (cudaGetLastError() != cudaSuccess) return -5;
   a.sig = sig;
   if (max_splits > 1) {

@@ -7,6 +7,7 @@ servers broadcast admitted requests from rank 0 before each step).
 
 from __future__ import annotations
 
+import os
 import time
 from typing import Iterable, Optional
 
@@ -82,6 +83,14 @@ class LLMEngine:
         if config.speculative is not None:
             from ..spec_decode.propose import attach_speculation
             attach_speculation(self)
+        # The objects built so far (weights' wrappers, graphs, tables) live as long as the
+        # engine: take them out of the cyclic collector's generations, so that a full
+        # collection during serving does not walk them. With several ranks stepping in lockstep
+        # a long collection on one rank stalls all of them.
+        if os.environ.get("AB200_GC_FREEZE", "1") != "0":
+            import gc
+            gc.collect()
+            gc.freeze()
 
     @classmethod
     def from_engine_args(cls, args: EngineArgs, device=None, comm=None) -> "LLMEngine":

@@ -200,7 +200,10 @@ def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_spl
     tile_strides = None
     if w.tiled:
         assert w.q.stride(3) == 1 and w.q.stride(2) == 128
-        tile_strides = (w.q.stride(0), w.q.stride(1))
+        # (the stride of a dimension of size 1 is arbitrary: substitute the packed value)
+        sk = w.q.stride(1) if w.q.shape[1] > 1 else 2048
+        sn = w.q.stride(0) if w.q.shape[0] > 1 else sk * w.q.shape[1]
+        tile_strides = (sn, sk)
         ldw = K
     else:
         assert w.q.stride(1) == 1
