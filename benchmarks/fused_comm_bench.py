@@ -7,8 +7,12 @@ of one node (one process per GPU):
 Cases (Llama-3.1-8B shapes, bf16; n = tokens per rank):
 
 * qkv_scatter: QKV projection whose epilogue stores every head shard into the rank that owns
-  it (Ulysses sequence -> head exchange) vs the same GEMM into local memory followed by
-  ``all_to_all_single``;
+  it (Ulysses sequence -> head exchange) and signals from its last block, followed by a
+  consumer kernel (the activation quantiser over the received rows) that waits for the ranks'
+  signals, vs the same GEMM into local memory, ``all_to_all_single`` and the same consumer;
+* gemm_reduce_norm: row-parallel o_proj leaving its partial product in the symmetric heap +
+  the kernel that waits for the ranks' signals, sums the partials, adds the residual and
+  normalises, vs the GEMM, ``dist.all_reduce`` and the RMSNorm(+residual) kernel;
 * allreduce: row-parallel o_proj writing its partial product into the symmetric heap + the
   peer-memory all-reduce (one-shot and two-shot kernels) vs the GEMM + ``dist.all_reduce``.
 
@@ -82,7 +86,11 @@ def main():
     for n in sizes:
         x = R(n, H)
         # ---- QKV GEMM with the head exchange in its epilogue
-        t_fused = timed(lambda: comm.qkv_scatter_heads(x, wqkv, blk), a.iters)
+        def fused_x1():
+            view = comm.qkv_scatter_heads(x, wqkv, blk)
+            return ops.quant_fp8_row(view, sync=comm.take_wait("qkv"))
+
+        t_fused = timed(fused_x1, a.iters)
         send = torch.empty(n, world * blk, dtype=torch.bfloat16, device=dev)
         recv = torch.empty(world * n, blk, dtype=torch.bfloat16, device=dev)
 
@@ -91,6 +99,7 @@ def main():
             # [n, W*blk] -> W chunks of [n, blk]
             chunks = send.view(n, world, blk).transpose(0, 1).contiguous()
             dist.all_to_all_single(recv.view(world, n, blk), chunks)
+            return ops.quant_fp8_row(recv)
 
         t_base = timed(unfused, a.iters)
         flops = 2.0 * n * world * blk * H
@@ -125,6 +134,28 @@ def main():
             roof = max(flops / (peak * 1e12), moved / (LINK_GBS * 1e9)) * 1e6
             res.append({"case": "gemm_allreduce_" + algo, "tokens": n, "fused_us": t_f,
                         "gemm_then_nccl_us": t_b, "speedup": t_b / t_f, "roofline_us": roof,
+                        "fraction_of_roofline": roof / t_f, "bytes_read_per_gpu": moved,
+                        "flops": flops})
+        # ---- row-parallel GEMM + reduction folded into the following RMSNorm
+        if comm.folds_reduce(n, H):
+            gamma = R(H)
+            resid = R(n, H)
+
+            def fused_rn():
+                comm.begin_forward()
+                pend = comm.linear_partial(a_in, wo)
+                return comm.reduce_rmsnorm(pend, gamma, 1e-5, residual=resid)
+
+            def nccl_rn():
+                ops.linear(a_in, wo, out=out_local)
+                dist.all_reduce(out_local)
+                return ops.rmsnorm(out_local, gamma, 1e-5, residual=resid)
+
+            t_f, t_b2 = timed(fused_rn, a.iters), timed(nccl_rn, a.iters)
+            moved = n * H * 2.0 * (world - 1)
+            roof = max(flops / (peak * 1e12), moved / (LINK_GBS * 1e9)) * 1e6
+            res.append({"case": "gemm_reduce_norm", "tokens": n, "fused_us": t_f,
+                        "gemm_nccl_norm_us": t_b2, "speedup": t_b2 / t_f, "roofline_us": roof,
                         "fraction_of_roofline": roof / t_f, "bytes_read_per_gpu": moved,
                         "flops": flops})
     ops.check_status()
