@@ -43,6 +43,9 @@ typedef struct Ab200LinearDesc {
   // 16-row tiles and between k-tiles (both 0: row-major). `ldw` is ignored for a tiled weight.
   long long w_tile_stride_n;
   long long w_tile_stride_k;
+  // 1: w is a parameter that no kernel of the stream writes; its first tiles may then be
+  // requested before the kernel waits for the kernel launched before it
+  int w_static;
 } Ab200LinearDesc;
 
 // ---- gemm_bf16.cu

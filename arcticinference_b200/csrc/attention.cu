@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include "api.h"
+#include "common/pdl.cuh"
 #include "common/peer.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
@@ -110,7 +111,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const unsigned int total_blocks = gridDim.x * gridDim.y;
+  // The kernel before this one in the stream may still be running (programmatic dependent
+  // launch): barrier and TMEM set-up and the clearing of the K/V stages below overlap its
+  // tail. The work list is uploaded by the host before the step's first kernel and is the
+  // only global memory read ahead of pdl_wait(); nothing is written before it.
+  pdl_trigger();
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need 1024-byte alignment
+    pdl_wait();
     if (threadIdx.x == 0) report_error(p.status, kErrBadArgument, 900, (int)(smem_u32(smem) & 1023u));
     tail_signal(p.sig, total_blocks);
     return;
@@ -144,6 +151,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int q_tok0 = wk[1];
   const int n_q_tok = wk[2];
   if (n_q_tok <= 0) {  // padding entry of a fixed-size work list
+    pdl_wait();
     tail_signal(p.sig, total_blocks);
     return;
   }
@@ -193,6 +201,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;           // S buffers at columns 0, TK
   const uint32_t tO = tmem_base + 2 * TK;  // output accumulator, D columns
@@ -634,6 +643,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ o_part,
                                        const int* __restrict__ tok_splits, long long T, int Hq,
                                        __nv_bfloat16* __restrict__ out, long long ldo,
                                        float* __restrict__ lse_out, AttnArgs pa) {
+  pdl_wait();
+  pdl_trigger();
   const long long tok = blockIdx.x;
   const int ns = tok_splits[tok];
   if (ns <= 1) {
@@ -756,12 +767,14 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
   }
   if (max_splits <= 1) a.sig = sig;
   dim3 grid((unsigned)num_work, (unsigned)Hkv);
-  attention_kernel<D, TK><<<grid, AttnShape<TK>::kThreads, smem, stream>>>(tq, tk, tv, a);
+  (void)launch_pdl(attention_kernel<D, TK>, grid, dim3(AttnShape<TK>::kThreads), smem, stream, tq,
+                   tk, tv, a);
   if (cudaGetLastError() != cudaSuccess) return -5;
   a.sig = sig;
   if (max_splits > 1) {
-    attention_merge_kernel<D><<<(unsigned)T, 128, 0, stream>>>(
-        o_part, lse_part, tok_splits, T, Hq, reinterpret_cast<__nv_bfloat16*>(out), ldo, lse_out, a);
+    (void)launch_pdl(attention_merge_kernel<D>, dim3((unsigned)T), dim3(128), 0, stream, o_part,
+                     lse_part, tok_splits, T, Hq, reinterpret_cast<__nv_bfloat16*>(out), ldo,
+                     lse_out, a);
     if (cudaGetLastError() != cudaSuccess) return -5;
   }
   return 0;

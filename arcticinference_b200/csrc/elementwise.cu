@@ -13,6 +13,7 @@
 #include <math.h>
 
 #include "api.h"
+#include "common/pdl.cuh"
 #include "common/peer.cuh"
 #include "common/ptx.cuh"
 
@@ -55,6 +56,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void embedding_kernel(const long long* __restrict__ ids, const bf16* __restrict__ table,
                                  bf16* __restrict__ out, int hidden, long long vocab,
                                  long long vocab_start) {
+  pdl_wait();
+  pdl_trigger();
   const long long t = blockIdx.x;
   long long id = ids[t] - vocab_start;
   const bool valid = id >= 0 && id < vocab;
@@ -74,6 +77,8 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ residual,
                const bf16* __restrict__ weight, bf16* __restrict__ y, long long ldy, int hidden,
                float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int nvec = hidden / 8;
@@ -124,6 +129,8 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fixed_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ residual,
                      const bf16* __restrict__ weight, bf16* __restrict__ y, long long ldy,
                      float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   constexpr int hidden = VPT * 8 * kNormThreads;
   const long long row = blockIdx.x;
@@ -175,6 +182,8 @@ __global__ void __launch_bounds__(kNormThreads)
 layernorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
                  const bf16* __restrict__ gamma, const bf16* __restrict__ beta,
                  bf16* __restrict__ y, int hidden, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int nvec = hidden / 8;
@@ -240,6 +249,8 @@ constexpr int kSiluUnroll = 4;
 __global__ void __launch_bounds__(256, 4)
 silu_mul_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, long long T, int inter,
                 int nblk) {
+  pdl_wait();
+  pdl_trigger();
   const int nvec = inter / 8;
   const long long per_row = (long long)nblk * nvec;
   const long long total = T * per_row;
@@ -288,6 +299,8 @@ rope_cache_kernel(bf16* __restrict__ qkv, long long ld, const long long* __restr
                   bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int Hq, int Hkv, int D,
                   int block_size, long long num_slots, int rotate_q, int* status,
                   const PeerWait wait) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float cs[];  // cos[D/2] | sin[D/2]
   // rows scattered here by the other ranks' QKV projections: wait for their completion signal
   if (wait.world > 0) {
@@ -361,6 +374,8 @@ rope_cache_kernel(bf16* __restrict__ qkv, long long ld, const long long* __restr
 __global__ void gather_rows_kernel(const bf16* __restrict__ src, long long ld,
                                    const long long* __restrict__ idx, bf16* __restrict__ dst,
                                    int hidden) {
+  pdl_wait();
+  pdl_trigger();
   const long long r = blockIdx.x;
   const uint4* s = reinterpret_cast<const uint4*>(src + idx[r] * ld);
   uint4* d = reinterpret_cast<uint4*>(dst + r * (long long)hidden);
@@ -397,6 +412,8 @@ argmax_sample_kernel(const T* __restrict__ logits, long long ld, int V,
                      const float* __restrict__ temperature,
                      const unsigned long long* __restrict__ seeds, long long* __restrict__ out_ids,
                      float* __restrict__ out_vals, long long index_offset) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sv[32];
   __shared__ int si[32];
   const long long row = blockIdx.x;
@@ -459,6 +476,8 @@ argmax_sample_kernel(const T* __restrict__ logits, long long ld, int V,
 __global__ void patch_ids_kernel(long long* __restrict__ ids, const long long* __restrict__ src_rows,
                                  const long long* __restrict__ prev_ids, long long n,
                                  long long n_prev) {
+  pdl_wait();
+  pdl_trigger();
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long long j = src_rows[i];
@@ -475,7 +494,7 @@ int ab200_embedding(const void* ids, const void* table, void* out, long long T, 
                     long long vocab, long long vocab_start, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hidden % 8) return -2;
-  embedding_kernel<<<(unsigned)T, 128, 0, stream>>>(
+  (void)launch_pdl(embedding_kernel, dim3((unsigned)T), dim3(128), 0, stream, 
       reinterpret_cast<const long long*>(ids), reinterpret_cast<const bf16*>(table),
       reinterpret_cast<bf16*>(out), hidden, vocab, vocab_start);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -492,13 +511,13 @@ int ab200_rmsnorm(const void* x, long long ldx, void* residual, const void* weig
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) |
                          reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (aligned && hidden == 8 * kNormThreads)
-    rmsnorm_fixed_kernel<1><<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, eps);
+    (void)launch_pdl(rmsnorm_fixed_kernel<1>, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, eps);
   else if (aligned && hidden == 16 * kNormThreads)
-    rmsnorm_fixed_kernel<2><<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, eps);
+    (void)launch_pdl(rmsnorm_fixed_kernel<2>, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, eps);
   else if (aligned && hidden == 32 * kNormThreads)
-    rmsnorm_fixed_kernel<4><<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, eps);
+    (void)launch_pdl(rmsnorm_fixed_kernel<4>, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, eps);
   else
-    rmsnorm_kernel<<<(unsigned)T, kNormThreads, 0, stream>>>(xp, ldx, rp, wp, yp, ldy, hidden, eps);
+    (void)launch_pdl(rmsnorm_kernel, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, hidden, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -506,7 +525,7 @@ int ab200_layernorm(const void* x, const void* residual, const void* gamma, cons
                     void* y, long long T, int hidden, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((hidden % 8) || hidden > kNormThreads * kMaxVec * 8) return -2;
-  layernorm_kernel<<<(unsigned)T, kNormThreads, 0, stream>>>(
+  (void)launch_pdl(layernorm_kernel, dim3((unsigned)T), dim3(kNormThreads), 0, stream, 
       reinterpret_cast<const bf16*>(x), reinterpret_cast<const bf16*>(residual),
       reinterpret_cast<const bf16*>(gamma), reinterpret_cast<const bf16*>(beta),
       reinterpret_cast<bf16*>(y), hidden, eps);
@@ -520,7 +539,7 @@ int ab200_silu_mul(const void* x, void* out, long long T, int inter, int nblk,
   const long long total = T * nblk * (inter / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const bf16*>(x),
+  (void)launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, reinterpret_cast<const bf16*>(x),
                                                         reinterpret_cast<bf16*>(out), T, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
@@ -550,7 +569,7 @@ int ab200_rope_cache_wait(void* qkv, long long ld, const void* positions, const 
     w.epoch_ctr = reinterpret_cast<const unsigned int*>(sync->wait_epoch_ctr);
     w.world = sync->wait_world;
   }
-  rope_cache_kernel<<<(unsigned)T, 256, D * sizeof(float), stream>>>(
+  (void)launch_pdl(rope_cache_kernel, dim3((unsigned)T), dim3(256), D * sizeof(float), stream, 
       reinterpret_cast<bf16*>(qkv), ld, reinterpret_cast<const long long*>(positions),
       reinterpret_cast<const long long*>(slots), reinterpret_cast<const float*>(inv_freq),
       reinterpret_cast<bf16*>(k_cache), reinterpret_cast<bf16*>(v_cache), Hq, Hkv, D, block_size,
@@ -562,7 +581,7 @@ int ab200_gather_rows(const void* src, long long ld, const void* idx, void* dst,
                       int hidden, cudaStream_t stream) {
   if (R <= 0) return 0;
   if ((hidden % 8) || (ld % 8)) return -2;
-  gather_rows_kernel<<<(unsigned)R, 128, 0, stream>>>(
+  (void)launch_pdl(gather_rows_kernel, dim3((unsigned)R), dim3(128), 0, stream, 
       reinterpret_cast<const bf16*>(src), ld, reinterpret_cast<const long long*>(idx),
       reinterpret_cast<bf16*>(dst), hidden);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -571,7 +590,7 @@ int ab200_gather_rows(const void* src, long long ld, const void* idx, void* dst,
 int ab200_patch_ids(void* ids, const void* src_rows, const void* prev_ids, long long n,
                     long long n_prev, cudaStream_t stream) {
   if (n <= 0) return 0;
-  patch_ids_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+  (void)launch_pdl(patch_ids_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 
       reinterpret_cast<long long*>(ids), reinterpret_cast<const long long*>(src_rows),
       reinterpret_cast<const long long*>(prev_ids), n, n_prev);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -583,12 +602,12 @@ int ab200_argmax_sample(const void* logits, int dtype, long long ld, long long B
                         long long index_offset, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (dtype == 0)
-    argmax_sample_kernel<bf16><<<(unsigned)B, 1024, 0, stream>>>(
+    (void)launch_pdl(argmax_sample_kernel<bf16>, dim3((unsigned)B), dim3(1024), 0, stream, 
         reinterpret_cast<const bf16*>(logits), ld, V, reinterpret_cast<const float*>(temperature),
         reinterpret_cast<const unsigned long long*>(seeds), reinterpret_cast<long long*>(out_ids),
         reinterpret_cast<float*>(out_vals), index_offset);
   else
-    argmax_sample_kernel<float><<<(unsigned)B, 1024, 0, stream>>>(
+    (void)launch_pdl(argmax_sample_kernel<float>, dim3((unsigned)B), dim3(1024), 0, stream, 
         reinterpret_cast<const float*>(logits), ld, V, reinterpret_cast<const float*>(temperature),
         reinterpret_cast<const unsigned long long*>(seeds), reinterpret_cast<long long*>(out_ids),
         reinterpret_cast<float*>(out_vals), index_offset);

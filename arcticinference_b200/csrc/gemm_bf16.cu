@@ -29,6 +29,7 @@
 #include <unordered_map>
 
 #include "api.h"
+#include "common/pdl.cuh"
 #include "common/peer.cuh"
 #include "common/ptx.cuh"
 #include "common/tensormap.h"
@@ -61,6 +62,7 @@ struct GemmArgs {
   int a_tiled, b_tiled;  // the operand is an fp8 weight stored as [rows/16][K/128][16][128]
   int fp8;         // 1: operands are e4m3 bytes (kind::f8f6f4), 128 k-elements per stage
   int kblock_elems;  // k-elements per stage: 64 (bf16) or 128 (fp8)
+  int prefetch_w;    // 1: the weight operand is written by no kernel of the stream (a parameter)
   const float* scale_a;  // fp8: one factor per A-operand row (null = 1)
   const float* scale_b;  // fp8: one factor per B-operand row
   uint32_t tmem_cols;
@@ -112,6 +114,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // the next kernel of the stream may be placed as SMs free up; it waits for this one itself
+  pdl_trigger();
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -140,6 +145,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    // The weight operand is written by no kernel, so its first tiles are requested before
+    // this kernel waits for the one before it in the stream: the stream of weights starts
+    // while that kernel drains. Each of these stages has had its weight bytes announced to
+    // its full barrier; the activation tile and the barrier's arrival follow after the wait.
+    const bool w_is_b = !p.transposed;
+    int pre = 0;
+    if (lane == 0 && p.prefetch_w && blockIdx.x < total_work) {
+      const int w0 = blockIdx.x;
+      const int tile_a0 = w0 % p.tiles_a;
+      const int rest0 = w0 / p.tiles_a;
+      const int tile_b0 = rest0 % p.tiles_b;
+      const int kb00 = (rest0 / p.tiles_b) * p.kblocks_per_split;
+      const int kb01 = min(kb00 + p.kblocks_per_split, p.kblocks_total);
+      pre = min(p.stages, kb01 - kb00);
+      for (int s = 0; s < pre; ++s) {
+        const int kb = kb00 + s;
+        const uint32_t dst = smem_base + (uint32_t)s * stage_bytes;
+        if (w_is_b) {
+          mbar_expect_tx(full_bar(s), b_bytes);
+          if (p.b_tiled)
+            tma_load_4d(dst + kABytes, &tmap_b, full_bar(s), 0, 0, kb, tile_b0 * (p.bn / 16));
+          else
+            tma_load_2d(dst + kABytes, &tmap_b, full_bar(s), kb * p.kblock_elems, tile_b0 * p.bn);
+        } else {
+          mbar_expect_tx(full_bar(s), kABytes);
+          if (p.a_tiled)
+            tma_load_4d(dst, &tmap_a, full_bar(s), 0, 0, kb, tile_a0 * (kBlockM / 16));
+          else
+            tma_load_2d(dst, &tmap_a, full_bar(s), kb * p.kblock_elems, tile_a0 * kBlockM);
+        }
+      }
+    }
+    pdl_wait();
     bool peers_ok = true;
     if (p.wait.world > 0) {
       peers_ok = wait_peers(p.wait, p.status, kWaitLimitNs);
@@ -151,6 +189,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = peers_ok;
+      if (!ok) {
+        // the prefetched weight tiles still land: let their barriers complete, then leave
+        for (int s = 0; s < pre; ++s) {
+          mbar_arrive(full_bar(s));
+          mbar_drain(full_bar(s), 0);
+        }
+      }
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const int tile_a = w % p.tiles_a;
         const int rest = w / p.tiles_a;
@@ -163,13 +208,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+          const bool have_w = issued < pre;   // this stage's weight tile is already on its way
+          const bool load_a = !(have_w && !w_is_b);
+          const bool load_b = !(have_w && w_is_b);
+          mbar_arrive_expect_tx(full_bar(stage),
+                                have_w ? (w_is_b ? (uint32_t)kABytes : b_bytes) : stage_bytes);
           const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes;
-          if (p.a_tiled)
-            tma_load_4d(a_dst, &tmap_a, full_bar(stage), 0, 0, kb, tile_a * (kBlockM / 16));
-          else
-            tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * p.kblock_elems, tile_a * kBlockM);
-          if (p.b_tiled) {
+          if (load_a) {
+            if (p.a_tiled)
+              tma_load_4d(a_dst, &tmap_a, full_bar(stage), 0, 0, kb, tile_a * (kBlockM / 16));
+            else
+              tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * p.kblock_elems, tile_a * kBlockM);
+          }
+          if (!load_b) {
+          } else if (p.b_tiled) {
             // 2 KB pieces (16 rows x 128 bytes) that are contiguous in memory, bn / 16 of them
             tma_load_4d(a_dst + kABytes, &tmap_b, full_bar(stage), 0, 0, kb, tile_b * (p.bn / 16));
           } else if (!p.b_mn_major) {
@@ -260,6 +312,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // --------------------------------- epilogue --------------------------------
+    pdl_wait();  // scales, bias and residual come from earlier kernels; the output may still be read by one
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     const int row = quad * 32 + lane;
     int acc = 0;
@@ -480,6 +533,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
                                      const __nv_bfloat16* __restrict__ residual, long long ldr,
                                      int act, const float* __restrict__ scale_m,
                                      const float* __restrict__ scale_n, const TailSignal sig) {
+  pdl_wait();
+  pdl_trigger();
   const long long n4 = N / 4;
   const long long total = (long long)M * n4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -650,7 +705,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
                          cudaStream_t stream, const void* const* peer_ptrs, int world,
                          int peer_cols, long long peer_row_off, const float* scale_x = nullptr,
                          const float* scale_w = nullptr, const Ab200PeerSync* sync = nullptr,
-                         long long w_tile_stride_n = 0, long long w_tile_stride_k = 0) {
+                         long long w_tile_stride_n = 0, long long w_tile_stride_k = 0,
+                         int w_static = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const bool fp8 = scale_x != nullptr;  // e4m3 operands with per-token / per-feature scales
   const int opa = fp8 ? 16 : 8;         // operand rows must start on 16-byte boundaries
@@ -818,6 +874,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   CUtensorMap ta, tb;
   a.a_tiled = (w_tiled && a.transposed) ? 1 : 0;
   a.b_tiled = (w_tiled && !a.transposed) ? 1 : 0;
+  a.prefetch_w = w_static ? 1 : 0;
   if (get_tmap(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K,
                a.a_tiled ? (uint64_t)w_tile_stride_k : (uint64_t)lda, kBlockM, fp8,
                a.a_tiled ? (uint64_t)w_tile_stride_n : 0) != 0)
@@ -831,19 +888,21 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   const int grid = total < sms ? total : sms;
   const size_t smem =
       (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 1024;
-  gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, a);
-  if (cudaGetLastError() != cudaSuccess) return -5;
+  if (launch_pdl(gemm_bf16_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, a) !=
+      cudaSuccess)
+    return -5;
 
   if (a.splits > 1) {
     const long long total4 = (long long)M * (N / 4);
     int blocks = (int)((total4 + 255) / 256);
     if (blocks > sms * 8) blocks = sms * 8;
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(
-        reinterpret_cast<const float*>(workspace), a.splits, a.partial_stride, M, N,
-        reinterpret_cast<__nv_bfloat16*>(final_out), ldo,
-        reinterpret_cast<const __nv_bfloat16*>(bias),
-        reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act, scale_x, scale_w, sig);
-    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream,
+                   reinterpret_cast<const float*>(workspace), a.splits, a.partial_stride, M, N,
+                   reinterpret_cast<__nv_bfloat16*>(final_out), ldo,
+                   reinterpret_cast<const __nv_bfloat16*>(bias),
+                   reinterpret_cast<const __nv_bfloat16*>(residual), ldr, act, scale_x, scale_w,
+                   sig) != cudaSuccess)
+      return -5;
   }
   return 0;
 }
@@ -911,7 +970,7 @@ int ab200_linear_desc(const Ab200LinearDesc* d, cudaStream_t stream) {
                        stream, scatter ? d->peer_ptrs : nullptr, scatter ? d->world : 0,
                        scatter ? d->peer_cols : 0, scatter ? d->peer_row_off : 0,
                        reinterpret_cast<const float*>(d->sx), reinterpret_cast<const float*>(d->sw),
-                       &d->sync, d->w_tile_stride_n, d->w_tile_stride_k);
+                       &d->sync, d->w_tile_stride_n, d->w_tile_stride_k, d->w_static);
 }
 
 // out[M,N] = x[M,K] * wt[K,N] with wt row-major (N contiguous): exercises the

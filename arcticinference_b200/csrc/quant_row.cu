@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "api.h"
+#include "common/pdl.cuh"
 #include "common/peer.cuh"
 #include "common/ptx.cuh"
 
@@ -96,6 +97,8 @@ __global__ void __launch_bounds__(512)
 quant_fp8_row_kernel(const bf16* __restrict__ x, long long ldx, uint8_t* __restrict__ xq,
                      long long ldq, float* __restrict__ sx, int K, const PeerWait wait,
                      int* status) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   // x may be rows that other ranks' attention kernels scattered here: wait for their signal
   if (wait.world > 0) {
@@ -148,6 +151,8 @@ rmsnorm_quant_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict
                      const bf16* __restrict__ weight, uint8_t* __restrict__ yq, long long ldq,
                      float* __restrict__ sy, bf16* __restrict__ y, long long ldy, int hidden,
                      float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int nvec = hidden / 8;
@@ -239,6 +244,8 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4& gq, const uint4& uq) {
 __global__ void __launch_bounds__(kSiluQThreads)
 silu_mul_quant_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ outq, long long ldq,
                       float* __restrict__ so, int inter, int nblk) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ uint4 prod[];   // nblk * inter / 8 vectors of 8 bf16
   __shared__ float red[32];
   const long long row = blockIdx.x;
@@ -319,15 +326,15 @@ int ab200_quant_fp8_row_wait(const void* x, long long ldx, void* xq, long long l
   float* sp = reinterpret_cast<float*>(sx);
   const int nvec = K / 8;
   if (nvec <= 256)
-    quant_fp8_row_kernel<1><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<1>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 512)
-    quant_fp8_row_kernel<2><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<2>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 1024)
-    quant_fp8_row_kernel<4><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<4>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 2048)
-    quant_fp8_row_kernel<8><<<(unsigned)M, 256, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<8>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
   else
-    quant_fp8_row_kernel<8><<<(unsigned)M, 512, 0, stream>>>(xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<8>, dim3((unsigned)M), dim3(512), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -347,7 +354,7 @@ int ab200_rmsnorm_quant(const void* x, long long ldx, void* residual, const void
   bf16* yp = reinterpret_cast<bf16*>(y);
   const int nvec = hidden / 8;
 #define AB200_LAUNCH_NQ(V)                                                                     \
-  rmsnorm_quant_kernel<V><<<(unsigned)T, kQThreads, 0, stream>>>(xp, ldx, rp, wp, qp, ldq, sp, \
+  (void)launch_pdl(rmsnorm_quant_kernel<V>, dim3((unsigned)T), dim3(kQThreads), 0, stream, xp, ldx, rp, wp, qp, ldq, sp, \
                                                                  yp, ldy, hidden, eps)
   if (nvec <= 256) AB200_LAUNCH_NQ(1);
   else if (nvec <= 512) AB200_LAUNCH_NQ(2);
@@ -378,7 +385,7 @@ int ab200_silu_mul_quant(const void* x, void* outq, long long ldq, void* so, lon
       return -3;
     attr_set[dev] = true;
   }
-  silu_mul_quant_kernel<<<(unsigned)T, kSiluQThreads, smem, stream>>>(xp, qp, ldq, sp, inter, nblk);
+  (void)launch_pdl(silu_mul_quant_kernel, dim3((unsigned)T), dim3(kSiluQThreads), smem, stream, xp, qp, ldq, sp, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -17,6 +17,7 @@
 #include <math.h>
 
 #include "api.h"
+#include "common/pdl.cuh"
 #include "common/ptx.cuh"
 
 namespace ab200 {
@@ -49,6 +50,8 @@ __global__ void __launch_bounds__(kSpecThreads)
 spec_ln_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w,
                const bf16* __restrict__ b, bf16* __restrict__ y, long long ldy, int hidden,
                float eps, float out_scale) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   float v[kSpecMaxPerThread];
@@ -78,6 +81,8 @@ mlp_spec_step_kernel(const bf16* __restrict__ proj, long long ldp, const bf16* _
                      const long long* __restrict__ tok, float emb_scale,
                      const bf16* __restrict__ ln_w, const bf16* __restrict__ ln_b,
                      bf16* __restrict__ out, long long ldo, int dim, float eps, int tanh_approx) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const bf16* e = emb + tok[row] * (long long)dim;
@@ -112,6 +117,8 @@ sum_lstm_kernel(const bf16* __restrict__ gates, long long ldg, const bf16* __res
                 const bf16* __restrict__ b_cell, const bf16* __restrict__ w_state,
                 const bf16* __restrict__ b_state, bf16* __restrict__ c_out,
                 bf16* __restrict__ h_out, long long ldo, int D, float eps, int tanh_approx) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const bf16* e = emb + tok[row] * (long long)emb_cols;
@@ -182,6 +189,8 @@ __global__ void verify_greedy_kernel(const long long* __restrict__ input_ids,
                                      int* __restrict__ accepted, long long* __restrict__ next_tok,
                                      long long* __restrict__ sel_row,
                                      long long* __restrict__ out_tokens) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= R) return;
   const int s = row_start[r];
@@ -209,7 +218,7 @@ int ab200_spec_ln(const void* x, long long ldx, const void* w, const void* b, vo
                   cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (hidden > kSpecThreads * kSpecMaxPerThread) return -2;
-  spec_ln_kernel<<<(unsigned)rows, kSpecThreads, 0, stream>>>(
+  (void)launch_pdl(spec_ln_kernel, dim3((unsigned)rows), dim3(kSpecThreads), 0, stream, 
       reinterpret_cast<const bf16*>(x), ldx, reinterpret_cast<const bf16*>(w),
       reinterpret_cast<const bf16*>(b), reinterpret_cast<bf16*>(y), ldy, hidden, eps, out_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -221,7 +230,7 @@ int ab200_mlp_spec_step(const void* proj, long long ldp, const void* emb, const 
                         cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (dim > kSpecThreads * kSpecMaxPerThread) return -2;
-  mlp_spec_step_kernel<<<(unsigned)rows, kSpecThreads, 0, stream>>>(
+  (void)launch_pdl(mlp_spec_step_kernel, dim3((unsigned)rows), dim3(kSpecThreads), 0, stream, 
       reinterpret_cast<const bf16*>(proj), ldp, reinterpret_cast<const bf16*>(emb),
       reinterpret_cast<const long long*>(tok), emb_scale, reinterpret_cast<const bf16*>(ln_w),
       reinterpret_cast<const bf16*>(ln_b), reinterpret_cast<bf16*>(out), ldo, dim, eps, tanh_approx);
@@ -235,7 +244,7 @@ int ab200_sum_lstm(const void* gates, long long ldg, const void* emb, int emb_co
                    int D, float eps, int tanh_approx, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D > kSpecThreads * kSpecMaxPerThread / 2 || (emb_cols != D && emb_cols != 4 * D)) return -2;
-  sum_lstm_kernel<<<(unsigned)rows, kSpecThreads, 0, stream>>>(
+  (void)launch_pdl(sum_lstm_kernel, dim3((unsigned)rows), dim3(kSpecThreads), 0, stream, 
       reinterpret_cast<const bf16*>(gates), ldg, reinterpret_cast<const bf16*>(emb), emb_cols,
       reinterpret_cast<const long long*>(tok), alpha, reinterpret_cast<const bf16*>(prev_c), ldc,
       reinterpret_cast<const bf16*>(w_cell), reinterpret_cast<const bf16*>(b_cell),
@@ -248,7 +257,7 @@ int ab200_verify_greedy(const void* input_ids, const void* target, const void* r
                         const void* num_draft, int R, int max_draft, void* accepted,
                         void* next_tok, void* sel_row, void* out_tokens, cudaStream_t stream) {
   if (R <= 0) return 0;
-  verify_greedy_kernel<<<(R + 127) / 128, 128, 0, stream>>>(
+  (void)launch_pdl(verify_greedy_kernel, dim3((R + 127) / 128), dim3(128), 0, stream, 
       reinterpret_cast<const long long*>(input_ids), reinterpret_cast<const long long*>(target),
       reinterpret_cast<const int*>(row_start), reinterpret_cast<const int*>(num_draft), R,
       max_draft, reinterpret_cast<int*>(accepted), reinterpret_cast<long long*>(next_tok),

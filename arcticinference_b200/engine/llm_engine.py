@@ -83,6 +83,9 @@ class LLMEngine:
         if config.speculative is not None:
             from ..spec_decode.propose import attach_speculation
             attach_speculation(self)
+        if self.device.type == "cuda":
+            from .sleep import mark_static_weights
+            mark_static_weights(self)
         # The objects built so far (weights' wrappers, graphs, tables) live as long as the
         # engine: take them out of the cyclic collector's generations, so that a full
         # collection during serving does not walk them. With several ranks stepping in lockstep

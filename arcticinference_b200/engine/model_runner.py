@@ -79,7 +79,7 @@ class PendingStep:
     """A step that has been queued on the device."""
 
     __slots__ = ("out", "rows", "ids_dev", "hidden", "num_tokens", "mode", "ids_host", "event",
-                 "row_of", "logprobs", "prompt_logprobs")
+                 "row_of", "logprobs", "prompt_logprobs", "verified")
 
     def __init__(self, out, rows, ids_dev, hidden, num_tokens, mode):
         self.out, self.rows, self.ids_dev, self.hidden = out, rows, ids_dev, hidden
@@ -89,6 +89,9 @@ class PendingStep:
         self.row_of = {}
         self.logprobs = None      # (chosen [rows], top values [rows, k], top ids [rows, k])
         self.prompt_logprobs = None   # (values [n], [(request, first position, count)])
+        # device-side verification: (accepted tokens [R, max_draft + 1] on the host, -1 padded,
+        # the speculator's drafts [R, n] on the host) for the R sampling requests of the step
+        self.verified = None
 
 
 @dataclass
@@ -483,6 +486,7 @@ class ModelRunner:
                 ids_dev, hidden = g.replay(prev.ids_dev if src_rows is not None else None)
             self.h2d_total += g.h64.numel() * 8 + g.h32.numel() * 4
             pend = PendingStep(out, rows, ids_dev, hidden, g.bucket, g.mode)
+            input_sel = g.batch.input_ids       # every row of a decode graph is a sampled row
         else:
             with trace_range("prepare"):
                 batch, rows = self.prepare(out)
@@ -517,6 +521,9 @@ class ModelRunner:
                     if logits.shape[0] else None
             pend = PendingStep(out, rows, ids_dev, hidden, batch.num_tokens, batch.mode)
             pend.logprobs, self._step_logprobs = self._step_logprobs, None
+            input_sel = None
+            if self.proposer is not None and ids_dev is not None:
+                input_sel = batch.input_ids[batch.logits_indices[:batch.num_sampled]]
             if prompt_lp is not None:
                 pend.prompt_logprobs = (prompt_lp, batch.prompt_rows)
         # the device result may be overwritten by the next replay of the same graph: take the
@@ -528,11 +535,49 @@ class ModelRunner:
                 self._ids_host[self._ids_flip] = host
             pend.ids_host = host[:pend.ids_dev.numel()]
             pend.ids_host.copy_(pend.ids_dev, non_blocking=True)
+            if self.proposer is not None:
+                self._verify_and_draft(pend, input_sel)
             pend.event = torch.cuda.Event()
             pend.event.record()
             self._ids_flip ^= 1
+        elif self.proposer is not None and pend.ids_dev is not None:
+            self._verify_and_draft(pend, input_sel)
         pend.row_of = {id(s.request): rr[0] for s, rr in zip(out.scheduled, rows) if rr}
         return pend
+
+    def _verify_and_draft(self, pend: "PendingStep", input_sel: torch.Tensor) -> None:
+        """Accept drafts and draft again without leaving the stream: one kernel compares every
+        request's draft tokens with the tokens the model produced after them, the speculator
+        then runs from the hidden state at each request's last accepted row and the token that
+        follows it, and both results travel to pinned host memory behind the step's tokens.
+        The host reads them in ``finish`` after the one synchronisation it does anyway (the
+        reference verifies in its rejection sampler and feeds the proposer from device tensors:
+        arctic_inference/vllm/model_runner.py:1008-1023, spec_dec/arctic_proposer.py:130-209)."""
+        from ..ops import spec_ops
+        sched, rows = pend.out.scheduled, pend.rows
+        live = [(s, rr) for s, rr in zip(sched, rows) if s.samples]
+        R = len(live)
+        if R == 0:
+            return
+        meta = np.empty(2 * R, dtype=np.int32)
+        meta[:R] = [rr[0] for _, rr in live]
+        meta[R:] = [s.num_draft for s, _ in live]
+        max_draft = int(meta[R:].max())
+        meta_dev = ops.upload(meta, self.device)
+        self.h2d_total += meta.nbytes
+        _, next_tok, sel_row, out_tokens = spec_ops.verify_greedy(
+            input_sel, pend.ids_dev, meta_dev[:R], meta_dev[R:], max_draft)
+        cfg = self.config.speculative
+        n_predict = cfg.num_speculative_tokens or self.proposer.n_predict
+        cuda = pend.hidden.is_cuda
+        h = ops.gather_rows(pend.hidden, sel_row) if cuda else pend.hidden[sel_row]
+        drafts = self.proposer.propose(h, next_tok, n_predict)
+        out_host = torch.empty(out_tokens.shape, dtype=torch.int64, pin_memory=cuda)
+        out_host.copy_(out_tokens, non_blocking=True)
+        drafts_host = torch.empty(drafts.shape, dtype=torch.int64, pin_memory=cuda)
+        drafts_host.copy_(drafts, non_blocking=True)
+        self.d2h_total += (out_tokens.numel() + drafts.numel()) * 8
+        pend.verified = (out_host, drafts_host)
 
     @torch.inference_mode()
     def finish(self, pend: "PendingStep") -> StepResult:
@@ -569,8 +614,24 @@ class ModelRunner:
             chosen, topv, topi = (t.tolist() for t in pend.logprobs)
             lp_rows = (chosen, topv, topi)
             logprobs = {}
+        arctic = None
+        if pend.verified is not None:
+            # the device compared drafts with targets already: its rows are the accepted
+            # tokens and the one that follows them
+            out_host, drafts_host = pend.verified
+            arctic = drafts_host.tolist()
+            live = [(s, rr) for s, rr in zip(sched, rows) if s.samples]
+            for (s, rr), row in zip(live, out_host.tolist()):
+                r = s.request
+                toks = row[:s.num_draft + 1]
+                if toks[-1] < 0:
+                    toks = toks[:toks.index(-1)]
+                new_tokens[r.request_id] = toks
+                accepted_rows.append(rr[len(toks) - 1])
+                if lp_rows is not None and r.sampling_params.logprobs is not None:
+                    logprobs[r.request_id] = self._logprob_entries(lp_rows, rr[:len(toks)], r)
         for s, rr in zip(sched, rows):
-            if not s.samples:
+            if not s.samples or pend.verified is not None:
                 continue
             r = s.request
             if len(rr) == 1:
@@ -594,5 +655,6 @@ class ModelRunner:
         if self.proposer is not None or self.suffix_cache is not None:
             from ..spec_decode.propose import propose_drafts
             with trace_range("draft"):
-                drafts = propose_drafts(self, sched, rows, new_tokens, pend.hidden, accepted_rows)
+                drafts = propose_drafts(self, sched, rows, new_tokens, pend.hidden, accepted_rows,
+                                        arctic=arctic)
         return StepResult(new_tokens, drafts, pend.num_tokens, pend.mode, logprobs)

@@ -39,6 +39,17 @@ def _model_tensors(engine):
     return out
 
 
+def mark_static_weights(engine) -> None:
+    """Tell the linear layers which tensors are parameters (``ops.mark_static``)."""
+    from .. import ops
+    ops.clear_static()
+    for owner, name in _model_tensors(engine):
+        t = _get(owner, name) if (isinstance(owner, dict) and name in owner) or \
+            (not isinstance(owner, dict) and hasattr(owner, name)) else None
+        if isinstance(t, torch.Tensor) and t.is_cuda:
+            ops.mark_static(t)
+
+
 def _get(owner, name):
     return owner[name] if isinstance(owner, dict) else getattr(owner, name)
 
@@ -61,7 +72,9 @@ def sleep_engine(engine, level: int = 1) -> None:
     engine._sleep_store = {}
     if level == 2:
         seen = {}
+        from .. import ops
         from ..models.quant import Fp8Weight
+        ops.clear_static()
         engine._sleep_shadows = []
         for owner, name in _model_tensors(engine):
             if isinstance(owner, Fp8Weight) and owner.shadow is not None:
@@ -100,6 +113,7 @@ def wake_engine(engine, tags=None) -> None:
             w.make_shadow()
         engine._sleep_shadows = []
         engine._awake_tags.add("weights")
+        mark_static_weights(engine)
     if "kv_cache" in tags and "kv_cache" not in engine._awake_tags:
         engine.runner.init_kv_cache(engine.num_blocks)
         engine._awake_tags.add("kv_cache")

@@ -140,8 +140,33 @@ def quant_fp8_row(x: torch.Tensor, sync=None):
     return quant.QuantAct(xq, sx)
 
 
+# Storages of parameters (weights that no kernel of the compute stream writes). A linear layer
+# whose weight lives in one of them requests its first weight tiles before it waits for the
+# kernel launched before it, so the weight stream starts under that kernel's tail.
+_static_storages: set = set()
+
+
+def mark_static(t) -> None:
+    """Declare ``t`` (a tensor or a quantised weight) a parameter. An in-place update of a
+    parameter (a weight sync) is followed by other kernels before the next linear layer that
+    reads it, which is what makes the early read safe."""
+    if t is None:
+        return
+    q = getattr(t, "q", t)
+    if isinstance(q, torch.Tensor) and q.is_cuda:
+        _static_storages.add(q.untyped_storage().data_ptr())
+
+
+def clear_static() -> None:
+    _static_storages.clear()
+
+
+def _is_static(t: torch.Tensor) -> bool:
+    return bool(_static_storages) and t.untyped_storage().data_ptr() in _static_storages
+
+
 def _linear_desc(x, ldx, sx, w, ldw, sw, out_ptr, ldo, M, N, K, bias, residual, act,
-                 force_splits, peer, sync, device, w_tile_strides=None):
+                 force_splits, peer, sync, device, w_tile_strides=None, w_static=False):
     """Fill an ``Ab200LinearDesc`` and launch it."""
     import ctypes
     nat = _native()
@@ -164,6 +189,7 @@ def _linear_desc(x, ldx, sx, w, ldw, sw, out_ptr, ldo, M, N, K, bias, residual, 
         d.sync = sync
     if w_tile_strides is not None:
         d.w_tile_stride_n, d.w_tile_stride_k = w_tile_strides
+    d.w_static = 1 if w_static else 0
     d.status = nat.status_buffer(device).data_ptr()
     rc = nat.lib().ab200_linear_desc(ctypes.byref(d), nat.stream_ptr())
     return rc
@@ -219,7 +245,8 @@ def linear_fp8_row(x, w, bias=None, residual=None, act=None, out=None, force_spl
         return out
     rc = _linear_desc(xq.q.data_ptr(), xq.q.stride(0), xq.scale.data_ptr(), w.q.data_ptr(),
                       ldw, w.scale.data_ptr(), out_ptr, ldo, M, N, K, bias, residual,
-                      act, force_splits, peer, gemm_sync, w.device, tile_strides)
+                      act, force_splits, peer, gemm_sync, w.device, tile_strides,
+                      w_static=_is_static(w.q))
     nat.check(rc, "linear_fp8_row M=%d N=%d K=%d" % (M, N, K))
     launch_counter.add(1)
     return out
@@ -355,10 +382,11 @@ def linear(x: torch.Tensor, w, bias=None, residual=None, act=None, out=None,
     assert out.stride(1) == 1
     if M == 0:
         return out
-    if sync is not None:
+    static = _is_static(w)
+    if sync is not None or static:
         rc = _linear_desc(x.data_ptr(), x.stride(0), None, w.data_ptr(), w.stride(0), None,
                           out.data_ptr(), out.stride(0), M, N, K, bias, residual, act,
-                          force_splits, None, sync, x.device)
+                          force_splits, None, sync, x.device, w_static=static)
         nat.check(rc, "linear_bf16 M=%d N=%d K=%d" % (M, N, K))
         launch_counter.add(1)
         return out

@@ -40,7 +40,8 @@ class LinearDesc(ctypes.Structure):
                 ("peer_ptrs", c_void_p), ("world", c_int), ("peer_cols", c_int),
                 ("peer_row_off", c_longlong),
                 ("sync", PeerSync), ("status", c_void_p),
-                ("w_tile_stride_n", c_longlong), ("w_tile_stride_k", c_longlong)]
+                ("w_tile_stride_n", c_longlong), ("w_tile_stride_k", c_longlong),
+                ("w_static", c_int)]
 
 
 class KernelError(RuntimeError):

@@ -84,22 +84,22 @@ def _suffix_draft(runner, req, cfg):
 
 
 def propose_drafts(runner, sched, rows, new_tokens: dict, hidden: torch.Tensor,
-                   accepted_rows: list) -> dict:
+                   accepted_rows: list, arctic: list = None) -> dict:
     """Drafts for the next step. The speculator's heads are queued on the GPU first and their
     tokens start their way to pinned host memory; the suffix trees are then searched on the
     CPU while the GPU drafts, and only after that does the host wait for the speculator's
     tokens (the reference overlaps the same two with a copy stream:
     arctic_inference/vllm/model_runner.py:1323-1628, its mode "B"). Per request the suffix
     draft wins when its score reaches the speculator's draft length, else the speculator's
-    draft is used (model_runner.py:1008-1023)."""
+    draft is used (model_runner.py:1008-1023). ``arctic`` carries the speculator's drafts when
+    the step already produced them on the device behind its verification kernel."""
     cfg = runner.config.speculative
     reqs = [s.request for s in sched if s.samples]
     drafts: dict = {}
     if not reqs:
         return drafts
-    arctic = None
     arctic_dev = arctic_host = arctic_event = None
-    if runner.proposer is not None:
+    if runner.proposer is not None and arctic is None:
         n_predict = cfg.num_speculative_tokens or runner.proposer.n_predict
         idx = torch.tensor(accepted_rows, dtype=torch.int64, device=hidden.device)
         tok = torch.tensor([new_tokens[r.request_id][-1] for r in reqs], dtype=torch.int64,

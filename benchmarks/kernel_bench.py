@@ -137,6 +137,8 @@ def main():
     ap.add_argument("--no-time", action="store_true", help="three plain launches (for ncu)")
     ap.add_argument("--splits", type=int, default=0,
                     help="force the split-K factor of the bf16 GEMM cases (0 = the kernel's choice)")
+    ap.add_argument("--tile-keys", type=int, default=0,
+                    help="force the key-tile size (64 or 128) of the attention cases")
     a = ap.parse_args()
     names = sorted(CASES) if a.case == "all" else a.case.split(",")
     for name in names:
@@ -169,6 +171,8 @@ def run_case(a, case):
         xq = ops.quant_fp8_row(R(M, K))
         tiled = None if kind == "gemm_fp8row" else False     # None: tiled storage on the GPU
         ws = [quant.quantize_weight_fp8_row(R(N, K), tiled=tiled) for _ in range(nc)]
+        for w_ in ws:
+            ops.mark_static(w_)      # parameters, as in a loaded model
         fn = lambda i=0: ops.linear(xq, ws[i], force_splits=a.splits)
         flops, byts = 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
     elif kind == "gemm_fp8blk":
@@ -183,6 +187,9 @@ def run_case(a, case):
         byts = sum(b_ * 8 * 128 * 2 * 2.0 for b_ in kl) + 2.0 * sum(ql) * 32 * 128 * 2
         nc = copies_for(byts)
         sets = [paged(ql, kl) for _ in range(nc)]
+        if a.tile_keys:
+            for st in sets:
+                st[3].tile_keys = a.tile_keys
         fn = lambda i=0: ops.attention(sets[i][0], sets[i][1], sets[i][2], sets[i][3], 32, 8, 128)
         flops = sum(4.0 * a_ * (b_ - a_ / 2.0) * 32 * 128 for a_, b_ in zip(ql, kl))
     elif kind == "rmsnorm":

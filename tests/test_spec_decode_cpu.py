@@ -107,3 +107,30 @@ def test_acceptance_histogram_by_position():
     assert all(a <= d for a, d in zip(accepted, drafted))
     assert all(x >= y for x, y in zip(accepted, accepted[1:]))
     assert st["tp_steps"] == st["steps"] and st["sp_steps"] == 0
+
+
+@pytest.mark.parametrize("fmt", ["bin", "safetensors"])
+def test_speculator_checkpoint_round_trip(tmp_path, fmt):
+    """A speculator directory holds ``config.json`` plus safetensors files or, in older
+    releases, ``pytorch_model.bin`` (the reference reads both:
+    arctic_inference/server/weight_sync/utils.py:437-461)."""
+    import dataclasses
+    import json
+    import torch
+    from arcticinference_b200.models.speculator import SpeculatorConfig, build_speculator
+    from arcticinference_b200.utils.safetensors_io import write_safetensors
+    cfg = SpeculatorConfig(n_predict=3, vocab_size=64, emb_dim=32, inner_dim=32, proj_dim=32,
+                           input_hidden_dim=32, method="sum_lstm")
+    src = build_speculator(cfg, device="cpu", seed=3)
+    d = dataclasses.asdict(cfg)
+    d["architectures"] = [d.pop("architecture")]
+    (tmp_path / "config.json").write_text(json.dumps(d))
+    state = {"speculator." + k: v.clone() for k, v in src.w.items()}
+    if fmt == "bin":
+        torch.save(state, tmp_path / "pytorch_model.bin")
+    else:
+        write_safetensors(str(tmp_path / "model.safetensors"), state)
+    got = build_speculator(str(tmp_path), device="cpu")
+    h = torch.randn(5, 32, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16)
+    tok = torch.arange(5, dtype=torch.int64)
+    assert torch.equal(src.propose(h, tok, 3), got.propose(h, tok, 3))
