@@ -25,6 +25,7 @@
 // per-channel scales: arctic_inference/vllm/spec_dec/fp8.py:34-309).
 
 #include <math.h>
+#include <stdlib.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -63,6 +64,11 @@ struct GemmArgs {
   int fp8;         // 1: operands are e4m3 bytes (kind::f8f6f4), 128 k-elements per stage
   int kblock_elems;  // k-elements per stage: 64 (bf16) or 128 (fp8)
   int prefetch_w;    // 1: the weight operand is written by no kernel of the stream (a parameter)
+  // > 1: the launch is made of clusters of this many CTAs. The CTAs of a cluster share one
+  // output tile and split its K range; they exchange their fp32 partial sums through each
+  // other's shared memory and each finishes and stores bn / cluster_splits columns (the
+  // split-K of a one-row-of-tiles GEMM with no workspace traffic and no second kernel).
+  int cluster_splits;
   const float* scale_a;  // fp8: one factor per A-operand row (null = 1)
   const float* scale_b;  // fp8: one factor per B-operand row
   uint32_t tmem_cols;
@@ -89,6 +95,22 @@ struct GemmArgs {
 
 __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+
+// Work item -> (A tile, B tile, K split). Cluster launches hold one item per CTA, the K splits
+// of a tile being the consecutive CTAs of one cluster.
+__device__ __forceinline__ void decode_work(const GemmArgs& p, int w, int& tile_a, int& tile_b,
+                                            int& split) {
+  if (p.cluster_splits > 1) {
+    tile_a = 0;
+    split = w % p.cluster_splits;
+    tile_b = w / p.cluster_splits;
+    return;
+  }
+  tile_a = w % p.tiles_a;
+  const int rest = w / p.tiles_a;
+  tile_b = rest % p.tiles_b;
+  split = rest / p.tiles_b;
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -142,6 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t acc_stride = p.tmem_cols / 2;
 
   const int total_work = p.tiles_a * p.tiles_b * p.splits;
+  bool cluster_acc_ok = false;   // epilogue threads of a cluster launch: the accumulator is complete
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -152,11 +175,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool w_is_b = !p.transposed;
     int pre = 0;
     if (lane == 0 && p.prefetch_w && blockIdx.x < total_work) {
-      const int w0 = blockIdx.x;
-      const int tile_a0 = w0 % p.tiles_a;
-      const int rest0 = w0 / p.tiles_a;
-      const int tile_b0 = rest0 % p.tiles_b;
-      const int kb00 = (rest0 / p.tiles_b) * p.kblocks_per_split;
+      int tile_a0, tile_b0, split0;
+      decode_work(p, blockIdx.x, tile_a0, tile_b0, split0);
+      const int kb00 = split0 * p.kblocks_per_split;
       const int kb01 = min(kb00 + p.kblocks_per_split, p.kblocks_total);
       pre = min(p.stages, kb01 - kb00);
       for (int s = 0; s < pre; ++s) {
@@ -197,10 +218,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int tile_a = w % p.tiles_a;
-        const int rest = w / p.tiles_a;
-        const int tile_b = rest % p.tiles_b;
-        const int split = rest / p.tiles_b;
+        int tile_a, tile_b, split;
+        decode_work(p, w, tile_a, tile_b, split);
         const int kb0 = split * p.kblocks_per_split;
         const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -266,7 +285,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int split = (w / p.tiles_a) / p.tiles_b;
+        int tile_a, tile_b, split;
+        decode_work(p, w, tile_a, tile_b, split);
         const int kb0 = split * p.kblocks_per_split;
         const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 200 + acc, w)) break;
@@ -317,11 +337,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    if (p.cluster_splits > 1) {
+      // one work item per CTA; what follows the accumulator is the cluster exchange below
+      cluster_acc_ok = mbar_wait(tfull_bar(0), 0, abort_flag, p.status, 400, (int)blockIdx.x);
+      tc_fence_after();
+    } else
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const int tile_a = w % p.tiles_a;
-      const int rest = w / p.tiles_a;
-      const int tile_b = rest % p.tiles_b;
-      const int split = rest / p.tiles_b;
+      int tile_a, tile_b, split;
+      decode_work(p, w, tile_a, tile_b, split);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 400 + acc, w)) break;
       tc_fence_after();
       const uint32_t t_addr =
@@ -516,6 +539,105 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
+  if (p.cluster_splits > 1) {
+    // ---- split-K inside a cluster: partial sums cross through shared memory ----
+    // CTA r of the cluster owns columns [r * cw, (r + 1) * cw) of the tile. Every CTA writes,
+    // for each owner, its fp32 partial sums of the owner's columns into the owner's shared
+    // memory (the pipeline stages, idle by now), slot [source CTA][row][cw + 4 pad]; the
+    // owner adds the slots in source order, so the result does not depend on timing.
+    const int ns = p.cluster_splits;
+    const int cw = p.bn / ns;
+    const int pitch = cw + 4;   // words; 16 B of padding keeps 16-byte row accesses of a warp
+                                // on distinct banks
+    const uint32_t my = cluster_ctarank();
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    // first barrier: every CTA of the cluster has consumed its last pipeline stage (its
+    // epilogue warps arrive only after their accumulator is complete)
+    cluster_sync();
+    if (warp >= 2 && cluster_acc_ok) {
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+        uint32_t r[16];
+        __syncwarp();
+        tmem_ld_x16(t_addr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        const uint32_t owner = (uint32_t)(c0 / cw);
+        const uint32_t local =
+            smem_base + (uint32_t)(((int)my * kBlockM + row) * pitch + (c0 % cw)) * 4u;
+        const uint32_t remote = map_to_cta(local, owner);
+#pragma unroll
+        for (int t = 0; t < 16; t += 4)
+          st_cluster_v4(remote + 4u * t, r[t], r[t + 1], r[t + 2], r[t + 3]);
+      }
+    }
+    // second barrier: all partial sums have landed (release / acquire at cluster scope)
+    cluster_sync();
+    if (warp >= 2 && cluster_acc_ok && !*abort_flag) {
+      int tile_a, tile_b, split;
+      decode_work(p, (int)blockIdx.x, tile_a, tile_b, split);
+      const long long a_row = row;
+      const bool row_ok = a_row < p.rows_a;
+      const long long col0 = (long long)tile_b * p.bn + (long long)my * cw;
+      const float sa = (p.scale_a != nullptr && row_ok) ? p.scale_a[a_row] : 1.f;
+      const float* slots = reinterpret_cast<const float*>(smem);
+      for (int j = 0; j < cw; j += 8) {
+        float v[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) v[t] = 0.f;
+        for (int src = 0; src < ns; ++src) {
+          const float* q = slots + ((size_t)src * kBlockM + row) * pitch + j;
+          const float4 x0 = *reinterpret_cast<const float4*>(q);
+          const float4 x1 = *reinterpret_cast<const float4*>(q + 4);
+          v[0] += x0.x; v[1] += x0.y; v[2] += x0.z; v[3] += x0.w;
+          v[4] += x1.x; v[5] += x1.y; v[6] += x1.z; v[7] += x1.w;
+        }
+        const long long col = col0 + j;
+        if (!row_ok || col + 8 > p.rows_b) continue;
+        if (p.scale_a != nullptr) {
+          const float4 s0 = *reinterpret_cast<const float4*>(p.scale_b + col);
+          const float4 s1 = *reinterpret_cast<const float4*>(p.scale_b + col + 4);
+          v[0] *= sa * s0.x; v[1] *= sa * s0.y; v[2] *= sa * s0.z; v[3] *= sa * s0.w;
+          v[4] *= sa * s1.x; v[5] *= sa * s1.y; v[6] *= sa * s1.z; v[7] *= sa * s1.w;
+        }
+        if (p.bias != nullptr) {
+          const uint4 q = *reinterpret_cast<const uint4*>(p.bias + col);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 f = __bfloat1622float2(h[u]);
+            v[2 * u] += f.x;
+            v[2 * u + 1] += f.y;
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int t = 0; t < 8; ++t) v[t] = gelu_erf(v[t]);
+        }
+        if (p.residual != nullptr) {
+          const uint4 q = *reinterpret_cast<const uint4*>(p.residual + a_row * p.ldr + col);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 f = __bfloat1622float2(h[u]);
+            v[2 * u] += f.x;
+            v[2 * u + 1] += f.y;
+          }
+        }
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + a_row * p.ldo + col;
+        if (p.peer_cols > 0)  // eight columns never straddle a destination (peer_cols % 8 == 0)
+          dst = p.peer_out[col / p.peer_cols] + (a_row + p.peer_row_off) * p.ldo +
+                col % p.peer_cols;
+        uint4 q;
+        q.x = pack_bf16x2(v[0], v[1]);
+        q.y = pack_bf16x2(v[2], v[3]);
+        q.z = pack_bf16x2(v[4], v[5]);
+        q.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dst) = q;
+      }
+    }
+  }
+
   tail_signal(p.sig, gridDim.x);
   tc_fence_before();
   __syncthreads();
@@ -649,6 +771,51 @@ static int pick_stages(int bn) {
   int s = (227 * 1024 - 2048 - 4 * kStoreStageBytes) / stage_bytes;
   if (s > kMaxStages) s = kMaxStages;
   return s;
+}
+
+// How many clusters of `cs` CTAs (one CTA per SM: the kernel takes an SM's shared memory) the
+// device can hold at once; 0 when such a cluster cannot be placed.
+static int cluster_capacity(int cs, size_t smem) {
+  static int cache[64][4];   // [device][log2 cs]: 0 unknown, -1 none, else capacity
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int lg = cs == 2 ? 1 : cs == 4 ? 2 : cs == 8 ? 3 : -1;
+  if (dev < 0 || dev >= 64 || lg < 0) return 0;
+  if (cache[dev][lg] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cs * 16);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cache[dev][lg] = n > 0 ? n : -1;
+  }
+  return cache[dev][lg] > 0 ? cache[dev][lg] : 0;
+}
+
+// Rough time (us) of a one-row-of-tiles GEMM plan: every wave pays its k-loop (four MMA
+// instructions per k-block at the measured issue interval, ~0.45 us per k-block with its
+// stage turnaround) plus a fixed ramp; split-K through the workspace pays the fp32 partials'
+// round trip and a second kernel, split-K inside a cluster a shared-memory exchange.
+static double plan_cost_us(int tiles, int splits, int kblocks, int capacity, bool cluster, int M,
+                           int N) {
+  const int ctas = tiles * splits;
+  const int waves = (ctas + capacity - 1) / capacity;
+  const int per = (kblocks + splits - 1) / splits;
+  double t = waves * (per * 0.45 + 2.0);
+  if (splits > 1)
+    t += cluster ? 1.0 : 3.0 + 2.0 * splits * (double)M * N * 4.0 / 3.0e6;
+  return t;
 }
 
 static uint32_t pow2_at_least(uint32_t v) {
@@ -834,10 +1001,53 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
       a.splits = splits;
     }
   }
+  // One row of tiles (at most 128 tokens): consider splitting K inside thread-block clusters
+  // instead of through the workspace. The scatter epilogue qualifies too: the CTA that
+  // finishes a column range stores it to the rank that owns it.
+  static const bool cluster_off = [] {
+    const char* e = getenv("AB200_GEMM_CLUSTER");
+    return e != nullptr && e[0] == '0';
+  }();
+  if (!a.transposed && a.tiles_a == 1 && !cluster_off && (force_splits == 0 || peer_cols > 0) &&
+      N % 8 == 0 && ldo % 8 == 0 && (peer_cols == 0 || peer_cols % 8 == 0) &&
+      (reinterpret_cast<uintptr_t>(bias) % 16) == 0 && (residual == nullptr || ldr % 8 == 0)) {
+    double best = plan_cost_us(a.tiles_b, a.splits, a.kblocks_total, sms, false, M, N);
+    int best_bn = 0, best_s = 0, best_ctas = 0;
+    const size_t smem_full = 227 * 1024 - 1024;
+    for (int bn = 256; bn >= 64; bn -= 64) {
+      if (bn > ((N + 63) / 64) * 64) continue;
+      const int tiles = (N + bn - 1) / bn;
+      for (int cs = 2; cs <= 8; cs *= 2) {
+        if (bn % (16 * cs) != 0 || a.kblocks_total < 2 * cs) continue;
+        const int per = (a.kblocks_total + cs - 1) / cs;
+        if ((a.kblocks_total + per - 1) / per != cs) continue;   // every CTA of a cluster has work
+        const int cap = cluster_capacity(cs, smem_full) * cs;
+        if (cap <= 0 || tiles * cs > 4 * cap) continue;
+        const double c = plan_cost_us(tiles, cs, a.kblocks_total, cap, true, M, N);
+        if (c < best - 0.25 || (c < best + 0.25 && best_s > 0 && tiles * cs > best_ctas)) {
+          best = c < best ? c : best;
+          best_bn = bn;
+          best_s = cs;
+          best_ctas = tiles * cs;
+        }
+      }
+    }
+    if (best_s > 0) {
+      a.bn = best_bn;
+      a.tiles_b = (N + a.bn - 1) / a.bn;
+      a.splits = best_s;
+      a.cluster_splits = best_s;
+    }
+  }
   a.kblocks_per_split = (a.kblocks_total + a.splits - 1) / a.splits;
   a.splits = (a.kblocks_total + a.kblocks_per_split - 1) / a.kblocks_per_split;
   a.stages = pick_stages(a.bn);
   a.tmem_cols = pow2_at_least(2u * (uint32_t)a.bn);
+  if (a.cluster_splits > 1 &&
+      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) <
+          (size_t)kBlockM * (a.bn + 4 * a.cluster_splits) * sizeof(float)) {
+    return -2;   // cannot happen for the tile sizes above: the exchange slots fit the pipeline
+  }
 
   a.coalesce = !a.transposed && a.splits == 1 && a.bn % 64 == 0 &&
                N % 8 == 0 && ldo % 8 == 0 && (peer_cols == 0 || peer_cols % 64 == 0) &&
@@ -863,8 +1073,9 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     }
   }
   void* final_out = out;
-  if (a.splits == 1) a.sig = sig;   // with split-K the reduce kernel writes the output
-  if (a.splits > 1) {
+  const bool ws_split = a.splits > 1 && a.cluster_splits <= 1;
+  if (!ws_split) a.sig = sig;   // with split-K through the workspace the reduce kernel writes the output
+  if (ws_split) {
     a.out_f32 = 1;
     a.out = workspace;
     a.ldo = N;  // partials are stored as [split][M][N] regardless of orientation
@@ -885,14 +1096,15 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     return -4;
 
   const int total = a.tiles_a * a.tiles_b * a.splits;
-  const int grid = total < sms ? total : sms;
+  const int grid = (a.cluster_splits > 1 || total < sms) ? total : sms;
   const size_t smem =
       (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 1024;
-  if (launch_pdl(gemm_bf16_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, ta, tb, a) !=
-      cudaSuccess)
+  if (launch_pdl_cluster(gemm_bf16_kernel, dim3(grid), dim3(kGemmThreads), smem, stream,
+                         a.cluster_splits > 1 ? (unsigned)a.cluster_splits : 1u, ta, tb,
+                         a) != cudaSuccess)
     return -5;
 
-  if (a.splits > 1) {
+  if (ws_split) {
     const long long total4 = (long long)M * (N / 4);
     int blocks = (int)((total4 + 255) / 256);
     if (blocks > sms * 8) blocks = sms * 8;

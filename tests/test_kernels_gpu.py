@@ -541,6 +541,35 @@ def test_linear_fp8_row_epilogue(M):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 4096, 4096), (64, 6144, 4096), (128, 4096, 14336),
+                                   (3, 512, 1024), (128, 1000, 2048), (96, 4096, 512)])
+def test_linear_one_row_of_tiles_splits_k_inside_clusters(M, N, K):
+    """At most 128 tokens and few output tiles: the K range is split over the CTAs of a
+    thread-block cluster, which add their partial sums through shared memory. The result
+    matches the fp32 reference, does not depend on timing, and is the same whether or not
+    the weight was declared a parameter (its first tiles are then requested early)."""
+    x = _rand(M, K)
+    wf = _rand(N, K, scale=1.0 / math.sqrt(K))
+    b, r = _rand(N), _rand(M, N)
+    # bf16 operands
+    y = ops.linear(x, wf, bias=b, residual=r)
+    ops.check_status()
+    _close(y, ref.linear(x, wf, b, r), 3e-2, 2e-2)
+    assert torch.equal(y, ops.linear(x, wf, bias=b, residual=r))
+    ops.mark_static(wf)
+    assert torch.equal(y, ops.linear(x, wf, bias=b, residual=r))
+    # e4m3 operands
+    w = quant.quantize_weight_fp8_row(wf)
+    xq = ops.quant_fp8_row(x)
+    yq = ops.linear(xq, w, residual=r)
+    ops.check_status()
+    _close(yq, _row_ref(xq, w, residual=r), 4e-2, 2e-2)
+    ops.mark_static(w)
+    assert torch.equal(yq, ops.linear(xq, w, residual=r))
+    ops.clear_static()
+    ops.check_status()
+
+
 @pytest.mark.parametrize("splits", [1, 2, 4, 8])
 def test_linear_fp8_row_split_k(splits):
     M, N, K = 24, 1024, 4096
