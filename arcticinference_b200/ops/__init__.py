@@ -802,24 +802,6 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
     return work, tok_splits, max_splits
 
 
-def wave_splits(ctas: int, slots: int, max_splits: int = 4) -> int:
-    """KV splits per sequence for a decode call with at least as many CTAs as CTA slots: the
-    CTAs run in rounds of ``slots`` and all take about the same time, so a last round that is
-    mostly empty costs a full round (1024 CTAs on 296 slots: four rounds for the work of
-    3.46). Cutting every sequence in ``s`` pieces makes the rounds shorter and the last one
-    fuller; the smallest ``s`` that brings the rounds to within 4 % of full is chosen, if it
-    gains at least 5 % (the partial results cost a small merge kernel)."""
-    def eff(s):
-        x = ctas * s / float(slots)
-        return x / math.ceil(x)
-    base = eff(1)
-    for s in range(2, max_splits + 1):
-        e = eff(s)
-        if e >= base + 0.05 and (e >= 0.96 or s == max_splits):
-            return s
-    return 1
-
-
 def _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split, max_splits_cap):
     """The planner above for the one-token-per-sequence case, on arrays (same rows, same
     order): a serving step with a thousand sequences must not spend milliseconds here."""
@@ -833,11 +815,6 @@ def _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split, m
         want = max(1, num_sms // max(1, R * Hkv))
         cand = np.minimum(np.minimum(16, max_splits_cap), np.minimum(want, np.maximum(1, key_tiles // 2)))
         ns = np.where(key_tiles > 4, cand, 1)
-    elif allow_split and max_splits_cap > 1:
-        # more CTAs than slots: even out the rounds (sequences of at least 4 tiles per piece)
-        s = wave_splits(R * Hkv, num_sms, int(min(4, max_splits_cap)))
-        if s > 1:
-            ns = np.where(key_tiles >= 4 * s, s, 1)
     tps = (key_tiles + ns - 1) // ns
     ns = (key_tiles + tps - 1) // tps
     seq = np.arange(R, dtype=np.int64) if seq_rows is None else np.asarray(seq_rows, dtype=np.int64)
