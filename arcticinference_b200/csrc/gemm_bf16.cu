@@ -125,6 +125,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint8_t* store_stage = reinterpret_cast<uint8_t*>(bars) + 256;
+  // the tile's per-column scales, fetched while the k-loop runs (a lone tile per CTA pays for
+  // every load that waits until the accumulator is complete)
+  // (one private copy per epilogue warp, so that no barrier between warps is involved)
+  float* col_scale = reinterpret_cast<float*>(store_stage + 4 * kStoreStageBytes) +
+                     ((threadIdx.x >> 5) & 3) * 256;
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bars_base = smem_u32(bars);
@@ -337,23 +342,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    const bool scaled = p.scale_a != nullptr && !p.out_f32;
     if (p.cluster_splits > 1) {
       // one work item per CTA; what follows the accumulator is the cluster exchange below
+      if (scaled) {
+        const int cw = p.bn / p.cluster_splits;
+        const long long c0 = (long long)(blockIdx.x / p.cluster_splits) * p.bn +
+                             (long long)(blockIdx.x % p.cluster_splits) * cw;
+        for (int i = lane; i < cw; i += 32)
+          col_scale[i] = (c0 + i < p.rows_b) ? p.scale_b[c0 + i] : 0.f;
+        __syncwarp();
+      }
       cluster_acc_ok = mbar_wait(tfull_bar(0), 0, abort_flag, p.status, 400, (int)blockIdx.x);
       tc_fence_after();
     } else
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       int tile_a, tile_b, split;
       decode_work(p, w, tile_a, tile_b, split);
+      const long long a_row = (long long)tile_a * kBlockM + row;
+      const bool row_ok = a_row < p.rows_a;
+      const long long b0 = (long long)tile_b * p.bn;
+      const float sa = (scaled && row_ok) ? p.scale_a[a_row] : 1.f;
+      if (scaled) {
+        __syncwarp();   // the previous tile's reads are done
+        for (int i = lane; i < p.bn; i += 32)
+          col_scale[i] = (b0 + i < p.rows_b) ? p.scale_b[b0 + i] : 0.f;
+        __syncwarp();
+      }
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 400 + acc, w)) break;
       tc_fence_after();
       const uint32_t t_addr =
           tmem_base + (uint32_t)acc * acc_stride + ((uint32_t)(quad * 32) << 16);
-      const long long a_row = (long long)tile_a * kBlockM + row;
-      const bool row_ok = a_row < p.rows_a;
-      const long long b0 = (long long)tile_b * p.bn;
-      const bool scaled = p.scale_a != nullptr && !p.out_f32;
-      const float sa = (scaled && row_ok) ? p.scale_a[a_row] : 1.f;
 
       if (p.coalesce) {
         // 64 output columns at a time: each thread converts its row, the warp transposes
@@ -375,10 +394,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int t = 0; t < 8; ++t)
                 v[t] = __uint_as_float(j < 4 ? r0[8 * j + t] : r1[8 * (j - 4) + t]);
               const long long cj = col + 8 * j;
-              if (cj + 8 <= p.rows_b) {
+              if (cj + 8 <= p.rows_b && c0 + 8 * j + 8 <= p.bn) {
                 if (scaled) {
-                  const float4 s0 = *reinterpret_cast<const float4*>(p.scale_b + cj);
-                  const float4 s1 = *reinterpret_cast<const float4*>(p.scale_b + cj + 4);
+                  const float4 s0 = *reinterpret_cast<const float4*>(col_scale + c0 + 8 * j);
+                  const float4 s1 = *reinterpret_cast<const float4*>(col_scale + c0 + 8 * j + 4);
                   v[0] *= sa * s0.x; v[1] *= sa * s0.y; v[2] *= sa * s0.z; v[3] *= sa * s0.w;
                   v[4] *= sa * s1.x; v[5] *= sa * s1.y; v[6] *= sa * s1.z; v[7] *= sa * s1.w;
                 }
@@ -427,7 +446,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int it = 0; it < 8; ++it) {
             const int rr = it * 4 + (lane >> 3);
             const long long grow = (long long)tile_a * kBlockM + quad * 32 + rr;
-            if (grow < p.rows_a && col + 8 * ch + 8 <= p.rows_b) {
+            if (grow < p.rows_a && col + 8 * ch + 8 <= p.rows_b && c0 + 8 * ch + 8 <= p.bn) {
               const uint4 q = *reinterpret_cast<const uint4*>(stg + rr * kStoreStagePitch + 16 * ch);
               *reinterpret_cast<uint4*>(base + (grow + row_off) * p.ldo + 8 * ch) = q;
             }
@@ -463,8 +482,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (scaled) {
 #pragma unroll
-          for (int t = 0; t < 16; ++t)
-            if (b0 + c0 + t < p.rows_b) v[t] *= sa * p.scale_b[b0 + c0 + t];
+          for (int t = 0; t < 16; ++t) v[t] *= sa * col_scale[c0 + t];
         }
         if (!p.transposed) {
           const long long col = b0 + c0;
@@ -595,8 +613,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const long long col = col0 + j;
         if (!row_ok || col + 8 > p.rows_b) continue;
         if (p.scale_a != nullptr) {
-          const float4 s0 = *reinterpret_cast<const float4*>(p.scale_b + col);
-          const float4 s1 = *reinterpret_cast<const float4*>(p.scale_b + col + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(col_scale + j);
+          const float4 s1 = *reinterpret_cast<const float4*>(col_scale + j + 4);
           v[0] *= sa * s0.x; v[1] *= sa * s0.y; v[2] *= sa * s0.z; v[3] *= sa * s0.w;
           v[4] *= sa * s1.x; v[5] *= sa * s1.y; v[6] *= sa * s1.z; v[7] *= sa * s1.w;
         }
@@ -768,7 +786,7 @@ static int num_sms() {
 
 static int pick_stages(int bn) {
   const int stage_bytes = (int)kABytes + bn * kBlockK * 2;
-  int s = (227 * 1024 - 2048 - 4 * kStoreStageBytes) / stage_bytes;
+  int s = (227 * 1024 - 6144 - 4 * kStoreStageBytes) / stage_bytes;
   if (s > kMaxStages) s = kMaxStages;
   return s;
 }
@@ -1018,7 +1036,9 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
       if (bn > ((N + 63) / 64) * 64) continue;
       const int tiles = (N + bn - 1) / bn;
       for (int cs = 2; cs <= 8; cs *= 2) {
-        if (bn % (16 * cs) != 0 || a.kblocks_total < 2 * cs) continue;
+        // (each CTA keeps at least 8 k-blocks: with fewer, the cluster's placement and its two
+        // barriers cost more than the shorter loop saves; measured on the 4096 x 4096 o_proj)
+        if (bn % (16 * cs) != 0 || a.kblocks_total < 8 * cs) continue;
         const int per = (a.kblocks_total + cs - 1) / cs;
         if ((a.kblocks_total + per - 1) / per != cs) continue;   // every CTA of a cluster has work
         const int cap = cluster_capacity(cs, smem_full) * cs;
@@ -1049,8 +1069,9 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
     return -2;   // cannot happen for the tile sizes above: the exchange slots fit the pipeline
   }
 
-  a.coalesce = !a.transposed && a.splits == 1 && a.bn % 64 == 0 &&
-               N % 8 == 0 && ldo % 8 == 0 && (peer_cols == 0 || peer_cols % 64 == 0) &&
+  a.coalesce = !a.transposed && a.splits == 1 && a.bn % 8 == 0 &&
+               N % 8 == 0 && ldo % 8 == 0 &&
+               (peer_cols == 0 || (peer_cols % 64 == 0 && a.bn % 64 == 0)) &&
                (reinterpret_cast<uintptr_t>(bias) % 16) == 0 &&
                (residual == nullptr || ldr % 8 == 0);
 
@@ -1098,7 +1119,7 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   const int total = a.tiles_a * a.tiles_b * a.splits;
   const int grid = (a.cluster_splits > 1 || total < sms) ? total : sms;
   const size_t smem =
-      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 1024;
+      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 4096 + 1024;
   if (launch_pdl_cluster(gemm_bf16_kernel, dim3(grid), dim3(kGemmThreads), smem, stream,
                          a.cluster_splits > 1 ? (unsigned)a.cluster_splits : 1u, ta, tb,
                          a) != cudaSuccess)
@@ -1221,7 +1242,7 @@ int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long l
   const int sms = num_sms();
   const int grid = total < sms ? total : sms;
   const size_t smem =
-      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 1024;
+      (size_t)a.stages * (kABytes + (size_t)a.bn * kBlockK * 2) + 256 + 4 * kStoreStageBytes + 4096 + 1024;
   gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(ta, tb, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

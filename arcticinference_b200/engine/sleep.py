@@ -69,6 +69,9 @@ def sleep_engine(engine, level: int = 1) -> None:
     engine.kv_manager.reset_prefix_cache()
     engine.runner.kv.free()
     engine.runner._graphs.clear()
+    prop = getattr(engine.runner, "proposer", None)
+    if prop is not None and getattr(prop, "_graphs", None):
+        prop._graphs.clear()       # its graphs hold the addresses of the weights
     engine._sleep_store = {}
     if level == 2:
         seen = {}

@@ -207,11 +207,52 @@ class ArcticSpeculator:
         return sum(t.numel() for t in self.w.values())
 
     # ------------------------------------------------------------------------ forward
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+
     def propose(self, hidden: torch.Tensor, tokens: torch.Tensor,
                 n_predict: Optional[int] = None) -> torch.Tensor:
         """hidden: [B, input_hidden_dim] target hidden states at the last accepted tokens;
-        tokens: [B] int64 the tokens just sampled. Returns draft tokens int64 [B, n_predict]."""
+        tokens: [B] int64 the tokens just sampled. Returns draft tokens int64 [B, n_predict].
+
+        On a GPU the whole n-head loop (4n + 1 small kernels) runs as one CUDA graph per padded
+        batch size, replayed on static input buffers (the reference captures the same loop:
+        arctic_inference/vllm/spec_dec/arctic_speculator.py:350-420,923-981);
+        ``ARCTIC_B200_SPEC_GRAPH=0`` or a capture in progress runs it eagerly."""
         n = n_predict or self.n_predict
+        B = hidden.shape[0]
+        if (hidden.is_cuda and self.use_graph and 0 < B <= self.GRAPH_BUCKETS[-1]
+                and not torch.cuda.is_current_stream_capturing()):
+            return self._propose_graphed(hidden, tokens, n)
+        return self._propose(hidden, tokens, n)
+
+    @property
+    def use_graph(self) -> bool:
+        import os
+        return os.environ.get("ARCTIC_B200_SPEC_GRAPH", "1") != "0"
+
+    def _propose_graphed(self, hidden, tokens, n):
+        B = hidden.shape[0]
+        bucket = next(b for b in self.GRAPH_BUCKETS if b >= B)
+        key = (bucket, n, hidden.shape[1])
+        graphs = self.__dict__.setdefault("_graphs", {})
+        g = graphs.get(key)
+        if g is None:
+            h_buf = torch.zeros(bucket, hidden.shape[1], dtype=hidden.dtype, device=hidden.device)
+            t_buf = torch.zeros(bucket, dtype=torch.int64, device=hidden.device)
+            self._propose(h_buf, t_buf, n)          # warm-up outside the capture
+            torch.cuda.synchronize(hidden.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._propose(h_buf, t_buf, n)
+            g = graphs[key] = (graph, h_buf, t_buf, out)
+        graph, h_buf, t_buf, out = g
+        h_buf[:B].copy_(hidden)
+        t_buf[:B].copy_(tokens)
+        graph.replay()
+        # the buffers are rewritten by the next call: hand out a copy
+        return out[:B].clone()
+
+    def _propose(self, hidden: torch.Tensor, tokens: torch.Tensor, n: int) -> torch.Tensor:
         B = hidden.shape[0]
         w = self.w
         out = torch.empty(B, n, dtype=torch.int64, device=hidden.device)
