@@ -110,7 +110,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  const unsigned int total_blocks = gridDim.x * gridDim.y;
+  const unsigned int total_blocks = gridDim.x;
   // The kernel before this one in the stream may still be running (programmatic dependent
   // launch): barrier and TMEM set-up and the clearing of the K/V stages below overlap its
   // tail. The work list is uploaded by the host before the step's first kernel and is the
@@ -146,7 +146,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int* wk = p.work + (long long)blockIdx.x * 8;
+  // one block per (work item, KV head), work item major: blocks start in work-list order, so
+  // the planner's order (heaviest items first, the pieces of cut sequences last) is the order
+  // in which the GPU picks them up
+  const int* wk = p.work + (long long)(blockIdx.x / p.Hkv) * 8;
   const int seq = wk[0];
   const int q_tok0 = wk[1];
   const int n_q_tok = wk[2];
@@ -160,7 +163,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   int kv_end = wk[5];
   const int split = wk[6];
   const int num_splits = wk[7];
-  const int kvh = blockIdx.y;
+  const int kvh = blockIdx.x % p.Hkv;
   if (p.causal) kv_end = min(kv_end, q_pos0 + n_q_tok);
   const int n_tiles = kv_end > kv_start ? (kv_end - kv_start + TK - 1) / TK : 0;
 
@@ -766,7 +769,7 @@ static int launch_attention(const void* q, long long ldq, const void* k, const v
     sig.world = sync->sig_world;
   }
   if (max_splits <= 1) a.sig = sig;
-  dim3 grid((unsigned)num_work, (unsigned)Hkv);
+  dim3 grid((unsigned)num_work * (unsigned)Hkv);
   (void)launch_pdl(attention_kernel<D, TK>, grid, dim3(AttnShape<TK>::kThreads), smem, stream, tq,
                    tk, tv, a);
   if (cudaGetLastError() != cudaSuccess) return -5;

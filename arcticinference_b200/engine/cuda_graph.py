@@ -47,9 +47,16 @@ class DecodeGraph:
         cfg = runner.config
         self.max_blocks = (cfg.scheduler.max_model_len + runner.block_size - 1) // runner.block_size
         hkv = m.hkv
-        # enough KV splits to occupy the GPU when the batch is small
+        # enough KV splits to occupy the GPU when the batch is small; for a large batch the
+        # sequences of the last, partly filled round of CTAs are cut (ops.tail_split_plan)
+        max_q = 1 + (cfg.speculative.max_draft_tokens if cfg.speculative else 0)
+        small_tiles = max_q * runner.G <= 32 and runner.block_size <= 64
         self.splits = int(max(1, min(16, 148 // max(1, bucket * hkv))))
         self.work_cap = bucket * self.splits + 1
+        n_cut, pieces = ops.tail_split_plan(bucket, hkv, 148 * (2 if small_tiles else 1))
+        if self.splits == 1 and n_cut > 0 and max_q == 1:
+            self.splits = pieces
+            self.work_cap = bucket + n_cut * (pieces - 1) + 1
         n64 = 4 * bucket      # ids | positions | slots | source rows of run-ahead tokens
         n32 = bucket * self.max_blocks + self.work_cap * 8 + bucket
         pin = dev.type == "cuda"
@@ -64,8 +71,7 @@ class DecodeGraph:
         self.meta.tok_splits = self.d32[B * MB + self.work_cap * 8:]
         self.meta.num_work = self.work_cap
         self.meta.max_splits = self.splits
-        max_q = 1 + (cfg.speculative.max_draft_tokens if cfg.speculative else 0)
-        self.meta.tile_keys = 64 if max_q * runner.G <= 32 and runner.block_size <= 64 else 128
+        self.meta.tile_keys = 64 if small_tiles else 128
         if self.splits > 1:
             self.meta.o_part = torch.empty(self.splits, B, m.h, m.D, dtype=torch.float32, device=dev)
             self.meta.lse_part = torch.empty(self.splits, B, m.h, dtype=torch.float32, device=dev)

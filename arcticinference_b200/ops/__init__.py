@@ -802,6 +802,22 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
     return work, tok_splits, max_splits
 
 
+def tail_split_plan(n_seqs: int, Hkv: int, slots: int, max_splits: int = 4):
+    """Decode call with more CTAs (sequences x KV heads) than the GPU holds at once: the CTAs
+    run in rounds of ``slots``, all of about the same length, and the last round is partly
+    empty (1024 CTAs on 296 slots: three full rounds and 136 CTAs in a fourth). Returns
+    (number of sequences to cut, pieces per cut sequence): the sequences of that last round
+    are cut so that their pieces cover all slots, e.g. 17 sequences in 2 pieces each; with the
+    pieces placed last in the work list the call takes 3.5 rounds instead of 4. (Cutting
+    every sequence instead measured no gain: every CTA then pays its set-up twice.)"""
+    ctas = n_seqs * Hkv
+    full, rem = divmod(ctas, slots)
+    if full < 1 or rem == 0 or rem > 0.7 * slots:
+        return 0, 1
+    pieces = int(min(max_splits, max(2, round(slots / float(rem)))))
+    return -(-rem // Hkv), pieces
+
+
 def _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split, max_splits_cap):
     """The planner above for the one-token-per-sequence case, on arrays (same rows, same
     order): a serving step with a thousand sequences must not spend milliseconds here."""
@@ -815,6 +831,13 @@ def _plan_decode_work(kv_lens, G, causal, num_sms, Hkv, seq_rows, allow_split, m
         want = max(1, num_sms // max(1, R * Hkv))
         cand = np.minimum(np.minimum(16, max_splits_cap), np.minimum(want, np.maximum(1, key_tiles // 2)))
         ns = np.where(key_tiles > 4, cand, 1)
+    elif allow_split and max_splits_cap > 1:
+        n_cut, pieces = tail_split_plan(R, Hkv, num_sms, int(min(4, max_splits_cap)))
+        if n_cut > 0:
+            # the longest sequences are cut (at least 4 tiles per piece)
+            longest = np.argsort(-kl, kind="stable")[:n_cut]
+            longest = longest[key_tiles[longest] >= 4 * pieces]
+            ns[longest] = pieces
     tps = (key_tiles + ns - 1) // ns
     ns = (key_tiles + tps - 1) // tps
     seq = np.arange(R, dtype=np.int64) if seq_rows is None else np.asarray(seq_rows, dtype=np.int64)
