@@ -427,6 +427,14 @@ Draft SuffixTree::speculate(const int32_t* context, size_t n, int32_t max_spec_t
   // because callers may speculate on one tree from several threads
   static thread_local Draft scratch;
   Draft& d = scratch;
+  // both buffers hold a full draft from the start: no growth while a candidate is built
+  const size_t cap = (size_t)std::max(1, max_spec_tokens);
+  best.token_ids.reserve(cap);
+  best.parents.reserve(cap);
+  best.probs.reserve(cap);
+  d.token_ids.reserve(cap);
+  d.parents.reserve(cap);
+  d.probs.reserve(cap);
   const size_t max_m = std::min(n, (size_t)std::max(1, max_depth_ - 1));
   for (size_t m = 1; m <= max_m; ++m) {
     Match mt;
