@@ -199,9 +199,35 @@ class ArcticSpeculator:
             n += 1
         return n
 
+    QHEAD_MAX_BATCH = 32
+
+    def make_qheads(self) -> int:
+        """Keep an fp8 copy (one scale per vocabulary row) of every bf16 LM head beside the
+        head itself; drafts for at most ``QHEAD_MAX_BATCH`` requests read the fp8 copy, where
+        the head is a pure weight stream and half the bytes is half the time, larger batches
+        the bf16 head (the reference's rule: arctic_speculator.py:324-325, its ``qhead`` is
+        built at :519-535). Returns the number of copies made."""
+        from .quant import quantize_weight_fp8_row
+        self.qhead = {}
+        for k, t in self.w.items():
+            if k.startswith("head") and isinstance(t, torch.Tensor) and t.dim() == 2 and \
+                    t.is_cuda and t.shape[0] % 8 == 0 and t.shape[1] % 16 == 0:
+                self.qhead[k] = quantize_weight_fp8_row(t)
+        return len(self.qhead)
+
+    def _head(self, key: str, batch: int):
+        q = getattr(self, "qhead", None)
+        if q and batch <= self.QHEAD_MAX_BATCH and key in q:
+            return q[key]
+        return self.w[key]
+
     def weight_slots(self):
         """(owner, key) pairs of every tensor, for sleep / wake and weight sync."""
-        return [(self.w, k) for k in list(self.w)]
+        slots = [(self.w, k) for k in list(self.w)]
+        q = getattr(self, "qhead", None)
+        if q:
+            slots += [(q, k) for k in list(q)]
+        return slots
 
     def num_parameters(self) -> int:
         return sum(t.numel() for t in self.w.values())
@@ -268,14 +294,14 @@ class ArcticSpeculator:
                                             w["cell_ln.0.weight"], w.get("cell_ln.0.bias"),
                                             w["state_ln.0.weight"], w.get("state_ln.0.bias"),
                                             self.LN_EPS)
-                head = w["head.0.weight"]
+                head = self._head("head.0.weight", B)
             else:
                 k = self._idx("emb", i)
                 proj = ops.linear(prev, w["proj.%d.weight" % self._idx("proj", i)])
                 prev = spec_ops.mlp_spec_step(proj, w["emb.%d.weight" % k], tok, self.alpha,
                                               w["ln.%d.weight" % k], w.get("ln.%d.bias" % k),
                                               self.LN_EPS)
-                head = w["head.%d.weight" % k]
+                head = self._head("head.%d.weight" % k, B)
             logits = ops.linear(prev, head)
             tok, _ = ops.argmax_sample(logits)
             tok = tok.clamp_(0, self.cfg.vocab_size - 1)

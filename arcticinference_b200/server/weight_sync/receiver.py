@@ -67,6 +67,10 @@ def _apply_speculator(engine, stream) -> dict:
         if new is not None and new is not dst:
             dst.copy_(new.to(dst.dtype))
             prop.w[k] = dst
+    # the fp8 copies of the LM heads follow their (now updated) bf16 originals, in place
+    for k, q in (getattr(prop, "qhead", None) or {}).items():
+        if k in prop.w:
+            q.requantize_from(prop.w[k])
     return {"tensors": n, "layers": 0, "incomplete_layers": []}
 
 

@@ -45,7 +45,10 @@ def attach_speculation(engine) -> None:
             runner.proposer = build_speculator(cfg.model, runner.device)
         if cfg.quantization == "fp8":
             n = runner.proposer.quantize_fp8()
-            logger.info("speculator: %d matrices stored as block-scaled fp8", n)
+            logger.info("speculator: %d matrices stored as fp8 with per-row scales", n)
+        elif runner.device.type == "cuda":
+            n = runner.proposer.make_qheads()
+            logger.info("speculator: %d fp8 LM-head copies for small batches", n)
         if cfg.num_speculative_tokens is None:
             cfg.num_speculative_tokens = runner.proposer.n_predict
         if runner.proposer.cfg.vocab_size != m.vocab_size:

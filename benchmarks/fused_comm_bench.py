@@ -10,6 +10,11 @@ Cases (Llama-3.1-8B shapes, bf16; n = tokens per rank):
   it (Ulysses sequence -> head exchange) and signals from its last block, followed by a
   consumer kernel (the activation quantiser over the received rows) that waits for the ranks'
   signals, vs the same GEMM into local memory, ``all_to_all_single`` and the same consumer;
+* attention_scatter: attention over all ranks' tokens for this rank's heads whose epilogue
+  stores every token's output row into the rank that owns the token (Ulysses head -> sequence
+  exchange), followed by the consumer that waits, vs attention into local memory,
+  ``all_to_all_single``, the re-layout copy and the same consumer (prefill: sequences of up to
+  2048 tokens; at 64 tokens per rank: one query token per sequence over 2000 cached tokens);
 * gemm_reduce_norm: row-parallel o_proj leaving its partial product in the symmetric heap +
   the kernel that waits for the ranks' signals, sums the partials, adds the residual and
   normalises, vs the GEMM, ``dist.all_reduce`` and the RMSNorm(+residual) kernel;
@@ -108,6 +113,44 @@ def main():
         res.append({"case": "qkv_scatter", "tokens_per_rank": n, "fused_us": t_fused, "gemm_then_nccl_us": t_base,
                     "speedup": t_base / t_fused, "roofline_us": roof, "fraction_of_roofline": roof / t_fused,
                     "bytes_sent_per_gpu": sent, "flops": flops})
+        # ---- attention with the head -> sequence exchange in its epilogue
+        N = n * world
+        if n >= 256:
+            seq = min(N, 2048)
+            q_lens = [seq] * (N // seq)
+            kv_lens = list(q_lens)
+        else:
+            q_lens, kv_lens = [1] * N, [2000] * N
+        bs = 64
+        nblk = [(k + bs - 1) // bs for k in kv_lens]
+        bt = torch.zeros(len(q_lens), max(nblk), dtype=torch.int32)
+        o = 1
+        for i, nb in enumerate(nblk):
+            bt[i, :nb] = torch.arange(o, o + nb)
+            o += nb
+        q_in, kc, vc = R(N, h * D), R(o, hkv, bs, D), R(o, hkv, bs, D)
+        meta = ops.build_attention_metadata(q_lens, kv_lens, bt.to(dev), h // hkv, h, D, dev, Hkv=hkv)
+        scale = D ** -0.5
+
+        def fused_x2():
+            view = comm.attention_gather_tokens(q_in, kc, vc, meta, h, hkv, D, scale)
+            return ops.quant_fp8_row(view, sync=comm.take_wait("attn"))
+
+        recv2 = torch.empty(world, n, h * D, dtype=torch.bfloat16, device=dev)
+
+        def unfused_x2():
+            out = ops.attention(q_in, kc, vc, meta, h, hkv, D, scale)
+            dist.all_to_all_single(recv2, out.view(world, n, h * D))
+            return ops.quant_fp8_row(recv2.transpose(0, 1).reshape(n, world * h * D))
+
+        t_f, t_b = timed(fused_x2, a.iters), timed(unfused_x2, a.iters)
+        flops = sum(4.0 * a_ * (b_ - a_ / 2.0) * h * D for a_, b_ in zip(q_lens, kv_lens))
+        sent = n * (world - 1) * h * D * 2.0
+        roof = max(flops / (peak * 1e12), sent / (LINK_GBS * 1e9)) * 1e6
+        res.append({"case": "attention_scatter", "tokens_per_rank": n, "fused_us": t_f,
+                    "attention_then_nccl_us": t_b, "speedup": t_b / t_f, "roofline_us": roof,
+                    "fraction_of_roofline": roof / t_f, "bytes_sent_per_gpu": sent, "flops": flops})
+        del kc, vc, q_in
         # ---- row-parallel GEMM + all-reduce
         a_in = R(n, h * D)
 

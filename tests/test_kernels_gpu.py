@@ -240,14 +240,16 @@ def test_linear_strided_views():
     assert float(out_buf[:, :128].abs().max()) == 0 and float(out_buf[:, 512:].abs().max()) == 0
 
 
-@pytest.mark.parametrize("M,blk", [(300, 192), (64, 192), (1000, 80)])
-def test_linear_scatter_epilogue_local_destinations(M, blk):
+@pytest.mark.parametrize("M,blk,K", [(300, 192, 512), (64, 192, 512), (1000, 80, 512),
+                                     (64, 192, 4096), (128, 512, 2048), (5, 128, 8192)])
+def test_linear_scatter_epilogue_local_destinations(M, blk, K):
     """The scatter epilogue with both destinations in this GPU's memory: feature block j of
     token m must land in buffer j at row m + offset (blk=192 takes the coalesced store path,
-    blk=80 the direct one)."""
+    blk=80 the direct one; with at most 128 tokens and a long K the CTAs of a cluster split K
+    and the CTA that finishes a column range stores it to its owner)."""
     import ctypes
     from arcticinference_b200.ops import native
-    world, K, off = 2, 512, 7
+    world, off = 2, 7
     x = _rand(M, K)
     w = _rand(world * blk, K, scale=1.0 / math.sqrt(K))
     bufs = [torch.zeros(M + 2 * off, blk, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
@@ -592,10 +594,11 @@ def test_linear_fp8_row_shard_views():
     ops.check_status()
 
 
-@pytest.mark.parametrize("M,blk", [(300, 192), (64, 192), (1000, 80)])
-def test_linear_fp8_row_scatter_epilogue_local_destinations(M, blk):
+@pytest.mark.parametrize("M,blk,K", [(300, 192, 512), (64, 192, 512), (1000, 80, 512),
+                                     (64, 192, 4096), (128, 512, 4096), (5, 128, 8192)])
+def test_linear_fp8_row_scatter_epilogue_local_destinations(M, blk, K):
     import ctypes
-    world, K, off = 2, 512, 7
+    world, off = 2, 7
     xq = ops.quant_fp8_row(_rand(M, K))
     w = quant.quantize_weight_fp8_row(_rand(world * blk, K, scale=1.0 / math.sqrt(K)))
     bufs = [torch.zeros(M + 2 * off, blk, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
