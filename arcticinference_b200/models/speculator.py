@@ -199,6 +199,29 @@ class ArcticSpeculator:
             n += 1
         return n
 
+    # ---------------------------------------------------------------- vocabulary shards
+    def shard_heads(self, comm) -> bool:
+        """Keep only this rank's slice of every LM head's vocabulary rows: each rank then
+        streams 1/W of the head per draft token and the ranks exchange one (value, token)
+        candidate per row (``comm.argmax_exchange``, 16 bytes per row per rank; the
+        reference's top-1 exchange: arctic_speculator.py:328-342). Embeddings stay replicated
+        (a row gather, no reduction to pay for). Returns False, leaving the heads whole, when
+        the vocabulary does not split into multiples of 16 rows."""
+        W = comm.ways
+        V = self.cfg.vocab_size
+        if W <= 1 or V % (16 * W):
+            return False
+        per = V // W
+        off = comm.rank * per
+        for k in [k for k in self.w if k.startswith("head")]:
+            t = self.w[k]
+            if isinstance(t, torch.Tensor):
+                self.w[k] = t[off:off + per].clone()
+            else:                                   # a quantised head: slice codes and scales
+                self.w[k] = t[off:off + per]
+        self.tp_comm, self.tp_offset, self.tp_rows = comm, off, per
+        return True
+
     QHEAD_MAX_BATCH = 32
 
     def make_qheads(self) -> int:
@@ -303,7 +326,12 @@ class ArcticSpeculator:
                                               self.LN_EPS)
                 head = self._head("head.%d.weight" % k, B)
             logits = ops.linear(prev, head)
-            tok, _ = ops.argmax_sample(logits)
+            tp = getattr(self, "tp_comm", None)
+            if tp is None:
+                tok, _ = ops.argmax_sample(logits)
+            else:
+                ids, vals = ops.argmax_sample(logits, index_offset=self.tp_offset)
+                tok = tp.argmax_exchange(ids, vals)
             tok = tok.clamp_(0, self.cfg.vocab_size - 1)
             out[:, i] = tok
         return out

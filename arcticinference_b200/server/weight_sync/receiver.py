@@ -65,6 +65,9 @@ def _apply_speculator(engine, stream) -> dict:
     for k, dst in old.items():
         new = prop.w.get(k)
         if new is not None and new is not dst:
+            if new.shape != dst.shape and getattr(prop, "tp_comm", None) is not None and \
+                    k.startswith("head"):
+                new = new[prop.tp_offset:prop.tp_offset + prop.tp_rows]   # this rank's vocabulary rows
             dst.copy_(new.to(dst.dtype))
             prop.w[k] = dst
     # the fp8 copies of the LM heads follow their (now updated) bf16 originals, in place

@@ -43,6 +43,9 @@ def attach_speculation(engine) -> None:
             runner.proposer = build_speculator(scfg, runner.device, seed=engine.config.seed + 1)
         else:
             runner.proposer = build_speculator(cfg.model, runner.device)
+        comm = getattr(engine, "comm", None)
+        if comm is not None and comm.ways > 1 and runner.proposer.shard_heads(comm):
+            logger.info("speculator: LM heads sharded by vocabulary over %d ranks", comm.ways)
         if cfg.quantization == "fp8":
             n = runner.proposer.quantize_fp8()
             logger.info("speculator: %d matrices stored as fp8 with per-row scales", n)

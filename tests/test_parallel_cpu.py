@@ -169,3 +169,70 @@ def test_run_ahead_on_two_ranks_with_chunked_prompts_and_mode_shifts():
     assert len(a) == len(b) and all(abs(x - y) < 5e-2 for x, y in zip(a, b))
     assert lp_two_ranks[0][0] == lp_one_rank[0][0]
     assert abs(lp_two_ranks[1][0] - lp_one_rank[1][0]) < 5e-2 and len(lp_two_ranks[1]) == 4
+
+
+def _spec_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    sys.path.insert(0, ROOT)
+    torch.set_num_threads(1)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from arcticinference_b200 import LLM
+    from arcticinference_b200.parallel.comm import Communicator
+    comm = Communicator(world, 1, None)
+    llm = LLM(model="llama-tiny", device="cpu", comm=comm, num_gpu_blocks_override=64, block_size=16,
+              max_model_len=512, tensor_parallel_size=world, speculative_config=_SPEC)
+    prop = llm.engine.runner.proposer
+    h, tok = _spec_inputs(prop.cfg.input_hidden_dim)
+    drafts = prop.propose(h, tok, 3)
+    rows = prop.w["head.0.weight"].shape[0]
+    from arcticinference_b200 import SamplingParams
+    outs = llm.generate([{"prompt_token_ids": p} for p in PROMPTS[:2]],
+                        SamplingParams(temperature=0, max_tokens=6, ignore_eos=True))
+    toks = [o.outputs[0].token_ids for o in outs]
+    if rank == 0:
+        q.put((drafts.numpy(), rows, toks, llm.engine.stats["draft_tokens"]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+_SPEC = {"method": "arctic", "model": "random", "num_speculative_tokens": 3}
+
+
+def _spec_inputs(dim):
+    g = torch.Generator().manual_seed(5)
+    return torch.randn(6, dim, generator=g).to(torch.bfloat16), torch.arange(6, dtype=torch.int64) * 7
+
+
+def test_speculator_heads_sharded_by_vocabulary_draft_the_same_tokens():
+    """Tensor-parallel ranks keep 1/W of each speculator LM head and exchange one
+    (value, token) candidate per row; the drafts equal the single-rank speculator's."""
+    from arcticinference_b200 import LLM
+    ref = LLM(model="llama-tiny", device="cpu", num_gpu_blocks_override=64, block_size=16,
+              max_model_len=512, speculative_config=_SPEC)
+    prop = ref.engine.runner.proposer
+    h, tok = _spec_inputs(prop.cfg.input_hidden_dim)
+    want = prop.propose(h, tok, 3)
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_spec_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got, rows, toks, drafted = _result_or_child_failure(q, procs, 300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert rows == prop.cfg.vocab_size // world
+    assert (got == want.numpy()).all(), (got, want)
+    # and the two-rank engine generates with them (drafts verified and re-drafted in the step)
+    from arcticinference_b200 import SamplingParams
+    assert drafted > 0 and [len(t) for t in toks] == [6, 6]
+    base = LLM(model="llama-tiny", device="cpu", num_gpu_blocks_override=64, block_size=16,
+               max_model_len=512)
+    want_toks = [o.outputs[0].token_ids for o in base.generate(
+        [{"prompt_token_ids": p} for p in PROMPTS[:2]],
+        SamplingParams(temperature=0, max_tokens=6, ignore_eos=True))]
+    assert [t[0] for t in toks] == [t[0] for t in want_toks]
