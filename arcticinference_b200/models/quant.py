@@ -266,7 +266,16 @@ def quantize_model_fp8(model, prefill_shadow="auto", scheme: str = "channel") ->
     180 GB part), otherwise long prefill expands each weight into a shared scratch matrix."""
     if scheme not in ("channel", "block"):
         raise ValueError("fp8 scheme must be 'channel' or 'block'")
-    quant = quantize_weight_fp8_row if scheme == "channel" else quantize_weight_fp8
+    ways = max(1, int(getattr(model, "n_stored", 1)))
+
+    def quant(w):
+        if scheme != "channel":
+            return quantize_weight_fp8(w)
+        # tiled storage only when every rank's row and column shard falls on tile boundaries
+        n, k = w.shape
+        aligned = n % (TILE_ROWS * ways) == 0 and k % (TILE_K * ways) == 0
+        return quantize_weight_fp8_row(w, tiled=None if aligned else False)
+
     for lw in model.layers:
         for name in ("wqkv", "wo", "wgu", "wdown"):
             w = getattr(lw, name)

@@ -24,7 +24,8 @@ Cases (Llama-3.1-8B shapes, bf16; n = tokens per rank):
 Times are CUDA events on the launching stream, median of ``--iters`` after warm-up, maximum
 over ranks. For each fused case the roofline time is the slower of FLOPs / measured bf16 peak
 and bytes sent per GPU / 770 GB/s (measured peer-copy bandwidth per direction on this pool;
-nominal 900); the printed fraction is roofline time / measured time.
+nominal 900), for attention also its K/V bytes / 6533.5 GB/s measured copy bandwidth; the
+printed fraction is roofline time / measured time.
 """
 
 import argparse
@@ -40,6 +41,7 @@ from arcticinference_b200 import ops  # noqa: E402
 from arcticinference_b200.parallel.comm import init_communicator  # noqa: E402
 
 LINK_GBS = 770.0
+HBM_GBS = 6533.5     # measured copy bandwidth of this pool (decode attention is bound by KV bytes)
 
 
 def peaks():
@@ -146,7 +148,8 @@ def main():
         t_f, t_b = timed(fused_x2, a.iters), timed(unfused_x2, a.iters)
         flops = sum(4.0 * a_ * (b_ - a_ / 2.0) * h * D for a_, b_ in zip(q_lens, kv_lens))
         sent = n * (world - 1) * h * D * 2.0
-        roof = max(flops / (peak * 1e12), sent / (LINK_GBS * 1e9)) * 1e6
+        kv_bytes = sum(kv_lens) * hkv * D * 2 * 2.0       # K and V of this rank's heads, read once
+        roof = max(flops / (peak * 1e12), sent / (LINK_GBS * 1e9), kv_bytes / (HBM_GBS * 1e9)) * 1e6
         res.append({"case": "attention_scatter", "tokens_per_rank": n, "fused_us": t_f,
                     "attention_then_nccl_us": t_b, "speedup": t_b / t_f, "roofline_us": roof,
                     "fraction_of_roofline": roof / t_f, "bytes_sent_per_gpu": sent, "flops": flops})
