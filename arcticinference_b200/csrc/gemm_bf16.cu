@@ -64,6 +64,7 @@ struct GemmArgs {
   int fp8;         // 1: operands are e4m3 bytes (kind::f8f6f4), 128 k-elements per stage
   int kblock_elems;  // k-elements per stage: 64 (bf16) or 128 (fp8)
   int prefetch_w;    // 1: the weight operand is written by no kernel of the stream (a parameter)
+  int b_parts;       // TMA boxes per B stage (1, or more boxes of bn / b_parts rows each)
   // > 1: the launch is made of clusters of this many CTAs. The CTAs of a cluster share one
   // output tile and split its K range; they exchange their fp32 partial sums through each
   // other's shared memory and each finishes and stores bn / cluster_splits columns (the
@@ -190,10 +191,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t dst = smem_base + (uint32_t)s * stage_bytes;
         if (w_is_b) {
           mbar_expect_tx(full_bar(s), b_bytes);
-          if (p.b_tiled)
-            tma_load_4d(dst + kABytes, &tmap_b, full_bar(s), 0, 0, kb, tile_b0 * (p.bn / 16));
-          else
-            tma_load_2d(dst + kABytes, &tmap_b, full_bar(s), kb * p.kblock_elems, tile_b0 * p.bn);
+          const int pr = p.bn / p.b_parts;
+          for (int h = 0; h < p.b_parts; ++h) {
+            const uint32_t d2 = dst + kABytes + (uint32_t)(h * pr) * 128u;
+            if (p.b_tiled)
+              tma_load_4d(d2, &tmap_b, full_bar(s), 0, 0, kb, tile_b0 * (p.bn / 16) + h * (pr / 16));
+            else
+              tma_load_2d(d2, &tmap_b, full_bar(s), kb * p.kblock_elems, tile_b0 * p.bn + h * pr);
+          }
         } else {
           mbar_expect_tx(full_bar(s), kABytes);
           if (p.a_tiled)
@@ -245,12 +250,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * p.kblock_elems, tile_a * kBlockM);
           }
           if (!load_b) {
-          } else if (p.b_tiled) {
-            // 2 KB pieces (16 rows x 128 bytes) that are contiguous in memory, bn / 16 of them
-            tma_load_4d(a_dst + kABytes, &tmap_b, full_bar(stage), 0, 0, kb, tile_b * (p.bn / 16));
           } else if (!p.b_mn_major) {
-            tma_load_2d(a_dst + kABytes, &tmap_b, full_bar(stage), kb * p.kblock_elems,
-                        tile_b * p.bn);
+            // tiled storage: 2 KB pieces (16 rows x 128 bytes) that are contiguous in memory
+            const int pr = p.bn / p.b_parts;
+            for (int h = 0; h < p.b_parts; ++h) {
+              const uint32_t d2 = a_dst + kABytes + (uint32_t)(h * pr) * 128u;
+              if (p.b_tiled)
+                tma_load_4d(d2, &tmap_b, full_bar(stage), 0, 0, kb,
+                            tile_b * (p.bn / 16) + h * (pr / 16));
+              else
+                tma_load_2d(d2, &tmap_b, full_bar(stage), kb * p.kblock_elems,
+                            tile_b * p.bn + h * pr);
+            }
           } else {
             // [64 k-rows][64 n] boxes, one per 64-wide atom along N
             for (int j = 0; j < p.bn / 64; ++j)
@@ -1107,12 +1118,17 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
   a.a_tiled = (w_tiled && a.transposed) ? 1 : 0;
   a.b_tiled = (w_tiled && !a.transposed) ? 1 : 0;
   a.prefetch_w = w_static ? 1 : 0;
+  // One row of tiles over a row-major weight: two half-height boxes per stage instead of one
+  // (the same bytes in flight as twice as many TMA operations: 35.6 -> 33.8 us on the 128-token
+  // gate/up projection; thirteen 16-row boxes, in contrast, took 54 us).
+  a.b_parts = (a.tiles_a == 1 && !a.transposed && !a.b_tiled && a.bn % 16 == 0) ? 2 : 1;
   if (get_tmap(&ta, pa, (uint64_t)a.rows_a, (uint64_t)K,
                a.a_tiled ? (uint64_t)w_tile_stride_k : (uint64_t)lda, kBlockM, fp8,
                a.a_tiled ? (uint64_t)w_tile_stride_n : 0) != 0)
     return -4;
   if (get_tmap(&tb, pb, (uint64_t)a.rows_b, (uint64_t)K,
-               a.b_tiled ? (uint64_t)w_tile_stride_k : (uint64_t)ldb, (uint32_t)a.bn, fp8,
+               a.b_tiled ? (uint64_t)w_tile_stride_k : (uint64_t)ldb,
+               (uint32_t)(a.bn / a.b_parts), fp8,
                a.b_tiled ? (uint64_t)w_tile_stride_n : 0) != 0)
     return -4;
 
@@ -1228,6 +1244,7 @@ int ab200_gemm_bf16_nn(const void* x, long long ldx, const void* wt, long long l
   a.rows_a = M;
   a.rows_b = N;
   a.b_mn_major = 1;
+  a.b_parts = 1;
   a.bn = (N % 128 == 0) ? 128 : 64;
   a.tiles_a = (M + kBlockM - 1) / kBlockM;
   a.tiles_b = N / a.bn;

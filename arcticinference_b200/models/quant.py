@@ -127,12 +127,12 @@ class Fp8RowWeight(Fp8Weight):
     carry their scales along; column slices (the K shards of row-parallel layers) keep all of
     them.
 
-    Storage of the codes: row-major [N, K], or ("tiled", the default on a GPU when N % 16 == 0
-    and K % 128 == 0) [N/16, K/128, 16, 128], in which each 16-row x 128-byte piece is 2 KB of
-    consecutive memory. A GEMM stage's weight tile is then a few dozen KB in 2 KB bursts
-    instead of hundreds of 128-byte pieces one row stride apart, which is what a decode step,
-    whose time is the time to stream the weights once, needs from DRAM. Shard views are slices
-    of the first two dimensions."""
+    Storage of the codes: row-major [N, K] (the default), or "tiled" (N % 16 == 0 and
+    K % 128 == 0) [N/16, K/128, 16, 128], in which each 16-row x 128-byte piece is 2 KB of
+    consecutive memory (a GEMM stage's weight tile is then a few dozen KB in 2 KB bursts
+    instead of hundreds of 128-byte pieces one row stride apart). Measured on the decode GEMMs
+    it is no faster than row-major storage, so nothing selects it by default. Shard views of
+    tiled storage are slices of the first two dimensions."""
 
     __slots__ = ("tiled",)
 
@@ -190,15 +190,14 @@ class Fp8RowWeight(Fp8Weight):
         self.scale.copy_(q.scale)
 
 
-def quantize_weight_fp8_row(w: torch.Tensor, tiled=None) -> Fp8RowWeight:
+def quantize_weight_fp8_row(w: torch.Tensor, tiled: bool = False) -> Fp8RowWeight:
     """bf16 [N, K] -> e4m3 codes + one scale per row (scale = amax / 448). ``tiled``: storage
-    layout of the codes (see :class:`Fp8RowWeight`); None picks tiles for GPU tensors whose
-    dimensions allow them."""
+    layout of the codes (see :class:`Fp8RowWeight`); row-major unless asked for."""
     N, K = w.shape
     if K % 16:
         raise ValueError("fp8 quantisation needs K to be a multiple of 16, got %d" % K)
-    if tiled is None:
-        tiled = w.is_cuda and N % TILE_ROWS == 0 and K % TILE_K == 0
+    if tiled and (N % TILE_ROWS or K % TILE_K):
+        raise ValueError("tiled fp8 storage needs N %% %d == 0 and K %% %d == 0" % (TILE_ROWS, TILE_K))
     wf = w.float()
     scale = wf.abs().amax(dim=1).clamp_min(1e-10) / FP8_MAX
     q = (wf / scale[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
@@ -266,15 +265,13 @@ def quantize_model_fp8(model, prefill_shadow="auto", scheme: str = "channel") ->
     180 GB part), otherwise long prefill expands each weight into a shared scratch matrix."""
     if scheme not in ("channel", "block"):
         raise ValueError("fp8 scheme must be 'channel' or 'block'")
-    ways = max(1, int(getattr(model, "n_stored", 1)))
-
     def quant(w):
         if scheme != "channel":
             return quantize_weight_fp8(w)
-        # tiled storage only when every rank's row and column shard falls on tile boundaries
-        n, k = w.shape
-        aligned = n % (TILE_ROWS * ways) == 0 and k % (TILE_K * ways) == 0
-        return quantize_weight_fp8_row(w, tiled=None if aligned else False)
+        # row-major codes: the tiled storage (see Fp8RowWeight) measured no faster, constrains
+        # shard boundaries to 16 rows x 128 columns, and the decode GEMM splits a row-major
+        # stage into two TMA boxes, which is worth a few per cent
+        return quantize_weight_fp8_row(w, tiled=False)
 
     for lw in model.layers:
         for name in ("wqkv", "wo", "wgu", "wdown"):

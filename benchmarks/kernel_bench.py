@@ -109,9 +109,9 @@ CASES = {
     "gemm_fp8row_decode_128": ("gemm_fp8row", (128, 28672, 4096)),
     "gemm_fp8row_decode_128_down": ("gemm_fp8row", (128, 4096, 14336)),
     "gemm_fp8row_decode_o": ("gemm_fp8row", (32, 4096, 4096)),
-    "gemm_fp8row_decode_128_rowmajor": ("gemm_fp8row_rm", (128, 28672, 4096)),
-    "gemm_fp8row_decode_128_down_rowmajor": ("gemm_fp8row_rm", (128, 4096, 14336)),
-    "gemm_fp8row_prefill_rowmajor": ("gemm_fp8row_rm", (8192, 28672, 4096)),
+    "gemm_fp8row_decode_128_tiled": ("gemm_fp8row_tiled", (128, 28672, 4096)),
+    "gemm_fp8row_decode_128_down_tiled": ("gemm_fp8row_tiled", (128, 4096, 14336)),
+    "gemm_fp8row_prefill_tiled": ("gemm_fp8row_tiled", (8192, 28672, 4096)),
     "gemm_fp8row_decode_qkv": ("gemm_fp8row", (128, 6144, 4096)),
     "gemm_w8a8_block_prefill": ("gemm_fp8blk", (8192, 28672, 4096)),
     "attn_prefill": ("attn", ([8192], [8192])),
@@ -164,12 +164,12 @@ def run_case(a, case):
         x, ws = R(M, K), [quant.quantize_weight_fp8(R(N, K)) for _ in range(nc)]
         fn = lambda i=0: ops.linear(x, ws[i])
         flops, byts = 2.0 * M * N * K, 2.0 * (M * K + M * N) + 1.0 * N * K
-    elif kind in ("gemm_fp8row", "gemm_fp8row_rm"):
+    elif kind in ("gemm_fp8row", "gemm_fp8row_tiled"):
         from arcticinference_b200.models import quant
         M, N, K = prm
         nc = copies_for(N * K)
         xq = ops.quant_fp8_row(R(M, K))
-        tiled = None if kind == "gemm_fp8row" else False     # None: tiled storage on the GPU
+        tiled = kind != "gemm_fp8row"     # the "_tiled" cases store 16-row x 128-byte tiles
         ws = [quant.quantize_weight_fp8_row(R(N, K), tiled=tiled) for _ in range(nc)]
         for w_ in ws:
             ops.mark_static(w_)      # parameters, as in a loaded model

@@ -582,6 +582,22 @@ def test_linear_fp8_row_split_k(splits):
     _close(y, _row_ref(xq, w), 3e-2, 2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 4096, 4096), (24, 1024, 512), (700, 2048, 1024), (200, 512, 256)])
+def test_linear_fp8_row_tiled_storage(M, N, K):
+    """The optional 16-row x 128-byte tile storage of the codes gives the same product, also
+    through shard views on tile boundaries."""
+    wf = _rand(N, K, scale=1.0 / math.sqrt(K))
+    xq = ops.quant_fp8_row(_rand(M, K))
+    flat, tiled = quant.quantize_weight_fp8_row(wf), quant.quantize_weight_fp8_row(wf, tiled=True)
+    assert not flat.tiled and tiled.tiled
+    y = ops.linear(xq, flat)
+    assert torch.equal(ops.linear(xq, tiled), y)
+    assert torch.equal(ops.linear(xq, tiled[N // 4:N // 2]), ops.linear(xq, flat[N // 4:N // 2]))
+    xs = ops.quant_fp8_row(_rand(M, K // 2))
+    assert torch.equal(ops.linear(xs, tiled[:, K // 2:]), ops.linear(xs, flat[:, K // 2:]))
+    ops.check_status()
+
+
 def test_linear_fp8_row_shard_views():
     w = quant.quantize_weight_fp8_row(_rand(2048, 2048, scale=0.03))
     xk = ops.quant_fp8_row(_rand(64, 2048))
