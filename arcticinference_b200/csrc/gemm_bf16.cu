@@ -65,6 +65,11 @@ struct GemmArgs {
   int kblock_elems;  // k-elements per stage: 64 (bf16) or 128 (fp8)
   int prefetch_w;    // 1: the weight operand is written by no kernel of the stream (a parameter)
   int b_parts;       // TMA boxes per B stage (1, or more boxes of bn / b_parts rows each)
+  // Scatter epilogue: every rank walks the B tiles starting this many tiles in, i.e. at its own
+  // share of the columns, so that at any moment the ranks store into different destination
+  // ranks. With all ranks starting at tile 0 they all store into rank 0 first, then rank 1,
+  // ...: one NVLink ingress carries everything while the others idle.
+  int tile_b_rot;
   // > 1: the launch is made of clusters of this many CTAs. The CTAs of a cluster share one
   // output tile and split its K range; they exchange their fp32 partial sums through each
   // other's shared memory and each finishes and stores bn / cluster_splits columns (the
@@ -105,13 +110,18 @@ __device__ __forceinline__ void decode_work(const GemmArgs& p, int w, int& tile_
   if (p.cluster_splits > 1) {
     tile_a = 0;
     split = w % p.cluster_splits;
-    tile_b = w / p.cluster_splits;
+    tile_b = w / p.cluster_splits + p.tile_b_rot;
+    if (tile_b >= p.tiles_b) tile_b -= p.tiles_b;
     return;
   }
   tile_a = w % p.tiles_a;
   const int rest = w / p.tiles_a;
   tile_b = rest % p.tiles_b;
   split = rest / p.tiles_b;
+  if (p.tile_b_rot) {
+    tile_b += p.tile_b_rot;
+    if (tile_b >= p.tiles_b) tile_b -= p.tiles_b;
+  }
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -358,8 +368,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // one work item per CTA; what follows the accumulator is the cluster exchange below
       if (scaled) {
         const int cw = p.bn / p.cluster_splits;
-        const long long c0 = (long long)(blockIdx.x / p.cluster_splits) * p.bn +
-                             (long long)(blockIdx.x % p.cluster_splits) * cw;
+        int ta, tb, sp;
+        decode_work(p, (int)blockIdx.x, ta, tb, sp);
+        const long long c0 = (long long)tb * p.bn + (long long)sp * cw;
         for (int i = lane; i < cw; i += 32)
           col_scale[i] = (c0 + i < p.rows_b) ? p.scale_b[c0 + i] : 0.f;
         __syncwarp();
@@ -1104,6 +1115,8 @@ static int launch_linear(const void* x, long long ldx, const void* w, long long 
       sig.world = sync->sig_world;
     }
   }
+  if (peer_cols > 0 && sig.world > 1)
+    a.tile_b_rot = (int)(((long long)sig.my_rank * a.tiles_b) / sig.world);
   void* final_out = out;
   const bool ws_split = a.splits > 1 && a.cluster_splits <= 1;
   if (!ws_split) a.sig = sig;   // with split-K through the workspace the reduce kernel writes the output

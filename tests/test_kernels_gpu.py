@@ -610,6 +610,37 @@ def test_linear_fp8_row_shard_views():
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,blk,K,rank", [(300, 192, 512, 1), (64, 192, 4096, 1), (128, 512, 4096, 2),
+                                          (2000, 256, 1024, 3)])
+def test_linear_fp8_row_scatter_walks_tiles_from_its_own_rank(M, blk, K, rank):
+    """With a completion signal attached the scatter GEMM knows its rank and starts its walk
+    over the output tiles at its own share of the columns (so that ranks store into different
+    destinations at any moment). Same result; the signal reaches every rank's flag word."""
+    import ctypes
+    from arcticinference_b200.ops import native
+    world, off = 4, 3
+    xq = ops.quant_fp8_row(_rand(M, K))
+    w = quant.quantize_weight_fp8_row(_rand(world * blk, K, scale=1.0 / math.sqrt(K)))
+    bufs = [torch.zeros(M + 2 * off, blk, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    chan = torch.zeros(world, 64, device=DEV, dtype=torch.int32)   # per "rank": flags | done | epoch
+    flag_ptrs = (ctypes.c_void_p * world)(*[chan[r].data_ptr() for r in range(world)])
+    sync = native.PeerSync()
+    sync.sig_flag_ptrs = ctypes.cast(flag_ptrs, ctypes.c_void_p)
+    sync.sig_done_ctr = chan[rank].data_ptr() + 128
+    sync.sig_epoch_ctr = chan[rank].data_ptr() + 192
+    sync.sig_rank, sync.sig_world = rank, world
+    ops.linear_fp8_row(xq, w, peer=(ptrs, world, blk, off, blk), sync=sync)
+    ops.check_status()
+    want = _row_ref(xq, w)
+    for j, b in enumerate(bufs):
+        _close(b[off:off + M], want[:, j * blk:(j + 1) * blk], 3e-2, 2e-2)
+        assert float(b[:off].abs().max()) == 0 and float(b[off + M:].abs().max()) == 0
+    c = chan.cpu()
+    assert all(int(c[r, rank]) == 1 for r in range(world))     # every rank's word of this sender
+    assert int(c[rank, 48]) == 1 and int(c[rank, 32]) == 0      # epoch advanced, counter reset
+
+
 @pytest.mark.parametrize("M,blk,K", [(300, 192, 512), (64, 192, 512), (1000, 80, 512),
                                      (64, 192, 4096), (128, 512, 4096), (5, 128, 8192)])
 def test_linear_fp8_row_scatter_epilogue_local_destinations(M, blk, K):
