@@ -26,11 +26,15 @@ __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// AB200_PDL=0 launches every kernel with ordinary stream ordering.
+// Off unless AB200_PDL=1: measured end to end, the overlap gains 2 us per back-to-back decode
+// GEMM in isolation and loses about 1 % on the serving benchmark (on one and on two GPUs),
+// whose decode steps are replayed from CUDA graphs and whose early-resident successor CTAs
+// compete with the running kernel for the memory system. Without the attribute the two
+// griddepcontrol instructions are no-ops and kernels follow ordinary stream order.
 inline bool pdl_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("AB200_PDL");
-    return !(e != nullptr && e[0] == '0');
+    return e != nullptr && e[0] == '1';
   }();
   return on;
 }

@@ -49,7 +49,8 @@ def parse_args():
     ap.add_argument("--max-num-batched-tokens", type=int, default=None,
                     help="token budget of one engine step; default 8192 per GPU, so that a step "
                          "gives every GPU the same work whatever N is")
-    ap.add_argument("--shift-parallel-threshold", type=int, default=512)
+    ap.add_argument("--shift-parallel-threshold", type=int, default=None,
+                    help="default: each arm's own default (this engine 128, the reference 512)")
     ap.add_argument("--speculative-config", type=str, default=None)
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--no-clocks", action="store_true")
@@ -166,7 +167,7 @@ def run_reference(args, rank, local_rank):
                "--steps", str(args.steps), "--warmup", str(args.warmup),
                "--requests-per-gpu", str(args.requests_per_gpu),
                "--input-len", str(args.input_len), "--output-len", str(args.output_len),
-               "--shift-parallel-threshold", str(args.shift_parallel_threshold),
+               "--shift-parallel-threshold", str(args.shift_parallel_threshold or 512),
                "--quantization", str(args.quantization)]
         if args.max_num_batched_tokens:
             cmd += ["--max-num-batched-tokens", str(args.max_num_batched_tokens)]
@@ -252,8 +253,9 @@ def main():
               enable_prefix_caching=False, enforce_eager=args.enforce_eager,
               quantization=quant, speculative_config=args.speculative_config)
     if n_gpus > 1:
-        kw.update(ulysses_sequence_parallel_size=n_gpus, enable_shift_parallel=True,
-                  shift_parallel_threshold=args.shift_parallel_threshold)
+        kw.update(ulysses_sequence_parallel_size=n_gpus, enable_shift_parallel=True)
+        if args.shift_parallel_threshold is not None:
+            kw.update(shift_parallel_threshold=args.shift_parallel_threshold)
     llm = LLM(**kw)
     engine = llm.engine
     vocab = engine.config.model.vocab_size

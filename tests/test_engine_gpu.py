@@ -299,3 +299,35 @@ def test_fp8_engine_matches_the_cpu_path(scheme):
     ops.check_status()
     err = (hs[0] - hs[1]).abs().max().item()
     assert err < 0.1 * max(1.0, hs[1].abs().max().item()), err
+
+
+@pytest.mark.gpu
+def test_programmatic_dependent_launch_gives_the_same_tokens():
+    """AB200_PDL=1 launches the serving kernels with programmatic stream serialisation (set-up
+    and the first weight tiles of a kernel overlap the tail of the one before it). The switch is
+    read once per process, so the opted-in run is a child process; greedy tokens must agree."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import json, sys; sys.path.insert(0, %r)\n"
+        "from arcticinference_b200 import LLM, SamplingParams, ops\n"
+        "llm = LLM(model='llama-small', device='cuda:0', max_model_len=1024, num_gpu_blocks_override=256,"
+        " quantization='fp8')\n"
+        "outs = llm.generate([{'prompt_token_ids': list(range(1, 200))}, {'prompt_token_ids': [5, 6, 7]}],"
+        " SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))\n"
+        "ops.check_status()\n"
+        "print('TOKENS ' + json.dumps([o.outputs[0].token_ids for o in outs]))\n" % root)
+    toks = {}
+    for flag in ("0", "1"):
+        env = dict(os.environ, AB200_PDL=flag, ARCTIC_B200_NO_AUTOBUILD="1")
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                             timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+        line = [l for l in out.stdout.splitlines() if l.startswith("TOKENS ")][-1]
+        toks[flag] = json.loads(line[len("TOKENS "):])
+    same = sum(int(a == b) for x, y in zip(toks["0"], toks["1"]) for a, b in zip(x, y))
+    assert [t[0] for t in toks["0"]] == [t[0] for t in toks["1"]]
+    assert same >= 0.75 * sum(len(t) for t in toks["0"])
