@@ -19,6 +19,8 @@ views of shift parallelism), so ``ops.linear(x, w)`` works with either a bf16 te
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 BLOCK = 128
@@ -271,7 +273,12 @@ def quantize_model_fp8(model, prefill_shadow="auto", scheme: str = "channel") ->
         # row-major codes: the tiled storage (see Fp8RowWeight) measured no faster, constrains
         # shard boundaries to 16 rows x 128 columns, and the decode GEMM splits a row-major
         # stage into two TMA boxes, which is worth a few per cent
-        return quantize_weight_fp8_row(w, tiled=False)
+        # (AB200_FP8_TILED=1 selects the tiles where every rank's shards fall on tile boundaries)
+        n, k = w.shape
+        ways = max(1, int(getattr(model, "n_stored", 1)))
+        tiled = (os.environ.get("AB200_FP8_TILED") == "1" and
+                 n % (TILE_ROWS * ways) == 0 and k % (TILE_K * ways) == 0)
+        return quantize_weight_fp8_row(w, tiled=tiled)
 
     for lw in model.layers:
         for name in ("wqkv", "wo", "wgu", "wdown"):
