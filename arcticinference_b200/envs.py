@@ -23,6 +23,24 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ARCTIC_WEIGHT_SYNC_STRICT_NAMES": _flag("ARCTIC_WEIGHT_SYNC_STRICT_NAMES", "1"),
     "ARCTIC_B200_NO_AUTOBUILD": _flag("ARCTIC_B200_NO_AUTOBUILD"),
     "ARCTIC_B200_COMM_BACKEND": lambda: os.getenv("ARCTIC_B200_COMM_BACKEND", "fused"),
+    # ---- tuning switches of the kernel library and the communicator (docs/kernels.md,
+    # docs/parallelism.md); each names the default in its second argument
+    # programmatic dependent launch of the serving kernels (read once by the kernel library)
+    "AB200_PDL": _flag("AB200_PDL", "0"),
+    # split-K of one-row-of-tiles GEMMs inside thread-block clusters (0: through the workspace)
+    "AB200_GEMM_CLUSTER": _flag("AB200_GEMM_CLUSTER", "1"),
+    # fp8 codes stored in 16-row x 128-byte tiles instead of row-major
+    "AB200_FP8_TILED": _flag("AB200_FP8_TILED", "0"),
+    # small tensor-parallel reductions folded into the following RMSNorm kernel
+    "AB200_FOLD_REDUCE": _flag("AB200_FOLD_REDUCE", "1"),
+    # all-reduce kernel: "auto" (by size), "oneshot" or "twoshot"
+    "AB200_ALLREDUCE": lambda: os.getenv("AB200_ALLREDUCE", "auto"),
+    # a barrier kernel after every cross-rank exchange instead of signals and in-kernel waits
+    "AB200_FUSED_BARRIERS": _flag("AB200_FUSED_BARRIERS", "0"),
+    # long-lived engine objects frozen out of the cyclic garbage collector
+    "AB200_GC_FREEZE": _flag("AB200_GC_FREEZE", "1"),
+    # the speculator's n-head loop replayed from CUDA graphs
+    "ARCTIC_B200_SPEC_GRAPH": _flag("ARCTIC_B200_SPEC_GRAPH", "1"),
 }
 
 
