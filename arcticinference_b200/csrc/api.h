@@ -183,11 +183,6 @@ long long ab200_allreduce2_flag_bytes();
 int ab200_allreduce2(const void* const* part_ptrs, const void* const* res_ptrs,
                      const void* const* flag_ptrs, void* epochs, int my_rank, int world,
                      long long n_elems, int* status, cudaStream_t stream);
-int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long rows_per_rank,
-                            const void* idx, void* dst, long long R, int hidden,
-                            cudaStream_t stream);
-
-
 // ---- variants with cross-rank ordering built in (see Ab200PeerSync)
 int ab200_attention_scatter_sync(const void* q, long long ldq, const void* k, const void* v,
                                  long long num_blocks, int block_size, const void* block_tables,

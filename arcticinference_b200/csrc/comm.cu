@@ -14,8 +14,6 @@
 //   * allreduce_kernel   -- one-shot sum of W peers' partial buffers (bf16 in,
 //     fp32 accumulate in rank order 0..W-1 so that every rank produces the same
 //     bits), optional residual add fused.
-//   * gather_rows_peers  -- copies selected rows of a token-sliced tensor from
-//     the ranks that own them (last-token gather of sequence-parallel mode).
 //
 // The reference reaches the same points with NCCL calls
 // (arctic_inference/vllm/ulysses.py:436-455, vLLM row-parallel all-reduce).
@@ -179,20 +177,6 @@ allreduce2_kernel(PeerTable parts, PeerTable res, PeerTable flags, unsigned int*
   if (threadIdx.x == 0) epochs[b] = e;
 }
 
-// dst[r] = src_{owner(idx[r])}[idx[r] - owner*rows_per_rank], rows of `hidden` bf16.
-__global__ void gather_rows_peers_kernel(PeerTable src, long long rows_per_rank,
-                                         const long long* __restrict__ idx,
-                                         __nv_bfloat16* __restrict__ dst, int hidden) {
-  const long long r = blockIdx.x;
-  const long long g = idx[r];
-  const int owner = (int)(g / rows_per_rank);
-  const long long local = g - owner * rows_per_rank;
-  const uint4* s = reinterpret_cast<const uint4*>(
-      reinterpret_cast<const __nv_bfloat16*>(src.ptr[owner]) + local * hidden);
-  uint4* d = reinterpret_cast<uint4*>(dst + r * (long long)hidden);
-  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) d[i] = ld_sys_v4(s + i);
-}
-
 }  // namespace ab200
 
 using namespace ab200;
@@ -268,19 +252,6 @@ int ab200_allreduce2(const void* const* part_ptrs, const void* const* res_ptrs,
   allreduce2_kernel<<<(unsigned)blocks, 512, 0, stream>>>(
       p, r, f, reinterpret_cast<unsigned int*>(epochs), my_rank, world, n_vec, status,
       kWaitLimitNs);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
-}
-
-int ab200_gather_rows_peers(const void* const* src_ptrs, int world, long long rows_per_rank,
-                            const void* idx, void* dst, long long R, int hidden,
-                            cudaStream_t stream) {
-  if (world < 1 || world > kMaxPeers || (hidden % 8)) return -2;
-  if (R <= 0) return 0;
-  PeerTable t;
-  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < world ? const_cast<void*>(src_ptrs[i]) : nullptr;
-  gather_rows_peers_kernel<<<(unsigned)R, 128, 0, stream>>>(
-      t, rows_per_rank, reinterpret_cast<const long long*>(idx),
-      reinterpret_cast<__nv_bfloat16*>(dst), hidden);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -189,7 +189,6 @@ class FusedCommunicator(Communicator):
         native.declare("ab200_barrier", I, [P, I, I, P, P, P])
         native.declare("ab200_allreduce", I, [P, I, P, P, LL, P])
         native.declare("ab200_allreduce2", I, [P, P, P, P, I, I, LL, P, P])
-        native.declare("ab200_gather_rows_peers", I, [P, I, LL, P, P, LL, I, P])
         native.declare("ab200_push_rows", I, [P, LL, P, LL, LL, I, I, P, P, P, LL, I, P])
         native.declare("ab200_rmsnorm_allgather", I, [P, LL, P, P, P, LL, I, I, LL, I, F, P])
         native.declare("ab200_argmax_exchange", I, [P, P, I, I, P, P, I, I, P, P, P, P, P])
