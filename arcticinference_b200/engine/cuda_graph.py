@@ -48,7 +48,7 @@ class DecodeGraph:
         self.max_blocks = (cfg.scheduler.max_model_len + runner.block_size - 1) // runner.block_size
         hkv = m.hkv
         # enough KV splits to occupy the GPU when the batch is small; for a large batch the
-        # sequences of the last, partly filled round of CTAs are cut (ops.tail_split_plan)
+        # sequences of the last, partly filled wave of CTAs are cut (ops.tail_split_plan)
         max_q = 1 + (cfg.speculative.max_draft_tokens if cfg.speculative else 0)
         small_tiles = max_q * runner.G <= 32 and runner.block_size <= 64
         self.splits = int(max(1, min(16, 148 // max(1, bucket * hkv))))

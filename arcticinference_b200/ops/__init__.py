@@ -804,11 +804,11 @@ def plan_attention_work(q_lens, kv_lens, G: int, causal: bool = True, num_sms: i
 
 def tail_split_plan(n_seqs: int, Hkv: int, slots: int, max_splits: int = 4):
     """Decode call with more CTAs (sequences x KV heads) than the GPU holds at once: the CTAs
-    run in rounds of ``slots``, all of about the same length, and the last round is partly
-    empty (1024 CTAs on 296 slots: three full rounds and 136 CTAs in a fourth). Returns
-    (number of sequences to cut, pieces per cut sequence): the sequences of that last round
+    run in waves of ``slots``, all of about the same length, and the last wave is partly
+    empty (1024 CTAs on 296 slots: three full waves and 136 CTAs in a fourth). Returns
+    (number of sequences to cut, pieces per cut sequence): the sequences of that last wave
     are cut so that their pieces cover all slots, e.g. 17 sequences in 2 pieces each; with the
-    pieces placed last in the work list the call takes 3.5 rounds instead of 4. (Cutting
+    pieces placed last in the work list the call takes 3.5 waves instead of 4. (Cutting
     every sequence instead measured no gain: every CTA then pays its set-up twice.)"""
     ctas = n_seqs * Hkv
     full, rem = divmod(ctas, slots)

@@ -141,7 +141,7 @@ def run_reference(args, rank, local_rank):
     runner = os.path.join(REPO, "baseline", "run_reference.py")
     if not os.path.isdir(os.path.join(REPO, "baseline", "_ref", "arctic_inference")):
         print(json.dumps({"impl": "reference", "unavailable":
-                          "baseline/_ref holds no copy of the reference (see DESIGN.md, Reference arm)"}))
+                          "baseline/_ref holds no copy of the reference"}))
         return 0
     env = {k: v for k, v in os.environ.items()
            if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK",

@@ -21,11 +21,11 @@ def _covered(work, n_seq, kv_lens):
 
 
 def test_tail_split_plan_cuts_the_last_round_only():
-    # 128 sequences x 8 KV heads on 296 CTA slots: three full rounds and 136 CTAs in a fourth;
-    # the 17 sequences of that round are cut in two so that their pieces cover the slots
+    # 128 sequences x 8 KV heads on 296 CTA slots: three full waves and 136 CTAs in a fourth;
+    # the 17 sequences of that wave are cut in two so that their pieces cover the slots
     assert ops.tail_split_plan(128, 8, 296) == (17, 2)
-    assert ops.tail_split_plan(64, 8, 296) == (0, 1)     # last round 73 % full: left alone
-    assert ops.tail_split_plan(37, 8, 296) == (0, 1)     # exactly one round
+    assert ops.tail_split_plan(64, 8, 296) == (0, 1)     # last wave 73 % full: left alone
+    assert ops.tail_split_plan(37, 8, 296) == (0, 1)     # exactly one wave
     assert ops.tail_split_plan(16, 8, 296) == (0, 1)     # fewer CTAs than slots: other rule
 
 
