@@ -391,9 +391,16 @@ class EngineConfig:
         # Options this engine parses for command-line compatibility but cannot honour are
         # refused here rather than ignored.
         if p.pipeline_parallel_size > 1:
-            raise NotImplementedError(
-                "pipeline_parallel_size > 1: this engine executes the SP x TP plane of one "
-                "replica; pipeline stages are only enumerated (parallel/layout.py)")
+            # whole-model stages (parallel/pipeline.py): one rank per stage, nothing sharded
+            # inside a stage, no drafting (the drafter lives with the last stage's hidden states)
+            if p.tp * p.sp > 1:
+                raise NotImplementedError(
+                    "pipeline_parallel_size > 1 together with tensor or sequence parallelism: "
+                    "pipeline stages are whole-model stages here (TP = SP = 1)")
+            if self.speculative is not None:
+                raise NotImplementedError("speculative decoding with pipeline parallelism")
+            if p.pipeline_parallel_size > m.num_hidden_layers:
+                raise ValueError("more pipeline stages than decoder layers")
         if p.enable_expert_parallel:
             raise NotImplementedError("enable_expert_parallel: no mixture-of-experts model is "
                                       "implemented, so there is nothing to shard by expert")

@@ -67,6 +67,11 @@ class AsyncLLM:
                                      backend=args.comm_backend)
             if device is None and comm.device is not None:
                 device = str(comm.device)
+        elif comm is None and args.pipeline_parallel_size > 1:
+            from ..parallel.pipeline import init_pipeline
+            comm = init_pipeline(args.pipeline_parallel_size, device)
+            if device is None and comm.device is not None:
+                device = str(comm.device)
         return cls(LLMEngine.from_engine_args(args, device=device, comm=comm))
 
     @property

@@ -193,10 +193,14 @@ class KVCacheTensors:
     """Device memory of the cache: one (K, V) pair per layer."""
 
     def __init__(self, num_layers: int, num_blocks: int, local_kv_heads: int, block_size: int,
-                 head_dim: int, dtype: torch.dtype, device):
+                 head_dim: int, dtype: torch.dtype, device, layers: Optional[range] = None):
+        """``layers``: the layers this rank runs (a pipeline stage); the others get no memory."""
         self.shape = (num_blocks, local_kv_heads, block_size, head_dim)
-        self.k = [torch.zeros(self.shape, dtype=dtype, device=device) for _ in range(num_layers)]
-        self.v = [torch.zeros(self.shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        own = range(num_layers) if layers is None else layers
+        self.k = [torch.zeros(self.shape, dtype=dtype, device=device) if l in own else None
+                  for l in range(num_layers)]
+        self.v = [torch.zeros(self.shape, dtype=dtype, device=device) if l in own else None
+                  for l in range(num_layers)]
         self._tables: dict = {}
 
     def pointer_tables(self, first: int, count: int):

@@ -30,6 +30,11 @@ class LLM:
                                      backend=self.engine_args.comm_backend)
             if device is None and comm.device is not None:
                 device = str(comm.device)
+        elif comm is None and self.engine_args.pipeline_parallel_size > 1:
+            from ..parallel.pipeline import init_pipeline
+            comm = init_pipeline(self.engine_args.pipeline_parallel_size, device)
+            if device is None and comm.device is not None:
+                device = str(comm.device)
         self.engine = LLMEngine.from_engine_args(self.engine_args, device=device, comm=comm)
 
     def get_tokenizer(self):

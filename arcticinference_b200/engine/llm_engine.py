@@ -57,6 +57,9 @@ class LLMEngine:
                        sp * m.h * m.D, swiftkv=config.model.is_swiftkv)
         self.runner.load_model()
         self.num_blocks = self.runner.determine_num_blocks()
+        if self.runner.pp is not None:
+            # the stages hold different amounts of weights; their schedulers must see one pool size
+            self.num_blocks = self.runner.pp.min_over_stages(self.num_blocks, self.device)
         self.runner.init_kv_cache(self.num_blocks)
         self.kv_manager = KVCacheManager(self.num_blocks, config.cache.block_size,
                                          config.cache.enable_prefix_caching)
@@ -105,6 +108,10 @@ class LLMEngine:
         if request_id is None:
             request_id = "req-%d" % self._seq
         self._seq += 1
+        if self.runner.pp is not None and (params.logprobs is not None or
+                                           params.prompt_logprobs is not None):
+            raise NotImplementedError("log-probabilities with pipeline parallelism (the logits "
+                                      "exist on the last stage only)")
         text = None
         if isinstance(prompt, str):
             text = prompt

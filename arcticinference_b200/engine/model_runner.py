@@ -120,6 +120,10 @@ class ModelRunner:
         self.shard = shard or ShardSpec()
         mcfg = config.model
         self.model = LlamaForCausalLM(mcfg, self.shard, self.device, torch.bfloat16, comm=comm)
+        # a pipeline stage (parallel/pipeline.py): the communicator is then the stage's handle
+        self.pp = comm if getattr(comm, "stages", 1) > 1 else None
+        if self.pp is not None:
+            self.model.set_pipeline(self.pp)
         self.kv: Optional[KVCacheTensors] = None
         self.num_blocks = 0
         self.block_size = config.cache.block_size
@@ -169,7 +173,7 @@ class ModelRunner:
     def determine_num_blocks(self) -> int:
         cfg = self.config
         m = self.model
-        per_block = KVCacheTensors.bytes_per_block(cfg.model.num_hidden_layers, m.hkv,
+        per_block = KVCacheTensors.bytes_per_block(m.layer_hi - m.layer_lo, m.hkv,
                                                    self.block_size, m.D)
         if cfg.cache.num_gpu_blocks is not None:
             return cfg.cache.num_gpu_blocks
@@ -191,7 +195,8 @@ class ModelRunner:
         m = self.model
         self.num_blocks = num_blocks
         self.kv = KVCacheTensors(self.config.model.num_hidden_layers, num_blocks, m.hkv,
-                                 self.block_size, m.D, torch.bfloat16, self.device)
+                                 self.block_size, m.D, torch.bfloat16, self.device,
+                                 layers=range(m.layer_lo, m.layer_hi) if self.pp else None)
 
     # ------------------------------------------------------------- mode choice
     def choose_mode(self, total_tokens: int) -> str:
@@ -402,8 +407,8 @@ class ModelRunner:
 
     def _decode_graph(self, out: SchedulerOutput):
         """The captured graph for this step, or None when the step must run eagerly."""
-        if self.config.enforce_eager or self.device.type != "cuda":
-            return None
+        if self.config.enforce_eager or self.device.type != "cuda" or self.pp is not None:
+            return None      # (a pipeline stage's step contains point-to-point transfers)
         fc = self.config.forest_cascade
         if fc.enabled and len(out.scheduled) >= fc.min_batch_size:
             return None  # cascade steps plan their own attention work list
@@ -504,6 +509,13 @@ class ModelRunner:
                 return PendingStep(out, rows, None, None, batch.num_tokens, batch.mode)
             with trace_range("forward", tokens=batch.num_tokens, mode=batch.mode):
                 hidden = self.model.forward(batch, self.kv)
+            if self.pp is not None and hidden is None:
+                # an earlier pipeline stage: the last stage samples and sends the ids to all
+                if batch.prompt_rows:
+                    raise NotImplementedError("prompt log-probabilities with pipeline parallelism")
+                ids_dev = self.pp.broadcast_ids(None, batch.num_sampled, self.device)
+                pend = PendingStep(out, rows, ids_dev, None, batch.num_tokens, batch.mode)
+                return self._after_launch(pend, out, rows)
             with trace_range("sample"):
                 logits = self.model.compute_logits(hidden, fp32=self.config.fp32_lm_head)
                 self._step_logprobs = None
@@ -519,6 +531,8 @@ class ModelRunner:
                     logits = logits[:n_s]
                 ids_dev = self._sample(logits, out.scheduled, rows, gathered) \
                     if logits.shape[0] else None
+                if self.pp is not None and ids_dev is not None:
+                    ids_dev = self.pp.broadcast_ids(ids_dev.contiguous(), ids_dev.numel(), self.device)
             pend = PendingStep(out, rows, ids_dev, hidden, batch.num_tokens, batch.mode)
             pend.logprobs, self._step_logprobs = self._step_logprobs, None
             input_sel = None
@@ -526,6 +540,11 @@ class ModelRunner:
                 input_sel = batch.input_ids[batch.logits_indices[:batch.num_sampled]]
             if prompt_lp is not None:
                 pend.prompt_logprobs = (prompt_lp, batch.prompt_rows)
+        return self._after_launch(pend, out, rows, input_sel)
+
+    def _after_launch(self, pend, out, rows, input_sel=None):
+        """Start the step's tokens on their way to the host (and, with a speculator, verify
+        and draft on the device)."""
         # the device result may be overwritten by the next replay of the same graph: take the
         # host copy now, read it in finish()
         if self.device.type == "cuda" and pend.ids_dev is not None:

@@ -18,6 +18,8 @@ def _model_tensors(engine):
     m = engine.runner.model
     items = [(m, "embed"), (m, "norm"), (m, "lm_head"), (m, "norm_swiftkv"), (m, "wkv_swiftkv")]
     for lw in m.layers:
+        if lw is None:
+            continue
         for name in ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown"):
             items.append((lw, name))
         for key in list(lw.extra):

@@ -123,6 +123,16 @@ class LlamaModel:
         # fp8 weights with per-token activation scales: the norm and SiLU kernels that feed the
         # linear layers emit quantised rows directly (set by quantize_model_fp8)
         self.act_quant = False
+        # pipeline parallelism (parallel/pipeline.py): this rank keeps the layers
+        # [layer_lo, layer_hi) only; embedding on the first stage, norm + LM head on the last
+        self.pp = None
+        self.layer_lo, self.layer_hi = 0, cfg.num_hidden_layers
+
+    def set_pipeline(self, pp) -> None:
+        if self.cfg.is_swiftkv:
+            raise NotImplementedError("pipeline parallelism with SwiftKV models")
+        self.pp = pp
+        self.layer_lo, self.layer_hi = pp.layer_range(self.cfg.num_hidden_layers)
 
     # ------------------------------------------------------------------ weights
     def kv_head_of_block(self, p: int) -> range:
@@ -150,6 +160,8 @@ class LlamaModel:
         if self.lm_head is not self.embed:
             n += self.lm_head.numel()
         for lw in self.layers:
+            if lw is None:
+                continue
             n += sum(t.numel() for t in (lw.input_norm, lw.post_norm, lw.wqkv, lw.wo, lw.wgu,
                                          lw.wdown))
         if self.wkv_swiftkv is not None:
@@ -164,6 +176,8 @@ class LlamaModel:
             yield "norm_swiftkv", self.norm_swiftkv
             yield "wkv_swiftkv", self.wkv_swiftkv
         for i, lw in enumerate(self.layers):
+            if lw is None:
+                continue
             for name in ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown"):
                 yield "layers.%d.%s" % (i, name), getattr(lw, name)
 
@@ -324,6 +338,22 @@ class LlamaForCausalLM(LlamaModel):
             comm.begin_forward()
         if mode == "sp" and comm is not None and comm.sp > 1:
             ids = comm.local_token_slice(ids)  # contiguous N/SP slice of this rank
+        pp = self.pp
+        if pp is not None:
+            # one stage of the pipeline: take the stream from the stage before, run the local
+            # layers, hand it on; only the last stage has logits to offer
+            if pp.is_first:
+                h, residual = ops.embedding(ids, self.embed), None
+            else:
+                h, residual = pp.recv_hidden(ids.numel(), cfg.hidden_size, self.dtype, self.device)
+            h, residual = self._run_layers(self.layer_lo, self.layer_hi, h, residual, batch, kv,
+                                           mode, batch.attn_meta, positions, slots)
+            if not pp.is_last:
+                pp.send_hidden(h, residual)
+                return None
+            h = ops.gather_rows(h, batch.logits_indices)
+            residual = ops.gather_rows(residual, batch.logits_indices)
+            return ops.rmsnorm(h, self.norm, eps, residual=residual)
         h = ops.embedding(ids, self.embed)
         h, residual = self._run_layers(0, self.n_kv_layers, h, None, batch, kv, mode,
                                        batch.attn_meta, positions, slots)

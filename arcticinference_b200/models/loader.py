@@ -158,6 +158,8 @@ def load_llama_state(model, state: Iterable) -> None:
             l, key = int(m.group(1)), m.group(2)
             if l >= cfg.num_hidden_layers:
                 return
+            if not (getattr(model, "layer_lo", 0) <= l < getattr(model, "layer_hi", l + 1)):
+                return      # another pipeline stage's layer
             d = pending.setdefault(l, {})
             d[key] = tensor
             if all(r in d for r in _required(model, l)):
@@ -184,7 +186,8 @@ def load_llama_state(model, state: Iterable) -> None:
             continue
         deliver(name, tensor)
 
-    missing = [l for l, lw in enumerate(model.layers) if lw is None]
+    lo, hi = getattr(model, "layer_lo", 0), getattr(model, "layer_hi", cfg.num_hidden_layers)
+    missing = [l for l, lw in enumerate(model.layers) if lw is None and lo <= l < hi]
     if missing or model.embed is None or model.norm is None:
         raise ValueError("checkpoint is incomplete: layers %s, embed=%s, norm=%s" %
                          (missing[:8], model.embed is not None, model.norm is not None))

@@ -248,6 +248,8 @@ SHADOW_MAX_FRACTION = 0.2     # of the device's memory
 def model_fp8_weights(model) -> list:
     out = []
     for lw in model.layers:
+        if lw is None:
+            continue
         for name in ("wqkv", "wo", "wgu", "wdown"):
             w = getattr(lw, name)
             if isinstance(w, Fp8Weight):
@@ -281,6 +283,8 @@ def quantize_model_fp8(model, prefill_shadow="auto", scheme: str = "channel") ->
         return quantize_weight_fp8_row(w, tiled=tiled)
 
     for lw in model.layers:
+        if lw is None:          # another pipeline stage's layer
+            continue
         for name in ("wqkv", "wo", "wgu", "wdown"):
             w = getattr(lw, name)
             if isinstance(w, torch.Tensor):

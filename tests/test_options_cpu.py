@@ -102,8 +102,9 @@ def test_abort_reaches_every_sample_of_a_parallel_request():
 
 def test_options_that_cannot_be_honoured_are_refused():
     import pytest
-    for kw in (dict(pipeline_parallel_size=2), dict(enable_expert_parallel=True),
-               dict(kv_cache_dtype="nvfp4")):
+    for kw in (dict(pipeline_parallel_size=2, tensor_parallel_size=2),
+               dict(enable_expert_parallel=True), dict(kv_cache_dtype="nvfp4")):
         with pytest.raises(NotImplementedError):
             EngineArgs(model="llama-tiny", **kw).create_engine_config()
     EngineArgs(model="llama-tiny", kv_cache_dtype="auto").create_engine_config()
+    EngineArgs(model="llama-tiny", pipeline_parallel_size=2).create_engine_config()   # whole-model stages

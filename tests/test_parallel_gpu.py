@@ -248,3 +248,50 @@ def test_fused_serving_steps_call_no_library_collective(model):
     assert first >= len(toks) - 1, (toks, want)
     same = sum(int(a == b) for t, w in zip(toks, want) for a, b in zip(t, w))
     assert same >= 0.5 * sum(len(t) for t in toks), (toks, want)
+
+
+def _pipeline_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    sys.path.insert(0, ROOT)
+    torch.cuda.set_device(rank)
+    from arcticinference_b200 import LLM, SamplingParams, ops
+    kw = dict(model="llama-small", num_gpu_blocks_override=128, block_size=16, max_model_len=1024,
+              quantization="fp8")
+    llm = LLM(pipeline_parallel_size=world, **kw)
+    sp = SamplingParams(temperature=0, max_tokens=8, ignore_eos=True)
+    prompts = [{"prompt_token_ids": p} for p in PROMPTS]
+    toks = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    ops.check_status()
+    m = llm.engine.runner.model
+    layers = [i for i, lw in enumerate(m.layers) if lw is not None]
+    if rank == 0:
+        ref = LLM(device="cuda:0", **kw)
+        want = [o.outputs[0].token_ids for o in ref.generate(prompts, sp)]
+        q.put((toks, want, layers, len(m.layers)))
+    import torch.distributed as dist
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_pipeline_stages_match_single_gpu():
+    """Whole-model pipeline stages over NCCL point-to-point transfers: the same kernels on the
+    same inputs as the one-GPU engine, so the greedy tokens agree; each stage keeps its own
+    layers only."""
+    world = min(_world(), 2)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pipeline_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    toks, want, layers, total = _result_or_child_failure(q, procs, 600)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert layers == list(range(len(layers))) and 0 < len(layers) < total
+    assert [t[0] for t in toks] == [t[0] for t in want], (toks, want)
+    same = sum(int(a == b) for t, w in zip(toks, want) for a, b in zip(t, w))
+    assert same >= 0.75 * sum(len(t) for t in toks), (toks, want)
