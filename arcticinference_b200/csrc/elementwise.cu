@@ -511,13 +511,17 @@ int ab200_rmsnorm(const void* x, long long ldx, void* residual, const void* weig
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) |
                          reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (aligned && hidden == 8 * kNormThreads)
-    (void)launch_pdl(rmsnorm_fixed_kernel<1>, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, eps);
+    (void)launch_pdl(rmsnorm_fixed_kernel<1>, dim3((unsigned)T), dim3(kNormThreads), 0, stream,
+                     xp, ldx, rp, wp, yp, ldy, eps);
   else if (aligned && hidden == 16 * kNormThreads)
-    (void)launch_pdl(rmsnorm_fixed_kernel<2>, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, eps);
+    (void)launch_pdl(rmsnorm_fixed_kernel<2>, dim3((unsigned)T), dim3(kNormThreads), 0, stream,
+                     xp, ldx, rp, wp, yp, ldy, eps);
   else if (aligned && hidden == 32 * kNormThreads)
-    (void)launch_pdl(rmsnorm_fixed_kernel<4>, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, eps);
+    (void)launch_pdl(rmsnorm_fixed_kernel<4>, dim3((unsigned)T), dim3(kNormThreads), 0, stream,
+                     xp, ldx, rp, wp, yp, ldy, eps);
   else
-    (void)launch_pdl(rmsnorm_kernel, dim3((unsigned)T), dim3(kNormThreads), 0, stream, xp, ldx, rp, wp, yp, ldy, hidden, eps);
+    (void)launch_pdl(rmsnorm_kernel, dim3((unsigned)T), dim3(kNormThreads), 0, stream,
+                     xp, ldx, rp, wp, yp, ldy, hidden, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -539,7 +543,8 @@ int ab200_silu_mul(const void* x, void* out, long long T, int inter, int nblk,
   const long long total = T * nblk * (inter / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  (void)launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, reinterpret_cast<const bf16*>(x),
+  (void)launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
+                   reinterpret_cast<const bf16*>(x),
                                                         reinterpret_cast<bf16*>(out), T, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

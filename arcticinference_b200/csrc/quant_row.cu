@@ -326,15 +326,20 @@ int ab200_quant_fp8_row_wait(const void* x, long long ldx, void* xq, long long l
   float* sp = reinterpret_cast<float*>(sx);
   const int nvec = K / 8;
   if (nvec <= 256)
-    (void)launch_pdl(quant_fp8_row_kernel<1>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<1>, dim3((unsigned)M), dim3(256), 0, stream,
+                     xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 512)
-    (void)launch_pdl(quant_fp8_row_kernel<2>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<2>, dim3((unsigned)M), dim3(256), 0, stream,
+                     xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 1024)
-    (void)launch_pdl(quant_fp8_row_kernel<4>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<4>, dim3((unsigned)M), dim3(256), 0, stream,
+                     xp, ldx, qp, ldq, sp, K, w, status);
   else if (nvec <= 2048)
-    (void)launch_pdl(quant_fp8_row_kernel<8>, dim3((unsigned)M), dim3(256), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<8>, dim3((unsigned)M), dim3(256), 0, stream,
+                     xp, ldx, qp, ldq, sp, K, w, status);
   else
-    (void)launch_pdl(quant_fp8_row_kernel<8>, dim3((unsigned)M), dim3(512), 0, stream, xp, ldx, qp, ldq, sp, K, w, status);
+    (void)launch_pdl(quant_fp8_row_kernel<8>, dim3((unsigned)M), dim3(512), 0, stream,
+                     xp, ldx, qp, ldq, sp, K, w, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -353,9 +358,9 @@ int ab200_rmsnorm_quant(const void* x, long long ldx, void* residual, const void
   float* sp = reinterpret_cast<float*>(sy);
   bf16* yp = reinterpret_cast<bf16*>(y);
   const int nvec = hidden / 8;
-#define AB200_LAUNCH_NQ(V)                                                                     \
-  (void)launch_pdl(rmsnorm_quant_kernel<V>, dim3((unsigned)T), dim3(kQThreads), 0, stream, xp, ldx, rp, wp, qp, ldq, sp, \
-                                                                 yp, ldy, hidden, eps)
+#define AB200_LAUNCH_NQ(V)                                                                   \
+  (void)launch_pdl(rmsnorm_quant_kernel<V>, dim3((unsigned)T), dim3(kQThreads), 0, stream, xp, \
+                   ldx, rp, wp, qp, ldq, sp, yp, ldy, hidden, eps)
   if (nvec <= 256) AB200_LAUNCH_NQ(1);
   else if (nvec <= 512) AB200_LAUNCH_NQ(2);
   else if (nvec <= 1024) AB200_LAUNCH_NQ(4);
@@ -385,7 +390,8 @@ int ab200_silu_mul_quant(const void* x, void* outq, long long ldq, void* so, lon
       return -3;
     attr_set[dev] = true;
   }
-  (void)launch_pdl(silu_mul_quant_kernel, dim3((unsigned)T), dim3(kSiluQThreads), smem, stream, xp, qp, ldq, sp, inter, nblk);
+  (void)launch_pdl(silu_mul_quant_kernel, dim3((unsigned)T), dim3(kSiluQThreads), smem, stream,
+                   xp, qp, ldq, sp, inter, nblk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
