@@ -18,7 +18,6 @@ steps use those sizes times SP so that the per-rank shapes stay canonical.
 
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from .. import ops

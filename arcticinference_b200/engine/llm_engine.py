@@ -18,7 +18,7 @@ from ..utils.tokenizer import get_tokenizer
 from .kv_cache import KVCacheManager
 from .model_runner import ModelRunner
 from .outputs import CompletionOutput, RequestOutput
-from .request import Request, RequestStatus, StopStringMatcher
+from .request import Request, StopStringMatcher
 from .sampling_params import SamplingParams
 from .scheduler import Scheduler
 

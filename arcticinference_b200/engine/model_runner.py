@@ -15,7 +15,6 @@ same paged KV cache.
 
 from __future__ import annotations
 
-import math
 import time
 from dataclasses import dataclass
 from typing import Optional

@@ -19,7 +19,7 @@ from typing import Any, Optional, Union
 
 from fastapi import FastAPI, HTTPException, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
-from pydantic import BaseModel, Field
+from pydantic import BaseModel
 
 from ..engine.async_llm import AsyncLLM
 from ..engine.sampling_params import SamplingParams

@@ -19,7 +19,6 @@ Packing turns the per-projection matrices into the rank-major fused layout of
 from __future__ import annotations
 
 import glob
-import json
 import os
 import re
 from typing import Iterable, Iterator

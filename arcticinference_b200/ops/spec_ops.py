@@ -4,7 +4,6 @@ restatements below, which are also the test oracles."""
 
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn.functional as F

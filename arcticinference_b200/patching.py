@@ -15,7 +15,6 @@ so ``cls`` is the class they are called on), records the origin of each attribut
 
 from __future__ import annotations
 
-from types import MethodType
 from typing import Generic, TypeVar
 
 T = TypeVar("T")

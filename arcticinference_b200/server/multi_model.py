@@ -13,7 +13,7 @@ from __future__ import annotations
 import asyncio
 import logging
 import uuid
-from typing import Any, Callable, Optional
+from typing import Callable, Optional
 
 from .config import ServerModelConfig
 from .replica_pool import GpuAllocator, ReplicaPool

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import asyncio
 import logging
-from typing import Any, Awaitable, Callable, Iterable, Optional
+from typing import Awaitable, Callable, Iterable, Optional
 
 logger = logging.getLogger(__name__)
 

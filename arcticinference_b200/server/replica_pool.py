@@ -13,11 +13,11 @@ from __future__ import annotations
 import asyncio
 import logging
 import time
-from typing import Any, Callable, Optional
+from typing import Callable, Optional
 
 from .config import ServerModelConfig
 from .scheduler import Scheduler, prefix_affinity_routing, utilization_based_concurrency
-from .worker import ProcessWorker, WorkerStatus
+from .worker import ProcessWorker
 
 logger = logging.getLogger(__name__)
 

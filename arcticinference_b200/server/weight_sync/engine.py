@@ -28,7 +28,7 @@ from typing import Callable, Iterator, Optional
 import torch
 import torch.distributed as dist
 
-from .schedule import TensorMeta, TransferSchedule, dtype_from_name
+from .schedule import TransferSchedule, dtype_from_name
 
 logger = logging.getLogger(__name__)
 
