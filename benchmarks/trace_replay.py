@@ -8,7 +8,8 @@ serve.py:101-116, datasets.py:353-373). ``--synthetic N`` generates one instead:
 arrivals at ``--rate`` requests/s, log-normal prompt lengths, fixed output length.
 
 Targets:
-    --base-url http://host:port     an OpenAI-compatible server (streaming completions)
+    --base-url http://host:port     an OpenAI-compatible server (streaming completions);
+                                    several, comma-separated: least requests in flight
     --in-process MODEL [--engine-arg k=v ...]   an engine inside this process
 
     python benchmarks/trace_replay.py --in-process llama-3.1-8b --synthetic 256 --rate 8 \
@@ -105,9 +106,15 @@ class InProcessTarget:
 
 
 class HttpTarget:
+    """An OpenAI-compatible server, or several behind a comma-separated ``base_url``: each
+    request then goes to the server with the fewest requests of this client in flight (the
+    independent-replicas layout of a parallelism comparison)."""
+
     def __init__(self, base_url: str, model: str, vocab: int):
         import aiohttp
-        self.base = base_url.rstrip("/")
+        self.bases = [u.strip().rstrip("/") for u in base_url.split(",") if u.strip()]
+        self.inflight = [0] * len(self.bases)
+        self.sent = [0] * len(self.bases)
         self.model = model
         self.vocab = vocab
         self.session = None
@@ -119,21 +126,27 @@ class HttpTarget:
                 timeout=self._aiohttp.ClientTimeout(total=None))
         body = {"model": self.model, "prompt": prompt, "max_tokens": req.output_len,
                 "temperature": 0.0, "ignore_eos": True, "stream": True}
+        which = min(range(len(self.bases)), key=lambda i: (self.inflight[i], self.sent[i]))
+        self.inflight[which] += 1
+        self.sent[which] += 1
         t0 = time.perf_counter()
         first = None
         n = 0
-        async with self.session.post(self.base + "/v1/completions", json=body) as resp:
-            if resp.status != 200:
-                req.error = "HTTP %d" % resp.status
-                return
-            async for raw in resp.content:
-                if not raw.startswith(b"data: {"):
-                    continue
-                obj = json.loads(raw[6:])
-                if obj.get("usage"):
-                    n = obj["usage"]["completion_tokens"]
-                if first is None and any(c.get("text") for c in obj.get("choices", [])):
-                    first = time.perf_counter()
+        try:
+            async with self.session.post(self.bases[which] + "/v1/completions", json=body) as resp:
+                if resp.status != 200:
+                    req.error = "HTTP %d" % resp.status
+                    return
+                async for raw in resp.content:
+                    if not raw.startswith(b"data: {"):
+                        continue
+                    obj = json.loads(raw[6:])
+                    if obj.get("usage"):
+                        n = obj["usage"]["completion_tokens"]
+                    if first is None and any(c.get("text") for c in obj.get("choices", [])):
+                        first = time.perf_counter()
+        finally:
+            self.inflight[which] -= 1
         finish(req, t0, first, time.perf_counter(), n or req.output_len)
 
     def close(self) -> None:

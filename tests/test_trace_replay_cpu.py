@@ -58,10 +58,52 @@ def test_replay_over_http():
         time.sleep(0.05)
     try:
         res = tr.main(["--synthetic", "4", "--rate", "100", "--median-input", "10", "--sigma", "0.1",
-                       "--output-len", "4", "--base-url", "http://127.0.0.1:18441", "--model", "tiny",
+                       "--output-len", "4", "--model", "tiny",
+                       # two "replicas" (the same server under two spellings): least in flight
+                       "--base-url", "http://127.0.0.1:18441, http://localhost:18441/",
                        "--vocab-size", "1000"])
         assert res["completed"] == 4 and res["output_tokens"] == 16 and res["p50_ttft_ms"] > 0
     finally:
         srv.should_exit = True
         th.join(5)
         llm.shutdown()
+
+
+def test_trace_tools_convert_inspect_summarize(tmp_path):
+    import trace_tools as tt
+    src = tmp_path / "t.csv"
+    with open(src, "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["TIMESTAMP", "ContextTokens", "GeneratedTokens"])
+        w.writerow(["2023-11-16 18:15:46.6805900", 374, 44])       # 7 fractional digits
+        w.writerow(["2023-11-16 18:15:50.9951690", 396, 109])
+        w.writerow(["2023-11-16 18:15:50.9951690", 879, 55])       # arrives with the one before
+        w.writerow(["2023-11-16 18:16:51", 1000, 0])               # generates nothing: dropped
+        w.writerow(["2023-11-16 18:17:46.680590", 91, 7])          # exactly 2 minutes in
+        w.writerow(["2023-11-16 18:30:00.0", 5, 5])                # outside the window
+    assert tt.parse_timestamp("2023-11-16 18:15:46.6805900").microsecond == 680590
+    dst = tmp_path / "t.jsonl"
+    res = tt.main(["convert", str(src), str(dst), "--from-min", "0.05", "--to-min", "2"])
+    assert res["written"] == 3
+    recs = tt.read_records(str(dst))
+    # re-based to the first kept request (the 4.3 s one)
+    assert [r["timestamp"] for r in recs] == [0.0, 0.0, 115685.0]
+    assert [r["input_length"] for r in recs] == [396, 879, 91]
+    assert tr.load_trace(str(dst))[2].output_len == 7              # the replay reads it
+
+    info = tt.main(["inspect", str(dst), "--window-s", "60", "--groups"])
+    assert info["requests"] == 3 and info["arrival_groups"] == 2
+    assert info["largest_group"] == 2 and info["largest_group_prompt_tokens"] == 396 + 879
+    assert info["total_output_tokens"] == 109 + 55 + 7
+    assert info["peak_rate_per_s"] == pytest.approx(2 / 60)
+    assert tt.request_rate(recs, 60.0) == [(0.0, pytest.approx(2 / 60)), (60.0, pytest.approx(1 / 60))]
+
+    rep = tmp_path / "r.csv"
+    reqs = [tr.TraceRequest(0, 0.0, 10, 5, 20.0, 2.0, 28.0), tr.TraceRequest(1, 100.0, 30, 5, 40.0, 4.0, 56.0),
+            tr.TraceRequest(2, 200.0, 30, 5)]                      # one that failed
+    tr.write_csv(reqs, str(rep))
+    summ = tt.main(["summarize", str(rep)])
+    assert summ["requests"] == 3 and summ["completed"] == 2
+    assert summ["ttft_ms"]["p50"] == pytest.approx(30.0) and summ["tpot_ms"]["max"] == 4.0
+    assert summ["duration_s"] == pytest.approx(0.156)
+    assert summ["combined_tokens_per_s"] == pytest.approx(50 / 0.156)
