@@ -32,7 +32,8 @@ SHIFT_PARALLEL_THRESHOLD = 128
 
 @dataclass
 class ModelConfig:
-    """Architecture of a decoder (Llama family, optionally SwiftKV) or encoder (BERT)."""
+    """Architecture of a decoder (Llama, Mistral and Qwen3 dense models, optionally SwiftKV for
+    Llama) or encoder (BERT)."""
 
     architecture: str = "LlamaForCausalLM"
     model_type: str = "llama"
@@ -51,6 +52,8 @@ class ModelConfig:
     # SwiftKV: layers >= num_key_value_layers take K/V from a projection of the hidden
     # state after layer num_key_value_layers - 1 (None: plain Llama).
     num_key_value_layers: Optional[int] = None
+    # Qwen3: RMSNorm over head_dim on every query and key head before RoPE
+    qk_norm: bool = False
     # encoder-only fields
     type_vocab_size: int = 2
     layer_norm_eps: float = 1e-12
@@ -85,6 +88,8 @@ class ModelConfig:
             raise ValueError("quantization must be None or 'fp8'")
         if self.fp8_scheme not in ("channel", "block"):
             raise ValueError("fp8_scheme must be 'channel' or 'block'")
+        if self.qk_norm and self.is_swiftkv:
+            raise NotImplementedError("SwiftKV with per-head query / key norms")
 
     @classmethod
     def from_hf_dict(cls, d: dict, name_or_path: str = "") -> "ModelConfig":
@@ -95,6 +100,21 @@ class ModelConfig:
         eos = d.get("eos_token_id")
         if isinstance(eos, list):
             eos = eos[0] if eos else None
+        if mt not in DECODER_MODEL_TYPES and mt != "bert":
+            raise NotImplementedError("model_type %r (supported: %s, bert)" %
+                                      (mt, ", ".join(DECODER_MODEL_TYPES)))
+        if d.get("attention_bias") or d.get("mlp_bias"):
+            raise NotImplementedError("linear layers with bias (attention_bias / mlp_bias)")
+        window = d.get("sliding_window") if d.get("use_sliding_window", True) else None
+        if window is not None and window < d.get("max_position_embeddings", 4096):
+            raise NotImplementedError("sliding-window attention (sliding_window=%d)" % window)
+        # transformers >= 5 writes one ``rope_parameters`` dict (theta, type and the scaling
+        # fields together); older checkpoints have ``rope_theta`` beside ``rope_scaling``
+        rope = d.get("rope_parameters") or {}
+        theta = d.get("rope_theta", rope.get("rope_theta", 10000.0))
+        scaling = d.get("rope_scaling")
+        if scaling is None and rope.get("rope_type", rope.get("type", "default")) != "default":
+            scaling = {k: v for k, v in rope.items() if k != "rope_theta"}
         cfg = cls(
             architecture=archs[0], model_type=mt, hidden_size=hidden,
             num_hidden_layers=d.get("num_hidden_layers", 32), num_attention_heads=heads,
@@ -103,10 +123,11 @@ class ModelConfig:
             intermediate_size=d.get("intermediate_size", 4 * hidden),
             vocab_size=d.get("vocab_size", 32000),
             rms_norm_eps=d.get("rms_norm_eps", 1e-5),
-            rope_theta=d.get("rope_theta", 10000.0), rope_scaling=d.get("rope_scaling"),
+            rope_theta=theta, rope_scaling=scaling,
             max_position_embeddings=d.get("max_position_embeddings", 4096),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             num_key_value_layers=d.get("num_key_value_layers"),
+            qk_norm=(mt == "qwen3"),
             type_vocab_size=d.get("type_vocab_size", 2),
             layer_norm_eps=d.get("layer_norm_eps", 1e-12),
             hidden_act=d.get("hidden_act", "silu"),
@@ -125,6 +146,12 @@ class ModelConfig:
             return dataclasses.replace(PRESETS[path], name_or_path=path)
         with open(os.path.join(path, "config.json")) as f:
             return cls.from_hf_dict(json.load(f), path)
+
+
+# decoder families the Llama code path serves: Mistral is Llama under another name once its
+# sliding window is off; Qwen3 (dense) adds the per-head query / key norms and a head_dim that
+# is not hidden_size / heads
+DECODER_MODEL_TYPES = ("llama", "llama_swiftkv", "mistral", "qwen3")
 
 
 def _llama(layers, hidden, heads, kv, inter, **kw) -> ModelConfig:
@@ -154,6 +181,20 @@ PRESETS: dict[str, ModelConfig] = {
                                       rope_theta=10000.0, num_key_value_layers=2,
                                       model_type="llama_swiftkv",
                                       architecture="LlamaSwiftKVForCausalLM"),
+    "mistral-7b": _llama(32, 4096, 32, 8, 14336, architecture="MistralForCausalLM",
+                         model_type="mistral", vocab_size=32768, rope_theta=1000000.0,
+                         max_position_embeddings=32768),
+    "qwen3-8b": _llama(36, 4096, 32, 8, 12288, architecture="Qwen3ForCausalLM",
+                       model_type="qwen3", qk_norm=True, vocab_size=151936, rope_theta=1000000.0,
+                       rms_norm_eps=1e-6, max_position_embeddings=40960),
+    "qwen3-32b": _llama(64, 5120, 64, 8, 25600, architecture="Qwen3ForCausalLM",
+                        model_type="qwen3", qk_norm=True, vocab_size=151936, rope_theta=1000000.0,
+                        rms_norm_eps=1e-6, max_position_embeddings=40960),
+    "qwen3-tiny": ModelConfig(architecture="Qwen3ForCausalLM", model_type="qwen3", qk_norm=True,
+                              hidden_size=256, num_hidden_layers=2, num_attention_heads=8,
+                              num_key_value_heads=2, head_dim=64, intermediate_size=512,
+                              vocab_size=1024, max_position_embeddings=4096, rope_theta=10000.0,
+                              rms_norm_eps=1e-6),
     "llama-small": ModelConfig(hidden_size=1024, num_hidden_layers=4, num_attention_heads=8,
                                num_key_value_heads=8, head_dim=128, intermediate_size=2816,
                                vocab_size=32000, max_position_embeddings=8192),
@@ -544,7 +585,10 @@ class EngineArgs:
             model.quantization = self.quantization
         if self.fp8_scheme is not None:
             model.fp8_scheme = self.fp8_scheme
-        model.dtype = self.dtype
+        if self.dtype not in ("auto", "bfloat16", "bf16"):
+            raise NotImplementedError("dtype=%r: weights, activations and the KV cache are "
+                                      "bfloat16 (the kernels accumulate in fp32)" % self.dtype)
+        model.dtype = "bfloat16"
         max_len = self.max_model_len or min(model.max_position_embeddings, 8192)
         parallel = ParallelConfig(
             tensor_parallel_size=self.tensor_parallel_size,

@@ -20,7 +20,7 @@ def _model_tensors(engine):
     for lw in m.layers:
         if lw is None:
             continue
-        for name in ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown"):
+        for name, _ in lw.tensors():
             items.append((lw, name))
         for key in list(lw.extra):
             items.append((lw.extra, key))

@@ -52,6 +52,9 @@ def compute_inv_freq(cfg: ModelConfig, device) -> torch.Tensor:
         inv = scaled
     elif rs and rs.get("rope_type", rs.get("type")) == "linear":
         inv = inv / rs["factor"]
+    elif rs and rs.get("rope_type", rs.get("type", "default")) != "default":
+        raise NotImplementedError("rope scaling of type %r (supported: llama3, linear)" %
+                                  rs.get("rope_type", rs.get("type")))
     return inv.float().to(device)
 
 
@@ -78,14 +81,25 @@ class ShardSpec:
         return range(self.tp_rank * self.sp, (self.tp_rank + 1) * self.sp)
 
 
+# per-layer tensors in the order every walk over a layer uses (q_norm / k_norm: Qwen3 only)
+LAYER_TENSORS = ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown", "q_norm", "k_norm")
+
+
 class LlamaLayerWeights:
-    __slots__ = ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown", "wq_swiftkv",
-                 "extra")
+    __slots__ = LAYER_TENSORS + ("wq_swiftkv", "extra")
 
     def __init__(self):
         self.input_norm = self.post_norm = self.wqkv = self.wo = self.wgu = self.wdown = None
+        self.q_norm = self.k_norm = None   # [head_dim] each, shared by all heads of the layer
         self.wq_swiftkv = None
         self.extra = {}
+
+    def tensors(self):
+        """(slot name, tensor) of every tensor this layer holds."""
+        for name in LAYER_TENSORS:
+            t = getattr(self, name)
+            if t is not None:
+                yield name, t
 
 
 class LlamaModel:
@@ -162,8 +176,7 @@ class LlamaModel:
         for lw in self.layers:
             if lw is None:
                 continue
-            n += sum(t.numel() for t in (lw.input_norm, lw.post_norm, lw.wqkv, lw.wo, lw.wgu,
-                                         lw.wdown))
+            n += sum(t.numel() for _, t in lw.tensors())
         if self.wkv_swiftkv is not None:
             n += self.wkv_swiftkv.numel() + self.norm_swiftkv.numel()
         return n
@@ -178,8 +191,8 @@ class LlamaModel:
         for i, lw in enumerate(self.layers):
             if lw is None:
                 continue
-            for name in ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown"):
-                yield "layers.%d.%s" % (i, name), getattr(lw, name)
+            for name, t in lw.tensors():
+                yield "layers.%d.%s" % (i, name), t
 
 
 @dataclass
@@ -252,6 +265,12 @@ class LlamaForCausalLM(LlamaModel):
             qkv = ops.linear(x, w)
         # rows that other ranks scattered into qkv: the first kernel that reads them waits
         wait = comm.take_wait("qkv") if (comm is not None and comm.fused) else None
+        if lw.q_norm is not None:
+            # Qwen3: every query and key head is normalised over head_dim before RoPE; as the
+            # first reader of rows that other ranks stored, this kernel takes the wait
+            ops.qk_norm(qkv, lw.q_norm, lw.k_norm, h, 0 if q_only else hkv, D,
+                        self.cfg.rms_norm_eps, sync=wait)
+            wait = None
         if q_only:
             ops.rope_cache(qkv, positions, None, self.inv_freq, kv.k[layer], kv.v[layer], h, 0, D,
                            sync=wait)

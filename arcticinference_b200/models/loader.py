@@ -3,8 +3,9 @@
 Accepted formats (reference: arctic_inference/vllm/swiftkv/llama_swiftkv.py:748-820,
 arctic_inference/vllm/spec_dec/fp8.py:140-180):
 
-* Hugging Face Llama safetensors (``q_proj/k_proj/v_proj/o_proj``,
-  ``gate_proj/up_proj/down_proj``, norms, ``embed_tokens``, ``lm_head``);
+* Hugging Face Llama / Mistral / Qwen3 safetensors (``q_proj/k_proj/v_proj/o_proj``,
+  ``gate_proj/up_proj/down_proj``, norms, ``embed_tokens``, ``lm_head``; for Qwen3 also
+  ``self_attn.q_norm`` and ``self_attn.k_norm``);
 * SwiftKV: ``model_type = llama_swiftkv``, ``num_key_value_layers`` and, for each layer
   >= num_key_value_layers, ``self_attn.{q,k,v}_proj_swiftkv`` plus ``model.norm_swiftkv``;
 * fp8 checkpoints: fp8 ``weight`` with a per-tensor / per-channel ``weight_scale`` or a
@@ -50,6 +51,9 @@ def random_llama_state(cfg, seed: int, std: float, device, dtype) -> Iterator:
         b = 100 + 20 * l
         yield p + "input_layernorm.weight", ones()
         yield p + "post_attention_layernorm.weight", ones()
+        if cfg.qk_norm:
+            yield p + "self_attn.q_norm.weight", (1.0 + 10 * rnd(b + 8, D).float()).to(dtype)
+            yield p + "self_attn.k_norm.weight", (1.0 + 10 * rnd(b + 9, D).float()).to(dtype)
         later = cfg.is_swiftkv and l >= cfg.num_key_value_layers
         sfx = "_swiftkv" if later else ""
         yield p + "self_attn.q_proj%s.weight" % sfx, rnd(b + 1, Hq * D, H)
@@ -76,10 +80,11 @@ def _expand_fp8(weight: torch.Tensor, scale: torch.Tensor, inverse_block: bool) 
 def _required(model, l: int) -> list[str]:
     later = model.cfg.is_swiftkv and l >= model.n_kv_layers
     sfx = "_swiftkv" if later else ""
+    norms = ["self_attn.q_norm.weight", "self_attn.k_norm.weight"] if model.cfg.qk_norm else []
     return ["input_layernorm.weight", "post_attention_layernorm.weight",
             "self_attn.q_proj%s.weight" % sfx, "self_attn.k_proj%s.weight" % sfx,
             "self_attn.v_proj%s.weight" % sfx, "self_attn.o_proj.weight",
-            "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"]
+            "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"] + norms
 
 
 def pack_llama_layer(model, l: int, t: dict) -> None:
@@ -111,6 +116,9 @@ def pack_llama_layer(model, l: int, t: dict) -> None:
     lw.wdown = to(t["mlp.down_proj.weight"][:, p0 * Ib:(p0 + n) * Ib]).contiguous()
     lw.input_norm = to(t["input_layernorm.weight"]).contiguous()
     lw.post_norm = to(t["post_attention_layernorm.weight"]).contiguous()
+    if model.cfg.qk_norm:
+        lw.q_norm = to(t["self_attn.q_norm.weight"]).contiguous()
+        lw.k_norm = to(t["self_attn.k_norm.weight"]).contiguous()
     model.layers[l] = lw
     if later:
         n_later = model.cfg.num_hidden_layers - model.n_kv_layers
@@ -286,8 +294,8 @@ class LlamaWeightUpdater:
         finally:
             m.wkv_swiftkv = real_wkv
         new = m.layers[l]
-        for slot in ("wqkv", "wo", "wgu", "wdown", "input_norm", "post_norm"):
-            assign_in_place(getattr(old, slot), getattr(new, slot))
+        for slot, tensor in new.tensors():
+            assign_in_place(getattr(old, slot), tensor)
         m.layers[l] = old
         self.layers_done.add(l)
 

@@ -546,6 +546,25 @@ def rope_cache(qkv, positions, slots, inv_freq, k_cache, v_cache, Hq, Hkv, D, ro
     launch_counter.add(1)
 
 
+def qk_norm(qkv, wq, wk, Hq, Hkv, D, eps: float, sync=None):
+    """In-place RMSNorm over head_dim of the ``Hq`` query and ``Hkv`` key heads of every row of
+    ``qkv`` [T, (Hq + 2*Hkv) * D] (the value heads stay as they are); ``wq`` / ``wk`` [D] are
+    shared by the heads. Runs between the QKV projection and RoPE in Qwen3. ``sync``: wait for
+    the ranks that store rows of ``qkv`` before reading it."""
+    if not qkv.is_cuda:
+        return ref.qk_norm(qkv, wq, wk, Hq, Hkv, D, eps)
+    nat = _native()
+    import ctypes
+    assert wq.is_contiguous() and (wk is None or wk.is_contiguous())
+    rc = nat.lib().ab200_qk_norm(qkv.data_ptr(), qkv.stride(0), wq.data_ptr(), nat.ptr(wk),
+                                 qkv.shape[0], Hq, Hkv, D, float(eps),
+                                 ctypes.byref(sync) if sync is not None else None,
+                                 nat.status_buffer(qkv.device).data_ptr(), nat.stream_ptr())
+    nat.check(rc, "qk_norm")
+    launch_counter.add(1)
+    return qkv
+
+
 def peer_barrier(flag_arrays, my_rank: int, epoch_counter: torch.Tensor, limit_ms: int = 1000) -> None:
     """Flag barrier among ``len(flag_arrays)`` ranks with a bounded wait. ``flag_arrays[r]`` is
     rank r's array of uint32 arrival slots (int32 tensors of >= 16 elements, here or in peer

@@ -44,6 +44,19 @@ def rmsnorm(x, weight, eps, residual=None):
     return (xf * inv * weight.float()).to(x.dtype)
 
 
+def qk_norm(qkv, wq, wk, Hq, Hkv, D, eps):
+    """In place: RMSNorm over head_dim of each of the Hq query and Hkv key heads of every row
+    of ``qkv`` [T, (Hq + 2*Hkv) * D]; ``wq`` / ``wk`` [D] are shared by the heads."""
+    T = qkv.shape[0]
+    for lo, n, w in ((0, Hq, wq), (Hq * D, Hkv, wk)):
+        if n == 0:
+            continue
+        x = qkv[:, lo:lo + n * D].reshape(T, n, D).float()
+        inv = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        qkv[:, lo:lo + n * D] = (x * inv * w.float()).to(qkv.dtype).reshape(T, n * D)
+    return qkv
+
+
 def layernorm(x, gamma, beta, eps, residual=None):
     xf = x.float()
     if residual is not None:

@@ -57,7 +57,8 @@ def _ensure_registered() -> None:
         return BertEncoder(*a, **k)
 
     register_config("llama_swiftkv", "Llama with SwiftKV (num_key_value_layers)")
-    for arch in ("LlamaForCausalLM", "LlamaSwiftKVForCausalLM"):
+    for arch in ("LlamaForCausalLM", "LlamaSwiftKVForCausalLM", "MistralForCausalLM",
+                 "Qwen3ForCausalLM"):
         register_model(arch, _llama)
     for arch in ("ArcticMLPSpeculatorPreTrainedModel", "ArcticLSTMSpeculatorPreTrainedModel",
                  "MLPVariantSpeculatorPreTrainedModel", "MLPSpeculatorPreTrainedModel"):

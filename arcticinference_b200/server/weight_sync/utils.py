@@ -95,6 +95,9 @@ def export_llama_state(model) -> Iterator:
                 vs[kvh.start] = wkv[r0 + hkv * D:r0 + width]
         yield p + "input_layernorm.weight", lw.input_norm
         yield p + "post_attention_layernorm.weight", lw.post_norm
+        if lw.q_norm is not None:
+            yield p + "self_attn.q_norm.weight", lw.q_norm
+            yield p + "self_attn.k_norm.weight", lw.k_norm
         yield p + "self_attn.q_proj%s.weight" % sfx, torch.cat(qs, 0)
         yield p + "self_attn.k_proj%s.weight" % sfx, torch.cat([ks[k] for k in sorted(ks)], 0)
         yield p + "self_attn.v_proj%s.weight" % sfx, torch.cat([vs[k] for k in sorted(vs)], 0)
@@ -128,7 +131,7 @@ def engine_weight_norm(engine) -> float:
     if m.lm_head is not m.embed:
         ts.append(m.lm_head)
     for lw in m.layers:
-        ts += [lw.input_norm, lw.post_norm, lw.wqkv, lw.wo, lw.wgu, lw.wdown]
+        ts += [t for _, t in lw.tensors()]
     for t in ts:
         if t is None:
             continue

@@ -12,6 +12,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from typing import Iterator
 
 import numpy as np
@@ -48,7 +49,11 @@ def read_safetensors(path: str) -> Iterator:
             yield name, torch.empty(info["shape"], dtype=dt)
             continue
         raw = np.frombuffer(mm, dtype=np.uint8, count=e - b, offset=base + b)
-        t = torch.from_numpy(raw.copy() if not raw.flags.writeable and False else raw)
+        with warnings.catch_warnings():
+            # the view is read-only on purpose (consumers copy into engine storage); torch
+            # warns about every non-writable array it wraps
+            warnings.simplefilter("ignore", UserWarning)
+            t = torch.from_numpy(raw)
         yield name, t.view(dt).reshape(info["shape"])
 
 

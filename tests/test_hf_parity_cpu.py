@@ -1,0 +1,93 @@
+"""Checkpoints written by Hugging Face transformers load into the engine and give the same
+next-token distribution as the transformers implementation (fp32, CPU) of the same
+architecture: Llama (llama3 rope scaling, grouped-query attention), Mistral, Qwen3 (per-head
+query / key norms, head_dim * heads != hidden_size). Teacher-forced: the log-probability of
+every prompt token given the tokens before it, so one near-tie cannot derail the comparison.
+Query and key projections are scaled up so that attention is sharp and a wrong rotary
+frequency, a missing norm or a wrong head mapping moves the result by far more than bf16
+rounding does."""
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from arcticinference_b200 import LLM, SamplingParams  # noqa: E402
+
+COMMON = dict(hidden_size=128, num_hidden_layers=2, intermediate_size=256, vocab_size=1000,
+              head_dim=64, max_position_embeddings=512, tie_word_embeddings=False,
+              eos_token_id=None, bos_token_id=1)
+LLAMA3 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 64}
+
+
+def _make(kind: str):
+    t = transformers
+    if kind == "llama":
+        cfg = t.LlamaConfig(num_attention_heads=4, num_key_value_heads=2, rope_theta=500000.0,
+                            rope_scaling=dict(LLAMA3), rms_norm_eps=1e-5, **COMMON)
+        return t.LlamaForCausalLM(cfg)
+    if kind == "mistral":
+        cfg = t.MistralConfig(num_attention_heads=2, num_key_value_heads=1, rope_theta=1000000.0,
+                              rms_norm_eps=1e-5, sliding_window=None, **COMMON)
+        return t.MistralForCausalLM(cfg)
+    cfg = t.Qwen3Config(num_attention_heads=4, num_key_value_heads=2, rope_theta=1000000.0,
+                        rms_norm_eps=1e-6, use_sliding_window=False, **COMMON)
+    return t.Qwen3ForCausalLM(cfg)
+
+
+def _prompt_logprobs(path, ids, **kw):
+    llm = LLM(model=path, max_model_len=256, device="cpu", **kw)
+    out = llm.generate([{"prompt_token_ids": ids}],
+                       SamplingParams(temperature=0, max_tokens=1, prompt_logprobs=0))
+    return llm, out[0].prompt_logprobs[1:]
+
+
+@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen3"])
+def test_prompt_logprobs_match_transformers(kind, tmp_path):
+    torch.manual_seed(0)
+    m = _make(kind).float().eval()
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if "q_norm" in name or "k_norm" in name:
+                p.copy_(1 + 0.3 * torch.randn_like(p))
+            elif kind != "qwen3" and ("q_proj" in name or "k_proj" in name):
+                p.mul_(6.0)          # (Qwen3's norms already make its attention sharp)
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    ids = torch.randint(2, 1000, (1, 100))
+    with torch.no_grad():
+        lg = m(ids).logits.log_softmax(-1)
+    ref = [lg[0, i, ids[0, i + 1]].item() for i in range(99)]
+
+    llm, got = _prompt_logprobs(str(tmp_path), ids[0].tolist())
+    cfg = llm.engine.config.model
+    assert cfg.rope_theta == (500000.0 if kind == "llama" else 1000000.0)
+    assert cfg.qk_norm == (kind == "qwen3")
+    assert (cfg.rope_scaling or {}).get("rope_type") == ("llama3" if kind == "llama" else None)
+    err = max(abs(a - b) for a, b in zip(ref, got))
+    assert err < 0.03, err
+
+    # the comparison notices what it is there to notice
+    wrong = {"qk_norm": False} if kind == "qwen3" else {"rope_theta": 10000.0}
+    _, off = _prompt_logprobs(str(tmp_path), ids[0].tolist(), hf_overrides=wrong)
+    assert max(abs(a - b) for a, b in zip(ref, off)) > 5 * max(err, 0.01)
+
+
+def test_unsupported_architectures_are_refused():
+    from arcticinference_b200.config import ModelConfig
+    base = dict(hidden_size=128, num_attention_heads=4, num_hidden_layers=2)
+    with pytest.raises(NotImplementedError, match="sliding-window"):
+        ModelConfig.from_hf_dict(dict(base, model_type="mistral", sliding_window=4096,
+                                      max_position_embeddings=32768))
+    with pytest.raises(NotImplementedError, match="bias"):
+        ModelConfig.from_hf_dict(dict(base, model_type="llama", attention_bias=True))
+    with pytest.raises(NotImplementedError, match="model_type"):
+        ModelConfig.from_hf_dict(dict(base, model_type="qwen2"))
+    # Qwen3 checkpoints carry a window size that is switched off
+    cfg = ModelConfig.from_hf_dict(dict(base, model_type="qwen3", head_dim=64, sliding_window=4096,
+                                        use_sliding_window=False, max_position_embeddings=40960))
+    assert cfg.qk_norm and cfg.head_dim == 64
+    from arcticinference_b200.models.llama import compute_inv_freq
+    cfg.rope_scaling = {"rope_type": "yarn", "factor": 4.0}
+    with pytest.raises(NotImplementedError, match="yarn"):
+        compute_inv_freq(cfg, "cpu")
