@@ -96,6 +96,10 @@ MODEL_CONFIGS: dict[GPUType, dict[str, dict[str, Any]]] = {
                                        ulysses_sequence_parallel_size=8, enable_shift_parallel=True),
         "Llama-3.1-70B-Instruct": dict(model="llama-3.3-70b", quantization="fp8",
                                        ulysses_sequence_parallel_size=4, enable_shift_parallel=True),
+        "Qwen3-8B": dict(model="qwen3-8b", quantization="fp8"),
+        "Qwen3-32B": dict(model="qwen3-32b", quantization="fp8",
+                          ulysses_sequence_parallel_size=4, enable_shift_parallel=True),
+        "Mistral-7B-Instruct": dict(model="mistral-7b", quantization="fp8"),
     },
     GPUType.H200: {},
 }

@@ -6,7 +6,7 @@
 #   examples/reproducibility/server.sh [shift|tp|dp] [MODEL] [GPUS]
 set -euo pipefail
 layout=${1:-shift}
-model=${2:-llama-3.3-70b}
+model=${2:-llama-3.3-70b}        # or qwen3-32b, a checkpoint directory, ...
 gpus=${3:-8}
 common="--quantization fp8 --no-enable-prefix-caching --max-num-batched-tokens 131072 --port 8000"
 case "$layout" in
