@@ -196,6 +196,10 @@ int ab200_rope_cache_wait(void* qkv, long long ld, const void* positions, const 
                           const void* inv_freq, void* k_cache, void* v_cache, long long T, int Hq,
                           int Hkv, int D, int block_size, long long num_slots, int rotate_q,
                           const Ab200PeerSync* sync, int* status, cudaStream_t stream);
+// ---- sampling.cu: y = x / temperature restricted to the top-k / top-p set, -inf elsewhere
+int ab200_topk_topp_mask(const void* logits, long long ld_in, void* out, long long ld_out, int B,
+                         int V, const void* temperature, const void* top_k, const void* top_p,
+                         cudaStream_t stream);
 // ---- qk_norm.cu: in-place RMSNorm over head_dim of the Hq query and Hkv key heads of every row
 int ab200_qk_norm(void* qkv, long long ld, const void* wq, const void* wk, long long T, int Hq,
                   int Hkv, int D, float eps, const Ab200PeerSync* sync, int* status,

@@ -1,9 +1,11 @@
-"""Full-distribution sampling (top-k / top-p / log-probabilities).
+"""Sampling from truncated distributions (top-k / top-p / grammar masks) and log-probabilities.
 
-The common cases (greedy, plain temperature sampling) never materialise a
-probability vector: they run the fused arg-max / Gumbel-max kernel on the raw
-logits. Requests that truncate the distribution take this slower path, which
-is framework-level PyTorch on the gathered logits."""
+No case materialises a probability vector or sorts a row: greedy and plain temperature
+sampling run the fused arg-max / Gumbel-max kernel on the raw logits; requests that truncate
+the distribution first pass through the selection kernel (``ops.topk_topp_mask``: the k-th
+largest logit and the top-p cut are found by counting and summing passes over the row, which
+stays in L2), then through the same Gumbel-max kernel. ``apply_top_k_top_p`` is the sort-based
+formulation of the same truncation, kept as the oracle of the tests."""
 
 from __future__ import annotations
 
@@ -60,9 +62,10 @@ def row_seed(request, j: int) -> int:
 
 
 def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
-    """Sampling from distributions truncated by top-k / top-p / grammar masks. The truncated,
-    temperature-scaled logits go through the same per-row Gumbel-max kernel as plain sampling
-    (a masked token's -inf never wins), keyed per row by :func:`row_seed`."""
+    """Sampling from distributions truncated by top-k / top-p / grammar masks. The selection
+    kernel leaves the temperature-scaled logits of the kept tokens and -inf elsewhere; they go
+    through the same per-row Gumbel-max kernel as plain sampling (a masked token's -inf never
+    wins), keyed per row by :func:`row_seed`."""
     from .. import ops
     B = logits.shape[0]
     dev = logits.device
@@ -80,9 +83,8 @@ def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
             top_p[row] = sp.top_p
             draw[row] = 0.0 if sp.greedy else 1.0
             seeds[row] = row_seed(s.request, j)
-    temp_t = torch.from_numpy(temp).to(dev)
-    lf = apply_top_k_top_p(lf / temp_t.unsqueeze(1), torch.from_numpy(top_k).to(dev),
-                           torch.from_numpy(top_p).to(dev)).contiguous()
+    lf = ops.topk_topp_mask(lf.contiguous(), torch.from_numpy(temp).to(dev),
+                            torch.from_numpy(top_k).to(dev), torch.from_numpy(top_p).to(dev))
     ids, _ = ops.argmax_sample(lf, torch.from_numpy(draw).to(dev), torch.from_numpy(seeds).to(dev))
     return ids
 

@@ -746,6 +746,28 @@ def argmax_sample(logits: torch.Tensor, temperature=None, seeds=None, index_offs
     return out_ids, out_vals
 
 
+def topk_topp_mask(logits: torch.Tensor, temperature=None, top_k=None, top_p=None):
+    """fp32 [B, V]: ``logits / temperature`` for the tokens of each row's top-k / top-p set and
+    -inf for the rest, ready for :func:`argmax_sample` (no sort, no probability vector).
+    temperature fp32 [B]; top_k int64 [B] (<= 0: off); top_p fp32 [B] (>= 1: off). Tokens with
+    equal logits stay or go together."""
+    if not logits.is_cuda:
+        return ref.topk_topp_mask(logits, temperature, top_k, top_p)
+    nat = _native()
+    x = logits if logits.dtype == torch.float32 else logits.float()
+    assert x.stride(1) == 1
+    B, V = x.shape
+    out = torch.empty(B, V, dtype=torch.float32, device=x.device)
+    for t, dt in ((temperature, torch.float32), (top_k, torch.int64), (top_p, torch.float32)):
+        assert t is None or (t.dtype == dt and t.is_contiguous() and t.numel() == B)
+    rc = nat.lib().ab200_topk_topp_mask(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0),
+                                        B, V, nat.ptr(temperature), nat.ptr(top_k),
+                                        nat.ptr(top_p), nat.stream_ptr())
+    nat.check(rc, "topk_topp_mask")
+    launch_counter.add(1)
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------------------

@@ -91,6 +91,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "ab200_silu_mul_quant": (I, [P, P, LL, P, LL, I, I, P]),
         "ab200_linear_desc": (I, [P, P]),
         "ab200_rope_cache_wait": (I, [P, LL, P, P, P, P, P, LL, I, I, I, I, LL, I, P, P, P]),
+        "ab200_topk_topp_mask": (I, [P, LL, P, LL, I, I, P, P, P, P]),
         "ab200_qk_norm": (I, [P, LL, P, P, LL, I, I, I, F, P, P, P]),
         "ab200_quant_fp8_row_wait": (I, [P, LL, P, LL, P, LL, I, P, P, P]),
         "ab200_spec_ln": (I, [P, LL, P, P, P, LL, LL, I, F, F, P]),

@@ -44,6 +44,37 @@ def rmsnorm(x, weight, eps, residual=None):
     return (xf * inv * weight.float()).to(x.dtype)
 
 
+def topk_topp_mask(logits, temperature=None, top_k=None, top_p=None):
+    """y = logits / temperature where a token is in the top-k / top-p set, -inf elsewhere. The
+    k largest stay; of those a token stays iff the probability mass of the tokens strictly more
+    likely than it is at most top_p (of the top-k set's mass). Ties for the k-th place go to
+    the lowest token ids; at the top-p cut equal logits stay or go together. logits fp32 [B, V]; temperature fp32 [B]; top_k int64 [B] (<= 0: off); top_p
+    fp32 [B] (>= 1: off)."""
+    B, V = logits.shape
+    x = logits.float()
+    if temperature is not None:
+        x = x * (1.0 / temperature.float().clamp(min=1e-5)).unsqueeze(1)
+    vals, order = x.sort(dim=-1, descending=True, stable=True)   # ties in token-id order
+    keep = torch.ones_like(x, dtype=torch.bool)
+    in_k_sorted = None
+    if top_k is not None:
+        k = torch.where((top_k > 0) & (top_k < V), top_k, torch.full_like(top_k, V))
+        in_k_sorted = torch.arange(V, device=x.device).unsqueeze(0) < k.unsqueeze(1)
+        keep = torch.zeros_like(keep).scatter(1, order, in_k_sorted)
+    if top_p is not None:
+        m = vals[:, :1]
+        w_sorted = torch.exp(vals - m)
+        if in_k_sorted is not None:
+            w_sorted = w_sorted * in_k_sorted
+        z = w_sorted.sum(-1, keepdim=True)
+        before = w_sorted.cumsum(-1) - w_sorted          # mass ahead of each sorted position
+        # mass strictly above a value: what lies ahead of the first position holding it
+        first = torch.searchsorted((-vals).contiguous(), (-x).contiguous(), side="left")
+        above = before.gather(1, first.clamp(max=V - 1))
+        keep &= (above <= top_p.float().unsqueeze(1) * z) | (top_p.float().unsqueeze(1) >= 1.0)
+    return torch.where(keep, x, torch.full_like(x, float("-inf")))
+
+
 def qk_norm(qkv, wq, wk, Hq, Hkv, D, eps):
     """In place: RMSNorm over head_dim of each of the Hq query and Hkv key heads of every row
     of ``qkv`` [T, (Hq + 2*Hkv) * D]; ``wq`` / ``wk`` [D] are shared by the heads."""
