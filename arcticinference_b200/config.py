@@ -67,6 +67,9 @@ class ModelConfig:
     # "channel": a scale per output feature, activations per token; "block": 128 x 128 blocks
     fp8_scheme: str = "channel"
     eos_token_id: Optional[int] = None
+    # further end-of-sequence ids (a list in config.json or generation_config.json, e.g. the
+    # end-of-turn token of instruction-tuned Llama 3): they end a request like EOS does
+    extra_eos_token_ids: tuple = ()
     bos_token_id: Optional[int] = None
     name_or_path: str = ""
 
@@ -97,9 +100,9 @@ class ModelConfig:
         mt = d.get("model_type", "llama")
         heads = d.get("num_attention_heads", 32)
         hidden = d.get("hidden_size", 4096)
-        eos = d.get("eos_token_id")
+        eos, extra_eos = d.get("eos_token_id"), ()
         if isinstance(eos, list):
-            eos = eos[0] if eos else None
+            eos, extra_eos = (eos[0] if eos else None), tuple(int(t) for t in eos[1:])
         if mt not in DECODER_MODEL_TYPES and mt != "bert":
             raise NotImplementedError("model_type %r (supported: %s, bert)" %
                                       (mt, ", ".join(DECODER_MODEL_TYPES)))
@@ -131,7 +134,8 @@ class ModelConfig:
             type_vocab_size=d.get("type_vocab_size", 2),
             layer_norm_eps=d.get("layer_norm_eps", 1e-12),
             hidden_act=d.get("hidden_act", "silu"),
-            eos_token_id=eos, bos_token_id=d.get("bos_token_id"), name_or_path=name_or_path)
+            eos_token_id=eos, extra_eos_token_ids=extra_eos, bos_token_id=d.get("bos_token_id"),
+            name_or_path=name_or_path)
         q = d.get("quantization_config")
         if q and q.get("quant_method") in ("fp8", "compressed-tensors"):
             cfg.quantization = "fp8"
@@ -145,7 +149,17 @@ class ModelConfig:
         if path in PRESETS:
             return dataclasses.replace(PRESETS[path], name_or_path=path)
         with open(os.path.join(path, "config.json")) as f:
-            return cls.from_hf_dict(json.load(f), path)
+            cfg = cls.from_hf_dict(json.load(f), path)
+        gen = os.path.join(path, "generation_config.json")
+        if os.path.exists(gen):
+            with open(gen) as f:
+                ids = json.load(f).get("eos_token_id")
+            ids = [] if ids is None else ([int(t) for t in ids] if isinstance(ids, list) else [int(ids)])
+            if cfg.eos_token_id is None and ids:
+                cfg.eos_token_id = ids[0]
+            known = {cfg.eos_token_id, *cfg.extra_eos_token_ids}
+            cfg.extra_eos_token_ids += tuple(t for t in dict.fromkeys(ids) if t not in known)
+        return cfg
 
 
 # decoder families the Llama code path serves: Mistral is Llama under another name once its

@@ -128,6 +128,7 @@ class LLMEngine:
         eos = self.config.model.eos_token_id
         if eos is None:
             eos = getattr(self.tokenizer, "eos_token_id", None)
+        extra = () if params.ignore_eos else self.config.model.extra_eos_token_ids
         if params.prompt_logprobs is not None and self.config.model.is_swiftkv:
             raise ValueError("prompt_logprobs is not available for SwiftKV models: their later "
                              "layers run on the sampled rows only")
@@ -142,7 +143,8 @@ class LLMEngine:
 
         if params.n == 1:
             self.scheduler.add_request(Request(request_id, ids, params, prompt=text,
-                                               eos_token_id=eos, arrival_time=now,
+                                               eos_token_id=eos, extra_stop_ids=extra,
+                                               arrival_time=now,
                                                routing_key=routing_key,
                                                grammar=self._grammar_for(params, eos),
                                                stop_matcher=stops()))
@@ -151,7 +153,8 @@ class LLMEngine:
             for i in range(params.n):
                 self.scheduler.add_request(Request(
                     "%s#%d" % (request_id, i), ids, params.clone_for_sample(i), prompt=text,
-                    eos_token_id=eos, parent_id=request_id, sample_index=i, arrival_time=now,
+                    eos_token_id=eos, extra_stop_ids=extra, parent_id=request_id, sample_index=i,
+                    arrival_time=now,
                     grammar=self._grammar_for(params, eos, copy_given=True),
                     stop_matcher=stops()))
         return request_id

@@ -35,6 +35,7 @@ class Request:
     sampling_params: SamplingParams
     prompt: Optional[str] = None
     eos_token_id: Optional[int] = None
+    extra_stop_ids: tuple = ()        # the model's further end-of-sequence ids (unless ignore_eos)
     parent_id: Optional[str] = None   # set for the samples of an n > 1 request
     sample_index: int = 0
     arrival_time: float = field(default_factory=time.time)
@@ -128,7 +129,8 @@ class Request:
             if not sp.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id:
                 self.status = RequestStatus.FINISHED_STOPPED
                 return True
-            if sp.stop_token_ids and last in sp.stop_token_ids:
+            if (sp.stop_token_ids and last in sp.stop_token_ids) or \
+                    (self.extra_stop_ids and last in self.extra_stop_ids):
                 self.status = RequestStatus.FINISHED_STOPPED
                 return True
             if self.stop_matcher is not None and self.stop_matcher.hit(self):

@@ -108,3 +108,32 @@ def test_options_that_cannot_be_honoured_are_refused():
             EngineArgs(model="llama-tiny", **kw).create_engine_config()
     EngineArgs(model="llama-tiny", kv_cache_dtype="auto").create_engine_config()
     EngineArgs(model="llama-tiny", pipeline_parallel_size=2).create_engine_config()   # whole-model stages
+
+
+def test_every_end_of_sequence_id_of_the_checkpoint_ends_a_request(tmp_path):
+    """Instruction-tuned checkpoints list several end-of-sequence ids (config.json and
+    generation_config.json): each of them ends a request, unless it asks to ignore EOS."""
+    import json
+    from arcticinference_b200.config import ModelConfig
+    base = dict(model_type="llama", hidden_size=128, num_attention_heads=2, num_hidden_layers=1,
+                head_dim=64, vocab_size=1000)
+    (tmp_path / "config.json").write_text(json.dumps(dict(base, eos_token_id=[7, 9])))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [7, 11, 9]}))
+    cfg = ModelConfig.from_pretrained(str(tmp_path))
+    assert cfg.eos_token_id == 7 and cfg.extra_eos_token_ids == (9, 11)
+    (tmp_path / "config.json").write_text(json.dumps(dict(base, eos_token_id=5)))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 5}))
+    cfg = ModelConfig.from_pretrained(str(tmp_path))
+    assert cfg.eos_token_id == 5 and cfg.extra_eos_token_ids == ()
+
+    kw = dict(model="llama-tiny", device="cpu", max_model_len=128, num_gpu_blocks_override=32,
+              block_size=16)
+    prompt = [{"prompt_token_ids": list(range(5, 30))}]
+    free = LLM(**kw).generate(prompt, SamplingParams(temperature=0, max_tokens=8, ignore_eos=True))
+    toks = free[0].outputs[0].token_ids
+    stop_at = next(i for i, t in enumerate(toks) if t not in toks[:i] and i >= 2)
+    llm = LLM(hf_overrides={"extra_eos_token_ids": (toks[stop_at],)}, **kw)
+    out = llm.generate(prompt, SamplingParams(temperature=0, max_tokens=8))[0].outputs[0]
+    assert out.token_ids == toks[:stop_at + 1] and out.finish_reason == "stop"
+    out = llm.generate(prompt, SamplingParams(temperature=0, max_tokens=8, ignore_eos=True))
+    assert out[0].outputs[0].token_ids == toks and out[0].outputs[0].finish_reason == "length"
