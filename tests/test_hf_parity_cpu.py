@@ -91,3 +91,29 @@ def test_unsupported_architectures_are_refused():
     cfg.rope_scaling = {"rope_type": "yarn", "factor": 4.0}
     with pytest.raises(NotImplementedError, match="yarn"):
         compute_inv_freq(cfg, "cpu")
+
+
+@pytest.mark.parametrize("pooling", ["cls", "mean"])
+def test_bert_embeddings_match_transformers(pooling, tmp_path):
+    from arcticinference_b200.embedding.engine import EmbeddingEngine
+    torch.manual_seed(0)
+    cfg = transformers.BertConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=2,
+                                  intermediate_size=256, vocab_size=1000,
+                                  max_position_embeddings=128, type_vocab_size=2)
+    m = transformers.BertModel(cfg, add_pooling_layer=False).float().eval()
+    with torch.no_grad():
+        for name, p in m.named_parameters():       # norms and biases away from their 1 / 0 init
+            if "LayerNorm" in name:
+                p.add_(0.2 * torch.randn_like(p))
+            elif "bias" in name:
+                p.add_(0.1 * torch.randn_like(p))
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    eng = EmbeddingEngine(model=str(tmp_path), device="cpu", dtype=torch.float32)
+    seqs = [torch.randint(5, 1000, (n,)).tolist() for n in (7, 50, 128, 1)]
+    got = torch.from_numpy(eng.encode(seqs, pooling=pooling)).float()
+    want = []
+    with torch.no_grad():
+        for s in seqs:
+            h = m(torch.tensor([s])).last_hidden_state[0]
+            want.append(torch.nn.functional.normalize(h[0] if pooling == "cls" else h.mean(0), dim=0))
+    assert (got - torch.stack(want)).abs().max().item() < 1e-5
