@@ -60,10 +60,9 @@ class LLM:
     def chat(self, messages, sampling_params: Optional[SamplingParams] = None, **kw):
         if messages and isinstance(messages[0], dict):
             messages = [messages]
+        from ..utils.tokenizer import chat_token_ids
         tok = self.engine.tokenizer
-        prompts = [{"prompt_token_ids": tok.apply_chat_template(m, tokenize=True,
-                                                                add_generation_prompt=True)}
-                   for m in messages]
+        prompts = [{"prompt_token_ids": chat_token_ids(tok, m)} for m in messages]
         return self.generate(prompts, sampling_params)
 
     def sleep(self, level: int = 1) -> None:

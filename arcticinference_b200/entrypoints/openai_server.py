@@ -23,6 +23,7 @@ from pydantic import BaseModel
 
 from ..engine.async_llm import AsyncLLM
 from ..engine.sampling_params import SamplingParams
+from ..utils.tokenizer import chat_token_ids
 
 
 class CompletionRequest(BaseModel):
@@ -157,9 +158,7 @@ def build_app(llm: AsyncLLM, served_model_name: Optional[str] = None) -> FastAPI
 
     def chat_prompt_ids(req) -> list:
         msgs = [{"role": m.role, "content": _message_text(m)} for m in req.messages]
-        ids = tok.apply_chat_template(msgs, tokenize=True,
-                                      add_generation_prompt=getattr(req, "add_generation_prompt", True))
-        return list(ids["input_ids"]) if isinstance(ids, dict) else list(ids)
+        return chat_token_ids(tok, msgs, getattr(req, "add_generation_prompt", True))
 
     # ------------------------------------------------------------------ plumbing
     @app.get("/health")

@@ -35,6 +35,19 @@ class ByteTokenizer:
         return self.encode(text) if tokenize else text
 
 
+def chat_token_ids(tokenizer, messages, add_generation_prompt: bool = True, **kw) -> list:
+    """Token ids of a conversation under the tokenizer's chat template. Hugging Face
+    tokenizers return a plain list (transformers 4) or a ``BatchEncoding`` with ``input_ids``
+    (transformers 5, which is a ``UserDict``, not a ``dict``); both are accepted."""
+    out = tokenizer.apply_chat_template(messages, tokenize=True,
+                                        add_generation_prompt=add_generation_prompt, **kw)
+    if hasattr(out, "keys") and "input_ids" in out:
+        out = out["input_ids"]
+    if len(out) and isinstance(out[0], (list, tuple)):      # a batch of one
+        out = out[0]
+    return [int(t) for t in out]
+
+
 def get_tokenizer(name_or_path: Optional[str], vocab_size: int = 1024):
     if name_or_path and os.path.isdir(name_or_path):
         try:
