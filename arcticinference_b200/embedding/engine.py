@@ -93,7 +93,12 @@ class EmbeddingEngine:
                 ids = list(ids["input_ids"]) if isinstance(ids, dict) else list(ids)
             else:
                 ids = p
-            a = np.asarray(ids, dtype=np.int64).reshape(-1)[: self.max_len]
+            a = np.asarray(ids, dtype=np.int64).reshape(-1)
+            if a.size > self.max_len:
+                # cut like a tokenizer with truncation does: the closing [SEP] stays
+                sep = getattr(self.tokenizer, "sep_token_id", None)
+                keep_last = isinstance(p, str) and sep is not None and a[-1] == sep
+                a = np.concatenate([a[: self.max_len - 1], a[-1:]]) if keep_last else a[: self.max_len]
             out.append(a if a.size else np.zeros(1, dtype=np.int64))
         return out
 
