@@ -32,8 +32,8 @@ SHIFT_PARALLEL_THRESHOLD = 128
 
 @dataclass
 class ModelConfig:
-    """Architecture of a decoder (Llama, Mistral and Qwen3 dense models, optionally SwiftKV for
-    Llama) or encoder (BERT)."""
+    """Architecture of a decoder (Llama, Mistral, Qwen2 and Qwen3 dense models, optionally
+    SwiftKV for Llama) or encoder (BERT)."""
 
     architecture: str = "LlamaForCausalLM"
     model_type: str = "llama"
@@ -54,6 +54,8 @@ class ModelConfig:
     num_key_value_layers: Optional[int] = None
     # Qwen3: RMSNorm over head_dim on every query and key head before RoPE
     qk_norm: bool = False
+    # Qwen2: a bias on the query / key / value projections (none on o_proj or the MLP)
+    qkv_bias: bool = False
     # encoder-only fields
     type_vocab_size: int = 2
     layer_norm_eps: float = 1e-12
@@ -91,8 +93,11 @@ class ModelConfig:
             raise ValueError("quantization must be None or 'fp8'")
         if self.fp8_scheme not in ("channel", "block"):
             raise ValueError("fp8_scheme must be 'channel' or 'block'")
-        if self.qk_norm and self.is_swiftkv:
-            raise NotImplementedError("SwiftKV with per-head query / key norms")
+        if (self.qk_norm or self.qkv_bias) and self.is_swiftkv:
+            raise NotImplementedError("SwiftKV with per-head query / key norms or a QKV bias")
+        if self.qkv_bias and self.quantization == "fp8" and self.fp8_scheme == "block":
+            raise NotImplementedError("a QKV bias with block-scaled fp8 linears: use "
+                                      "fp8_scheme='channel'")
 
     @classmethod
     def from_hf_dict(cls, d: dict, name_or_path: str = "") -> "ModelConfig":
@@ -107,6 +112,8 @@ class ModelConfig:
             raise NotImplementedError("model_type %r (supported: %s, bert)" %
                                       (mt, ", ".join(DECODER_MODEL_TYPES)))
         if d.get("attention_bias") or d.get("mlp_bias"):
+            # (Llama's attention_bias also puts a bias on o_proj; Qwen2's QKV-only bias is
+            # part of its architecture and has no flag)
             raise NotImplementedError("linear layers with bias (attention_bias / mlp_bias)")
         window = d.get("sliding_window") if d.get("use_sliding_window", True) else None
         if window is not None and window < d.get("max_position_embeddings", 4096):
@@ -130,7 +137,7 @@ class ModelConfig:
             max_position_embeddings=d.get("max_position_embeddings", 4096),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             num_key_value_layers=d.get("num_key_value_layers"),
-            qk_norm=(mt == "qwen3"),
+            qk_norm=(mt == "qwen3"), qkv_bias=(mt == "qwen2"),
             type_vocab_size=d.get("type_vocab_size", 2),
             layer_norm_eps=d.get("layer_norm_eps", 1e-12),
             hidden_act=d.get("hidden_act", "silu"),
@@ -163,9 +170,9 @@ class ModelConfig:
 
 
 # decoder families the Llama code path serves: Mistral is Llama under another name once its
-# sliding window is off; Qwen3 (dense) adds the per-head query / key norms and a head_dim that
-# is not hidden_size / heads
-DECODER_MODEL_TYPES = ("llama", "llama_swiftkv", "mistral", "qwen3")
+# sliding window is off; Qwen2 adds a bias on the QKV projection; Qwen3 (dense) adds the
+# per-head query / key norms and a head_dim that is not hidden_size / heads
+DECODER_MODEL_TYPES = ("llama", "llama_swiftkv", "mistral", "qwen2", "qwen3")
 
 
 def _llama(layers, hidden, heads, kv, inter, **kw) -> ModelConfig:
@@ -198,6 +205,14 @@ PRESETS: dict[str, ModelConfig] = {
     "mistral-7b": _llama(32, 4096, 32, 8, 14336, architecture="MistralForCausalLM",
                          model_type="mistral", vocab_size=32768, rope_theta=1000000.0,
                          max_position_embeddings=32768),
+    "qwen2.5-7b": _llama(28, 3584, 28, 4, 18944, architecture="Qwen2ForCausalLM",
+                         model_type="qwen2", qkv_bias=True, vocab_size=152064,
+                         rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768),
+    "qwen2-tiny": ModelConfig(architecture="Qwen2ForCausalLM", model_type="qwen2", qkv_bias=True,
+                              hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                              num_key_value_heads=2, head_dim=64, intermediate_size=512,
+                              vocab_size=1024, max_position_embeddings=4096, rope_theta=10000.0,
+                              rms_norm_eps=1e-6),
     "qwen3-8b": _llama(36, 4096, 32, 8, 12288, architecture="Qwen3ForCausalLM",
                        model_type="qwen3", qk_norm=True, vocab_size=151936, rope_theta=1000000.0,
                        rms_norm_eps=1e-6, max_position_embeddings=40960),

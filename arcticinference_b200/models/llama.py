@@ -81,8 +81,10 @@ class ShardSpec:
         return range(self.tp_rank * self.sp, (self.tp_rank + 1) * self.sp)
 
 
-# per-layer tensors in the order every walk over a layer uses (q_norm / k_norm: Qwen3 only)
-LAYER_TENSORS = ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown", "q_norm", "k_norm")
+# per-layer tensors in the order every walk over a layer uses (q_norm / k_norm: Qwen3 only;
+# bqkv: Qwen2 only, in the row order of wqkv)
+LAYER_TENSORS = ("input_norm", "post_norm", "wqkv", "wo", "wgu", "wdown", "q_norm", "k_norm",
+                 "bqkv")
 
 
 class LlamaLayerWeights:
@@ -91,6 +93,7 @@ class LlamaLayerWeights:
     def __init__(self):
         self.input_norm = self.post_norm = self.wqkv = self.wo = self.wgu = self.wdown = None
         self.q_norm = self.k_norm = None   # [head_dim] each, shared by all heads of the layer
+        self.bqkv = None
         self.wq_swiftkv = None
         self.extra = {}
 
@@ -222,6 +225,11 @@ class LlamaForCausalLM(LlamaModel):
     def __init__(self, cfg, shard=None, device="cuda", dtype=torch.bfloat16, comm=None):
         super().__init__(cfg, shard, device, dtype)
         self.comm = comm
+        if cfg.qkv_bias and comm is not None and getattr(comm, "fused", False) and comm.sp > 1:
+            raise NotImplementedError(
+                "a QKV bias (Qwen2) with the fused communicator in sequence-parallel mode: the "
+                "scattering GEMM epilogue adds none; use comm_backend='nccl' or tensor "
+                "parallelism")
 
     # --------------------------------------------------------------- shard views
     def _qkv_w(self, lw, mode):
@@ -229,6 +237,12 @@ class LlamaForCausalLM(LlamaModel):
             return lw.wqkv
         i = self.shard.sp_rank
         return lw.wqkv[i * self.blk_rows:(i + 1) * self.blk_rows]
+
+    def _qkv_b(self, lw, mode):
+        if lw.bqkv is None or mode == "sp" or self.n_stored == 1:
+            return lw.bqkv
+        i = self.shard.sp_rank
+        return lw.bqkv[i * self.blk_rows:(i + 1) * self.blk_rows]
 
     def _gu_w(self, lw, mode):
         if mode == "sp" or self.n_stored == 1:
@@ -257,12 +271,12 @@ class LlamaForCausalLM(LlamaModel):
         h, hkv, D = self.h, self.hkv, self.D
         if mode == "sp" and comm is not None and comm.sp > 1:
             # local tokens x all stored head blocks -> all tokens x own head block
-            qkv = comm.qkv_scatter_heads(x, lw.wqkv, self.blk_rows)
+            qkv = comm.qkv_scatter_heads(x, lw.wqkv, self.blk_rows, bias=lw.bqkv)
         else:
-            w = self._qkv_w(lw, mode)
+            w, b = self._qkv_w(lw, mode), self._qkv_b(lw, mode)
             if q_only:
                 w = w[: h * D]
-            qkv = ops.linear(x, w)
+            qkv = ops.linear(x, w, bias=b)
         # rows that other ranks scattered into qkv: the first kernel that reads them waits
         wait = comm.take_wait("qkv") if (comm is not None and comm.fused) else None
         if lw.q_norm is not None:

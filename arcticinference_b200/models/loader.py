@@ -3,9 +3,9 @@
 Accepted formats (reference: arctic_inference/vllm/swiftkv/llama_swiftkv.py:748-820,
 arctic_inference/vllm/spec_dec/fp8.py:140-180):
 
-* Hugging Face Llama / Mistral / Qwen3 safetensors (``q_proj/k_proj/v_proj/o_proj``,
-  ``gate_proj/up_proj/down_proj``, norms, ``embed_tokens``, ``lm_head``; for Qwen3 also
-  ``self_attn.q_norm`` and ``self_attn.k_norm``);
+* Hugging Face Llama / Mistral / Qwen2 / Qwen3 safetensors (``q_proj/k_proj/v_proj/o_proj``,
+  ``gate_proj/up_proj/down_proj``, norms, ``embed_tokens``, ``lm_head``; for Qwen2 also the
+  ``q_proj/k_proj/v_proj`` biases, for Qwen3 ``self_attn.q_norm`` and ``self_attn.k_norm``);
 * SwiftKV: ``model_type = llama_swiftkv``, ``num_key_value_layers`` and, for each layer
   >= num_key_value_layers, ``self_attn.{q,k,v}_proj_swiftkv`` plus ``model.norm_swiftkv``;
 * fp8 checkpoints: fp8 ``weight`` with a per-tensor / per-channel ``weight_scale`` or a
@@ -51,6 +51,10 @@ def random_llama_state(cfg, seed: int, std: float, device, dtype) -> Iterator:
         b = 100 + 20 * l
         yield p + "input_layernorm.weight", ones()
         yield p + "post_attention_layernorm.weight", ones()
+        if cfg.qkv_bias:
+            yield p + "self_attn.q_proj.bias", 5 * rnd(b + 10, Hq * D)
+            yield p + "self_attn.k_proj.bias", 5 * rnd(b + 11, Hkv * D)
+            yield p + "self_attn.v_proj.bias", 5 * rnd(b + 12, Hkv * D)
         if cfg.qk_norm:
             yield p + "self_attn.q_norm.weight", (1.0 + 10 * rnd(b + 8, D).float()).to(dtype)
             yield p + "self_attn.k_norm.weight", (1.0 + 10 * rnd(b + 9, D).float()).to(dtype)
@@ -81,6 +85,8 @@ def _required(model, l: int) -> list[str]:
     later = model.cfg.is_swiftkv and l >= model.n_kv_layers
     sfx = "_swiftkv" if later else ""
     norms = ["self_attn.q_norm.weight", "self_attn.k_norm.weight"] if model.cfg.qk_norm else []
+    if model.cfg.qkv_bias:
+        norms += ["self_attn.q_proj.bias", "self_attn.k_proj.bias", "self_attn.v_proj.bias"]
     return ["input_layernorm.weight", "post_attention_layernorm.weight",
             "self_attn.q_proj%s.weight" % sfx, "self_attn.k_proj%s.weight" % sfx,
             "self_attn.v_proj%s.weight" % sfx, "self_attn.o_proj.weight",
@@ -100,12 +106,16 @@ def pack_llama_layer(model, l: int, t: dict) -> None:
     gate, up = t["mlp.gate_proj.weight"], t["mlp.up_proj.weight"]
     blocks = list(model.shard.stored_blocks)
     lw = LlamaLayerWeights()
-    qkv_rows, gu_rows, kv_rows = [], [], []
+    qkv_rows, gu_rows, kv_rows, bias_rows = [], [], [], []
     for p in blocks:
         kvh = model.kv_head_of_block(p)
         ks = k[kvh.start * D: kvh.stop * D]
         vs = v[kvh.start * D: kvh.stop * D]
         qkv_rows += [q[p * h * D:(p + 1) * h * D], ks, vs]
+        if model.cfg.qkv_bias:
+            bias_rows += [t["self_attn.q_proj.bias"][p * h * D:(p + 1) * h * D],
+                          t["self_attn.k_proj.bias"][kvh.start * D: kvh.stop * D],
+                          t["self_attn.v_proj.bias"][kvh.start * D: kvh.stop * D]]
         gu_rows += [gate[p * Ib:(p + 1) * Ib], up[p * Ib:(p + 1) * Ib]]
         kv_rows.append((ks, vs))
     to = lambda x: x.to(device=dev, dtype=dt)
@@ -116,6 +126,8 @@ def pack_llama_layer(model, l: int, t: dict) -> None:
     lw.wdown = to(t["mlp.down_proj.weight"][:, p0 * Ib:(p0 + n) * Ib]).contiguous()
     lw.input_norm = to(t["input_layernorm.weight"]).contiguous()
     lw.post_norm = to(t["post_attention_layernorm.weight"]).contiguous()
+    if bias_rows:
+        lw.bqkv = to(torch.cat(bias_rows, 0)).contiguous()
     if model.cfg.qk_norm:
         lw.q_norm = to(t["self_attn.q_norm.weight"]).contiguous()
         lw.k_norm = to(t["self_attn.k_norm.weight"]).contiguous()

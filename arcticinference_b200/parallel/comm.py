@@ -109,10 +109,10 @@ class Communicator:
         return t[s * n:(s + 1) * n]
 
     # ----------------------------------------------------------- Ulysses exchange
-    def qkv_scatter_heads(self, x_local, wqkv, blk_rows: int) -> torch.Tensor:
+    def qkv_scatter_heads(self, x_local, wqkv, blk_rows: int, bias=None) -> torch.Tensor:
         """[n, H] local tokens -> [N, blk_rows] all tokens x this rank's head block."""
         n = x_local.shape[0]
-        qkv = ops.linear(x_local, wqkv)                       # [n, SP*blk_rows]
+        qkv = ops.linear(x_local, wqkv, bias=bias)            # [n, SP*blk_rows]
         send = qkv.view(n, self.sp, blk_rows).transpose(0, 1).contiguous()  # [SP, n, blk]
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv.view(self.sp * n, blk_rows), send.view(self.sp * n, blk_rows),

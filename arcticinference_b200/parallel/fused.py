@@ -221,10 +221,14 @@ class FusedCommunicator(Communicator):
         """The operand wait that the consumer of the last ``name`` exchange must apply (once)."""
         return self._pending_wait.pop(name, None)
 
-    def qkv_scatter_heads(self, x_local, wqkv, blk_rows: int) -> torch.Tensor:
+    def qkv_scatter_heads(self, x_local, wqkv, blk_rows: int, bias=None) -> torch.Tensor:
         """The projection's epilogue stores each head block into its owner's buffer and its last
         block signals every rank; the caller's next kernel on the result (RoPE + cache write)
         must wait with ``take_wait("qkv")``."""
+        if bias is not None:
+            raise NotImplementedError("a QKV bias with the fused communicator in sequence-"
+                                      "parallel mode (the scattering epilogue adds none): use "
+                                      "comm_backend='nccl', or tensor parallelism")
         n = x_local.shape[0]
         N = n * self.sp
         s = self.topo.sp_rank

@@ -58,7 +58,7 @@ def _ensure_registered() -> None:
 
     register_config("llama_swiftkv", "Llama with SwiftKV (num_key_value_layers)")
     for arch in ("LlamaForCausalLM", "LlamaSwiftKVForCausalLM", "MistralForCausalLM",
-                 "Qwen3ForCausalLM"):
+                 "Qwen2ForCausalLM", "Qwen3ForCausalLM"):
         register_model(arch, _llama)
     for arch in ("ArcticMLPSpeculatorPreTrainedModel", "ArcticLSTMSpeculatorPreTrainedModel",
                  "MLPVariantSpeculatorPreTrainedModel", "MLPSpeculatorPreTrainedModel"):

@@ -98,6 +98,17 @@ def export_llama_state(model) -> Iterator:
         if lw.q_norm is not None:
             yield p + "self_attn.q_norm.weight", lw.q_norm
             yield p + "self_attn.k_norm.weight", lw.k_norm
+        if lw.bqkv is not None:
+            bq, bk, bv = [], {}, {}
+            for i, b in enumerate(blocks):
+                blk = lw.bqkv[i * rows:(i + 1) * rows]
+                kvh = model.kv_head_of_block(b)
+                bq.append(blk[:h * D])
+                bk[kvh.start] = blk[h * D:(h + hkv) * D]
+                bv[kvh.start] = blk[(h + hkv) * D:]
+            yield p + "self_attn.q_proj.bias", torch.cat(bq, 0)
+            yield p + "self_attn.k_proj.bias", torch.cat([bk[k] for k in sorted(bk)], 0)
+            yield p + "self_attn.v_proj.bias", torch.cat([bv[k] for k in sorted(bv)], 0)
         yield p + "self_attn.q_proj%s.weight" % sfx, torch.cat(qs, 0)
         yield p + "self_attn.k_proj%s.weight" % sfx, torch.cat([ks[k] for k in sorted(ks)], 0)
         yield p + "self_attn.v_proj%s.weight" % sfx, torch.cat([vs[k] for k in sorted(vs)], 0)

@@ -1,7 +1,7 @@
 """Checkpoints written by Hugging Face transformers load into the engine and give the same
 next-token distribution as the transformers implementation (fp32, CPU) of the same
-architecture: Llama (llama3 rope scaling, grouped-query attention), Mistral, Qwen3 (per-head
-query / key norms, head_dim * heads != hidden_size). Teacher-forced: the log-probability of
+architecture: Llama (llama3 rope scaling, grouped-query attention), Mistral, Qwen2 (QKV bias),
+Qwen3 (per-head query / key norms, head_dim * heads != hidden_size). Teacher-forced: the log-probability of
 every prompt token given the tokens before it, so one near-tie cannot derail the comparison.
 Query and key projections are scaled up so that attention is sharp and a wrong rotary
 frequency, a missing norm or a wrong head mapping moves the result by far more than bf16
@@ -31,6 +31,12 @@ def _make(kind: str):
         cfg = t.MistralConfig(num_attention_heads=2, num_key_value_heads=1, rope_theta=1000000.0,
                               rms_norm_eps=1e-5, sliding_window=None, **COMMON)
         return t.MistralForCausalLM(cfg)
+    if kind == "qwen2":
+        cfg = t.Qwen2Config(num_attention_heads=4, num_key_value_heads=2, rope_theta=1000000.0,
+                            rms_norm_eps=1e-6, use_sliding_window=False,
+                            **{k: v for k, v in COMMON.items() if k != "head_dim"})
+        cfg.hidden_size = 256          # Qwen2 has no head_dim field: hidden_size / heads = 64
+        return t.Qwen2ForCausalLM(cfg)
     cfg = t.Qwen3Config(num_attention_heads=4, num_key_value_heads=2, rope_theta=1000000.0,
                         rms_norm_eps=1e-6, use_sliding_window=False, **COMMON)
     return t.Qwen3ForCausalLM(cfg)
@@ -43,7 +49,7 @@ def _prompt_logprobs(path, ids, **kw):
     return llm, out[0].prompt_logprobs[1:]
 
 
-@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen3"])
+@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen2", "qwen3"])
 def test_prompt_logprobs_match_transformers(kind, tmp_path):
     torch.manual_seed(0)
     m = _make(kind).float().eval()
@@ -51,6 +57,8 @@ def test_prompt_logprobs_match_transformers(kind, tmp_path):
         for name, p in m.named_parameters():
             if "q_norm" in name or "k_norm" in name:
                 p.copy_(1 + 0.3 * torch.randn_like(p))
+            elif name.endswith("proj.bias"):
+                p.copy_(0.5 * torch.randn_like(p))
             elif kind != "qwen3" and ("q_proj" in name or "k_proj" in name):
                 p.mul_(6.0)          # (Qwen3's norms already make its attention sharp)
     m.save_pretrained(str(tmp_path), safe_serialization=True)
@@ -62,7 +70,7 @@ def test_prompt_logprobs_match_transformers(kind, tmp_path):
     llm, got = _prompt_logprobs(str(tmp_path), ids[0].tolist())
     cfg = llm.engine.config.model
     assert cfg.rope_theta == (500000.0 if kind == "llama" else 1000000.0)
-    assert cfg.qk_norm == (kind == "qwen3")
+    assert cfg.qk_norm == (kind == "qwen3") and cfg.qkv_bias == (kind == "qwen2")
     assert (cfg.rope_scaling or {}).get("rope_type") == ("llama3" if kind == "llama" else None)
     err = max(abs(a - b) for a, b in zip(ref, got))
     assert err < 0.03, err
@@ -82,7 +90,7 @@ def test_unsupported_architectures_are_refused():
     with pytest.raises(NotImplementedError, match="bias"):
         ModelConfig.from_hf_dict(dict(base, model_type="llama", attention_bias=True))
     with pytest.raises(NotImplementedError, match="model_type"):
-        ModelConfig.from_hf_dict(dict(base, model_type="qwen2"))
+        ModelConfig.from_hf_dict(dict(base, model_type="qwen3_moe"))
     # Qwen3 checkpoints carry a window size that is switched off
     cfg = ModelConfig.from_hf_dict(dict(base, model_type="qwen3", head_dim=64, sliding_window=4096,
                                         use_sliding_window=False, max_position_embeddings=40960))

@@ -96,6 +96,8 @@ def _launch(tp, sp, shift, model_name):
     (1, 2, True, "llama-tiny-swiftkv"),
     (1, 2, True, "qwen3-tiny"),
     (2, 1, False, "qwen3-tiny"),
+    (1, 2, True, "qwen2-tiny"),
+    (2, 1, False, "qwen2-tiny"),
 ])
 def test_parallel_modes_match_single_rank(tp, sp, shift, model):
     ref_llm = _full_weights(model)

@@ -93,7 +93,8 @@ def test_channel_stream_roundtrip():
 
 @pytest.mark.parametrize("model,quant", [("llama-tiny", None), ("llama-tiny-swiftkv", None),
                                           ("llama-tiny", "fp8"), ("qwen3-tiny", None),
-                                          ("qwen3-tiny", "fp8")])
+                                          ("qwen3-tiny", "fp8"), ("qwen2-tiny", None),
+                                          ("qwen2-tiny", "fp8")])
 def test_engine_update_matches_fresh_engine(model, quant):
     kw = {"quantization": quant} if quant else {}
     eng = engine(model, **kw)
