@@ -29,6 +29,7 @@ def model_dir(tmp_path_factory):
     vocab = {"<pad>": 0, "<s>": 1, "</s>": 2, "<unk>": 3, "<|user|>": 4, "<|assistant|>": 5,
              "<|eot|>": 6}
     vocab.update({w: 7 + i for i, w in enumerate(WORDS)})
+    vocab.update({"w%d" % i: i for i in range(len(vocab), 1024)})   # every model output decodes
     tk = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="<unk>"))
     tk.pre_tokenizer = tokenizers.pre_tokenizers.WhitespaceSplit()
     fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tk, bos_token="<s>",
@@ -99,5 +100,30 @@ def test_openai_chat_endpoint_with_a_hugging_face_tokenizer(model_dir):
             body = r.json()
             assert body["usage"]["prompt_tokens"] == 1 + 5 + 1 + 1
             assert isinstance(body["choices"][0]["message"]["content"], str)
+    finally:
+        llm.shutdown()
+
+
+def test_streamed_chat_deltas_add_up_to_the_full_text(model_dir):
+    from fastapi.testclient import TestClient
+    from arcticinference_b200.config import EngineArgs
+    from arcticinference_b200.engine.async_llm import AsyncLLM
+    from arcticinference_b200.entrypoints.openai_server import build_app
+    llm = AsyncLLM.from_engine_args(EngineArgs(model=model_dir, max_model_len=128, block_size=16,
+                                               num_gpu_blocks_override=32), device="cpu").start()
+    body = {"model": "m", "max_tokens": 10, "temperature": 0, "ignore_eos": True,
+            "messages": [{"role": "user", "content": "how are you today ?"}]}
+    try:
+        with TestClient(build_app(llm, "m")) as client:
+            whole = client.post("/v1/chat/completions", json=body).json()
+            text = whole["choices"][0]["message"]["content"]
+            parts = []
+            with client.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as r:
+                for line in r.iter_lines():
+                    if line.startswith("data: {"):
+                        d = json.loads(line[6:])
+                        for c in d.get("choices", []):
+                            parts.append(c.get("delta", {}).get("content") or "")
+            assert "".join(parts) == text and len([p for p in parts if p]) > 1
     finally:
         llm.shutdown()
