@@ -35,12 +35,37 @@ from .. import ops
 from ..config import ModelConfig
 
 
+def _rope_type(rs) -> str:
+    return (rs or {}).get("rope_type", (rs or {}).get("type", "default")) or "default"
+
+
+def rope_attention_factor(cfg: ModelConfig) -> float:
+    """YaRN scales the rotated queries and keys by an attention factor (cos and sin are
+    multiplied by it); here it is folded into the softmax scale as its square. 1 for every
+    other rope type."""
+    rs = cfg.rope_scaling
+    if _rope_type(rs) != "yarn":
+        return 1.0
+    if rs.get("attention_factor") is not None:
+        return float(rs["attention_factor"])
+    factor = float(rs["factor"])
+
+    def mscale(scale, m=1.0):
+        return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+
+    if rs.get("mscale") and rs.get("mscale_all_dim"):
+        return mscale(factor, rs["mscale"]) / mscale(factor, rs["mscale_all_dim"])
+    return mscale(factor)
+
+
 def compute_inv_freq(cfg: ModelConfig, device) -> torch.Tensor:
-    """RoPE inverse frequencies [head_dim/2] fp32, with Llama-3 frequency scaling baked in."""
+    """RoPE inverse frequencies [head_dim/2] fp32, with the checkpoint's frequency scaling
+    (llama3, linear, yarn) baked in."""
     D = cfg.head_dim
     inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
     rs = cfg.rope_scaling
-    if rs and rs.get("rope_type", rs.get("type")) == "llama3":
+    kind = _rope_type(rs)
+    if kind == "llama3":
         factor = rs["factor"]
         lo, hi = rs["low_freq_factor"], rs["high_freq_factor"]
         old = rs["original_max_position_embeddings"]
@@ -50,11 +75,30 @@ def compute_inv_freq(cfg: ModelConfig, device) -> torch.Tensor:
                              torch.where(wavelen < old / hi, inv,
                                          (1 - smooth) * inv / factor + smooth * inv))
         inv = scaled
-    elif rs and rs.get("rope_type", rs.get("type")) == "linear":
+    elif kind == "linear":
         inv = inv / rs["factor"]
-    elif rs and rs.get("rope_type", rs.get("type", "default")) != "default":
-        raise NotImplementedError("rope scaling of type %r (supported: llama3, linear)" %
-                                  rs.get("rope_type", rs.get("type")))
+    elif kind == "yarn":
+        # high frequencies (many rotations within the original context) keep their value,
+        # low ones are interpolated by `factor`, with a linear ramp between the two
+        factor = float(rs["factor"])
+        old = rs.get("original_max_position_embeddings") or cfg.max_position_embeddings
+        fast, slow = rs.get("beta_fast") or 32, rs.get("beta_slow") or 1
+
+        def correction_dim(rotations):
+            return D * math.log(old / (rotations * 2 * math.pi)) / (2 * math.log(cfg.rope_theta))
+
+        low, high = correction_dim(fast), correction_dim(slow)
+        if rs.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, D - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(D // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        keep = 1 - ramp                                   # 1: extrapolate (unscaled frequency)
+        inv = (inv / factor) * (1 - keep) + inv * keep
+    elif kind != "default":
+        raise NotImplementedError("rope scaling of type %r (supported: llama3, linear, yarn)"
+                                  % kind)
     return inv.float().to(device)
 
 
@@ -135,7 +179,7 @@ class LlamaModel:
         self.norm_swiftkv = None
         self.wkv_swiftkv = None   # fused [L_later * 2*hkv*D (per stored block...), H]
         self.inv_freq = compute_inv_freq(cfg, self.device)
-        self.scale = 1.0 / math.sqrt(self.D)
+        self.scale = rope_attention_factor(cfg) ** 2 / math.sqrt(self.D)
         self.n_kv_layers = cfg.num_key_value_layers if cfg.is_swiftkv else cfg.num_hidden_layers
         # fp8 weights with per-token activation scales: the norm and SiLU kernels that feed the
         # linear layers emit quantised rows directly (set by quantize_model_fp8)

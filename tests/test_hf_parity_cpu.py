@@ -1,7 +1,7 @@
 """Checkpoints written by Hugging Face transformers load into the engine and give the same
 next-token distribution as the transformers implementation (fp32, CPU) of the same
 architecture: Llama (llama3 rope scaling, grouped-query attention), Mistral, Qwen2 (QKV bias),
-Qwen3 (per-head query / key norms, head_dim * heads != hidden_size). Teacher-forced: the log-probability of
+Qwen3 (per-head query / key norms, head_dim * heads != hidden_size; also with YaRN scaling). Teacher-forced: the log-probability of
 every prompt token given the tokens before it, so one near-tie cannot derail the comparison.
 Query and key projections are scaled up so that attention is sharp and a wrong rotary
 frequency, a missing norm or a wrong head mapping moves the result by far more than bf16
@@ -37,8 +37,12 @@ def _make(kind: str):
                             **{k: v for k, v in COMMON.items() if k != "head_dim"})
         cfg.hidden_size = 256          # Qwen2 has no head_dim field: hidden_size / heads = 64
         return t.Qwen2ForCausalLM(cfg)
+    extra = {}
+    if kind == "qwen3-yarn":          # the long-context form: prompt positions beyond the original 64
+        extra = dict(rope_scaling={"rope_type": "yarn", "factor": 4.0,
+                                   "original_max_position_embeddings": 64})
     cfg = t.Qwen3Config(num_attention_heads=4, num_key_value_heads=2, rope_theta=1000000.0,
-                        rms_norm_eps=1e-6, use_sliding_window=False, **COMMON)
+                        rms_norm_eps=1e-6, use_sliding_window=False, **extra, **COMMON)
     return t.Qwen3ForCausalLM(cfg)
 
 
@@ -49,7 +53,7 @@ def _prompt_logprobs(path, ids, **kw):
     return llm, out[0].prompt_logprobs[1:]
 
 
-@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen2", "qwen3"])
+@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen2", "qwen3", "qwen3-yarn"])
 def test_prompt_logprobs_match_transformers(kind, tmp_path):
     torch.manual_seed(0)
     m = _make(kind).float().eval()
@@ -59,7 +63,7 @@ def test_prompt_logprobs_match_transformers(kind, tmp_path):
                 p.copy_(1 + 0.3 * torch.randn_like(p))
             elif name.endswith("proj.bias"):
                 p.copy_(0.5 * torch.randn_like(p))
-            elif kind != "qwen3" and ("q_proj" in name or "k_proj" in name):
+            elif not kind.startswith("qwen3") and ("q_proj" in name or "k_proj" in name):
                 p.mul_(6.0)          # (Qwen3's norms already make its attention sharp)
     m.save_pretrained(str(tmp_path), safe_serialization=True)
     ids = torch.randint(2, 1000, (1, 100))
@@ -70,13 +74,15 @@ def test_prompt_logprobs_match_transformers(kind, tmp_path):
     llm, got = _prompt_logprobs(str(tmp_path), ids[0].tolist())
     cfg = llm.engine.config.model
     assert cfg.rope_theta == (500000.0 if kind == "llama" else 1000000.0)
-    assert cfg.qk_norm == (kind == "qwen3") and cfg.qkv_bias == (kind == "qwen2")
-    assert (cfg.rope_scaling or {}).get("rope_type") == ("llama3" if kind == "llama" else None)
+    assert cfg.qk_norm == kind.startswith("qwen3") and cfg.qkv_bias == (kind == "qwen2")
+    assert (cfg.rope_scaling or {}).get("rope_type") == {"llama": "llama3",
+                                                         "qwen3-yarn": "yarn"}.get(kind)
     err = max(abs(a - b) for a, b in zip(ref, got))
     assert err < 0.03, err
 
     # the comparison notices what it is there to notice
-    wrong = {"qk_norm": False} if kind == "qwen3" else {"rope_theta": 10000.0}
+    wrong = {"qk_norm": False} if kind == "qwen3" else \
+        {"rope_scaling": None} if kind == "qwen3-yarn" else {"rope_theta": 10000.0}
     _, off = _prompt_logprobs(str(tmp_path), ids[0].tolist(), hf_overrides=wrong)
     assert max(abs(a - b) for a, b in zip(ref, off)) > 5 * max(err, 0.01)
 
@@ -96,8 +102,8 @@ def test_unsupported_architectures_are_refused():
                                         use_sliding_window=False, max_position_embeddings=40960))
     assert cfg.qk_norm and cfg.head_dim == 64
     from arcticinference_b200.models.llama import compute_inv_freq
-    cfg.rope_scaling = {"rope_type": "yarn", "factor": 4.0}
-    with pytest.raises(NotImplementedError, match="yarn"):
+    cfg.rope_scaling = {"rope_type": "longrope", "factor": 4.0}
+    with pytest.raises(NotImplementedError, match="longrope"):
         compute_inv_freq(cfg, "cpu")
 
 
