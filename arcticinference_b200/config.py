@@ -471,6 +471,11 @@ class EngineConfig:
                 raise NotImplementedError("speculative decoding with pipeline parallelism")
             if p.pipeline_parallel_size > m.num_hidden_layers:
                 raise ValueError("more pipeline stages than decoder layers")
+        if p.data_parallel_size > 1:
+            raise NotImplementedError(
+                "data_parallel_size > 1: replicas are separate engines here; start one server "
+                "per replica, or use the replica pool (python -m arcticinference_b200.server.cli), "
+                "which routes requests over them")
         if p.enable_expert_parallel:
             raise NotImplementedError("enable_expert_parallel: no mixture-of-experts model is "
                                       "implemented, so there is nothing to shard by expert")

@@ -137,3 +137,9 @@ def test_every_end_of_sequence_id_of_the_checkpoint_ends_a_request(tmp_path):
     assert out.token_ids == toks[:stop_at + 1] and out.finish_reason == "stop"
     out = llm.generate(prompt, SamplingParams(temperature=0, max_tokens=8, ignore_eos=True))
     assert out[0].outputs[0].token_ids == toks and out[0].outputs[0].finish_reason == "length"
+
+
+def test_data_parallel_replicas_are_not_one_engine():
+    from arcticinference_b200.config import EngineArgs
+    with pytest.raises(NotImplementedError, match="replica"):
+        EngineArgs(model="llama-tiny", data_parallel_size=2).create_engine_config()
