@@ -1,6 +1,7 @@
 """Engine options that have no test elsewhere: the fp32 LM head (flag and environment
 switch) and per-sample forced lengths for rollout replay."""
 
+import pytest
 import torch
 
 from arcticinference_b200 import LLM, SamplingParams
