@@ -98,6 +98,10 @@ def make_parser() -> argparse.ArgumentParser:
     s.add_argument("--port", type=int, default=8000)
     s.add_argument("--device", default=None)
     s.add_argument("--uvicorn-log-level", default="info")
+    # flags of `vllm serve` command lines that need nothing here: requests are not logged,
+    # no checkpoint code is ever executed, statistics are served on /metrics only
+    for flag in ("--disable-log-requests", "--trust-remote-code", "--disable-log-stats"):
+        s.add_argument(flag, action="store_true", help="accepted for command-line compatibility")
     EngineArgs.add_cli_args(s)
     s.set_defaults(fn=_serve)
     r = sub.add_parser("server", help="replica-pool REST server (/init, /generate, ...)")
