@@ -208,6 +208,12 @@ PRESETS: dict[str, ModelConfig] = {
     "qwen2.5-7b": _llama(28, 3584, 28, 4, 18944, architecture="Qwen2ForCausalLM",
                          model_type="qwen2", qkv_bias=True, vocab_size=152064,
                          rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768),
+    # the reasoning model of the Dynasor examples (a Qwen2 architecture)
+    "deepseek-r1-distill-qwen-1.5b": ModelConfig(
+        architecture="Qwen2ForCausalLM", model_type="qwen2", qkv_bias=True, hidden_size=1536,
+        num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+        intermediate_size=8960, vocab_size=151936, rope_theta=10000.0, rms_norm_eps=1e-6,
+        max_position_embeddings=131072),
     "qwen2-tiny": ModelConfig(architecture="Qwen2ForCausalLM", model_type="qwen2", qkv_bias=True,
                               hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
                               num_key_value_heads=2, head_dim=64, intermediate_size=512,
@@ -596,8 +602,10 @@ class EngineArgs:
                        action="store_false")
         g.add_argument("--max-num-batched-tokens", type=int, default=None)
         g.add_argument("--max-num-seqs", type=int, default=256)
+        g.add_argument("--enable-chunked-prefill", dest="enable_chunked_prefill",
+                       action="store_true", default=True)
         g.add_argument("--no-enable-chunked-prefill", dest="enable_chunked_prefill",
-                       action="store_false", default=True)
+                       action="store_false")
         g.add_argument("--async-scheduling", dest="async_scheduling", action="store_true", default=True,
                        help="queue the next decode step before the previous step's tokens are read")
         g.add_argument("--no-async-scheduling", dest="async_scheduling", action="store_false")
