@@ -56,6 +56,8 @@ class ModelConfig:
     qk_norm: bool = False
     # Qwen2: a bias on the query / key / value projections (none on o_proj or the MLP)
     qkv_bias: bool = False
+    # K/V heads of the checkpoint when ``num_key_value_heads`` was raised (see __post_init__)
+    checkpoint_kv_heads: Optional[int] = None
     # encoder-only fields
     type_vocab_size: int = 2
     layer_norm_eps: float = 1e-12
@@ -74,6 +76,28 @@ class ModelConfig:
     extra_eos_token_ids: tuple = ()
     bos_token_id: Optional[int] = None
     name_or_path: str = ""
+
+    def __post_init__(self):
+        """The attention kernels pack the G = heads / kv_heads query heads of a K/V head into
+        128-row tiles, so G must divide 128. A checkpoint with another ratio (Qwen2.5-7B: 7,
+        14B / 32B: 5, 1.5B: 6) is served with each of its K/V heads stored r times, r the
+        smallest divisor of G that leaves G / r a divisor of 128: the model is the same
+        function, the KV cache is r times larger. ``num_key_value_heads`` is the number of
+        heads stored; ``checkpoint_kv_heads`` keeps the checkpoint's."""
+        hq, hkv = self.num_attention_heads, self.num_key_value_heads
+        if self.is_encoder or hkv <= 0 or hq % hkv:
+            return
+        g = hq // hkv
+        if 128 % g == 0:
+            return
+        r = next(r for r in range(2, g + 1) if g % r == 0 and 128 % (g // r) == 0)
+        if self.checkpoint_kv_heads is None:
+            self.checkpoint_kv_heads = hkv
+        self.num_key_value_heads = hkv * r
+
+    @property
+    def kv_head_replication(self) -> int:
+        return self.num_key_value_heads // (self.checkpoint_kv_heads or self.num_key_value_heads)
 
     @property
     def is_swiftkv(self) -> bool:
@@ -464,6 +488,12 @@ class EngineConfig:
             raise ValueError("num_key_value_heads and tensor_parallel_size must divide evenly")
         if m.is_swiftkv and p.pipeline_parallel_size > 1:
             raise ValueError("SwiftKV models do not support pipeline parallelism")
+        if not m.is_encoder:
+            per_rank = (m.num_attention_heads // ways) // max(1, m.num_key_value_heads // ways)
+            if per_rank < 1 or 128 % per_rank:
+                raise NotImplementedError(
+                    "%d query heads per K/V head on a rank (TP*SP = %d): the attention kernels "
+                    "need a divisor of 128" % (per_rank, ways))
         # Options this engine parses for command-line compatibility but cannot honour are
         # refused here rather than ignored.
         if p.pipeline_parallel_size > 1:

@@ -81,6 +81,20 @@ def _expand_fp8(weight: torch.Tensor, scale: torch.Tensor, inverse_block: bool) 
     return (w * s).to(torch.bfloat16)
 
 
+def expand_kv_heads(cfg, w: torch.Tensor) -> torch.Tensor:
+    """K or V projection rows (or bias) of the checkpoint's heads -> of the heads the engine
+    stores: each head ``cfg.kv_head_replication`` times in a row (a tensor that already has
+    the stored number of heads passes through)."""
+    r, D = cfg.kv_head_replication, cfg.head_dim
+    if r == 1 or w.shape[0] == cfg.num_key_value_heads * D:
+        return w
+    if w.shape[0] != cfg.checkpoint_kv_heads * D:
+        raise ValueError("K/V projection with %d rows; expected %d heads of %d" %
+                         (w.shape[0], cfg.checkpoint_kv_heads, D))
+    heads = w.reshape(cfg.checkpoint_kv_heads, D, *w.shape[1:])
+    return heads.repeat_interleave(r, dim=0).reshape(-1, *w.shape[1:])
+
+
 def _required(model, l: int) -> list[str]:
     later = model.cfg.is_swiftkv and l >= model.n_kv_layers
     sfx = "_swiftkv" if later else ""
@@ -101,8 +115,12 @@ def pack_llama_layer(model, l: int, t: dict) -> None:
     later = model.cfg.is_swiftkv and l >= model.n_kv_layers
     sfx = "_swiftkv" if later else ""
     q = t["self_attn.q_proj%s.weight" % sfx]
-    k = t["self_attn.k_proj%s.weight" % sfx]
-    v = t["self_attn.v_proj%s.weight" % sfx]
+    k = expand_kv_heads(model.cfg, t["self_attn.k_proj%s.weight" % sfx])
+    v = expand_kv_heads(model.cfg, t["self_attn.v_proj%s.weight" % sfx])
+    if model.cfg.qkv_bias:
+        t = dict(t)
+        for name in ("self_attn.k_proj.bias", "self_attn.v_proj.bias"):
+            t[name] = expand_kv_heads(model.cfg, t[name])
     gate, up = t["mlp.gate_proj.weight"], t["mlp.up_proj.weight"]
     blocks = list(model.shard.stored_blocks)
     lw = LlamaLayerWeights()

@@ -21,7 +21,8 @@ def expected_llama_tensors(cfg, dtype: torch.dtype = torch.bfloat16) -> list[Ten
     """Names, full (unsharded) shapes and dtype of the checkpoint tensors a Llama / SwiftKV
     engine consumes."""
     H, D = cfg.hidden_size, cfg.head_dim
-    Hq, Hkv, I = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
+    Hq, I = cfg.num_attention_heads, cfg.intermediate_size
+    Hkv = cfg.checkpoint_kv_heads or cfg.num_key_value_heads     # the trainer's shapes
     dn = dtype_name(dtype)
     out = [TensorMeta("model.embed_tokens.weight", (cfg.vocab_size, H), dn, True),
            TensorMeta("model.norm.weight", (H,), dn, True)]
@@ -44,6 +45,13 @@ def expected_llama_tensors(cfg, dtype: torch.dtype = torch.bfloat16) -> list[Ten
                 TensorMeta(p + "mlp.gate_proj.weight", (I, H), dn),
                 TensorMeta(p + "mlp.up_proj.weight", (I, H), dn),
                 TensorMeta(p + "mlp.down_proj.weight", (H, I), dn)]
+        if cfg.qk_norm:
+            out += [TensorMeta(p + "self_attn.q_norm.weight", (D,), dn),
+                    TensorMeta(p + "self_attn.k_norm.weight", (D,), dn)]
+        if cfg.qkv_bias:
+            out += [TensorMeta(p + "self_attn.q_proj.bias", (Hq * D,), dn),
+                    TensorMeta(p + "self_attn.k_proj.bias", (Hkv * D,), dn),
+                    TensorMeta(p + "self_attn.v_proj.bias", (Hkv * D,), dn)]
     return out
 
 
@@ -107,15 +115,24 @@ def export_llama_state(model) -> Iterator:
                 bk[kvh.start] = blk[h * D:(h + hkv) * D]
                 bv[kvh.start] = blk[(h + hkv) * D:]
             yield p + "self_attn.q_proj.bias", torch.cat(bq, 0)
-            yield p + "self_attn.k_proj.bias", torch.cat([bk[k] for k in sorted(bk)], 0)
-            yield p + "self_attn.v_proj.bias", torch.cat([bv[k] for k in sorted(bv)], 0)
+            yield p + "self_attn.k_proj.bias", _checkpoint_heads(cfg, [bk[k] for k in sorted(bk)])
+            yield p + "self_attn.v_proj.bias", _checkpoint_heads(cfg, [bv[k] for k in sorted(bv)])
         yield p + "self_attn.q_proj%s.weight" % sfx, torch.cat(qs, 0)
-        yield p + "self_attn.k_proj%s.weight" % sfx, torch.cat([ks[k] for k in sorted(ks)], 0)
-        yield p + "self_attn.v_proj%s.weight" % sfx, torch.cat([vs[k] for k in sorted(vs)], 0)
+        yield p + "self_attn.k_proj%s.weight" % sfx, _checkpoint_heads(cfg, [ks[k] for k in sorted(ks)])
+        yield p + "self_attn.v_proj%s.weight" % sfx, _checkpoint_heads(cfg, [vs[k] for k in sorted(vs)])
         yield p + "self_attn.o_proj.weight", _dense(lw.wo)
         yield p + "mlp.gate_proj.weight", torch.cat(gs, 0)
         yield p + "mlp.up_proj.weight", torch.cat(us, 0)
         yield p + "mlp.down_proj.weight", _dense(lw.wdown)
+
+
+def _checkpoint_heads(cfg, parts: list) -> torch.Tensor:
+    """Stored K/V heads back to the checkpoint's: one of every ``kv_head_replication``."""
+    w = torch.cat(parts, 0)
+    r, D = cfg.kv_head_replication, cfg.head_dim
+    if r == 1:
+        return w
+    return w.reshape(-1, r, D, *w.shape[1:])[:, 0].reshape(-1, *w.shape[1:])
 
 
 def requantize_into(dst, dense: torch.Tensor) -> None:

@@ -31,6 +31,14 @@ def _make(kind: str):
         cfg = t.MistralConfig(num_attention_heads=2, num_key_value_heads=1, rope_theta=1000000.0,
                               rms_norm_eps=1e-5, sliding_window=None, **COMMON)
         return t.MistralForCausalLM(cfg)
+    if kind == "qwen2-gqa3":
+        # three query heads per K/V head: not a divisor of the kernels' 128-row tiles, so the
+        # engine stores every K/V head three times
+        cfg = t.Qwen2Config(num_attention_heads=6, num_key_value_heads=2, rope_theta=1000000.0,
+                            rms_norm_eps=1e-6, use_sliding_window=False,
+                            **{k: v for k, v in COMMON.items() if k != "head_dim"})
+        cfg.hidden_size = 384
+        return t.Qwen2ForCausalLM(cfg)
     if kind == "qwen2":
         cfg = t.Qwen2Config(num_attention_heads=4, num_key_value_heads=2, rope_theta=1000000.0,
                             rms_norm_eps=1e-6, use_sliding_window=False,
@@ -53,7 +61,7 @@ def _prompt_logprobs(path, ids, **kw):
     return llm, out[0].prompt_logprobs[1:]
 
 
-@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen2", "qwen3", "qwen3-yarn"])
+@pytest.mark.parametrize("kind", ["llama", "mistral", "qwen2", "qwen2-gqa3", "qwen3", "qwen3-yarn"])
 def test_prompt_logprobs_match_transformers(kind, tmp_path):
     torch.manual_seed(0)
     m = _make(kind).float().eval()
@@ -74,7 +82,23 @@ def test_prompt_logprobs_match_transformers(kind, tmp_path):
     llm, got = _prompt_logprobs(str(tmp_path), ids[0].tolist())
     cfg = llm.engine.config.model
     assert cfg.rope_theta == (500000.0 if kind == "llama" else 1000000.0)
-    assert cfg.qk_norm == kind.startswith("qwen3") and cfg.qkv_bias == (kind == "qwen2")
+    assert cfg.qk_norm == kind.startswith("qwen3") and cfg.qkv_bias == kind.startswith("qwen2")
+    if kind == "qwen2-gqa3":
+        assert (cfg.num_key_value_heads, cfg.checkpoint_kv_heads, cfg.kv_head_replication) == (6, 2, 3)
+        lw = llm.engine.runner.model.layers[0]
+        D = 64
+        assert lw.wqkv.shape[0] == (6 + 6 + 6) * D and lw.bqkv.shape[0] == 18 * D
+        # the trainer-facing view keeps the checkpoint's shapes, and exporting gives them back
+        from arcticinference_b200.server.weight_sync.utils import (expected_llama_tensors,
+                                                                   export_llama_state)
+        shapes = {t.name: tuple(t.shape) for t in expected_llama_tensors(cfg)}
+        assert shapes["model.layers.0.self_attn.k_proj.weight"] == (2 * D, 384)
+        assert shapes["model.layers.1.self_attn.v_proj.bias"] == (2 * D,)
+        back = dict(export_llama_state(llm.engine.runner.model))
+        sd = m.state_dict()
+        for name in ("model.layers.0.self_attn.k_proj.weight", "model.layers.1.self_attn.v_proj.bias",
+                     "model.layers.1.self_attn.q_proj.weight"):
+            assert torch.equal(back[name].float(), sd[name].to(torch.bfloat16).float())
     assert (cfg.rope_scaling or {}).get("rope_type") == {"llama": "llama3",
                                                          "qwen3-yarn": "yarn"}.get(kind)
     err = max(abs(a - b) for a, b in zip(ref, got))
