@@ -212,3 +212,35 @@ def test_transfer_plan_travels_as_validated_json():
         TransferSchedule.from_json(json.dumps(bad))
     with pytest.raises(ValueError):
         TransferSchedule.from_json(json.dumps({"version": 2}))
+
+
+def test_sync_into_an_engine_that_stores_replicated_kv_heads():
+    """Three query heads per K/V head: the engine stores every K/V head three times, the
+    trainer sends (and /weights_info lists) the checkpoint's two."""
+    from arcticinference_b200.models.loader import load_llama_state
+    from arcticinference_b200.server.weight_sync.receiver import engine_weights_info
+    over = {"hf_overrides": {"num_attention_heads": 6, "num_key_value_heads": 2, "hidden_size": 384,
+                             "qkv_bias": True}}
+    eng = engine("llama-tiny", **over)
+    cfg = eng.config.model
+    assert (cfg.num_key_value_heads, cfg.checkpoint_kv_heads) == (6, 2)
+    D = cfg.head_dim
+    state = {}
+    for name, t in random_llama_state(cfg, 77, 0.05, "cpu", torch.bfloat16):
+        if ".k_proj." in name or ".v_proj." in name:          # the trainer's two heads
+            t = t.reshape(2, 3, D, *t.shape[1:])[:, 0].reshape(2 * D, *t.shape[1:]).contiguous()
+        state[name] = t
+    info = {d["name"]: tuple(d["shape"]) for d in engine_weights_info(eng)}
+    assert all(info[n] == tuple(t.shape) for n, t in state.items())
+    before = greedy(eng)
+    p = port()
+    sender = WeightSender(state, device="cpu", direct_names=["model.embed_tokens.weight", "lm_head.weight"])
+    th = sender.start([{"master_addr": "127.0.0.1", "master_port": p, "replica_ids": [0]}],
+                      bucket_size=1 << 20, timeout=60)
+    res = engine_sync_weights(eng, {"master_addr": "127.0.0.1", "master_port": p, "timeout": 60})
+    sender.join(th)
+    assert res["incomplete_layers"] == []
+    ref = engine("llama-tiny", **over)
+    load_llama_state(ref.runner.model, state.items())
+    after = greedy(eng)
+    assert after == greedy(ref) and after != before
