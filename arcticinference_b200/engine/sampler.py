@@ -52,6 +52,43 @@ def apply_grammar_masks(lf: torch.Tensor, sched, rows) -> torch.Tensor:
     return out
 
 
+def apply_penalties(lf: torch.Tensor, sched, rows) -> torch.Tensor:
+    """Repetition / presence / frequency penalties and logit bias on the raw logits (before
+    temperature), for the requests that ask for them. Row j of a request under verification
+    counts the draft tokens before it as generated."""
+    out = lf
+    V = lf.shape[-1]
+    for s, rr in zip(sched, rows):
+        sp = s.request.sampling_params
+        if not rr or not (sp.presence_penalty or sp.frequency_penalty or
+                          sp.repetition_penalty != 1.0 or sp.logit_bias):
+            continue
+        if out is lf:
+            out = lf.clone()
+        req = s.request
+        draft = list(req.spec_token_ids[:s.num_draft]) if s.num_draft else []
+        for j, row in enumerate(rr):
+            generated = [t for t in list(req.output_token_ids) + draft[:j] if 0 <= t < V]
+            x = out[row]
+            if sp.repetition_penalty != 1.0:
+                seen = sorted({t for t in req.prompt_token_ids if 0 <= t < V} | set(generated))
+                if seen:
+                    idx = torch.tensor(seen, dtype=torch.int64, device=x.device)
+                    v = x[idx]
+                    x[idx] = torch.where(v > 0, v / sp.repetition_penalty, v * sp.repetition_penalty)
+            if generated and (sp.presence_penalty or sp.frequency_penalty):
+                ids, counts = np.unique(np.asarray(generated, dtype=np.int64), return_counts=True)
+                idx = torch.from_numpy(ids).to(x.device)
+                cnt = torch.from_numpy(counts.astype(np.float32)).to(x.device)
+                x[idx] -= sp.frequency_penalty * cnt + sp.presence_penalty
+            if sp.logit_bias:
+                keep = [(t, b) for t, b in sp.logit_bias.items() if 0 <= t < V]
+                if keep:
+                    idx = torch.tensor([t for t, _ in keep], dtype=torch.int64, device=x.device)
+                    x[idx] += torch.tensor([b for _, b in keep], dtype=x.dtype, device=x.device)
+    return out
+
+
 def row_seed(request, j: int) -> int:
     """Noise key of the j-th row a request samples in this step: its own seed (or a hash of its
     id) and its token index, so a draw depends neither on the step's other requests nor on the
@@ -69,8 +106,10 @@ def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
     from .. import ops
     B = logits.shape[0]
     dev = logits.device
-    lf = apply_grammar_masks(logits.float(), sched, rows)
+    lf = apply_penalties(logits.float(), sched, rows)
+    lf = apply_grammar_masks(lf, sched, rows)
     temp = np.ones(B, dtype=np.float32)
+    min_p = np.zeros(B, dtype=np.float32)
     top_k = np.zeros(B, dtype=np.int64)
     top_p = np.ones(B, dtype=np.float32)
     draw = np.zeros(B, dtype=np.float32)      # 1: sample, 0: arg-max
@@ -81,10 +120,17 @@ def sample_full(logits: torch.Tensor, sched, rows) -> torch.Tensor:
             temp[row] = max(sp.temperature, 1e-5)
             top_k[row] = sp.top_k
             top_p[row] = sp.top_p
+            min_p[row] = sp.min_p
             draw[row] = 0.0 if sp.greedy else 1.0
             seeds[row] = row_seed(s.request, j)
     lf = ops.topk_topp_mask(lf.contiguous(), torch.from_numpy(temp).to(dev),
                             torch.from_numpy(top_k).to(dev), torch.from_numpy(top_p).to(dev))
+    if min_p.any():
+        # a token stays iff its probability is at least min_p times the most likely one's:
+        # in (scaled) logit space, within ln(min_p) of the row's maximum
+        floor = lf.max(-1, keepdim=True).values + \
+            torch.log(torch.from_numpy(min_p).to(dev).clamp(min=1e-30)).unsqueeze(1)
+        lf = lf.masked_fill(lf < floor, float("-inf"))
     ids, _ = ops.argmax_sample(lf, torch.from_numpy(draw).to(dev), torch.from_numpy(seeds).to(dev))
     return ids
 

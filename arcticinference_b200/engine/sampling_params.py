@@ -14,6 +14,14 @@ class SamplingParams:
     temperature: float = 1.0
     top_p: float = 1.0
     top_k: int = -1
+    min_p: float = 0.0
+    # penalties on tokens already generated (presence: once, frequency: per occurrence) and on
+    # tokens of the prompt or the output (repetition: divides positive logits, multiplies
+    # negative ones); logit_bias adds to the logits of the given token ids
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    logit_bias: Optional[dict] = None
     max_tokens: Optional[int] = 16
     min_tokens: int = 0
     ignore_eos: bool = False
@@ -43,6 +51,12 @@ class SamplingParams:
             raise ValueError("temperature must be >= 0")
         if not 0 < self.top_p <= 1:
             raise ValueError("top_p must be in (0, 1]")
+        if not 0 <= self.min_p <= 1:
+            raise ValueError("min_p must be in [0, 1]")
+        if self.repetition_penalty <= 0:
+            raise ValueError("repetition_penalty must be > 0")
+        if self.logit_bias:
+            self.logit_bias = {int(k): float(v) for k, v in self.logit_bias.items()}
         if self.max_tokens is not None and self.max_tokens < 1:
             raise ValueError("max_tokens must be >= 1")
         if self.max_tokens_n is not None and len(self.max_tokens_n) != self.n:
@@ -57,11 +71,17 @@ class SamplingParams:
     @property
     def needs_full_logits(self) -> bool:
         """True when arg-max / Gumbel-max over raw logits is not enough."""
-        return (self.top_p < 1.0 or self.top_k > 0 or self.logprobs is not None or
+        return (self.top_p < 1.0 or self.top_k > 0 or self.adjusts_logits or
+                self.logprobs is not None or
                 self.prompt_logprobs is not None or
                 self.guided_choice is not None or self.guided_json is not None or
                 self.guided_regex is not None or
                 self.grammar is not None)
+
+    @property
+    def adjusts_logits(self) -> bool:
+        return bool(self.min_p > 0.0 or self.presence_penalty or self.frequency_penalty or
+                    self.repetition_penalty != 1.0 or self.logit_bias)
 
     def clone_for_sample(self, i: int) -> "SamplingParams":
         import copy

@@ -33,6 +33,11 @@ class CompletionRequest(BaseModel):
     temperature: float = 1.0
     top_p: float = 1.0
     top_k: int = -1
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    logit_bias: Optional[dict[str, float]] = None
     n: int = 1
     stream: bool = False
     stop: Optional[Union[str, list[str]]] = None
@@ -64,6 +69,11 @@ class ChatCompletionRequest(BaseModel):
     temperature: float = 1.0
     top_p: float = 1.0
     top_k: int = -1
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    logit_bias: Optional[dict[str, float]] = None
     n: int = 1
     stream: bool = False
     stop: Optional[Union[str, list[str]]] = None
@@ -127,6 +137,9 @@ def _sampling(req, max_tokens) -> SamplingParams:
     lp = getattr(req, "top_logprobs", None) if isinstance(req, ChatCompletionRequest) and req.logprobs \
         else (req.logprobs if not isinstance(req, ChatCompletionRequest) else None)
     return SamplingParams(n=req.n, temperature=req.temperature, top_p=req.top_p, top_k=req.top_k,
+                          min_p=req.min_p, presence_penalty=req.presence_penalty,
+                          frequency_penalty=req.frequency_penalty,
+                          repetition_penalty=req.repetition_penalty, logit_bias=req.logit_bias,
                           max_tokens=max_tokens, stop=req.stop, stop_token_ids=req.stop_token_ids,
                           seed=req.seed, logprobs=lp, ignore_eos=req.ignore_eos,
                           prompt_logprobs=getattr(req, "prompt_logprobs", None),

@@ -117,3 +117,51 @@ def test_kernel_search_replayed_on_the_host():
         assert diff.sum() <= 1, (b, diff.sum())
         same = np.isfinite(got) & np.isfinite(want[b])
         np.testing.assert_allclose(got[same], want[b][same], rtol=1e-6)
+
+
+KW = dict(model="llama-tiny", device="cpu", num_gpu_blocks_override=64, block_size=16, max_model_len=256)
+
+
+def _gen(llm, **sp):
+    from arcticinference_b200 import SamplingParams
+    out = llm.generate([{"prompt_token_ids": list(range(5, 40))}],
+                       SamplingParams(max_tokens=24, ignore_eos=True, **sp))
+    return out[0].outputs[0].token_ids
+
+
+def test_penalties_bias_and_min_p_through_the_engine():
+    from arcticinference_b200 import LLM
+    llm = LLM(**KW)
+    plain = _gen(llm, temperature=0)
+    assert len(set(plain)) < len(plain)                     # a tiny random model repeats itself
+    # a large frequency penalty: no token twice
+    assert len(set(_gen(llm, temperature=0, frequency_penalty=100.0))) == 24
+    assert len(set(_gen(llm, temperature=0, presence_penalty=100.0))) == 24
+    # repetition penalty also covers the prompt: nothing from the prompt, nothing twice
+    rep = _gen(llm, temperature=0, repetition_penalty=1e4)
+    assert len(set(rep)) == 24 and not set(rep) & set(range(5, 40))
+    # neutral values change nothing
+    assert _gen(llm, temperature=0, repetition_penalty=1.0, presence_penalty=0.0, min_p=0.0) == plain
+    # a bias picks the token; a negative one bans the model's favourites
+    assert _gen(llm, temperature=0, logit_bias={"77": 100.0}) == [77] * 24
+    banned = _gen(llm, temperature=0, logit_bias={t: -100.0 for t in set(plain)})
+    assert not set(banned) & set(plain)
+    # min_p = 1 leaves only the most likely token: sampling is greedy decoding
+    assert _gen(llm, temperature=1.0, min_p=1.0, seed=3) == plain
+    # and a small min_p still samples (differs from greedy with this seed)
+    assert _gen(llm, temperature=1.5, min_p=0.001, seed=3) != plain
+
+
+def test_penalty_arithmetic():
+    from types import SimpleNamespace as NS
+    from arcticinference_b200 import SamplingParams
+    from arcticinference_b200.engine.sampler import apply_penalties
+    lf = torch.tensor([[2.0, -2.0, 1.0, 0.5, 0.0, 3.0]])
+    sp = SamplingParams(repetition_penalty=2.0, presence_penalty=0.5, frequency_penalty=0.25,
+                        logit_bias={5: -1.0, 99: 7.0})
+    req = NS(sampling_params=sp, prompt_token_ids=[0, 1], output_token_ids=[2, 2, 3], spec_token_ids=[])
+    out = apply_penalties(lf, [NS(request=req, num_draft=0)], [[0]])
+    # prompt tokens 0, 1 and generated 2, 3: repetition (positive halved, negative doubled);
+    # generated 2 (twice) and 3 (once): presence + frequency; token 5: bias
+    want = [1.0, -4.0, 0.5 - 0.5 - 0.5, 0.25 - 0.5 - 0.25, 0.0, 2.0]
+    assert torch.allclose(out[0], torch.tensor(want)) and torch.equal(lf[0, :2], torch.tensor([2.0, -2.0]))

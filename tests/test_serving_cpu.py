@@ -90,6 +90,15 @@ def test_openai_routes(async_llm, offline_tokens):
     r = client.post("/v1/completions", json=body).json()
     assert r["choices"][0]["token_ids"] == offline_tokens[0]
     assert r["usage"] == {"prompt_tokens": 5, "completion_tokens": 12, "total_tokens": 17}
+    # the OpenAI sampling fields reach the sampler: a bias forces the token, a frequency
+    # penalty forbids repeats, zeros (what client libraries send by default) change nothing
+    r = client.post("/v1/completions", json=dict(body, logit_bias={"77": 100})).json()
+    assert r["choices"][0]["token_ids"] == [77] * 12
+    r = client.post("/v1/completions", json=dict(body, frequency_penalty=100.0)).json()
+    assert len(set(r["choices"][0]["token_ids"])) == 12
+    r = client.post("/v1/completions", json=dict(body, presence_penalty=0, frequency_penalty=0)).json()
+    assert r["choices"][0]["token_ids"] == offline_tokens[0]
+    assert client.post("/v1/completions", json=dict(body, min_p=2.0)).status_code == 400
     # batch of prompts, n samples
     r = client.post("/v1/completions", json=dict(body, prompt=[PROMPTS[0], PROMPTS[2]], n=2,
                                                  temperature=0.5, seed=1)).json()
