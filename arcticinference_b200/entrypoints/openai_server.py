@@ -38,6 +38,8 @@ class CompletionRequest(BaseModel):
     frequency_penalty: float = 0.0
     repetition_penalty: float = 1.0
     logit_bias: Optional[dict[str, float]] = None
+    include_stop_str_in_output: bool = False
+    skip_special_tokens: bool = True
     n: int = 1
     stream: bool = False
     stop: Optional[Union[str, list[str]]] = None
@@ -74,6 +76,8 @@ class ChatCompletionRequest(BaseModel):
     frequency_penalty: float = 0.0
     repetition_penalty: float = 1.0
     logit_bias: Optional[dict[str, float]] = None
+    include_stop_str_in_output: bool = False
+    skip_special_tokens: bool = True
     n: int = 1
     stream: bool = False
     stop: Optional[Union[str, list[str]]] = None
@@ -140,6 +144,8 @@ def _sampling(req, max_tokens) -> SamplingParams:
                           min_p=req.min_p, presence_penalty=req.presence_penalty,
                           frequency_penalty=req.frequency_penalty,
                           repetition_penalty=req.repetition_penalty, logit_bias=req.logit_bias,
+                          include_stop_str_in_output=req.include_stop_str_in_output,
+                          skip_special_tokens=req.skip_special_tokens,
                           max_tokens=max_tokens, stop=req.stop, stop_token_ids=req.stop_token_ids,
                           seed=req.seed, logprobs=lp, ignore_eos=req.ignore_eos,
                           prompt_logprobs=getattr(req, "prompt_logprobs", None),
