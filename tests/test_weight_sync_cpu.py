@@ -3,6 +3,7 @@ update of a live engine (bf16 and fp8, plain and SwiftKV), the reverse direction
 shared-memory hand-over, and the full path through worker and pool."""
 
 import asyncio
+import os
 import threading
 
 import pytest
@@ -244,3 +245,55 @@ def test_sync_into_an_engine_that_stores_replicated_kv_heads():
     load_llama_state(ref.runner.model, state.items())
     after = greedy(eng)
     assert after == greedy(ref) and after != before
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+def test_reference_named_channel_and_helpers(reverse, tmp_path):
+    """The names a trainer written against the reference imports."""
+    import threading
+    from arcticinference_b200.server import (ModelConfig as SM, NCCLEngine, Pipeline, ReplicaPool,  # noqa: F401
+                                             WeightInfo, build_weights_info, ensure_ray)
+    from arcticinference_b200.server.weight_sync import (cleanup_shm, load_spec_checkpoint,
+                                                         load_weights_from_shm, save_weights_to_shm,
+                                                         spec_bucket_size)
+    from arcticinference_b200.utils.safetensors_io import write_safetensors
+    assert ensure_ray() is None
+    g = torch.Generator().manual_seed(1)
+    weights = {"a.weight": torch.randn(300, 70, generator=g).to(torch.bfloat16),
+               "b.bias": torch.randn(70, generator=g), "c": torch.arange(10, dtype=torch.int64)}
+    weights["tied"] = weights["a.weight"]
+    p = port()
+    got, stats = {}, {}
+
+    def recv():
+        eng = NCCLEngine("127.0.0.1", p, rank=1, world_size=2, device="cpu", reverse=reverse, timeout=60)
+        for name, t in eng.receive_weights():
+            got[name] = t if isinstance(t, str) else t.clone()
+        eng.destroy()
+
+    th = threading.Thread(target=recv)
+    th.start()
+    eng = NCCLEngine("127.0.0.1", p, rank=0, world_size=2, device="cpu", bucket_size=16 << 10,
+                     reverse=reverse, timeout=60)
+    stats = eng.send_weights(weights.items())
+    eng.destroy()
+    th.join(60)
+    assert stats["num_tensors"] == 4 and stats["num_buckets"] >= 2
+    for n in ("a.weight", "b.bias", "c"):
+        assert torch.equal(got[n], weights[n])
+    assert got["tied"] == "a.weight" or torch.equal(got["tied"], weights["a.weight"])
+
+    # names, shapes and dtypes from safetensors headers; speculator checkpoints; shm hand-over
+    write_safetensors(str(tmp_path / "model.safetensors"),
+                      {"speculator.head.0.weight": weights["a.weight"], "speculator.ln": weights["b.bias"]})
+    infos = {i.name: i for i in build_weights_info(str(tmp_path))}
+    w = infos["speculator.head.0.weight"]
+    assert tuple(w.shape) == (300, 70) and w.dtype == torch.bfloat16 and w.nbytes == 300 * 70 * 2
+    assert WeightInfo.from_dict(w.to_dict()).shape == w.shape
+    spec = load_spec_checkpoint(str(tmp_path))
+    assert set(spec) == {"head.0.weight", "ln"} and 300 * 70 * 2 <= spec_bucket_size(spec) <= 256 << 20
+    key = "t%d" % p
+    save_weights_to_shm({"x": weights["b.bias"]}, key, shm_dir=str(tmp_path))
+    assert torch.equal(load_weights_from_shm(key, shm_dir=str(tmp_path))["x"], weights["b.bias"])
+    cleanup_shm(key, shm_dir=str(tmp_path))
+    assert not [f for f in os.listdir(tmp_path) if key in f]
