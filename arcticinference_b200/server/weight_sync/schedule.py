@@ -1,4 +1,5 @@
-"""Transfer plan: which tensor travels in which bucket at which offset.
+"""Transfer plans: which trainer rank feeds which serving rank (:class:`SenderSchedule`), and
+which tensor travels in which bucket at which offset (:class:`TransferSchedule`).
 
 Tensors are packed back to back (256-byte aligned) into buckets of at most ``bucket_size``
 bytes, in an order that lets the receiver finish one decoder layer after another (a layer's
@@ -6,7 +7,8 @@ fused weights can be rebuilt and its staging memory released as soon as its last
 has arrived). A tensor larger than a bucket gets a bucket of its own; tensors marked
 ``direct`` skip the buckets and are received straight into the engine's storage. Tied
 tensors (same storage under two names) travel once.
-(reference: arctic_inference/server/weight_sync/schedule.py:54-146.)
+(reference: arctic_inference/server/weight_sync/schedule.py:54-146 for the assignment of
+senders to targets; its bucket packing happens inside the engine, engine.py:86-169.)
 """
 
 from __future__ import annotations
@@ -91,7 +93,13 @@ class TransferSchedule:
         return (1, int(m.group(1)), name) if m else (0, 0, name)
 
     @classmethod
-    def build(cls, metas: Iterable[TensorMeta], bucket_size: int = 256 << 20) -> "TransferSchedule":
+    def build(cls, metas: Iterable[TensorMeta] = (), bucket_size: int = 256 << 20, *more, **kw):
+        """The bucket plan of ``metas``. Called the way the reference's class of this name is
+        (``build(training_sharding, training_gpus, inference_replicas, inference_tp)``), it
+        returns the :class:`SenderSchedule` of that deployment instead."""
+        if isinstance(metas, str) or "training_sharding" in kw:
+            args = ([metas, bucket_size] if isinstance(metas, str) else []) + list(more)
+            return SenderSchedule.build(*args, **kw)
         metas = sorted(metas, key=lambda m: cls.order_key(m.name))
         buckets, direct, aliases = [], [], []
         cur = Bucket()
@@ -171,6 +179,87 @@ class TransferSchedule:
             buckets.append(bk)
         return cls(buckets, [meta(e, True) for e in d["direct"]],
                    [meta(e) for e in d["aliases"]], int(d["bucket_size"]))
+
+
+@dataclass
+class TransferGroup:
+    """One sending trainer rank and the serving ranks it feeds. Every (replica, tp_rank)
+    target has its own two-party channel with the sender."""
+
+    group_id: int
+    sender_train_rank: int
+    targets: list            # (replica_id, tp_rank) pairs
+
+    WORLD_SIZE = 2
+
+    @property
+    def world_size(self) -> int:
+        return self.WORLD_SIZE
+
+    @property
+    def replica_ids(self) -> list:
+        return sorted({r for r, _ in self.targets})
+
+
+@dataclass
+class SenderSchedule:
+    """Which trainer rank sends to which serving rank, fixed once per deployment. Serving rank
+    ``(r, t)`` listens on ``base_port + r * inference_tp + t``.
+
+    ``dp`` (every trainer rank holds the model) and ``fsdp`` (every rank ends up with each
+    gathered parameter) use ``min(training_gpus, targets)`` senders and deal the targets out
+    round-robin. ``zero3`` gathers parameters in a collective that every trainer rank must
+    join, so every rank is a sender (possibly with no target) and, so that no sender walks the
+    parameters twice while a gather is in flight, there must be at least as many trainer ranks
+    as targets."""
+
+    training_sharding: str
+    training_gpus: int
+    inference_replicas: int
+    inference_tp: int
+    groups: list = field(default_factory=list)
+
+    @classmethod
+    def build(cls, training_sharding: str, training_gpus: int, inference_replicas: int,
+              inference_tp: int) -> "SenderSchedule":
+        if training_sharding not in ("dp", "fsdp", "zero3"):
+            raise ValueError("training_sharding must be 'dp', 'fsdp' or 'zero3', not %r"
+                             % (training_sharding,))
+        if min(training_gpus, inference_replicas, inference_tp) < 1:
+            raise ValueError("training_gpus, inference_replicas and inference_tp must be >= 1")
+        targets = [(r, t) for r in range(inference_replicas) for t in range(inference_tp)]
+        if training_sharding == "zero3":
+            if training_gpus < len(targets):
+                raise ValueError("zero3 needs training_gpus (%d) >= inference_replicas * "
+                                 "inference_tp (%d): one target per sender at most"
+                                 % (training_gpus, len(targets)))
+            senders = training_gpus
+        else:
+            senders = min(training_gpus, len(targets))
+        dealt = [targets[i::senders] for i in range(senders)]
+        return cls(training_sharding, training_gpus, inference_replicas, inference_tp,
+                   [TransferGroup(i, i, t) for i, t in enumerate(dealt)])
+
+    def port_for_target(self, replica_id: int, tp_rank: int, base_port: int) -> int:
+        return base_port + replica_id * self.inference_tp + tp_rank
+
+    @property
+    def num_groups(self) -> int:
+        return len(self.groups)
+
+    @property
+    def active_sender_ranks(self) -> list:
+        return [g.sender_train_rank for g in self.groups]
+
+    def targets_of(self, train_rank: int) -> list:
+        """(replica_id, tp_rank) pairs trainer rank ``train_rank`` sends to (possibly none)."""
+        for g in self.groups:
+            if g.sender_train_rank == train_rank:
+                return list(g.targets)
+        return []
+
+    def ports_of(self, train_rank: int, base_port: int) -> list:
+        return [self.port_for_target(r, t, base_port) for r, t in self.targets_of(train_rank)]
 
 
 def find_aliases(named: dict) -> dict:

@@ -79,6 +79,20 @@ class WeightSender:
                     threads.append(th)
         return threads
 
+    def start_ports(self, host: str, ports: Iterable[int], bucket_size: int = 256 << 20,
+                    timeout: float = 120.0, reverse: bool = False) -> list:
+        """One channel per port (a trainer rank's share of a :class:`SenderSchedule`:
+        ``plan.ports_of(train_rank, base_port)``); returns the threads. Call ``join``."""
+        sched = self.build_schedule(bucket_size)
+        self.last_stats = []
+        threads = []
+        for port in ports:
+            th = threading.Thread(target=self._serve, daemon=True,
+                                  args=(host, int(port), sched, timeout, self.last_stats, reverse))
+            th.start()
+            threads.append(th)
+        return threads
+
     def join(self, threads: list) -> list:
         for th in threads:
             th.join()

@@ -297,3 +297,62 @@ def test_reference_named_channel_and_helpers(reverse, tmp_path):
     assert torch.equal(load_weights_from_shm(key, shm_dir=str(tmp_path))["x"], weights["b.bias"])
     cleanup_shm(key, shm_dir=str(tmp_path))
     assert not [f for f in os.listdir(tmp_path) if key in f]
+
+
+def test_sender_schedule_deals_targets_to_trainer_ranks():
+    from arcticinference_b200.server.weight_sync import SenderSchedule, TransferGroup
+    # 8 trainer ranks, 4 replicas of TP 2: one target each
+    s = TransferSchedule.build("fsdp", 8, 4, 2)               # the reference's call
+    assert isinstance(s, SenderSchedule) and s.num_groups == 8
+    assert [g.targets for g in s.groups[:3]] == [[(0, 0)], [(0, 1)], [(1, 0)]]
+    assert s.port_for_target(3, 1, 5000) == 5007 and s.ports_of(7, 5000) == [5007]
+    # 4 trainer ranks for the same 8 targets: two each, round-robin
+    s = SenderSchedule.build("dp", 4, 4, 2)
+    assert [g.targets for g in s.groups] == [[(0, 0), (2, 0)], [(0, 1), (2, 1)],
+                                             [(1, 0), (3, 0)], [(1, 1), (3, 1)]]
+    assert s.groups[2].replica_ids == [1, 3] and s.groups[0].world_size == 2
+    assert s.active_sender_ranks == [0, 1, 2, 3] and s.targets_of(9) == []
+    covered = sorted(t for g in s.groups for t in g.targets)
+    assert covered == [(r, t) for r in range(4) for t in range(2)]
+    # more trainer ranks than targets: dp / fsdp leave the rest idle, zero3 keeps them in step
+    assert SenderSchedule.build("dp", 8, 1, 2).num_groups == 2
+    z = TransferSchedule.build(training_sharding="zero3", training_gpus=8, inference_replicas=1,
+                               inference_tp=2)
+    assert z.num_groups == 8 and [len(g.targets) for g in z.groups] == [1, 1, 0, 0, 0, 0, 0, 0]
+    with pytest.raises(ValueError, match="zero3"):
+        SenderSchedule.build("zero3", 4, 4, 2)
+    with pytest.raises(ValueError, match="training_sharding"):
+        SenderSchedule.build("pp", 4, 4, 2)
+    assert isinstance(s.groups[0], TransferGroup)
+
+
+def test_two_trainer_ranks_feed_two_replicas_by_plan():
+    """Each trainer rank opens the channels the plan gives it; every replica is updated."""
+    from arcticinference_b200.server.weight_sync import SenderSchedule
+    plan = SenderSchedule.build("dp", 2, 2, 1)
+    engines = [engine(), engine()]
+    before = [greedy(e) for e in engines]
+    state = new_state(seed=321)
+    base = port()
+    PORT[0] += 4
+    senders, threads = [], []
+    for rank in plan.active_sender_ranks:
+        s = WeightSender(state, device="cpu")
+        senders.append(s)
+        threads.append(s.start_ports("127.0.0.1", plan.ports_of(rank, base), bucket_size=1 << 20,
+                                     timeout=60))
+    results = [None, None]
+
+    def recv(i):
+        results[i] = engine_sync_weights(engines[i], {"master_addr": "127.0.0.1",
+                                                      "master_port": plan.port_for_target(i, 0, base),
+                                                      "timeout": 60})
+
+    rts = [threading.Thread(target=recv, args=(i,)) for i in range(2)]
+    [t.start() for t in rts]
+    [t.join(60) for t in rts]
+    for s, th in zip(senders, threads):
+        s.join(th)
+    assert all(r["incomplete_layers"] == [] for r in results)
+    after = [greedy(e) for e in engines]
+    assert after[0] == after[1] and after[0] != before[0]
