@@ -54,7 +54,7 @@ def _as_i32(tokens) -> np.ndarray:
 
 
 class SuffixDecodingCache:
-    def __init__(self, max_tree_depth: int = 64, max_cached_requests: int = 100000):
+    def __init__(self, max_tree_depth: int = 64, max_cached_requests: int = -1):
         if max_cached_requests > 0x7FFFFFFF:
             raise ValueError("max_cached_requests must fit in int32")
         self.max_tree_depth = max_tree_depth
