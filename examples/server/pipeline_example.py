@@ -33,6 +33,15 @@ async def main(fake: bool):
     data = [{"doc": "d%d" % (i % 10), "text": "paragraph %d" % i} for i in range(100)]
     res = await summarize.run(data, progress=lambda done, n: None)
     print(len(res), "results;", res[0])
+
+    # the same job in the reference's call shape: one registered task, run by the pipeline,
+    # sampling parameters as keywords, text returned
+    @pipe.task
+    async def title(sample, llm):
+        return await llm.generate(prompt="Title for: " + sample["text"], max_tokens=8, temperature=0.0)
+
+    titles = await pipe.run(data[:10], max_retries=2)
+    print(len(titles), "titles;", titles[0])
     await pool.shutdown()
 
 

@@ -294,6 +294,49 @@ def test_pipeline_retries_and_order():
     run(main())
 
 
+def test_pipeline_in_the_reference_call_shape():
+    """``@pipeline.task`` + ``await pipeline.run(dataset)`` with an LLM handle whose
+    ``generate`` / ``generate_token_ids`` take sampling parameters as keywords."""
+    async def main():
+        pool, _ = _pool(2)
+        await pool.initialize(CFG, num_replicas=2)
+        pipe = Pipeline(pool)
+        pipe.retry_delay = 0.01
+        with pytest.raises(RuntimeError, match="no task"):
+            await pipe.run([1])
+        with pytest.raises(ValueError, match="async"):
+            pipe.task(lambda sample, llm: None)
+        flaky = {"left": 2}
+
+        @pipe.task
+        async def process(sample, llm):
+            if sample["id"] == 1 and flaky["left"] > 0:
+                flaky["left"] -= 1
+                raise RuntimeError("transient")
+            if sample["id"] == 4:
+                raise ValueError("never works")
+            ids = await llm.generate_token_ids(sample["ids"], max_tokens=3)
+            text = await llm.generate(prompt=sample["ids"], max_tokens=3)
+            return {"id": sample["id"], "ids": ids, "text": text}
+
+        data = [{"id": i, "ids": [i, i + 1]} for i in range(6)]
+        res = await pipe.run(data, max_retries=2, show_progress=False)
+        assert [r.get("id") for r in res] == [0, 1, 2, 3, None, 5]
+        assert res[4] == {"__error__": "never works"}
+        assert res[2]["ids"] == dummy_tokens([2, 3], 3) and isinstance(res[2]["text"], str)
+
+        # several pools: the task gets a dict of handles
+        both = Pipeline({"a": pool, "b": pool})
+
+        @both.task
+        async def two(sample, llms):
+            return [await llms[k].generate_token_ids(sample, max_tokens=1) for k in ("a", "b")]
+        out = await both.run([[7, 8]], max_retries=0)
+        assert out[0][0] == out[0][1] == dummy_tokens([7, 8], 1)
+        await pool.shutdown()
+    run(main())
+
+
 def test_rest_api():
     pool, made = _pool(2)
     api.set_backend(pool)
