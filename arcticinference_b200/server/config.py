@@ -35,7 +35,7 @@ class ServerModelConfig(BaseModel):
     tensor_parallel_size: int = 1
     ulysses_sequence_parallel_size: int = 1
     enable_shift_parallel: bool = False
-    shift_parallel_threshold: int = 512
+    shift_parallel_threshold: Optional[int] = None      # None: the engine's default
     max_model_len: int = 32768
     max_num_seqs: int = 1024
     max_num_batched_tokens: Optional[int] = None
@@ -45,6 +45,11 @@ class ServerModelConfig(BaseModel):
     enable_prefix_caching: bool = True
     kv_cache_dtype: Optional[str] = None
     enable_sleep_mode: bool = True
+    enable_expert_parallel: bool = False    # passed on; the engine refuses it (no MoE model)
+    # fields of the reference's schema that need nothing here: no checkpoint code is ever
+    # executed, and replicas are processes pinned to whole GPUs, not Ray actors
+    trust_remote_code: bool = True
+    ray_num_gpus: Optional[float] = None
     use_fca: bool = False
     spec_model: str = ""
     extra_engine_kwargs: dict[str, Any] = Field(default_factory=dict)
@@ -56,7 +61,8 @@ class ServerModelConfig(BaseModel):
         return self.tensor_parallel_size * self.ulysses_sequence_parallel_size
 
     def to_engine_kwargs(self) -> dict[str, Any]:
-        skip = {"use_fca", "spec_model", "extra_engine_kwargs", "extra_env", "gpus_per_replica"}
+        skip = {"use_fca", "spec_model", "extra_engine_kwargs", "extra_env", "gpus_per_replica",
+                "trust_remote_code", "ray_num_gpus"}
         kw = {k: v for k, v in self.model_dump().items() if v is not None and k not in skip}
         kw.update(self.extra_engine_kwargs)
         # the Arctic features are part of this engine, so they are on unless the launcher's or
