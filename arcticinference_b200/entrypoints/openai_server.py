@@ -177,6 +177,14 @@ def build_app(llm: AsyncLLM, served_model_name: Optional[str] = None) -> FastAPI
 
     def chat_prompt_ids(req) -> list:
         msgs = [{"role": m.role, "content": _message_text(m)} for m in req.messages]
+        extra = {}
+        if getattr(req, "continue_final_message", False):
+            # the last message is a partial assistant turn that the model goes on writing
+            if getattr(req, "add_generation_prompt", True) and "add_generation_prompt" in req.model_fields_set:
+                raise HTTPException(status_code=400, detail="continue_final_message and "
+                                    "add_generation_prompt exclude each other")
+            extra["continue_final_message"] = True
+            return chat_token_ids(tok, msgs, False, **extra)
         return chat_token_ids(tok, msgs, getattr(req, "add_generation_prompt", True))
 
     # ------------------------------------------------------------------ plumbing

@@ -28,9 +28,12 @@ class ByteTokenizer:
                    if not (skip_special_tokens and i < self._offset))
         return bs.decode("utf-8", errors="replace")
 
-    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True, **kw):
+    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True,
+                            continue_final_message=False, **kw):
         text = "".join("<|%s|>\n%s\n" % (m["role"], m["content"]) for m in messages)
-        if add_generation_prompt:
+        if continue_final_message:
+            text = text[:-1]          # the last turn stays open
+        elif add_generation_prompt:
             text += "<|assistant|>\n"
         return self.encode(text) if tokenize else text
 

@@ -127,3 +127,12 @@ def test_streamed_chat_deltas_add_up_to_the_full_text(model_dir):
             assert "".join(parts) == text and len([p for p in parts if p]) > 1
     finally:
         llm.shutdown()
+
+
+def test_continue_final_message_leaves_the_last_turn_open():
+    from arcticinference_b200.utils.tokenizer import ByteTokenizer
+    tok = ByteTokenizer(1024)
+    msgs = [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "The answer is"}]
+    closed = chat_token_ids(tok, msgs, True)
+    opened = chat_token_ids(tok, msgs, False, continue_final_message=True)
+    assert tok.decode(opened).endswith("The answer is") and len(opened) < len(closed)

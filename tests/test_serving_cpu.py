@@ -119,6 +119,13 @@ def test_openai_routes(async_llm, offline_tokens):
     with client.stream("POST", "/v1/chat/completions", json=dict(chat, stream=True)) as resp:
         chunks = [json.loads(l[6:]) for l in resp.iter_lines() if l.startswith("data: {")]
     assert chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+    # an open assistant turn: the model continues it (no generation prompt is appended)
+    open_turn = dict(chat, messages=chat["messages"] + [{"role": "assistant", "content": "So"}])
+    closed = client.post("/v1/chat/completions", json=open_turn).json()["usage"]["prompt_tokens"]
+    cont = client.post("/v1/chat/completions", json=dict(open_turn, continue_final_message=True))
+    assert cont.status_code == 200 and cont.json()["usage"]["prompt_tokens"] < closed
+    assert client.post("/v1/chat/completions", json=dict(open_turn, continue_final_message=True,
+                                                         add_generation_prompt=True)).status_code == 400
     # plumbing
     t = client.post("/tokenize", json={"prompt": "abc"}).json()
     assert client.post("/detokenize", json={"tokens": t["tokens"]}).json()["prompt"] == "abc"
