@@ -581,6 +581,11 @@ class EngineArgs:
         # Sequence parallelism always runs one process per GPU (arctic_inference/vllm/args.py:71-73).
         if self.ulysses_sequence_parallel_size > 1:
             self.distributed_executor_backend = "mp"
+        if self.distributed_executor_backend not in (None, "mp", "external_launcher"):
+            # one process per GPU under torch.distributed is the only executor there is
+            raise NotImplementedError("distributed_executor_backend=%r (ranks are processes "
+                                      "started by serve or torch.distributed.run)"
+                                      % self.distributed_executor_backend)
         if _env_flag("ARCTIC_FP32_LM_HEAD"):
             self.fp32_lm_head = True
 
