@@ -56,6 +56,9 @@ class ModelConfig:
     qk_norm: bool = False
     # Qwen2: a bias on the query / key / value projections (none on o_proj or the MLP)
     qkv_bias: bool = False
+    # attention window of the checkpoint (Mistral v0.1): contexts up to this length see every
+    # earlier token, so they are served; longer ones are refused (no windowed attention kernel)
+    sliding_window: Optional[int] = None
     # K/V heads of the checkpoint when ``num_key_value_heads`` was raised (see __post_init__)
     checkpoint_kv_heads: Optional[int] = None
     # encoder-only fields
@@ -140,8 +143,6 @@ class ModelConfig:
             # part of its architecture and has no flag)
             raise NotImplementedError("linear layers with bias (attention_bias / mlp_bias)")
         window = d.get("sliding_window") if d.get("use_sliding_window", True) else None
-        if window is not None and window < d.get("max_position_embeddings", 4096):
-            raise NotImplementedError("sliding-window attention (sliding_window=%d)" % window)
         # transformers >= 5 writes one ``rope_parameters`` dict (theta, type and the scaling
         # fields together); older checkpoints have ``rope_theta`` beside ``rope_scaling``
         rope = d.get("rope_parameters") or {}
@@ -161,7 +162,7 @@ class ModelConfig:
             max_position_embeddings=d.get("max_position_embeddings", 4096),
             tie_word_embeddings=d.get("tie_word_embeddings", False),
             num_key_value_layers=d.get("num_key_value_layers"),
-            qk_norm=(mt == "qwen3"), qkv_bias=(mt == "qwen2"),
+            qk_norm=(mt == "qwen3"), qkv_bias=(mt == "qwen2"), sliding_window=window,
             type_vocab_size=d.get("type_vocab_size", 2),
             layer_norm_eps=d.get("layer_norm_eps", 1e-12),
             hidden_act=d.get("hidden_act", "silu"),
@@ -488,6 +489,11 @@ class EngineConfig:
             raise ValueError("num_key_value_heads and tensor_parallel_size must divide evenly")
         if m.is_swiftkv and p.pipeline_parallel_size > 1:
             raise ValueError("SwiftKV models do not support pipeline parallelism")
+        if m.sliding_window is not None and self.scheduler.max_model_len > m.sliding_window:
+            raise NotImplementedError(
+                "sliding-window attention: this checkpoint attends to the last %d tokens only; "
+                "contexts up to that length are served (max_model_len=%d asks for more)"
+                % (m.sliding_window, self.scheduler.max_model_len))
         if not m.is_encoder:
             per_rank = (m.num_attention_heads // ways) // max(1, m.num_key_value_heads // ways)
             if per_rank < 1 or 128 % per_rank:
@@ -666,7 +672,8 @@ class EngineArgs:
             raise NotImplementedError("dtype=%r: weights, activations and the KV cache are "
                                       "bfloat16 (the kernels accumulate in fp32)" % self.dtype)
         model.dtype = "bfloat16"
-        max_len = self.max_model_len or min(model.max_position_embeddings, 8192)
+        max_len = self.max_model_len or min(model.max_position_embeddings, 8192,
+                                            model.sliding_window or 8192)
         parallel = ParallelConfig(
             tensor_parallel_size=self.tensor_parallel_size,
             ulysses_sequence_parallel_size=self.ulysses_sequence_parallel_size,

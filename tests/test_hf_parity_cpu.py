@@ -114,9 +114,20 @@ def test_prompt_logprobs_match_transformers(kind, tmp_path):
 def test_unsupported_architectures_are_refused():
     from arcticinference_b200.config import ModelConfig
     base = dict(hidden_size=128, num_attention_heads=4, num_hidden_layers=2)
+    # a windowed checkpoint is served up to its window and refused beyond it
+    from arcticinference_b200.config import EngineArgs
+    import dataclasses
+    win = ModelConfig.from_hf_dict(dict(base, model_type="mistral", sliding_window=64, head_dim=64,
+                                        num_key_value_heads=2, max_position_embeddings=32768))
+    assert win.sliding_window == 64
+
+    def engine_config(max_len):
+        args = EngineArgs(model="llama-tiny", max_model_len=max_len,
+                          hf_overrides={"sliding_window": 64})
+        return args.create_engine_config()
+    assert engine_config(64).scheduler.max_model_len == 64
     with pytest.raises(NotImplementedError, match="sliding-window"):
-        ModelConfig.from_hf_dict(dict(base, model_type="mistral", sliding_window=4096,
-                                      max_position_embeddings=32768))
+        engine_config(65)
     with pytest.raises(NotImplementedError, match="bias"):
         ModelConfig.from_hf_dict(dict(base, model_type="llama", attention_bias=True))
     with pytest.raises(NotImplementedError, match="model_type"):
