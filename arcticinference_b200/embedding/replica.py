@@ -124,10 +124,38 @@ class InferenceServer:
         await self.server.wait_for_termination()
 
 
+def start_metrics_server(engine, port: int, host: str = "0.0.0.0"):
+    """Serve the engine's counters in the Prometheus text format on ``port`` (its own registry;
+    values are read from ``engine.stats`` at scrape time). Returns (server, thread)."""
+    from prometheus_client import CollectorRegistry, start_http_server
+    from prometheus_client.core import CounterMetricFamily, GaugeMetricFamily
+
+    class Collector:
+        def collect(self):
+            st = engine.stats
+            for name, doc in (("requests", "Encode requests served"),
+                              ("sequences", "sequences embedded"), ("tokens", "tokens embedded"),
+                              ("batches", "packed batches run"),
+                              ("h2d_bytes", "bytes copied host to device"),
+                              ("d2h_bytes", "bytes copied device to host")):
+                c = CounterMetricFamily("ab200_embedding_" + name, doc)
+                c.add_metric([], float(getattr(st, name)))
+                yield c
+            g = GaugeMetricFamily("ab200_embedding_busy_seconds", "seconds spent running batches")
+            g.add_metric([], float(st.busy_seconds))
+            yield g
+
+    registry = CollectorRegistry()
+    registry.register(Collector())
+    return start_http_server(port, addr=host, registry=registry)
+
+
 async def serve(args) -> None:
     engine = EmbeddingEngine(args.model, device=args.device,
                              max_num_batched_tokens=args.max_num_batched_tokens,
                              max_num_seqs=args.max_num_seqs, pooling=args.pooling)
+    if getattr(args, "metrics_port", None):
+        start_metrics_server(engine, args.metrics_port, args.host)
     server = InferenceServer(InferenceServicer(engine, args.served_model_name), args.host, args.port)
     await server.start()
     stop = asyncio.Event()
@@ -151,6 +179,8 @@ def make_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-num-batched-tokens", type=int, default=16384)
     ap.add_argument("--max-num-seqs", type=int, default=2048)
     ap.add_argument("--pooling", default=None, choices=[None, "cls", "mean", "last"])
+    ap.add_argument("--metrics-port", type=int, default=0,
+                    help="serve Prometheus metrics on this port (0: off)")
     ap.add_argument("--workers", type=int, default=16, help="accepted for compatibility; the "
                     "server is asynchronous and needs no worker pool")
     return ap

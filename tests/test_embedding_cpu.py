@@ -228,3 +228,22 @@ def test_openai_embeddings_endpoint(tiny_engine):
             assert c.get("/stats").json()["sequences"] >= 5
     finally:
         aeng.stop()
+
+
+def test_replica_metrics_endpoint(tiny_engine):
+    import socket
+    import urllib.request
+    from arcticinference_b200.embedding.replica import start_metrics_server
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server, thread = start_metrics_server(tiny_engine, port, "127.0.0.1")
+    try:
+        before = tiny_engine.stats.sequences
+        tiny_engine.encode([[5, 6, 7], [8, 9]])
+        text = urllib.request.urlopen("http://127.0.0.1:%d/metrics" % port, timeout=10).read().decode()
+        assert "ab200_embedding_sequences_total %.1f" % (before + 2) in text
+        assert "ab200_embedding_tokens_total" in text and "ab200_embedding_busy_seconds" in text
+    finally:
+        server.shutdown()
+        thread.join(5)
