@@ -23,13 +23,17 @@ def _generate(llm):
     return [o.outputs[0].token_ids for o in outs]
 
 
-def _worker(rank, world, port, q):
+def _kw(model):
+    return dict(KW, model=model)
+
+
+def _worker(rank, world, port, q, model="llama-tiny"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                       WORLD_SIZE=str(world))
     sys.path.insert(0, ROOT)
     torch.set_num_threads(1)
     from arcticinference_b200 import LLM
-    llm = LLM(pipeline_parallel_size=world, **KW)
+    llm = LLM(pipeline_parallel_size=world, **_kw(model))
     toks = _generate(llm)
     m, r = llm.engine.runner.model, llm.engine.runner
     info = dict(rank=rank, toks=toks, layers=[i for i, lw in enumerate(m.layers) if lw is not None],
@@ -42,14 +46,15 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_pipeline_stages_match_single_rank(world):
+@pytest.mark.parametrize("world,model", [(2, "llama-tiny"), (3, "llama-tiny"), (2, "qwen3-tiny"),
+                                         (2, "qwen2-tiny")])
+def test_pipeline_stages_match_single_rank(world, model):
     from arcticinference_b200 import LLM
-    want = _generate(LLM(**KW))
+    want = _generate(LLM(**_kw(model)))
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, model)) for r in range(world)]
     for p in procs:
         p.start()
     infos = [_result_or_child_failure(q, procs, 300) for _ in range(world)]
