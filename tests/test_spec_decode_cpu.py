@@ -134,3 +134,14 @@ def test_speculator_checkpoint_round_trip(tmp_path, fmt):
     h = torch.randn(5, 32, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16)
     tok = torch.arange(5, dtype=torch.int64)
     assert torch.equal(src.propose(h, tok, 3), got.propose(h, tok, 3))
+
+
+@pytest.mark.parametrize("model", ["qwen3-tiny", "qwen2-tiny"])
+def test_speculation_preserves_output_on_the_qwen_paths(model):
+    """Verification rows pass through the per-head norms / the QKV bias like any other row."""
+    kw = dict(KW, model=model)
+    want = _tokens(LLM(**kw).generate(PROMPTS, SP))
+    llm = LLM(speculative_config={"method": "arctic", "model": "random", "num_speculative_tokens": 3,
+                                  "enable_suffix_decoding": True}, **kw)
+    assert _tokens(llm.generate(PROMPTS, SP)) == want
+    assert llm.engine.stats["draft_tokens"] > 0 and llm.engine.stats["accepted_tokens"] > 0
