@@ -21,6 +21,13 @@ def test_latency_bench_reports_ttft_and_tpot():
     assert res["mean_ttft_ms"] > 0 and res["mean_tpot_ms"] > 0 and res["output_tokens_per_s"] > 0
 
 
+def test_host_step_cost_counts_every_request():
+    res = _load("host_step_cost").main(["--requests", "24", "--prompt-len", "100", "--steps", "10"])
+    assert res["running_requests"] == 24 and res["steps"] == 10
+    parts = res["schedule_ms"] + res["prepare_ms"] + res["launch_other_ms"] + res["update_ms"] + res["wait_ms"]
+    assert 0 < parts <= res["ms_per_step"] * 1.05
+
+
 def test_json_mode_eval_documents_conform():
     res = _load("json_mode_eval").main(["--in-process", "llama-tiny", "--num-questions", "1",
                                         "--max-tokens", "700", "--engine-arg", "device=cpu",
