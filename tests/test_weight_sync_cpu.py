@@ -27,9 +27,29 @@ from arcticinference_b200.server.worker import InferenceWorker
 PORT = [41200]
 
 
-def port():
-    PORT[0] += 3
-    return PORT[0]
+def port(span: int = 8):
+    """A base port with ``span`` consecutive free ports above it (a transfer to replica r, rank
+    t listens on base + r * ranks + t). Probed by binding, because a fixed number can collide
+    with an ephemeral port some other connection of the machine holds."""
+    import socket
+    base = PORT[0]
+    while True:
+        base += span
+        if base + span >= 60000:
+            base = 20000
+        socks = []
+        try:
+            for p in range(base, base + span):
+                sk = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+                socks.append(sk)
+                sk.bind(("127.0.0.1", p))
+            PORT[0] = base
+            return base
+        except OSError:
+            continue
+        finally:
+            for sk in socks:
+                sk.close()
 
 
 def engine(model="llama-tiny", **kw):
@@ -334,7 +354,6 @@ def test_two_trainer_ranks_feed_two_replicas_by_plan():
     before = [greedy(e) for e in engines]
     state = new_state(seed=321)
     base = port()
-    PORT[0] += 4
     senders, threads = [], []
     for rank in plan.active_sender_ranks:
         s = WeightSender(state, device="cpu")
